@@ -1,0 +1,136 @@
+/*
+ * ncnn_b200.h -- C ABI of the B200 (sm_100a) inference runtime that stands in for
+ * the shared library emitted by hqu-little-boy/ncnn-compiler's `ncnn-compile`.
+ *
+ * The reference product exports, per compiled model, one function
+ *     int <model>(const float *input1, ..., float *output1, ...)
+ * (tools/ncnn-compile.cpp:1108-1162; wrapper built by lib/Transforms/GenerateCAPI/
+ * GenerateCAPI.cpp:975-1090) with status codes 0..5 (tools/ncnn-compile.cpp:955-960),
+ * caller-owned contiguous fp32 [C][H][W] buffers, and loads `.param`/`.bin` in its
+ * front end (lib/Graph/graph.cpp:2129-2333, API include/ncnn-mlir/Graph/graph.hpp:379-380).
+ * This header is what an FFI binds instead: plain pointers and sizes, no C++ types,
+ * no exceptions across the boundary.  There is no CPU path: every entry point that
+ * computes needs a B200 and fails with NCNN_B200_STATUS_RUNTIME otherwise.
+ */
+#ifndef NCNN_B200_H_
+#define NCNN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes.  0..5 keep the meaning of the reference's generated header
+ * (tools/ncnn-compile.cpp:955-960); 6.. are additions of this runtime. */
+#define NCNN_B200_STATUS_SUCCESS 0
+#define NCNN_B200_STATUS_NULL_POINTER 1
+#define NCNN_B200_STATUS_INVALID_SHAPE 2
+#define NCNN_B200_STATUS_CONSTRAINT_VIOLATION 3
+#define NCNN_B200_STATUS_SHAPE_OVERFLOW 4
+#define NCNN_B200_STATUS_OUTPUT_CAPACITY 5
+#define NCNN_B200_STATUS_RUNTIME 6  /* CUDA error, out of memory, no device */
+#define NCNN_B200_STATUS_TIMEOUT 7  /* a bounded device-side wait gave up */
+#define NCNN_B200_STATUS_LOAD 8     /* .param/.bin rejected or layer unsupported */
+
+/* Accuracy modes of fp32 contractions (Convolution, InnerProduct, Gemm). */
+#define NCNN_B200_FP32_SPLIT 0 /* tensor cores, 3xTF32 split operands, ~1e-5 relative */
+#define NCNN_B200_TF32 1       /* tensor cores, single TF32 pass, ~1e-3 relative     */
+#define NCNN_B200_FP32_CUDA 2  /* CUDA-core fp32 FMA                                 */
+
+typedef struct ncnn_b200_model ncnn_b200_model;
+
+typedef struct ncnn_b200_options {
+  uint32_t struct_size;   /* sizeof(ncnn_b200_options) */
+  int32_t accuracy_mode;  /* NCNN_B200_FP32_SPLIT (default) ... */
+  int32_t device;         /* CUDA device ordinal, -1 = current */
+  int32_t use_cuda_graph; /* 1 = replay a captured graph per batch size (default) */
+  /* Shapes for Input layers that carry no dimensions (the reference takes them from
+   * `--input-shape`, tools/ncnn-compile.cpp:40-198), in Input order: for each, the rank
+   * followed by that many extents, outermost first ([c,h,w]). */
+  int32_t input_shape_count;
+  const int64_t *input_shapes;
+} ncnn_b200_options;
+
+/* Replaces ncnn_graph::Graph::load + the compile pipeline (graph.hpp:379-380,
+ * tools/ncnn-compile.cpp:1824-1888): reads the files, fuses and plans the graph, packs
+ * and uploads the weights.  On failure *out is NULL and ncnn_b200_last_error(NULL)
+ * describes why. */
+int ncnn_b200_load(const char *param_path, const char *bin_path, const ncnn_b200_options *options,
+                   ncnn_b200_model **out);
+void ncnn_b200_free(ncnn_b200_model *model);
+
+/* Message of the last failure on `model`, or of the last failed load when model is
+ * NULL.  The pointer stays valid until the next call on the same model/thread. */
+const char *ncnn_b200_last_error(const ncnn_b200_model *model);
+
+/* Argument order follows the reference: Input-layer tops in layer order, then output
+ * blobs in creation order (lib/Graph/graph.cpp:2311-2324).  Shapes are per image,
+ * outermost first; the return value is the rank (1..3) or -1. */
+int ncnn_b200_input_count(const ncnn_b200_model *model);
+int ncnn_b200_output_count(const ncnn_b200_model *model);
+int ncnn_b200_input_shape(const ncnn_b200_model *model, int index, int64_t dims[3]);
+int ncnn_b200_output_shape(const ncnn_b200_model *model, int index, int64_t dims[3]);
+const char *ncnn_b200_input_name(const ncnn_b200_model *model, int index);
+const char *ncnn_b200_output_name(const ncnn_b200_model *model, int index);
+
+/* One image, host buffers: the body of the reference's exported
+ * `int <model>(const float *input1, ..., float *output1, ...)`
+ * (GenerateCAPI.cpp:1032-1090).  Any NULL pointer returns 1, like the wrapper's
+ * null checks (:1053-1077). */
+int ncnn_b200_run(ncnn_b200_model *model, const float *const *inputs, float *const *outputs);
+
+/* Extension (the reference has no batch dimension, NCNNToTosa.cpp:48-52): n images
+ * back to back per argument; equals n calls of ncnn_b200_run. */
+int ncnn_b200_run_batch(ncnn_b200_model *model, int64_t n, const float *const *inputs,
+                        float *const *outputs);
+
+/* Same with device pointers on the caller's CUDA stream (a cudaStream_t passed as
+ * void*); asynchronous.  ncnn_b200_check_status reports a device-side time-out after
+ * the caller synchronised. */
+int ncnn_b200_run_batch_device(ncnn_b200_model *model, int64_t n, const float *const *inputs,
+                               float *const *outputs, void *stream);
+int ncnn_b200_check_status(ncnn_b200_model *model);
+
+/* Number of kernel launches one run of batch n issues. */
+int ncnn_b200_launch_count(ncnn_b200_model *model, int64_t n);
+
+/* Per-launch timing of batch n (CUDA events, `repeat` runs after one warm-up), written
+ * as text lines "kernel<TAB>layer<TAB>ms<TAB>flops<TAB>bytes".  Returns the number
+ * of bytes needed (excluding the terminator) or a negative status. */
+int64_t ncnn_b200_profile(ncnn_b200_model *model, int64_t n, int repeat, char *buffer,
+                          size_t capacity);
+
+/* Loader only, no GPU needed: text in the layout of the reference's Graph::dump()
+ * (lib/Graph/graph.cpp:2335-2446) plus one FNV-1a hash per weight tensor, or
+ * "ERROR: <message>".  Returns the number of bytes needed (excluding the terminator). */
+int64_t ncnn_b200_describe(const char *param_path, const char *bin_path, char *buffer,
+                           size_t capacity);
+
+/* Writes `<dir>/<name>.h` in the layout of the reference's generated header
+ * (tools/ncnn-compile.cpp:945-1218) and `<dir>/<name>.c`, a stub that exports
+ * `int <name>(const float *input1, ..., float *output1, ...)`, lazily loads the
+ * given .param/.bin through this library and forwards to ncnn_b200_run. */
+int ncnn_b200_emit_stub(const ncnn_b200_model *model, const char *name, const char *param_path,
+                        const char *bin_path, const char *directory);
+
+/* Stand-alone int8 boundary operators on device arrays (cudaStream_t as void*).
+ * Element i belongs to channel (i / inner) % channels; scale/bias counts are 1 or
+ * `channels`.  Replace ConvertQuantize / ConvertDequantize / ConvertRequantize
+ * (lib/Conversion/NCNNToTosa/NCNNToTosa.cpp:4802-4888). */
+int ncnn_b200_op_quantize(const float *x, int8_t *y, int64_t count, int64_t inner, int32_t channels,
+                          const float *scale, int32_t scale_count, void *stream);
+int ncnn_b200_op_dequantize(const int32_t *x, float *y, int64_t count, int64_t inner,
+                            int32_t channels, const float *scale, int32_t scale_count,
+                            const float *bias, int32_t bias_count, void *stream);
+int ncnn_b200_op_requantize(const int32_t *x, int8_t *y, int64_t count, int64_t inner,
+                            int32_t channels, const float *scale_in, int32_t scale_in_count,
+                            const float *scale_out, int32_t scale_out_count, const float *bias,
+                            int32_t bias_count, int32_t relu, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* NCNN_B200_H_ */

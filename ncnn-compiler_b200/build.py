@@ -1,0 +1,50 @@
+"""Builds libncnn_b200.so in-tree: nvcc for sm_100a only, static CUDA runtime."""
+from __future__ import annotations
+
+import os
+import subprocess
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIB = os.path.join(HERE, "libncnn_b200.so")
+SOURCES = ["engine.cu", "tc_gemm.cu", "c_api.cu", "loader.cpp"]
+HEADERS = ["exports.map", "engine.h", "tc_gemm.h", "tc_gemm.cuh", "ptx_sm100.cuh", "kernels.cuh", "loader.h",
+           os.path.join("..", "..", "include", "ncnn_b200.h")]
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "-Xcompiler", "-fPIC"]
+
+
+def needs_build() -> bool:
+    if not os.path.exists(LIB):
+        return True
+    built = os.path.getmtime(LIB)
+    return any(os.path.getmtime(os.path.join(CSRC, f)) > built for f in SOURCES + HEADERS)
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    if not force and not needs_build():
+        return LIB
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    objects = []
+    procs = []
+    for src in SOURCES:
+        obj = os.path.join(CSRC, os.path.splitext(src)[0] + ".o")
+        objects.append(obj)
+        cmd = [nvcc, *NVCC_FLAGS, "-x", "cu", "-c", os.path.join(CSRC, src), "-o", obj]
+        if verbose:
+            cmd.insert(1, "-Xptxas=-v")
+        procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    for src, proc in procs:
+        out, _ = proc.communicate()
+        if proc.returncode != 0:
+            raise RuntimeError(f"nvcc failed on {src}:\n{out}")
+        if verbose and out:
+            print(out)
+    # only the C ABI is exported, as the reference restricts its library to the entry symbols
+    subprocess.check_call([nvcc, "-shared", "-o", LIB, *objects, "-Xlinker", "--no-undefined", "-Xlinker",
+                           "--version-script=" + os.path.join(CSRC, "exports.map")])
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force=True, verbose=True))

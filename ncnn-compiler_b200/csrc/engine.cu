@@ -1,0 +1,1880 @@
+#include "engine.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <functional>
+#include <limits>
+#include <map>
+#include <sstream>
+
+#include "kernels.cuh"
+#include "loader.h"
+#include "tc_gemm.h"
+
+namespace nb {
+namespace {
+
+enum NodeKind { N_CONV, N_DW, N_IP, N_GEMM, N_POOL, N_BINARY, N_UNARY, N_RELAYOUT };
+enum Impl { IMPL_NONE, IMPL_TC, IMPL_DIRECT };
+
+struct Tensor {
+  std::string name;
+  int rank = 0;
+  int c = 1, h = 1, w = 1;  // logical dims (rank 1: w; rank 2: h x w; rank 3: c x h x w)
+  bool i8 = false;
+  int alias = -1;  // Split: shares the storage of another tensor
+  bool is_input = false;
+  int input_index = -1;
+  // storage
+  int fmt = FMT_F32;
+  int Cp = 1, Wp = 1, w_off = 0;  // padded layout of a stem input
+  float input_quant_scale = 0.0f;  // > 0: the input edge quantises to int8
+  size_t plane_elems = 0;          // storage elements per image and plane
+  size_t plane_bytes = 0;          // per image, rounded to 256
+  size_t offset = 0;               // byte offset per image inside the arena
+  int first_def = -1, last_use = -1;
+  bool dedicated = false;          // never shares arena space (padding must stay zero)
+
+  long long logical() const { return static_cast<long long>(c) * h * w; }
+  int planes() const { return fmt == FMT_SPLIT ? 2 : 1; }
+};
+
+struct Node {
+  NodeKind kind = N_UNARY;
+  std::string name, type;
+  std::vector<int> in;
+  int out = -1;
+  // contraction geometry
+  int KH = 1, KW = 1, sh = 1, sw = 1, pt = 0, pl = 0, dh = 1, dw = 1, O = 0, OH = 1, OW = 1;
+  int term = 0;
+  int act = ACT_NONE;
+  float act_a = 0.0f, act_b = 0.0f;
+  int res = -1;
+  int impl = IMPL_NONE;
+  bool stem = false;
+  // host-side parameters
+  std::vector<float> w_f32;   // [O][I][KH][KW] (conv), [O][K] (ip/gemm), [C][KH][KW] (dw)
+  std::vector<int8_t> w_i8;
+  std::vector<float> bias, deq;  // deq = 1/(s_w*s_in) per output channel
+  float s_in = 0.0f, s_out = 0.0f, s_b = 0.0f;
+  bool has_bias = false;
+  int K = 0;                     // contraction length (ip / gemm)
+  float alpha = 1.0f, beta = 1.0f;
+  // pooling / element-wise
+  PoolParams pool{};
+  BinaryParams bin{};
+  UnaryParams un{};
+  std::vector<float> un_scale, un_offset;
+  RelayoutParams relayout{};
+  // device-side parameters
+  void* d_w0 = nullptr;
+  void* d_w1 = nullptr;
+  float* d_bias = nullptr;
+  float* d_deq = nullptr;
+  float* d_scale = nullptr;
+  float* d_offset = nullptr;
+  int k_elems = 0;
+  double flops = 0.0;  // per image
+};
+
+struct Step {
+  std::string name, kernel;
+  std::function<cudaError_t(cudaStream_t)> run;
+  double flops = 0.0, bytes = 0.0;
+};
+
+struct Plan {
+  int64_t n = 0;
+  std::vector<Step> steps;
+  std::vector<float*> d_in, d_out;  // staging used by run_host
+  cudaGraphExec_t graph = nullptr;
+  std::vector<const void*> graph_ptrs;  // the edge pointers the graph was captured with
+};
+
+size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+int grid_for(long long work, int block = 256) {
+  const long long g = (work + block - 1) / block;
+  return static_cast<int>(std::max<long long>(1, std::min<long long>(g, 148ll * 32)));
+}
+
+int conv_extent(int in, int k, int s, int d, int p0, int p1) {
+  return 1 + (in + p0 + p1 - ((k - 1) * d + 1)) / s;
+}
+
+void same_pads(int in, int k, int s, int d, bool lower, int* before, int* after) {
+  const int extent = d * (k - 1) + 1;
+  const int out = 1 + (in - 1) / s;
+  const int total = std::max((out - 1) * s + extent - in, 0);
+  *before = lower ? total / 2 + total % 2 : total / 2;
+  *after = total - *before;
+}
+
+int host_quantize(float x, float s) {
+  volatile float v = x * s;
+  volatile float t;
+  float r;
+  if (v >= 0.0f) {
+    t = v + 0.5f;
+    r = std::floor(t);
+  } else {
+    t = v + -0.5f;
+    r = std::ceil(t);
+  }
+  r = std::max(std::min(r, 127.0f), -127.0f);
+  return static_cast<int>(r);
+}
+
+}  // namespace
+
+class EngineImpl {
+ public:
+  ~EngineImpl() {
+    for (auto& kv : plans_) {
+      if (kv.second.graph != nullptr) cudaGraphExecDestroy(kv.second.graph);
+      for (float* p : kv.second.d_in) cudaFree(p);
+      for (float* p : kv.second.d_out) cudaFree(p);
+    }
+    for (void* p : device_allocs_) cudaFree(p);
+    if (arena_ != nullptr) cudaFree(arena_);
+    if (stream_ != nullptr) cudaStreamDestroy(stream_);
+  }
+
+  bool build(const std::string& param, const std::string& bin, const EngineOptions& opt,
+             std::string* err);
+  int run(int64_t n, const float* const* in, float* const* out, bool host, cudaStream_t stream);
+  int profile(int64_t n, int repeat, std::vector<LayerTiming>* out);
+  Plan* plan_for(int64_t n);
+
+  EngineOptions opt_;
+  ModelDef model_;
+  std::vector<Tensor> tensors_;
+  std::vector<Node> nodes_;
+  std::map<std::string, int> by_name_;
+  std::vector<int> inputs_, outputs_;
+  std::string error_;
+  std::map<int64_t, Plan> plans_;
+  std::vector<void*> device_allocs_;
+  uint8_t* arena_ = nullptr;
+  size_t arena_bytes_ = 0;
+  size_t arena_per_image_ = 0;
+  int* d_status_ = nullptr;
+  int sm_count_ = 148;
+  cudaStream_t stream_ = nullptr;
+  bool any_fp32_tc_ = false;
+
+ private:
+  int resolve(int t) const {
+    while (tensors_[t].alias >= 0) t = tensors_[t].alias;
+    return t;
+  }
+  int new_tensor(const std::string& name) {
+    Tensor t;
+    t.name = name;
+    tensors_.push_back(t);
+    by_name_[name] = static_cast<int>(tensors_.size()) - 1;
+    return static_cast<int>(tensors_.size()) - 1;
+  }
+  bool fail(std::string* err, const std::string& msg) {
+    *err = msg;
+    return false;
+  }
+  template <class T>
+  T* upload(const std::vector<T>& v) {
+    if (v.empty()) return nullptr;
+    void* d = nullptr;
+    if (cudaMalloc(&d, v.size() * sizeof(T)) != cudaSuccess) return nullptr;
+    cudaMemcpy(d, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice);
+    device_allocs_.push_back(d);
+    return static_cast<T*>(d);
+  }
+
+  bool import_layers(std::string* err);
+  bool import_conv(const LayerDef& l, bool depthwise, std::string* err);
+  bool import_ip(const LayerDef& l, std::string* err);
+  bool import_gemm(const LayerDef& l, std::string* err);
+  bool import_pool(const LayerDef& l, std::string* err);
+  bool decode_activation(const LayerDef& l, int id_type, int id_params, Node* n, std::string* err);
+  void fold_batchnorm();
+  void fuse();
+  bool choose_impl(std::string* err);
+  bool prepare_weights(std::string* err);
+  void plan_memory();
+  ActRef ref(int tensor, int64_t n) const;
+  bool emit_node(Plan& plan, const Node& node, int64_t n, std::string* err);
+};
+
+// ---------------------------------------------------------------------- import
+bool EngineImpl::decode_activation(const LayerDef& l, int id_type, int id_params, Node* n,
+                                   std::string* err) {
+  // The reference splits a fused activation into its own op and accepts none(0),
+  // ReLU(1) and Sigmoid(4) (lib/Importer/ImportConvolution.cpp:69-78,236-246).  This
+  // runtime takes 0, 1, leaky ReLU (2, one parameter) and clip (3, two parameters);
+  // everything else is rejected.
+  const int64_t type = l.params.get_int(id_type, 0);
+  const std::vector<float>* ap = l.params.get_float_array(id_params);
+  if (type == 0) return true;
+  if (type == 1) {
+    n->act = ACT_RELU;
+    return true;
+  }
+  if (type == 2 && ap != nullptr && ap->size() == 1) {
+    n->act = ACT_LEAKY;
+    n->act_a = (*ap)[0];
+    return true;
+  }
+  if (type == 3 && ap != nullptr && ap->size() == 2) {
+    n->act = ACT_CLIP;
+    n->act_a = (*ap)[0];
+    n->act_b = (*ap)[1];
+    return true;
+  }
+  return fail(err, "layer " + l.name + ": activation_type " + std::to_string(type) +
+                       " is outside the supported path");
+}
+
+bool EngineImpl::import_conv(const LayerDef& l, bool depthwise, std::string* err) {
+  const std::string where = "layer " + l.name + " (" + l.type + "): ";
+  if (l.bottoms.size() != 1 || l.tops.size() != 1) return fail(err, where + "expects one input and one output");
+  const int in = by_name_.at(l.bottoms[0]);
+  const Tensor ti = tensors_[resolve(in)];  // copy: new_tensor() below may reallocate
+  if (ti.rank != 3) return fail(err, where + "convolution input must have [C,H,W] layout");
+  const ParamDict& p = l.params;
+  if (p.get_int(19, 0) != 0) return fail(err, where + "dynamic weights are not supported");
+  Node n;
+  n.kind = depthwise ? N_DW : N_CONV;
+  n.name = l.name;
+  n.type = l.type;
+  n.O = static_cast<int>(p.get_int(0, 0));
+  n.KW = static_cast<int>(p.get_int(1, 0));
+  n.KH = static_cast<int>(p.get_int(11, n.KW));
+  n.dw = static_cast<int>(p.get_int(2, 1));
+  n.dh = static_cast<int>(p.get_int(12, n.dw));
+  n.sw = static_cast<int>(p.get_int(3, 1));
+  n.sh = static_cast<int>(p.get_int(13, n.sw));
+  int pl = static_cast<int>(p.get_int(4, 0));
+  int pr = static_cast<int>(p.get_int(15, pl));
+  int pt = static_cast<int>(p.get_int(14, pl));
+  int pb = static_cast<int>(p.get_int(16, pt));
+  n.has_bias = p.get_int(5, 0) == 1;
+  n.term = static_cast<int>(p.get_int(8, 0));
+  if (n.dw <= 0 || n.dh <= 0 || n.sw <= 0 || n.sh <= 0) return fail(err, where + "stride and dilation must be positive");
+  if (p.get_float(18, 0.0f) != 0.0f) return fail(err, where + "non-zero pad_value is not supported");
+  if (!decode_activation(l, 9, 10, &n, err)) return false;
+  const bool same_u = pl == -233 && pr == -233 && pt == -233 && pb == -233;
+  const bool same_l = pl == -234 && pr == -234 && pt == -234 && pb == -234;
+  if (same_u || same_l) {
+    // NormalizeNCNN.cpp:30-50: SAME padding becomes explicit pads, output = ceil(in/stride)
+    same_pads(ti.h, n.KH, n.sh, n.dh, same_l, &pt, &pb);
+    same_pads(ti.w, n.KW, n.sw, n.dw, same_l, &pl, &pr);
+  } else if (pl < 0 || pr < 0 || pt < 0 || pb < 0) {
+    return fail(err, where + "convolution padding has unsupported value");
+  }
+  if (ti.h + pt + pb < (n.KH - 1) * n.dh + 1) return fail(err, where + "convolution kernel exceeds padded input height");
+  if (ti.w + pl + pr < (n.KW - 1) * n.dw + 1) return fail(err, where + "convolution kernel exceeds padded input width");
+  n.pt = pt;
+  n.pl = pl;
+  n.OH = conv_extent(ti.h, n.KH, n.sh, n.dh, pt, pb);
+  n.OW = conv_extent(ti.w, n.KW, n.sw, n.dw, pl, pr);
+  const size_t expected = 1 + (n.has_bias ? 1 : 0) + (n.term ? 2 : 0) + (n.term > 100 ? 1 : 0);
+  if (l.weights.size() != expected) return fail(err, where + "weights are missing (was a .bin supplied?)");
+  const WeightTensor& wt = l.weights[0];
+  const int I = static_cast<int>(wt.shape[1]);
+  if (depthwise) {
+    const int group = static_cast<int>(p.get_int(7, 1));
+    if (!(group == ti.c && n.O == ti.c && I == 1))
+      return fail(err, where + "only pure depthwise (group == channels == num_output) is supported");
+  } else if (I != ti.c) {
+    return fail(err, where + "convolution input channels do not match weight channels");
+  }
+  if (n.term == 0 && wt.type == WeightType::kI8) return fail(err, where + "non-quantized convolution weight cannot be i8");
+  if (n.term != 0 && wt.type == WeightType::kF16) return fail(err, where + "quantized convolution weight must be f32 or i8");
+  if (ti.i8 && n.term == 0) return fail(err, where + "non-quantized convolution input must be f32");
+  size_t wi = 1;
+  if (n.has_bias) n.bias = l.weights[wi++].as_f32();
+  if (n.term != 0) {
+    std::vector<float> ws = l.weights[wi++].as_f32();
+    n.s_in = l.weights[wi++].as_f32()[0];
+    if (n.term > 100) n.s_out = l.weights[wi++].as_f32()[0];
+    if (ws.size() == 1 && n.O > 1) ws.assign(n.O, ws[0]);
+    for (float s : ws)
+      if (!(s >= 0.0f) || !std::isfinite(s)) return fail(err, where + "int8 scales must be finite and non-negative");
+    if (!(n.s_in > 0.0f) || (n.term > 100 && !(n.s_out > 0.0f))) return fail(err, where + "int8 activation scales must be positive");
+    // dequantizeAccumulator (NCNNToTosa.cpp:577-596): r = 1/(s_w*s_in), 0 where s_w == 0
+    n.deq.resize(n.O);
+    for (int o = 0; o < n.O; ++o) {
+      volatile float combined = ws[o] * n.s_in;
+      n.deq[o] = ws[o] == 0.0f ? 0.0f : 1.0f / combined;
+    }
+    if (wt.type == WeightType::kI8) {
+      n.w_i8.assign(wt.as_i8(), wt.as_i8() + wt.count());
+    } else {
+      // quantizeConstantToI8 (NCNNToTosa.cpp:234-301): per output channel
+      const std::vector<float> wf = wt.as_f32();
+      const size_t row = wf.size() / n.O;
+      n.w_i8.resize(wf.size());
+      for (size_t i = 0; i < wf.size(); ++i)
+        n.w_i8[i] = static_cast<int8_t>(host_quantize(wf[i], ws[i / row]));
+    }
+  } else {
+    n.w_f32 = wt.as_f32();
+  }
+  n.in = {in};
+  n.out = new_tensor(l.tops[0]);
+  Tensor& to = tensors_[n.out];
+  to.rank = 3;
+  to.c = n.O;
+  to.h = n.OH;
+  to.w = n.OW;
+  to.i8 = n.term > 100;
+  if (to.i8 && n.act != ACT_NONE && n.act != ACT_RELU)
+    return fail(err, where + "only ReLU can follow an int8 result");
+  n.flops = 2.0 * n.OH * n.OW * n.O * (depthwise ? 1 : ti.c) * n.KH * n.KW;
+  nodes_.push_back(std::move(n));
+  return true;
+}
+
+bool EngineImpl::import_ip(const LayerDef& l, std::string* err) {
+  const std::string where = "layer " + l.name + " (InnerProduct): ";
+  if (l.bottoms.size() != 1 || l.tops.size() != 1) return fail(err, where + "expects one input and one output");
+  const int in = by_name_.at(l.bottoms[0]);
+  const Tensor ti = tensors_[resolve(in)];  // copy: new_tensor() below may reallocate
+  const ParamDict& p = l.params;
+  Node n;
+  n.kind = N_IP;
+  n.name = l.name;
+  n.type = l.type;
+  n.O = static_cast<int>(p.get_int(0, 0));
+  n.has_bias = p.get_int(1, 0) == 1;
+  n.term = static_cast<int>(p.get_int(8, 0));
+  if (!decode_activation(l, 9, 10, &n, err)) return false;
+  const size_t expected = 1 + (n.has_bias ? 1 : 0) + (n.term ? 2 : 0);
+  if (l.weights.size() != expected) return fail(err, where + "weights are missing (was a .bin supplied?)");
+  const WeightTensor& wt = l.weights[0];
+  n.K = static_cast<int>(wt.shape[1]);
+  if (ti.i8) return fail(err, where + "quantized InnerProduct input must be f32");
+  // NCNNOps.cpp:1247-1312: static form flattens any input with numel == K; the
+  // rank-2 form [M,K] -> [M,O] keeps the rows.
+  bool rows = false;
+  if (ti.rank == 2 && ti.w == n.K && ti.logical() != n.K) {
+    rows = true;
+  } else if (ti.logical() != n.K) {
+    return fail(err, where + "input element count does not match the weight");
+  }
+  if (n.term == 0 && wt.type == WeightType::kI8) return fail(err, where + "InnerProduct kernel element type does not match scale term");
+  size_t wi = 1;
+  if (n.has_bias) n.bias = l.weights[wi++].as_f32();
+  if (n.term != 0) {
+    std::vector<float> ws = l.weights[wi++].as_f32();
+    n.s_in = l.weights[wi++].as_f32()[0];
+    if (!(n.s_in > 0.0f)) return fail(err, where + "int8 activation scale must be positive");
+    n.deq.resize(n.O);
+    for (int o = 0; o < n.O; ++o) {
+      volatile float combined = ws[o] * n.s_in;
+      n.deq[o] = ws[o] == 0.0f ? 0.0f : 1.0f / combined;
+    }
+    if (wt.type == WeightType::kI8) {
+      n.w_i8.assign(wt.as_i8(), wt.as_i8() + wt.count());
+    } else {
+      const std::vector<float> wf = wt.as_f32();
+      n.w_i8.resize(wf.size());
+      for (size_t i = 0; i < wf.size(); ++i)
+        n.w_i8[i] = static_cast<int8_t>(host_quantize(wf[i], ws[i / n.K]));
+    }
+  } else {
+    n.w_f32 = wt.as_f32();
+  }
+  n.in = {in};
+  n.out = new_tensor(l.tops[0]);
+  Tensor& to = tensors_[n.out];
+  if (rows) {
+    to.rank = 2;
+    to.h = ti.h;
+    to.w = n.O;
+  } else {
+    to.rank = 1;
+    to.w = n.O;
+  }
+  n.flops = 2.0 * (rows ? ti.h : 1) * n.K * n.O;
+  nodes_.push_back(std::move(n));
+  return true;
+}
+
+bool EngineImpl::import_gemm(const LayerDef& l, std::string* err) {
+  const std::string where = "layer " + l.name + " (Gemm): ";
+  const ParamDict& p = l.params;
+  if (l.bottoms.size() != 1 || l.weights.empty())
+    return fail(err, where + "only dynamic-A, transposed constant-B Gemm with optional row bias and optional int8 B is supported");
+  const int in = by_name_.at(l.bottoms[0]);
+  const Tensor ti = tensors_[resolve(in)];  // copy: new_tensor() below may reallocate
+  Node n;
+  n.kind = N_GEMM;
+  n.name = l.name;
+  n.type = l.type;
+  n.alpha = p.get_float(0, 1.0f);
+  n.beta = p.get_float(1, 1.0f);
+  n.O = static_cast<int>(p.get_int(8, 0));
+  n.K = static_cast<int>(p.get_int(9, 0));
+  n.term = static_cast<int>(p.get_int(18, 0));
+  if (ti.rank != 2 || ti.w != n.K) return fail(err, where + "A must be a rank-2 [M,K] tensor");
+  const WeightTensor& wt = l.weights[0];
+  size_t wi = 1;
+  if (p.get_int(10, 0) == 4) {
+    n.has_bias = true;
+    n.bias = l.weights[wi++].as_f32();
+    // reference order: y = (A*B^T + beta*C) * alpha; beta*C is one fp32 product
+    for (float& b : n.bias) {
+      volatile float t = b * n.beta;
+      b = t;
+    }
+  }
+  if (n.term != 0) {
+    n.s_b = l.weights[wi++].as_f32()[0];
+    if (wt.type == WeightType::kI8) {
+      n.w_i8.assign(wt.as_i8(), wt.as_i8() + wt.count());
+    } else {
+      const std::vector<float> wf = wt.as_f32();
+      n.w_i8.resize(wf.size());
+      for (size_t i = 0; i < wf.size(); ++i) n.w_i8[i] = static_cast<int8_t>(host_quantize(wf[i], n.s_b));
+    }
+  } else {
+    if (wt.type == WeightType::kI8) return fail(err, where + "int8 B requires int8_scale_term");
+    n.w_f32 = wt.as_f32();
+  }
+  n.in = {in};
+  n.out = new_tensor(l.tops[0]);
+  Tensor& to = tensors_[n.out];
+  to.rank = 2;
+  to.h = ti.h;
+  to.w = n.O;
+  n.flops = 2.0 * ti.h * n.K * n.O;
+  nodes_.push_back(std::move(n));
+  return true;
+}
+
+bool EngineImpl::import_pool(const LayerDef& l, std::string* err) {
+  const std::string where = "layer " + l.name + " (Pooling): ";
+  const int in = by_name_.at(l.bottoms[0]);
+  const Tensor ti = tensors_[resolve(in)];  // copy: new_tensor() below may reallocate
+  if (ti.rank != 3) return fail(err, where + "pooling input must have [C,H,W] layout");
+  const ParamDict& p = l.params;
+  const int kind = static_cast<int>(p.get_int(0, 0));
+  int kw = static_cast<int>(p.get_int(1, 0)), kh = static_cast<int>(p.get_int(11, kw));
+  int sw = static_cast<int>(p.get_int(2, 1)), sh = static_cast<int>(p.get_int(12, sw));
+  int pl = static_cast<int>(p.get_int(3, 0)), pr = static_cast<int>(p.get_int(14, pl));
+  int pt = static_cast<int>(p.get_int(13, pl)), pb = static_cast<int>(p.get_int(15, pt));
+  const int global = static_cast<int>(p.get_int(4, 0));
+  const int mode = static_cast<int>(p.get_int(5, 0));
+  if (kind != 0 && kind != 1) return fail(err, where + "pooling kind or boolean mode parameter is invalid");
+  if (mode < 0 || mode > 3) return fail(err, where + "pooling pad_mode must be in [0, 3]");
+  if (p.get_int(7, 0) != 0) return fail(err, where + "adaptive pooling is outside the supported path");
+  if (ti.i8 && kind != 0) return fail(err, where + "signed i8 pooling only supports maximum");
+  Node n;
+  n.kind = N_POOL;
+  n.name = l.name;
+  n.type = l.type;
+  n.in = {in};
+  n.out = new_tensor(l.tops[0]);
+  Tensor& to = tensors_[n.out];
+  to.i8 = ti.i8;
+  PoolParams& pp = n.pool;
+  pp.kind = kind;
+  pp.H = ti.h;
+  pp.W = ti.w;
+  pp.C = ti.c;
+  if (global) {
+    // ImportPooling.cpp:71-77: pads and include_pad are ignored, result shape is [C]
+    pp.KH = ti.h;
+    pp.KW = ti.w;
+    pp.sh = pp.sw = 1;
+    pp.pt = pp.pl = 0;
+    pp.OH = pp.OW = 1;
+    to.rank = 1;
+    to.w = ti.c;
+  } else {
+    if (kw <= 0 || kh <= 0 || sw <= 0 || sh <= 0) return fail(err, where + "kernel and stride must be positive");
+    if (pl < 0 || pr < 0 || pt < 0 || pb < 0) return fail(err, where + "padding must be non-negative");
+    if (p.get_int(6, 0) == 1 && kind == 1 && (pl || pr || pt || pb))
+      return fail(err, where + "avgpool_count_include_pad=1 with padding is rejected, as the reference's strict gate does");
+    auto extent = [&](int inp, int k, int s, int p0, int p1) {
+      // inferRegularDimension (NCNNOps.cpp:488-531)
+      if (mode == 2 || mode == 3) return 1 + (inp - 1) / s;
+      const int num = inp + p0 + p1;
+      if (mode == 0) {
+        const int diff = num - k;
+        return (diff % s == 0 ? 1 : 2) + diff / s;
+      }
+      return 1 + (num - k) / s;
+    };
+    if (mode == 2 || mode == 3) {
+      same_pads(ti.h, kh, sh, 1, mode == 3, &pt, &pb);
+      same_pads(ti.w, kw, sw, 1, mode == 3, &pl, &pr);
+    } else if (ti.h + pt + pb < kh || ti.w + pl + pr < kw) {
+      return fail(err, where + "kernel exceeds padded input");
+    }
+    pp.KH = kh;
+    pp.KW = kw;
+    pp.sh = sh;
+    pp.sw = sw;
+    pp.pt = pt;
+    pp.pl = pl;
+    pp.OH = extent(ti.h, kh, sh, pt, pb);
+    pp.OW = extent(ti.w, kw, sw, pl, pr);
+    to.rank = 3;
+    to.c = ti.c;
+    to.h = pp.OH;
+    to.w = pp.OW;
+  }
+  nodes_.push_back(std::move(n));
+  return true;
+}
+
+bool EngineImpl::import_layers(std::string* err) {
+  size_t next_shape = 0;
+  for (const LayerDef& l : model_.layers) {
+    const std::string where = "layer " + l.name + " (" + l.type + "): ";
+    for (const auto& b : l.bottoms)
+      if (by_name_.find(b) == by_name_.end()) return fail(err, where + "unknown bottom blob " + b);
+    const std::string& t = l.type;
+    if (t == "Input") {
+      // ImportInput.cpp:22-80: w/h/c all given (rank 3) or all omitted plus an override
+      const int64_t w = l.params.get_int(0, 0), h = l.params.get_int(1, 0), c = l.params.get_int(2, 0);
+      for (const auto& top : l.tops) {
+        const int id = new_tensor(top);
+        Tensor& x = tensors_[id];
+        if (w == 0 && h == 0 && c == 0) {
+          if (next_shape >= opt_.input_shapes.size())
+            return fail(err, where + "Input dimensions are omitted without an override");
+          const auto& s = opt_.input_shapes[next_shape++];
+          if (s.empty() || s.size() > 3) return fail(err, where + "input shape override must have rank 1..3");
+          for (int64_t d : s)
+            if (d <= 0) return fail(err, where + "input shape override must have positive extents");
+          x.rank = static_cast<int>(s.size());
+          if (x.rank == 3) {
+            x.c = static_cast<int>(s[0]);
+            x.h = static_cast<int>(s[1]);
+            x.w = static_cast<int>(s[2]);
+          } else if (x.rank == 2) {
+            x.h = static_cast<int>(s[0]);
+            x.w = static_cast<int>(s[1]);
+          } else {
+            x.w = static_cast<int>(s[0]);
+          }
+        } else {
+          if (w <= 0 || h <= 0 || c <= 0 || l.params.get_int(11, 0) != 0)
+            return fail(err, where + "Input requires positive w/h/c and unsupported depth must be 0");
+          x.rank = 3;
+          x.c = static_cast<int>(c);
+          x.h = static_cast<int>(h);
+          x.w = static_cast<int>(w);
+        }
+        x.is_input = true;
+        x.input_index = static_cast<int>(inputs_.size());
+        inputs_.push_back(id);
+      }
+    } else if (t == "Convolution") {
+      if (!import_conv(l, false, err)) return false;
+    } else if (t == "ConvolutionDepthWise") {
+      if (!import_conv(l, true, err)) return false;
+    } else if (t == "InnerProduct") {
+      if (!import_ip(l, err)) return false;
+    } else if (t == "Gemm") {
+      if (!import_gemm(l, err)) return false;
+    } else if (t == "Pooling") {
+      if (!import_pool(l, err)) return false;
+    } else if (t == "Split") {
+      const int in = by_name_.at(l.bottoms[0]);
+      for (const auto& top : l.tops) {
+        const int id = new_tensor(top);
+        tensors_[id] = tensors_[resolve(in)];
+        tensors_[id].name = top;
+        tensors_[id].alias = resolve(in);
+        tensors_[id].is_input = false;
+      }
+    } else if (t == "ReLU" || t == "Clip") {
+      const int in = by_name_.at(l.bottoms[0]);
+      const Tensor ti = tensors_[resolve(in)];
+      Node n;
+      n.kind = N_UNARY;
+      n.name = l.name;
+      n.type = t;
+      n.un.op = UN_ACT;
+      if (t == "ReLU") {
+        const float slope = l.params.get_float(0, 0.0f);
+        n.un.inner = 1;
+        n.un.channels = 1;
+        n.un.act = slope == 0.0f ? ACT_RELU : ACT_LEAKY;
+        n.un.act_a = slope;
+        if (ti.i8 && slope != 0.0f) return fail(err, where + "leaky ReLU on an int8 tensor is not supported");
+      } else {
+        // Extension: the reference has no Clip importer (NCNNImporter.cpp:110-160).
+        // ncnn semantics: min(max(x, min), max).
+        if (ti.i8) return fail(err, where + "Clip on an int8 tensor is not supported");
+        n.un.act = ACT_CLIP;
+        n.un.act_a = l.params.get_float(0, -std::numeric_limits<float>::max());
+        n.un.act_b = l.params.get_float(1, std::numeric_limits<float>::max());
+      }
+      n.in = {in};
+      n.out = new_tensor(l.tops[0]);
+      Tensor& to = tensors_[n.out];
+      const std::string keep = to.name;
+      to = ti;
+      to.name = keep;
+      to.alias = -1;
+      to.is_input = false;
+      nodes_.push_back(std::move(n));
+    } else if (t == "Eltwise" || t == "BinaryOp") {
+      Node n;
+      n.kind = N_BINARY;
+      n.name = l.name;
+      n.type = t;
+      const int a = by_name_.at(l.bottoms[0]);
+      const Tensor ta = tensors_[resolve(a)];
+      if (t == "Eltwise") {
+        // ImportOps.cpp:435-506: two inputs, SUM, optional two coefficients
+        const std::vector<float>* coeff = l.params.get_float_array(1);
+        if (l.bottoms.size() != 2 || l.params.get_int(0, 1) != 1 || (coeff != nullptr && coeff->size() != 2) ||
+            (l.params.has(1) && coeff == nullptr))
+          return fail(err, where + "Eltwise supports unweighted or coefficient-weighted SUM of two inputs only");
+        n.bin.op = BIN_ADD;
+        if (coeff != nullptr) {
+          n.bin.scale_a = (*coeff)[0] != 1.0f;
+          n.bin.scale_b = (*coeff)[1] != 1.0f;
+          n.bin.ca = (*coeff)[0];
+          n.bin.cb = (*coeff)[1];
+        }
+      } else {
+        const int64_t op = l.params.get_int(0, 0);
+        if (op != 0 && op != 1 && op != 2 && op != 4) return fail(err, where + "BinaryOp supports add, sub, mul and max");
+        n.bin.op = static_cast<int>(op);
+        n.bin.use_scalar = l.params.get_int(1, 0) == 1;
+        n.bin.scalar = l.params.get_float(2, 0.0f);
+        if (!n.bin.use_scalar && l.bottoms.size() != 2) return fail(err, where + "BinaryOp needs two inputs or a scalar");
+      }
+      n.in = {a};
+      if (!n.bin.use_scalar) {
+        const int b = by_name_.at(l.bottoms[1]);
+        const Tensor& tb = tensors_[resolve(b)];
+        if (tb.rank != ta.rank || tb.c != ta.c || tb.h != ta.h || tb.w != ta.w)
+          return fail(err, where + "broadcasting between different shapes is outside the supported path");
+        if (ta.i8 != tb.i8 || (ta.i8 && n.bin.op != BIN_MAX))
+          return fail(err, where + "int8 operands support only two-input max");
+        n.in.push_back(b);
+      } else if (ta.i8) {
+        return fail(err, where + "int8 operands support only two-input max");
+      }
+      n.out = new_tensor(l.tops[0]);
+      Tensor& to = tensors_[n.out];
+      const std::string keep = to.name;
+      to = ta;
+      to.name = keep;
+      to.alias = -1;
+      to.is_input = false;
+      nodes_.push_back(std::move(n));
+    } else if (t == "BatchNorm") {
+      const int in = by_name_.at(l.bottoms[0]);
+      const Tensor ti = tensors_[resolve(in)];
+      if (l.weights.size() != 4) return fail(err, where + "weights are missing (was a .bin supplied?)");
+      const int ch = static_cast<int>(l.params.get_int(0, 0));
+      // channel axis: the last storage axis for rank 3, dimension 0 otherwise (NCNNToTosa.cpp:4752-4754)
+      if (ti.i8 || (ti.rank == 3 && ti.c != ch) || (ti.rank == 1 && ti.w != ch) || (ti.rank == 2 && ti.h != ch))
+        return fail(err, where + "BatchNorm channel count does not match its input");
+      const float eps = l.params.get_float(1, 0.0f);
+      const std::vector<float> slope = l.weights[0].as_f32(), mean = l.weights[1].as_f32(),
+                               var = l.weights[2].as_f32(), bias = l.weights[3].as_f32();
+      Node n;
+      n.kind = N_UNARY;
+      n.name = l.name;
+      n.type = t;
+      n.un.op = UN_AFFINE;
+      n.un.channels = ch;
+      n.un.inner = ti.rank == 2 ? ti.w : 1;
+      n.un_scale.resize(ch);
+      n.un_offset.resize(ch);
+      for (int c = 0; c < ch; ++c) {
+        // FoldNCNNBatchNorm.cpp:99-124 / ConvertBatchNorm (NCNNToTosa.cpp:4740-4800)
+        volatile float ve = var[c] + eps;
+        const float inv = ve == 0.0f ? 10000.0f : std::pow(static_cast<float>(ve), -0.5f);
+        volatile float scale = slope[c] * inv;
+        volatile float sm = scale * mean[c];
+        n.un_scale[c] = scale;
+        n.un_offset[c] = bias[c] - sm;
+      }
+      n.in = {in};
+      n.out = new_tensor(l.tops[0]);
+      Tensor& to = tensors_[n.out];
+      const std::string keep = to.name;
+      to = ti;
+      to.name = keep;
+      to.alias = -1;
+      to.is_input = false;
+      nodes_.push_back(std::move(n));
+    } else if (t == "Quantize") {
+      const int in = by_name_.at(l.bottoms[0]);
+      const Tensor ti = tensors_[resolve(in)];
+      if (ti.i8 || l.weights.size() != 1) return fail(err, where + "Quantize needs an f32 input and its scale");
+      Node n;
+      n.kind = N_UNARY;
+      n.name = l.name;
+      n.type = t;
+      n.un.op = UN_QUANT;
+      n.un_scale = l.weights[0].as_f32();
+      n.un.nscale = static_cast<int>(n.un_scale.size());
+      n.un.channels = ti.rank == 3 ? ti.c : ti.w;
+      n.un.inner = 1;
+      // ConvertQuantize (NCNNToTosa.cpp:4802-4824): scalar scale or one per channel (dim 0)
+      if (n.un.nscale != 1 && (n.un.nscale != n.un.channels || ti.rank == 2))
+        return fail(err, where + "Quantize scale count must be 1 or the channel count");
+      n.in = {in};
+      n.out = new_tensor(l.tops[0]);
+      Tensor& to = tensors_[n.out];
+      const std::string keep = to.name;
+      to = ti;
+      to.name = keep;
+      to.alias = -1;
+      to.is_input = false;
+      to.i8 = true;
+      nodes_.push_back(std::move(n));
+    } else if (t == "Flatten" || t == "Reshape" || t == "Squeeze" || t == "ExpandDims" || t == "Permute") {
+      const int in = by_name_.at(l.bottoms[0]);
+      const Tensor ti = tensors_[resolve(in)];
+      Node n;
+      n.kind = N_RELAYOUT;
+      n.name = l.name;
+      n.type = t;
+      n.in = {in};
+      n.out = new_tensor(l.tops[0]);
+      Tensor& to = tensors_[n.out];
+      to.i8 = ti.i8;
+      bool transpose = false;
+      if (t == "Flatten") {
+        to.rank = 1;
+        to.w = static_cast<int>(ti.logical());
+      } else if (t == "Reshape") {
+        // ncnn Reshape: 0=w 1=h 2=c, -233 marks an unused dimension, 0 copies, -1 infers
+        int64_t d[3] = {l.params.get_int(0, -233), l.params.get_int(1, -233), l.params.get_int(2, -233)};
+        const int src[3] = {ti.w, ti.rank >= 2 ? ti.h : 1, ti.rank == 3 ? ti.c : 1};
+        int rank = d[2] != -233 ? 3 : (d[1] != -233 ? 2 : 1);
+        long long known = 1;
+        int infer = -1;
+        for (int i = 0; i < rank; ++i) {
+          if (d[i] == 0) d[i] = src[i];
+          if (d[i] == -1) {
+            infer = i;
+          } else {
+            known *= d[i];
+          }
+        }
+        if (infer >= 0) d[infer] = ti.logical() / std::max<long long>(known, 1);
+        long long total = 1;
+        for (int i = 0; i < rank; ++i) total *= d[i];
+        if (total != ti.logical()) return fail(err, where + "Reshape does not preserve the element count");
+        to.rank = rank;
+        to.w = static_cast<int>(d[0]);
+        to.h = rank >= 2 ? static_cast<int>(d[1]) : 1;
+        to.c = rank == 3 ? static_cast<int>(d[2]) : 1;
+      } else if (t == "Squeeze") {
+        std::vector<int> dims;
+        if (ti.rank == 3) dims = {ti.c, ti.h, ti.w};
+        if (ti.rank == 2) dims = {ti.h, ti.w};
+        if (ti.rank == 1) dims = {ti.w};
+        std::vector<int> kept;
+        for (int v : dims)
+          if (v != 1) kept.push_back(v);
+        if (kept.empty()) kept.push_back(1);
+        to.rank = static_cast<int>(kept.size());
+        to.w = kept.back();
+        to.h = to.rank >= 2 ? kept[to.rank - 2] : 1;
+        to.c = to.rank == 3 ? kept[0] : 1;
+      } else if (t == "ExpandDims") {
+        return fail(err, where + "ExpandDims is outside the supported path");
+      } else {  // Permute
+        const int64_t order = l.params.get_int(0, 0);
+        if (ti.rank != 2 || (order != 0 && order != 1)) return fail(err, where + "only rank-2 Permute is supported");
+        to.rank = 2;
+        if (order == 1) {
+          to.h = ti.w;
+          to.w = ti.h;
+          transpose = true;
+        } else {
+          to.h = ti.h;
+          to.w = ti.w;
+        }
+      }
+      RelayoutParams& r = n.relayout;
+      r.count = ti.logical();
+      r.src_rank = ti.rank;
+      r.sc = ti.c;
+      r.sh = ti.h;
+      r.sw = ti.w;
+      r.dst_rank = to.rank;
+      r.dc = to.c;
+      r.dh = to.h;
+      r.dw = to.w;
+      r.transpose2d = transpose ? 1 : 0;
+      nodes_.push_back(std::move(n));
+    } else if (t == "Dequantize" || t == "Requantize") {
+      return fail(err, where + "needs an int32 producer, which no importable layer provides; "
+                               "use the operator entry points instead");
+    } else {
+      return fail(err, where + "layer type is outside the supported path");
+    }
+  }
+  for (const auto& name : model_.outputs) outputs_.push_back(by_name_.at(name));
+  if (inputs_.empty() || outputs_.empty()) return fail(err, "model has no inputs or no outputs");
+  return true;
+}
+
+// ---------------------------------------------------------------------- graph passes
+void EngineImpl::fold_batchnorm() {
+  // FoldNCNNBatchNorm.cpp:55-178: fp32, non-quantised, single-use conv followed by BatchNorm.
+  std::vector<int> uses(tensors_.size(), 0);
+  for (const Node& n : nodes_)
+    for (int t : n.in) ++uses[resolve(t)];
+  for (int o : outputs_) ++uses[resolve(o)];
+  for (size_t k = 0; k < nodes_.size(); ++k) {
+    Node& bn = nodes_[k];
+    if (bn.kind != N_UNARY || bn.un.op != UN_AFFINE) continue;
+    const int src = resolve(bn.in[0]);
+    if (uses[src] != 1) continue;
+    for (size_t j = 0; j < k; ++j) {
+      Node& cv = nodes_[j];
+      if ((cv.kind != N_CONV && cv.kind != N_DW) || resolve(cv.out) != src) continue;
+      if (cv.term != 0 || cv.act != ACT_NONE) break;
+      const size_t row = cv.w_f32.size() / cv.O;
+      for (size_t i = 0; i < cv.w_f32.size(); ++i) {
+        volatile float t = cv.w_f32[i] * bn.un_scale[i / row];
+        cv.w_f32[i] = t;
+      }
+      if (cv.has_bias) {
+        for (int o = 0; o < cv.O; ++o) {
+          volatile float t = cv.bias[o] * bn.un_scale[o];
+          cv.bias[o] = t + bn.un_offset[o];
+        }
+      } else {
+        cv.bias = bn.un_offset;
+        cv.has_bias = true;
+      }
+      cv.out = bn.out;
+      nodes_.erase(nodes_.begin() + k);
+      --k;
+      break;
+    }
+  }
+}
+
+void EngineImpl::fuse() {
+  auto count_uses = [&]() {
+    std::vector<int> uses(tensors_.size(), 0);
+    for (const Node& n : nodes_) {
+      for (int t : n.in) ++uses[resolve(t)];
+      if (n.res >= 0) ++uses[resolve(n.res)];
+    }
+    for (int o : outputs_) ++uses[resolve(o)];
+    return uses;
+  };
+  auto producer_of = [&](int tensor, size_t before) -> int {
+    for (size_t j = 0; j < before && j < nodes_.size(); ++j)
+      if (resolve(nodes_[j].out) == tensor) return static_cast<int>(j);
+    return -1;
+  };
+  auto fuse_activations = [&]() {
+    for (size_t k = 0; k < nodes_.size(); ++k) {
+      Node& u = nodes_[k];
+      if (u.kind != N_UNARY || u.un.op != UN_ACT) continue;
+      const std::vector<int> uses = count_uses();
+      const int src = resolve(u.in[0]);
+      if (uses[src] != 1) continue;
+      const int pj = producer_of(src, k);
+      if (pj < 0) continue;
+      Node& p = nodes_[pj];
+      const bool contraction = p.kind == N_CONV || p.kind == N_DW || p.kind == N_IP;
+      const bool binary = p.kind == N_BINARY;
+      if (!(contraction || binary)) continue;
+      if (contraction && p.act != ACT_NONE) continue;
+      if (binary && p.bin.act != ACT_NONE) continue;
+      if (tensors_[src].i8 && u.un.act != ACT_RELU) continue;
+      if (p.kind == N_GEMM) continue;
+      if (contraction) {
+        p.act = u.un.act;
+        p.act_a = u.un.act_a;
+        p.act_b = u.un.act_b;
+      } else {
+        p.bin.act = u.un.act;
+        p.bin.act_a = u.un.act_a;
+        p.bin.act_b = u.un.act_b;
+      }
+      p.out = u.out;
+      nodes_.erase(nodes_.begin() + k);
+      --k;
+    }
+  };
+  fuse_activations();
+  // residual: Eltwise SUM (no coefficients) of two fp32 tensors, one of which is the
+  // single-use result of a contraction without activation that runs after the other
+  // operand exists.
+  for (size_t k = 0; k < nodes_.size(); ++k) {
+    Node& b = nodes_[k];
+    if (b.kind != N_BINARY || b.bin.op != BIN_ADD || b.bin.use_scalar || b.bin.scale_a || b.bin.scale_b) continue;
+    if (tensors_[resolve(b.in[0])].i8) continue;
+    const std::vector<int> uses = count_uses();
+    int best = -1, other = -1;
+    for (int side = 0; side < 2; ++side) {
+      const int x = resolve(b.in[side]), y = resolve(b.in[1 - side]);
+      if (x == y || uses[x] != 1) continue;
+      const int pj = producer_of(x, k);
+      if (pj < 0) continue;
+      const Node& p = nodes_[pj];
+      if (!(p.kind == N_CONV || p.kind == N_DW) || p.act != ACT_NONE || p.res >= 0) continue;
+      if (tensors_[x].i8) continue;
+      const int py = producer_of(y, k);  // -1: graph input, always available
+      if (py >= pj) continue;
+      if (pj > best) {
+        best = pj;
+        other = y;
+      }
+    }
+    if (best < 0) continue;
+    Node& p = nodes_[best];
+    p.res = other;
+    p.out = b.out;
+    p.act = b.bin.act;
+    p.act_a = b.bin.act_a;
+    p.act_b = b.bin.act_b;
+    nodes_.erase(nodes_.begin() + k);
+    --k;
+  }
+  fuse_activations();
+}
+
+bool EngineImpl::choose_impl(std::string* err) {
+  const bool exact = opt_.accuracy_mode == kAccuracyFp32Cuda;
+  std::vector<int> uses(tensors_.size(), 0);
+  for (const Node& n : nodes_) {
+    for (int t : n.in) ++uses[resolve(t)];
+    if (n.res >= 0) ++uses[resolve(n.res)];
+  }
+  for (int o : outputs_) ++uses[resolve(o)];
+  for (Node& n : nodes_) {
+    if (n.kind == N_CONV) {
+      const Tensor& ti = tensors_[resolve(n.in[0])];
+      const bool i8 = n.term != 0;
+      const int kind = i8 ? GEMM_I8 : GEMM_TF32;
+      const int last_w = -n.pl + (n.OW - 1) * n.sw - (ti.w - 1);
+      const int last_h = -n.pt + (n.OH - 1) * n.sh - (ti.h - 1);
+      const bool geometry_ok = n.sw <= 8 && n.sh <= 8 && n.pl <= 128 && n.pt <= 128 && last_w >= -128 &&
+                               last_w <= 127 && last_h >= -128 && last_h <= 127 &&
+                               (n.KW - 1) * n.dw < 65536 && (n.KH - 1) * n.dh < 65536;
+      n.impl = IMPL_DIRECT;
+      if ((!exact || i8) && geometry_ok) {
+        if (tc_k_elems(kind, ti.c) > 0) {
+          n.impl = IMPL_TC;
+        } else {
+          // stem: few channels, graph input consumed only here -> overlapping-window view
+          const int cp = i8 ? 16 : 4;
+          const int window = i8 ? 128 : 32;
+          if (ti.is_input && uses[resolve(n.in[0])] == 1 && ti.c <= 4 && n.dw == 1 && n.KW * cp <= window &&
+              (n.sw * cp * (i8 ? 1 : 4)) % 16 == 0) {
+            n.impl = IMPL_TC;
+            n.stem = true;
+          }
+        }
+      }
+      if (n.impl == IMPL_TC && !i8) any_fp32_tc_ = true;
+    } else if (n.kind == N_IP || n.kind == N_GEMM) {
+      const bool i8 = n.term != 0;
+      n.impl = IMPL_DIRECT;
+      if (n.kind == N_GEMM && i8) continue;  // per-row dynamic scales: dedicated kernel
+      const int es = i8 ? 1 : 4;
+      if ((!exact || i8) && (static_cast<long long>(n.K) * es) % 16 == 0) n.impl = IMPL_TC;
+      if (n.impl == IMPL_TC && !i8) any_fp32_tc_ = true;
+    } else if (n.kind == N_DW) {
+      n.impl = IMPL_DIRECT;
+    }
+  }
+  (void)err;
+  return true;
+}
+
+bool EngineImpl::prepare_weights(std::string* err) {
+  const int f32_kind = opt_.accuracy_mode == kAccuracyTf32 ? GEMM_TF32 : GEMM_TF32X3;
+  // insert Quantize steps in front of int8 contractions whose input is fp32
+  for (size_t k = 0; k < nodes_.size(); ++k) {
+    Node& n = nodes_[k];
+    if (!((n.kind == N_CONV || n.kind == N_DW || n.kind == N_IP) && n.term != 0)) continue;
+    const int src = resolve(n.in[0]);
+    if (tensors_[src].i8) continue;
+    if (n.stem) {
+      tensors_[src].input_quant_scale = n.s_in;  // the input edge quantises directly
+      continue;
+    }
+    Node q;
+    q.kind = N_UNARY;
+    q.name = n.name + ":quantize";
+    q.type = "Quantize";
+    q.un.op = UN_QUANT;
+    q.un_scale = {n.s_in};
+    q.un.nscale = 1;
+    q.un.channels = 1;
+    q.un.inner = 1;
+    q.in = {src};
+    q.out = new_tensor(n.name + ":q");
+    Tensor& tq = tensors_[q.out];
+    const std::string keep = tq.name;
+    tq = tensors_[src];
+    tq.name = keep;
+    tq.alias = -1;
+    tq.is_input = false;
+    tq.i8 = true;
+    n.in[0] = q.out;
+    nodes_.insert(nodes_.begin() + k, std::move(q));
+    ++k;
+  }
+  // formats
+  for (Tensor& t : tensors_) {
+    t.Cp = t.rank == 3 ? t.c : 1;
+    t.Wp = t.w;
+    t.w_off = 0;
+    if (t.i8) {
+      t.fmt = FMT_I8;
+    } else if (any_fp32_tc_) {
+      t.fmt = opt_.accuracy_mode == kAccuracyTf32 ? FMT_TF32 : FMT_SPLIT;
+    } else {
+      t.fmt = FMT_F32;
+    }
+  }
+  for (Node& n : nodes_) {
+    const bool i8 = n.term != 0;
+    if (n.has_bias) n.d_bias = upload(n.bias);
+    if (!n.deq.empty()) n.d_deq = upload(n.deq);
+    if (!n.un_scale.empty()) n.d_scale = upload(n.un_scale);
+    if (!n.un_offset.empty()) n.d_offset = upload(n.un_offset);
+    n.un.scale = n.d_scale;
+    n.un.offset = n.d_offset;
+    if (n.kind == N_CONV) {
+      const int src = resolve(n.in[0]);
+      Tensor& ti = tensors_[src];
+      const int C = ti.c;
+      if (n.impl == IMPL_TC) {
+        const int kind = i8 ? GEMM_I8 : f32_kind;
+        if (n.stem) {
+          const int cp = i8 ? 16 : 4;
+          const int window = i8 ? 128 : 32;
+          n.k_elems = window;
+          // storage of the input: rows padded on the left by pad_l, wide enough for the
+          // last window, channels padded to cp
+          ti.Cp = cp;
+          ti.w_off = n.pl;
+          ti.Wp = std::max(ti.w + n.pl, ((n.OW - 1) * n.sw * cp + window + cp - 1) / cp);
+          ti.dedicated = true;
+          if (i8) {
+            ti.i8 = true;
+            ti.fmt = FMT_I8;
+          }
+          // virtual weights [O][I' = window][KH][1], I' index = kw*cp + c
+          if (i8) {
+            std::vector<int8_t> v(static_cast<size_t>(n.O) * window * n.KH, 0), packed;
+            for (int o = 0; o < n.O; ++o)
+              for (int c = 0; c < C; ++c)
+                for (int kh = 0; kh < n.KH; ++kh)
+                  for (int kw = 0; kw < n.KW; ++kw)
+                    v[(static_cast<size_t>(o) * window + kw * cp + c) * n.KH + kh] =
+                        n.w_i8[((static_cast<size_t>(o) * C + c) * n.KH + kh) * n.KW + kw];
+            tc_pack_weights_i8(v.data(), n.O, window, n.KH, 1, window, &packed);
+            n.d_w0 = upload(packed);
+          } else {
+            std::vector<float> v(static_cast<size_t>(n.O) * window * n.KH, 0.0f), hi, lo;
+            for (int o = 0; o < n.O; ++o)
+              for (int c = 0; c < C; ++c)
+                for (int kh = 0; kh < n.KH; ++kh)
+                  for (int kw = 0; kw < n.KW; ++kw)
+                    v[(static_cast<size_t>(o) * window + kw * cp + c) * n.KH + kh] =
+                        n.w_f32[((static_cast<size_t>(o) * C + c) * n.KH + kh) * n.KW + kw];
+            tc_pack_weights_f32(kind, v.data(), n.O, window, n.KH, 1, window, &hi, &lo);
+            n.d_w0 = upload(hi);
+            if (kind == GEMM_TF32X3) n.d_w1 = upload(lo);
+          }
+        } else {
+          n.k_elems = tc_k_elems(kind, C);
+          if (i8) {
+            std::vector<int8_t> packed;
+            tc_pack_weights_i8(n.w_i8.data(), n.O, C, n.KH, n.KW, n.k_elems, &packed);
+            n.d_w0 = upload(packed);
+          } else {
+            std::vector<float> hi, lo;
+            tc_pack_weights_f32(kind, n.w_f32.data(), n.O, C, n.KH, n.KW, n.k_elems, &hi, &lo);
+            n.d_w0 = upload(hi);
+            if (kind == GEMM_TF32X3) n.d_w1 = upload(lo);
+          }
+        }
+      } else {
+        // direct kernel: [KH*KW][C][O]
+        const size_t total = static_cast<size_t>(n.KH) * n.KW * C * n.O;
+        if (i8) {
+          std::vector<int8_t> v(total);
+          for (int o = 0; o < n.O; ++o)
+            for (int c = 0; c < C; ++c)
+              for (int t = 0; t < n.KH * n.KW; ++t)
+                v[(static_cast<size_t>(t) * C + c) * n.O + o] = n.w_i8[(static_cast<size_t>(o) * C + c) * n.KH * n.KW + t];
+          n.d_w0 = upload(v);
+        } else {
+          std::vector<float> v(total);
+          for (int o = 0; o < n.O; ++o)
+            for (int c = 0; c < C; ++c)
+              for (int t = 0; t < n.KH * n.KW; ++t)
+                v[(static_cast<size_t>(t) * C + c) * n.O + o] = n.w_f32[(static_cast<size_t>(o) * C + c) * n.KH * n.KW + t];
+          n.d_w0 = upload(v);
+        }
+      }
+      if (n.d_w0 == nullptr) return fail(err, "out of device memory while uploading weights of " + n.name);
+    } else if (n.kind == N_DW) {
+      const int C = n.O, taps = n.KH * n.KW;
+      if (i8) {
+        std::vector<int8_t> v(static_cast<size_t>(taps) * C);
+        for (int c = 0; c < C; ++c)
+          for (int t = 0; t < taps; ++t) v[static_cast<size_t>(t) * C + c] = n.w_i8[static_cast<size_t>(c) * taps + t];
+        n.d_w0 = upload(v);
+      } else {
+        std::vector<float> v(static_cast<size_t>(taps) * C);
+        for (int c = 0; c < C; ++c)
+          for (int t = 0; t < taps; ++t) v[static_cast<size_t>(t) * C + c] = n.w_f32[static_cast<size_t>(c) * taps + t];
+        n.d_w0 = upload(v);
+      }
+    } else if (n.kind == N_IP || n.kind == N_GEMM) {
+      const Tensor& ti = tensors_[resolve(n.in[0])];
+      // The reference flattens in [C][H][W] order (NCNNToTosa.cpp:5305-5337); activations
+      // are stored channel-last, so the weight columns are permuted once here.
+      std::vector<int> perm(n.K);
+      for (int k = 0; k < n.K; ++k) perm[k] = k;
+      if (n.kind == N_IP && ti.rank == 3) {
+        for (int c = 0; c < ti.c; ++c)
+          for (int h = 0; h < ti.h; ++h)
+            for (int w = 0; w < ti.w; ++w) perm[(h * ti.w + w) * ti.c + c] = (c * ti.h + h) * ti.w + w;
+      }
+      if (n.kind == N_GEMM && i8) {
+        n.d_w0 = upload(n.w_i8);  // [N][K] as is
+      } else if (n.impl == IMPL_TC) {
+        const int kind = i8 ? GEMM_I8 : f32_kind;
+        n.k_elems = i8 ? 128 : 32;
+        if (i8) {
+          std::vector<int8_t> v(n.w_i8.size()), packed;
+          for (int o = 0; o < n.O; ++o)
+            for (int k = 0; k < n.K; ++k) v[static_cast<size_t>(o) * n.K + k] = n.w_i8[static_cast<size_t>(o) * n.K + perm[k]];
+          tc_pack_weights_i8(v.data(), n.O, n.K, 1, 1, n.k_elems, &packed);
+          n.d_w0 = upload(packed);
+        } else {
+          std::vector<float> v(n.w_f32.size()), hi, lo;
+          for (int o = 0; o < n.O; ++o)
+            for (int k = 0; k < n.K; ++k) v[static_cast<size_t>(o) * n.K + k] = n.w_f32[static_cast<size_t>(o) * n.K + perm[k]];
+          tc_pack_weights_f32(kind, v.data(), n.O, n.K, 1, 1, n.k_elems, &hi, &lo);
+          n.d_w0 = upload(hi);
+          if (kind == GEMM_TF32X3) n.d_w1 = upload(lo);
+        }
+      } else {
+        // direct kernel: [K][N]
+        if (i8) {
+          std::vector<int8_t> v(n.w_i8.size());
+          for (int o = 0; o < n.O; ++o)
+            for (int k = 0; k < n.K; ++k) v[static_cast<size_t>(k) * n.O + o] = n.w_i8[static_cast<size_t>(o) * n.K + perm[k]];
+          n.d_w0 = upload(v);
+        } else {
+          std::vector<float> v(n.w_f32.size());
+          for (int o = 0; o < n.O; ++o)
+            for (int k = 0; k < n.K; ++k) v[static_cast<size_t>(k) * n.O + o] = n.w_f32[static_cast<size_t>(o) * n.K + perm[k]];
+          n.d_w0 = upload(v);
+        }
+      }
+      if (n.d_w0 == nullptr) return fail(err, "out of device memory while uploading weights of " + n.name);
+    }
+  }
+  // host copies are no longer needed
+  for (Node& n : nodes_) {
+    std::vector<float>().swap(n.w_f32);
+    std::vector<int8_t>().swap(n.w_i8);
+  }
+  return true;
+}
+
+void EngineImpl::plan_memory() {
+  // sizes
+  for (Tensor& t : tensors_) {
+    if (t.alias >= 0) continue;
+    t.plane_elems = t.rank == 3 ? static_cast<size_t>(t.h) * t.Wp * t.Cp : static_cast<size_t>(t.logical());
+    if (t.dedicated) t.plane_elems += 256;  // the last window may read past the last row
+    t.plane_bytes = round_up(t.plane_elems * (t.fmt == FMT_I8 ? 1 : 4), 256);
+  }
+  // liveness over node order; inputs are defined before node 0, outputs live to the end
+  const int end = static_cast<int>(nodes_.size());
+  for (Tensor& t : tensors_) {
+    t.first_def = -1;
+    t.last_use = -1;
+  }
+  for (int k = 0; k < end; ++k) {
+    const Node& n = nodes_[k];
+    Tensor& o = tensors_[resolve(n.out)];
+    if (o.first_def < 0) o.first_def = k;
+    o.last_use = std::max(o.last_use, k);
+    for (int t : n.in) tensors_[resolve(t)].last_use = std::max(tensors_[resolve(t)].last_use, k);
+    if (n.res >= 0) tensors_[resolve(n.res)].last_use = std::max(tensors_[resolve(n.res)].last_use, k);
+  }
+  for (int t : inputs_) {
+    tensors_[resolve(t)].first_def = -1;
+    tensors_[resolve(t)].last_use = std::max(tensors_[resolve(t)].last_use, 0);
+  }
+  for (int t : outputs_) tensors_[resolve(t)].last_use = end;
+  // greedy first fit, largest first
+  struct Placed {
+    size_t off, size;
+    int a, b;
+  };
+  std::vector<int> order;
+  for (size_t i = 0; i < tensors_.size(); ++i)
+    if (tensors_[i].alias < 0 && (tensors_[i].last_use >= 0 || tensors_[i].is_input)) order.push_back(static_cast<int>(i));
+  std::sort(order.begin(), order.end(), [&](int x, int y) {
+    return tensors_[x].plane_bytes * tensors_[x].planes() > tensors_[y].plane_bytes * tensors_[y].planes();
+  });
+  std::vector<Placed> placed;
+  size_t top = 0;
+  for (int id : order) {
+    Tensor& t = tensors_[id];
+    const size_t size = t.plane_bytes * t.planes();
+    const int a = t.dedicated ? -2 : t.first_def, b = t.dedicated ? end + 1 : t.last_use;
+    size_t off = 0;
+    bool moved = true;
+    while (moved) {
+      moved = false;
+      for (const Placed& p : placed) {
+        const bool time_overlap = !(b < p.a || p.b < a);
+        const bool space_overlap = off < p.off + p.size && p.off < off + size;
+        if (time_overlap && space_overlap) {
+          off = p.off + p.size;
+          moved = true;
+        }
+      }
+    }
+    t.offset = off;
+    placed.push_back({off, size, a, b});
+    top = std::max(top, off + size);
+  }
+  arena_per_image_ = top;
+}
+
+ActRef EngineImpl::ref(int tensor, int64_t n) const {
+  const Tensor& t = tensors_[resolve(tensor)];
+  ActRef r;
+  r.fmt = t.fmt;
+  uint8_t* base = arena_ + t.offset * static_cast<size_t>(n);
+  if (t.fmt == FMT_I8) {
+    r.q = reinterpret_cast<int8_t*>(base);
+  } else {
+    r.p0 = reinterpret_cast<float*>(base);
+    if (t.fmt == FMT_SPLIT) r.p1 = reinterpret_cast<float*>(base + t.plane_bytes * static_cast<size_t>(n));
+  }
+  return r;
+}
+
+// ---------------------------------------------------------------------- build
+bool EngineImpl::build(const std::string& param, const std::string& bin, const EngineOptions& opt,
+                       std::string* err) {
+  opt_ = opt;
+  if (opt.accuracy_mode < 0 || opt.accuracy_mode > 2) return fail(err, "unknown accuracy mode");
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0)
+    return fail(err, "no CUDA device is available: this runtime has no CPU path");
+  if (opt.device >= 0 && cudaSetDevice(opt.device) != cudaSuccess) return fail(err, "cannot select the requested CUDA device");
+  int dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return fail(err, "cannot query the CUDA device");
+  if (prop.major != 10) return fail(err, std::string("this runtime is built for sm_100a only; device is ") + prop.name);
+  sm_count_ = prop.multiProcessorCount;
+  if (!load_model(param, bin, &model_, err)) return false;
+  if (!model_.weights_loaded) return fail(err, "a .bin file is required");
+  if (!import_layers(err)) return false;
+  fold_batchnorm();
+  fuse();
+  if (!choose_impl(err)) return false;
+  if (!prepare_weights(err)) return false;
+  plan_memory();
+  if (cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking) != cudaSuccess) return fail(err, "cannot create a stream");
+  void* st = nullptr;
+  if (cudaMalloc(&st, 256) != cudaSuccess) return fail(err, "out of device memory");
+  cudaMemset(st, 0, 256);
+  device_allocs_.push_back(st);
+  d_status_ = static_cast<int*>(st);
+  return true;
+}
+
+static cudaError_t launch_ok() { return cudaGetLastError(); }
+
+bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string* err) {
+  const Tensor& to = tensors_[resolve(node.out)];
+  const ActRef out = ref(node.out, n);
+  Step s;
+  s.name = node.name;
+  s.flops = node.flops * n;
+  const int f32_kind = opt_.accuracy_mode == kAccuracyTf32 ? GEMM_TF32 : GEMM_TF32X3;
+  auto bytes_of = [&](int t) {
+    const Tensor& x = tensors_[resolve(t)];
+    return static_cast<double>(x.logical()) * (x.i8 ? 1 : 4) * n;
+  };
+  s.bytes = bytes_of(node.out);
+  for (int t : node.in) s.bytes += bytes_of(t);
+  if (node.res >= 0) s.bytes += bytes_of(node.res);
+
+  if (node.kind == N_CONV || node.kind == N_IP || node.kind == N_GEMM || node.kind == N_DW) {
+    const Tensor& ti = tensors_[resolve(node.in[0])];
+    const ActRef in = ref(node.in[0], n);
+    const bool i8 = node.term != 0;
+    ConvEpilogue e{};
+    e.bias = node.d_bias;
+    e.scale = node.d_deq;
+    e.out_scale = node.s_out;
+    e.act = node.act;
+    e.act_a = node.act_a;
+    e.act_b = node.act_b;
+    e.has_res = node.res >= 0;
+    if (e.has_res) e.res = ref(node.res, n);
+    if (node.kind == N_GEMM && i8) {
+      const int K = node.K, N = node.O;
+      const long long M = static_cast<long long>(ti.h) * n;
+      const int8_t* wq = static_cast<const int8_t*>(node.d_w0);
+      const float s_b = node.s_b, alpha = node.alpha, beta = 1.0f;
+      const float* c_bias = node.d_bias;
+      const int has_c = node.has_bias, scale_alpha = node.alpha != 1.0f;
+      s.kernel = "k_gemm_i8_rowscale";
+      s.run = [=](cudaStream_t st) {
+        k_gemm_i8_rowscale<<<static_cast<unsigned>(M), 128, K, st>>>(in, out, wq, K, N, s_b, c_bias, alpha, beta, has_c, scale_alpha);
+        return launch_ok();
+      };
+      plan.steps.push_back(std::move(s));
+      return true;
+    }
+    if (node.impl == IMPL_TC) {
+      TcEpilogue te;
+      te.bias = node.d_bias;
+      te.scale = node.d_deq;
+      te.out0 = out.p0;
+      te.out1 = out.p1;
+      te.outq = out.q;
+      te.ldo = node.O;
+      te.act = node.act;
+      te.act_a = node.act_a;
+      te.act_b = node.act_b;
+      te.out_scale = node.s_out;
+      te.status = d_status_;
+      te.out_mode = to.fmt == FMT_I8 ? OUT_I8 : (to.fmt == FMT_SPLIT ? OUT_F32_SPLIT : (to.fmt == FMT_TF32 ? OUT_F32_TF32 : OUT_F32));
+      if (node.res >= 0) {
+        const ActRef r = ref(node.res, n);
+        te.res0 = r.p0;
+        te.res1 = r.p1;
+      }
+      const int kind = i8 ? GEMM_I8 : f32_kind;
+      auto launch = std::make_shared<TcLaunch>();
+      std::string perr;
+      if (node.kind == N_CONV) {
+        TcIm2colView v;
+        v.plane0 = i8 ? static_cast<const void*>(in.q) : static_cast<const void*>(in.p0);
+        v.plane1 = in.p1;
+        const size_t es = i8 ? 1 : 4;
+        if (node.stem) {
+          v.C = node.k_elems;
+          v.W = node.OW;
+          v.H = ti.h;
+          v.N = n;
+          v.stride_w = static_cast<uint64_t>(node.sw) * ti.Cp * es;
+          v.stride_h = static_cast<uint64_t>(ti.Wp) * ti.Cp * es;
+          v.stride_n = v.stride_h * ti.h;
+          v.KH = node.KH;
+          v.KW = 1;
+          v.stride_conv_h = node.sh;
+          v.stride_conv_w = 1;
+          v.pad_t = node.pt;
+          v.pad_l = 0;
+          v.dil_h = node.dh;
+          v.dil_w = 1;
+        } else {
+          v.C = ti.c;
+          v.W = ti.w;
+          v.H = ti.h;
+          v.N = n;
+          v.stride_w = static_cast<uint64_t>(ti.c) * es;
+          v.stride_h = v.stride_w * ti.w;
+          v.stride_n = v.stride_h * ti.h;
+          v.KH = node.KH;
+          v.KW = node.KW;
+          v.stride_conv_h = node.sh;
+          v.stride_conv_w = node.sw;
+          v.pad_t = node.pt;
+          v.pad_l = node.pl;
+          v.dil_h = node.dh;
+          v.dil_w = node.dw;
+        }
+        v.OH = node.OH;
+        v.OW = node.OW;
+        perr = tc_plan_conv(launch.get(), kind, v, node.d_w0, node.d_w1, node.O, te, sm_count_);
+      } else {
+        const long long M = (to.rank == 2 ? static_cast<long long>(ti.h) : 1) * n;
+        const void* a0 = i8 ? static_cast<const void*>(in.q) : static_cast<const void*>(in.p0);
+        perr = tc_plan_gemm(launch.get(), kind, a0, in.p1, M, node.K, node.K, node.d_w0, node.d_w1, node.O, te, sm_count_);
+      }
+      if (!perr.empty()) return fail(err, "layer " + node.name + ": " + perr);
+      s.kernel = kind == GEMM_I8 ? "tc_gemm_kernel<i8>" : (kind == GEMM_TF32 ? "tc_gemm_kernel<tf32>" : "tc_gemm_kernel<tf32x3>");
+      s.run = [launch](cudaStream_t st) { return tc_launch(*launch, st); };
+      plan.steps.push_back(std::move(s));
+    } else if (node.kind == N_CONV || node.kind == N_DW) {
+      ConvGeom g{};
+      g.images = n;
+      g.H = ti.h;
+      g.W = ti.w;
+      g.C = ti.c;
+      g.OH = node.OH;
+      g.OW = node.OW;
+      g.O = node.O;
+      g.KH = node.KH;
+      g.KW = node.KW;
+      g.sh = node.sh;
+      g.sw = node.sw;
+      g.pt = node.pt;
+      g.pl = node.pl;
+      g.dh = node.dh;
+      g.dw = node.dw;
+      const void* w = node.d_w0;
+      if (node.kind == N_DW) {
+        const bool vec = ti.c % 4 == 0;
+        const long long work = n * node.OH * node.OW * (vec ? ti.c / 4 : ti.c);
+        const int grid = grid_for(work);
+        s.kernel = i8 ? "k_depthwise<i8>" : "k_depthwise<f32>";
+        s.run = [=](cudaStream_t st) {
+          if (i8) {
+            if (vec) k_depthwise<4, true><<<grid, 256, 0, st>>>(in, out, w, g, e);
+            else k_depthwise<1, true><<<grid, 256, 0, st>>>(in, out, w, g, e);
+          } else {
+            if (vec) k_depthwise<4, false><<<grid, 256, 0, st>>>(in, out, w, g, e);
+            else k_depthwise<1, false><<<grid, 256, 0, st>>>(in, out, w, g, e);
+          }
+          return launch_ok();
+        };
+      } else {
+        const int grid = grid_for(n * node.OH * node.OW * node.O);
+        s.kernel = i8 ? "k_conv_direct<i8>" : "k_conv_direct<f32>";
+        s.run = [=](cudaStream_t st) {
+          if (i8) k_conv_direct<true><<<grid, 256, 0, st>>>(in, out, w, g, e);
+          else k_conv_direct<false><<<grid, 256, 0, st>>>(in, out, w, g, e);
+          return launch_ok();
+        };
+      }
+      plan.steps.push_back(std::move(s));
+    } else {
+      const long long M = (to.rank == 2 ? static_cast<long long>(ti.h) : 1) * n;
+      const int K = node.K, N = node.O;
+      const void* w = node.d_w0;
+      const int grid = grid_for(M * N);
+      s.kernel = i8 ? "k_matmul_direct<i8>" : "k_matmul_direct<f32>";
+      s.run = [=](cudaStream_t st) {
+        if (i8) k_matmul_direct<true><<<grid, 256, 0, st>>>(in, out, w, M, K, N, e, 0.0f);
+        else k_matmul_direct<false><<<grid, 256, 0, st>>>(in, out, w, M, K, N, e, 0.0f);
+        return launch_ok();
+      };
+      plan.steps.push_back(std::move(s));
+    }
+    if (node.kind == N_GEMM && node.alpha != 1.0f) {
+      Step m;
+      m.name = node.name + ":alpha";
+      m.kernel = "k_binary";
+      BinaryParams bp{};
+      bp.op = BIN_MUL;
+      bp.use_scalar = 1;
+      bp.scalar = node.alpha;
+      const long long count = to.logical() * n;
+      const int grid = grid_for(count);
+      m.run = [=](cudaStream_t st) {
+        k_binary<1><<<grid, 256, 0, st>>>(out, out, out, count, bp);
+        return launch_ok();
+      };
+      plan.steps.push_back(std::move(m));
+    }
+    return true;
+  }
+  if (node.kind == N_POOL) {
+    const ActRef in = ref(node.in[0], n);
+    PoolParams p = node.pool;
+    p.images = n;
+    const bool vec = p.C % 4 == 0;
+    const int grid = grid_for(n * p.OH * p.OW * (vec ? p.C / 4 : p.C));
+    s.kernel = "k_pool";
+    s.run = [=](cudaStream_t st) {
+      if (vec) k_pool<4><<<grid, 256, 0, st>>>(in, out, p);
+      else k_pool<1><<<grid, 256, 0, st>>>(in, out, p);
+      return launch_ok();
+    };
+    plan.steps.push_back(std::move(s));
+    return true;
+  }
+  if (node.kind == N_BINARY) {
+    const ActRef a = ref(node.in[0], n);
+    const ActRef b = node.in.size() > 1 ? ref(node.in[1], n) : a;
+    const BinaryParams bp = node.bin;
+    const long long count = to.logical() * n;
+    const bool vec = count % 4 == 0;
+    const int grid = grid_for(vec ? count / 4 : count);
+    s.kernel = "k_binary";
+    s.run = [=](cudaStream_t st) {
+      if (vec) k_binary<4><<<grid, 256, 0, st>>>(a, b, out, count, bp);
+      else k_binary<1><<<grid, 256, 0, st>>>(a, b, out, count, bp);
+      return launch_ok();
+    };
+    plan.steps.push_back(std::move(s));
+    return true;
+  }
+  if (node.kind == N_UNARY) {
+    const ActRef in = ref(node.in[0], n);
+    const UnaryParams up = node.un;
+    const long long count = to.logical() * n;
+    const bool vec = count % 4 == 0;
+    const int grid = grid_for(vec ? count / 4 : count);
+    s.kernel = "k_unary";
+    s.run = [=](cudaStream_t st) {
+      if (vec) k_unary<4><<<grid, 256, 0, st>>>(in, out, count, up);
+      else k_unary<1><<<grid, 256, 0, st>>>(in, out, count, up);
+      return launch_ok();
+    };
+    plan.steps.push_back(std::move(s));
+    return true;
+  }
+  if (node.kind == N_RELAYOUT) {
+    const ActRef in = ref(node.in[0], n);
+    RelayoutParams rp = node.relayout;
+    rp.images = n;
+    const int grid = grid_for(rp.count * n);
+    s.kernel = "k_relayout";
+    s.run = [=](cudaStream_t st) {
+      k_relayout<<<grid, 256, 0, st>>>(in, out, rp);
+      return launch_ok();
+    };
+    plan.steps.push_back(std::move(s));
+    return true;
+  }
+  return fail(err, "internal: unknown node kind");
+}
+
+Plan* EngineImpl::plan_for(int64_t n) {
+  auto it = plans_.find(n);
+  if (it != plans_.end()) return &it->second;
+  // the arena is shared by all plans; grow it when a larger batch arrives.  Offsets
+  // scale with n, so plans of other batch sizes stay valid only for their own n.
+  const size_t need = arena_per_image_ * static_cast<size_t>(n) + 4096;
+  if (need > arena_bytes_) {
+    for (auto& kv : plans_) {
+      if (kv.second.graph != nullptr) cudaGraphExecDestroy(kv.second.graph);
+      for (float* p : kv.second.d_in) cudaFree(p);
+      for (float* p : kv.second.d_out) cudaFree(p);
+    }
+    plans_.clear();
+    if (arena_ != nullptr) cudaFree(arena_);
+    arena_ = nullptr;
+    void* p = nullptr;
+    if (cudaMalloc(&p, need) != cudaSuccess) {
+      error_ = "out of device memory for a batch of " + std::to_string(n) + " (" + std::to_string(need >> 20) + " MiB of activations)";
+      arena_bytes_ = 0;
+      return nullptr;
+    }
+    arena_ = static_cast<uint8_t*>(p);
+    arena_bytes_ = need;
+  }
+  // padding of stem inputs must read as zero: clear once, nothing writes there later
+  cudaMemsetAsync(arena_, 0, arena_bytes_, stream_);
+  cudaStreamSynchronize(stream_);
+  Plan plan;
+  plan.n = n;
+  for (const Node& node : nodes_) {
+    std::string err;
+    if (!emit_node(plan, node, n, &err)) {
+      error_ = err;
+      return nullptr;
+    }
+  }
+  auto res = plans_.emplace(n, std::move(plan));
+  return &res.first->second;
+}
+
+int EngineImpl::run(int64_t n, const float* const* in, float* const* out, bool host, cudaStream_t user_stream) {
+  if (n <= 0) {
+    error_ = "batch size must be positive";
+    return 2;
+  }
+  Plan* plan = plan_for(n);
+  if (plan == nullptr) return 6;
+  cudaStream_t st = host ? stream_ : user_stream;
+  std::vector<const float*> d_in(inputs_.size());
+  std::vector<float*> d_out(outputs_.size());
+  if (host) {
+    if (plan->d_in.empty()) {
+      for (int t : inputs_) {
+        void* p = nullptr;
+        if (cudaMalloc(&p, tensors_[resolve(t)].logical() * 4 * n) != cudaSuccess) {
+          error_ = "out of device memory for input staging";
+          return 6;
+        }
+        plan->d_in.push_back(static_cast<float*>(p));
+      }
+      for (int t : outputs_) {
+        void* p = nullptr;
+        if (cudaMalloc(&p, tensors_[resolve(t)].logical() * 4 * n) != cudaSuccess) {
+          error_ = "out of device memory for output staging";
+          return 6;
+        }
+        plan->d_out.push_back(static_cast<float*>(p));
+      }
+    }
+    for (size_t i = 0; i < inputs_.size(); ++i) {
+      d_in[i] = plan->d_in[i];
+      cudaMemcpyAsync(plan->d_in[i], in[i], tensors_[resolve(inputs_[i])].logical() * 4 * n, cudaMemcpyHostToDevice, st);
+    }
+    for (size_t i = 0; i < outputs_.size(); ++i) d_out[i] = plan->d_out[i];
+  } else {
+    for (size_t i = 0; i < inputs_.size(); ++i) d_in[i] = in[i];
+    for (size_t i = 0; i < outputs_.size(); ++i) d_out[i] = out[i];
+  }
+
+  auto issue = [&](cudaStream_t s) -> cudaError_t {
+    for (size_t i = 0; i < inputs_.size(); ++i) {
+      const Tensor& t = tensors_[resolve(inputs_[i])];
+      const ActRef dst = ref(inputs_[i], n);
+      if (t.rank == 3) {
+        EdgeParams ep{};
+        ep.images = n;
+        ep.C = t.c;
+        ep.H = t.h;
+        ep.W = t.w;
+        ep.Cp = t.Cp;
+        ep.Wp = t.Wp;
+        ep.w_off = t.w_off;
+        ep.quant_scale = t.input_quant_scale;
+        if (t.c <= 4 && (t.Cp == 4 || t.Cp == 16)) {
+          k_chw_to_nhwc_small<<<grid_for(n * t.h * t.w), 256, 0, s>>>(d_in[i], dst, ep);
+        } else {
+          const dim3 grid((t.h * t.w + 31) / 32, (t.c + 31) / 32, static_cast<unsigned>(n));
+          k_chw_to_nhwc_tiled<<<grid, dim3(32, 8), 0, s>>>(d_in[i], dst, ep);
+        }
+      } else {
+        ActRef src;
+        src.fmt = FMT_F32;
+        src.p0 = const_cast<float*>(d_in[i]);
+        UnaryParams up{};
+        up.inner = 1;
+        up.channels = 1;
+        up.op = UN_COPY;
+        const long long count = t.logical() * n;
+        k_unary<1><<<grid_for(count), 256, 0, s>>>(src, dst, count, up);
+      }
+      const cudaError_t e = cudaGetLastError();
+      if (e != cudaSuccess) return e;
+    }
+    for (const Step& step : plan->steps) {
+      const cudaError_t e = step.run(s);
+      if (e != cudaSuccess) {
+        error_ = "launch of " + step.kernel + " for layer " + step.name + " failed: " + cudaGetErrorString(e);
+        return e;
+      }
+    }
+    for (size_t i = 0; i < outputs_.size(); ++i) {
+      const Tensor& t = tensors_[resolve(outputs_[i])];
+      const ActRef src = ref(outputs_[i], n);
+      if (t.rank == 3) {
+        const dim3 grid((t.h * t.w + 31) / 32, (t.c + 31) / 32, static_cast<unsigned>(n));
+        k_nhwc_to_chw_tiled<<<grid, dim3(32, 8), 0, s>>>(src, d_out[i], n, t.c, t.h * t.w, t.Cp);
+      } else {
+        ActRef dst;
+        dst.fmt = FMT_F32;
+        dst.p0 = d_out[i];
+        UnaryParams up{};
+        up.inner = 1;
+        up.channels = 1;
+        up.op = UN_COPY;
+        const long long count = t.logical() * n;
+        k_unary<1><<<grid_for(count), 256, 0, s>>>(src, dst, count, up);
+      }
+      const cudaError_t e = cudaGetLastError();
+      if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
+  };
+
+  cudaError_t e = cudaSuccess;
+  if (opt_.use_cuda_graph) {
+    std::vector<const void*> ptrs;
+    for (auto p : d_in) ptrs.push_back(p);
+    for (auto p : d_out) ptrs.push_back(p);
+    if (plan->graph == nullptr || plan->graph_ptrs != ptrs) {
+      if (plan->graph != nullptr) {
+        cudaGraphExecDestroy(plan->graph);
+        plan->graph = nullptr;
+      }
+      cudaStream_t cap = stream_;
+      if (!host) cudaStreamSynchronize(cap);
+      cudaGraph_t g = nullptr;
+      e = cudaStreamBeginCapture(cap, cudaStreamCaptureModeThreadLocal);
+      if (e == cudaSuccess) {
+        const cudaError_t ie = issue(cap);
+        const cudaError_t ee = cudaStreamEndCapture(cap, &g);
+        e = ie != cudaSuccess ? ie : ee;
+      }
+      if (e == cudaSuccess) e = cudaGraphInstantiate(&plan->graph, g, 0);
+      if (g != nullptr) cudaGraphDestroy(g);
+      if (e != cudaSuccess) {
+        if (error_.empty()) error_ = std::string("CUDA graph capture failed: ") + cudaGetErrorString(e);
+        plan->graph = nullptr;
+        return 6;
+      }
+      plan->graph_ptrs = ptrs;
+    }
+    e = cudaGraphLaunch(plan->graph, st);
+  } else {
+    e = issue(st);
+  }
+  if (e != cudaSuccess) {
+    if (error_.empty()) error_ = std::string("launch failed: ") + cudaGetErrorString(e);
+    return 6;
+  }
+  if (host) {
+    for (size_t i = 0; i < outputs_.size(); ++i)
+      cudaMemcpyAsync(out[i], plan->d_out[i], tensors_[resolve(outputs_[i])].logical() * 4 * n, cudaMemcpyDeviceToHost, st);
+    int status = 0;
+    cudaMemcpyAsync(&status, d_status_, 4, cudaMemcpyDeviceToHost, st);
+    e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) {
+      error_ = std::string("execution failed: ") + cudaGetErrorString(e);
+      return 6;
+    }
+    if (status != 0) {
+      error_ = "a tensor-core pipeline wait timed out (status " + std::to_string(status) + ")";
+      cudaMemset(d_status_, 0, 4);
+      return 7;
+    }
+  }
+  return 0;
+}
+
+int EngineImpl::profile(int64_t n, int repeat, std::vector<LayerTiming>* out) {
+  Plan* plan = plan_for(n);
+  if (plan == nullptr) return 6;
+  out->clear();
+  std::vector<cudaEvent_t> ev(plan->steps.size() + 1);
+  for (auto& e : ev) cudaEventCreate(&e);
+  std::vector<double> total(plan->steps.size(), 0.0);
+  for (int r = 0; r < repeat + 1; ++r) {
+    cudaEventRecord(ev[0], stream_);
+    for (size_t i = 0; i < plan->steps.size(); ++i) {
+      const cudaError_t e = plan->steps[i].run(stream_);
+      if (e != cudaSuccess) {
+        error_ = std::string("launch failed while profiling: ") + cudaGetErrorString(e);
+        return 6;
+      }
+      cudaEventRecord(ev[i + 1], stream_);
+    }
+    if (cudaStreamSynchronize(stream_) != cudaSuccess) {
+      error_ = "execution failed while profiling";
+      return 6;
+    }
+    if (r == 0) continue;  // warm-up
+    for (size_t i = 0; i < plan->steps.size(); ++i) {
+      float ms = 0.0f;
+      cudaEventElapsedTime(&ms, ev[i], ev[i + 1]);
+      total[i] += ms;
+    }
+  }
+  for (size_t i = 0; i < plan->steps.size(); ++i) {
+    LayerTiming t;
+    t.name = plan->steps[i].name;
+    t.kernel = plan->steps[i].kernel;
+    t.ms = static_cast<float>(total[i] / std::max(repeat, 1));
+    t.flops = plan->steps[i].flops;
+    t.bytes = plan->steps[i].bytes;
+    out->push_back(t);
+  }
+  for (auto& e : ev) cudaEventDestroy(e);
+  return 0;
+}
+
+// ---------------------------------------------------------------------- Engine
+Engine::Engine() : impl_(new EngineImpl) {}
+Engine::~Engine() = default;
+
+std::unique_ptr<Engine> Engine::create(const std::string& param_path, const std::string& bin_path,
+                                       const EngineOptions& options, std::string* error) {
+  std::unique_ptr<Engine> e(new Engine);
+  if (!e->impl_->build(param_path, bin_path, options, error)) return nullptr;
+  return e;
+}
+
+int Engine::input_count() const { return static_cast<int>(impl_->inputs_.size()); }
+int Engine::output_count() const { return static_cast<int>(impl_->outputs_.size()); }
+
+static TensorShape shape_of(const Tensor& t) {
+  TensorShape s;
+  s.rank = t.rank;
+  if (t.rank == 3) {
+    s.dims[0] = t.c;
+    s.dims[1] = t.h;
+    s.dims[2] = t.w;
+  } else if (t.rank == 2) {
+    s.dims[0] = t.h;
+    s.dims[1] = t.w;
+  } else {
+    s.dims[0] = t.w;
+  }
+  return s;
+}
+
+TensorShape Engine::input_shape(int i) const { return shape_of(impl_->tensors_[impl_->inputs_[i]]); }
+TensorShape Engine::output_shape(int i) const {
+  int t = impl_->outputs_[i];
+  while (impl_->tensors_[t].alias >= 0) t = impl_->tensors_[t].alias;
+  return shape_of(impl_->tensors_[t]);
+}
+const std::string& Engine::input_name(int i) const { return impl_->tensors_[impl_->inputs_[i]].name; }
+const std::string& Engine::output_name(int i) const { return impl_->tensors_[impl_->outputs_[i]].name; }
+
+int Engine::run_host(int64_t n, const float* const* inputs, float* const* outputs) {
+  impl_->error_.clear();
+  return impl_->run(n, inputs, outputs, true, nullptr);
+}
+int Engine::run_device(int64_t n, const float* const* inputs, float* const* outputs, cudaStream_t stream) {
+  impl_->error_.clear();
+  return impl_->run(n, inputs, outputs, false, stream);
+}
+int Engine::profile(int64_t n, int repeat, std::vector<LayerTiming>* out) { return impl_->profile(n, repeat, out); }
+int Engine::check_status() {
+  int status = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess ||
+      cudaMemcpy(&status, impl_->d_status_, 4, cudaMemcpyDeviceToHost) != cudaSuccess) {
+    impl_->error_ = "execution failed";
+    return 6;
+  }
+  if (status != 0) {
+    impl_->error_ = "a tensor-core pipeline wait timed out (status " + std::to_string(status) + ")";
+    cudaMemset(impl_->d_status_, 0, 4);
+    return 7;
+  }
+  return 0;
+}
+int Engine::launches_per_run(int64_t n) {
+  Plan* p = impl_->plan_for(n);
+  if (p == nullptr) return -1;
+  return static_cast<int>(p->steps.size() + impl_->inputs_.size() + impl_->outputs_.size());
+}
+const std::string& Engine::last_error() const { return impl_->error_; }
+
+std::string Engine::plan_summary(int64_t n) {
+  Plan* p = impl_->plan_for(n);
+  std::ostringstream o;
+  if (p == nullptr) return "error: " + impl_->error_;
+  o << "batch " << n << ": " << p->steps.size() << " launches, arena "
+    << (impl_->arena_per_image_ * n >> 10) << " KiB\n";
+  for (const Step& s : p->steps) o << "  " << s.kernel << "  " << s.name << "\n";
+  return o.str();
+}
+
+}  // namespace nb

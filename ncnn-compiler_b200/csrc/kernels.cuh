@@ -1,0 +1,616 @@
+// Memory-bound and CUDA-core kernels of the runtime.  Activations live in HBM as
+// channel-last arrays ([image][h][w][c], c contiguous) in one of three formats:
+//   FMT_F32    one fp32 plane
+//   FMT_SPLIT  two fp32 planes hi/lo with x == hi + lo exactly (hi is x rounded to
+//              tf32); feeds the 3xTF32 tensor-core path
+//   FMT_I8     one int8 plane
+//   FMT_TF32   one fp32 plane whose values are rounded to tf32 when stored
+// All kernels index with 64-bit offsets, use 128-bit accesses when the channel
+// count allows, and keep the reference's order of operations where it affects
+// the result (no FMA in int8 epilogues, sequential window sums).
+#pragma once
+
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "tc_gemm.cuh"
+
+namespace nb {
+
+enum : int { FMT_F32 = 0, FMT_SPLIT = 1, FMT_I8 = 2, FMT_TF32 = 3 };
+
+struct ActRef {
+  float* p0 = nullptr;
+  float* p1 = nullptr;
+  int8_t* q = nullptr;
+  int fmt = FMT_F32;
+};
+
+__device__ __forceinline__ float act_load(const ActRef& a, long long i) {
+  if (a.fmt == FMT_I8) return static_cast<float>(a.q[i]);
+  float v = a.p0[i];
+  if (a.fmt == FMT_SPLIT) v = __fadd_rn(v, a.p1[i]);
+  return v;
+}
+
+__device__ __forceinline__ void act_store(const ActRef& a, long long i, float v) {
+  if (a.fmt == FMT_I8) {
+    a.q[i] = static_cast<int8_t>(static_cast<int>(v));
+  } else if (a.fmt == FMT_F32) {
+    a.p0[i] = v;
+  } else {
+    const float hi = round_tf32(v);
+    a.p0[i] = hi;
+    if (a.fmt == FMT_SPLIT) a.p1[i] = __fadd_rn(v, -hi);
+  }
+}
+
+__device__ __forceinline__ float4 act_load4(const ActRef& a, long long i) {
+  if (a.fmt == FMT_I8) {
+    const char4 c = *reinterpret_cast<const char4*>(a.q + i);
+    return make_float4(c.x, c.y, c.z, c.w);
+  }
+  float4 v = *reinterpret_cast<const float4*>(a.p0 + i);
+  if (a.fmt == FMT_SPLIT) {
+    const float4 l = *reinterpret_cast<const float4*>(a.p1 + i);
+    v.x = __fadd_rn(v.x, l.x);
+    v.y = __fadd_rn(v.y, l.y);
+    v.z = __fadd_rn(v.z, l.z);
+    v.w = __fadd_rn(v.w, l.w);
+  }
+  return v;
+}
+
+__device__ __forceinline__ void act_store4(const ActRef& a, long long i, float4 v) {
+  if (a.fmt == FMT_I8) {
+    *reinterpret_cast<char4*>(a.q + i) =
+        make_char4(static_cast<signed char>(static_cast<int>(v.x)),
+                   static_cast<signed char>(static_cast<int>(v.y)),
+                   static_cast<signed char>(static_cast<int>(v.z)),
+                   static_cast<signed char>(static_cast<int>(v.w)));
+  } else if (a.fmt == FMT_F32) {
+    *reinterpret_cast<float4*>(a.p0 + i) = v;
+  } else {
+    const float4 hi = make_float4(round_tf32(v.x), round_tf32(v.y), round_tf32(v.z), round_tf32(v.w));
+    *reinterpret_cast<float4*>(a.p0 + i) = hi;
+    if (a.fmt == FMT_SPLIT)
+      *reinterpret_cast<float4*>(a.p1 + i) =
+          make_float4(__fadd_rn(v.x, -hi.x), __fadd_rn(v.y, -hi.y), __fadd_rn(v.z, -hi.z),
+                      __fadd_rn(v.w, -hi.w));
+  }
+}
+
+// ----------------------------------------------------------------- layout edges
+// Caller's [image][C][H*W] fp32  ->  channel-last [image][H][Wp][Cp] (pixel (h,w) is
+// stored at row offset w + w_off; padding columns/channels stay zero).  With
+// quant_scale > 0 the values are quantised to int8 on the way.
+struct EdgeParams {
+  long long images;
+  int C, H, W, Cp, Wp, w_off;
+  float quant_scale;
+};
+
+static __global__ void k_chw_to_nhwc_tiled(const float* __restrict__ src, ActRef dst, EdgeParams p) {
+  __shared__ float tile[32][33];
+  const long long img = blockIdx.z;
+  const int hw = p.H * p.W;
+  const int p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+  const float* s = src + img * static_cast<long long>(p.C) * hw;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int c = c0 + r, px = p0 + threadIdx.x;
+    tile[r][threadIdx.x] = (c < p.C && px < hw) ? s[static_cast<long long>(c) * hw + px] : 0.0f;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int px = p0 + r, c = c0 + threadIdx.x;
+    if (px < hw && c < p.C) {
+      const int h = px / p.W, w = px - h * p.W;
+      const long long o =
+          ((img * p.H + h) * static_cast<long long>(p.Wp) + w + p.w_off) * p.Cp + c;
+      float v = tile[threadIdx.x][r];
+      if (p.quant_scale > 0.0f) v = static_cast<float>(quantize_rha(v, p.quant_scale));
+      act_store(dst, o, v);
+    }
+  }
+}
+
+// Few channels (C <= 4): one thread per pixel, one 16-byte store per plane.
+static __global__ void k_chw_to_nhwc_small(const float* __restrict__ src, ActRef dst, EdgeParams p) {
+  const long long hw = static_cast<long long>(p.H) * p.W;
+  const long long total = p.images * hw;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long img = i / hw;
+    const long long px = i - img * hw;
+    const int h = static_cast<int>(px / p.W), w = static_cast<int>(px - static_cast<long long>(h) * p.W);
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int c = 0; c < p.C; ++c) v[c] = src[(img * p.C + c) * hw + px];
+    const long long o = ((img * p.H + h) * static_cast<long long>(p.Wp) + w + p.w_off) * p.Cp;
+    if (dst.fmt == FMT_I8) {
+      // Cp == 16: channels 0..3 carry data, the rest of the 16-byte pixel is zero
+      uint32_t w0 = 0;
+      for (int c = 0; c < p.C; ++c)
+        w0 |= (static_cast<uint32_t>(quantize_rha(v[c], p.quant_scale)) & 0xffu) << (8 * c);
+      *reinterpret_cast<uint4*>(dst.q + o) = make_uint4(w0, 0u, 0u, 0u);
+    } else {
+      act_store4(dst, o, make_float4(v[0], v[1], v[2], v[3]));
+    }
+  }
+}
+
+// Channel-last [image][HW][Cp] -> caller's [image][C][HW] fp32.
+static __global__ void k_nhwc_to_chw_tiled(ActRef src, float* __restrict__ dst, long long images, int C,
+                                    int HW, int Cp) {
+  __shared__ float tile[32][33];
+  const long long img = blockIdx.z;
+  const int p0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int px = p0 + r, c = c0 + threadIdx.x;
+    tile[r][threadIdx.x] =
+        (px < HW && c < C) ? act_load(src, (img * HW + px) * static_cast<long long>(Cp) + c) : 0.0f;
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int c = c0 + r, px = p0 + threadIdx.x;
+    if (c < C && px < HW) dst[(img * C + c) * static_cast<long long>(HW) + px] = tile[threadIdx.x][r];
+  }
+}
+
+// ----------------------------------------------------------------- element-wise
+enum : int { UN_COPY = 0, UN_ACT = 1, UN_AFFINE = 2, UN_QUANT = 3 };
+struct UnaryParams {
+  int op;
+  int act;
+  float act_a, act_b;
+  const float* scale;   // UN_AFFINE: per-channel scale; UN_QUANT: scale(s)
+  const float* offset;  // UN_AFFINE: per-channel offset
+  int nscale;           // UN_QUANT: 1 or channels
+  int channels = 1;     // channel index of element i = (i / inner) % channels
+  int inner = 1;        // 1 for channel-last storage, row length for rank-2 tensors
+};
+
+__device__ __forceinline__ float unary_apply(const UnaryParams& u, float v, long long i) {
+  if (u.op == UN_ACT) return apply_act(v, u.act, u.act_a, u.act_b);
+  if (u.op == UN_AFFINE) {
+    const int c = static_cast<int>((i / u.inner) % u.channels);
+    return __fadd_rn(__fmul_rn(v, u.scale[c]), u.offset[c]);
+  }
+  if (u.op == UN_QUANT) {
+    const float s = u.nscale == 1 ? u.scale[0] : u.scale[(i / u.inner) % u.channels];
+    return static_cast<float>(quantize_rha(v, s));
+  }
+  return v;
+}
+
+template <int VEC>
+static __global__ void k_unary(ActRef in, ActRef out, long long count, UnaryParams u) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * VEC;
+  for (long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) * VEC;
+       i < count; i += stride) {
+    if (VEC == 4) {
+      float4 v = act_load4(in, i);
+      v.x = unary_apply(u, v.x, i);
+      v.y = unary_apply(u, v.y, i + 1);
+      v.z = unary_apply(u, v.z, i + 2);
+      v.w = unary_apply(u, v.w, i + 3);
+      act_store4(out, i, v);
+    } else {
+      act_store(out, i, unary_apply(u, act_load(in, i), i));
+    }
+  }
+}
+
+// out = act(op(a * ca?, b * cb?)): Eltwise SUM with coefficients (a coefficient of
+// exactly 1 is skipped, as the reference does) and BinaryOp add/sub/mul/max.
+enum : int { BIN_ADD = 0, BIN_SUB = 1, BIN_MUL = 2, BIN_MAX = 4 };
+struct BinaryParams {
+  int op;
+  int use_scalar;
+  float scalar;
+  int scale_a, scale_b;
+  float ca, cb;
+  int act;
+  float act_a, act_b;
+};
+
+__device__ __forceinline__ float binary_apply(const BinaryParams& b, float x, float y) {
+  if (b.scale_a) x = __fmul_rn(x, b.ca);
+  if (b.scale_b) y = __fmul_rn(y, b.cb);
+  float r;
+  switch (b.op) {
+    case BIN_ADD: r = __fadd_rn(x, y); break;
+    case BIN_SUB: r = __fadd_rn(x, -y); break;
+    case BIN_MUL: r = __fmul_rn(x, y); break;
+    default: r = fmaxf(x, y); break;
+  }
+  return apply_act(r, b.act, b.act_a, b.act_b);
+}
+
+template <int VEC>
+static __global__ void k_binary(ActRef a, ActRef b, ActRef out, long long count, BinaryParams p) {
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x * VEC;
+  for (long long i = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) * VEC;
+       i < count; i += stride) {
+    if (VEC == 4) {
+      const float4 x = act_load4(a, i);
+      const float4 y = p.use_scalar ? make_float4(p.scalar, p.scalar, p.scalar, p.scalar)
+                                    : act_load4(b, i);
+      act_store4(out, i, make_float4(binary_apply(p, x.x, y.x), binary_apply(p, x.y, y.y),
+                                     binary_apply(p, x.z, y.z), binary_apply(p, x.w, y.w)));
+    } else {
+      const float x = act_load(a, i);
+      const float y = p.use_scalar ? p.scalar : act_load(b, i);
+      act_store(out, i, binary_apply(p, x, y));
+    }
+  }
+}
+
+// ----------------------------------------------------------------- pooling
+struct PoolParams {
+  long long images;
+  int H, W, C, OH, OW;
+  int kind;  // 0 max, 1 average over in-bounds elements
+  int KH, KW, sh, sw, pt, pl;
+};
+
+template <int VEC>
+static __global__ void k_pool(ActRef in, ActRef out, PoolParams p) {
+  const int cv = p.C / VEC;
+  const long long total = p.images * p.OH * p.OW * cv;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(i % cv) * VEC;
+    long long r = i / cv;
+    const int ow = static_cast<int>(r % p.OW);
+    r /= p.OW;
+    const int oh = static_cast<int>(r % p.OH);
+    const long long img = r / p.OH;
+    float acc[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[e] = p.kind == 0 ? -INFINITY : 0.0f;
+    int count = 0;
+    for (int kh = 0; kh < p.KH; ++kh) {
+      const int ih = oh * p.sh - p.pt + kh;
+      if (ih < 0 || ih >= p.H) continue;
+      for (int kw = 0; kw < p.KW; ++kw) {
+        const int iw = ow * p.sw - p.pl + kw;
+        if (iw < 0 || iw >= p.W) continue;
+        const long long idx = ((img * p.H + ih) * p.W + iw) * p.C + c;
+        float v[VEC];
+        if (VEC == 4) {
+          const float4 t = act_load4(in, idx);
+          v[0] = t.x;
+          v[1 % VEC] = t.y;
+          v[2 % VEC] = t.z;
+          v[3 % VEC] = t.w;
+        } else {
+          v[0] = act_load(in, idx);
+        }
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+          acc[e] = p.kind == 0 ? fmaxf(acc[e], v[e]) : __fadd_rn(acc[e], v[e]);
+        ++count;
+      }
+    }
+    if (p.kind == 1) {
+      const float n = static_cast<float>(count);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[e] = __fdiv_rn(acc[e], n);
+    }
+    const long long o = ((img * p.OH + oh) * p.OW + ow) * p.C + c;
+    if (VEC == 4) {
+      act_store4(out, o, make_float4(acc[0], acc[1 % VEC], acc[2 % VEC], acc[3 % VEC]));
+    } else {
+      act_store(out, o, acc[0]);
+    }
+  }
+}
+
+// ----------------------------------------------------------------- depthwise conv
+struct ConvGeom {
+  long long images;
+  int H, W, C, OH, OW, O;
+  int KH, KW, sh, sw, pt, pl, dh, dw;
+};
+
+struct ConvEpilogue {
+  const float* bias;   // [O] or null
+  const float* scale;  // int8: dequantisation factor per output channel
+  float out_scale;     // int8 output: requantisation scale
+  int act;
+  float act_a, act_b;
+  ActRef res;          // optional residual
+  int has_res;
+};
+
+__device__ __forceinline__ float conv_finish_f32(const ConvEpilogue& e, float acc, float res) {
+  if (e.has_res) acc = __fadd_rn(acc, res);
+  return apply_act(acc, e.act, e.act_a, e.act_b);
+}
+
+// int8 epilogue in the reference's order: float(acc) * r, + bias, (+ residual), then
+// either requantise (ReLU applied on the int8 value) or activation on fp32.
+__device__ __forceinline__ float conv_finish_i8(const ConvEpilogue& e, int acc, int o, float res,
+                                                bool out_i8) {
+  float y = __fmul_rn(static_cast<float>(acc), e.scale[o]);
+  if (e.bias != nullptr) y = __fadd_rn(y, e.bias[o]);
+  if (e.has_res) y = __fadd_rn(y, res);
+  if (out_i8) {
+    int q = quantize_rha(y, e.out_scale);
+    if (e.act == ACT_RELU) q = max(q, 0);
+    return static_cast<float>(q);
+  }
+  return apply_act(y, e.act, e.act_a, e.act_b);
+}
+
+// Weights are stored [KH*KW][C] so that neighbouring threads (neighbouring channels)
+// read neighbouring weights.  One thread computes VEC channels of one output pixel.
+template <int VEC, bool INT8>
+static __global__ void k_depthwise(ActRef in, ActRef out, const void* __restrict__ weights, ConvGeom g,
+                            ConvEpilogue e) {
+  const int cv = g.C / VEC;
+  const long long total = g.images * g.OH * g.OW * cv;
+  const float* wf = static_cast<const float*>(weights);
+  const int8_t* wq = static_cast<const int8_t*>(weights);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>(i % cv) * VEC;
+    long long r = i / cv;
+    const int ow = static_cast<int>(r % g.OW);
+    r /= g.OW;
+    const int oh = static_cast<int>(r % g.OH);
+    const long long img = r / g.OH;
+    float acc[VEC];
+    int iacc[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      acc[v] = (!INT8 && e.bias != nullptr) ? e.bias[c + v] : 0.0f;
+      iacc[v] = 0;
+    }
+    for (int kh = 0; kh < g.KH; ++kh) {
+      const int ih = oh * g.sh - g.pt + kh * g.dh;
+      if (ih < 0 || ih >= g.H) continue;
+      for (int kw = 0; kw < g.KW; ++kw) {
+        const int iw = ow * g.sw - g.pl + kw * g.dw;
+        if (iw < 0 || iw >= g.W) continue;
+        const long long idx = ((img * g.H + ih) * g.W + iw) * g.C + c;
+        const int widx = (kh * g.KW + kw) * g.C + c;
+        float x[VEC];
+        if (VEC == 4) {
+          const float4 t = act_load4(in, idx);
+          x[0] = t.x;
+          x[1 % VEC] = t.y;
+          x[2 % VEC] = t.z;
+          x[3 % VEC] = t.w;
+        } else {
+          x[0] = act_load(in, idx);
+        }
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) {
+          if (INT8) {
+            iacc[v] += static_cast<int>(x[v]) * static_cast<int>(wq[widx + v]);
+          } else {
+            acc[v] = fmaf(x[v], wf[widx + v], acc[v]);
+          }
+        }
+      }
+    }
+    const long long o = ((img * g.OH + oh) * g.OW + ow) * g.C + c;
+    float y[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      const float res = e.has_res ? act_load(e.res, o + v) : 0.0f;
+      y[v] = INT8 ? conv_finish_i8(e, iacc[v], c + v, res, out.fmt == FMT_I8)
+                  : conv_finish_f32(e, acc[v], res);
+    }
+    if (VEC == 4) {
+      act_store4(out, o, make_float4(y[0], y[1 % VEC], y[2 % VEC], y[3 % VEC]));
+    } else {
+      act_store(out, o, y[0]);
+    }
+  }
+}
+
+// ----------------------------------------------------------------- direct conv / matmul
+// CUDA-core convolution: exact fp32 accumulation (fused multiply-add), any geometry.
+// Weights are stored [KH*KW][C][O].  One thread per (pixel, output channel); threads
+// of a warp share the pixel, so activation reads are broadcasts and weight reads coalesce.
+template <bool INT8>
+static __global__ void k_conv_direct(ActRef in, ActRef out, const void* __restrict__ weights, ConvGeom g,
+                              ConvEpilogue e) {
+  const long long total = g.images * g.OH * g.OW * g.O;
+  const float* wf = static_cast<const float*>(weights);
+  const int8_t* wq = static_cast<const int8_t*>(weights);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int o = static_cast<int>(i % g.O);
+    long long r = i / g.O;
+    const int ow = static_cast<int>(r % g.OW);
+    r /= g.OW;
+    const int oh = static_cast<int>(r % g.OH);
+    const long long img = r / g.OH;
+    float acc = (!INT8 && e.bias != nullptr) ? e.bias[o] : 0.0f;
+    int iacc = 0;
+    for (int kh = 0; kh < g.KH; ++kh) {
+      const int ih = oh * g.sh - g.pt + kh * g.dh;
+      if (ih < 0 || ih >= g.H) continue;
+      for (int kw = 0; kw < g.KW; ++kw) {
+        const int iw = ow * g.sw - g.pl + kw * g.dw;
+        if (iw < 0 || iw >= g.W) continue;
+        const long long xb = ((img * g.H + ih) * g.W + iw) * g.C;
+        const long long wb = static_cast<long long>(kh * g.KW + kw) * g.C * g.O + o;
+        for (int c = 0; c < g.C; ++c) {
+          if (INT8) {
+            iacc += static_cast<int>(in.q[xb + c]) * static_cast<int>(wq[wb + static_cast<long long>(c) * g.O]);
+          } else {
+            acc = fmaf(act_load(in, xb + c), wf[wb + static_cast<long long>(c) * g.O], acc);
+          }
+        }
+      }
+    }
+    const float res = e.has_res ? act_load(e.res, i) : 0.0f;
+    const float y = INT8 ? conv_finish_i8(e, iacc, o, res, out.fmt == FMT_I8)
+                         : conv_finish_f32(e, acc, res);
+    act_store(out, i, y);
+  }
+}
+
+// InnerProduct / Gemm on CUDA cores: y[m][n] = sum_k a[m][k] * w[k][n] (weights
+// stored [K][N]); bias is added after the sum, as the reference's matmul + add does.
+template <bool INT8>
+static __global__ void k_matmul_direct(ActRef a, ActRef out, const void* __restrict__ weights,
+                                long long M, int K, int N, ConvEpilogue e, float gemm_beta_unused) {
+  const long long total = M * N;
+  const float* wf = static_cast<const float*>(weights);
+  const int8_t* wq = static_cast<const int8_t*>(weights);
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int n = static_cast<int>(i % N);
+    const long long m = i / N;
+    float acc = 0.0f;
+    int iacc = 0;
+    for (int k = 0; k < K; ++k) {
+      if (INT8) {
+        iacc += static_cast<int>(a.q[m * K + k]) * static_cast<int>(wq[static_cast<long long>(k) * N + n]);
+      } else {
+        acc = fmaf(act_load(a, m * K + k), wf[static_cast<long long>(k) * N + n], acc);
+      }
+    }
+    float y;
+    if (INT8) {
+      y = conv_finish_i8(e, iacc, n, 0.0f, out.fmt == FMT_I8);
+    } else {
+      if (e.bias != nullptr) acc = __fadd_rn(acc, e.bias[n]);
+      y = conv_finish_f32(e, acc, 0.0f);
+    }
+    act_store(out, i, y);
+  }
+}
+
+// Gemm with int8 weights and per-row dynamic activation scales
+// (reference: computeGemmRowScales + dequantizeGemmAccumulator): one block per row.
+//   s_m = absmax == 0 ? 1 : 127 / absmax;  a_q = Q(a, s_m);
+//   y = float(acc) / (s_m * s_B);  y = (y + beta*c) * alpha
+static __global__ void k_gemm_i8_rowscale(ActRef a, ActRef out,
+                                   const int8_t* __restrict__ wq /*[N][K]*/, int K, int N,
+                                   float s_b, const float* __restrict__ c_bias, float alpha,
+                                   float beta, int has_c, int scale_alpha) {
+  extern __shared__ int8_t row_q[];
+  __shared__ float red[32];
+  __shared__ float s_row;
+  const long long m = blockIdx.x;
+  float mx = 0.0f;
+  for (int k = threadIdx.x; k < K; k += blockDim.x) mx = fmaxf(mx, fabsf(act_load(a, m * K + k)));
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.0f;
+    for (int w = 0; w < (blockDim.x + 31) / 32; ++w) t = fmaxf(t, red[w]);
+    s_row = t == 0.0f ? 1.0f : __fdiv_rn(127.0f, t);
+  }
+  __syncthreads();
+  const float s = s_row;
+  for (int k = threadIdx.x; k < K; k += blockDim.x)
+    row_q[k] = static_cast<int8_t>(quantize_rha(act_load(a, m * K + k), s));
+  __syncthreads();
+  const float combined = __fmul_rn(s, s_b);
+  for (int n = threadIdx.x; n < N; n += blockDim.x) {
+    int acc = 0;
+    for (int k = 0; k < K; ++k) acc += static_cast<int>(row_q[k]) * static_cast<int>(wq[static_cast<long long>(n) * K + k]);
+    float y = __fdiv_rn(static_cast<float>(acc), combined);
+    if (has_c) y = __fadd_rn(y, __fmul_rn(c_bias[n], beta));
+    if (scale_alpha) y = __fmul_rn(y, alpha);
+    act_store(out, m * N + n, y);
+  }
+}
+
+// Copy between two logical tensors whose elements correspond by logical (ncnn
+// row-major [c][h][w]) index, optionally transposing a rank-2 source: serves
+// Flatten/Reshape/Squeeze/ExpandDims and rank-2 Permute.
+struct RelayoutParams {
+  long long images;
+  long long count;            // logical elements per image
+  int src_rank, sc, sh, sw;   // logical dims (rank 1: sw; rank 2: sh x sw; rank 3: sc x sh x sw)
+  int dst_rank, dc, dh, dw;
+  int transpose2d;            // source is read as its rank-2 transpose
+};
+
+__device__ __forceinline__ long long storage_offset(int rank, int c_dim, int h_dim, int w_dim,
+                                                    long long logical) {
+  if (rank != 3) return logical;
+  const int w = static_cast<int>(logical % w_dim);
+  const long long r = logical / w_dim;
+  const int h = static_cast<int>(r % h_dim);
+  const int c = static_cast<int>(r / h_dim);
+  return (static_cast<long long>(h) * w_dim + w) * c_dim + c;
+}
+
+static __global__ void k_relayout(ActRef in, ActRef out, RelayoutParams p) {
+  const long long total = p.images * p.count;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long img = i / p.count;
+    const long long l = i - img * p.count;
+    long long src_l = l;
+    if (p.transpose2d) {
+      // destination is [dh][dw] = source[sw'][sh'] transposed
+      const int col = static_cast<int>(l % p.dw);
+      const int row = static_cast<int>(l / p.dw);
+      src_l = static_cast<long long>(col) * p.sw + row;
+    }
+    const long long so = img * p.count + storage_offset(p.src_rank, p.sc, p.sh, p.sw, src_l);
+    const long long dof = img * p.count + storage_offset(p.dst_rank, p.dc, p.dh, p.dw, l);
+    act_store(out, dof, act_load(in, so));
+  }
+}
+
+// ----------------------------------------------------------------- standalone int8 boundary ops
+// Element i belongs to channel (i / inner) % channels.  Scales/bias hold one value or
+// one per channel.
+//   quantize:    y = Q(x, s[c])                                   (ConvertQuantize)
+//   dequantize:  y = float(v) * s[c] (+ bias[c])                  (dequantizeNcnn)
+//   requantize:  t = float(v) * s_in[c] (+ bias[c]); relu?; y = Q(t, s_out[c])
+struct QuantOpParams {
+  long long count;
+  long long inner;
+  int channels;
+  const float* scale_in;
+  int nscale_in;
+  const float* scale_out;
+  int nscale_out;
+  const float* bias;
+  int nbias;
+  int relu;
+};
+
+static __global__ void k_op_quantize(const float* __restrict__ x, int8_t* __restrict__ y, QuantOpParams p) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < p.count;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>((i / p.inner) % p.channels);
+    y[i] = static_cast<int8_t>(quantize_rha(x[i], p.scale_in[p.nscale_in == 1 ? 0 : c]));
+  }
+}
+
+static __global__ void k_op_dequantize(const int* __restrict__ v, float* __restrict__ y, QuantOpParams p) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < p.count;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>((i / p.inner) % p.channels);
+    float t = __fmul_rn(static_cast<float>(v[i]), p.scale_in[p.nscale_in == 1 ? 0 : c]);
+    if (p.bias != nullptr) t = __fadd_rn(t, p.bias[p.nbias == 1 ? 0 : c]);
+    y[i] = t;
+  }
+}
+
+static __global__ void k_op_requantize(const int* __restrict__ v, int8_t* __restrict__ y, QuantOpParams p) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < p.count;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int c = static_cast<int>((i / p.inner) % p.channels);
+    float t = __fmul_rn(static_cast<float>(v[i]), p.scale_in[p.nscale_in == 1 ? 0 : c]);
+    if (p.bias != nullptr) t = __fadd_rn(t, p.bias[p.nbias == 1 ? 0 : c]);
+    if (p.relu) t = fmaxf(t, 0.0f);
+    y[i] = static_cast<int8_t>(quantize_rha(t, p.scale_out[p.nscale_out == 1 ? 0 : c]));
+  }
+}
+
+}  // namespace nb

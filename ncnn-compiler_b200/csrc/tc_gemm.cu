@@ -1,0 +1,341 @@
+#include "tc_gemm.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <mutex>
+
+namespace nb {
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+using EncodeIm2colFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                    const cuuint64_t*, const cuuint64_t*, const int*, const int*,
+                                    cuuint32_t, cuuint32_t, const cuuint32_t*,
+                                    CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn g_encode_tiled = nullptr;
+EncodeIm2colFn g_encode_im2col = nullptr;
+std::once_flag g_driver_once;
+std::string g_driver_error;
+
+void load_driver_entry_points() {
+  std::call_once(g_driver_once, [] {
+    cudaDriverEntryPointQueryResult query;
+    void* fn = nullptr;
+    cudaError_t err =
+        cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &query);
+    if (err != cudaSuccess || query != cudaDriverEntryPointSuccess || fn == nullptr) {
+      g_driver_error = "cuTensorMapEncodeTiled is not available from this driver";
+      return;
+    }
+    g_encode_tiled = reinterpret_cast<EncodeTiledFn>(fn);
+    fn = nullptr;
+    err = cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &query);
+    if (err != cudaSuccess || query != cudaDriverEntryPointSuccess || fn == nullptr) {
+      g_driver_error = "cuTensorMapEncodeIm2col is not available from this driver";
+      return;
+    }
+    g_encode_im2col = reinterpret_cast<EncodeIm2colFn>(fn);
+  });
+}
+
+CUtensorMapSwizzle swizzle_for(int row_bytes) {
+  return row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                          : (row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                             : CU_TENSOR_MAP_SWIZZLE_32B);
+}
+
+CUtensorMapDataType dtype_for(int kind) {
+  return kind == GEMM_I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+}
+
+int elem_bytes(int kind) { return kind == GEMM_I8 ? 1 : 4; }
+
+std::string encode_tiled_2d(CUtensorMap* map, int kind, const void* base, uint64_t inner,
+                            uint64_t outer, uint64_t outer_stride_bytes, uint32_t box_inner,
+                            uint32_t box_outer, int row_bytes) {
+  const cuuint64_t dims[2] = {inner, outer};
+  const cuuint64_t strides[1] = {outer_stride_bytes};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  const CUresult r = g_encode_tiled(map, dtype_for(kind), 2, const_cast<void*>(base), dims,
+                                    strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                    swizzle_for(row_bytes), CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    return "cuTensorMapEncodeTiled failed with code " + std::to_string(static_cast<int>(r)) +
+           " (inner " + std::to_string(inner) + ", outer " + std::to_string(outer) + ", stride " +
+           std::to_string(outer_stride_bytes) + ")";
+  }
+  return {};
+}
+
+std::string encode_im2col(CUtensorMap* map, int kind, const void* base, const TcIm2colView& v,
+                          uint32_t channels_per_pixel, int row_bytes) {
+  const cuuint64_t dims[4] = {v.C, v.W, v.H, v.N};
+  const cuuint64_t strides[3] = {v.stride_w, v.stride_h, v.stride_n};
+  // Bounding box of filter-origin positions: the first is -pad, the last is the
+  // origin of the last output pixel; TMA wants it relative to the tensor's far edge.
+  const int last_w = -v.pad_l + (v.OW - 1) * v.stride_conv_w;
+  const int last_h = -v.pad_t + (v.OH - 1) * v.stride_conv_h;
+  const int lower[2] = {-v.pad_l, -v.pad_t};
+  const int upper[2] = {last_w - (static_cast<int>(v.W) - 1), last_h - (static_cast<int>(v.H) - 1)};
+  const cuuint32_t elem_strides[4] = {1, static_cast<cuuint32_t>(v.stride_conv_w),
+                                      static_cast<cuuint32_t>(v.stride_conv_h), 1};
+  const CUresult r = g_encode_im2col(
+      map, dtype_for(kind), 4, const_cast<void*>(base), dims, strides, lower, upper,
+      channels_per_pixel, kTcBlockM, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+      swizzle_for(row_bytes), CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    return "cuTensorMapEncodeIm2col failed with code " + std::to_string(static_cast<int>(r)) +
+           " (C " + std::to_string(v.C) + ", W " + std::to_string(v.W) + ", H " +
+           std::to_string(v.H) + ", N " + std::to_string(v.N) + ", strides " +
+           std::to_string(v.stride_w) + "/" + std::to_string(v.stride_h) + "/" +
+           std::to_string(v.stride_n) + ", corners " + std::to_string(lower[0]) + "," +
+           std::to_string(lower[1]) + " / " + std::to_string(upper[0]) + "," +
+           std::to_string(upper[1]) + ")";
+  }
+  return {};
+}
+
+// Tile width: every multiple of 16 up to 128 is a legal UMMA N.  Cost model:
+// waves over the SMs times (columns computed + a fixed per-tile term for the
+// A traffic and pipeline fill, which do not shrink with the tile).
+int choose_block_n(long long tiles_m, int N, int sm_count) {
+  int best = 16;
+  double best_cost = 1e300;
+  for (int bn = 16; bn <= 128; bn += 16) {
+    const long long tiles = tiles_m * ((N + bn - 1) / bn);
+    const long long waves = (tiles + sm_count - 1) / sm_count;
+    const double cost = static_cast<double>(waves) * (bn + 24);
+    if (cost < best_cost - 1e-9 || (std::fabs(cost - best_cost) <= 1e-9 && bn > best)) {
+      best_cost = cost;
+      best = bn;
+    }
+  }
+  return best;
+}
+
+void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e, int sm_count) {
+  TcGemmParams& p = L->p;
+  p.M = static_cast<int>(M);
+  p.N = N;
+  p.tiles_m = static_cast<int>((M + kTcBlockM - 1) / kTcBlockM);
+  p.block_n = choose_block_n(p.tiles_m, N, sm_count);
+  p.tiles_n = (N + p.block_n - 1) / p.block_n;
+  const int planes = kind == GEMM_TF32X3 ? 2 : 1;
+  const int stage_bytes = 2 * planes * kTcBlockM * p.row_bytes;
+  const int budget = 200 * 1024;
+  p.stages = std::max(2, std::min(kTcMaxStages, budget / stage_bytes));
+  L->smem_bytes = p.stages * stage_bytes + 1024;
+  // never fewer bytes than half an SM's shared memory: two CTAs must not share an
+  // SM, each allocates tensor memory for itself
+  L->smem_bytes = std::max(L->smem_bytes, 120 * 1024);
+  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  L->grid = static_cast<int>(std::min<long long>(tiles, sm_count));
+  L->kind = kind;
+  p.bias = e.bias;
+  p.scale = e.scale;
+  p.out0 = e.out0;
+  p.out1 = e.out1;
+  p.outq = e.outq;
+  p.res0 = e.res0;
+  p.res1 = e.res1;
+  p.ldo = e.ldo;
+  p.out_mode = e.out_mode;
+  p.act = e.act;
+  p.act_a = e.act_a;
+  p.act_b = e.act_b;
+  p.out_scale = e.out_scale;
+  p.status = e.status;
+}
+
+}  // namespace
+
+int tc_row_bytes(int kind, int channels) {
+  if (kind == GEMM_I8) {
+    if (channels % 16 != 0) return 0;
+    return channels > 64 ? 128 : (channels > 32 ? 64 : 32);
+  }
+  if (channels % 4 != 0) return 0;
+  return 128;
+}
+
+int tc_k_elems(int kind, int channels) {
+  const int rb = tc_row_bytes(kind, channels);
+  if (rb == 0) return 0;
+  return kind == GEMM_I8 ? rb : rb / 4;
+}
+
+std::string tc_plan_conv(TcLaunch* L, int kind, const TcIm2colView& v, const void* w0,
+                         const void* w1, int out_channels, const TcEpilogue& e, int sm_count) {
+  load_driver_entry_points();
+  if (!g_driver_error.empty()) return g_driver_error;
+  const int rb = tc_row_bytes(kind, static_cast<int>(v.C));
+  if (rb == 0) return "channel count is not addressable by TMA (row not a multiple of 16 bytes)";
+  TcGemmParams& p = L->p;
+  std::memset(&p, 0, sizeof(p));
+  p.row_bytes = rb;
+  p.k_elems = kind == GEMM_I8 ? rb : rb / 4;
+  p.c_blocks = static_cast<int>((v.C + p.k_elems - 1) / p.k_elems);
+  p.k_blocks = v.KH * v.KW * p.c_blocks;
+  p.a_im2col = 1;
+  p.OH = v.OH;
+  p.OW = v.OW;
+  p.KW = v.KW;
+  p.stride_h = v.stride_conv_h;
+  p.stride_w = v.stride_conv_w;
+  p.pad_t = v.pad_t;
+  p.pad_l = v.pad_l;
+  p.dil_h = v.dil_h;
+  p.dil_w = v.dil_w;
+  const long long M = static_cast<long long>(v.N) * v.OH * v.OW;
+  if (M > 0x7fffffffll) return "too many output pixels for one launch";
+  finish_plan(L, kind, M, out_channels, e, sm_count);
+
+  std::string err = encode_im2col(&L->map_a0, kind, v.plane0, v, p.k_elems, rb);
+  if (!err.empty()) return err;
+  if (kind == GEMM_TF32X3) {
+    err = encode_im2col(&L->map_a1, kind, v.plane1, v, p.k_elems, rb);
+    if (!err.empty()) return err;
+  } else {
+    L->map_a1 = L->map_a0;
+  }
+  const uint64_t k_total = static_cast<uint64_t>(p.k_blocks) * p.k_elems;
+  err = encode_tiled_2d(&L->map_b0, kind, w0, k_total, out_channels,
+                        k_total * elem_bytes(kind), p.k_elems, p.block_n, rb);
+  if (!err.empty()) return err;
+  if (kind == GEMM_TF32X3) {
+    err = encode_tiled_2d(&L->map_b1, kind, w1, k_total, out_channels,
+                          k_total * elem_bytes(kind), p.k_elems, p.block_n, rb);
+    if (!err.empty()) return err;
+  } else {
+    L->map_b1 = L->map_b0;
+  }
+  return {};
+}
+
+std::string tc_plan_gemm(TcLaunch* L, int kind, const void* a0, const void* a1, long long M, int K,
+                         long long lda, const void* w0, const void* w1, int N,
+                         const TcEpilogue& e, int sm_count) {
+  load_driver_entry_points();
+  if (!g_driver_error.empty()) return g_driver_error;
+  const int es = elem_bytes(kind);
+  if ((lda * es) % 16 != 0) return "row stride of A is not a multiple of 16 bytes";
+  if (M > 0x7fffffffll) return "too many rows for one launch";
+  TcGemmParams& p = L->p;
+  std::memset(&p, 0, sizeof(p));
+  p.row_bytes = 128;
+  p.k_elems = 128 / es;
+  p.c_blocks = (K + p.k_elems - 1) / p.k_elems;
+  p.k_blocks = p.c_blocks;
+  p.a_im2col = 0;
+  p.OH = p.OW = p.KW = 1;
+  p.stride_h = p.stride_w = p.dil_h = p.dil_w = 1;
+  finish_plan(L, kind, M, N, e, sm_count);
+  std::string err = encode_tiled_2d(&L->map_a0, kind, a0, K, M, lda * es, p.k_elems, kTcBlockM, 128);
+  if (!err.empty()) return err;
+  if (kind == GEMM_TF32X3) {
+    err = encode_tiled_2d(&L->map_a1, kind, a1, K, M, lda * es, p.k_elems, kTcBlockM, 128);
+    if (!err.empty()) return err;
+  } else {
+    L->map_a1 = L->map_a0;
+  }
+  const uint64_t k_total = static_cast<uint64_t>(p.k_blocks) * p.k_elems;
+  err = encode_tiled_2d(&L->map_b0, kind, w0, k_total, N, k_total * es, p.k_elems, p.block_n, 128);
+  if (!err.empty()) return err;
+  if (kind == GEMM_TF32X3) {
+    err = encode_tiled_2d(&L->map_b1, kind, w1, k_total, N, k_total * es, p.k_elems, p.block_n, 128);
+    if (!err.empty()) return err;
+  } else {
+    L->map_b1 = L->map_b0;
+  }
+  return {};
+}
+
+cudaError_t tc_launch(const TcLaunch& L, cudaStream_t stream) {
+  static std::once_flag attr_once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(attr_once, [] {
+    const int max_smem = 226 * 1024;  // 227 KB per block minus the static barriers
+    cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<GEMM_TF32>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(tc_gemm_kernel<GEMM_TF32X3>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(tc_gemm_kernel<GEMM_I8>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    attr_err = e;
+  });
+  if (attr_err != cudaSuccess) return attr_err;
+  const dim3 grid(L.grid), block(kTcThreads);
+  switch (L.kind) {
+    case GEMM_TF32:
+      tc_gemm_kernel<GEMM_TF32>
+          <<<grid, block, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1);
+      break;
+    case GEMM_TF32X3:
+      tc_gemm_kernel<GEMM_TF32X3>
+          <<<grid, block, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1);
+      break;
+    default:
+      tc_gemm_kernel<GEMM_I8>
+          <<<grid, block, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1);
+      break;
+  }
+  return cudaGetLastError();
+}
+
+float tf32_round_host(float x) {
+  // round to nearest, ties away from zero, onto 10 explicit mantissa bits
+  uint32_t u;
+  std::memcpy(&u, &x, 4);
+  if ((u & 0x7f800000u) == 0x7f800000u) return x;
+  u += 0x1000u;
+  u &= 0xffffe000u;
+  float r;
+  std::memcpy(&r, &u, 4);
+  return r;
+}
+
+void tc_pack_weights_f32(int kind, const float* w, int O, int I, int KH, int KW, int k_elems,
+                         std::vector<float>* hi, std::vector<float>* lo) {
+  const int c_blocks = (I + k_elems - 1) / k_elems;
+  const size_t cpad = static_cast<size_t>(c_blocks) * k_elems;
+  const size_t k_total = static_cast<size_t>(KH) * KW * cpad;
+  hi->assign(static_cast<size_t>(O) * k_total, 0.0f);
+  if (lo != nullptr) lo->assign(kind == GEMM_TF32X3 ? hi->size() : 0, 0.0f);
+  for (int o = 0; o < O; ++o)
+    for (int i = 0; i < I; ++i)
+      for (int kh = 0; kh < KH; ++kh)
+        for (int kw = 0; kw < KW; ++kw) {
+          const float v = w[((static_cast<size_t>(o) * I + i) * KH + kh) * KW + kw];
+          const size_t dst = o * k_total + (static_cast<size_t>(kh) * KW + kw) * cpad + i;
+          const float h = tf32_round_host(v);
+          (*hi)[dst] = h;
+          if (kind == GEMM_TF32X3 && lo != nullptr) (*lo)[dst] = v - h;
+        }
+}
+
+void tc_pack_weights_i8(const int8_t* w, int O, int I, int KH, int KW, int k_elems,
+                        std::vector<int8_t>* packed) {
+  const int c_blocks = (I + k_elems - 1) / k_elems;
+  const size_t cpad = static_cast<size_t>(c_blocks) * k_elems;
+  const size_t k_total = static_cast<size_t>(KH) * KW * cpad;
+  packed->assign(static_cast<size_t>(O) * k_total, 0);
+  for (int o = 0; o < O; ++o)
+    for (int i = 0; i < I; ++i)
+      for (int kh = 0; kh < KH; ++kh)
+        for (int kw = 0; kw < KW; ++kw)
+          (*packed)[o * k_total + (static_cast<size_t>(kh) * KW + kw) * cpad + i] =
+              w[((static_cast<size_t>(o) * I + i) * KH + kh) * KW + kw];
+}
+
+}  // namespace nb

@@ -1,0 +1,441 @@
+// Tensor-core contraction kernel for sm_100a: out[M,N] = epilogue(A[M,K] * B[N,K]^T).
+//
+// One kernel serves Convolution (A rows are output pixels gathered from an NHWC
+// activation tensor by TMA im2col loads, K runs over filter taps x input
+// channels), InnerProduct and Gemm (A is a plain row-major matrix loaded by
+// tiled TMA).  B is always the packed weight matrix [N][K], K contiguous.
+//
+// Pipeline per CTA (persistent, one CTA per SM, 192 threads):
+//   warp 0     TMA producer: fills a ring of shared-memory stages (A tile 128 x K-block,
+//              B tile block_n x K-block, 128B/64B-swizzled rows)
+//   warp 1     MMA issuer: tcgen05.mma from shared memory into one of two TMEM
+//              accumulators (128 lanes x block_n fp32/int32 columns)
+//   warps 2-5  epilogue: tcgen05.ld of the finished accumulator, then bias, residual,
+//              activation, dequantise/requantise, store (fp32, fp32 split hi/lo, int8)
+// The accumulator is double-buffered so the epilogue of tile i overlaps the
+// main loop of tile i+1.
+//
+// Arithmetic kinds:
+//   GEMM_TF32    one kind::tf32 MMA per K step (fast mode, ~1e-3 relative error)
+//   GEMM_TF32X3  operands are stored as hi/lo tf32 planes (x = hi + lo exactly);
+//                three MMAs lo*hi + hi*lo + hi*hi recover ~fp32 accuracy
+//   GEMM_I8      kind::i8, int32 accumulation, exact
+#pragma once
+
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "ptx_sm100.cuh"
+
+namespace nb {
+
+enum : int { GEMM_TF32 = 0, GEMM_TF32X3 = 1, GEMM_I8 = 2 };
+enum : int { ACT_NONE = 0, ACT_RELU = 1, ACT_LEAKY = 2, ACT_CLIP = 3 };
+// OUT_F32        plain fp32
+// OUT_F32_SPLIT  two fp32 planes: hi = value rounded to tf32, lo = value - hi
+// OUT_I8         int8 after requantisation with out_scale
+// OUT_F32_TF32   fp32 rounded to tf32 (fast mode keeps operands unbiased)
+enum : int { OUT_F32 = 0, OUT_F32_SPLIT = 1, OUT_I8 = 2, OUT_F32_TF32 = 3 };
+
+enum : int {
+  TC_OK = 0,
+  TC_TIMEOUT_PRODUCER = 1,
+  TC_TIMEOUT_MMA = 2,
+  TC_TIMEOUT_EPILOGUE = 3,
+};
+
+constexpr int kTcThreads = 192;
+constexpr int kTcBlockM = 128;
+constexpr int kTcMaxStages = 8;
+constexpr uint32_t kTcTmemCols = 256;           // two accumulators of up to 128 columns
+constexpr uint64_t kTcWaitLimitNs = 2000000000ull;  // a wait longer than 2 s is a bug
+
+struct TcGemmParams {
+  int M, N;
+  int tiles_m, tiles_n, block_n;
+  int k_blocks;   // K iterations per tile = taps * c_blocks
+  int c_blocks;   // channel blocks per filter tap (K blocks for a plain GEMM)
+  int k_elems;    // elements per K block
+  int row_bytes;  // bytes per shared-memory operand row: 128 or 64
+  int stages;
+  // A addressing
+  int a_im2col;
+  int OH, OW, KW;
+  int stride_h, stride_w, pad_t, pad_l, dil_h, dil_w;
+  // epilogue
+  const float* bias;   // [N] or null
+  const float* scale;  // [N] int8 dequantisation factor 1/(s_w*s_in), GEMM_I8 only
+  float* out0;
+  float* out1;
+  int8_t* outq;
+  const float* res0;  // optional residual (same layout as the output), plane hi
+  const float* res1;  // optional residual plane lo
+  long long ldo;      // output row stride in elements
+  int out_mode;
+  int act;
+  float act_a, act_b;  // leaky slope / clip bounds
+  float out_scale;     // requantisation scale (OUT_I8)
+  int* status;         // device word, stays 0 unless a bounded wait gave up
+};
+
+// round-half-away-from-zero exactly as the reference evaluates it in fp32:
+// floor(v + 0.5f) for v >= 0, ceil(v - 0.5f) otherwise, then clamp to [-127, 127].
+__device__ __forceinline__ int quantize_rha(float x, float s) {
+  const float v = __fmul_rn(x, s);
+  const float r = v >= 0.0f ? floorf(__fadd_rn(v, 0.5f)) : ceilf(__fadd_rn(v, -0.5f));
+  const float c = fmaxf(fminf(r, 127.0f), -127.0f);
+  return static_cast<int>(c);
+}
+
+__device__ __forceinline__ float round_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return __uint_as_float(r);
+}
+
+__device__ __forceinline__ float apply_act(float y, int act, float a, float b) {
+  if (act == ACT_RELU) return fmaxf(y, 0.0f);
+  if (act == ACT_LEAKY) return y >= 0.0f ? y : __fmul_rn(y, a);
+  if (act == ACT_CLIP) return fminf(fmaxf(y, a), b);
+  return y;
+}
+
+template <int KIND>
+__device__ __forceinline__ void tc_epilogue_chunk(const TcGemmParams& p, const uint32_t (&v)[16],
+                                                  long long m, int n_first) {
+  float y[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const int n = n_first + j;
+    float t;
+    if (n < p.N) {
+      if (KIND == GEMM_I8) {
+        t = __fmul_rn(static_cast<float>(static_cast<int>(v[j])), __ldg(p.scale + n));
+      } else {
+        t = __uint_as_float(v[j]);
+      }
+      if (p.bias != nullptr) t = __fadd_rn(t, __ldg(p.bias + n));
+    } else {
+      t = 0.0f;
+    }
+    y[j] = t;
+  }
+  const long long row = m * p.ldo;
+  const bool vec4 = (p.ldo % 4 == 0) && (n_first % 4 == 0);
+  if (p.res0 != nullptr) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const int n = n_first + 4 * g;
+      if (vec4 && n + 3 < p.N) {
+        float4 r = __ldg(reinterpret_cast<const float4*>(p.res0 + row + n));
+        if (p.res1 != nullptr) {
+          const float4 l = __ldg(reinterpret_cast<const float4*>(p.res1 + row + n));
+          r.x = __fadd_rn(r.x, l.x);
+          r.y = __fadd_rn(r.y, l.y);
+          r.z = __fadd_rn(r.z, l.z);
+          r.w = __fadd_rn(r.w, l.w);
+        }
+        y[4 * g + 0] = __fadd_rn(y[4 * g + 0], r.x);
+        y[4 * g + 1] = __fadd_rn(y[4 * g + 1], r.y);
+        y[4 * g + 2] = __fadd_rn(y[4 * g + 2], r.z);
+        y[4 * g + 3] = __fadd_rn(y[4 * g + 3], r.w);
+      } else {
+        for (int e = 0; e < 4; ++e) {
+          if (n + e < p.N) {
+            float r = __ldg(p.res0 + row + n + e);
+            if (p.res1 != nullptr) r = __fadd_rn(r, __ldg(p.res1 + row + n + e));
+            y[4 * g + e] = __fadd_rn(y[4 * g + e], r);
+          }
+        }
+      }
+    }
+  }
+  if (p.out_mode == OUT_I8) {
+    int q[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      int t = quantize_rha(y[j], p.out_scale);
+      if (p.act == ACT_RELU) t = max(t, 0);
+      q[j] = t;
+    }
+    if ((p.ldo % 16 == 0) && (n_first % 16 == 0) && n_first + 15 < p.N) {
+      uint32_t w[4];
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        w[g] = (static_cast<uint32_t>(q[4 * g + 0]) & 0xffu) |
+               ((static_cast<uint32_t>(q[4 * g + 1]) & 0xffu) << 8) |
+               ((static_cast<uint32_t>(q[4 * g + 2]) & 0xffu) << 16) |
+               ((static_cast<uint32_t>(q[4 * g + 3]) & 0xffu) << 24);
+      }
+      *reinterpret_cast<uint4*>(p.outq + row + n_first) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+      for (int j = 0; j < 16; ++j)
+        if (n_first + j < p.N) p.outq[row + n_first + j] = static_cast<int8_t>(q[j]);
+    }
+    return;
+  }
+#pragma unroll
+  for (int j = 0; j < 16; ++j) y[j] = apply_act(y[j], p.act, p.act_a, p.act_b);
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const int n = n_first + 4 * g;
+    float hi[4], lo[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float t = y[4 * g + e];
+      if (p.out_mode == OUT_F32) {
+        hi[e] = t;
+        lo[e] = 0.0f;
+      } else {
+        hi[e] = round_tf32(t);
+        lo[e] = __fadd_rn(t, -hi[e]);
+      }
+    }
+    if (vec4 && n + 3 < p.N) {
+      *reinterpret_cast<float4*>(p.out0 + row + n) = make_float4(hi[0], hi[1], hi[2], hi[3]);
+      if (p.out_mode == OUT_F32_SPLIT)
+        *reinterpret_cast<float4*>(p.out1 + row + n) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+    } else {
+      for (int e = 0; e < 4; ++e) {
+        if (n + e < p.N) {
+          p.out0[row + n + e] = hi[e];
+          if (p.out_mode == OUT_F32_SPLIT) p.out1[row + n + e] = lo[e];
+        }
+      }
+    }
+  }
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(kTcThreads, 1)
+tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ CUtensorMap map_a0,
+               const __grid_constant__ CUtensorMap map_a1,
+               const __grid_constant__ CUtensorMap map_b0,
+               const __grid_constant__ CUtensorMap map_b1) {
+  using namespace ptx;
+  constexpr int PLANES = KIND == GEMM_TF32X3 ? 2 : 1;
+
+  extern __shared__ uint8_t tc_smem_raw[];
+  __shared__ __align__(8) uint64_t full_bar[kTcMaxStages];
+  __shared__ __align__(8) uint64_t empty_bar[kTcMaxStages];
+  __shared__ __align__(8) uint64_t tfull_bar[2];
+  __shared__ __align__(8) uint64_t tempty_bar[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(tc_smem_raw) + 1023u) & ~1023u;
+  const uint32_t slot = static_cast<uint32_t>(kTcBlockM) * p.row_bytes;
+  const uint32_t stage_bytes = 2u * PLANES * slot;
+  const uint32_t tx_bytes = PLANES * (slot + static_cast<uint32_t>(p.block_n) * p.row_bytes);
+  const int S = p.stages;
+  const int total_tiles = p.tiles_m * p.tiles_n;
+  volatile int* abort_ptr = &abort_flag;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int i = 0; i < S; ++i) {
+      mbar_init(smem_u32(&full_bar[i]), 1);
+      mbar_init(smem_u32(&empty_bar[i]), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&tfull_bar[i]), 1);
+      mbar_init(smem_u32(&tempty_bar[i]), 4);
+    }
+    fence_mbar_init();
+    prefetch_tensormap(&map_a0);
+    prefetch_tensormap(&map_b0);
+    if (PLANES == 2) {
+      prefetch_tensormap(&map_a1);
+      prefetch_tensormap(&map_b1);
+    }
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_slot), kTcTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      long long issued = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int m_blk = tile / p.tiles_n;
+        const int n_blk = tile - m_blk * p.tiles_n;
+        const long long m0 = static_cast<long long>(m_blk) * kTcBlockM;
+        const int n0 = n_blk * p.block_n;
+        int img = 0, h_base = 0, w_base = 0;
+        if (p.a_im2col) {
+          const long long per_img = static_cast<long long>(p.OH) * p.OW;
+          img = static_cast<int>(m0 / per_img);
+          const int r = static_cast<int>(m0 - img * per_img);
+          const int oh = r / p.OW;
+          const int ow = r - oh * p.OW;
+          h_base = oh * p.stride_h - p.pad_t;
+          w_base = ow * p.stride_w - p.pad_l;
+        }
+        int tap = 0, cb = 0;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait_bounded(smem_u32(&empty_bar[s]), ph ^ 1u, abort_ptr, kTcWaitLimitNs)) {
+            ok = false;
+            break;
+          }
+          const uint32_t fb = smem_u32(&full_bar[s]);
+          mbar_arrive_expect_tx(fb, tx_bytes);
+          const uint32_t a_dst = smem_base + s * stage_bytes;
+          const uint32_t b_dst = a_dst + PLANES * slot;
+          if (p.a_im2col) {
+            const int kh = tap / p.KW;
+            const int kw = tap - kh * p.KW;
+            const uint16_t off_w = static_cast<uint16_t>(kw * p.dil_w);
+            const uint16_t off_h = static_cast<uint16_t>(kh * p.dil_h);
+            tma_load_im2col_4d(a_dst, &map_a0, fb, cb * p.k_elems, w_base, h_base, img, off_w,
+                               off_h);
+            if (PLANES == 2)
+              tma_load_im2col_4d(a_dst + slot, &map_a1, fb, cb * p.k_elems, w_base, h_base, img,
+                                 off_w, off_h);
+          } else {
+            tma_load_2d(a_dst, &map_a0, fb, kb * p.k_elems, static_cast<int>(m0));
+            if (PLANES == 2)
+              tma_load_2d(a_dst + slot, &map_a1, fb, kb * p.k_elems, static_cast<int>(m0));
+          }
+          tma_load_2d(b_dst, &map_b0, fb, kb * p.k_elems, n0);
+          if (PLANES == 2) tma_load_2d(b_dst + slot, &map_b1, fb, kb * p.k_elems, n0);
+          ++issued;
+          if (++cb == p.c_blocks) {
+            cb = 0;
+            ++tap;
+          }
+          if (++s == S) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        if (atomicCAS(const_cast<int*>(abort_ptr), 0, 1) == 0) atomicCAS(p.status, 0, TC_TIMEOUT_PRODUCER);
+      }
+      if (*abort_ptr != 0) {
+        // Some role gave up.  Copies this thread issued may still be landing in
+        // shared memory: wait (bounded) for each of the last S fills to finish.
+        int zero = 0;
+        const long long first = issued > S ? issued - S : 0;
+        for (long long i = first; i < issued; ++i) {
+          const int st = static_cast<int>(i % S);
+          const uint32_t par = static_cast<uint32_t>((i / S) & 1);
+          mbar_wait_bounded(smem_u32(&full_bar[st]), par, &zero, 200000000ull);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = KIND == GEMM_I8
+                                 ? instr_desc(2u, 1u, kTcBlockM, static_cast<uint32_t>(p.block_n))
+                                 : instr_desc(1u, 2u, kTcBlockM, static_cast<uint32_t>(p.block_n));
+      const int k_steps = p.row_bytes / 32;
+      int s = 0;
+      uint32_t ph = 0;
+      int acc = 0;
+      uint32_t acc_ph = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait_bounded(smem_u32(&tempty_bar[acc]), acc_ph ^ 1u, abort_ptr,
+                               kTcWaitLimitNs)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * 128u;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!mbar_wait_bounded(smem_u32(&full_bar[s]), ph, abort_ptr, kTcWaitLimitNs)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_base + s * stage_bytes;
+          const uint32_t b_addr = a_addr + PLANES * slot;
+          for (int k = 0; k < k_steps; ++k) {
+            const uint32_t first = (kb | k) != 0 ? 1u : 0u;
+            const uint64_t a0 = smem_desc_kmajor(a_addr + k * 32, p.row_bytes);
+            const uint64_t b0 = smem_desc_kmajor(b_addr + k * 32, p.row_bytes);
+            if (KIND == GEMM_TF32) {
+              mma_tf32(d_tmem, a0, b0, idesc, first);
+            } else if (KIND == GEMM_TF32X3) {
+              const uint64_t a1 = smem_desc_kmajor(a_addr + slot + k * 32, p.row_bytes);
+              const uint64_t b1 = smem_desc_kmajor(b_addr + slot + k * 32, p.row_bytes);
+              mma_tf32(d_tmem, a1, b0, idesc, first);  // lo * hi
+              mma_tf32(d_tmem, a0, b1, idesc, 1u);     // hi * lo
+              mma_tf32(d_tmem, a0, b0, idesc, 1u);     // hi * hi
+            } else {
+              mma_i8(d_tmem, a0, b0, idesc, first);
+            }
+          }
+          tc_commit(smem_u32(&empty_bar[s]));
+          if (++s == S) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+        if (!ok) break;
+        tc_commit(smem_u32(&tfull_bar[acc]));
+        acc ^= 1;
+        if (acc == 0) acc_ph ^= 1u;
+      }
+      if (!ok) {
+        if (atomicCAS(const_cast<int*>(abort_ptr), 0, 1) == 0) atomicCAS(p.status, 0, TC_TIMEOUT_MMA);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+31] belong to this warp
+    int acc = 0;
+    uint32_t acc_ph = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      const int m_blk = tile / p.tiles_n;
+      const int n_blk = tile - m_blk * p.tiles_n;
+      const long long m = static_cast<long long>(m_blk) * kTcBlockM + quarter * 32 + lane;
+      const int n0 = n_blk * p.block_n;
+      // the vote keeps the warp together: tcgen05.ld below needs all 32 lanes
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&tfull_bar[acc]), acc_ph, abort_ptr,
+                                                     kTcWaitLimitNs)
+                                       ? 1
+                                       : 0) != 0;
+      if (!ok) break;
+      tc_fence_after_sync();
+      const uint32_t t_row =
+          tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc) * 128u;
+      for (int c0 = 0; c0 < p.block_n; c0 += 16) {
+        uint32_t v[16];
+        tmem_ld16(t_row + static_cast<uint32_t>(c0), v);
+        tmem_ld_wait();
+        if (m < p.M && n0 + c0 < p.N) tc_epilogue_chunk<KIND>(p, v, m, n0 + c0);
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+      acc ^= 1;
+      if (acc == 0) acc_ph ^= 1u;
+    }
+    if (!ok && lane == 0) {
+      if (atomicCAS(const_cast<int*>(abort_ptr), 0, 1) == 0) atomicCAS(p.status, 0, TC_TIMEOUT_EPILOGUE);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 1) tmem_dealloc(tmem_base, kTcTmemCols);
+}
+
+}  // namespace nb

@@ -1,0 +1,88 @@
+// Host-side planning for the tensor-core contraction kernel: encodes the TMA
+// tensor maps, picks the tile shape and stage count, and launches.
+#pragma once
+
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "tc_gemm.cuh"
+
+namespace nb {
+
+struct TcLaunch {
+  TcGemmParams p{};
+  alignas(64) CUtensorMap map_a0{};
+  alignas(64) CUtensorMap map_a1{};
+  alignas(64) CUtensorMap map_b0{};
+  alignas(64) CUtensorMap map_b1{};
+  int kind = GEMM_TF32;
+  int grid = 0;
+  int smem_bytes = 0;
+};
+
+// Activation tensor as TMA sees it for an im2col load, innermost dimension first:
+// channels, width, height, images.  For an ordinary NHWC tensor the strides are the
+// dense ones; the 7x7 stem uses an overlapping-window view of a channel-padded image.
+struct TcIm2colView {
+  const void* plane0 = nullptr;
+  const void* plane1 = nullptr;  // lo plane (GEMM_TF32X3 only)
+  uint64_t C = 0, W = 0, H = 0, N = 0;
+  uint64_t stride_w = 0, stride_h = 0, stride_n = 0;  // bytes
+  int KH = 1, KW = 1;
+  int stride_conv_h = 1, stride_conv_w = 1;
+  int pad_t = 0, pad_l = 0;
+  int dil_h = 1, dil_w = 1;
+  int OH = 0, OW = 0;
+};
+
+struct TcEpilogue {
+  const float* bias = nullptr;
+  const float* scale = nullptr;
+  float* out0 = nullptr;
+  float* out1 = nullptr;
+  int8_t* outq = nullptr;
+  const float* res0 = nullptr;
+  const float* res1 = nullptr;
+  long long ldo = 0;
+  int out_mode = OUT_F32;
+  int act = ACT_NONE;
+  float act_a = 0.0f, act_b = 0.0f;
+  float out_scale = 1.0f;
+  int* status = nullptr;
+};
+
+// Elements per K block for a kind and a channel count; 0 when the tensor-core
+// path cannot address that channel count (rows must be multiples of 16 bytes).
+int tc_k_elems(int kind, int channels);
+int tc_row_bytes(int kind, int channels);
+
+// Convolution: M = view.N*OH*OW pixels, N = out_channels.  `w0`/`w1` are the packed
+// weights [out_channels][KH*KW*c_blocks*k_elems] (see tc_pack_weights).
+// Returns an empty string on success, else the reason.
+std::string tc_plan_conv(TcLaunch* launch, int kind, const TcIm2colView& view, const void* w0,
+                         const void* w1, int out_channels, const TcEpilogue& epilogue,
+                         int sm_count);
+
+// Plain GEMM: A is [M][K] row-major with row stride lda elements (planes a0/a1),
+// weights packed [N][Kpad].
+std::string tc_plan_gemm(TcLaunch* launch, int kind, const void* a0, const void* a1, long long M,
+                         int K, long long lda, const void* w0, const void* w1, int N,
+                         const TcEpilogue& epilogue, int sm_count);
+
+cudaError_t tc_launch(const TcLaunch& launch, cudaStream_t stream);
+
+// Packs [O][I][KH][KW] (ncnn order) weights into [O][KH*KW][c_blocks*k_elems] with
+// zero padding, channel innermost.  For fp32 kinds `hi` receives the values
+// rounded to tf32 (GEMM_TF32, GEMM_TF32X3) and `lo` the remainders (GEMM_TF32X3).
+void tc_pack_weights_f32(int kind, const float* w, int O, int I, int KH, int KW, int k_elems,
+                         std::vector<float>* hi, std::vector<float>* lo);
+void tc_pack_weights_i8(const int8_t* w, int O, int I, int KH, int KW, int k_elems,
+                        std::vector<int8_t>* packed);
+
+float tf32_round_host(float x);
+
+}  // namespace nb

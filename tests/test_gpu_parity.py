@@ -1,0 +1,306 @@
+"""Parity of the CUDA path (through the C ABI) against the CPU oracle.
+
+Bars: int8 graphs bit exact; fp32 graphs within a per-tensor relative-L2 bound that
+each test states (the benchmark contract allows at most 1e-3; the default 3xTF32
+mode is held to 1e-4, the CUDA-core mode to 2e-6, the single-pass TF32 fast mode
+to 5e-3 and reported separately).  Element-wise ops (max pooling, Eltwise, BinaryOp,
+ReLU) are exact in every mode that stores plain fp32.
+"""
+import os
+
+import numpy as np
+import pytest
+
+from conftest import FIXTURES, fixture, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+TOL = {0: 1e-4, 1: 5e-3, 2: 2e-6}  # accuracy mode -> relative L2 bound
+
+
+def oracle_batch(oracle, param, bin_, x, shapes=None):
+    m = oracle.Model(param, bin_, input_shapes=shapes)
+    return np.stack([m.run([xi])[0] for xi in x])
+
+
+def run_both(pkg, oracle, param, bin_, x, mode, shapes=None, graph=True):
+    want = oracle_batch(oracle, param, bin_, x, shapes)
+    model = pkg.Model(param, bin_, accuracy_mode=mode, input_shapes=shapes, use_cuda_graph=graph)
+    got = model.run(x)[0]
+    model.close()
+    assert got.shape == want.shape, (got.shape, want.shape)
+    return got, want
+
+
+# ------------------------------------------------------------------ reference fixtures, fp32
+F32_FIXTURES = [
+    ("convolution", (1, 4, 4)), ("convolution_no_bias", (1, 4, 4)), ("convolution_dilated", (1, 7, 7)),
+    ("convolution_asymmetric", (1, 5, 6)), ("convolution_asymmetric_stride", (1, 9, 8)),
+    ("convolution_same_upper", (1, 5, 5)), ("convolution_same_lower", (1, 5, 5)),
+    ("convolution_fp16_storage", (1, 4, 4)), ("convolution_depthwise", (2, 5, 5)),
+    ("convolution_depthwise_fp16_storage", (2, 5, 5)), ("convolution_depthwise_7x7", None),
+    ("convolution_depthwise_asymmetric", None), ("convolution_depthwise_same_upper", None),
+    ("convolution_depthwise_same_lower", None), ("inner_product", (1, 1, 8)),
+    ("inner_product_fused_relu", (2, 1, 3)), ("batch_norm", None),
+    ("pooling", (2, 5, 5)), ("pooling_tail", (2, 4, 4)), ("pooling_average", (2, 5, 5)),
+    ("pooling_asymmetric", None), ("pooling_global_average", (2, 5, 5)),
+    ("pooling_global_average_ignored_params", None), ("pooling_global_max", None),
+    ("pooling_global_max_ignored_params", None), ("pooling_same_upper", (2, 4, 5)),
+    ("pooling_same_lower", None), ("relu", None), ("relu_leaky", (3, 4, 5)), ("binary_mul_scalar", None),
+]
+
+
+def _input_shape(pkg, param, bin_):
+    m = pkg.Model(param, bin_, accuracy_mode=2)
+    s = m.input_shapes
+    m.close()
+    return s
+
+
+@pytest.mark.parametrize("name,shape", F32_FIXTURES)
+@pytest.mark.parametrize("mode", [0, 2])
+def test_reference_fixture_fp32(pkg, oracle, name, shape, mode):  # noqa: ARG001 (shape: documentation)
+    param, bin_ = fixture(name)
+    shapes = _input_shape(pkg, param, bin_)
+    rng = np.random.default_rng(hash(name) % 2**31)
+    x = rng.standard_normal((3, *shapes[0])).astype(np.float32)
+    got, want = run_both(pkg, oracle, param, bin_, x, mode)
+    exact = name.startswith(("pooling_global_max", "relu", "binary")) or name in ("pooling", "pooling_tail",
+                                                                                   "pooling_asymmetric",
+                                                                                   "pooling_same_upper",
+                                                                                   "pooling_same_lower")
+    if exact:
+        assert np.array_equal(got, want)
+    else:
+        assert rel_l2(got, want) <= TOL[mode]
+
+
+@pytest.mark.parametrize("name", ["eltwise_weighted", "binary_add"])
+def test_two_input_fixtures_exact(pkg, oracle, name):
+    param, bin_ = fixture(name)
+    m = pkg.Model(param, bin_, accuracy_mode=2)
+    rng = np.random.default_rng(5)
+    a = rng.standard_normal((4, *m.input_shapes[0])).astype(np.float32)
+    b = rng.standard_normal((4, *m.input_shapes[1])).astype(np.float32)
+    got = m.run(a, b)[0]
+    om = oracle.Model(param, bin_)
+    want = np.stack([om.run([a[i], b[i]])[0] for i in range(4)])
+    assert np.array_equal(got, want)  # the reference's own tests demand exact equality here
+
+
+def test_inner_product_dynamic_m_rows(pkg, oracle):
+    param, bin_ = fixture("inner_product_dynamic_m")
+    shapes = [[1, 5, 4]]
+    x = np.random.default_rng(3).standard_normal((2, 1, 5, 4)).astype(np.float32)
+    for mode in (0, 2):
+        got, want = run_both(pkg, oracle, param, bin_, x, mode, shapes)
+        assert got.shape == (2, 5, 3)
+        assert rel_l2(got, want) <= TOL[mode]
+
+
+def test_gemm_fixture(pkg, oracle):
+    param, bin_ = fixture("gemm")
+    x = np.random.default_rng(4).standard_normal((3, 2, 1, 3)).astype(np.float32)
+    got, want = run_both(pkg, oracle, param, bin_, x, 2)
+    assert got.shape == (3, 3, 4)
+    assert rel_l2(got, want) <= 2e-6
+
+
+# ------------------------------------------------------------------ reference fixtures, int8 (bit exact)
+INT8_FIXTURES = [
+    ("convolution_int8_term1", [2, 3, 4]), ("convolution_int8_term2", [2, 3, 4]),
+    ("convolution_int8_term101", [2, 3, 4]), ("convolution_int8_term102", [2, 3, 4]),
+    ("depthwise_int8_term1", [3, 3, 4]), ("depthwise_int8_term2", [3, 3, 4]),
+    ("depthwise_int8_term101", [3, 3, 4]), ("depthwise_int8_term102", [3, 3, 4]),
+    ("inner_product_int8_term1", [1, 1, 4]), ("inner_product_int8_term2", [1, 1, 4]),
+    ("int8_complete_chain", [2, 3, 4]),
+]
+
+
+@pytest.mark.parametrize("name,shape", INT8_FIXTURES)
+def test_reference_fixture_int8_bit_exact(pkg, oracle, name, shape):
+    param, bin_ = fixture(name)
+    rng = np.random.default_rng(0xC001)
+    x = rng.uniform(-1.5, 1.5, (5, *shape)).astype(np.float32)  # the reference's int8 test range
+    got, want = run_both(pkg, oracle, param, bin_, x, 0, [shape])
+    assert np.array_equal(got, want)
+
+
+def test_gemm_int8_fixture_bit_exact(pkg, oracle):
+    param, bin_ = fixture("gemm_int8_term2")
+    x = np.random.default_rng(0x6E22).uniform(-1.5, 1.5, (4, 2, 1, 3)).astype(np.float32)
+    x[1, :, :, 1] = 0.0  # an all-zero row takes the scale-1 branch
+    got, want = run_both(pkg, oracle, param, bin_, x, 0)
+    assert np.array_equal(got, want)
+
+
+def test_quantize_rounding_adversarial(pkg):
+    """x*s values that separate floor(v+0.5f) from roundf/rintf, through the operator ABI."""
+    import torch
+    v = np.array([0.49999997, -0.49999997, 0.5, -0.5, 1.5, -1.5, 2.5, -2.5, 126.5, -126.5, 127.49, -127.49,
+                  200.0, -200.0, 0.0, -0.0, 8388609.0], np.float32)
+    # 0.49999997f + 0.5f rounds to 1.0f in fp32, so the reference yields 1 (roundf would give 0)
+    want = np.array([1, -1, 1, -1, 2, -2, 3, -3, 127, -127, 127, -127, 127, -127, 0, 0, 127], np.int8)
+    x = torch.from_numpy(v).cuda()
+    s = torch.ones(1, device="cuda")
+    y = torch.empty(v.size, dtype=torch.int8, device="cuda")
+    pkg.op_quantize(x.data_ptr(), y.data_ptr(), v.size, 1, 1, s.data_ptr(), 1, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert np.array_equal(y.cpu().numpy(), want)
+
+
+def test_standalone_dequantize_requantize(pkg, oracle):
+    import torch
+    rng = np.random.default_rng(11)
+    C, inner = 6, 35
+    acc = rng.integers(-(2**26), 2**26, (3, inner, C)).astype(np.int32)  # channel-last, |acc| > 2^24 included
+    s_in = rng.uniform(1e-4, 1e-3, C).astype(np.float32)
+    s_out = rng.uniform(0.5, 4.0, C).astype(np.float32)
+    bias = rng.standard_normal(C).astype(np.float32)
+    t = lambda a: torch.from_numpy(a).cuda()
+    d_acc, d_si, d_so, d_b = t(acc), t(s_in), t(s_out), t(bias)
+    y = torch.empty(acc.shape, dtype=torch.float32, device="cuda")
+    q = torch.empty(acc.shape, dtype=torch.int8, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    pkg.op_dequantize(d_acc.data_ptr(), y.data_ptr(), acc.size, 1, C, d_si.data_ptr(), C, d_b.data_ptr(), C, st)
+    pkg.op_requantize(d_acc.data_ptr(), q.data_ptr(), acc.size, 1, C, d_si.data_ptr(), C, d_so.data_ptr(), C,
+                      d_b.data_ptr(), C, True, st)
+    torch.cuda.synchronize()
+    assert np.array_equal(y.cpu().numpy(), oracle.op_dequantize(acc, s_in, bias))
+    assert np.array_equal(q.cpu().numpy(), oracle.op_requantize(acc, s_in, s_out, bias, relu=True))
+
+
+# ------------------------------------------------------------------ benchmark configurations
+def test_config0_single_conv(pkg, oracle, tmp_path):
+    param, bin_ = pkg.zoo.single_conv(str(tmp_path / "cfg0"))
+    x = np.random.default_rng(100).uniform(-1, 1, (2, 64, 56, 56)).astype(np.float32)
+    errs = {}
+    for mode in (0, 1, 2):
+        got, want = run_both(pkg, oracle, param, bin_, x, mode)
+        errs[mode] = rel_l2(got, want)
+        assert errs[mode] <= TOL[mode], errs
+    print("config0 rel-L2 by mode", errs)
+
+
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_resnet18_fp32(pkg, oracle, tmp_path, mode):
+    param, bin_ = pkg.zoo.resnet18(str(tmp_path / "r18"))
+    x = np.random.default_rng(200).uniform(-1, 1, (3, 3, 224, 224)).astype(np.float32)
+    got, want = run_both(pkg, oracle, param, bin_, x, mode)
+    err = rel_l2(got, want)
+    print(f"resnet18 mode {mode} rel-L2 {err:.3e}")
+    assert err <= {0: 2e-4, 1: 2e-2, 2: 1e-5}[mode]
+    if mode != 1:
+        assert np.array_equal(np.argmax(got, 1), np.argmax(want, 1))
+
+
+def test_resnet18_int8_bit_exact(pkg, oracle, tmp_path):
+    param, bin_ = pkg.zoo.resnet18(str(tmp_path / "r18q"), int8=True)
+    x = np.random.default_rng(400).uniform(-1, 1, (3, 3, 224, 224)).astype(np.float32)
+    got, want = run_both(pkg, oracle, param, bin_, x, 0)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("mode", [0, 2])
+def test_mobilenet_v2_fp32(pkg, oracle, tmp_path, mode):
+    param, bin_ = pkg.zoo.mobilenet_v2(str(tmp_path / "mbv2"))
+    x = np.random.default_rng(300).uniform(-1, 1, (2, 3, 224, 224)).astype(np.float32)
+    got, want = run_both(pkg, oracle, param, bin_, x, mode)
+    err = rel_l2(got, want)
+    print(f"mobilenet_v2 mode {mode} rel-L2 {err:.3e}")
+    assert err <= {0: 2e-4, 2: 1e-5}[mode]
+
+
+@pytest.mark.parametrize("m,k,n", [(1, 512, 512), (32, 1024, 512), (256, 512, 4096)])
+def test_inner_product_sweep(pkg, oracle, tmp_path, m, k, n):
+    x = np.random.default_rng(500).uniform(-1, 1, (m, 1, 1, k)).astype(np.float32)
+    param, bin_ = pkg.zoo.inner_product(str(tmp_path / "ip"), k, n)
+    got, want = run_both(pkg, oracle, param, bin_, x, 0)
+    assert rel_l2(got, want) <= 1e-4
+    param, bin_ = pkg.zoo.inner_product(str(tmp_path / "ipq"), k, n, int8=True)
+    got, want = run_both(pkg, oracle, param, bin_, x, 0)
+    assert np.array_equal(got, want)
+
+
+# ------------------------------------------------------------------ properties at full size
+def test_batch_equals_single_calls(pkg, tmp_path):
+    """The batched entry is an extension: it must equal n single-image calls bit for bit."""
+    param, bin_ = pkg.zoo.resnet18(str(tmp_path / "r18q"), int8=True, size=64)
+    x = np.random.default_rng(1).uniform(-1, 1, (5, 3, 64, 64)).astype(np.float32)
+    m = pkg.Model(param, bin_)
+    batched = m.run(x)[0]
+    singles = np.stack([m.run(xi)[0] for xi in x])
+    assert np.array_equal(batched, singles)
+    m.close()
+    param, bin_ = pkg.zoo.mobilenet_v2(str(tmp_path / "mb"), size=64)
+    m = pkg.Model(param, bin_)
+    batched = m.run(x)[0]
+    singles = np.stack([m.run(xi)[0] for xi in x])
+    assert np.array_equal(batched, singles)  # same kernels, same order of operations per image
+
+
+def test_full_batch_properties(pkg, tmp_path):
+    """Batch 64 at 224x224 (too slow for the oracle): images are independent, so permuting
+    the batch permutes the outputs, and repeated calls give identical bytes."""
+    param, bin_ = pkg.zoo.resnet18(str(tmp_path / "r18"))
+    x = np.random.default_rng(2).uniform(-1, 1, (64, 3, 224, 224)).astype(np.float32)
+    m = pkg.Model(param, bin_)
+    y0 = m.run(x)[0]
+    y1 = m.run(x)[0]
+    assert np.array_equal(y0, y1)
+    perm = np.random.default_rng(3).permutation(64)
+    y2 = m.run(x[perm])[0]
+    assert np.array_equal(y2, y0[perm])
+    assert np.isfinite(y0).all()
+
+
+def test_graph_replay_equals_eager(pkg, tmp_path):
+    param, bin_ = pkg.zoo.mobilenet_v2(str(tmp_path / "mb"), size=96)
+    x = np.random.default_rng(9).uniform(-1, 1, (4, 3, 96, 96)).astype(np.float32)
+    a = pkg.Model(param, bin_, use_cuda_graph=True).run(x)[0]
+    b = pkg.Model(param, bin_, use_cuda_graph=False).run(x)[0]
+    assert np.array_equal(a, b)
+
+
+def test_device_pointer_entry(pkg, tmp_path):
+    import torch
+    param, bin_ = pkg.zoo.single_conv(str(tmp_path / "c"), h=20, w=24)
+    m = pkg.Model(param, bin_)
+    x = torch.rand(6, 64, 20, 24, device="cuda") * 2 - 1
+    y = torch.empty(6, 64, 20, 24, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    m.run_device(6, [x.data_ptr()], [y.data_ptr()], stream)
+    torch.cuda.synchronize()
+    m.check_status()
+    host = m.run(x.cpu().numpy())[0]
+    assert np.array_equal(y.cpu().numpy(), host)
+
+
+def test_null_pointer_and_bad_batch_status(pkg, tmp_path):
+    param, bin_ = pkg.zoo.single_conv(str(tmp_path / "c"), h=8, w=8)
+    m = pkg.Model(param, bin_)
+    x = np.zeros((1, 64, 8, 8), np.float32)
+    y = np.zeros((1, 64, 8, 8), np.float32)
+    assert m.run_raw(1, [None], [y.ctypes.data]) == 1  # NULL input -> status 1, like the reference wrapper
+    assert m.run_raw(1, [x.ctypes.data], [None]) == 1
+    assert m.run_raw(0, [x.ctypes.data], [y.ctypes.data]) == 2
+    assert m.run_raw(1, [x.ctypes.data], [y.ctypes.data]) == 0
+
+
+def test_unsupported_layers_fail_loudly(pkg, tmp_path):
+    for name in ("softmax", "sigmoid", "deconvolution", "concat"):
+        param = os.path.join(FIXTURES, name + ".param")
+        with pytest.raises(pkg.NcnnB200Error) as e:
+            pkg.Model(param, os.path.join(FIXTURES, "relu.bin"))
+        assert e.value.status == 8
+
+
+def test_emit_stub_header_matches_reference_layout(pkg, tmp_path):
+    param, bin_ = fixture("relu")
+    m = pkg.Model(param, bin_)
+    m.emit_stub("relu_all", param, bin_, str(tmp_path))
+    header = (tmp_path / "relu_all.h").read_text()
+    # the reference records 1217 bytes for this header (test/Native/static_artifact_baseline.json:10-13)
+    assert len(header.encode()) == 1217
+    assert "int relu_all(const float *input1, float *output1);" in header
+    assert "#define RELU_ALL_INPUT1_ELEMENTS UINT64_C(60)" in header
