@@ -203,6 +203,8 @@ class EngineImpl {
   void plan_memory();
   ActRef ref(int tensor, int64_t n) const;
   bool emit_node(Plan& plan, const Node& node, int64_t n, std::string* err);
+  void make_edge_steps(int64_t n, const std::vector<const float*>& d_in, const std::vector<float*>& d_out,
+                       std::vector<Step>* pre, std::vector<Step>* post);
 };
 
 // ---------------------------------------------------------------------- import
@@ -1559,6 +1561,90 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
   return fail(err, "internal: unknown node kind");
 }
 
+void EngineImpl::make_edge_steps(int64_t n, const std::vector<const float*>& d_in,
+                                 const std::vector<float*>& d_out, std::vector<Step>* pre,
+                                 std::vector<Step>* post) {
+  for (size_t i = 0; i < inputs_.size(); ++i) {
+    const Tensor& t = tensors_[resolve(inputs_[i])];
+    const ActRef dst = ref(inputs_[i], n);
+    const float* src_ptr = d_in[i];
+    Step s;
+    s.name = "input:" + t.name;
+    s.bytes = static_cast<double>(t.logical()) * n * (4 + (t.fmt == FMT_I8 ? 1 : 4 * t.planes()));
+    if (t.rank == 3) {
+      EdgeParams ep{};
+      ep.images = n;
+      ep.C = t.c;
+      ep.H = t.h;
+      ep.W = t.w;
+      ep.Cp = t.Cp;
+      ep.Wp = t.Wp;
+      ep.w_off = t.w_off;
+      ep.quant_scale = t.input_quant_scale;
+      if (t.c <= 4 && (t.Cp == 4 || t.Cp == 16)) {
+        const int grid = grid_for(n * t.h * t.w);
+        s.kernel = "k_chw_to_nhwc_small";
+        s.run = [=](cudaStream_t st) {
+          k_chw_to_nhwc_small<<<grid, 256, 0, st>>>(src_ptr, dst, ep);
+          return launch_ok();
+        };
+      } else {
+        const dim3 grid((t.h * t.w + 31) / 32, (t.c + 31) / 32, static_cast<unsigned>(n));
+        s.kernel = "k_chw_to_nhwc_tiled";
+        s.run = [=](cudaStream_t st) {
+          k_chw_to_nhwc_tiled<<<grid, dim3(32, 8), 0, st>>>(src_ptr, dst, ep);
+          return launch_ok();
+        };
+      }
+    } else {
+      ActRef src;
+      src.fmt = FMT_F32;
+      src.p0 = const_cast<float*>(src_ptr);
+      UnaryParams up{};
+      up.op = UN_COPY;
+      const long long count = t.logical() * n;
+      const int grid = grid_for(count);
+      s.kernel = "k_unary";
+      s.run = [=](cudaStream_t st) {
+        k_unary<1><<<grid, 256, 0, st>>>(src, dst, count, up);
+        return launch_ok();
+      };
+    }
+    pre->push_back(std::move(s));
+  }
+  for (size_t i = 0; i < outputs_.size(); ++i) {
+    const Tensor& t = tensors_[resolve(outputs_[i])];
+    const ActRef src = ref(outputs_[i], n);
+    float* dst_ptr = d_out[i];
+    Step s;
+    s.name = "output:" + t.name;
+    s.bytes = static_cast<double>(t.logical()) * n * (4 + (t.fmt == FMT_I8 ? 1 : 4 * t.planes()));
+    if (t.rank == 3) {
+      const dim3 grid((t.h * t.w + 31) / 32, (t.c + 31) / 32, static_cast<unsigned>(n));
+      const int C = t.c, HW = t.h * t.w, Cp = t.Cp;
+      s.kernel = "k_nhwc_to_chw_tiled";
+      s.run = [=](cudaStream_t st) {
+        k_nhwc_to_chw_tiled<<<grid, dim3(32, 8), 0, st>>>(src, dst_ptr, n, C, HW, Cp);
+        return launch_ok();
+      };
+    } else {
+      ActRef dst;
+      dst.fmt = FMT_F32;
+      dst.p0 = dst_ptr;
+      UnaryParams up{};
+      up.op = UN_COPY;
+      const long long count = t.logical() * n;
+      const int grid = grid_for(count);
+      s.kernel = "k_unary";
+      s.run = [=](cudaStream_t st) {
+        k_unary<1><<<grid, 256, 0, st>>>(src, dst, count, up);
+        return launch_ok();
+      };
+    }
+    post->push_back(std::move(s));
+  }
+}
+
 Plan* EngineImpl::plan_for(int64_t n) {
   auto it = plans_.find(n);
   if (it != plans_.end()) return &it->second;
@@ -1638,66 +1724,17 @@ int EngineImpl::run(int64_t n, const float* const* in, float* const* out, bool h
     for (size_t i = 0; i < outputs_.size(); ++i) d_out[i] = out[i];
   }
 
+  std::vector<Step> pre, post;
+  make_edge_steps(n, d_in, d_out, &pre, &post);
   auto issue = [&](cudaStream_t s) -> cudaError_t {
-    for (size_t i = 0; i < inputs_.size(); ++i) {
-      const Tensor& t = tensors_[resolve(inputs_[i])];
-      const ActRef dst = ref(inputs_[i], n);
-      if (t.rank == 3) {
-        EdgeParams ep{};
-        ep.images = n;
-        ep.C = t.c;
-        ep.H = t.h;
-        ep.W = t.w;
-        ep.Cp = t.Cp;
-        ep.Wp = t.Wp;
-        ep.w_off = t.w_off;
-        ep.quant_scale = t.input_quant_scale;
-        if (t.c <= 4 && (t.Cp == 4 || t.Cp == 16)) {
-          k_chw_to_nhwc_small<<<grid_for(n * t.h * t.w), 256, 0, s>>>(d_in[i], dst, ep);
-        } else {
-          const dim3 grid((t.h * t.w + 31) / 32, (t.c + 31) / 32, static_cast<unsigned>(n));
-          k_chw_to_nhwc_tiled<<<grid, dim3(32, 8), 0, s>>>(d_in[i], dst, ep);
+    for (const std::vector<Step>* list : {static_cast<const std::vector<Step>*>(&pre), static_cast<const std::vector<Step>*>(&plan->steps), static_cast<const std::vector<Step>*>(&post)}) {
+      for (const Step& step : *list) {
+        const cudaError_t e = step.run(s);
+        if (e != cudaSuccess) {
+          error_ = "launch of " + step.kernel + " for layer " + step.name + " failed: " + cudaGetErrorString(e);
+          return e;
         }
-      } else {
-        ActRef src;
-        src.fmt = FMT_F32;
-        src.p0 = const_cast<float*>(d_in[i]);
-        UnaryParams up{};
-        up.inner = 1;
-        up.channels = 1;
-        up.op = UN_COPY;
-        const long long count = t.logical() * n;
-        k_unary<1><<<grid_for(count), 256, 0, s>>>(src, dst, count, up);
       }
-      const cudaError_t e = cudaGetLastError();
-      if (e != cudaSuccess) return e;
-    }
-    for (const Step& step : plan->steps) {
-      const cudaError_t e = step.run(s);
-      if (e != cudaSuccess) {
-        error_ = "launch of " + step.kernel + " for layer " + step.name + " failed: " + cudaGetErrorString(e);
-        return e;
-      }
-    }
-    for (size_t i = 0; i < outputs_.size(); ++i) {
-      const Tensor& t = tensors_[resolve(outputs_[i])];
-      const ActRef src = ref(outputs_[i], n);
-      if (t.rank == 3) {
-        const dim3 grid((t.h * t.w + 31) / 32, (t.c + 31) / 32, static_cast<unsigned>(n));
-        k_nhwc_to_chw_tiled<<<grid, dim3(32, 8), 0, s>>>(src, d_out[i], n, t.c, t.h * t.w, t.Cp);
-      } else {
-        ActRef dst;
-        dst.fmt = FMT_F32;
-        dst.p0 = d_out[i];
-        UnaryParams up{};
-        up.inner = 1;
-        up.channels = 1;
-        up.op = UN_COPY;
-        const long long count = t.logical() * n;
-        k_unary<1><<<grid_for(count), 256, 0, s>>>(src, dst, count, up);
-      }
-      const cudaError_t e = cudaGetLastError();
-      if (e != cudaSuccess) return e;
     }
     return cudaSuccess;
   };
@@ -1761,13 +1798,26 @@ int EngineImpl::profile(int64_t n, int repeat, std::vector<LayerTiming>* out) {
   Plan* plan = plan_for(n);
   if (plan == nullptr) return 6;
   out->clear();
-  std::vector<cudaEvent_t> ev(plan->steps.size() + 1);
+  // every launch of one run: input edges, layers, output edges (edges need the staging
+  // buffers a previous host-pointer run of this batch size created)
+  std::vector<Step> all;
+  if (!plan->d_in.empty()) {
+    std::vector<Step> pre, post;
+    std::vector<const float*> d_in(plan->d_in.begin(), plan->d_in.end());
+    make_edge_steps(n, d_in, plan->d_out, &pre, &post);
+    all = pre;
+    all.insert(all.end(), plan->steps.begin(), plan->steps.end());
+    all.insert(all.end(), post.begin(), post.end());
+  } else {
+    all = plan->steps;
+  }
+  std::vector<cudaEvent_t> ev(all.size() + 1);
   for (auto& e : ev) cudaEventCreate(&e);
-  std::vector<double> total(plan->steps.size(), 0.0);
+  std::vector<double> total(all.size(), 0.0);
   for (int r = 0; r < repeat + 1; ++r) {
     cudaEventRecord(ev[0], stream_);
-    for (size_t i = 0; i < plan->steps.size(); ++i) {
-      const cudaError_t e = plan->steps[i].run(stream_);
+    for (size_t i = 0; i < all.size(); ++i) {
+      const cudaError_t e = all[i].run(stream_);
       if (e != cudaSuccess) {
         error_ = std::string("launch failed while profiling: ") + cudaGetErrorString(e);
         return 6;
@@ -1779,19 +1829,19 @@ int EngineImpl::profile(int64_t n, int repeat, std::vector<LayerTiming>* out) {
       return 6;
     }
     if (r == 0) continue;  // warm-up
-    for (size_t i = 0; i < plan->steps.size(); ++i) {
+    for (size_t i = 0; i < all.size(); ++i) {
       float ms = 0.0f;
       cudaEventElapsedTime(&ms, ev[i], ev[i + 1]);
       total[i] += ms;
     }
   }
-  for (size_t i = 0; i < plan->steps.size(); ++i) {
+  for (size_t i = 0; i < all.size(); ++i) {
     LayerTiming t;
-    t.name = plan->steps[i].name;
-    t.kernel = plan->steps[i].kernel;
+    t.name = all[i].name;
+    t.kernel = all[i].kernel;
     t.ms = static_cast<float>(total[i] / std::max(repeat, 1));
-    t.flops = plan->steps[i].flops;
-    t.bytes = plan->steps[i].bytes;
+    t.flops = all[i].flops;
+    t.bytes = all[i].bytes;
     out->push_back(t);
   }
   for (auto& e : ev) cudaEventDestroy(e);
