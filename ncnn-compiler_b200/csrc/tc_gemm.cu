@@ -130,10 +130,12 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
   p.block_n = choose_block_n(p.tiles_m, N, sm_count);
   p.tiles_n = (N + p.block_n - 1) / p.block_n;
   const int planes = kind == GEMM_TF32X3 ? 2 : 1;
-  const int stage_bytes = 2 * planes * kTcBlockM * p.row_bytes;
-  const int budget = 200 * 1024;
-  p.stages = std::max(2, std::min(kTcMaxStages, budget / stage_bytes));
-  L->smem_bytes = p.stages * stage_bytes + 1024;
+  // a stage holds the A tile(s) and block_n rows of B, every sub-buffer 1 KB aligned
+  const int b_bytes = (p.block_n * p.row_bytes + 1023) / 1024 * 1024;
+  p.stage_bytes = planes * (kTcBlockM * p.row_bytes + b_bytes);
+  const int budget = 220 * 1024;
+  p.stages = std::max(2, std::min(kTcMaxStages, budget / p.stage_bytes));
+  L->smem_bytes = p.stages * p.stage_bytes + 1024;
   // never fewer bytes than half an SM's shared memory: two CTAs must not share an
   // SM, each allocates tensor memory for itself
   L->smem_bytes = std::max(L->smem_bytes, 120 * 1024);
@@ -154,6 +156,7 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
   p.act_b = e.act_b;
   p.out_scale = e.out_scale;
   p.status = e.status;
+  p.trace = e.trace;
 }
 
 }  // namespace

@@ -59,6 +59,7 @@ struct TcGemmParams {
   int k_elems;    // elements per K block
   int row_bytes;  // bytes per shared-memory operand row: 128 or 64
   int stages;
+  int stage_bytes;  // bytes of one ring stage: planes * (A tile + B tile rounded to 1 KB)
   // A addressing
   int a_im2col;
   int OH, OW, KW;
@@ -77,6 +78,7 @@ struct TcGemmParams {
   float act_a, act_b;  // leaky slope / clip bounds
   float out_scale;     // requantisation scale (OUT_I8)
   int* status;         // device word, stays 0 unless a bounded wait gave up
+  long long* trace;    // optional (bring-up): per-role clock stamps of CTA 0, 8 values per tile
 };
 
 // round-half-away-from-zero exactly as the reference evaluates it in fp32:
@@ -228,7 +230,8 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
   const int lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(tc_smem_raw) + 1023u) & ~1023u;
   const uint32_t slot = static_cast<uint32_t>(kTcBlockM) * p.row_bytes;
-  const uint32_t stage_bytes = 2u * PLANES * slot;
+  const uint32_t stage_bytes = static_cast<uint32_t>(p.stage_bytes);
+  const uint32_t b_slot = (stage_bytes / PLANES) - slot;  // B tile, rounded to 1 KB
   const uint32_t tx_bytes = PLANES * (slot + static_cast<uint32_t>(p.block_n) * p.row_bytes);
   const int S = p.stages;
   const int total_tiles = p.tiles_m * p.tiles_n;
@@ -283,6 +286,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
           h_base = oh * p.stride_h - p.pad_t;
           w_base = ow * p.stride_w - p.pad_l;
         }
+        if (p.trace != nullptr && blockIdx.x == 0) p.trace[(tile / gridDim.x) * 8 + 0] = clock64();
         int tap = 0, cb = 0;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait_bounded(smem_u32(&empty_bar[s]), ph ^ 1u, abort_ptr, kTcWaitLimitNs)) {
@@ -309,7 +313,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
               tma_load_2d(a_dst + slot, &map_a1, fb, kb * p.k_elems, static_cast<int>(m0));
           }
           tma_load_2d(b_dst, &map_b0, fb, kb * p.k_elems, n0);
-          if (PLANES == 2) tma_load_2d(b_dst + slot, &map_b1, fb, kb * p.k_elems, n0);
+          if (PLANES == 2) tma_load_2d(b_dst + b_slot, &map_b1, fb, kb * p.k_elems, n0);
           ++issued;
           if (++cb == p.c_blocks) {
             cb = 0;
@@ -355,6 +359,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
           break;
         }
         tc_fence_after_sync();
+        if (p.trace != nullptr && blockIdx.x == 0) p.trace[(tile / gridDim.x) * 8 + 1] = clock64();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * 128u;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait_bounded(smem_u32(&full_bar[s]), ph, abort_ptr, kTcWaitLimitNs)) {
@@ -372,7 +377,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
               mma_tf32(d_tmem, a0, b0, idesc, first);
             } else if (KIND == GEMM_TF32X3) {
               const uint64_t a1 = smem_desc_kmajor(a_addr + slot + k * 32, p.row_bytes);
-              const uint64_t b1 = smem_desc_kmajor(b_addr + slot + k * 32, p.row_bytes);
+              const uint64_t b1 = smem_desc_kmajor(b_addr + b_slot + k * 32, p.row_bytes);
               mma_tf32(d_tmem, a1, b0, idesc, first);  // lo * hi
               mma_tf32(d_tmem, a0, b1, idesc, 1u);     // hi * lo
               mma_tf32(d_tmem, a0, b0, idesc, 1u);     // hi * hi
@@ -388,6 +393,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
         }
         if (!ok) break;
         tc_commit(smem_u32(&tfull_bar[acc]));
+        if (p.trace != nullptr && blockIdx.x == 0) p.trace[(tile / gridDim.x) * 8 + 2] = clock64();
         acc ^= 1;
         if (acc == 0) acc_ph ^= 1u;
       }
@@ -406,6 +412,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
       const int n_blk = tile - m_blk * p.tiles_n;
       const long long m = static_cast<long long>(m_blk) * kTcBlockM + quarter * 32 + lane;
       const int n0 = n_blk * p.block_n;
+      if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64) p.trace[(tile / gridDim.x) * 8 + 3] = clock64();
       // the vote keeps the warp together: tcgen05.ld below needs all 32 lanes
       ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&tfull_bar[acc]), acc_ph, abort_ptr,
                                                      kTcWaitLimitNs)
@@ -413,6 +420,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
                                        : 0) != 0;
       if (!ok) break;
       tc_fence_after_sync();
+      if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64) p.trace[(tile / gridDim.x) * 8 + 4] = clock64();
       const uint32_t t_row =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc) * 128u;
       for (int c0 = 0; c0 < p.block_n; c0 += 16) {
@@ -423,6 +431,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
       }
       tc_fence_before_sync();
       __syncwarp();
+      if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64) p.trace[(tile / gridDim.x) * 8 + 5] = clock64();
       if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
       acc ^= 1;
       if (acc == 0) acc_ph ^= 1u;

@@ -53,6 +53,7 @@ struct TcEpilogue {
   float act_a = 0.0f, act_b = 0.0f;
   float out_scale = 1.0f;
   int* status = nullptr;
+  long long* trace = nullptr;
 };
 
 // Elements per K block for a kind and a channel count; 0 when the tensor-core
