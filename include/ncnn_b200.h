@@ -129,6 +129,23 @@ int ncnn_b200_op_requantize(const int32_t *x, int8_t *y, int64_t count, int64_t 
                             const float *scale_out, int32_t scale_out_count, const float *bias,
                             int32_t bias_count, int32_t relu, void *stream);
 
+/* No counterpart in the reference.  For hosts that are not allowed to allocate on the
+ * GPU (a real-time loop after start-up, a sandbox that forbids cudaMalloc, a process whose
+ * own pool already owns the whole device): the int8 InnerProduct
+ *     y[m][n] = act(float(sum_k Q(x[m][k], input_scale) * weight[n][k]) / (weight_scales[n]*input_scale) + bias[n])
+ * on device arrays, with its only scratch (the int8 copy of x) taken from an 8 MiB array
+ * built into the library.  It calls no allocation routine.  Limits and rules:
+ * m*k <= 8 388 608, otherwise status 5 and a message in ncnn_b200_last_error(NULL); every
+ * GPU that loads the library holds those 8 MiB until exit; calls on one device share the
+ * array, so calls that may overlap on the GPU race and must be serialised; the first call
+ * on a device resolves the array's address and should happen before any stream capture.
+ * x is fp32 [m][k], weight int8 [n][k], bias fp32 [n] or NULL, y fp32 [m][n]; the
+ * arithmetic equals the InnerProduct layer of a loaded int8 model bit for bit. */
+int ncnn_b200_inner_product_int8_noalloc(const float *x, const int8_t *weight,
+                                         const float *weight_scales, float input_scale,
+                                         const float *bias, float *y, int64_t m, int32_t k, int32_t n,
+                                         int32_t relu, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -50,6 +50,11 @@ int grid_for(long long work) {
 
 }  // namespace
 
+namespace nb {
+// lets other translation units of the library report through ncnn_b200_last_error(NULL)
+void set_global_error(const std::string& message) { g_load_error = message; }
+}  // namespace nb
+
 extern "C" {
 
 int ncnn_b200_load(const char* param_path, const char* bin_path, const ncnn_b200_options* options,

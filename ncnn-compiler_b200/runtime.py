@@ -67,6 +67,8 @@ def load_library():
                                           c_void_p, c_int32, c_void_p]
     L.ncnn_b200_op_requantize.argtypes = [c_void_p, c_void_p, c_int64, c_int64, c_int32, c_void_p, c_int32,
                                           c_void_p, c_int32, c_void_p, c_int32, c_int32, c_void_p]
+    L.ncnn_b200_inner_product_int8_noalloc.argtypes = [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+                                                       c_int64, c_int32, c_int32, c_int32, c_void_p]
     _LIB = L
     return L
 
@@ -203,3 +205,14 @@ def op_requantize(x_ptr, y_ptr, count, inner, channels, scale_in_ptr, scale_in_c
     _op_status(load_library().ncnn_b200_op_requantize(x_ptr, y_ptr, count, inner, channels, scale_in_ptr,
                                                       scale_in_count, scale_out_ptr, scale_out_count, bias_ptr,
                                                       bias_count, 1 if relu else 0, c_void_p(stream)))
+
+
+def inner_product_int8_noalloc(x_ptr, weight_ptr, weight_scales_ptr, input_scale, bias_ptr, y_ptr, m, k, n,
+                               relu=False, stream=0):
+    """int8 InnerProduct on device arrays for hosts that may not allocate on the GPU: the
+    scratch lives in an 8 MiB array inside the library (m*k <= 8 388 608).  Returns the raw
+    status; the message of a refusal is ncnn_b200_last_error(NULL)."""
+    L = load_library()
+    st = L.ncnn_b200_inner_product_int8_noalloc(x_ptr, weight_ptr, weight_scales_ptr, c_float(input_scale), bias_ptr,
+                                                y_ptr, m, k, n, 1 if relu else 0, c_void_p(stream))
+    return st, L.ncnn_b200_last_error(None).decode()
