@@ -133,9 +133,18 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
   // a stage holds the A tile(s) and block_n rows of B, every sub-buffer 1 KB aligned
   const int b_bytes = (p.block_n * p.row_bytes + 1023) / 1024 * 1024;
   p.stage_bytes = planes * (kTcBlockM * p.row_bytes + b_bytes);
-  const int budget = 220 * 1024;
+  // fp32 results leave through TMA stores when rows are 16-byte multiples; the staging
+  // tiles (out hi/lo, residual hi/lo, 8 KB each) sit behind the ring
+  const bool f32_out = e.out_mode != OUT_I8;
+  const bool aligned = e.ldo % 4 == 0 && (reinterpret_cast<uintptr_t>(e.out0) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(e.out1) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(e.res0) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(e.res1) & 15) == 0;
+  p.tma_store = f32_out && aligned ? 1 : 0;
+  const int staging = p.tma_store ? 32 * 1024 : 0;
+  const int budget = 224 * 1024 - staging;
   p.stages = std::max(2, std::min(kTcMaxStages, budget / p.stage_bytes));
-  L->smem_bytes = p.stages * p.stage_bytes + 1024;
+  L->smem_bytes = p.stages * p.stage_bytes + staging + 1024;
   // never fewer bytes than half an SM's shared memory: two CTAs must not share an
   // SM, each allocates tensor memory for itself
   L->smem_bytes = std::max(L->smem_bytes, 120 * 1024);
@@ -157,6 +166,31 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
   p.out_scale = e.out_scale;
   p.status = e.status;
   p.trace = e.trace;
+  L->map_o0 = L->map_o1 = L->map_r0 = L->map_r1 = CUtensorMap{};
+}
+
+// [M][N] fp32 plane seen as a 2-D tensor (N innermost) with 16 x 128 boxes, 64-byte swizzle
+std::string encode_plane(CUtensorMap* map, const void* base, long long M, int N, long long ld) {
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 4};
+  const cuuint32_t box[2] = {16, static_cast<cuuint32_t>(kTcBlockM)};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  const CUresult r = g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base),
+                                    dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                    CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return "cuTensorMapEncodeTiled failed for an output plane with code " + std::to_string(static_cast<int>(r));
+  return {};
+}
+
+std::string encode_epilogue_maps(TcLaunch* L, const TcEpilogue& e) {
+  if (!L->p.tma_store) return {};
+  std::string err = encode_plane(&L->map_o0, e.out0, L->p.M, L->p.N, e.ldo);
+  if (err.empty() && e.out_mode == OUT_F32_SPLIT) err = encode_plane(&L->map_o1, e.out1, L->p.M, L->p.N, e.ldo);
+  if (err.empty() && e.res0 != nullptr) err = encode_plane(&L->map_r0, e.res0, L->p.M, L->p.N, e.ldo);
+  if (err.empty() && e.res1 != nullptr) err = encode_plane(&L->map_r1, e.res1, L->p.M, L->p.N, e.ldo);
+  return err;
 }
 
 }  // namespace
@@ -221,7 +255,7 @@ std::string tc_plan_conv(TcLaunch* L, int kind, const TcIm2colView& v, const voi
   } else {
     L->map_b1 = L->map_b0;
   }
-  return {};
+  return encode_epilogue_maps(L, e);
 }
 
 std::string tc_plan_gemm(TcLaunch* L, int kind, const void* a0, const void* a1, long long M, int K,
@@ -259,7 +293,7 @@ std::string tc_plan_gemm(TcLaunch* L, int kind, const void* a0, const void* a1, 
   } else {
     L->map_b1 = L->map_b0;
   }
-  return {};
+  return encode_epilogue_maps(L, e);
 }
 
 cudaError_t tc_launch(const TcLaunch& L, cudaStream_t stream) {
@@ -282,15 +316,18 @@ cudaError_t tc_launch(const TcLaunch& L, cudaStream_t stream) {
   switch (L.kind) {
     case GEMM_TF32:
       tc_gemm_kernel<GEMM_TF32>
-          <<<grid, block, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1);
+          <<<grid, block, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
+                                                  L.map_o1, L.map_r0, L.map_r1);
       break;
     case GEMM_TF32X3:
       tc_gemm_kernel<GEMM_TF32X3>
-          <<<grid, block, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1);
+          <<<grid, block, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
+                                                  L.map_o1, L.map_r0, L.map_r1);
       break;
     default:
       tc_gemm_kernel<GEMM_I8>
-          <<<grid, block, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1);
+          <<<grid, block, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
+                                                  L.map_o1, L.map_r0, L.map_r1);
       break;
   }
   return cudaGetLastError();

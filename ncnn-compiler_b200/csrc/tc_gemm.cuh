@@ -78,6 +78,7 @@ struct TcGemmParams {
   float act_a, act_b;  // leaky slope / clip bounds
   float out_scale;     // requantisation scale (OUT_I8)
   int* status;         // device word, stays 0 unless a bounded wait gave up
+  int tma_store;       // fp32 outputs leave through a shared-memory staging tile and TMA stores
   long long* trace;    // optional (bring-up): per-role clock stamps of CTA 0, 8 values per tile
 };
 
@@ -209,12 +210,44 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcGemmParams& p, const u
   }
 }
 
+// fp32 result of 16 accumulator columns: dequantise / bias, residual, activation.
+template <int KIND>
+__device__ __forceinline__ void tc_epilogue_values(const TcGemmParams& p, const uint32_t (&v)[16],
+                                                   int n_first, const float* res, float (&y)[16]) {
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    const int n = n_first + j;
+    float t = 0.0f;
+    if (n < p.N) {
+      if (KIND == GEMM_I8) {
+        t = __fmul_rn(static_cast<float>(static_cast<int>(v[j])), __ldg(p.scale + n));
+      } else {
+        t = __uint_as_float(v[j]);
+      }
+      if (p.bias != nullptr) t = __fadd_rn(t, __ldg(p.bias + n));
+      if (res != nullptr) t = __fadd_rn(t, res[j]);
+      t = apply_act(t, p.act, p.act_a, p.act_b);
+    }
+    y[j] = t;
+  }
+}
+
+// Staging tiles are [128 rows][16 fp32] with the 64-byte TMA swizzle: the 16-byte chunk j
+// of row r lives at r*64 + ((j ^ ((r >> 1) & 3)) * 16).
+__device__ __forceinline__ uint32_t stage_chunk_offset(int row, int j) {
+  return static_cast<uint32_t>(row * 64 + ((j ^ ((row >> 1) & 3)) << 4));
+}
+
 template <int KIND>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ CUtensorMap map_a0,
                const __grid_constant__ CUtensorMap map_a1,
                const __grid_constant__ CUtensorMap map_b0,
-               const __grid_constant__ CUtensorMap map_b1) {
+               const __grid_constant__ CUtensorMap map_b1,
+               const __grid_constant__ CUtensorMap map_o0,
+               const __grid_constant__ CUtensorMap map_o1,
+               const __grid_constant__ CUtensorMap map_r0,
+               const __grid_constant__ CUtensorMap map_r1) {
   using namespace ptx;
   constexpr int PLANES = KIND == GEMM_TF32X3 ? 2 : 1;
 
@@ -223,6 +256,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
   __shared__ __align__(8) uint64_t empty_bar[kTcMaxStages];
   __shared__ __align__(8) uint64_t tfull_bar[2];
   __shared__ __align__(8) uint64_t tempty_bar[2];
+  __shared__ __align__(8) uint64_t res_bar;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -247,6 +281,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
       mbar_init(smem_u32(&tfull_bar[i]), 1);
       mbar_init(smem_u32(&tempty_bar[i]), 4);
     }
+    mbar_init(smem_u32(&res_bar), 1);
     fence_mbar_init();
     prefetch_tensormap(&map_a0);
     prefetch_tensormap(&map_b0);
@@ -406,6 +441,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+31] belong to this warp
     int acc = 0;
     uint32_t acc_ph = 0;
+    uint32_t res_ph = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       const int m_blk = tile / p.tiles_n;
@@ -423,11 +459,92 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
       if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64) p.trace[(tile / gridDim.x) * 8 + 4] = clock64();
       const uint32_t t_row =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc) * 128u;
-      for (int c0 = 0; c0 < p.block_n; c0 += 16) {
-        uint32_t v[16];
-        tmem_ld16(t_row + static_cast<uint32_t>(c0), v);
-        tmem_ld_wait();
-        if (m < p.M && n0 + c0 < p.N) tc_epilogue_chunk<KIND>(p, v, m, n0 + c0);
+      if (p.tma_store) {
+        // staging area behind the ring: out hi, out lo, residual hi, residual lo (8 KB each)
+        const uint32_t stage0 = smem_base + static_cast<uint32_t>(S) * stage_bytes;
+        const int row = quarter * 32 + lane;
+        const bool leader = threadIdx.x == 64;
+        const bool split = p.out_mode == OUT_F32_SPLIT;
+        const int m_first = m_blk * kTcBlockM;
+        for (int c0 = 0; c0 < p.block_n && ok; c0 += 16) {
+          const bool live = n0 + c0 < p.N;  // uniform over the CTA
+          if (leader) tma_store_wait_read();
+          named_barrier_sync(1, 128);  // staging and residual tiles are free again
+          if (live && p.res0 != nullptr && leader) {
+            const uint32_t rb = smem_u32(&res_bar);
+            mbar_arrive_expect_tx(rb, (p.res1 != nullptr ? 2u : 1u) * 8192u);
+            tma_load_2d(stage0 + 16384u, &map_r0, rb, n0 + c0, m_first);
+            if (p.res1 != nullptr) tma_load_2d(stage0 + 24576u, &map_r1, rb, n0 + c0, m_first);
+          }
+          uint32_t v[16];
+          tmem_ld16(t_row + static_cast<uint32_t>(c0), v);
+          tmem_ld_wait();
+          if (!live) continue;
+          float r[16];
+          if (p.res0 != nullptr) {
+            ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&res_bar), res_ph, abort_ptr,
+                                                           kTcWaitLimitNs) ? 1 : 0) != 0;
+            res_ph ^= 1u;
+            if (!ok) break;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t off = stage_chunk_offset(row, j);
+              float4 a;
+              asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                           : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w)
+                           : "r"(stage0 + 16384u + off));
+              if (p.res1 != nullptr) {
+                float4 b;
+                asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                             : "=f"(b.x), "=f"(b.y), "=f"(b.z), "=f"(b.w)
+                             : "r"(stage0 + 24576u + off));
+                a.x = __fadd_rn(a.x, b.x);
+                a.y = __fadd_rn(a.y, b.y);
+                a.z = __fadd_rn(a.z, b.z);
+                a.w = __fadd_rn(a.w, b.w);
+              }
+              r[4 * j + 0] = a.x;
+              r[4 * j + 1] = a.y;
+              r[4 * j + 2] = a.z;
+              r[4 * j + 3] = a.w;
+            }
+          }
+          float y[16];
+          tc_epilogue_values<KIND>(p, v, n0 + c0, p.res0 != nullptr ? r : nullptr, y);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float hi[4], lo[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float t = y[4 * j + e];
+              hi[e] = p.out_mode == OUT_F32 ? t : round_tf32(t);
+              lo[e] = __fadd_rn(t, -hi[e]);
+            }
+            const uint32_t off = stage_chunk_offset(row, j);
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stage0 + off), "f"(hi[0]),
+                         "f"(hi[1]), "f"(hi[2]), "f"(hi[3])
+                         : "memory");
+            if (split)
+              asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stage0 + 8192u + off),
+                           "f"(lo[0]), "f"(lo[1]), "f"(lo[2]), "f"(lo[3])
+                           : "memory");
+          }
+          fence_proxy_async_smem();
+          named_barrier_sync(2, 128);
+          if (leader) {
+            tma_store_2d(&map_o0, stage0, n0 + c0, m_first);
+            if (split) tma_store_2d(&map_o1, stage0 + 8192u, n0 + c0, m_first);
+            tma_store_commit();
+          }
+        }
+        if (!ok) break;
+      } else {
+        for (int c0 = 0; c0 < p.block_n; c0 += 16) {
+          uint32_t v[16];
+          tmem_ld16(t_row + static_cast<uint32_t>(c0), v);
+          tmem_ld_wait();
+          if (m < p.M && n0 + c0 < p.N) tc_epilogue_chunk<KIND>(p, v, m, n0 + c0);
+        }
       }
       tc_fence_before_sync();
       __syncwarp();
@@ -439,6 +556,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
     if (!ok && lane == 0) {
       if (atomicCAS(const_cast<int*>(abort_ptr), 0, 1) == 0) atomicCAS(p.status, 0, TC_TIMEOUT_EPILOGUE);
     }
+    if (p.tma_store && threadIdx.x == 64) tma_store_wait_all();  // stores still read shared memory
   }
 
   tc_fence_before_sync();

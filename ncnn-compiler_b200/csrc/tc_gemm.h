@@ -19,6 +19,10 @@ struct TcLaunch {
   alignas(64) CUtensorMap map_a1{};
   alignas(64) CUtensorMap map_b0{};
   alignas(64) CUtensorMap map_b1{};
+  alignas(64) CUtensorMap map_o0{};  // output planes, boxes of 16 columns x 128 rows
+  alignas(64) CUtensorMap map_o1{};
+  alignas(64) CUtensorMap map_r0{};  // residual planes
+  alignas(64) CUtensorMap map_r1{};
   int kind = GEMM_TF32;
   int grid = 0;
   int smem_bytes = 0;
