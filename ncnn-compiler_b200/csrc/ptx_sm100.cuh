@@ -126,9 +126,18 @@ __device__ __forceinline__ void tma_store_commit() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 
-// all committed stores have finished READING shared memory (the staging buffer is free)
-__device__ __forceinline__ void tma_store_wait_read() {
-  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+// all but the `pending` most recent committed store groups have finished READING shared
+// memory (their staging buffers are free again)
+__device__ __forceinline__ void tma_store_wait_read(int pending) {
+  if (pending >= 3) {
+    asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory");
+  } else if (pending == 2) {
+    asm volatile("cp.async.bulk.wait_group.read 2;" ::: "memory");
+  } else if (pending == 1) {
+    asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+  } else {
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+  }
 }
 
 // all committed stores are complete

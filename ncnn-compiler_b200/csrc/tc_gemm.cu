@@ -141,8 +141,19 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
                        (reinterpret_cast<uintptr_t>(e.res0) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(e.res1) & 15) == 0;
   p.tma_store = f32_out && aligned ? 1 : 0;
-  const int staging = p.tma_store ? 32 * 1024 : 0;
-  const int budget = 224 * 1024 - staging;
+  // residual tiles (16 KB) + up to four output tiles of 8 KB per plane; fewer when the
+  // operand ring would drop below three stages
+  const int out_tile = (e.out_mode == OUT_F32_SPLIT ? 2 : 1) * 8192;
+  int staging = 0;
+  p.out_bufs = 1;
+  if (p.tma_store) {
+    for (int bufs : {4, 2, 1}) {
+      p.out_bufs = bufs;
+      staging = 16384 + bufs * out_tile;
+      if ((222 * 1024 - staging) / p.stage_bytes >= 3 || bufs == 1) break;
+    }
+  }
+  const int budget = 222 * 1024 - staging;
   p.stages = std::max(2, std::min(kTcMaxStages, budget / p.stage_bytes));
   L->smem_bytes = p.stages * p.stage_bytes + staging + 1024;
   // never fewer bytes than half an SM's shared memory: two CTAs must not share an
@@ -300,7 +311,7 @@ cudaError_t tc_launch(const TcLaunch& L, cudaStream_t stream) {
   static std::once_flag attr_once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(attr_once, [] {
-    const int max_smem = 226 * 1024;  // 227 KB per block minus the static barriers
+    const int max_smem = 224 * 1024;  // 227 KB per block minus static shared memory
     cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<GEMM_TF32>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
     if (e == cudaSuccess)

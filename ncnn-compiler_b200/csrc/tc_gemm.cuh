@@ -78,7 +78,8 @@ struct TcGemmParams {
   float act_a, act_b;  // leaky slope / clip bounds
   float out_scale;     // requantisation scale (OUT_I8)
   int* status;         // device word, stays 0 unless a bounded wait gave up
-  int tma_store;       // fp32 outputs leave through a shared-memory staging tile and TMA stores
+  int tma_store;       // fp32 outputs leave through shared-memory staging tiles and TMA stores
+  int out_bufs;        // staging tiles in flight (1..4), each 8 KB per output plane
   long long* trace;    // optional (bring-up): per-role clock stamps of CTA 0, 8 values per tile
 };
 
@@ -106,7 +107,8 @@ __device__ __forceinline__ float apply_act(float y, int act, float a, float b) {
 
 template <int KIND>
 __device__ __forceinline__ void tc_epilogue_chunk(const TcGemmParams& p, const uint32_t (&v)[16],
-                                                  long long m, int n_first) {
+                                                  long long m, int n_first, const float* tile_bias,
+                                                  const float* tile_scale) {
   float y[16];
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
@@ -114,11 +116,11 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcGemmParams& p, const u
     float t;
     if (n < p.N) {
       if (KIND == GEMM_I8) {
-        t = __fmul_rn(static_cast<float>(static_cast<int>(v[j])), __ldg(p.scale + n));
+        t = __fmul_rn(static_cast<float>(static_cast<int>(v[j])), tile_scale[j]);
       } else {
         t = __uint_as_float(v[j]);
       }
-      if (p.bias != nullptr) t = __fadd_rn(t, __ldg(p.bias + n));
+      if (p.bias != nullptr) t = __fadd_rn(t, tile_bias[j]);
     } else {
       t = 0.0f;
     }
@@ -210,25 +212,25 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcGemmParams& p, const u
   }
 }
 
-// fp32 result of 16 accumulator columns: dequantise / bias, residual, activation.
+// fp32 result of 16 accumulator columns: dequantise / bias, residual, activation.  Every
+// scalar arrives by value: reading them through the kernel-parameter struct inside the
+// unrolled loop costs a generic load per use.
 template <int KIND>
-__device__ __forceinline__ void tc_epilogue_values(const TcGemmParams& p, const uint32_t (&v)[16],
-                                                   int n_first, const float* res, float (&y)[16]) {
+__device__ __forceinline__ void tc_epilogue_values(const uint32_t (&v)[16], const float (&bias)[16],
+                                                   const float (&scale)[16], bool has_bias,
+                                                   const float* res, int act, float act_a,
+                                                   float act_b, float (&y)[16]) {
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
-    const int n = n_first + j;
-    float t = 0.0f;
-    if (n < p.N) {
-      if (KIND == GEMM_I8) {
-        t = __fmul_rn(static_cast<float>(static_cast<int>(v[j])), __ldg(p.scale + n));
-      } else {
-        t = __uint_as_float(v[j]);
-      }
-      if (p.bias != nullptr) t = __fadd_rn(t, __ldg(p.bias + n));
-      if (res != nullptr) t = __fadd_rn(t, res[j]);
-      t = apply_act(t, p.act, p.act_a, p.act_b);
+    float t;
+    if (KIND == GEMM_I8) {
+      t = __fmul_rn(static_cast<float>(static_cast<int>(v[j])), scale[j]);
+    } else {
+      t = __uint_as_float(v[j]);
     }
-    y[j] = t;
+    if (has_bias) t = __fadd_rn(t, bias[j]);
+    if (res != nullptr) t = __fadd_rn(t, res[j]);
+    y[j] = apply_act(t, act, act_a, act_b);
   }
 }
 
@@ -257,6 +259,8 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
   __shared__ __align__(8) uint64_t tfull_bar[2];
   __shared__ __align__(8) uint64_t tempty_bar[2];
   __shared__ __align__(8) uint64_t res_bar;
+  __shared__ __align__(16) float tile_bias[128];
+  __shared__ __align__(16) float tile_scale[128];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -321,7 +325,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
           h_base = oh * p.stride_h - p.pad_t;
           w_base = ow * p.stride_w - p.pad_l;
         }
-        if (p.trace != nullptr && blockIdx.x == 0) p.trace[(tile / gridDim.x) * 8 + 0] = clock64();
+        if (p.trace != nullptr && blockIdx.x == 0) p.trace[(tile / gridDim.x) * 16 + 0] = clock64();
         int tap = 0, cb = 0;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait_bounded(smem_u32(&empty_bar[s]), ph ^ 1u, abort_ptr, kTcWaitLimitNs)) {
@@ -394,7 +398,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
           break;
         }
         tc_fence_after_sync();
-        if (p.trace != nullptr && blockIdx.x == 0) p.trace[(tile / gridDim.x) * 8 + 1] = clock64();
+        if (p.trace != nullptr && blockIdx.x == 0) p.trace[(tile / gridDim.x) * 16 + 1] = clock64();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * 128u;
         for (int kb = 0; kb < p.k_blocks; ++kb) {
           if (!mbar_wait_bounded(smem_u32(&full_bar[s]), ph, abort_ptr, kTcWaitLimitNs)) {
@@ -428,7 +432,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
         }
         if (!ok) break;
         tc_commit(smem_u32(&tfull_bar[acc]));
-        if (p.trace != nullptr && blockIdx.x == 0) p.trace[(tile / gridDim.x) * 8 + 2] = clock64();
+        if (p.trace != nullptr && blockIdx.x == 0) p.trace[(tile / gridDim.x) * 16 + 2] = clock64();
         acc ^= 1;
         if (acc == 0) acc_ph ^= 1u;
       }
@@ -442,13 +446,21 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
     int acc = 0;
     uint32_t acc_ph = 0;
     uint32_t res_ph = 0;
+    int out_slot = 0;
     bool ok = true;
+    // a register copy: the helper below takes the struct by reference, and a reference to the
+    // kernel parameter itself turns every field access into a generic load
+    const TcGemmParams lp = p;
+    const int e_act = p.act;
+    const float e_act_a = p.act_a, e_act_b = p.act_b;
+    const bool e_has_bias = p.bias != nullptr, e_has_res = p.res0 != nullptr, e_res_split = p.res1 != nullptr;
+    const int e_out_mode = p.out_mode, e_N = p.N, e_block_n = p.block_n, e_out_bufs = p.out_bufs;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       const int m_blk = tile / p.tiles_n;
       const int n_blk = tile - m_blk * p.tiles_n;
       const long long m = static_cast<long long>(m_blk) * kTcBlockM + quarter * 32 + lane;
       const int n0 = n_blk * p.block_n;
-      if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64) p.trace[(tile / gridDim.x) * 8 + 3] = clock64();
+      if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64) p.trace[(tile / gridDim.x) * 16 + 3] = clock64();
       // the vote keeps the warp together: tcgen05.ld below needs all 32 lanes
       ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&tfull_bar[acc]), acc_ph, abort_ptr,
                                                      kTcWaitLimitNs)
@@ -456,32 +468,45 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
                                        : 0) != 0;
       if (!ok) break;
       tc_fence_after_sync();
-      if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64) p.trace[(tile / gridDim.x) * 8 + 4] = clock64();
+      if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64) p.trace[(tile / gridDim.x) * 16 + 4] = clock64();
       const uint32_t t_row =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc) * 128u;
+      {
+        // per-column constants of this tile, fetched once (every warp has left the previous
+        // tile's last chunk: it ends with a barrier)
+        const int t = static_cast<int>(threadIdx.x) - 64;
+        const int n = n0 + t;
+        tile_bias[t] = (p.bias != nullptr && n < p.N) ? __ldg(p.bias + n) : 0.0f;
+        tile_scale[t] = (KIND == GEMM_I8 && n < p.N) ? __ldg(p.scale + n) : 0.0f;
+      }
       if (p.tma_store) {
-        // staging area behind the ring: out hi, out lo, residual hi, residual lo (8 KB each)
-        const uint32_t stage0 = smem_base + static_cast<uint32_t>(S) * stage_bytes;
+        // staging area behind the ring: residual hi, residual lo (8 KB each), then a small
+        // ring of output tiles (hi [+ lo], 8 KB per plane) so stores overlap the next chunk
+        const uint32_t res_stage = smem_base + static_cast<uint32_t>(S) * stage_bytes;
+        const uint32_t out_stage = res_stage + 16384u;
         const int row = quarter * 32 + lane;
         const bool leader = threadIdx.x == 64;
-        const bool split = p.out_mode == OUT_F32_SPLIT;
+        const bool split = e_out_mode == OUT_F32_SPLIT;
         const int m_first = m_blk * kTcBlockM;
-        for (int c0 = 0; c0 < p.block_n && ok; c0 += 16) {
-          const bool live = n0 + c0 < p.N;  // uniform over the CTA
-          if (leader) tma_store_wait_read();
-          named_barrier_sync(1, 128);  // staging and residual tiles are free again
-          if (live && p.res0 != nullptr && leader) {
+        for (int c0 = 0; c0 < e_block_n && ok; c0 += 16) {
+          const bool live = n0 + c0 < e_N;  // uniform over the CTA
+          const uint32_t stage0 = out_stage + static_cast<uint32_t>(out_slot) * (split ? 16384u : 8192u);
+          if (leader) tma_store_wait_read(e_out_bufs - 1);
+          named_barrier_sync(1, 128);  // this output tile and the residual tiles are free again
+          if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64 && c0 == 0) p.trace[(tile / gridDim.x) * 16 + 6] = clock64();
+          if (live && e_has_res && leader) {
             const uint32_t rb = smem_u32(&res_bar);
-            mbar_arrive_expect_tx(rb, (p.res1 != nullptr ? 2u : 1u) * 8192u);
-            tma_load_2d(stage0 + 16384u, &map_r0, rb, n0 + c0, m_first);
-            if (p.res1 != nullptr) tma_load_2d(stage0 + 24576u, &map_r1, rb, n0 + c0, m_first);
+            mbar_arrive_expect_tx(rb, (e_res_split ? 2u : 1u) * 8192u);
+            tma_load_2d(res_stage, &map_r0, rb, n0 + c0, m_first);
+            if (e_res_split) tma_load_2d(res_stage + 8192u, &map_r1, rb, n0 + c0, m_first);
           }
           uint32_t v[16];
           tmem_ld16(t_row + static_cast<uint32_t>(c0), v);
           tmem_ld_wait();
+          if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64 && c0 == 0) p.trace[(tile / gridDim.x) * 16 + 7] = clock64();
           if (!live) continue;
           float r[16];
-          if (p.res0 != nullptr) {
+          if (e_has_res) {
             ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&res_bar), res_ph, abort_ptr,
                                                            kTcWaitLimitNs) ? 1 : 0) != 0;
             res_ph ^= 1u;
@@ -492,12 +517,12 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
               float4 a;
               asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
                            : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w)
-                           : "r"(stage0 + 16384u + off));
-              if (p.res1 != nullptr) {
+                           : "r"(res_stage + off));
+              if (e_res_split) {
                 float4 b;
                 asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
                              : "=f"(b.x), "=f"(b.y), "=f"(b.z), "=f"(b.w)
-                             : "r"(stage0 + 24576u + off));
+                             : "r"(res_stage + 8192u + off));
                 a.x = __fadd_rn(a.x, b.x);
                 a.y = __fadd_rn(a.y, b.y);
                 a.z = __fadd_rn(a.z, b.z);
@@ -510,14 +535,31 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
             }
           }
           float y[16];
-          tc_epilogue_values<KIND>(p, v, n0 + c0, p.res0 != nullptr ? r : nullptr, y);
+          float cb[16], cs[16];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float4 b4 = *reinterpret_cast<const float4*>(&tile_bias[c0 + 4 * j]);
+            cb[4 * j + 0] = b4.x;
+            cb[4 * j + 1] = b4.y;
+            cb[4 * j + 2] = b4.z;
+            cb[4 * j + 3] = b4.w;
+            if (KIND == GEMM_I8) {
+              const float4 s4 = *reinterpret_cast<const float4*>(&tile_scale[c0 + 4 * j]);
+              cs[4 * j + 0] = s4.x;
+              cs[4 * j + 1] = s4.y;
+              cs[4 * j + 2] = s4.z;
+              cs[4 * j + 3] = s4.w;
+            }
+          }
+          tc_epilogue_values<KIND>(v, cb, cs, e_has_bias, e_has_res ? r : nullptr, e_act, e_act_a, e_act_b, y);
+          if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64 && c0 == 0) p.trace[(tile / gridDim.x) * 16 + 8] = clock64();
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             float hi[4], lo[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               const float t = y[4 * j + e];
-              hi[e] = p.out_mode == OUT_F32 ? t : round_tf32(t);
+              hi[e] = e_out_mode == OUT_F32 ? t : round_tf32(t);
               lo[e] = __fadd_rn(t, -hi[e]);
             }
             const uint32_t off = stage_chunk_offset(row, j);
@@ -530,25 +572,32 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
                            : "memory");
           }
           fence_proxy_async_smem();
+          if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64 && c0 == 0) p.trace[(tile / gridDim.x) * 16 + 9] = clock64();
           named_barrier_sync(2, 128);
+          if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64 && c0 == 0) p.trace[(tile / gridDim.x) * 16 + 10] = clock64();
           if (leader) {
             tma_store_2d(&map_o0, stage0, n0 + c0, m_first);
             if (split) tma_store_2d(&map_o1, stage0 + 8192u, n0 + c0, m_first);
             tma_store_commit();
           }
+          if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64 && c0 == 0) p.trace[(tile / gridDim.x) * 16 + 11] = clock64();
+          if (++out_slot == e_out_bufs) out_slot = 0;
         }
         if (!ok) break;
       } else {
-        for (int c0 = 0; c0 < p.block_n; c0 += 16) {
+        named_barrier_sync(3, 128);
+        for (int c0 = 0; c0 < e_block_n; c0 += 16) {
           uint32_t v[16];
           tmem_ld16(t_row + static_cast<uint32_t>(c0), v);
           tmem_ld_wait();
-          if (m < p.M && n0 + c0 < p.N) tc_epilogue_chunk<KIND>(p, v, m, n0 + c0);
+          if (m < lp.M && n0 + c0 < e_N)
+            tc_epilogue_chunk<KIND>(lp, v, m, n0 + c0, tile_bias + c0, tile_scale + c0);
         }
+        named_barrier_sync(3, 128);  // nobody reads the tile constants any more
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64) p.trace[(tile / gridDim.x) * 8 + 5] = clock64();
+      if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64) p.trace[(tile / gridDim.x) * 16 + 5] = clock64();
       if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
       acc ^= 1;
       if (acc == 0) acc_ph ^= 1u;
