@@ -98,9 +98,23 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def use_all_host_threads():
+    """torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU baseline is meant to use
+    every host core, so the OpenMP runtime of the oracle library is told so explicitly."""
+    import ctypes
+    cores = os.cpu_count() or 1
+    os.environ["OMP_NUM_THREADS"] = str(cores)
+    try:
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(cores)
+    except OSError:
+        pass
+    return cores
+
+
 def cpu_oracle_rate(param, bin_, shape, budget_s, seed=1):
     """images/s of the CPU restatement on this box's cores: a bounded sample of single-image
     calls (the reference has no batch dimension)."""
+    use_all_host_threads()
     orc = entry._load_oracle()
     model = orc.Model(param, bin_)
     rng = np.random.default_rng(seed)
@@ -290,7 +304,7 @@ def main():
                 f.write(f"| {r['kernel']} | {r['layer']} | {r['ms']:.4f} | {r['flops'] / 1e9:.3f} | "
                         f"{r['bytes'] / 1e6:.2f} | {tf:.1f} | {gb:.0f} |\n")
 
-    if args.cpu_seconds > 0:
+    if args.cpu_seconds > 0 and world == 1:  # the CPU baseline is taken at N = 1 only
         cpu_rate, cpu_n, cpu_t = cpu_oracle_rate(param, bin_, in_shape, args.cpu_seconds)
     else:
         cpu_rate, cpu_n, cpu_t = None, 0, 0.0  # skipped on request (profiling runs)
@@ -306,8 +320,8 @@ def main():
         "gpu_launches": model.launch_count(n) * args.steps,
         "roofline": roofline,
         "cpu_baseline": {"value": cpu_rate, "unit": "images/s", "cores": os.cpu_count() or 1, "kind": "port",
-                         "sample": f"{cpu_n} single-image calls in {cpu_t:.1f} s of the CPU restatement "
-                                   "of the reference lowering"},
+                         "sample": (f"{cpu_n} single-image calls in {cpu_t:.1f} s of the CPU restatement "
+                                    "of the reference lowering") if cpu_n else "not sampled in this run (N > 1 or disabled)"},
         "clocks": clocks,
     }
     print(json.dumps(line), flush=True)

@@ -332,6 +332,8 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
             ok = false;
             break;
           }
+          const bool tr = p.trace != nullptr && blockIdx.x == 0 && tile == static_cast<int>(gridDim.x) && kb < 32;
+          if (tr) p.trace[1024 + kb * 4 + 0] = clock64();
           const uint32_t fb = smem_u32(&full_bar[s]);
           mbar_arrive_expect_tx(fb, tx_bytes);
           const uint32_t a_dst = smem_base + s * stage_bytes;
@@ -353,6 +355,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
           }
           tma_load_2d(b_dst, &map_b0, fb, kb * p.k_elems, n0);
           if (PLANES == 2) tma_load_2d(b_dst + b_slot, &map_b1, fb, kb * p.k_elems, n0);
+          if (tr) p.trace[1024 + kb * 4 + 1] = clock64();
           ++issued;
           if (++cb == p.c_blocks) {
             cb = 0;
@@ -385,7 +388,18 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
       const uint32_t idesc = KIND == GEMM_I8
                                  ? instr_desc(2u, 1u, kTcBlockM, static_cast<uint32_t>(p.block_n))
                                  : instr_desc(1u, 2u, kTcBlockM, static_cast<uint32_t>(p.block_n));
+      // One thread issues every MMA, so its instruction stream is the critical path:
+      // descriptors are formed by adding small constants to values computed once.
+      // (the start-address field counts 16-byte units; a K step is 32 bytes = 2 units)
       const int k_steps = p.row_bytes / 32;
+      const int k_blocks = p.k_blocks;
+      const uint64_t desc_fixed = smem_desc_kmajor(0u, static_cast<uint32_t>(p.row_bytes));
+      const uint64_t a_first = desc_fixed + ((smem_base & 0x3ffffu) >> 4);
+      const uint64_t stage_units = stage_bytes >> 4;
+      const uint64_t slot_units = slot >> 4;
+      const uint64_t b_slot_units = b_slot >> 4;
+      const uint64_t b_from_a = static_cast<uint64_t>(PLANES) * slot_units;
+      const bool tracing = p.trace != nullptr && blockIdx.x == 0;
       int s = 0;
       uint32_t ph = 0;
       int acc = 0;
@@ -398,33 +412,36 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
           break;
         }
         tc_fence_after_sync();
-        if (p.trace != nullptr && blockIdx.x == 0) p.trace[(tile / gridDim.x) * 16 + 1] = clock64();
+        if (tracing) p.trace[(tile / gridDim.x) * 16 + 1] = clock64();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * 128u;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        uint32_t accumulate = 0u;
+        for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait_bounded(smem_u32(&full_bar[s]), ph, abort_ptr, kTcWaitLimitNs)) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          const uint32_t a_addr = smem_base + s * stage_bytes;
-          const uint32_t b_addr = a_addr + PLANES * slot;
+          const bool tr = tracing && tile == static_cast<int>(gridDim.x) && kb < 32;
+          if (tr) p.trace[1024 + kb * 4 + 2] = clock64();
+          const uint64_t a0 = a_first + static_cast<uint64_t>(s) * stage_units;
+          const uint64_t b0 = a0 + b_from_a;
+#pragma unroll 4
           for (int k = 0; k < k_steps; ++k) {
-            const uint32_t first = (kb | k) != 0 ? 1u : 0u;
-            const uint64_t a0 = smem_desc_kmajor(a_addr + k * 32, p.row_bytes);
-            const uint64_t b0 = smem_desc_kmajor(b_addr + k * 32, p.row_bytes);
+            const uint64_t ka = a0 + 2u * k;
+            const uint64_t kbd = b0 + 2u * k;
             if (KIND == GEMM_TF32) {
-              mma_tf32(d_tmem, a0, b0, idesc, first);
+              mma_tf32(d_tmem, ka, kbd, idesc, accumulate);
             } else if (KIND == GEMM_TF32X3) {
-              const uint64_t a1 = smem_desc_kmajor(a_addr + slot + k * 32, p.row_bytes);
-              const uint64_t b1 = smem_desc_kmajor(b_addr + b_slot + k * 32, p.row_bytes);
-              mma_tf32(d_tmem, a1, b0, idesc, first);  // lo * hi
-              mma_tf32(d_tmem, a0, b1, idesc, 1u);     // hi * lo
-              mma_tf32(d_tmem, a0, b0, idesc, 1u);     // hi * hi
+              mma_tf32(d_tmem, ka + slot_units, kbd, idesc, accumulate);  // lo * hi
+              mma_tf32(d_tmem, ka, kbd + b_slot_units, idesc, 1u);        // hi * lo
+              mma_tf32(d_tmem, ka, kbd, idesc, 1u);                       // hi * hi
             } else {
-              mma_i8(d_tmem, a0, b0, idesc, first);
+              mma_i8(d_tmem, ka, kbd, idesc, accumulate);
             }
+            accumulate = 1u;
           }
           tc_commit(smem_u32(&empty_bar[s]));
+          if (tr) p.trace[1024 + kb * 4 + 3] = clock64();
           if (++s == S) {
             s = 0;
             ph ^= 1u;
@@ -432,7 +449,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
         }
         if (!ok) break;
         tc_commit(smem_u32(&tfull_bar[acc]));
-        if (p.trace != nullptr && blockIdx.x == 0) p.trace[(tile / gridDim.x) * 16 + 2] = clock64();
+        if (tracing) p.trace[(tile / gridDim.x) * 16 + 2] = clock64();
         acc ^= 1;
         if (acc == 0) acc_ph ^= 1u;
       }
