@@ -141,16 +141,16 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
                        (reinterpret_cast<uintptr_t>(e.res0) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(e.res1) & 15) == 0;
   p.tma_store = f32_out && aligned ? 1 : 0;
-  // residual tiles (16 KB) + up to four output tiles of 8 KB per plane; fewer when the
+  // residual tiles (16 KB) + two to four output tiles of 8 KB per plane; fewer when the
   // operand ring would drop below three stages
   const int out_tile = (e.out_mode == OUT_F32_SPLIT ? 2 : 1) * 8192;
   int staging = 0;
   p.out_bufs = 1;
   if (p.tma_store) {
-    for (int bufs : {4, 2, 1}) {
+    for (int bufs : {4, 3, 2}) {
       p.out_bufs = bufs;
       staging = 16384 + bufs * out_tile;
-      if ((222 * 1024 - staging) / p.stage_bytes >= 3 || bufs == 1) break;
+      if ((222 * 1024 - staging) / p.stage_bytes >= 3 || bufs == 2) break;
     }
   }
   const int budget = 222 * 1024 - staging;

@@ -213,13 +213,15 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcGemmParams& p, const u
 }
 
 // fp32 result of 16 accumulator columns: dequantise / bias, residual, activation.  Every
-// scalar arrives by value: reading them through the kernel-parameter struct inside the
-// unrolled loop costs a generic load per use.
+// scalar arrives by value (a reference to the kernel-parameter struct turns each field
+// access into a generic load) and every decision is taken outside the unrolled loops: one
+// thread's branches are not hidden by other warps here.  `bias` and `res` hold zeros when
+// the layer has none (adding +0 changes at most the sign of a zero).
 template <int KIND>
 __device__ __forceinline__ void tc_epilogue_values(const uint32_t (&v)[16], const float (&bias)[16],
-                                                   const float (&scale)[16], bool has_bias,
-                                                   const float* res, int act, float act_a,
-                                                   float act_b, float (&y)[16]) {
+                                                   const float (&scale)[16], const float (&res)[16],
+                                                   int act, float act_a, float act_b,
+                                                   float (&y)[16]) {
 #pragma unroll
   for (int j = 0; j < 16; ++j) {
     float t;
@@ -228,9 +230,17 @@ __device__ __forceinline__ void tc_epilogue_values(const uint32_t (&v)[16], cons
     } else {
       t = __uint_as_float(v[j]);
     }
-    if (has_bias) t = __fadd_rn(t, bias[j]);
-    if (res != nullptr) t = __fadd_rn(t, res[j]);
-    y[j] = apply_act(t, act, act_a, act_b);
+    y[j] = __fadd_rn(__fadd_rn(t, bias[j]), res[j]);
+  }
+  if (act == ACT_RELU) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) y[j] = fmaxf(y[j], 0.0f);
+  } else if (act == ACT_CLIP) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) y[j] = fminf(fmaxf(y[j], act_a), act_b);
+  } else if (act == ACT_LEAKY) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) y[j] = y[j] >= 0.0f ? y[j] : __fmul_rn(y[j], act_a);
   }
 }
 
@@ -497,35 +507,33 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
         tile_scale[t] = (KIND == GEMM_I8 && n < p.N) ? __ldg(p.scale + n) : 0.0f;
       }
       if (p.tma_store) {
-        // staging area behind the ring: residual hi, residual lo (8 KB each), then a small
-        // ring of output tiles (hi [+ lo], 8 KB per plane) so stores overlap the next chunk
+        // Staging area behind the ring: residual hi, residual lo (8 KB each), then a ring of
+        // e_out_bufs >= 2 output tiles (hi [+ lo], 8 KB per plane).  One barrier per chunk:
+        // everybody writes tile c, barrier, the leader stores it, waits until the tile
+        // that chunk c+2 will use has been read out, and fetches the residual of chunk c+1;
+        // the others learn all that at the barrier of chunk c+1.
         const uint32_t res_stage = smem_base + static_cast<uint32_t>(S) * stage_bytes;
         const uint32_t out_stage = res_stage + 16384u;
         const int row = quarter * 32 + lane;
         const bool leader = threadIdx.x == 64;
         const bool split = e_out_mode == OUT_F32_SPLIT;
+        const uint32_t out_tile_bytes = split ? 16384u : 8192u;
         const int m_first = m_blk * kTcBlockM;
-        for (int c0 = 0; c0 < e_block_n && ok; c0 += 16) {
-          const bool live = n0 + c0 < e_N;  // uniform over the CTA
-          const uint32_t stage0 = out_stage + static_cast<uint32_t>(out_slot) * (split ? 16384u : 8192u);
-          if (leader) tma_store_wait_read(e_out_bufs - 1);
-          named_barrier_sync(1, 128);  // this output tile and the residual tiles are free again
-          if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64 && c0 == 0) p.trace[(tile / gridDim.x) * 16 + 6] = clock64();
-          if (live && e_has_res && leader) {
-            const uint32_t rb = smem_u32(&res_bar);
-            mbar_arrive_expect_tx(rb, (e_res_split ? 2u : 1u) * 8192u);
-            tma_load_2d(res_stage, &map_r0, rb, n0 + c0, m_first);
-            if (e_res_split) tma_load_2d(res_stage + 8192u, &map_r1, rb, n0 + c0, m_first);
-          }
+        const uint32_t rb = smem_u32(&res_bar);
+        if (leader && e_has_res) {
+          mbar_arrive_expect_tx(rb, (e_res_split ? 2u : 1u) * 8192u);
+          tma_load_2d(res_stage, &map_r0, rb, n0, m_first);
+          if (e_res_split) tma_load_2d(res_stage + 8192u, &map_r1, rb, n0, m_first);
+        }
+        named_barrier_sync(1, 128);  // tile constants are in place
+        for (int c0 = 0; c0 < e_block_n && n0 + c0 < e_N; c0 += 16) {
+          const uint32_t stage0 = out_stage + static_cast<uint32_t>(out_slot) * out_tile_bytes;
           uint32_t v[16];
           tmem_ld16(t_row + static_cast<uint32_t>(c0), v);
           tmem_ld_wait();
-          if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64 && c0 == 0) p.trace[(tile / gridDim.x) * 16 + 7] = clock64();
-          if (!live) continue;
           float r[16];
           if (e_has_res) {
-            ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&res_bar), res_ph, abort_ptr,
-                                                           kTcWaitLimitNs) ? 1 : 0) != 0;
+            ok = __all_sync(0xffffffffu, mbar_wait_bounded(rb, res_ph, abort_ptr, kTcWaitLimitNs) ? 1 : 0) != 0;
             res_ph ^= 1u;
             if (!ok) break;
 #pragma unroll
@@ -550,6 +558,9 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
               r[4 * j + 2] = a.z;
               r[4 * j + 3] = a.w;
             }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r[j] = 0.0f;
           }
           float y[16];
           float cb[16], cs[16];
@@ -560,44 +571,52 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
             cb[4 * j + 1] = b4.y;
             cb[4 * j + 2] = b4.z;
             cb[4 * j + 3] = b4.w;
-            if (KIND == GEMM_I8) {
-              const float4 s4 = *reinterpret_cast<const float4*>(&tile_scale[c0 + 4 * j]);
-              cs[4 * j + 0] = s4.x;
-              cs[4 * j + 1] = s4.y;
-              cs[4 * j + 2] = s4.z;
-              cs[4 * j + 3] = s4.w;
-            }
+            const float4 s4 = *reinterpret_cast<const float4*>(&tile_scale[c0 + 4 * j]);
+            cs[4 * j + 0] = s4.x;
+            cs[4 * j + 1] = s4.y;
+            cs[4 * j + 2] = s4.z;
+            cs[4 * j + 3] = s4.w;
           }
-          tc_epilogue_values<KIND>(v, cb, cs, e_has_bias, e_has_res ? r : nullptr, e_act, e_act_a, e_act_b, y);
-          if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64 && c0 == 0) p.trace[(tile / gridDim.x) * 16 + 8] = clock64();
+          tc_epilogue_values<KIND>(v, cb, cs, r, e_act, e_act_a, e_act_b, y);
+          if (e_out_mode == OUT_F32) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            float hi[4], lo[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float t = y[4 * j + e];
-              hi[e] = e_out_mode == OUT_F32 ? t : round_tf32(t);
-              lo[e] = __fadd_rn(t, -hi[e]);
-            }
-            const uint32_t off = stage_chunk_offset(row, j);
-            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stage0 + off), "f"(hi[0]),
-                         "f"(hi[1]), "f"(hi[2]), "f"(hi[3])
-                         : "memory");
-            if (split)
-              asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stage0 + 8192u + off),
-                           "f"(lo[0]), "f"(lo[1]), "f"(lo[2]), "f"(lo[3])
+            for (int j = 0; j < 4; ++j)
+              asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stage0 + stage_chunk_offset(row, j)),
+                           "f"(y[4 * j]), "f"(y[4 * j + 1]), "f"(y[4 * j + 2]), "f"(y[4 * j + 3])
                            : "memory");
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float hi[4], lo[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                hi[e] = round_tf32(y[4 * j + e]);
+                lo[e] = __fadd_rn(y[4 * j + e], -hi[e]);
+              }
+              const uint32_t off = stage_chunk_offset(row, j);
+              asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stage0 + off), "f"(hi[0]),
+                           "f"(hi[1]), "f"(hi[2]), "f"(hi[3])
+                           : "memory");
+              if (split)
+                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stage0 + 8192u + off),
+                             "f"(lo[0]), "f"(lo[1]), "f"(lo[2]), "f"(lo[3])
+                             : "memory");
+            }
           }
           fence_proxy_async_smem();
-          if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64 && c0 == 0) p.trace[(tile / gridDim.x) * 16 + 9] = clock64();
           named_barrier_sync(2, 128);
-          if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64 && c0 == 0) p.trace[(tile / gridDim.x) * 16 + 10] = clock64();
           if (leader) {
             tma_store_2d(&map_o0, stage0, n0 + c0, m_first);
             if (split) tma_store_2d(&map_o1, stage0 + 8192u, n0 + c0, m_first);
             tma_store_commit();
+            tma_store_wait_read(e_out_bufs - 2);
+            const int c1 = c0 + 16;
+            if (e_has_res && c1 < e_block_n && n0 + c1 < e_N) {
+              mbar_arrive_expect_tx(rb, (e_res_split ? 2u : 1u) * 8192u);
+              tma_load_2d(res_stage, &map_r0, rb, n0 + c1, m_first);
+              if (e_res_split) tma_load_2d(res_stage + 8192u, &map_r1, rb, n0 + c1, m_first);
+            }
           }
-          if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64 && c0 == 0) p.trace[(tile / gridDim.x) * 16 + 11] = clock64();
           if (++out_slot == e_out_bufs) out_slot = 0;
         }
         if (!ok) break;
