@@ -145,12 +145,20 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
   // operand ring would drop below three stages
   const int out_tile = (e.out_mode == OUT_F32_SPLIT ? 2 : 1) * 8192;
   int staging = 0;
-  p.out_bufs = 1;
+  p.out_bufs = 2;
   if (p.tma_store) {
     for (int bufs : {4, 3, 2}) {
       p.out_bufs = bufs;
       staging = 16384 + bufs * out_tile;
       if ((222 * 1024 - staging) / p.stage_bytes >= 3 || bufs == 2) break;
+    }
+    // Deep contractions hide even a slow epilogue behind the main loop; there a third ring
+    // stage is worth more than the staging tiles.
+    const int with = (222 * 1024 - staging) / p.stage_bytes;
+    const int without = (222 * 1024) / p.stage_bytes;
+    if (with < 3 && without >= 3 && p.k_blocks >= 32) {
+      p.tma_store = 0;
+      staging = 0;
     }
   }
   const int budget = 222 * 1024 - staging;
