@@ -1443,7 +1443,18 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
       g.dh = node.dh;
       g.dw = node.dw;
       const void* w = node.d_w0;
-      if (node.kind == N_DW) {
+      if (node.kind == N_DW && !i8 && ti.c % 4 == 0 && node.KH == 3 && node.KW == 3 && node.dh == 1 &&
+          node.dw == 1 && node.sh == node.sw && (node.sh == 1 || node.sh == 2) && n <= 65535) {
+        const dim3 grid(((node.OH + 7) / 8) * ((node.OW + 7) / 8), (ti.c / 4 + 7) / 8, static_cast<unsigned>(n));
+        const int stride = node.sh;
+        const float* wf = static_cast<const float*>(w);
+        s.kernel = "k_depthwise3x3_tile";
+        s.run = [=](cudaStream_t st) {
+          if (stride == 1) k_depthwise3x3_tile<1><<<grid, 256, 0, st>>>(in, out, wf, g, e);
+          else k_depthwise3x3_tile<2><<<grid, 256, 0, st>>>(in, out, wf, g, e);
+          return launch_ok();
+        };
+      } else if (node.kind == N_DW) {
         const bool vec = ti.c % 4 == 0;
         const long long work = n * node.OH * node.OW * (vec ? ti.c / 4 : ti.c);
         const int grid = grid_for(work);

@@ -411,6 +411,69 @@ static __global__ void k_depthwise(ActRef in, ActRef out, const void* __restrict
   }
 }
 
+// 3x3 depthwise, fp32, dilation 1.  A block stages the input patch of an 8x8 output tile
+// for 32 channels in shared memory (hi + lo planes are summed on the way in), every thread
+// issuing several independent 128-bit loads, then each thread produces two outputs from
+// shared memory.  The patch is read once per tile (1.6x halo overhead at stride 1)
+// instead of once per filter tap.
+template <int STRIDE>
+static __global__ void __launch_bounds__(256) k_depthwise3x3_tile(ActRef in, ActRef out,
+                                                                  const float* __restrict__ weights,
+                                                                  ConvGeom g, ConvEpilogue e) {
+  constexpr int TO = 8;                      // output tile edge
+  constexpr int TI = (TO - 1) * STRIDE + 3;  // input patch edge
+  constexpr int CG = 8;                      // float4 channel groups per block
+  __shared__ float4 patch[TI * TI * CG];
+  const int tiles_w = (g.OW + TO - 1) / TO;
+  const int tile_y = blockIdx.x / tiles_w, tile_x = blockIdx.x - tile_y * tiles_w;
+  const int cg0 = blockIdx.y * CG;
+  const int cv = g.C / 4;
+  const long long img = blockIdx.z;
+  const int oy0 = tile_y * TO, ox0 = tile_x * TO;
+  const int iy0 = oy0 * STRIDE - g.pt, ix0 = ox0 * STRIDE - g.pl;
+  for (int idx = threadIdx.x; idx < TI * TI * CG; idx += 256) {
+    const int cg = idx % CG;
+    const int px = idx / CG;
+    const int py = px / TI;
+    const int iy = iy0 + py, ix = ix0 + (px - py * TI);
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (cg0 + cg < cv && iy >= 0 && iy < g.H && ix >= 0 && ix < g.W)
+      v = act_load4(in, ((img * g.H + iy) * g.W + ix) * static_cast<long long>(g.C) + (cg0 + cg) * 4);
+    patch[idx] = v;
+  }
+  __syncthreads();
+  for (int o = threadIdx.x; o < TO * TO * CG; o += 256) {
+    const int cg = o % CG;
+    const int p = o / CG;
+    const int ty = p / TO, tx = p - ty * TO;
+    const int oy = oy0 + ty, ox = ox0 + tx;
+    if (cg0 + cg >= cv || oy >= g.OH || ox >= g.OW) continue;
+    const int c = (cg0 + cg) * 4;
+    float4 acc = e.bias != nullptr ? *reinterpret_cast<const float4*>(e.bias + c)
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int kh = 0; kh < 3; ++kh) {
+#pragma unroll
+      for (int kw = 0; kw < 3; ++kw) {
+        const float4 x = patch[((ty * STRIDE + kh) * TI + tx * STRIDE + kw) * CG + cg];
+        const float4 k = __ldg(reinterpret_cast<const float4*>(weights + (kh * 3 + kw) * g.C + c));
+        acc.x = fmaf(x.x, k.x, acc.x);
+        acc.y = fmaf(x.y, k.y, acc.y);
+        acc.z = fmaf(x.z, k.z, acc.z);
+        acc.w = fmaf(x.w, k.w, acc.w);
+      }
+    }
+    const long long off = ((img * g.OH + oy) * g.OW + ox) * static_cast<long long>(g.C) + c;
+    float4 res = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (e.has_res) res = act_load4(e.res, off);
+    acc.x = conv_finish_f32(e, acc.x, res.x);
+    acc.y = conv_finish_f32(e, acc.y, res.y);
+    acc.z = conv_finish_f32(e, acc.z, res.z);
+    acc.w = conv_finish_f32(e, acc.w, res.w);
+    act_store4(out, off, acc);
+  }
+}
+
 // ----------------------------------------------------------------- direct conv / matmul
 // CUDA-core convolution: exact fp32 accumulation (fused multiply-add), any geometry.
 // Weights are stored [KH*KW][C][O].  One thread per (pixel, output channel); threads

@@ -304,3 +304,24 @@ def test_emit_stub_header_matches_reference_layout(pkg, tmp_path):
     assert len(header.encode()) == 1217
     assert "int relu_all(const float *input1, float *output1);" in header
     assert "#define RELU_ALL_INPUT1_ELEMENTS UINT64_C(60)" in header
+
+
+@pytest.mark.parametrize("c,h,w,stride,pad", [(8, 13, 9, 1, 1), (12, 20, 7, 2, 1), (4, 9, 9, 1, 0), (16, 17, 11, 2, 0), (40, 18, 18, 1, 1)])
+def test_depthwise_3x3_tile_kernel(pkg, oracle, tmp_path, c, h, w, stride, pad):
+    """Depthwise 3x3 with bias and ReLU over shapes that leave ragged tiles and channel groups."""
+    import struct
+    rng = np.random.default_rng(c * 100 + h)
+    wt = rng.standard_normal((c, 1, 3, 3)).astype(np.float32)
+    b = rng.standard_normal(c).astype(np.float32)
+    prefix = str(tmp_path / "dw")
+    with open(prefix + ".param", "w") as f:
+        f.write("7767517\n3 3\n")
+        f.write(f"Input input 0 1 data 0={w} 1={h} 2={c}\n")
+        f.write(f"ConvolutionDepthWise dw 1 1 data d 0={c} 1=3 3={stride} 4={pad} 5=1 6={wt.size} 7={c}\n")
+        f.write("ReLU relu 1 1 d output 0=0.0\n")
+    with open(prefix + ".bin", "wb") as f:
+        f.write(struct.pack("<I", 0) + wt.tobytes() + b.tobytes())
+    x = rng.standard_normal((3, c, h, w)).astype(np.float32)
+    for mode in (0, 2):
+        got, want = run_both(pkg, oracle, prefix + ".param", prefix + ".bin", x, mode)
+        assert rel_l2(got, want) <= 2e-6
