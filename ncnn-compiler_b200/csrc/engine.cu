@@ -1033,14 +1033,22 @@ bool EngineImpl::prepare_weights(std::string* err) {
     nodes_.insert(nodes_.begin() + k, std::move(q));
     ++k;
   }
-  // formats
-  for (Tensor& t : tensors_) {
+  // formats: an fp32 tensor is kept as hi/lo planes (or tf32-rounded in the fast mode) only
+  // when a tensor-core contraction reads it as its operand; everything else stays one
+  // plain fp32 plane, which halves the traffic of the memory-bound layers around it
+  std::vector<char> feeds_tc(tensors_.size(), 0);
+  for (const Node& n : nodes_) {
+    const bool contraction = n.kind == N_CONV || n.kind == N_IP || n.kind == N_GEMM;
+    if (contraction && n.impl == IMPL_TC && n.term == 0) feeds_tc[resolve(n.in[0])] = 1;
+  }
+  for (size_t i = 0; i < tensors_.size(); ++i) {
+    Tensor& t = tensors_[i];
     t.Cp = t.rank == 3 ? t.c : 1;
     t.Wp = t.w;
     t.w_off = 0;
     if (t.i8) {
       t.fmt = FMT_I8;
-    } else if (any_fp32_tc_) {
+    } else if (feeds_tc[resolve(static_cast<int>(i))]) {
       t.fmt = opt_.accuracy_mode == kAccuracyTf32 ? FMT_TF32 : FMT_SPLIT;
     } else {
       t.fmt = FMT_F32;
