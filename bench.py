@@ -290,9 +290,18 @@ def main():
     tc_flops = sum(r["flops"] for r in tc)
     total_ms = sum(r["ms"] for r in rows)
     achieved = tc_flops / (tc_ms * 1e-3) / 1e12 if tc_ms > 0 else 0.0
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "tc_gemm_dram_traffic.json")
+    workload = f"{args.model}-topology 3x224x224, batch {n} per GPU"
+    if os.path.exists(tpath) and args.accuracy_mode == 0:
+        with open(tpath) as f:
+            entry_ = json.load(f).get(workload)
+        if entry_:
+            traffic = entry_["dram_bytes_read"] + entry_["dram_bytes_write"]  # bytes per pass, from the ncu capture
     roofline = {"bound": "tensor", "kernel": tc[0]["kernel"] if tc else None, "achieved": achieved,
                 "peak": peaks["bf16_sustained"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_sustained"],
-                "peak_source": f"dense bf16 sustained, {peaks['source']}", "traffic": None,
+                "peak_source": f"dense bf16 sustained, {peaks['source']}", "traffic": traffic,
+                "traffic_note": "DRAM bytes of all tensor-core launches of one pass (ncu, profiles/)" if traffic else None,
                 "launches": len(tc), "share_of_step": tc_ms / total_ms if total_ms else None,
                 "flops_per_step": tc_flops}
     if args.per_layer:
@@ -313,7 +322,7 @@ def main():
         "metric": "images/sec", "value": total_images / (ms_dev * 1e-3), "unit": "images/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_dev / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
-        "config": {"workload": f"{args.model}-topology 3x224x224, batch {n} per GPU", "accuracy_mode": args.accuracy_mode,
+        "config": {"workload": workload, "accuracy_mode": args.accuracy_mode,
                    "l2": "flushed between timed iterations (256 MB write)", "gather": bool(gathered)},
         "e2e": {"value": total_images / (ms_e2e * 1e-3), "unit": "images/s",
                 "h2d_bytes_per_step": int(x_host.numel() * 4), "d2h_bytes_per_step": int(y_host.numel() * 4)},
