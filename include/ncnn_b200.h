@@ -51,6 +51,9 @@ typedef struct ncnn_b200_options {
    * followed by that many extents, outermost first ([c,h,w]). */
   int32_t input_shape_count;
   const int64_t *input_shapes;
+  /* 1 = parse, validate and infer shapes only, without touching a GPU: enough for
+   * ncnn_b200_emit_stub and the shape queries (a compile step), not for running. */
+  int32_t plan_only;
 } ncnn_b200_options;
 
 /* Replaces ncnn_graph::Graph::load + the compile pipeline (graph.hpp:379-380,

@@ -23,6 +23,7 @@ def needs_build() -> bool:
 
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not needs_build():
+        build_compile_tool()
         return LIB
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
     objects = []
@@ -43,7 +44,18 @@ def build(force: bool = False, verbose: bool = False) -> str:
     # only the C ABI is exported, as the reference restricts its library to the entry symbols
     subprocess.check_call([nvcc, "-shared", "-o", LIB, *objects, "-Xlinker", "--no-undefined", "-Xlinker",
                            "--version-script=" + os.path.join(CSRC, "exports.map")])
+    build_compile_tool()
     return LIB
+
+
+def build_compile_tool() -> str:
+    """ncnn-b200-compile: the sm_100a target of the reference's ncnn-compile (host tool, g++)."""
+    tool = os.path.join(HERE, "ncnn-b200-compile")
+    src = os.path.join(CSRC, "ncnn_b200_compile.cpp")
+    if not os.path.exists(tool) or os.path.getmtime(tool) < max(os.path.getmtime(src), os.path.getmtime(LIB)):
+        subprocess.check_call(["g++", "-std=c++17", "-O2", "-o", tool, src, "-L" + HERE, "-lncnn_b200",
+                               "-Wl,-rpath," + HERE])
+    return tool
 
 
 if __name__ == "__main__":

@@ -74,6 +74,7 @@ int ncnn_b200_load(const char* param_path, const char* bin_path, const ncnn_b200
     opt.accuracy_mode = options->accuracy_mode;
     opt.device = options->device;
     opt.use_cuda_graph = options->use_cuda_graph;
+    opt.plan_only = options->plan_only;
     const int64_t* p = options->input_shapes;
     for (int i = 0; i < options->input_shape_count && p != nullptr; ++i) {
       const int64_t rank = *p++;
@@ -267,7 +268,7 @@ int ncnn_b200_emit_stub(const ncnn_b200_model* m, const char* name, const char* 
   c << "/* Generated stub: exports the model entry point and forwards to libncnn_b200. */\n"
     << "#include <stddef.h>\n#include \"" << fn << ".h\"\n#include \"ncnn_b200.h\"\n\n"
     << "static ncnn_b200_model *g_model;\nstatic volatile int g_lock;\n\n"
-    << proto.str() << " {\n";
+    << "__attribute__((visibility(\"default\"))) " << proto.str() << " {\n";
   c << "  const float *inputs[" << e.input_count() << "] = {";
   for (int i = 0; i < e.input_count(); ++i) c << (i ? ", " : "") << "input" << i + 1;
   c << "};\n  float *outputs[" << e.output_count() << "] = {";

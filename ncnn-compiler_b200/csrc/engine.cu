@@ -1289,22 +1289,25 @@ bool EngineImpl::build(const std::string& param, const std::string& bin, const E
                        std::string* err) {
   opt_ = opt;
   if (opt.accuracy_mode < 0 || opt.accuracy_mode > 2) return fail(err, "unknown accuracy mode");
-  int count = 0;
-  if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0)
-    return fail(err, "no CUDA device is available: this runtime has no CPU path");
-  if (opt.device >= 0 && cudaSetDevice(opt.device) != cudaSuccess) return fail(err, "cannot select the requested CUDA device");
-  int dev = 0;
-  cudaGetDevice(&dev);
-  cudaDeviceProp prop;
-  if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return fail(err, "cannot query the CUDA device");
-  if (prop.major != 10) return fail(err, std::string("this runtime is built for sm_100a only; device is ") + prop.name);
-  sm_count_ = prop.multiProcessorCount;
+  if (!opt.plan_only) {
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0)
+      return fail(err, "no CUDA device is available: this runtime has no CPU path");
+    if (opt.device >= 0 && cudaSetDevice(opt.device) != cudaSuccess) return fail(err, "cannot select the requested CUDA device");
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return fail(err, "cannot query the CUDA device");
+    if (prop.major != 10) return fail(err, std::string("this runtime is built for sm_100a only; device is ") + prop.name);
+    sm_count_ = prop.multiProcessorCount;
+  }
   if (!load_model(param, bin, &model_, err)) return false;
   if (!model_.weights_loaded) return fail(err, "a .bin file is required");
   if (!import_layers(err)) return false;
   fold_batchnorm();
   fuse();
   if (!choose_impl(err)) return false;
+  if (opt.plan_only) return true;
   if (!prepare_weights(err)) return false;
   plan_memory();
   if (cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking) != cudaSuccess) return fail(err, "cannot create a stream");
@@ -1665,6 +1668,10 @@ void EngineImpl::make_edge_steps(int64_t n, const std::vector<const float*>& d_i
 }
 
 Plan* EngineImpl::plan_for(int64_t n) {
+  if (opt_.plan_only) {
+    error_ = "the model was loaded in plan-only mode and cannot run";
+    return nullptr;
+  }
   auto it = plans_.find(n);
   if (it != plans_.end()) return &it->second;
   // the arena is shared by all plans; grow it when a larger batch arrives.  Offsets
@@ -1705,6 +1712,10 @@ Plan* EngineImpl::plan_for(int64_t n) {
 }
 
 int EngineImpl::run(int64_t n, const float* const* in, float* const* out, bool host, cudaStream_t user_stream) {
+  if (opt_.plan_only) {
+    error_ = "the model was loaded in plan-only mode and cannot run";
+    return 6;
+  }
   if (n <= 0) {
     error_ = "batch size must be positive";
     return 2;
@@ -1916,6 +1927,7 @@ int Engine::run_device(int64_t n, const float* const* inputs, float* const* outp
 }
 int Engine::profile(int64_t n, int repeat, std::vector<LayerTiming>* out) { return impl_->profile(n, repeat, out); }
 int Engine::check_status() {
+  if (impl_->opt_.plan_only) return 0;
   int status = 0;
   if (cudaDeviceSynchronize() != cudaSuccess ||
       cudaMemcpy(&status, impl_->d_status_, 4, cudaMemcpyDeviceToHost) != cudaSuccess) {

@@ -25,6 +25,9 @@ struct EngineOptions {
   int accuracy_mode = kAccuracyFp32Split;
   int device = -1;        // -1: current device
   int use_cuda_graph = 1;
+  // 1: parse, validate, fuse and infer shapes only (no CUDA call, nothing uploaded); the
+  // model can describe itself and emit its stub but cannot run -- what a compile step needs
+  int plan_only = 0;
   // shape overrides for Input layers that carry no dimensions, in Input order,
   // each as ncnn dims [c,h,w] / [h,w] / [w]
   std::vector<std::vector<int64_t>> input_shapes;

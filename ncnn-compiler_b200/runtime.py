@@ -23,7 +23,7 @@ class NcnnB200Error(RuntimeError):
 class _Options(ctypes.Structure):
     _fields_ = [("struct_size", ctypes.c_uint32), ("accuracy_mode", c_int32), ("device", c_int32),
                 ("use_cuda_graph", c_int32), ("input_shape_count", c_int32),
-                ("input_shapes", POINTER(c_int64))]
+                ("input_shapes", POINTER(c_int64)), ("plan_only", c_int32)]
 
 
 def lib_path() -> str:
@@ -95,7 +95,7 @@ class Model:
     [*dims] for a single image), like n calls of the reference's entry point."""
 
     def __init__(self, param_path, bin_path, accuracy_mode=FP32_SPLIT, device=-1, use_cuda_graph=True,
-                 input_shapes=None):
+                 input_shapes=None, plan_only=False):
         self._L = load_library()
         self._h = c_void_p()
         flat = []
@@ -104,7 +104,7 @@ class Model:
             flat.extend(int(d) for d in s)
         arr = (c_int64 * max(len(flat), 1))(*flat)
         opt = _Options(ctypes.sizeof(_Options), accuracy_mode, device, 1 if use_cuda_graph else 0,
-                       len(input_shapes or []), ctypes.cast(arr, POINTER(c_int64)))
+                       len(input_shapes or []), ctypes.cast(arr, POINTER(c_int64)), 1 if plan_only else 0)
         st = self._L.ncnn_b200_load(param_path.encode(), bin_path.encode() if bin_path else None, byref(opt),
                                     byref(self._h))
         if st != 0:
