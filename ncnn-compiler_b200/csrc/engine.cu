@@ -37,7 +37,8 @@ struct Tensor {
   bool dedicated = false;          // never shares arena space (padding must stay zero)
 
   long long logical() const { return static_cast<long long>(c) * h * w; }
-  int planes() const { return fmt == FMT_SPLIT ? 2 : 1; }
+  int planes() const { return fmt == FMT_SPLIT || fmt == FMT_BF16X2 ? 2 : 1; }
+  int elem_bytes() const { return fmt == FMT_I8 ? 1 : (fmt == FMT_BF16X2 ? 2 : 4); }
 };
 
 struct Node {
@@ -1036,10 +1037,17 @@ bool EngineImpl::prepare_weights(std::string* err) {
   // formats: an fp32 tensor is kept as hi/lo planes (or tf32-rounded in the fast mode) only
   // when a tensor-core contraction reads it as its operand; everything else stays one
   // plain fp32 plane, which halves the traffic of the memory-bound layers around it
-  std::vector<char> feeds_tc(tensors_.size(), 0);
+  // In the accurate mode such a tensor is a bf16 pair (hi, mid) when every contraction that
+  // reads it can take 64-channel K blocks: three bf16 MMAs run at twice the rate of three
+  // tf32 MMAs on half the operand bytes, at the same ~1e-5 error.  Otherwise fp32 hi/lo planes.
+  std::vector<char> feeds_tc(tensors_.size(), 0), bf16_ok(tensors_.size(), 1);
   for (const Node& n : nodes_) {
     const bool contraction = n.kind == N_CONV || n.kind == N_IP || n.kind == N_GEMM;
-    if (contraction && n.impl == IMPL_TC && n.term == 0) feeds_tc[resolve(n.in[0])] = 1;
+    if (!(contraction && n.impl == IMPL_TC && n.term == 0)) continue;
+    const int src = resolve(n.in[0]);
+    feeds_tc[src] = 1;
+    const bool can = n.kind == N_CONV ? (!n.stem && tensors_[src].c % 64 == 0) : (n.K % 8 == 0);
+    if (!can) bf16_ok[src] = 0;
   }
   for (size_t i = 0; i < tensors_.size(); ++i) {
     Tensor& t = tensors_[i];
@@ -1049,7 +1057,7 @@ bool EngineImpl::prepare_weights(std::string* err) {
     if (t.i8) {
       t.fmt = FMT_I8;
     } else if (feeds_tc[resolve(static_cast<int>(i))]) {
-      t.fmt = opt_.accuracy_mode == kAccuracyTf32 ? FMT_TF32 : FMT_SPLIT;
+      t.fmt = opt_.accuracy_mode == kAccuracyTf32 ? FMT_TF32 : (bf16_ok[resolve(static_cast<int>(i))] ? FMT_BF16X2 : FMT_SPLIT);
     } else {
       t.fmt = FMT_F32;
     }
@@ -1067,7 +1075,7 @@ bool EngineImpl::prepare_weights(std::string* err) {
       Tensor& ti = tensors_[src];
       const int C = ti.c;
       if (n.impl == IMPL_TC) {
-        const int kind = i8 ? GEMM_I8 : f32_kind;
+        const int kind = i8 ? GEMM_I8 : (ti.fmt == FMT_BF16X2 ? GEMM_BF16X3 : f32_kind);
         if (n.stem) {
           const int cp = i8 ? 16 : 4;
           const int window = i8 ? 128 : 32;
@@ -1111,6 +1119,11 @@ bool EngineImpl::prepare_weights(std::string* err) {
             std::vector<int8_t> packed;
             tc_pack_weights_i8(n.w_i8.data(), n.O, C, n.KH, n.KW, n.k_elems, &packed);
             n.d_w0 = upload(packed);
+          } else if (kind == GEMM_BF16X3) {
+            std::vector<uint16_t> hi, mid;
+            tc_pack_weights_bf16x2(n.w_f32.data(), n.O, C, n.KH, n.KW, n.k_elems, &hi, &mid);
+            n.d_w0 = upload(hi);
+            n.d_w1 = upload(mid);
           } else {
             std::vector<float> hi, lo;
             tc_pack_weights_f32(kind, n.w_f32.data(), n.O, C, n.KH, n.KW, n.k_elems, &hi, &lo);
@@ -1165,14 +1178,22 @@ bool EngineImpl::prepare_weights(std::string* err) {
       if (n.kind == N_GEMM && i8) {
         n.d_w0 = upload(n.w_i8);  // [N][K] as is
       } else if (n.impl == IMPL_TC) {
-        const int kind = i8 ? GEMM_I8 : f32_kind;
-        n.k_elems = i8 ? 128 : 32;
+        const int kind = i8 ? GEMM_I8 : (ti.fmt == FMT_BF16X2 ? GEMM_BF16X3 : f32_kind);
+        n.k_elems = i8 ? 128 : (kind == GEMM_BF16X3 ? 64 : 32);
         if (i8) {
           std::vector<int8_t> v(n.w_i8.size()), packed;
           for (int o = 0; o < n.O; ++o)
             for (int k = 0; k < n.K; ++k) v[static_cast<size_t>(o) * n.K + k] = n.w_i8[static_cast<size_t>(o) * n.K + perm[k]];
           tc_pack_weights_i8(v.data(), n.O, n.K, 1, 1, n.k_elems, &packed);
           n.d_w0 = upload(packed);
+        } else if (kind == GEMM_BF16X3) {
+          std::vector<float> v(n.w_f32.size());
+          std::vector<uint16_t> hi, mid;
+          for (int o = 0; o < n.O; ++o)
+            for (int k = 0; k < n.K; ++k) v[static_cast<size_t>(o) * n.K + k] = n.w_f32[static_cast<size_t>(o) * n.K + perm[k]];
+          tc_pack_weights_bf16x2(v.data(), n.O, n.K, 1, 1, n.k_elems, &hi, &mid);
+          n.d_w0 = upload(hi);
+          n.d_w1 = upload(mid);
         } else {
           std::vector<float> v(n.w_f32.size()), hi, lo;
           for (int o = 0; o < n.O; ++o)
@@ -1212,7 +1233,7 @@ void EngineImpl::plan_memory() {
     if (t.alias >= 0) continue;
     t.plane_elems = t.rank == 3 ? static_cast<size_t>(t.h) * t.Wp * t.Cp : static_cast<size_t>(t.logical());
     if (t.dedicated) t.plane_elems += 256;  // the last window may read past the last row
-    t.plane_bytes = round_up(t.plane_elems * (t.fmt == FMT_I8 ? 1 : 4), 256);
+    t.plane_bytes = round_up(t.plane_elems * t.elem_bytes(), 256);
   }
   // liveness over node order; inputs are defined before node 0, outputs live to the end
   const int end = static_cast<int>(nodes_.size());
@@ -1279,7 +1300,7 @@ ActRef EngineImpl::ref(int tensor, int64_t n) const {
     r.q = reinterpret_cast<int8_t*>(base);
   } else {
     r.p0 = reinterpret_cast<float*>(base);
-    if (t.fmt == FMT_SPLIT) r.p1 = reinterpret_cast<float*>(base + t.plane_bytes * static_cast<size_t>(n));
+    if (t.planes() == 2) r.p1 = reinterpret_cast<float*>(base + t.plane_bytes * static_cast<size_t>(n));
   }
   return r;
 }
@@ -1320,6 +1341,15 @@ bool EngineImpl::build(const std::string& param, const std::string& bin, const E
 }
 
 static cudaError_t launch_ok() { return cudaGetLastError(); }
+
+// The patch-resident convolution kernel applies to stride-1 filters; measured inside whole
+// networks (batch 64, 3x3 filters at 56/28/14 pixels) it ties with the im2col kernel once the
+// operands are bf16 pairs, and loses a little where its 16x8 tiles overhang the image, so it
+// is opt-in: NCNN_B200_HALO=1 at load time selects it wherever it applies.
+static bool halo_preferred() {
+  const char* f = std::getenv("NCNN_B200_HALO");
+  return f != nullptr && f[0] == '1';
+}
 
 bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string* err) {
   const Tensor& to = tensors_[resolve(node.out)];
@@ -1377,20 +1407,51 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
       te.act_b = node.act_b;
       te.out_scale = node.s_out;
       te.status = d_status_;
-      te.out_mode = to.fmt == FMT_I8 ? OUT_I8 : (to.fmt == FMT_SPLIT ? OUT_F32_SPLIT : (to.fmt == FMT_TF32 ? OUT_F32_TF32 : OUT_F32));
+      te.out_mode = to.fmt == FMT_I8 ? OUT_I8 : (to.fmt == FMT_SPLIT ? OUT_F32_SPLIT : (to.fmt == FMT_TF32 ? OUT_F32_TF32 : (to.fmt == FMT_BF16X2 ? OUT_BF16X2 : OUT_F32)));
       if (node.res >= 0) {
         const ActRef r = ref(node.res, n);
         te.res0 = r.p0;
         te.res1 = r.p1;
+        te.res_bf16 = r.fmt == FMT_BF16X2;
       }
-      const int kind = i8 ? GEMM_I8 : f32_kind;
+      const int kind = i8 ? GEMM_I8 : (ti.fmt == FMT_BF16X2 ? GEMM_BF16X3 : f32_kind);
+      const char* kind_name = kind == GEMM_I8 ? "i8" : (kind == GEMM_TF32 ? "tf32" : (kind == GEMM_BF16X3 ? "bf16x3" : "tf32x3"));
       auto launch = std::make_shared<TcLaunch>();
       std::string perr;
+      // stride-1 filters with spatial extent: the patch-resident kernel loads each input pixel
+      // once per tile instead of once per tap
+      if (node.kind == N_CONV && !i8 && !node.stem && halo_preferred() &&
+          tc_halo_applies(kind, ti.c, node.KH, node.KW, node.sh, node.sw, node.dh, node.dw, node.OH, node.OW, node.O,
+                          te.out_mode)) {
+        TcHaloConv hc;
+        hc.in0 = in.p0;
+        hc.in1 = in.p1;
+        hc.images = static_cast<int>(n);
+        hc.H = ti.h;
+        hc.W = ti.w;
+        hc.C = ti.c;
+        hc.KH = node.KH;
+        hc.KW = node.KW;
+        hc.pad_t = node.pt;
+        hc.pad_l = node.pl;
+        hc.OH = node.OH;
+        hc.OW = node.OW;
+        hc.w0 = node.d_w0;
+        hc.w1 = node.d_w1;
+        hc.out_channels = node.O;
+        auto hl = std::make_shared<TcHaloLaunch>();
+        if (tc_plan_conv_halo(hl.get(), kind, hc, te, sm_count_).empty()) {
+          s.kernel = std::string("tc_conv_halo_kernel<") + kind_name + ">";
+          s.run = [hl](cudaStream_t st) { return tc_launch_halo(*hl, st); };
+          plan.steps.push_back(std::move(s));
+          return true;
+        }
+      }
       if (node.kind == N_CONV) {
         TcIm2colView v;
         v.plane0 = i8 ? static_cast<const void*>(in.q) : static_cast<const void*>(in.p0);
         v.plane1 = in.p1;
-        const size_t es = i8 ? 1 : 4;
+        const size_t es = static_cast<size_t>(tc_elem_bytes(kind));
         if (node.stem) {
           v.C = node.k_elems;
           v.W = node.OW;
@@ -1433,7 +1494,7 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
         perr = tc_plan_gemm(launch.get(), kind, a0, in.p1, M, node.K, node.K, node.d_w0, node.d_w1, node.O, te, sm_count_);
       }
       if (!perr.empty()) return fail(err, "layer " + node.name + ": " + perr);
-      s.kernel = kind == GEMM_I8 ? "tc_gemm_kernel<i8>" : (kind == GEMM_TF32 ? "tc_gemm_kernel<tf32>" : "tc_gemm_kernel<tf32x3>");
+      s.kernel = std::string("tc_gemm_kernel<") + kind_name + ">";
       s.run = [launch](cudaStream_t st) { return tc_launch(*launch, st); };
       plan.steps.push_back(std::move(s));
     } else if (node.kind == N_CONV || node.kind == N_DW) {
@@ -1592,7 +1653,7 @@ void EngineImpl::make_edge_steps(int64_t n, const std::vector<const float*>& d_i
     const float* src_ptr = d_in[i];
     Step s;
     s.name = "input:" + t.name;
-    s.bytes = static_cast<double>(t.logical()) * n * (4 + (t.fmt == FMT_I8 ? 1 : 4 * t.planes()));
+    s.bytes = static_cast<double>(t.logical()) * n * (4 + t.elem_bytes() * t.planes());
     if (t.rank == 3) {
       EdgeParams ep{};
       ep.images = n;
@@ -1640,7 +1701,7 @@ void EngineImpl::make_edge_steps(int64_t n, const std::vector<const float*>& d_i
     float* dst_ptr = d_out[i];
     Step s;
     s.name = "output:" + t.name;
-    s.bytes = static_cast<double>(t.logical()) * n * (4 + (t.fmt == FMT_I8 ? 1 : 4 * t.planes()));
+    s.bytes = static_cast<double>(t.logical()) * n * (4 + t.elem_bytes() * t.planes());
     if (t.rank == 3) {
       const dim3 grid((t.h * t.w + 31) / 32, (t.c + 31) / 32, static_cast<unsigned>(n));
       const int C = t.c, HW = t.h * t.w, Cp = t.Cp;

@@ -1,10 +1,12 @@
 // Memory-bound and CUDA-core kernels of the runtime.  Activations live in HBM as
-// channel-last arrays ([image][h][w][c], c contiguous) in one of three formats:
+// channel-last arrays ([image][h][w][c], c contiguous) in one of these formats:
 //   FMT_F32    one fp32 plane
 //   FMT_SPLIT  two fp32 planes hi/lo with x == hi + lo exactly (hi is x rounded to
 //              tf32); feeds the 3xTF32 tensor-core path
 //   FMT_I8     one int8 plane
 //   FMT_TF32   one fp32 plane whose values are rounded to tf32 when stored
+//   FMT_BF16X2 two bf16 planes hi/mid with x ~ hi + mid (16 significant bits); feeds the
+//              bf16x3 tensor-core path.  The planes are addressed through p0/p1.
 // All kernels index with 64-bit offsets, use 128-bit accesses when the channel
 // count allows, and keep the reference's order of operations where it affects
 // the result (no FMA in int8 epilogues, sequential window sums).
@@ -17,7 +19,7 @@
 
 namespace nb {
 
-enum : int { FMT_F32 = 0, FMT_SPLIT = 1, FMT_I8 = 2, FMT_TF32 = 3 };
+enum : int { FMT_F32 = 0, FMT_SPLIT = 1, FMT_I8 = 2, FMT_TF32 = 3, FMT_BF16X2 = 4 };
 
 struct ActRef {
   float* p0 = nullptr;
@@ -28,6 +30,10 @@ struct ActRef {
 
 __device__ __forceinline__ float act_load(const ActRef& a, long long i) {
   if (a.fmt == FMT_I8) return static_cast<float>(a.q[i]);
+  if (a.fmt == FMT_BF16X2) {
+    const uint32_t h = reinterpret_cast<const uint16_t*>(a.p0)[i], m = reinterpret_cast<const uint16_t*>(a.p1)[i];
+    return __fadd_rn(__uint_as_float(h << 16), __uint_as_float(m << 16));
+  }
   float v = a.p0[i];
   if (a.fmt == FMT_SPLIT) v = __fadd_rn(v, a.p1[i]);
   return v;
@@ -38,6 +44,11 @@ __device__ __forceinline__ void act_store(const ActRef& a, long long i, float v)
     a.q[i] = static_cast<int8_t>(static_cast<int>(v));
   } else if (a.fmt == FMT_F32) {
     a.p0[i] = v;
+  } else if (a.fmt == FMT_BF16X2) {
+    uint32_t hi, mid;
+    split_bf16x2(v, 0.0f, hi, mid);
+    reinterpret_cast<uint16_t*>(a.p0)[i] = static_cast<uint16_t>(hi & 0xffffu);
+    reinterpret_cast<uint16_t*>(a.p1)[i] = static_cast<uint16_t>(mid & 0xffffu);
   } else {
     const float hi = round_tf32(v);
     a.p0[i] = hi;
@@ -49,6 +60,12 @@ __device__ __forceinline__ float4 act_load4(const ActRef& a, long long i) {
   if (a.fmt == FMT_I8) {
     const char4 c = *reinterpret_cast<const char4*>(a.q + i);
     return make_float4(c.x, c.y, c.z, c.w);
+  }
+  if (a.fmt == FMT_BF16X2) {
+    const uint2 h = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(a.p0) + i);
+    const uint2 m = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(a.p1) + i);
+    return make_float4(__fadd_rn(bf16_low(h.x), bf16_low(m.x)), __fadd_rn(bf16_high(h.x), bf16_high(m.x)),
+                       __fadd_rn(bf16_low(h.y), bf16_low(m.y)), __fadd_rn(bf16_high(h.y), bf16_high(m.y)));
   }
   float4 v = *reinterpret_cast<const float4*>(a.p0 + i);
   if (a.fmt == FMT_SPLIT) {
@@ -70,6 +87,12 @@ __device__ __forceinline__ void act_store4(const ActRef& a, long long i, float4 
                    static_cast<signed char>(static_cast<int>(v.w)));
   } else if (a.fmt == FMT_F32) {
     *reinterpret_cast<float4*>(a.p0 + i) = v;
+  } else if (a.fmt == FMT_BF16X2) {
+    uint2 h, m;
+    split_bf16x2(v.x, v.y, h.x, m.x);
+    split_bf16x2(v.z, v.w, h.y, m.y);
+    *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(a.p0) + i) = h;
+    *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(a.p1) + i) = m;
   } else {
     const float4 hi = make_float4(round_tf32(v.x), round_tf32(v.y), round_tf32(v.z), round_tf32(v.w));
     *reinterpret_cast<float4*>(a.p0 + i) = hi;

@@ -51,10 +51,11 @@ CUtensorMapSwizzle swizzle_for(int row_bytes) {
 }
 
 CUtensorMapDataType dtype_for(int kind) {
-  return kind == GEMM_I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  return kind == GEMM_I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                         : (kind == GEMM_BF16X3 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32);
 }
 
-int elem_bytes(int kind) { return kind == GEMM_I8 ? 1 : 4; }
+int elem_bytes(int kind) { return tc_elem_bytes(kind); }
 
 std::string encode_tiled_2d(CUtensorMap* map, int kind, const void* base, uint64_t inner,
                             uint64_t outer, uint64_t outer_stride_bytes, uint32_t box_inner,
@@ -107,10 +108,10 @@ std::string encode_im2col(CUtensorMap* map, int kind, const void* base, const Tc
 // Tile width: every multiple of 16 up to 128 is a legal UMMA N.  Cost model:
 // waves over the SMs times (columns computed + a fixed per-tile term for the
 // A traffic and pipeline fill, which do not shrink with the tile).
-int choose_block_n(long long tiles_m, int N, int sm_count) {
-  int best = 16;
+int choose_block_n(long long tiles_m, int N, int sm_count, int step) {
+  int best = step;
   double best_cost = 1e300;
-  for (int bn = 16; bn <= 128; bn += 16) {
+  for (int bn = step; bn <= 128; bn += step) {
     const long long tiles = tiles_m * ((N + bn - 1) / bn);
     const long long waves = (tiles + sm_count - 1) / sm_count;
     const double cost = static_cast<double>(waves) * (bn + 24);
@@ -127,23 +128,30 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
   p.M = static_cast<int>(M);
   p.N = N;
   p.tiles_m = static_cast<int>((M + kTcBlockM - 1) / kTcBlockM);
-  p.block_n = choose_block_n(p.tiles_m, N, sm_count);
+  // a bf16-pair output or residual is staged 32 columns at a time
+  const int res_mode = e.res0 == nullptr ? RES_NONE : (e.res_bf16 ? RES_BF16X2 : (e.res1 != nullptr ? RES_SPLIT : RES_F32));
+  const bool wide = e.out_mode == OUT_BF16X2 || res_mode == RES_BF16X2;
+  p.block_n = choose_block_n(p.tiles_m, N, sm_count, wide ? 32 : 16);
   p.tiles_n = (N + p.block_n - 1) / p.block_n;
-  const int planes = kind == GEMM_TF32X3 ? 2 : 1;
+  const int planes = tc_planes(kind);
   // a stage holds the A tile(s) and block_n rows of B, every sub-buffer 1 KB aligned
   const int b_bytes = (p.block_n * p.row_bytes + 1023) / 1024 * 1024;
   p.stage_bytes = planes * (kTcBlockM * p.row_bytes + b_bytes);
   // fp32 results leave through TMA stores when rows are 16-byte multiples; the staging
   // tiles (out hi/lo, residual hi/lo, 8 KB each) sit behind the ring
   const bool f32_out = e.out_mode != OUT_I8;
-  const bool aligned = e.ldo % 4 == 0 && (reinterpret_cast<uintptr_t>(e.out0) & 15) == 0 &&
+  const bool aligned = e.ldo % (wide ? 8 : 4) == 0 && (reinterpret_cast<uintptr_t>(e.out0) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(e.out1) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(e.res0) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(e.res1) & 15) == 0;
-  p.tma_store = f32_out && aligned ? 1 : 0;
+  // (a wide chunk cannot carry fp32 hi/lo planes: that pairing does not occur, the direct path covers it)
+  p.tma_store = f32_out && aligned && !(wide && (e.out_mode == OUT_F32_SPLIT || e.out_mode == OUT_F32_TF32 ||
+                                                  res_mode == RES_SPLIT))
+                    ? 1
+                    : 0;
   // residual tiles (16 KB) + two to four output tiles of 8 KB per plane; fewer when the
   // operand ring would drop below three stages
-  const int out_tile = (e.out_mode == OUT_F32_SPLIT ? 2 : 1) * 8192;
+  const int out_tile = (e.out_mode == OUT_F32_SPLIT || wide ? 2 : 1) * 8192;
   int staging = 0;
   p.out_bufs = 2;
   if (p.tma_store) {
@@ -177,6 +185,7 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
   p.outq = e.outq;
   p.res0 = e.res0;
   p.res1 = e.res1;
+  p.res_mode = res_mode;
   p.ldo = e.ldo;
   p.out_mode = e.out_mode;
   p.act = e.act;
@@ -188,13 +197,15 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
   L->map_o0 = L->map_o1 = L->map_r0 = L->map_r1 = CUtensorMap{};
 }
 
-// [M][N] fp32 plane seen as a 2-D tensor (N innermost) with 16 x 128 boxes, 64-byte swizzle
-std::string encode_plane(CUtensorMap* map, const void* base, long long M, int N, long long ld) {
+// [M][N] plane seen as a 2-D tensor (N innermost) with boxes of 64 bytes (16 fp32 or 32 bf16)
+// x 128 rows, 64-byte swizzle
+std::string encode_plane(CUtensorMap* map, const void* base, long long M, int N, long long ld, bool bf16) {
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 4};
-  const cuuint32_t box[2] = {16, static_cast<cuuint32_t>(kTcBlockM)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * (bf16 ? 2 : 4)};
+  const cuuint32_t box[2] = {bf16 ? 32u : 16u, static_cast<cuuint32_t>(kTcBlockM)};
   const cuuint32_t elem_strides[2] = {1, 1};
-  const CUresult r = g_encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base),
+  const CUresult r = g_encode_tiled(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                                    const_cast<void*>(base),
                                     dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                     CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -205,10 +216,12 @@ std::string encode_plane(CUtensorMap* map, const void* base, long long M, int N,
 
 std::string encode_epilogue_maps(TcLaunch* L, const TcEpilogue& e) {
   if (!L->p.tma_store) return {};
-  std::string err = encode_plane(&L->map_o0, e.out0, L->p.M, L->p.N, e.ldo);
-  if (err.empty() && e.out_mode == OUT_F32_SPLIT) err = encode_plane(&L->map_o1, e.out1, L->p.M, L->p.N, e.ldo);
-  if (err.empty() && e.res0 != nullptr) err = encode_plane(&L->map_r0, e.res0, L->p.M, L->p.N, e.ldo);
-  if (err.empty() && e.res1 != nullptr) err = encode_plane(&L->map_r1, e.res1, L->p.M, L->p.N, e.ldo);
+  const bool ob = e.out_mode == OUT_BF16X2;
+  std::string err = encode_plane(&L->map_o0, e.out0, L->p.M, L->p.N, e.ldo, ob);
+  if (err.empty() && (e.out_mode == OUT_F32_SPLIT || ob))
+    err = encode_plane(&L->map_o1, e.out1, L->p.M, L->p.N, e.ldo, ob);
+  if (err.empty() && e.res0 != nullptr) err = encode_plane(&L->map_r0, e.res0, L->p.M, L->p.N, e.ldo, e.res_bf16);
+  if (err.empty() && e.res1 != nullptr) err = encode_plane(&L->map_r1, e.res1, L->p.M, L->p.N, e.ldo, e.res_bf16);
   return err;
 }
 
@@ -219,6 +232,7 @@ int tc_row_bytes(int kind, int channels) {
     if (channels % 16 != 0) return 0;
     return channels > 64 ? 128 : (channels > 32 ? 64 : 32);
   }
+  if (kind == GEMM_BF16X3) return channels % 64 == 0 ? 128 : 0;
   if (channels % 4 != 0) return 0;
   return 128;
 }
@@ -226,7 +240,7 @@ int tc_row_bytes(int kind, int channels) {
 int tc_k_elems(int kind, int channels) {
   const int rb = tc_row_bytes(kind, channels);
   if (rb == 0) return 0;
-  return kind == GEMM_I8 ? rb : rb / 4;
+  return rb / tc_elem_bytes(kind);
 }
 
 std::string tc_plan_conv(TcLaunch* L, int kind, const TcIm2colView& v, const void* w0,
@@ -238,7 +252,7 @@ std::string tc_plan_conv(TcLaunch* L, int kind, const TcIm2colView& v, const voi
   TcGemmParams& p = L->p;
   std::memset(&p, 0, sizeof(p));
   p.row_bytes = rb;
-  p.k_elems = kind == GEMM_I8 ? rb : rb / 4;
+  p.k_elems = rb / tc_elem_bytes(kind);
   p.c_blocks = static_cast<int>((v.C + p.k_elems - 1) / p.k_elems);
   p.k_blocks = v.KH * v.KW * p.c_blocks;
   p.a_im2col = 1;
@@ -257,7 +271,7 @@ std::string tc_plan_conv(TcLaunch* L, int kind, const TcIm2colView& v, const voi
 
   std::string err = encode_im2col(&L->map_a0, kind, v.plane0, v, p.k_elems, rb);
   if (!err.empty()) return err;
-  if (kind == GEMM_TF32X3) {
+  if (tc_planes(kind) == 2) {
     err = encode_im2col(&L->map_a1, kind, v.plane1, v, p.k_elems, rb);
     if (!err.empty()) return err;
   } else {
@@ -267,7 +281,7 @@ std::string tc_plan_conv(TcLaunch* L, int kind, const TcIm2colView& v, const voi
   err = encode_tiled_2d(&L->map_b0, kind, w0, k_total, out_channels,
                         k_total * elem_bytes(kind), p.k_elems, p.block_n, rb);
   if (!err.empty()) return err;
-  if (kind == GEMM_TF32X3) {
+  if (tc_planes(kind) == 2) {
     err = encode_tiled_2d(&L->map_b1, kind, w1, k_total, out_channels,
                           k_total * elem_bytes(kind), p.k_elems, p.block_n, rb);
     if (!err.empty()) return err;
@@ -297,7 +311,7 @@ std::string tc_plan_gemm(TcLaunch* L, int kind, const void* a0, const void* a1, 
   finish_plan(L, kind, M, N, e, sm_count);
   std::string err = encode_tiled_2d(&L->map_a0, kind, a0, K, M, lda * es, p.k_elems, kTcBlockM, 128);
   if (!err.empty()) return err;
-  if (kind == GEMM_TF32X3) {
+  if (tc_planes(kind) == 2) {
     err = encode_tiled_2d(&L->map_a1, kind, a1, K, M, lda * es, p.k_elems, kTcBlockM, 128);
     if (!err.empty()) return err;
   } else {
@@ -306,7 +320,7 @@ std::string tc_plan_gemm(TcLaunch* L, int kind, const void* a0, const void* a1, 
   const uint64_t k_total = static_cast<uint64_t>(p.k_blocks) * p.k_elems;
   err = encode_tiled_2d(&L->map_b0, kind, w0, k_total, N, k_total * es, p.k_elems, p.block_n, 128);
   if (!err.empty()) return err;
-  if (kind == GEMM_TF32X3) {
+  if (tc_planes(kind) == 2) {
     err = encode_tiled_2d(&L->map_b1, kind, w1, k_total, N, k_total * es, p.k_elems, p.block_n, 128);
     if (!err.empty()) return err;
   } else {
@@ -328,6 +342,9 @@ cudaError_t tc_launch(const TcLaunch& L, cudaStream_t stream) {
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(tc_gemm_kernel<GEMM_I8>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(tc_gemm_kernel<GEMM_BF16X3>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
     attr_err = e;
   });
   if (attr_err != cudaSuccess) return attr_err;
@@ -343,11 +360,162 @@ cudaError_t tc_launch(const TcLaunch& L, cudaStream_t stream) {
           <<<grid, block, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
                                                   L.map_o1, L.map_r0, L.map_r1);
       break;
+    case GEMM_BF16X3:
+      tc_gemm_kernel<GEMM_BF16X3>
+          <<<grid, block, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
+                                                  L.map_o1, L.map_r0, L.map_r1);
+      break;
     default:
       tc_gemm_kernel<GEMM_I8>
           <<<grid, block, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
                                                   L.map_o1, L.map_r0, L.map_r1);
       break;
+  }
+  return cudaGetLastError();
+}
+
+// ------------------------------------------------------------------ patch-resident convolution
+namespace {
+
+std::string encode_tiled_4d(CUtensorMap* map, bool bf16, const void* base, int C, int W, int H, int N, uint32_t box_c,
+                            uint32_t box_w, uint32_t box_h, CUtensorMapSwizzle swizzle) {
+  const cuuint64_t es = bf16 ? 2 : 4;
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(C), static_cast<cuuint64_t>(W), static_cast<cuuint64_t>(H),
+                              static_cast<cuuint64_t>(N)};
+  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(C) * es, static_cast<cuuint64_t>(C) * es * W,
+                                 static_cast<cuuint64_t>(C) * es * W * H};
+  const cuuint32_t box[4] = {box_c, box_w, box_h, 1};
+  const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
+  const CUresult r = g_encode_tiled(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4,
+                                    const_cast<void*>(base), dims, strides,
+                                    box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return "cuTensorMapEncodeTiled (4-D) failed with code " + std::to_string(static_cast<int>(r));
+  return {};
+}
+
+}  // namespace
+
+bool tc_halo_applies(int kind, int C, int KH, int KW, int stride_h, int stride_w, int dil_h, int dil_w, int OH,
+                     int OW, int out_channels, int out_mode) {
+  if (kind != GEMM_TF32 && kind != GEMM_TF32X3 && kind != GEMM_BF16X3) return false;
+  if (stride_h != 1 || stride_w != 1 || dil_h != 1 || dil_w != 1) return false;
+  if (KH * KW < 2 || KH > 7 || KW > 7) return false;  // a 1x1 filter has nothing to reuse
+  if (C % (kind == GEMM_BF16X3 ? 64 : 32) != 0 || out_channels % 4 != 0 || out_mode == OUT_I8) return false;
+  if (out_mode == OUT_BF16X2 && out_channels % 32 != 0) return false;
+  const double covered = static_cast<double>((OH + kHaloTileH - 1) / kHaloTileH * kHaloTileH) *
+                         ((OW + kHaloTileW - 1) / kHaloTileW * kHaloTileW);
+  return static_cast<double>(OH) * OW / covered >= 0.70;
+}
+
+std::string tc_plan_conv_halo(TcHaloLaunch* L, int kind, const TcHaloConv& c, const TcEpilogue& e, int sm_count) {
+  load_driver_entry_points();
+  if (!g_driver_error.empty()) return g_driver_error;
+  TcHaloParams& p = L->p;
+  std::memset(&p, 0, sizeof(p));
+  const int planes = tc_planes(kind);
+  const bool a_bf16 = kind == GEMM_BF16X3;
+  const int res_mode = e.res0 == nullptr ? RES_NONE : (e.res_bf16 ? RES_BF16X2 : (e.res1 != nullptr ? RES_SPLIT : RES_F32));
+  const bool out_bf16 = e.out_mode == OUT_BF16X2;
+  const bool wide = out_bf16 || res_mode == RES_BF16X2;
+  if (wide && (e.out_mode == OUT_F32_SPLIT || e.out_mode == OUT_F32_TF32 || res_mode == RES_SPLIT))
+    return "fp32 hi/lo planes cannot be staged together with a bf16-pair tensor";
+  if (e.ldo != c.out_channels) return "the patch-resident kernel writes dense channel-last rows";
+  p.images = c.images;
+  p.OH = c.OH;
+  p.OW = c.OW;
+  p.N = c.out_channels;
+  p.tiles_y = (c.OH + kHaloTileH - 1) / kHaloTileH;
+  p.tiles_x = (c.OW + kHaloTileW - 1) / kHaloTileW;
+  // an MMA of any N <= 128 costs the same issue time: take the widest tile
+  const int step = wide ? 32 : 16;
+  p.block_n = c.out_channels >= 128 ? 128 : (c.out_channels + step - 1) / step * step;
+  p.tiles_n = (c.out_channels + p.block_n - 1) / p.block_n;
+  p.k_elems = 128 / tc_elem_bytes(kind);
+  p.c_blocks = c.C / p.k_elems;
+  p.taps = c.KH * c.KW;
+  p.KW = c.KW;
+  p.pad_t = c.pad_t;
+  p.pad_l = c.pad_l;
+  p.patch_h = kHaloTileH + c.KH - 1;
+  p.patch_w = kHaloTileW + c.KW - 1;
+  p.patch_bytes = (p.patch_h * p.patch_w * 128 + 1023) / 1024 * 1024;
+  p.b_bytes = (p.block_n * 128 + 1023) / 1024 * 1024;
+  p.bias = e.bias;
+  p.res_mode = res_mode;
+  p.out_mode = e.out_mode;
+  p.act = e.act;
+  p.act_a = e.act_a;
+  p.act_b = e.act_b;
+  p.status = e.status;
+  const int out_tile = (e.out_mode == OUT_F32_SPLIT || wide ? 2 : 1) * 8192;
+  const int fixed = 2 * planes * p.patch_bytes + (res_mode != RES_NONE ? 16384 : 0);
+  p.out_bufs = 4;
+  p.stages = (222 * 1024 - fixed - p.out_bufs * out_tile) / (planes * p.b_bytes);
+  if (p.stages < 4) {
+    p.out_bufs = 2;
+    p.stages = (222 * 1024 - fixed - p.out_bufs * out_tile) / (planes * p.b_bytes);
+  }
+  p.stages = std::min(p.stages, kTcMaxStages);
+  if (p.stages < 2) return "shared memory cannot hold the patch buffers and two weight stages";
+  L->smem_bytes = fixed + p.out_bufs * out_tile + p.stages * planes * p.b_bytes + 1024;
+  L->smem_bytes = std::max(L->smem_bytes, 120 * 1024);
+  const long long tiles = static_cast<long long>(c.images) * p.tiles_y * p.tiles_x * p.tiles_n;
+  if (tiles > 0x7fffffffll) return "too many tiles for one launch";
+  L->grid = static_cast<int>(std::min<long long>(tiles, sm_count));
+  L->kind = kind;
+
+  std::string err = encode_tiled_4d(&L->map_a0, a_bf16, c.in0, c.C, c.W, c.H, c.images, p.k_elems, p.patch_w,
+                                    p.patch_h, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (err.empty() && planes == 2)
+    err = encode_tiled_4d(&L->map_a1, a_bf16, c.in1, c.C, c.W, c.H, c.images, p.k_elems, p.patch_w, p.patch_h,
+                          CU_TENSOR_MAP_SWIZZLE_128B);
+  if (!err.empty()) return err;
+  const uint64_t k_total = static_cast<uint64_t>(p.taps) * p.c_blocks * p.k_elems;
+  err = encode_tiled_2d(&L->map_b0, kind, c.w0, k_total, c.out_channels, k_total * tc_elem_bytes(kind), p.k_elems,
+                        p.block_n, 128);
+  if (err.empty() && planes == 2)
+    err = encode_tiled_2d(&L->map_b1, kind, c.w1, k_total, c.out_channels, k_total * tc_elem_bytes(kind), p.k_elems,
+                          p.block_n, 128);
+  if (!err.empty()) return err;
+  // outputs and residuals: [image][OH][OW][N], tiles of 64 bytes of channels x 8 x 16 pixels, 64-byte swizzle
+  auto plane = [&](CUtensorMap* map, const void* base, bool bf16) {
+    return encode_tiled_4d(map, bf16, base, c.out_channels, c.OW, c.OH, c.images, bf16 ? 32 : 16, kHaloTileW,
+                           kHaloTileH, CU_TENSOR_MAP_SWIZZLE_64B);
+  };
+  err = plane(&L->map_o0, e.out0, out_bf16);
+  if (err.empty() && (e.out_mode == OUT_F32_SPLIT || out_bf16)) err = plane(&L->map_o1, e.out1, out_bf16);
+  if (err.empty() && e.res0 != nullptr) err = plane(&L->map_r0, e.res0, e.res_bf16);
+  if (err.empty() && e.res1 != nullptr) err = plane(&L->map_r1, e.res1, e.res_bf16);
+  return err;
+}
+
+cudaError_t tc_launch_halo(const TcHaloLaunch& L, cudaStream_t stream) {
+  static std::once_flag attr_once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(attr_once, [] {
+    const int max_smem = 224 * 1024;
+    cudaError_t e = cudaFuncSetAttribute(tc_conv_halo_kernel<GEMM_TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         max_smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(tc_conv_halo_kernel<GEMM_TF32X3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               max_smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(tc_conv_halo_kernel<GEMM_BF16X3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               max_smem);
+    attr_err = e;
+  });
+  if (attr_err != cudaSuccess) return attr_err;
+  if (L.kind == GEMM_BF16X3) {
+    tc_conv_halo_kernel<GEMM_BF16X3><<<L.grid, kTcThreads, L.smem_bytes, stream>>>(
+        L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0, L.map_o1, L.map_r0, L.map_r1);
+  } else if (L.kind == GEMM_TF32X3) {
+    tc_conv_halo_kernel<GEMM_TF32X3><<<L.grid, kTcThreads, L.smem_bytes, stream>>>(
+        L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0, L.map_o1, L.map_r0, L.map_r1);
+  } else {
+    tc_conv_halo_kernel<GEMM_TF32><<<L.grid, kTcThreads, L.smem_bytes, stream>>>(
+        L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0, L.map_o1, L.map_r0, L.map_r1);
   }
   return cudaGetLastError();
 }
@@ -380,6 +548,41 @@ void tc_pack_weights_f32(int kind, const float* w, int O, int I, int KH, int KW,
           const float h = tf32_round_host(v);
           (*hi)[dst] = h;
           if (kind == GEMM_TF32X3 && lo != nullptr) (*lo)[dst] = v - h;
+        }
+}
+
+uint16_t bf16_round_host(float x) {
+  // round to nearest even onto 7 explicit mantissa bits; NaN stays NaN
+  uint32_t u;
+  std::memcpy(&u, &x, 4);
+  if ((u & 0x7f800000u) == 0x7f800000u) return static_cast<uint16_t>((u >> 16) | ((u & 0xffffu) ? 0x40u : 0u));
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return static_cast<uint16_t>(u >> 16);
+}
+
+float bf16_to_float_host(uint16_t h) {
+  const uint32_t u = static_cast<uint32_t>(h) << 16;
+  float r;
+  std::memcpy(&r, &u, 4);
+  return r;
+}
+
+void tc_pack_weights_bf16x2(const float* w, int O, int I, int KH, int KW, int k_elems,
+                            std::vector<uint16_t>* hi, std::vector<uint16_t>* mid) {
+  const int c_blocks = (I + k_elems - 1) / k_elems;
+  const size_t cpad = static_cast<size_t>(c_blocks) * k_elems;
+  const size_t k_total = static_cast<size_t>(KH) * KW * cpad;
+  hi->assign(static_cast<size_t>(O) * k_total, 0);
+  mid->assign(hi->size(), 0);
+  for (int o = 0; o < O; ++o)
+    for (int i = 0; i < I; ++i)
+      for (int kh = 0; kh < KH; ++kh)
+        for (int kw = 0; kw < KW; ++kw) {
+          const float v = w[((static_cast<size_t>(o) * I + i) * KH + kh) * KW + kw];
+          const size_t dst = o * k_total + (static_cast<size_t>(kh) * KW + kw) * cpad + i;
+          const uint16_t h = bf16_round_host(v);
+          (*hi)[dst] = h;
+          (*mid)[dst] = bf16_round_host(v - bf16_to_float_host(h));
         }
 }
 

@@ -19,6 +19,9 @@
 //   GEMM_TF32    one kind::tf32 MMA per K step (fast mode, ~1e-3 relative error)
 //   GEMM_TF32X3  operands are stored as hi/lo tf32 planes (x = hi + lo exactly);
 //                three MMAs lo*hi + hi*lo + hi*hi recover ~fp32 accuracy
+//   GEMM_BF16X3  operands are stored as two bf16 planes (x ~ hi + mid, 16 significant bits);
+//                three kind::f16 MMAs mid*hi + hi*mid + hi*hi, each at twice the tf32 rate
+//                on half the operand bytes, give ~1e-5 relative error
 //   GEMM_I8      kind::i8, int32 accumulation, exact
 #pragma once
 
@@ -30,13 +33,19 @@
 
 namespace nb {
 
-enum : int { GEMM_TF32 = 0, GEMM_TF32X3 = 1, GEMM_I8 = 2 };
+enum : int { GEMM_TF32 = 0, GEMM_TF32X3 = 1, GEMM_I8 = 2, GEMM_BF16X3 = 3 };
+
+__host__ __device__ constexpr int tc_planes(int kind) { return kind == GEMM_TF32X3 || kind == GEMM_BF16X3 ? 2 : 1; }
+__host__ __device__ constexpr int tc_elem_bytes(int kind) { return kind == GEMM_I8 ? 1 : (kind == GEMM_BF16X3 ? 2 : 4); }
 enum : int { ACT_NONE = 0, ACT_RELU = 1, ACT_LEAKY = 2, ACT_CLIP = 3 };
 // OUT_F32        plain fp32
 // OUT_F32_SPLIT  two fp32 planes: hi = value rounded to tf32, lo = value - hi
 // OUT_I8         int8 after requantisation with out_scale
 // OUT_F32_TF32   fp32 rounded to tf32 (fast mode keeps operands unbiased)
-enum : int { OUT_F32 = 0, OUT_F32_SPLIT = 1, OUT_I8 = 2, OUT_F32_TF32 = 3 };
+// OUT_BF16X2     two bf16 planes: hi = bf16(value), mid = bf16(value - hi)
+enum : int { OUT_F32 = 0, OUT_F32_SPLIT = 1, OUT_I8 = 2, OUT_F32_TF32 = 3, OUT_BF16X2 = 4 };
+// format of the optional residual operand of the epilogue
+enum : int { RES_NONE = 0, RES_F32 = 1, RES_SPLIT = 2, RES_BF16X2 = 3 };
 
 enum : int {
   TC_OK = 0,
@@ -60,8 +69,7 @@ struct TcGemmParams {
   int row_bytes;  // bytes per shared-memory operand row: 128 or 64
   int stages;
   int stage_bytes;  // bytes of one ring stage: planes * (A tile + B tile rounded to 1 KB)
-  // A addressing
-  int a_im2col;
+  int a_im2col;  // A addressing: 0 plain matrix (tiled TMA), 1 im2col TMA
   int OH, OW, KW;
   int stride_h, stride_w, pad_t, pad_l, dil_h, dil_w;
   // epilogue
@@ -72,6 +80,7 @@ struct TcGemmParams {
   int8_t* outq;
   const float* res0;  // optional residual (same layout as the output), plane hi
   const float* res1;  // optional residual plane lo
+  int res_mode;       // RES_*
   long long ldo;      // output row stride in elements
   int out_mode;
   int act;
@@ -96,6 +105,20 @@ __device__ __forceinline__ float round_tf32(float x) {
   uint32_t r;
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
   return __uint_as_float(r);
+}
+
+// two floats -> two bf16 (round to nearest even), `a` in the low half
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  return r;
+}
+__device__ __forceinline__ float bf16_low(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_high(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+// hi = bf16(x), mid = bf16(x - hi) for two values at once
+__device__ __forceinline__ void split_bf16x2(float a, float b, uint32_t& hi, uint32_t& mid) {
+  hi = pack_bf16x2(a, b);
+  mid = pack_bf16x2(__fadd_rn(a, -bf16_low(hi)), __fadd_rn(b, -bf16_high(hi)));
 }
 
 __device__ __forceinline__ float apply_act(float y, int act, float a, float b) {
@@ -128,7 +151,28 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcGemmParams& p, const u
   }
   const long long row = m * p.ldo;
   const bool vec4 = (p.ldo % 4 == 0) && (n_first % 4 == 0);
-  if (p.res0 != nullptr) {
+  if (p.res_mode == RES_BF16X2) {
+    const uint16_t* r0 = reinterpret_cast<const uint16_t*>(p.res0);
+    const uint16_t* r1 = reinterpret_cast<const uint16_t*>(p.res1);
+    if ((p.ldo % 8 == 0) && n_first + 15 < p.N) {
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4*>(r0 + row + n_first + 8 * g));
+        const uint4 b = __ldg(reinterpret_cast<const uint4*>(r1 + row + n_first + 8 * g));
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          y[8 * g + 2 * e] = __fadd_rn(y[8 * g + 2 * e], __fadd_rn(bf16_low(aw[e]), bf16_low(bw[e])));
+          y[8 * g + 2 * e + 1] = __fadd_rn(y[8 * g + 2 * e + 1], __fadd_rn(bf16_high(aw[e]), bf16_high(bw[e])));
+        }
+      }
+    } else {
+      for (int j = 0; j < 16; ++j)
+        if (n_first + j < p.N)
+          y[j] = __fadd_rn(y[j], __fadd_rn(__uint_as_float(static_cast<uint32_t>(r0[row + n_first + j]) << 16),
+                                           __uint_as_float(static_cast<uint32_t>(r1[row + n_first + j]) << 16)));
+    }
+  } else if (p.res0 != nullptr) {
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
       const int n = n_first + 4 * g;
@@ -182,6 +226,30 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcGemmParams& p, const u
   }
 #pragma unroll
   for (int j = 0; j < 16; ++j) y[j] = apply_act(y[j], p.act, p.act_a, p.act_b);
+  if (p.out_mode == OUT_BF16X2) {
+    uint16_t* o0 = reinterpret_cast<uint16_t*>(p.out0);
+    uint16_t* o1 = reinterpret_cast<uint16_t*>(p.out1);
+    uint32_t hi[8], mid[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) split_bf16x2(y[2 * e], y[2 * e + 1], hi[e], mid[e]);
+    if ((p.ldo % 8 == 0) && n_first + 15 < p.N) {
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        *reinterpret_cast<uint4*>(o0 + row + n_first + 8 * g) =
+            make_uint4(hi[4 * g], hi[4 * g + 1], hi[4 * g + 2], hi[4 * g + 3]);
+        *reinterpret_cast<uint4*>(o1 + row + n_first + 8 * g) =
+            make_uint4(mid[4 * g], mid[4 * g + 1], mid[4 * g + 2], mid[4 * g + 3]);
+      }
+    } else {
+      for (int j = 0; j < 16; ++j) {
+        if (n_first + j < p.N) {
+          o0[row + n_first + j] = static_cast<uint16_t>(j & 1 ? hi[j >> 1] >> 16 : hi[j >> 1] & 0xffffu);
+          o1[row + n_first + j] = static_cast<uint16_t>(j & 1 ? mid[j >> 1] >> 16 : mid[j >> 1] & 0xffffu);
+        }
+      }
+    }
+    return;
+  }
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
     const int n = n_first + 4 * g;
@@ -250,6 +318,191 @@ __device__ __forceinline__ uint32_t stage_chunk_offset(int row, int j) {
   return static_cast<uint32_t>(row * 64 + ((j ^ ((row >> 1) & 3)) << 4));
 }
 
+// ---- staged epilogue shared by the contraction kernels --------------------------------
+// Results leave through shared-memory staging tiles and TMA stores.  Shared-memory plan:
+// 16 KB of residual tiles at res_stage, then out_bufs output tiles at out_stage.  A chunk is
+// 16 accumulator columns, or 32 ("wide") as soon as a bf16-pair tensor takes part, because a
+// staging row is 64 bytes: 16 fp32 or 32 bf16.  Tiles per chunk:
+//   out  F32            one tile  [128][16 fp32]           (wide: two, columns +0 and +16)
+//   out  F32_SPLIT      hi tile, lo tile                   (never wide)
+//   out  BF16X2         hi tile, mid tile [128][32 bf16]   (always wide)
+//   res  F32 / SPLIT / BF16X2 likewise in the residual area
+// One barrier per chunk: all four warps write tile c, barrier, the leader stores it, waits
+// until the tile that chunk c+2 will use has been read out, and fetches the residual of
+// chunk c+1; the others learn all that at the barrier of chunk c+1.
+struct TcStageCfg {
+  uint32_t res_stage, out_stage, res_bar;
+  int out_bufs, out_mode, res_mode;
+  int act;
+  float act_a, act_b;
+  int N, block_n;
+};
+
+// IO: load_res(plane, smem_dst, bar, column) and store_out(plane, smem_src, column) issue the
+// TMA copies of one staging tile; the caller binds tensor maps and row coordinates.
+template <int KIND, class IO>
+__device__ __forceinline__ bool tc_staged_epilogue(const TcStageCfg c, const IO& io, uint32_t t_row, int n0,
+                                                   int row, bool leader, const float* tile_bias,
+                                                   const float* tile_scale, uint32_t& res_ph, int& out_slot,
+                                                   volatile int* abort_ptr) {
+  using namespace ptx;
+  const bool has_res = c.res_mode != RES_NONE;
+  const bool wide = c.out_mode == OUT_BF16X2 || c.res_mode == RES_BF16X2;
+  const int cw = wide ? 32 : 16;
+  const bool two_out = wide || c.out_mode == OUT_F32_SPLIT;
+  const uint32_t out_tile_bytes = two_out ? 16384u : 8192u;
+  const bool two_res = wide || c.res_mode == RES_SPLIT;
+  auto fetch_res = [&](int col) {
+    mbar_arrive_expect_tx(c.res_bar, two_res ? 16384u : 8192u);
+    io.load_res(0, c.res_stage, c.res_bar, col);
+    if (c.res_mode == RES_F32) {
+      if (wide) io.load_res(0, c.res_stage + 8192u, c.res_bar, col + 16);
+    } else {
+      io.load_res(1, c.res_stage + 8192u, c.res_bar, col);
+    }
+  };
+  if (leader && has_res) fetch_res(n0);
+  named_barrier_sync(1, 128);  // tile constants are in place
+  bool ok = true;
+  for (int c0 = 0; c0 < c.block_n && n0 + c0 < c.N; c0 += cw) {
+    const uint32_t stage0 = c.out_stage + static_cast<uint32_t>(out_slot) * out_tile_bytes;
+    if (has_res) {
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(c.res_bar, res_ph, abort_ptr, kTcWaitLimitNs) ? 1 : 0) != 0;
+      res_ph ^= 1u;
+      if (!ok) break;
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (h == 1 && !wide) break;
+      uint32_t v[16];
+      tmem_ld16(t_row + static_cast<uint32_t>(c0 + 16 * h), v);
+      tmem_ld_wait();
+      float r[16];
+      if (c.res_mode == RES_BF16X2) {
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
+          const uint32_t off = stage_chunk_offset(row, 2 * h + jj);
+          uint32_t a[4], b[4];
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(a[0]), "=r"(a[1]), "=r"(a[2]), "=r"(a[3])
+                       : "r"(c.res_stage + off));
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3])
+                       : "r"(c.res_stage + 8192u + off));
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            r[8 * jj + 2 * e] = __fadd_rn(bf16_low(a[e]), bf16_low(b[e]));
+            r[8 * jj + 2 * e + 1] = __fadd_rn(bf16_high(a[e]), bf16_high(b[e]));
+          }
+        }
+      } else if (has_res) {
+        const uint32_t base = c.res_stage + (wide ? 8192u * h : 0u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t off = stage_chunk_offset(row, j);
+          float4 a;
+          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                       : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w)
+                       : "r"(base + off));
+          if (c.res_mode == RES_SPLIT) {
+            float4 b;
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                         : "=f"(b.x), "=f"(b.y), "=f"(b.z), "=f"(b.w)
+                         : "r"(base + 8192u + off));
+            a.x = __fadd_rn(a.x, b.x);
+            a.y = __fadd_rn(a.y, b.y);
+            a.z = __fadd_rn(a.z, b.z);
+            a.w = __fadd_rn(a.w, b.w);
+          }
+          r[4 * j + 0] = a.x;
+          r[4 * j + 1] = a.y;
+          r[4 * j + 2] = a.z;
+          r[4 * j + 3] = a.w;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) r[j] = 0.0f;
+      }
+      float y[16], cb[16], cs[16];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float4 b4 = *reinterpret_cast<const float4*>(&tile_bias[c0 + 16 * h + 4 * j]);
+        cb[4 * j + 0] = b4.x;
+        cb[4 * j + 1] = b4.y;
+        cb[4 * j + 2] = b4.z;
+        cb[4 * j + 3] = b4.w;
+        if (KIND == GEMM_I8) {
+          const float4 s4 = *reinterpret_cast<const float4*>(&tile_scale[c0 + 16 * h + 4 * j]);
+          cs[4 * j + 0] = s4.x;
+          cs[4 * j + 1] = s4.y;
+          cs[4 * j + 2] = s4.z;
+          cs[4 * j + 3] = s4.w;
+        } else {
+          cs[4 * j + 0] = cs[4 * j + 1] = cs[4 * j + 2] = cs[4 * j + 3] = 0.0f;
+        }
+      }
+      tc_epilogue_values<KIND>(v, cb, cs, r, c.act, c.act_a, c.act_b, y);
+      if (c.out_mode == OUT_BF16X2) {
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
+          uint32_t hi[4], mid[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) split_bf16x2(y[8 * jj + 2 * e], y[8 * jj + 2 * e + 1], hi[e], mid[e]);
+          const uint32_t off = stage_chunk_offset(row, 2 * h + jj);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage0 + off), "r"(hi[0]), "r"(hi[1]),
+                       "r"(hi[2]), "r"(hi[3])
+                       : "memory");
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage0 + 8192u + off), "r"(mid[0]),
+                       "r"(mid[1]), "r"(mid[2]), "r"(mid[3])
+                       : "memory");
+        }
+      } else if (c.out_mode == OUT_F32) {
+        const uint32_t base = stage0 + (wide ? 8192u * h : 0u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(base + stage_chunk_offset(row, j)),
+                       "f"(y[4 * j]), "f"(y[4 * j + 1]), "f"(y[4 * j + 2]), "f"(y[4 * j + 3])
+                       : "memory");
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float hi[4], lo[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            hi[e] = round_tf32(y[4 * j + e]);
+            lo[e] = __fadd_rn(y[4 * j + e], -hi[e]);
+          }
+          const uint32_t off = stage_chunk_offset(row, j);
+          asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stage0 + off), "f"(hi[0]), "f"(hi[1]),
+                       "f"(hi[2]), "f"(hi[3])
+                       : "memory");
+          if (c.out_mode == OUT_F32_SPLIT)
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stage0 + 8192u + off), "f"(lo[0]),
+                         "f"(lo[1]), "f"(lo[2]), "f"(lo[3])
+                         : "memory");
+        }
+      }
+    }
+    fence_proxy_async_smem();
+    named_barrier_sync(2, 128);
+    if (leader) {
+      // rows and columns of a tile that fall outside the tensor are clipped by the store
+      io.store_out(0, stage0, n0 + c0);
+      if (c.out_mode == OUT_F32) {
+        if (wide && n0 + c0 + 16 < c.N) io.store_out(0, stage0 + 8192u, n0 + c0 + 16);
+      } else if (two_out) {
+        io.store_out(1, stage0 + 8192u, n0 + c0);
+      }
+      tma_store_commit();
+      tma_store_wait_read(c.out_bufs - 2);
+      const int c1 = c0 + cw;
+      if (has_res && c1 < c.block_n && n0 + c1 < c.N) fetch_res(n0 + c1);
+    }
+    if (++out_slot == c.out_bufs) out_slot = 0;
+  }
+  return ok;
+}
+
 template <int KIND>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ CUtensorMap map_a0,
@@ -261,7 +514,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
                const __grid_constant__ CUtensorMap map_r0,
                const __grid_constant__ CUtensorMap map_r1) {
   using namespace ptx;
-  constexpr int PLANES = KIND == GEMM_TF32X3 ? 2 : 1;
+  constexpr int PLANES = tc_planes(KIND);
 
   extern __shared__ uint8_t tc_smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kTcMaxStages];
@@ -395,9 +648,11 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
     if (lane == 0) {
+      // formats: kind::i8 s32 <- s8 (2, 1); kind::tf32 f32 <- tf32 (1, 2); kind::f16 f32 <- bf16 (1, 1)
       const uint32_t idesc = KIND == GEMM_I8
                                  ? instr_desc(2u, 1u, kTcBlockM, static_cast<uint32_t>(p.block_n))
-                                 : instr_desc(1u, 2u, kTcBlockM, static_cast<uint32_t>(p.block_n));
+                                 : instr_desc(1u, KIND == GEMM_BF16X3 ? 1u : 2u, kTcBlockM,
+                                              static_cast<uint32_t>(p.block_n));
       // One thread issues every MMA, so its instruction stream is the critical path:
       // descriptors are formed by adding small constants to values computed once.
       // (the start-address field counts 16-byte units; a K step is 32 bytes = 2 units)
@@ -445,6 +700,10 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
               mma_tf32(d_tmem, ka + slot_units, kbd, idesc, accumulate);  // lo * hi
               mma_tf32(d_tmem, ka, kbd + b_slot_units, idesc, 1u);        // hi * lo
               mma_tf32(d_tmem, ka, kbd, idesc, 1u);                       // hi * hi
+            } else if (KIND == GEMM_BF16X3) {
+              mma_f16(d_tmem, ka + slot_units, kbd, idesc, accumulate);  // mid * hi
+              mma_f16(d_tmem, ka, kbd + b_slot_units, idesc, 1u);        // hi * mid
+              mma_f16(d_tmem, ka, kbd, idesc, 1u);                       // hi * hi
             } else {
               mma_i8(d_tmem, ka, kbd, idesc, accumulate);
             }
@@ -480,7 +739,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
     const TcGemmParams lp = p;
     const int e_act = p.act;
     const float e_act_a = p.act_a, e_act_b = p.act_b;
-    const bool e_has_bias = p.bias != nullptr, e_has_res = p.res0 != nullptr, e_res_split = p.res1 != nullptr;
+    const int e_res_mode = p.res_mode;
     const int e_out_mode = p.out_mode, e_N = p.N, e_block_n = p.block_n, e_out_bufs = p.out_bufs;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       const int m_blk = tile / p.tiles_n;
@@ -507,118 +766,32 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
         tile_scale[t] = (KIND == GEMM_I8 && n < p.N) ? __ldg(p.scale + n) : 0.0f;
       }
       if (p.tma_store) {
-        // Staging area behind the ring: residual hi, residual lo (8 KB each), then a ring of
-        // e_out_bufs >= 2 output tiles (hi [+ lo], 8 KB per plane).  One barrier per chunk:
-        // everybody writes tile c, barrier, the leader stores it, waits until the tile
-        // that chunk c+2 will use has been read out, and fetches the residual of chunk c+1;
-        // the others learn all that at the barrier of chunk c+1.
-        const uint32_t res_stage = smem_base + static_cast<uint32_t>(S) * stage_bytes;
-        const uint32_t out_stage = res_stage + 16384u;
-        const int row = quarter * 32 + lane;
-        const bool leader = threadIdx.x == 64;
-        const bool split = e_out_mode == OUT_F32_SPLIT;
-        const uint32_t out_tile_bytes = split ? 16384u : 8192u;
+        // staging area behind the ring: residual tiles (16 KB), then the output tiles
+        TcStageCfg cfg;
+        cfg.res_stage = smem_base + static_cast<uint32_t>(S) * stage_bytes;
+        cfg.out_stage = cfg.res_stage + 16384u;
+        cfg.res_bar = smem_u32(&res_bar);
+        cfg.out_bufs = e_out_bufs;
+        cfg.out_mode = e_out_mode;
+        cfg.res_mode = e_res_mode;
+        cfg.act = e_act;
+        cfg.act_a = e_act_a;
+        cfg.act_b = e_act_b;
+        cfg.N = e_N;
+        cfg.block_n = e_block_n;
         const int m_first = m_blk * kTcBlockM;
-        const uint32_t rb = smem_u32(&res_bar);
-        if (leader && e_has_res) {
-          mbar_arrive_expect_tx(rb, (e_res_split ? 2u : 1u) * 8192u);
-          tma_load_2d(res_stage, &map_r0, rb, n0, m_first);
-          if (e_res_split) tma_load_2d(res_stage + 8192u, &map_r1, rb, n0, m_first);
-        }
-        named_barrier_sync(1, 128);  // tile constants are in place
-        for (int c0 = 0; c0 < e_block_n && n0 + c0 < e_N; c0 += 16) {
-          const uint32_t stage0 = out_stage + static_cast<uint32_t>(out_slot) * out_tile_bytes;
-          uint32_t v[16];
-          tmem_ld16(t_row + static_cast<uint32_t>(c0), v);
-          tmem_ld_wait();
-          float r[16];
-          if (e_has_res) {
-            ok = __all_sync(0xffffffffu, mbar_wait_bounded(rb, res_ph, abort_ptr, kTcWaitLimitNs) ? 1 : 0) != 0;
-            res_ph ^= 1u;
-            if (!ok) break;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint32_t off = stage_chunk_offset(row, j);
-              float4 a;
-              asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                           : "=f"(a.x), "=f"(a.y), "=f"(a.z), "=f"(a.w)
-                           : "r"(res_stage + off));
-              if (e_res_split) {
-                float4 b;
-                asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                             : "=f"(b.x), "=f"(b.y), "=f"(b.z), "=f"(b.w)
-                             : "r"(res_stage + 8192u + off));
-                a.x = __fadd_rn(a.x, b.x);
-                a.y = __fadd_rn(a.y, b.y);
-                a.z = __fadd_rn(a.z, b.z);
-                a.w = __fadd_rn(a.w, b.w);
-              }
-              r[4 * j + 0] = a.x;
-              r[4 * j + 1] = a.y;
-              r[4 * j + 2] = a.z;
-              r[4 * j + 3] = a.w;
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 16; ++j) r[j] = 0.0f;
+        struct {
+          const CUtensorMap *o0, *o1, *r0, *r1;
+          int m_first;
+          __device__ __forceinline__ void load_res(int plane, uint32_t dst, uint32_t bar, int col) const {
+            ptx::tma_load_2d(dst, plane ? r1 : r0, bar, col, m_first);
           }
-          float y[16];
-          float cb[16], cs[16];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float4 b4 = *reinterpret_cast<const float4*>(&tile_bias[c0 + 4 * j]);
-            cb[4 * j + 0] = b4.x;
-            cb[4 * j + 1] = b4.y;
-            cb[4 * j + 2] = b4.z;
-            cb[4 * j + 3] = b4.w;
-            const float4 s4 = *reinterpret_cast<const float4*>(&tile_scale[c0 + 4 * j]);
-            cs[4 * j + 0] = s4.x;
-            cs[4 * j + 1] = s4.y;
-            cs[4 * j + 2] = s4.z;
-            cs[4 * j + 3] = s4.w;
+          __device__ __forceinline__ void store_out(int plane, uint32_t src, int col) const {
+            ptx::tma_store_2d(plane ? o1 : o0, src, col, m_first);
           }
-          tc_epilogue_values<KIND>(v, cb, cs, r, e_act, e_act_a, e_act_b, y);
-          if (e_out_mode == OUT_F32) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stage0 + stage_chunk_offset(row, j)),
-                           "f"(y[4 * j]), "f"(y[4 * j + 1]), "f"(y[4 * j + 2]), "f"(y[4 * j + 3])
-                           : "memory");
-          } else {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              float hi[4], lo[4];
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                hi[e] = round_tf32(y[4 * j + e]);
-                lo[e] = __fadd_rn(y[4 * j + e], -hi[e]);
-              }
-              const uint32_t off = stage_chunk_offset(row, j);
-              asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stage0 + off), "f"(hi[0]),
-                           "f"(hi[1]), "f"(hi[2]), "f"(hi[3])
-                           : "memory");
-              if (split)
-                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stage0 + 8192u + off),
-                             "f"(lo[0]), "f"(lo[1]), "f"(lo[2]), "f"(lo[3])
-                             : "memory");
-            }
-          }
-          fence_proxy_async_smem();
-          named_barrier_sync(2, 128);
-          if (leader) {
-            tma_store_2d(&map_o0, stage0, n0 + c0, m_first);
-            if (split) tma_store_2d(&map_o1, stage0 + 8192u, n0 + c0, m_first);
-            tma_store_commit();
-            tma_store_wait_read(e_out_bufs - 2);
-            const int c1 = c0 + 16;
-            if (e_has_res && c1 < e_block_n && n0 + c1 < e_N) {
-              mbar_arrive_expect_tx(rb, (e_res_split ? 2u : 1u) * 8192u);
-              tma_load_2d(res_stage, &map_r0, rb, n0 + c1, m_first);
-              if (e_res_split) tma_load_2d(res_stage + 8192u, &map_r1, rb, n0 + c1, m_first);
-            }
-          }
-          if (++out_slot == e_out_bufs) out_slot = 0;
-        }
+        } io{&map_o0, &map_o1, &map_r0, &map_r1, m_first};
+        ok = tc_staged_epilogue<KIND>(cfg, io, t_row, n0, quarter * 32 + lane, threadIdx.x == 64, tile_bias,
+                                      tile_scale, res_ph, out_slot, abort_ptr);
         if (!ok) break;
       } else {
         named_barrier_sync(3, 128);

@@ -9,6 +9,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include "tc_conv_halo.cuh"
 #include "tc_gemm.cuh"
 
 namespace nb {
@@ -51,6 +52,7 @@ struct TcEpilogue {
   int8_t* outq = nullptr;
   const float* res0 = nullptr;
   const float* res1 = nullptr;
+  bool res_bf16 = false;  // the residual planes hold bf16 pairs (hi, mid)
   long long ldo = 0;
   int out_mode = OUT_F32;
   int act = ACT_NONE;
@@ -88,6 +90,46 @@ void tc_pack_weights_f32(int kind, const float* w, int O, int I, int KH, int KW,
 void tc_pack_weights_i8(const int8_t* w, int O, int I, int KH, int KW, int k_elems,
                         std::vector<int8_t>* packed);
 
+// GEMM_BF16X3: two bf16 planes, hi = bf16(w) and mid = bf16(w - hi), same layout.
+void tc_pack_weights_bf16x2(const float* w, int O, int I, int KH, int KW, int k_elems,
+                            std::vector<uint16_t>* hi, std::vector<uint16_t>* mid);
+
 float tf32_round_host(float x);
+uint16_t bf16_round_host(float x);
+float bf16_to_float_host(uint16_t h);
+
+// ---- stride-1 convolution with the input patch resident in shared memory (tc_conv_halo.cuh)
+struct TcHaloLaunch {
+  TcHaloParams p{};
+  alignas(64) CUtensorMap map_a0{};
+  alignas(64) CUtensorMap map_a1{};
+  alignas(64) CUtensorMap map_b0{};
+  alignas(64) CUtensorMap map_b1{};
+  alignas(64) CUtensorMap map_o0{};
+  alignas(64) CUtensorMap map_o1{};
+  alignas(64) CUtensorMap map_r0{};
+  alignas(64) CUtensorMap map_r1{};
+  int kind = GEMM_TF32;
+  int grid = 0;
+  int smem_bytes = 0;
+};
+
+struct TcHaloConv {
+  const void* in0 = nullptr;  // NHWC activation planes
+  const void* in1 = nullptr;
+  int images = 0, H = 0, W = 0, C = 0;
+  int KH = 1, KW = 1, pad_t = 0, pad_l = 0, OH = 0, OW = 0;
+  const void* w0 = nullptr;  // packed like tc_plan_conv's weights
+  const void* w1 = nullptr;
+  int out_channels = 0;
+};
+
+// True when the patch-resident kernel applies and is expected to win: fp32 kind, stride and
+// dilation 1, channels in blocks of 32, output rows of 16 bytes, tiles mostly inside the image.
+bool tc_halo_applies(int kind, int C, int KH, int KW, int stride_h, int stride_w, int dil_h, int dil_w, int OH,
+                     int OW, int out_channels, int out_mode);
+std::string tc_plan_conv_halo(TcHaloLaunch* launch, int kind, const TcHaloConv& conv, const TcEpilogue& epilogue,
+                              int sm_count);
+cudaError_t tc_launch_halo(const TcHaloLaunch& launch, cudaStream_t stream);
 
 }  // namespace nb

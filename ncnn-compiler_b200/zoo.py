@@ -144,6 +144,22 @@ def single_conv(prefix, seed=100, h=56, w=56, cin=64, cout=64, k=3, stride=1, pa
     return net.w.save(prefix)
 
 
+def residual_block(prefix, seed=600, h=16, w=16, c=64, cout=96, k=3):
+    """Input -> [k x k conv + ReLU -> k x k conv] + identity -> ReLU -> 1x1 conv to `cout` channels.
+    With c a multiple of 64 every tensor-core operand is a bf16 pair: the first convolution writes
+    one, the second adds a bf16-pair residual and writes one, the last writes plain fp32."""
+    net = _Net(seed)
+    wr = net.w
+    wr.layer("Input", "input", [], ["data"], f"0={w} 1={h} 2={c}")
+    wr.layer("Split", "split", ["data"], ["a", "b"])
+    net.conv("conv1", "a", "c1", c, c, k, 1, k // 2, act=1, zero_bias=False)
+    net.conv("conv2", "c1", "c2", c, c, k, 1, k // 2, act=0, zero_bias=False)
+    wr.layer("Eltwise", "add", ["c2", "b"], ["sum"], "0=1")
+    wr.layer("ReLU", "relu", ["sum"], ["act"], "0=0.0")
+    net.conv("conv3", "act", "output", c, cout, 1, 1, 0, act=0, zero_bias=False)
+    return wr.save(prefix)
+
+
 def resnet18(prefix, seed=200, int8=False, size=224, classes=1000):
     """Configs 1 and 3: ResNet-18 topology, BatchNorm folded (zero bias), He-normal weights."""
     net = _Net(seed if not int8 else seed + 200, int8=int8)

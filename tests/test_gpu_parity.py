@@ -325,3 +325,24 @@ def test_depthwise_3x3_tile_kernel(pkg, oracle, tmp_path, c, h, w, stride, pad):
     for mode in (0, 2):
         got, want = run_both(pkg, oracle, prefix + ".param", prefix + ".bin", x, mode)
         assert rel_l2(got, want) <= 2e-6
+
+
+@pytest.mark.parametrize("halo", ["0", "1"])
+@pytest.mark.parametrize("c,h,w,k,cout", [(64, 16, 16, 3, 96), (64, 30, 15, 3, 64), (128, 17, 9, 3, 256),
+                                          (64, 16, 24, 5, 32), (32, 16, 16, 3, 48), (192, 14, 14, 3, 100)])
+def test_residual_block_operand_formats(pkg, oracle, tmp_path, monkeypatch, halo, c, h, w, k, cout):
+    """A residual block whose tensor-core operands are bf16 pairs (channels a multiple of 64) or
+    fp32 hi/lo planes (otherwise), through the im2col kernel (halo=0) and the patch-resident
+    kernel where it applies (halo=1): fused bias, residual and ReLU in every output format."""
+    monkeypatch.setenv("NCNN_B200_HALO", halo)
+    param, bin_ = pkg.zoo.residual_block(str(tmp_path / "rb"), seed=600 + c + h, h=h, w=w, c=c, cout=cout, k=k)
+    x = np.random.default_rng(c + w).uniform(-1, 1, (5, c, h, w)).astype(np.float32)
+    got, want = run_both(pkg, oracle, param, bin_, x, 0)
+    assert rel_l2(got, want) <= TOL[0]
+    m = pkg.Model(param, bin_)
+    kernels = {row["kernel"] for row in m.profile(5, repeat=1)}
+    m.close()
+    kind = "bf16x3" if c % 64 == 0 else "tf32x3"
+    assert f"tc_gemm_kernel<{kind}>" in kernels  # the 1x1 convolution at least
+    halo_expected = halo == "1" and (h * w) / (-(-h // 16) * 16 * -(-w // 8) * 8) >= 0.70
+    assert (f"tc_conv_halo_kernel<{kind}>" in kernels) == halo_expected, kernels
