@@ -54,6 +54,7 @@ struct Node {
   int res = -1;
   int impl = IMPL_NONE;
   bool stem = false;
+  bool stem_bf16 = false;  // stem whose window view holds bf16 pairs (64-byte rows)
   // host-side parameters
   std::vector<float> w_f32;   // [O][I][KH][KW] (conv), [O][K] (ip/gemm), [C][KH][KW] (dw)
   std::vector<int8_t> w_i8;
@@ -204,6 +205,8 @@ class EngineImpl {
   void plan_memory();
   ActRef ref(int tensor, int64_t n) const;
   bool emit_node(Plan& plan, const Node& node, int64_t n, std::string* err);
+  void restore_padding(int64_t n, cudaStream_t st);
+  int64_t last_run_n_ = 0;  // batch size of the previous run (0: none yet)
   void make_edge_steps(int64_t n, const std::vector<const float*>& d_in, const std::vector<float*>& d_out,
                        std::vector<Step>* pre, std::vector<Step>* post);
 };
@@ -981,6 +984,9 @@ bool EngineImpl::choose_impl(std::string* err) {
               (n.sw * cp * (i8 ? 1 : 4)) % 16 == 0) {
             n.impl = IMPL_TC;
             n.stem = true;
+            // bf16 pairs halve the window to 64-byte rows and the MMA count with it; the pixel
+            // stride of the view must stay a multiple of 16 bytes
+            n.stem_bf16 = !i8 && opt_.accuracy_mode == kAccuracyFp32Split && (n.sw * cp * 2) % 16 == 0;
           }
         }
       }
@@ -1046,7 +1052,7 @@ bool EngineImpl::prepare_weights(std::string* err) {
     if (!(contraction && n.impl == IMPL_TC && n.term == 0)) continue;
     const int src = resolve(n.in[0]);
     feeds_tc[src] = 1;
-    const bool can = n.kind == N_CONV ? (!n.stem && tensors_[src].c % 64 == 0) : (n.K % 8 == 0);
+    const bool can = n.kind == N_CONV ? (n.stem ? n.stem_bf16 : tensors_[src].c % 32 == 0) : (n.K % 8 == 0);
     if (!can) bf16_ok[src] = 0;
   }
   for (size_t i = 0; i < tensors_.size(); ++i) {
@@ -1109,9 +1115,16 @@ bool EngineImpl::prepare_weights(std::string* err) {
                   for (int kw = 0; kw < n.KW; ++kw)
                     v[(static_cast<size_t>(o) * window + kw * cp + c) * n.KH + kh] =
                         n.w_f32[((static_cast<size_t>(o) * C + c) * n.KH + kh) * n.KW + kw];
-            tc_pack_weights_f32(kind, v.data(), n.O, window, n.KH, 1, window, &hi, &lo);
-            n.d_w0 = upload(hi);
-            if (kind == GEMM_TF32X3) n.d_w1 = upload(lo);
+            if (kind == GEMM_BF16X3) {
+              std::vector<uint16_t> bh, bm;
+              tc_pack_weights_bf16x2(v.data(), n.O, window, n.KH, 1, window, &bh, &bm);
+              n.d_w0 = upload(bh);
+              n.d_w1 = upload(bm);
+            } else {
+              tc_pack_weights_f32(kind, v.data(), n.O, window, n.KH, 1, window, &hi, &lo);
+              n.d_w0 = upload(hi);
+              if (kind == GEMM_TF32X3) n.d_w1 = upload(lo);
+            }
           }
         } else {
           n.k_elems = tc_k_elems(kind, C);
@@ -1772,6 +1785,20 @@ Plan* EngineImpl::plan_for(int64_t n) {
   return &res.first->second;
 }
 
+// Plans of different batch sizes lay the same arena out differently.  The zero padding
+// around a stem input is written once per plan, so after a run of another size it has to
+// be restored before this plan reads it.
+void EngineImpl::restore_padding(int64_t n, cudaStream_t st) {
+  if (last_run_n_ == n) return;
+  if (last_run_n_ != 0) {
+    for (const Tensor& t : tensors_) {
+      if (!t.dedicated || t.alias >= 0) continue;
+      cudaMemsetAsync(arena_ + t.offset * static_cast<size_t>(n), 0, t.plane_bytes * t.planes() * static_cast<size_t>(n), st);
+    }
+  }
+  last_run_n_ = n;
+}
+
 int EngineImpl::run(int64_t n, const float* const* in, float* const* out, bool host, cudaStream_t user_stream) {
   if (opt_.plan_only) {
     error_ = "the model was loaded in plan-only mode and cannot run";
@@ -1814,6 +1841,8 @@ int EngineImpl::run(int64_t n, const float* const* in, float* const* out, bool h
     for (size_t i = 0; i < inputs_.size(); ++i) d_in[i] = in[i];
     for (size_t i = 0; i < outputs_.size(); ++i) d_out[i] = out[i];
   }
+
+  restore_padding(n, st);
 
   std::vector<Step> pre, post;
   make_edge_steps(n, d_in, d_out, &pre, &post);
@@ -1888,6 +1917,7 @@ int EngineImpl::run(int64_t n, const float* const* in, float* const* out, bool h
 int EngineImpl::profile(int64_t n, int repeat, std::vector<LayerTiming>* out) {
   Plan* plan = plan_for(n);
   if (plan == nullptr) return 6;
+  restore_padding(n, stream_);
   out->clear();
   // every launch of one run: input edges, layers, output edges (edges need the staging
   // buffers a previous host-pointer run of this batch size created)

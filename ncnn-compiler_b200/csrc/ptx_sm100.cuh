@@ -76,14 +76,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
                                                   volatile int* abort_flag,
                                                   uint64_t limit_ns) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
+  // The clock is read only every 1024 polls, never before the first 1024: reading it costs
+  // hundreds of cycles, and a waiter that is about to be released must not sit in that read.
+  uint64_t t0 = 0;
   uint32_t polls = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++polls & 0x3ffu) == 0) {
       if (*abort_flag != 0) return false;
-      if (global_timer_ns() - t0 > limit_ns) return false;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > limit_ns) return false;
     }
   }
 }

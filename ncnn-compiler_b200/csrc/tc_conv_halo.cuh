@@ -23,6 +23,7 @@ namespace nb {
 
 constexpr int kHaloTileH = 16;
 constexpr int kHaloTileW = 8;
+constexpr int kHaloThreads = 192;  // warps: 0 producer, 1 MMA issuer, 2-5 epilogue
 
 struct TcHaloParams {
   int images, OH, OW, N;
@@ -43,7 +44,7 @@ struct TcHaloParams {
 };
 
 template <int KIND>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(kHaloThreads, 1)
 tc_conv_halo_kernel(const __grid_constant__ TcHaloParams p, const __grid_constant__ CUtensorMap map_a0,
                     const __grid_constant__ CUtensorMap map_a1,
                     const __grid_constant__ CUtensorMap map_b0,
@@ -125,54 +126,66 @@ tc_conv_halo_kernel(const __grid_constant__ TcHaloParams p, const __grid_constan
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer
-    if (lane == 0) {
-      const uint32_t a_tx = PLANES * static_cast<uint32_t>(p.patch_h * p.patch_w) * 128u;
-      const uint32_t b_tx = PLANES * static_cast<uint32_t>(p.block_n) * 128u;
-      int s = 0, ab = 0;
-      uint32_t ph = 0, a_ph = 0;
-      long long a_issued = 0, b_issued = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        int img, oy0, ox0, n0;
-        decode(tile, &img, &oy0, &ox0, &n0);
-        for (int cb = 0; cb < p.c_blocks && ok; ++cb) {
-          if (!mbar_wait_bounded(smem_u32(&a_empty[ab]), a_ph ^ 1u, abort_ptr, kTcWaitLimitNs)) {
+    // one lane per TMA copy (issuing is what costs): lanes 0/1 the weight planes of a tap,
+    // lanes 2/3 the patch planes of a channel block; lane 0 owns the barrier traffic
+    const bool b_issuer = lane < PLANES;
+    const bool a_issuer = lane >= 2 && lane < 2 + PLANES;
+    const int plane = lane & 1;
+    const uint32_t a_tx = PLANES * static_cast<uint32_t>(p.patch_h * p.patch_w) * 128u;
+    const uint32_t b_tx = PLANES * static_cast<uint32_t>(p.block_n) * 128u;
+    int s = 0, ab = 0;
+    uint32_t ph = 0, a_ph = 0;
+    long long a_issued = 0, b_issued = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      int img, oy0, ox0, n0;
+      decode(tile, &img, &oy0, &ox0, &n0);
+      for (int cb = 0; cb < p.c_blocks && ok; ++cb) {
+        const uint32_t ab_bar = smem_u32(&a_full[ab]);
+        int w = 1;
+        if (lane == 0) {
+          w = mbar_wait_bounded(smem_u32(&a_empty[ab]), a_ph ^ 1u, abort_ptr, kTcWaitLimitNs) ? 1 : 0;
+          if (w) mbar_arrive_expect_tx(ab_bar, a_tx);
+        }
+        w = __shfl_sync(0xffffffffu, w, 0);
+        if (!w) {
+          ok = false;
+          break;
+        }
+        if (a_issuer)
+          tma_load_4d(smem_base + static_cast<uint32_t>(ab) * a_buf_bytes + plane * patch_bytes,
+                      plane ? &map_a1 : &map_a0, ab_bar, cb * p.k_elems, ox0 - p.pad_l, oy0 - p.pad_t, img);
+        ++a_issued;
+        ab ^= 1;
+        if (ab == 0) a_ph ^= 1u;
+        for (int tap = 0; tap < p.taps; ++tap) {
+          const uint32_t fb = smem_u32(&b_full[s]);
+          if (lane == 0) {
+            w = mbar_wait_bounded(smem_u32(&b_empty[s]), ph ^ 1u, abort_ptr, kTcWaitLimitNs) ? 1 : 0;
+            if (w) mbar_arrive_expect_tx(fb, b_tx);
+          }
+          w = __shfl_sync(0xffffffffu, w, 0);
+          if (!w) {
             ok = false;
             break;
           }
-          const uint32_t ab_bar = smem_u32(&a_full[ab]);
-          const uint32_t a_dst = smem_base + static_cast<uint32_t>(ab) * a_buf_bytes;
-          mbar_arrive_expect_tx(ab_bar, a_tx);
-          tma_load_4d(a_dst, &map_a0, ab_bar, cb * p.k_elems, ox0 - p.pad_l, oy0 - p.pad_t, img);
-          if (PLANES == 2)
-            tma_load_4d(a_dst + patch_bytes, &map_a1, ab_bar, cb * p.k_elems, ox0 - p.pad_l, oy0 - p.pad_t, img);
-          ++a_issued;
-          ab ^= 1;
-          if (ab == 0) a_ph ^= 1u;
-          for (int tap = 0; tap < p.taps; ++tap) {
-            if (!mbar_wait_bounded(smem_u32(&b_empty[s]), ph ^ 1u, abort_ptr, kTcWaitLimitNs)) {
-              ok = false;
-              break;
-            }
-            const uint32_t fb = smem_u32(&b_full[s]);
-            const uint32_t b_dst = b_ring + static_cast<uint32_t>(s) * b_stage_bytes;
-            const int k0 = (tap * p.c_blocks + cb) * p.k_elems;
-            mbar_arrive_expect_tx(fb, b_tx);
-            tma_load_2d(b_dst, &map_b0, fb, k0, n0);
-            if (PLANES == 2) tma_load_2d(b_dst + b_bytes, &map_b1, fb, k0, n0);
-            ++b_issued;
-            if (++s == S) {
-              s = 0;
-              ph ^= 1u;
-            }
+          if (b_issuer)
+            tma_load_2d(b_ring + static_cast<uint32_t>(s) * b_stage_bytes + plane * b_bytes,
+                        plane ? &map_b1 : &map_b0, fb, (tap * p.c_blocks + cb) * p.k_elems, n0);
+          ++b_issued;
+          if (++s == S) {
+            s = 0;
+            ph ^= 1u;
           }
         }
       }
+    }
+    if (lane == 0) {
       if (!ok) {
         if (atomicCAS(const_cast<int*>(abort_ptr), 0, 1) == 0) atomicCAS(p.status, 0, TC_TIMEOUT_PRODUCER);
       }
       if (*abort_ptr != 0) {
-        // copies issued by this thread may still be landing: wait (bounded) for the last ones
+        // copies issued by this warp may still be landing: wait (bounded) for the last ones
         int zero = 0;
         for (long long i = b_issued > S ? b_issued - S : 0; i < b_issued; ++i)
           mbar_wait_bounded(smem_u32(&b_full[i % S]), static_cast<uint32_t>((i / S) & 1), &zero, 200000000ull);

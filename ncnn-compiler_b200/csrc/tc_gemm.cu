@@ -105,6 +105,13 @@ std::string encode_im2col(CUtensorMap* map, int kind, const void* base, const Tc
   return {};
 }
 
+// Dynamic shared memory a CTA may fill: 227 KB per block, minus ~1.2 KB of static shared
+// memory (barriers, per-tile constants), minus 1 KB of alignment slack.
+constexpr int kTcSmemBudget = 224 * 1024;
+// From this many K blocks per tile on, the main loop of the next tile hides even the slower
+// direct epilogue, and a third ring stage is worth more than the staging tiles.
+constexpr int kDirectEpilogueDepth = 32;
+
 // Tile width: every multiple of 16 up to 128 is a legal UMMA N.  Cost model:
 // waves over the SMs times (columns computed + a fixed per-tile term for the
 // A traffic and pipeline fill, which do not shrink with the tile).
@@ -157,19 +164,19 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
   if (p.tma_store) {
     for (int bufs : {4, 3, 2}) {
       p.out_bufs = bufs;
-      staging = 16384 + bufs * out_tile;
-      if ((222 * 1024 - staging) / p.stage_bytes >= 3 || bufs == 2) break;
+      staging = (res_mode != RES_NONE ? 16384 : 0) + bufs * out_tile;
+      if ((kTcSmemBudget - staging) / p.stage_bytes >= 3 || bufs == 2) break;
     }
     // Deep contractions hide even a slow epilogue behind the main loop; there a third ring
     // stage is worth more than the staging tiles.
-    const int with = (222 * 1024 - staging) / p.stage_bytes;
-    const int without = (222 * 1024) / p.stage_bytes;
-    if (with < 3 && without >= 3 && p.k_blocks >= 32) {
+    const int with = (kTcSmemBudget - staging) / p.stage_bytes;
+    const int without = (kTcSmemBudget) / p.stage_bytes;
+    if (with < 3 && without >= 3 && p.k_blocks >= kDirectEpilogueDepth) {
       p.tma_store = 0;
       staging = 0;
     }
   }
-  const int budget = 222 * 1024 - staging;
+  const int budget = kTcSmemBudget - staging;
   p.stages = std::max(2, std::min(kTcMaxStages, budget / p.stage_bytes));
   L->smem_bytes = p.stages * p.stage_bytes + staging + 1024;
   // never fewer bytes than half an SM's shared memory: two CTAs must not share an
@@ -232,7 +239,7 @@ int tc_row_bytes(int kind, int channels) {
     if (channels % 16 != 0) return 0;
     return channels > 64 ? 128 : (channels > 32 ? 64 : 32);
   }
-  if (kind == GEMM_BF16X3) return channels % 64 == 0 ? 128 : 0;
+  if (kind == GEMM_BF16X3) return channels % 64 == 0 ? 128 : (channels % 32 == 0 ? 64 : 0);
   if (channels % 4 != 0) return 0;
   return 128;
 }
@@ -333,7 +340,7 @@ cudaError_t tc_launch(const TcLaunch& L, cudaStream_t stream) {
   static std::once_flag attr_once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(attr_once, [] {
-    const int max_smem = 224 * 1024;  // 227 KB per block minus static shared memory
+    const int max_smem = kTcSmemBudget + 1024;  // contents + alignment slack
     cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<GEMM_TF32>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
     if (e == cudaSuccess)
@@ -452,10 +459,10 @@ std::string tc_plan_conv_halo(TcHaloLaunch* L, int kind, const TcHaloConv& c, co
   const int out_tile = (e.out_mode == OUT_F32_SPLIT || wide ? 2 : 1) * 8192;
   const int fixed = 2 * planes * p.patch_bytes + (res_mode != RES_NONE ? 16384 : 0);
   p.out_bufs = 4;
-  p.stages = (222 * 1024 - fixed - p.out_bufs * out_tile) / (planes * p.b_bytes);
+  p.stages = (kTcSmemBudget - fixed - p.out_bufs * out_tile) / (planes * p.b_bytes);
   if (p.stages < 4) {
     p.out_bufs = 2;
-    p.stages = (222 * 1024 - fixed - p.out_bufs * out_tile) / (planes * p.b_bytes);
+    p.stages = (kTcSmemBudget - fixed - p.out_bufs * out_tile) / (planes * p.b_bytes);
   }
   p.stages = std::min(p.stages, kTcMaxStages);
   if (p.stages < 2) return "shared memory cannot hold the patch buffers and two weight stages";
@@ -495,7 +502,7 @@ cudaError_t tc_launch_halo(const TcHaloLaunch& L, cudaStream_t stream) {
   static std::once_flag attr_once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(attr_once, [] {
-    const int max_smem = 224 * 1024;
+    const int max_smem = kTcSmemBudget + 1024;
     cudaError_t e = cudaFuncSetAttribute(tc_conv_halo_kernel<GEMM_TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          max_smem);
     if (e == cudaSuccess)
@@ -508,13 +515,13 @@ cudaError_t tc_launch_halo(const TcHaloLaunch& L, cudaStream_t stream) {
   });
   if (attr_err != cudaSuccess) return attr_err;
   if (L.kind == GEMM_BF16X3) {
-    tc_conv_halo_kernel<GEMM_BF16X3><<<L.grid, kTcThreads, L.smem_bytes, stream>>>(
+    tc_conv_halo_kernel<GEMM_BF16X3><<<L.grid, kHaloThreads, L.smem_bytes, stream>>>(
         L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0, L.map_o1, L.map_r0, L.map_r1);
   } else if (L.kind == GEMM_TF32X3) {
-    tc_conv_halo_kernel<GEMM_TF32X3><<<L.grid, kTcThreads, L.smem_bytes, stream>>>(
+    tc_conv_halo_kernel<GEMM_TF32X3><<<L.grid, kHaloThreads, L.smem_bytes, stream>>>(
         L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0, L.map_o1, L.map_r0, L.map_r1);
   } else {
-    tc_conv_halo_kernel<GEMM_TF32><<<L.grid, kTcThreads, L.smem_bytes, stream>>>(
+    tc_conv_halo_kernel<GEMM_TF32><<<L.grid, kHaloThreads, L.smem_bytes, stream>>>(
         L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0, L.map_o1, L.map_r0, L.map_r1);
   }
   return cudaGetLastError();

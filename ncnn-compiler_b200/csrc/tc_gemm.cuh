@@ -5,9 +5,9 @@
 // channels), InnerProduct and Gemm (A is a plain row-major matrix loaded by
 // tiled TMA).  B is always the packed weight matrix [N][K], K contiguous.
 //
-// Pipeline per CTA (persistent, one CTA per SM, 192 threads):
-//   warp 0     TMA producer: fills a ring of shared-memory stages (A tile 128 x K-block,
-//              B tile block_n x K-block, 128B/64B-swizzled rows)
+// Pipeline per CTA (persistent, one CTA per SM, 224 threads):
+//   warps 0,6  TMA producers (A tiles / B tiles): fill a ring of shared-memory stages
+//              (A tile 128 x K-block, B tile block_n x K-block, 128B/64B-swizzled rows)
 //   warp 1     MMA issuer: tcgen05.mma from shared memory into one of two TMEM
 //              accumulators (128 lanes x block_n fp32/int32 columns)
 //   warps 2-5  epilogue: tcgen05.ld of the finished accumulator, then bias, residual,
@@ -54,7 +54,7 @@ enum : int {
   TC_TIMEOUT_EPILOGUE = 3,
 };
 
-constexpr int kTcThreads = 192;
+constexpr int kTcThreads = 224;  // warps: 0 A producer, 1 MMA issuer, 2-5 epilogue, 6 B producer
 constexpr int kTcBlockM = 128;
 constexpr int kTcMaxStages = 8;
 constexpr uint32_t kTcTmemCols = 256;           // two accumulators of up to 128 columns
@@ -128,7 +128,9 @@ __device__ __forceinline__ float apply_act(float y, int act, float a, float b) {
   return y;
 }
 
-template <int KIND>
+// BF16IO: a bf16-pair tensor takes part (as output or residual); kept out of the other
+// instantiation so that the int8 and plain fp32 epilogues stay lean.
+template <int KIND, bool BF16IO>
 __device__ __forceinline__ void tc_epilogue_chunk(const TcGemmParams& p, const uint32_t (&v)[16],
                                                   long long m, int n_first, const float* tile_bias,
                                                   const float* tile_scale) {
@@ -151,7 +153,7 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcGemmParams& p, const u
   }
   const long long row = m * p.ldo;
   const bool vec4 = (p.ldo % 4 == 0) && (n_first % 4 == 0);
-  if (p.res_mode == RES_BF16X2) {
+  if (BF16IO && p.res_mode == RES_BF16X2) {
     const uint16_t* r0 = reinterpret_cast<const uint16_t*>(p.res0);
     const uint16_t* r1 = reinterpret_cast<const uint16_t*>(p.res1);
     if ((p.ldo % 8 == 0) && n_first + 15 < p.N) {
@@ -226,7 +228,7 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcGemmParams& p, const u
   }
 #pragma unroll
   for (int j = 0; j < 16; ++j) y[j] = apply_act(y[j], p.act, p.act_a, p.act_b);
-  if (p.out_mode == OUT_BF16X2) {
+  if (BF16IO && p.out_mode == OUT_BF16X2) {
     uint16_t* o0 = reinterpret_cast<uint16_t*>(p.out0);
     uint16_t* o1 = reinterpret_cast<uint16_t*>(p.out1);
     uint32_t hi[8], mid[8];
@@ -541,7 +543,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int i = 0; i < S; ++i) {
-      mbar_init(smem_u32(&full_bar[i]), 1);
+      mbar_init(smem_u32(&full_bar[i]), 2);  // one arrival per producer warp
       mbar_init(smem_u32(&empty_bar[i]), 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -566,75 +568,85 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ producer
-    if (lane == 0) {
-      int s = 0;
-      uint32_t ph = 0;
-      long long issued = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int m_blk = tile / p.tiles_n;
-        const int n_blk = tile - m_blk * p.tiles_n;
-        const long long m0 = static_cast<long long>(m_blk) * kTcBlockM;
-        const int n0 = n_blk * p.block_n;
-        int img = 0, h_base = 0, w_base = 0;
-        if (p.a_im2col) {
-          const long long per_img = static_cast<long long>(p.OH) * p.OW;
-          img = static_cast<int>(m0 / per_img);
-          const int r = static_cast<int>(m0 - img * per_img);
-          const int oh = r / p.OW;
-          const int ow = r - oh * p.OW;
-          h_base = oh * p.stride_h - p.pad_t;
-          w_base = ow * p.stride_w - p.pad_l;
+  if (warp == 0 || warp == 6) {
+    // ------------------------------------------------------------ producers
+    // Arming a stage and issuing its copies costs the issuing thread several hundred cycles per
+    // K block (about 450 for the barrier hand-shake plus about 120 per TMA instruction, whatever
+    // the box size), more than the MMAs of a narrow K block take.  So the work is split: warp 0
+    // feeds the A tiles, warp 6 the B tiles, each arming the stage for its own bytes (the full
+    // barrier counts two arrivals).  Within a warp lane p issues plane p.
+    const bool is_b = warp == 6;
+    const bool issuer = lane < PLANES;
+    const CUtensorMap* my_map = is_b ? (lane ? &map_b1 : &map_b0) : (lane ? &map_a1 : &map_a0);
+    const uint32_t my_off = is_b ? PLANES * slot + lane * b_slot : lane * slot;
+    const uint32_t my_tx = PLANES * (is_b ? static_cast<uint32_t>(p.block_n) * p.row_bytes : slot);
+    int s = 0;
+    uint32_t ph = 0;
+    long long issued = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      const int m_blk = tile / p.tiles_n;
+      const int n_blk = tile - m_blk * p.tiles_n;
+      const long long m0 = static_cast<long long>(m_blk) * kTcBlockM;
+      const int n0 = n_blk * p.block_n;
+      int img = 0, h_base = 0, w_base = 0;
+      if (p.a_im2col) {
+        const long long per_img = static_cast<long long>(p.OH) * p.OW;
+        img = static_cast<int>(m0 / per_img);
+        const int r = static_cast<int>(m0 - img * per_img);
+        const int oh = r / p.OW;
+        const int ow = r - oh * p.OW;
+        h_base = oh * p.stride_h - p.pad_t;
+        w_base = ow * p.stride_w - p.pad_l;
+      }
+      if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.trace[(tile / gridDim.x) * 16 + 0] = clock64();
+      int cb = 0, kh = 0, kw = 0;
+      for (int kb = 0; kb < p.k_blocks; ++kb) {
+        const uint32_t fb = smem_u32(&full_bar[s]);
+        int w = 1;
+        if (lane == 0) {
+          w = mbar_wait_bounded(smem_u32(&empty_bar[s]), ph ^ 1u, abort_ptr, kTcWaitLimitNs) ? 1 : 0;
+          if (w) mbar_arrive_expect_tx(fb, my_tx);
         }
-        if (p.trace != nullptr && blockIdx.x == 0) p.trace[(tile / gridDim.x) * 16 + 0] = clock64();
-        int tap = 0, cb = 0;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!mbar_wait_bounded(smem_u32(&empty_bar[s]), ph ^ 1u, abort_ptr, kTcWaitLimitNs)) {
-            ok = false;
-            break;
-          }
-          const bool tr = p.trace != nullptr && blockIdx.x == 0 && tile == static_cast<int>(gridDim.x) && kb < 32;
-          if (tr) p.trace[1024 + kb * 4 + 0] = clock64();
-          const uint32_t fb = smem_u32(&full_bar[s]);
-          mbar_arrive_expect_tx(fb, tx_bytes);
-          const uint32_t a_dst = smem_base + s * stage_bytes;
-          const uint32_t b_dst = a_dst + PLANES * slot;
-          if (p.a_im2col) {
-            const int kh = tap / p.KW;
-            const int kw = tap - kh * p.KW;
-            const uint16_t off_w = static_cast<uint16_t>(kw * p.dil_w);
-            const uint16_t off_h = static_cast<uint16_t>(kh * p.dil_h);
-            tma_load_im2col_4d(a_dst, &map_a0, fb, cb * p.k_elems, w_base, h_base, img, off_w,
-                               off_h);
-            if (PLANES == 2)
-              tma_load_im2col_4d(a_dst + slot, &map_a1, fb, cb * p.k_elems, w_base, h_base, img,
-                                 off_w, off_h);
+        w = __shfl_sync(0xffffffffu, w, 0);
+        if (!w) {
+          ok = false;
+          break;
+        }
+        const bool tr = p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0 && tile == static_cast<int>(gridDim.x) && kb < 32;
+        if (tr) p.trace[1024 + kb * 4 + 0] = clock64();
+        if (issuer) {
+          const uint32_t dst = smem_base + s * stage_bytes + my_off;
+          if (is_b) {
+            tma_load_2d(dst, my_map, fb, kb * p.k_elems, n0);
+          } else if (p.a_im2col) {
+            tma_load_im2col_4d(dst, my_map, fb, cb * p.k_elems, w_base, h_base, img,
+                               static_cast<uint16_t>(kw * p.dil_w), static_cast<uint16_t>(kh * p.dil_h));
           } else {
-            tma_load_2d(a_dst, &map_a0, fb, kb * p.k_elems, static_cast<int>(m0));
-            if (PLANES == 2)
-              tma_load_2d(a_dst + slot, &map_a1, fb, kb * p.k_elems, static_cast<int>(m0));
+            tma_load_2d(dst, my_map, fb, kb * p.k_elems, static_cast<int>(m0));
           }
-          tma_load_2d(b_dst, &map_b0, fb, kb * p.k_elems, n0);
-          if (PLANES == 2) tma_load_2d(b_dst + b_slot, &map_b1, fb, kb * p.k_elems, n0);
-          if (tr) p.trace[1024 + kb * 4 + 1] = clock64();
-          ++issued;
-          if (++cb == p.c_blocks) {
-            cb = 0;
-            ++tap;
+        }
+        if (tr) p.trace[1024 + kb * 4 + 1] = clock64();
+        ++issued;
+        if (++cb == p.c_blocks) {
+          cb = 0;
+          if (++kw == p.KW) {
+            kw = 0;
+            ++kh;
           }
-          if (++s == S) {
-            s = 0;
-            ph ^= 1u;
-          }
+        }
+        if (++s == S) {
+          s = 0;
+          ph ^= 1u;
         }
       }
+    }
+    if (lane == 0) {
       if (!ok) {
         if (atomicCAS(const_cast<int*>(abort_ptr), 0, 1) == 0) atomicCAS(p.status, 0, TC_TIMEOUT_PRODUCER);
       }
       if (*abort_ptr != 0) {
-        // Some role gave up.  Copies this thread issued may still be landing in
+        // Some role gave up.  Copies this warp issued may still be landing in
         // shared memory: wait (bounded) for each of the last S fills to finish.
         int zero = 0;
         const long long first = issued > S ? issued - S : 0;
@@ -769,7 +781,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
         // staging area behind the ring: residual tiles (16 KB), then the output tiles
         TcStageCfg cfg;
         cfg.res_stage = smem_base + static_cast<uint32_t>(S) * stage_bytes;
-        cfg.out_stage = cfg.res_stage + 16384u;
+        cfg.out_stage = cfg.res_stage + (e_res_mode != RES_NONE ? 16384u : 0u);
         cfg.res_bar = smem_u32(&res_bar);
         cfg.out_bufs = e_out_bufs;
         cfg.out_mode = e_out_mode;
@@ -795,12 +807,15 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
         if (!ok) break;
       } else {
         named_barrier_sync(3, 128);
+        const bool bf16_io = e_out_mode == OUT_BF16X2 || e_res_mode == RES_BF16X2;
         for (int c0 = 0; c0 < e_block_n; c0 += 16) {
           uint32_t v[16];
           tmem_ld16(t_row + static_cast<uint32_t>(c0), v);
           tmem_ld_wait();
-          if (m < lp.M && n0 + c0 < e_N)
-            tc_epilogue_chunk<KIND>(lp, v, m, n0 + c0, tile_bias + c0, tile_scale + c0);
+          if (m < lp.M && n0 + c0 < e_N) {
+            if (bf16_io) tc_epilogue_chunk<KIND, true>(lp, v, m, n0 + c0, tile_bias + c0, tile_scale + c0);
+            else tc_epilogue_chunk<KIND, false>(lp, v, m, n0 + c0, tile_bias + c0, tile_scale + c0);
+          }
         }
         named_barrier_sync(3, 128);  // nobody reads the tile constants any more
       }
