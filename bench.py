@@ -171,7 +171,7 @@ def main():
     ap.add_argument("--batch", type=int, default=64, help="images per GPU per step")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--model", default="resnet18", choices=["resnet18", "resnet18_int8", "mobilenet_v2", "single_conv"])
-    ap.add_argument("--accuracy-mode", type=int, default=0, help="0 fp32 via 3xTF32 (default), 1 tf32, 2 cuda-core fp32")
+    ap.add_argument("--accuracy-mode", type=int, default=0, help="0 fp32 via split operands, three bf16 MMAs per product (default), 1 tf32, 2 cuda-core fp32")
     ap.add_argument("--gather", action="store_true", help="all-gather the outputs over NCCL inside the timed region")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="budget of the cpu_baseline sample")
     ap.add_argument("--per-layer", default=None, help="write a per-launch roofline table (markdown) to this path")
@@ -201,7 +201,7 @@ def main():
     tmp = tempfile.mkdtemp(prefix=f"ncnn_b200_bench_r{rank}_")
     if args.model == "resnet18":
         param, bin_ = pkg.zoo.resnet18(os.path.join(tmp, "resnet18"))
-        dtype = "f32" if args.accuracy_mode == 2 else ("tf32x3" if args.accuracy_mode == 0 else "tf32")
+        dtype = "f32" if args.accuracy_mode == 2 else ("bf16x3" if args.accuracy_mode == 0 else "tf32")
     elif args.model == "resnet18_int8":
         param, bin_ = pkg.zoo.resnet18(os.path.join(tmp, "resnet18_int8"), int8=True)
         dtype = "int8"
@@ -210,7 +210,7 @@ def main():
             param, bin_ = pkg.zoo.single_conv(os.path.join(tmp, "single_conv"))
         else:
             param, bin_ = pkg.zoo.mobilenet_v2(os.path.join(tmp, "mobilenet_v2"))
-        dtype = "f32" if args.accuracy_mode == 2 else ("tf32x3" if args.accuracy_mode == 0 else "tf32")
+        dtype = "f32" if args.accuracy_mode == 2 else ("bf16x3" if args.accuracy_mode == 0 else "tf32")
     model = pkg.Model(param, bin_, accuracy_mode=args.accuracy_mode, device=local_rank)
     n = args.batch
     in_shape = model.input_shapes[0]
@@ -284,7 +284,7 @@ def main():
 
     # per-launch timing with CUDA events on the launching stream (same workload, eager launches)
     rows = model.profile(n, repeat=5)
-    tc = [r for r in rows if r["kernel"].startswith("tc_gemm_kernel")]
+    tc = [r for r in rows if r["kernel"].startswith(("tc_gemm_kernel", "tc_conv_halo_kernel"))]
     peaks = measured_peaks()
     tc_ms = sum(r["ms"] for r in tc)
     tc_flops = sum(r["flops"] for r in tc)

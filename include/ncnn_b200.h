@@ -35,7 +35,7 @@ extern "C" {
 #define NCNN_B200_STATUS_LOAD 8     /* .param/.bin rejected or layer unsupported */
 
 /* Accuracy modes of fp32 contractions (Convolution, InnerProduct, Gemm). */
-#define NCNN_B200_FP32_SPLIT 0 /* tensor cores, 3xTF32 split operands, ~1e-5 relative */
+#define NCNN_B200_FP32_SPLIT 0 /* tensor cores, split operands (bf16 pairs, else tf32 pairs), 3 MMAs, ~1e-5 relative */
 #define NCNN_B200_TF32 1       /* tensor cores, single TF32 pass, ~1e-3 relative     */
 #define NCNN_B200_FP32_CUDA 2  /* CUDA-core fp32 FMA                                 */
 

@@ -86,13 +86,40 @@ struct Step {
   double flops = 0.0, bytes = 0.0;
 };
 
+constexpr int kMaxChunks = 4;
+
 struct Plan {
   int64_t n = 0;
   std::vector<Step> steps;
-  std::vector<float*> d_in, d_out;  // staging used by run_host
+  std::vector<float*> d_in, d_out;  // staging used by host-pointer runs
   cudaGraphExec_t graph = nullptr;
   std::vector<const void*> graph_ptrs;  // the edge pointers the graph was captured with
+  // Pipelined host-pointer runs: the batch is uploaded in `chunks` pieces; as soon as a piece
+  // has landed, its input edge and the first `head_end` layers run on its images alone
+  // (head[c]); the remaining layers and the output edges run once on the whole batch (tail).
+  int chunks = 0;
+  int head_end = 0;
+  std::vector<Step> head[kMaxChunks], tail;
+  cudaGraphExec_t head_graph[kMaxChunks] = {};
+  cudaGraphExec_t tail_graph = nullptr;
+  void release() {
+    if (graph != nullptr) cudaGraphExecDestroy(graph);
+    graph = nullptr;
+    for (cudaGraphExec_t& g : head_graph) {
+      if (g != nullptr) cudaGraphExecDestroy(g);
+      g = nullptr;
+    }
+    if (tail_graph != nullptr) cudaGraphExecDestroy(tail_graph);
+    tail_graph = nullptr;
+    for (float* p : d_in) cudaFree(p);
+    for (float* p : d_out) cudaFree(p);
+    d_in.clear();
+    d_out.clear();
+  }
 };
+
+// Host-pointer runs that upload at least this much are pipelined.
+constexpr size_t kPipelineUploadBytes = 4u << 20;
 
 size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -133,19 +160,26 @@ int host_quantize(float x, float s) {
 class EngineImpl {
  public:
   ~EngineImpl() {
-    for (auto& kv : plans_) {
-      if (kv.second.graph != nullptr) cudaGraphExecDestroy(kv.second.graph);
-      for (float* p : kv.second.d_in) cudaFree(p);
-      for (float* p : kv.second.d_out) cudaFree(p);
-    }
+    for (auto& kv : plans_) kv.second.release();
     for (void* p : device_allocs_) cudaFree(p);
     if (arena_ != nullptr) cudaFree(arena_);
+    for (cudaEvent_t e : upload_done_)
+      if (e != nullptr) cudaEventDestroy(e);
+    if (copy_stream_ != nullptr) cudaStreamDestroy(copy_stream_);
     if (stream_ != nullptr) cudaStreamDestroy(stream_);
   }
 
   bool build(const std::string& param, const std::string& bin, const EngineOptions& opt,
              std::string* err);
   int run(int64_t n, const float* const* in, float* const* out, bool host, cudaStream_t stream);
+  int run_host_pipelined(Plan* plan, const float* const* in, float* const* out);
+  bool build_pipeline(Plan* plan);
+  bool ensure_staging(Plan* plan);
+  bool issue_steps(const std::vector<Step>& steps, cudaStream_t st);
+  cudaGraphExec_t capture_steps(const std::vector<Step>& steps);
+  int launch(Plan* plan, const std::vector<const float*>& d_in, const std::vector<float*>& d_out, cudaStream_t st);
+  int finish_host_run(cudaStream_t st);
+  void choose_head_limit();
   int profile(int64_t n, int repeat, std::vector<LayerTiming>* out);
   Plan* plan_for(int64_t n);
 
@@ -164,6 +198,12 @@ class EngineImpl {
   int* d_status_ = nullptr;
   int sm_count_ = 148;
   cudaStream_t stream_ = nullptr;
+  cudaStream_t copy_stream_ = nullptr;  // uploads of the pipelined host-pointer path
+  cudaEvent_t upload_done_[kMaxChunks] = {};
+  // image window applied by ref(): tensors are laid out for layout_n_ images (0: the n
+  // passed in) and pointers start at image img0_
+  int64_t layout_n_ = 0, img0_ = 0;
+  int head_limit_ = 0;  // layers [0, head_limit_) may run per chunk (their tensors never share arena space)
   bool any_fp32_tc_ = false;
 
  private:
@@ -1240,6 +1280,27 @@ bool EngineImpl::prepare_weights(std::string* err) {
   return true;
 }
 
+// How many leading layers may be run per upload chunk: as many as it takes to keep the GPU
+// busy for about the time the upload of the inputs needs (estimated per image at 50 GB/s over
+// PCIe against 150 TFLOP/s on the tensor cores, 8 TFLOP/s on the CUDA cores and 2 TB/s for
+// memory-bound layers).  Which of them a given batch really runs per chunk is decided per plan.
+void EngineImpl::choose_head_limit() {
+  double upload = 0.0;
+  for (int t : inputs_) upload += static_cast<double>(tensors_[resolve(t)].logical()) * 4.0 / 50e9;
+  double spent = 0.0;
+  head_limit_ = 0;
+  for (size_t k = 0; k < nodes_.size(); ++k) {
+    const Node& n = nodes_[k];
+    double bytes = static_cast<double>(tensors_[resolve(n.out)].logical()) * 4.0;
+    for (int t : n.in) bytes += static_cast<double>(tensors_[resolve(t)].logical()) * 4.0;
+    const bool contraction = n.kind == N_CONV || n.kind == N_IP || n.kind == N_GEMM;
+    const double cost = std::max(bytes / 2e12, contraction ? n.flops / (n.impl == IMPL_TC ? 150e12 : 8e12) : 0.0);
+    if (spent + cost > 1.25 * upload) break;
+    spent += cost;
+    head_limit_ = static_cast<int>(k) + 1;
+  }
+}
+
 void EngineImpl::plan_memory() {
   // sizes
   for (Tensor& t : tensors_) {
@@ -1267,6 +1328,16 @@ void EngineImpl::plan_memory() {
     tensors_[resolve(t)].last_use = std::max(tensors_[resolve(t)].last_use, 0);
   }
   for (int t : outputs_) tensors_[resolve(t)].last_use = end;
+  // Layers [0, head_limit_) may run chunk by chunk (pipelined host path): while one chunk
+  // is in them, another chunk's results of the same layers are waiting for the tail, so the
+  // tensors they touch must all be live together.
+  for (Tensor& t : tensors_) {
+    if (t.alias >= 0 || head_limit_ == 0) continue;
+    if (t.first_def < head_limit_ && (t.last_use >= 0 || t.is_input)) {
+      t.first_def = -1;
+      t.last_use = std::max(t.last_use, head_limit_ - 1);
+    }
+  }
   // greedy first fit, largest first
   struct Placed {
     size_t off, size;
@@ -1308,12 +1379,15 @@ ActRef EngineImpl::ref(int tensor, int64_t n) const {
   const Tensor& t = tensors_[resolve(tensor)];
   ActRef r;
   r.fmt = t.fmt;
-  uint8_t* base = arena_ + t.offset * static_cast<size_t>(n);
+  // layout for `ln` images; pointers start at image img0_ (images are dense inside a plane)
+  const size_t ln = static_cast<size_t>(layout_n_ > 0 ? layout_n_ : n);
+  const size_t image_elems = t.rank == 3 ? static_cast<size_t>(t.h) * t.Wp * t.Cp : static_cast<size_t>(t.logical());
+  uint8_t* base = arena_ + t.offset * ln + static_cast<size_t>(img0_) * image_elems * t.elem_bytes();
   if (t.fmt == FMT_I8) {
     r.q = reinterpret_cast<int8_t*>(base);
   } else {
     r.p0 = reinterpret_cast<float*>(base);
-    if (t.planes() == 2) r.p1 = reinterpret_cast<float*>(base + t.plane_bytes * static_cast<size_t>(n));
+    if (t.planes() == 2) r.p1 = reinterpret_cast<float*>(base + t.plane_bytes * ln);
   }
   return r;
 }
@@ -1343,6 +1417,7 @@ bool EngineImpl::build(const std::string& param, const std::string& bin, const E
   if (!choose_impl(err)) return false;
   if (opt.plan_only) return true;
   if (!prepare_weights(err)) return false;
+  choose_head_limit();
   plan_memory();
   if (cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking) != cudaSuccess) return fail(err, "cannot create a stream");
   void* st = nullptr;
@@ -1752,11 +1827,7 @@ Plan* EngineImpl::plan_for(int64_t n) {
   // scale with n, so plans of other batch sizes stay valid only for their own n.
   const size_t need = arena_per_image_ * static_cast<size_t>(n) + 4096;
   if (need > arena_bytes_) {
-    for (auto& kv : plans_) {
-      if (kv.second.graph != nullptr) cudaGraphExecDestroy(kv.second.graph);
-      for (float* p : kv.second.d_in) cudaFree(p);
-      for (float* p : kv.second.d_out) cudaFree(p);
-    }
+    for (auto& kv : plans_) kv.second.release();
     plans_.clear();
     if (arena_ != nullptr) cudaFree(arena_);
     arena_ = nullptr;
@@ -1799,6 +1870,222 @@ void EngineImpl::restore_padding(int64_t n, cudaStream_t st) {
   last_run_n_ = n;
 }
 
+bool EngineImpl::ensure_staging(Plan* plan) {
+  if (!plan->d_in.empty() || inputs_.empty()) return true;
+  for (int t : inputs_) {
+    void* p = nullptr;
+    if (cudaMalloc(&p, tensors_[resolve(t)].logical() * 4 * plan->n) != cudaSuccess) {
+      error_ = "out of device memory for input staging";
+      return false;
+    }
+    plan->d_in.push_back(static_cast<float*>(p));
+  }
+  for (int t : outputs_) {
+    void* p = nullptr;
+    if (cudaMalloc(&p, tensors_[resolve(t)].logical() * 4 * plan->n) != cudaSuccess) {
+      error_ = "out of device memory for output staging";
+      return false;
+    }
+    plan->d_out.push_back(static_cast<float*>(p));
+  }
+  return true;
+}
+
+bool EngineImpl::issue_steps(const std::vector<Step>& steps, cudaStream_t st) {
+  for (const Step& step : steps) {
+    const cudaError_t e = step.run(st);
+    if (e != cudaSuccess) {
+      error_ = "launch of " + step.kernel + " for layer " + step.name + " failed: " + cudaGetErrorString(e);
+      return false;
+    }
+  }
+  return true;
+}
+
+// Captures the steps into an executable graph.  Capture happens on the runtime's own stream
+// with nothing in flight, so that queued work does not end up inside the graph.
+cudaGraphExec_t EngineImpl::capture_steps(const std::vector<Step>& steps) {
+  cudaStreamSynchronize(stream_);
+  cudaGraph_t g = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  cudaError_t e = cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal);
+  if (e == cudaSuccess) {
+    const bool ok = issue_steps(steps, stream_);
+    const cudaError_t ee = cudaStreamEndCapture(stream_, &g);
+    e = ok ? ee : cudaErrorUnknown;
+  }
+  if (e == cudaSuccess) e = cudaGraphInstantiate(&exec, g, 0);
+  if (g != nullptr) cudaGraphDestroy(g);
+  if (e != cudaSuccess) {
+    if (error_.empty()) error_ = std::string("CUDA graph capture failed: ") + cudaGetErrorString(e);
+    return nullptr;
+  }
+  return exec;
+}
+
+// Enqueues one pass of `plan` on `st`: input edges, layers, output edges; as a replay of the
+// captured graph when graphs are enabled (re-captured when the edge pointers changed).
+int EngineImpl::launch(Plan* plan, const std::vector<const float*>& d_in, const std::vector<float*>& d_out,
+                       cudaStream_t st) {
+  const int64_t n = plan->n;
+  restore_padding(n, st);
+  std::vector<Step> all, post;
+  make_edge_steps(n, d_in, d_out, &all, &post);
+  all.insert(all.end(), plan->steps.begin(), plan->steps.end());
+  all.insert(all.end(), post.begin(), post.end());
+  if (!opt_.use_cuda_graph) return issue_steps(all, st) ? 0 : 6;
+  std::vector<const void*> ptrs;
+  for (auto p : d_in) ptrs.push_back(p);
+  for (auto p : d_out) ptrs.push_back(p);
+  if (plan->graph == nullptr || plan->graph_ptrs != ptrs) {
+    if (plan->graph != nullptr) {
+      cudaGraphExecDestroy(plan->graph);
+      plan->graph = nullptr;
+    }
+    plan->graph = capture_steps(all);
+    if (plan->graph == nullptr) return 6;
+    plan->graph_ptrs = ptrs;
+  }
+  const cudaError_t e = cudaGraphLaunch(plan->graph, st);
+  if (e != cudaSuccess) {
+    error_ = std::string("launch failed: ") + cudaGetErrorString(e);
+    return 6;
+  }
+  return 0;
+}
+
+// Reads back the device status word, waits for the stream and maps the outcome to a status.
+int EngineImpl::finish_host_run(cudaStream_t st) {
+  int status = 0;
+  cudaMemcpyAsync(&status, d_status_, 4, cudaMemcpyDeviceToHost, st);
+  const cudaError_t e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) {
+    error_ = std::string("execution failed: ") + cudaGetErrorString(e);
+    return 6;
+  }
+  if (status != 0) {
+    error_ = "a tensor-core pipeline wait timed out (status " + std::to_string(status) + ")";
+    cudaMemset(d_status_, 0, 4);
+    return 7;
+  }
+  return 0;
+}
+
+// Splits the plan into per-chunk heads and a whole-batch tail (see Plan).  A layer joins the
+// head only while a chunk still fills the GPU: a tensor-core convolution needs at least two
+// 128-pixel tiles per SM in every chunk.
+bool EngineImpl::build_pipeline(Plan* plan) {
+  if (plan->chunks != 0) return true;
+  const int64_t n = plan->n;
+  // four chunks measured best on a 64-image ResNet-18 batch (two leave more upload exposed,
+  // eight make the per-chunk layers too small)
+  const int chunks = n % 4 == 0 ? 4 : 2;
+  const int64_t cnt = n / chunks;
+  int head_end = 0;
+  for (; head_end < head_limit_; ++head_end) {
+    const Node& node = nodes_[head_end];
+    if ((node.kind == N_CONV && node.impl == IMPL_TC) &&
+        cnt * node.OH * node.OW < 2ll * kTcBlockM * sm_count_)
+      break;
+    if (node.kind == N_IP || node.kind == N_GEMM) break;
+  }
+  for (int c = 0; c < chunks; ++c) {
+    layout_n_ = n;
+    img0_ = c * cnt;
+    std::vector<const float*> d_in;
+    for (size_t i = 0; i < inputs_.size(); ++i)
+      d_in.push_back(plan->d_in[i] + static_cast<size_t>(tensors_[resolve(inputs_[i])].logical()) * img0_);
+    std::vector<Step> post;
+    plan->head[c].clear();
+    make_edge_steps(cnt, d_in, plan->d_out, &plan->head[c], &post);
+    Plan piece;
+    piece.n = cnt;
+    bool ok = true;
+    for (int k = 0; k < head_end && ok; ++k) {
+      std::string err;
+      ok = emit_node(piece, nodes_[k], cnt, &err);
+      if (!ok) error_ = err;
+    }
+    layout_n_ = 0;
+    img0_ = 0;
+    if (!ok) return false;
+    plan->head[c].insert(plan->head[c].end(), piece.steps.begin(), piece.steps.end());
+  }
+  {
+    Plan piece;
+    piece.n = n;
+    for (size_t k = head_end; k < nodes_.size(); ++k) {
+      std::string err;
+      if (!emit_node(piece, nodes_[k], n, &err)) {
+        error_ = err;
+        return false;
+      }
+    }
+    std::vector<const float*> d_in(plan->d_in.begin(), plan->d_in.end());
+    std::vector<Step> pre, post;
+    make_edge_steps(n, d_in, plan->d_out, &pre, &post);
+    plan->tail = piece.steps;
+    plan->tail.insert(plan->tail.end(), post.begin(), post.end());
+  }
+  if (opt_.use_cuda_graph) {
+    for (int c = 0; c < chunks; ++c) {
+      plan->head_graph[c] = capture_steps(plan->head[c]);
+      if (plan->head_graph[c] == nullptr) return false;
+    }
+    plan->tail_graph = capture_steps(plan->tail);
+    if (plan->tail_graph == nullptr) return false;
+  }
+  plan->head_end = head_end;
+  plan->chunks = chunks;
+  return true;
+}
+
+// Host-pointer run with the upload hidden behind the first layers: all chunks go to the copy
+// stream at once, the compute stream handles chunk c as soon as its upload has landed, then
+// the rest of the network runs on the whole batch.  Results equal the one-piece run bit for
+// bit: images are independent and every kernel accumulates in the same order.
+int EngineImpl::run_host_pipelined(Plan* plan, const float* const* in, float* const* out) {
+  const int64_t n = plan->n;
+  if (copy_stream_ == nullptr) {
+    bool ok = cudaStreamCreateWithFlags(&copy_stream_, cudaStreamNonBlocking) == cudaSuccess;
+    for (int c = 0; c < kMaxChunks && ok; ++c)
+      ok = cudaEventCreateWithFlags(&upload_done_[c], cudaEventDisableTiming) == cudaSuccess;
+    if (!ok) {
+      error_ = "cannot create the upload stream";
+      return 6;
+    }
+  }
+  if (!ensure_staging(plan) || !build_pipeline(plan)) return 6;
+  const int64_t cnt = n / plan->chunks;
+  for (int c = 0; c < plan->chunks; ++c) {
+    for (size_t i = 0; i < inputs_.size(); ++i) {
+      const size_t count = static_cast<size_t>(tensors_[resolve(inputs_[i])].logical()) * cnt;
+      cudaMemcpyAsync(plan->d_in[i] + count * c, in[i] + count * c, count * 4, cudaMemcpyHostToDevice, copy_stream_);
+    }
+    cudaEventRecord(upload_done_[c], copy_stream_);
+  }
+  restore_padding(n, stream_);
+  bool ok = true;
+  for (int c = 0; c < plan->chunks && ok; ++c) {
+    cudaStreamWaitEvent(stream_, upload_done_[c], 0);
+    if (opt_.use_cuda_graph) ok = cudaGraphLaunch(plan->head_graph[c], stream_) == cudaSuccess;
+    else ok = issue_steps(plan->head[c], stream_);
+  }
+  if (ok) {
+    if (opt_.use_cuda_graph) ok = cudaGraphLaunch(plan->tail_graph, stream_) == cudaSuccess;
+    else ok = issue_steps(plan->tail, stream_);
+  }
+  if (!ok) {
+    if (error_.empty()) error_ = "launch failed in the pipelined host path";
+    cudaStreamSynchronize(copy_stream_);
+    cudaStreamSynchronize(stream_);
+    return 6;
+  }
+  for (size_t i = 0; i < outputs_.size(); ++i)
+    cudaMemcpyAsync(out[i], plan->d_out[i], tensors_[resolve(outputs_[i])].logical() * 4 * n, cudaMemcpyDeviceToHost, stream_);
+  return finish_host_run(stream_);
+}
+
 int EngineImpl::run(int64_t n, const float* const* in, float* const* out, bool host, cudaStream_t user_stream) {
   if (opt_.plan_only) {
     error_ = "the model was loaded in plan-only mode and cannot run";
@@ -1810,28 +2097,18 @@ int EngineImpl::run(int64_t n, const float* const* in, float* const* out, bool h
   }
   Plan* plan = plan_for(n);
   if (plan == nullptr) return 6;
+  const char* pipe_env = std::getenv("NCNN_B200_PIPELINE");
+  if (host && n % 2 == 0 && !(pipe_env != nullptr && pipe_env[0] == '0')) {
+    // worth it when the upload is a visible part of the call: a few MB or more
+    size_t upload = 0;
+    for (int t : inputs_) upload += static_cast<size_t>(tensors_[resolve(t)].logical()) * 4 * n;
+    if (upload >= kPipelineUploadBytes) return run_host_pipelined(plan, in, out);
+  }
   cudaStream_t st = host ? stream_ : user_stream;
   std::vector<const float*> d_in(inputs_.size());
   std::vector<float*> d_out(outputs_.size());
   if (host) {
-    if (plan->d_in.empty()) {
-      for (int t : inputs_) {
-        void* p = nullptr;
-        if (cudaMalloc(&p, tensors_[resolve(t)].logical() * 4 * n) != cudaSuccess) {
-          error_ = "out of device memory for input staging";
-          return 6;
-        }
-        plan->d_in.push_back(static_cast<float*>(p));
-      }
-      for (int t : outputs_) {
-        void* p = nullptr;
-        if (cudaMalloc(&p, tensors_[resolve(t)].logical() * 4 * n) != cudaSuccess) {
-          error_ = "out of device memory for output staging";
-          return 6;
-        }
-        plan->d_out.push_back(static_cast<float*>(p));
-      }
-    }
+    if (!ensure_staging(plan)) return 6;
     for (size_t i = 0; i < inputs_.size(); ++i) {
       d_in[i] = plan->d_in[i];
       cudaMemcpyAsync(plan->d_in[i], in[i], tensors_[resolve(inputs_[i])].logical() * 4 * n, cudaMemcpyHostToDevice, st);
@@ -1841,75 +2118,12 @@ int EngineImpl::run(int64_t n, const float* const* in, float* const* out, bool h
     for (size_t i = 0; i < inputs_.size(); ++i) d_in[i] = in[i];
     for (size_t i = 0; i < outputs_.size(); ++i) d_out[i] = out[i];
   }
-
-  restore_padding(n, st);
-
-  std::vector<Step> pre, post;
-  make_edge_steps(n, d_in, d_out, &pre, &post);
-  auto issue = [&](cudaStream_t s) -> cudaError_t {
-    for (const std::vector<Step>* list : {static_cast<const std::vector<Step>*>(&pre), static_cast<const std::vector<Step>*>(&plan->steps), static_cast<const std::vector<Step>*>(&post)}) {
-      for (const Step& step : *list) {
-        const cudaError_t e = step.run(s);
-        if (e != cudaSuccess) {
-          error_ = "launch of " + step.kernel + " for layer " + step.name + " failed: " + cudaGetErrorString(e);
-          return e;
-        }
-      }
-    }
-    return cudaSuccess;
-  };
-
-  cudaError_t e = cudaSuccess;
-  if (opt_.use_cuda_graph) {
-    std::vector<const void*> ptrs;
-    for (auto p : d_in) ptrs.push_back(p);
-    for (auto p : d_out) ptrs.push_back(p);
-    if (plan->graph == nullptr || plan->graph_ptrs != ptrs) {
-      if (plan->graph != nullptr) {
-        cudaGraphExecDestroy(plan->graph);
-        plan->graph = nullptr;
-      }
-      cudaStream_t cap = stream_;
-      if (!host) cudaStreamSynchronize(cap);
-      cudaGraph_t g = nullptr;
-      e = cudaStreamBeginCapture(cap, cudaStreamCaptureModeThreadLocal);
-      if (e == cudaSuccess) {
-        const cudaError_t ie = issue(cap);
-        const cudaError_t ee = cudaStreamEndCapture(cap, &g);
-        e = ie != cudaSuccess ? ie : ee;
-      }
-      if (e == cudaSuccess) e = cudaGraphInstantiate(&plan->graph, g, 0);
-      if (g != nullptr) cudaGraphDestroy(g);
-      if (e != cudaSuccess) {
-        if (error_.empty()) error_ = std::string("CUDA graph capture failed: ") + cudaGetErrorString(e);
-        plan->graph = nullptr;
-        return 6;
-      }
-      plan->graph_ptrs = ptrs;
-    }
-    e = cudaGraphLaunch(plan->graph, st);
-  } else {
-    e = issue(st);
-  }
-  if (e != cudaSuccess) {
-    if (error_.empty()) error_ = std::string("launch failed: ") + cudaGetErrorString(e);
-    return 6;
-  }
+  const int rc = launch(plan, d_in, d_out, st);
+  if (rc != 0) return rc;
   if (host) {
     for (size_t i = 0; i < outputs_.size(); ++i)
       cudaMemcpyAsync(out[i], plan->d_out[i], tensors_[resolve(outputs_[i])].logical() * 4 * n, cudaMemcpyDeviceToHost, st);
-    int status = 0;
-    cudaMemcpyAsync(&status, d_status_, 4, cudaMemcpyDeviceToHost, st);
-    e = cudaStreamSynchronize(st);
-    if (e != cudaSuccess) {
-      error_ = std::string("execution failed: ") + cudaGetErrorString(e);
-      return 6;
-    }
-    if (status != 0) {
-      error_ = "a tensor-core pipeline wait timed out (status " + std::to_string(status) + ")";
-      cudaMemset(d_status_, 0, 4);
-      return 7;
-    }
+    return finish_host_run(st);
   }
   return 0;
 }
@@ -1919,10 +2133,9 @@ int EngineImpl::profile(int64_t n, int repeat, std::vector<LayerTiming>* out) {
   if (plan == nullptr) return 6;
   restore_padding(n, stream_);
   out->clear();
-  // every launch of one run: input edges, layers, output edges (edges need the staging
-  // buffers a previous host-pointer run of this batch size created)
+  // every launch of one run: input edges, layers, output edges
   std::vector<Step> all;
-  if (!plan->d_in.empty()) {
+  if (ensure_staging(plan) && !plan->d_in.empty()) {
     std::vector<Step> pre, post;
     std::vector<const float*> d_in(plan->d_in.begin(), plan->d_in.end());
     make_edge_steps(n, d_in, plan->d_out, &pre, &post);

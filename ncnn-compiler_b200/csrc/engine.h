@@ -16,7 +16,7 @@
 namespace nb {
 
 enum AccuracyMode : int {
-  kAccuracyFp32Split = 0,  // tensor cores, operands split into two tf32 terms (3 MMAs): ~1e-5
+  kAccuracyFp32Split = 0,  // tensor cores, operands split into two bf16 (or tf32) terms, 3 MMAs: ~1e-5
   kAccuracyTf32 = 1,       // tensor cores, one tf32 MMA: ~1e-3, reported separately
   kAccuracyFp32Cuda = 2,   // CUDA-core fp32 FMA for every contraction
 };

@@ -255,6 +255,30 @@ def test_alternating_batch_sizes_share_the_arena(pkg, tmp_path):
     m.close()
 
 
+@pytest.mark.parametrize("net,n", [("resnet18", 8), ("resnet18", 12), ("resnet18", 10), ("mobilenet_v2", 8), ("resnet18_int8", 8)])
+def test_pipelined_host_path_equals_one_piece(pkg, tmp_path, monkeypatch, net, n):
+    """Host-pointer runs that upload several MB overlap the upload with the first layers (chunk by
+    chunk); the result must equal the one-piece run bit for bit, call after call."""
+    if net == "mobilenet_v2":
+        param, bin_ = pkg.zoo.mobilenet_v2(str(tmp_path / "m"))
+    else:
+        param, bin_ = pkg.zoo.resnet18(str(tmp_path / "r"), int8=net.endswith("int8"))
+    rng = np.random.default_rng(n)
+    xs = [rng.uniform(-1, 1, (n, 3, 224, 224)).astype(np.float32) for _ in range(2)]
+    monkeypatch.setenv("NCNN_B200_PIPELINE", "0")
+    m = pkg.Model(param, bin_)
+    want = [m.run(x)[0].copy() for x in xs]
+    m.close()
+    monkeypatch.delenv("NCNN_B200_PIPELINE")
+    for graph in (True, False):
+        m = pkg.Model(param, bin_, use_cuda_graph=graph)
+        for x, w in zip(xs, want):
+            assert np.array_equal(m.run(x)[0], w)
+        assert np.array_equal(m.run(xs[0][:3])[0], want[0][:3])  # a small odd batch in between
+        assert np.array_equal(m.run(xs[1])[0], want[1])
+        m.close()
+
+
 def test_full_batch_properties(pkg, tmp_path):
     """Batch 64 at 224x224 (too slow for the oracle): images are independent, so permuting
     the batch permutes the outputs, and repeated calls give identical bytes."""
