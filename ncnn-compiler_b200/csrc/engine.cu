@@ -15,7 +15,7 @@
 namespace nb {
 namespace {
 
-enum NodeKind { N_CONV, N_DW, N_IP, N_GEMM, N_POOL, N_BINARY, N_UNARY, N_RELAYOUT };
+enum NodeKind { N_CONV, N_DW, N_IP, N_GEMM, N_POOL, N_BINARY, N_UNARY, N_RELAYOUT, N_SOFTMAX, N_CONCAT };
 enum Impl { IMPL_NONE, IMPL_TC, IMPL_DIRECT };
 
 struct Tensor {
@@ -69,6 +69,8 @@ struct Node {
   UnaryParams un{};
   std::vector<float> un_scale, un_offset;
   RelayoutParams relayout{};
+  SoftmaxParams softmax{};
+  std::vector<ConcatParams> concat;  // one per input
   // device-side parameters
   void* d_w0 = nullptr;
   void* d_w1 = nullptr;
@@ -256,7 +258,7 @@ bool EngineImpl::decode_activation(const LayerDef& l, int id_type, int id_params
                                    std::string* err) {
   // The reference splits a fused activation into its own op and accepts none(0),
   // ReLU(1) and Sigmoid(4) (lib/Importer/ImportConvolution.cpp:69-78,236-246).  This
-  // runtime takes 0, 1, leaky ReLU (2, one parameter) and clip (3, two parameters);
+  // runtime takes 0, 1, 4, leaky ReLU (2, one parameter) and clip (3, two parameters);
   // everything else is rejected.
   const int64_t type = l.params.get_int(id_type, 0);
   const std::vector<float>* ap = l.params.get_float_array(id_params);
@@ -274,6 +276,10 @@ bool EngineImpl::decode_activation(const LayerDef& l, int id_type, int id_params
     n->act = ACT_CLIP;
     n->act_a = (*ap)[0];
     n->act_b = (*ap)[1];
+    return true;
+  }
+  if (type == 4 && n->term == 0) {
+    n->act = ACT_SIGMOID;
     return true;
   }
   return fail(err, "layer " + l.name + ": activation_type " + std::to_string(type) +
@@ -669,6 +675,159 @@ bool EngineImpl::import_layers(std::string* err) {
       to.name = keep;
       to.alias = -1;
       to.is_input = false;
+      nodes_.push_back(std::move(n));
+    } else if (t == "Sigmoid" || t == "Swish" || t == "TanH" || t == "HardSigmoid" || t == "HardSwish" ||
+               t == "Dropout") {
+      if (l.bottoms.size() != 1 || l.tops.size() != 1) return fail(err, where + "expects one input and one output");
+      const int in = by_name_.at(l.bottoms[0]);
+      const Tensor ti = tensors_[resolve(in)];
+      if (ti.i8) return fail(err, where + "supports one f32 tensor only");
+      const bool hard = t == "HardSigmoid" || t == "HardSwish";
+      const int max_id = hard ? 1 : (t == "Dropout" ? 0 : -1);
+      // validate_param_ids (NCNNImporter.cpp:271-282): ids 30 and 31 are always allowed
+      for (const auto& entry : l.params.entries())
+        if ((entry.first > max_id || entry.first < 0) && entry.first != 30 && entry.first != 31)
+          return fail(err, where + "unsupported parameter id " + std::to_string(entry.first));
+      Node n;
+      n.kind = N_UNARY;
+      n.name = l.name;
+      n.type = t;
+      n.un.op = UN_ACT;
+      n.un.inner = 1;
+      n.un.channels = 1;
+      if (hard) {
+        // ImportOps.cpp:120-157: alpha (default 0.2, must be positive), beta (default 0.5)
+        n.un.act = t == "HardSwish" ? ACT_HARDSWISH : ACT_HARDSIGMOID;
+        n.un.act_a = l.params.get_float(0, 0.2f);
+        n.un.act_b = l.params.get_float(1, 0.5f);
+        if (!(n.un.act_a > 0.0f)) return fail(err, where + "alpha must be positive");
+      } else if (t == "Dropout") {
+        // ImportActivation.cpp:617-646, ConvertDropout (NCNNToTosa.cpp:2047-2070): x * scale, identity for 1
+        n.un.act = ACT_SCALE;
+        n.un.act_a = l.params.get_float(0, 1.0f);
+      } else {
+        n.un.act = t == "Sigmoid" ? ACT_SIGMOID : (t == "Swish" ? ACT_SWISH : ACT_TANH);
+      }
+      if (n.un.act == ACT_SCALE && n.un.act_a == 1.0f) {
+        const int id = new_tensor(l.tops[0]);
+        tensors_[id] = tensors_[resolve(in)];
+        tensors_[id].name = l.tops[0];
+        tensors_[id].alias = resolve(in);
+        tensors_[id].is_input = false;
+      } else {
+        n.in = {in};
+        n.out = new_tensor(l.tops[0]);
+        Tensor& to = tensors_[n.out];
+        const std::string keep = to.name;
+        to = ti;
+        to.name = keep;
+        to.alias = -1;
+        to.is_input = false;
+        nodes_.push_back(std::move(n));
+      }
+    } else if (t == "Softmax") {
+      // ImportActivation.cpp:648-695: axis (default 0) over the logical [c,h,w] / [h,w] / [w] dims,
+      // negative counts from the end; anything but axis 0 needs fixbug0 = 1; rank 1 forces axis 0
+      if (l.bottoms.size() != 1 || l.tops.size() != 1) return fail(err, where + "expects one input and one output");
+      const int in = by_name_.at(l.bottoms[0]);
+      const Tensor ti = tensors_[resolve(in)];
+      if (ti.i8) return fail(err, where + "supports one f32 tensor only");
+      int64_t axis = l.params.get_int(0, 0);
+      const int64_t fixbug = l.params.get_int(1, 0);
+      if (fixbug != 0 && fixbug != 1) return fail(err, where + "fixbug0 must be 0 or 1");
+      if (fixbug == 0 && axis != 0) return fail(err, where + "legacy Softmax only supports axis 0 unless fixbug0 is 1");
+      if (ti.rank == 1) axis = 0;
+      if (axis < 0) axis += ti.rank;
+      if (axis < 0 || axis >= ti.rank) return fail(err, where + "axis is out of range");
+      Node n;
+      n.kind = N_SOFTMAX;
+      n.name = l.name;
+      n.type = t;
+      // storage order: rank 3 [h][w][c]; logical axis 0 = c, 1 = h, 2 = w
+      SoftmaxParams& sp = n.softmax;
+      sp.image_elems = ti.logical();
+      if (ti.rank == 3) {
+        if (axis == 0) { sp.len = ti.c; sp.inner = 1; }
+        else if (axis == 1) { sp.len = ti.h; sp.inner = ti.w * ti.c; }
+        else { sp.len = ti.w; sp.inner = ti.c; }
+      } else if (ti.rank == 2) {
+        if (axis == 0) { sp.len = ti.h; sp.inner = ti.w; }
+        else { sp.len = ti.w; sp.inner = 1; }
+      } else {
+        sp.len = ti.w;
+        sp.inner = 1;
+      }
+      sp.lines = static_cast<int>(ti.logical() / sp.len);
+      n.in = {in};
+      n.out = new_tensor(l.tops[0]);
+      Tensor& to = tensors_[n.out];
+      const std::string keep = to.name;
+      to = ti;
+      to.name = keep;
+      to.alias = -1;
+      to.is_input = false;
+      nodes_.push_back(std::move(n));
+    } else if (t == "Concat") {
+      // ImportTensor.cpp:48-96: at least two inputs, axis (default 0) over the logical dims
+      if (l.bottoms.size() < 2 || l.tops.size() != 1) return fail(err, where + "requires at least two inputs and one output");
+      const Tensor t0 = tensors_[resolve(by_name_.at(l.bottoms[0]))];
+      int64_t axis = l.params.get_int(0, 0);
+      if (axis < 0) axis += t0.rank;
+      if (axis < 0 || axis >= t0.rank) return fail(err, where + "axis is out of range");
+      Node n;
+      n.kind = N_CONCAT;
+      n.name = l.name;
+      n.type = t;
+      auto dims_of = [](const Tensor& x) {
+        std::vector<int> d;
+        if (x.rank == 3) d = {x.c, x.h, x.w};
+        else if (x.rank == 2) d = {x.h, x.w};
+        else d = {x.w};
+        return d;
+      };
+      std::vector<int> od = dims_of(t0);
+      od[axis] = 0;
+      for (const std::string& b : l.bottoms) {
+        const int id = by_name_.at(b);
+        const Tensor& tb = tensors_[resolve(id)];
+        if (tb.rank != t0.rank || tb.i8 != t0.i8) return fail(err, where + "inputs must agree in rank and element type");
+        const std::vector<int> d = dims_of(tb);
+        for (int k = 0; k < t0.rank; ++k)
+          if (k != axis && d[k] != dims_of(t0)[k]) return fail(err, where + "inputs must agree outside the concatenation axis");
+        od[axis] += d[axis];
+        n.in.push_back(id);
+      }
+      n.out = new_tensor(l.tops[0]);
+      Tensor& to = tensors_[n.out];
+      const std::string keep = to.name;
+      to = t0;
+      to.name = keep;
+      to.alias = -1;
+      to.is_input = false;
+      if (t0.rank == 3) { to.c = od[0]; to.h = od[1]; to.w = od[2]; }
+      else if (t0.rank == 2) { to.h = od[0]; to.w = od[1]; }
+      else to.w = od[0];
+      // storage order: rank 3 [h][w][c] -> concatenation axis as (outer, len, inner)
+      int offset = 0;
+      for (int id : n.in) {
+        const Tensor& tb = tensors_[resolve(id)];
+        ConcatParams cp{};
+        cp.in_image_elems = tb.logical();
+        cp.out_image_elems = to.logical();
+        if (t0.rank == 3) {
+          if (axis == 0) { cp.outer = tb.h * tb.w; cp.len_in = tb.c; cp.len_out = to.c; cp.inner = 1; }
+          else if (axis == 1) { cp.outer = 1; cp.len_in = tb.h; cp.len_out = to.h; cp.inner = tb.w * tb.c; }
+          else { cp.outer = tb.h; cp.len_in = tb.w; cp.len_out = to.w; cp.inner = tb.c; }
+        } else if (t0.rank == 2) {
+          if (axis == 0) { cp.outer = 1; cp.len_in = tb.h; cp.len_out = to.h; cp.inner = tb.w; }
+          else { cp.outer = tb.h; cp.len_in = tb.w; cp.len_out = to.w; cp.inner = 1; }
+        } else {
+          cp.outer = 1; cp.len_in = tb.w; cp.len_out = to.w; cp.inner = 1;
+        }
+        cp.offset = offset;
+        offset += cp.len_in;
+        n.concat.push_back(cp);
+      }
       nodes_.push_back(std::move(n));
     } else if (t == "Eltwise" || t == "BinaryOp") {
       Node n;
@@ -1714,6 +1873,38 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
       return launch_ok();
     };
     plan.steps.push_back(std::move(s));
+    return true;
+  }
+  if (node.kind == N_SOFTMAX) {
+    const ActRef in = ref(node.in[0], n);
+    SoftmaxParams sp = node.softmax;
+    sp.images = n;
+    const int grid = grid_for(n * sp.lines * 32);
+    s.kernel = "k_softmax";
+    s.run = [=](cudaStream_t st) {
+      k_softmax<<<grid, 256, 0, st>>>(in, out, sp);
+      return launch_ok();
+    };
+    plan.steps.push_back(std::move(s));
+    return true;
+  }
+  if (node.kind == N_CONCAT) {
+    for (size_t k = 0; k < node.in.size(); ++k) {
+      Step c = s;
+      c.name = node.name + ":" + std::to_string(k);
+      c.flops = 0;
+      c.bytes = 2.0 * bytes_of(node.in[k]);
+      const ActRef in = ref(node.in[k], n);
+      ConcatParams cp = node.concat[k];
+      cp.images = n;
+      const int grid = grid_for(n * cp.in_image_elems);
+      c.kernel = "k_concat_copy";
+      c.run = [=](cudaStream_t st) {
+        k_concat_copy<<<grid, 256, 0, st>>>(in, out, cp);
+        return launch_ok();
+      };
+      plan.steps.push_back(std::move(c));
+    }
     return true;
   }
   if (node.kind == N_RELAYOUT) {

@@ -612,6 +612,60 @@ static __global__ void k_gemm_i8_rowscale(ActRef a, ActRef out,
 }
 
 // Copy between two logical tensors whose elements correspond by logical (ncnn
+// ----------------------------------------------------------------- softmax, concat
+// Softmax along one storage axis (ConvertSoftmax, NCNNToTosa.cpp:2072-2112): per line
+// m = max, e = exp(x - m), s = sum e, out = e * (1/s).  A line is `len` elements `inner`
+// apart; line l of an image starts at (l / inner) * len * inner + l % inner.  One warp per line.
+struct SoftmaxParams {
+  long long images, image_elems;
+  int lines, len, inner;
+};
+
+static __global__ void k_softmax(ActRef in, ActRef out, SoftmaxParams p) {
+  const int lane = threadIdx.x & 31;
+  const long long warps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  const long long total = p.images * p.lines;
+  for (long long l = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5; l < total; l += warps) {
+    const long long img = l / p.lines;
+    const int line = static_cast<int>(l - img * p.lines);
+    const long long base = img * p.image_elems + static_cast<long long>(line / p.inner) * p.len * p.inner + line % p.inner;
+    float m = __int_as_float(0xff800000);  // -inf
+    for (int k = lane; k < p.len; k += 32) m = fmaxf(m, act_load(in, base + static_cast<long long>(k) * p.inner));
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float s = 0.0f;
+    for (int k = lane; k < p.len; k += 32) s = __fadd_rn(s, expf(__fadd_rn(act_load(in, base + static_cast<long long>(k) * p.inner), -m)));
+    for (int o = 16; o > 0; o >>= 1) s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, o));
+    const float r = __fdiv_rn(1.0f, s);
+    for (int k = lane; k < p.len; k += 32) {
+      const long long i = base + static_cast<long long>(k) * p.inner;
+      act_store(out, i, __fmul_rn(expf(__fadd_rn(act_load(in, i), -m)), r));
+    }
+  }
+}
+
+// One input of a Concat (ConvertConcat, NCNNToTosa.cpp:2012-2045): copies [outer][len_in][inner]
+// into [outer][len_out][inner] at position `offset` along the middle axis, per image.
+struct ConcatParams {
+  long long images, in_image_elems, out_image_elems;
+  int outer, len_in, len_out, inner, offset;
+};
+
+static __global__ void k_concat_copy(ActRef in, ActRef out, ConcatParams p) {
+  const long long per = static_cast<long long>(p.outer) * p.len_in * p.inner;
+  const long long total = p.images * per;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long img = i / per;
+    long long r = i - img * per;
+    const int in_i = static_cast<int>(r % p.inner);
+    r /= p.inner;
+    const int l = static_cast<int>(r % p.len_in);
+    const int o = static_cast<int>(r / p.len_in);
+    const long long dst = img * p.out_image_elems + (static_cast<long long>(o) * p.len_out + p.offset + l) * p.inner + in_i;
+    act_store(out, dst, act_load(in, img * p.in_image_elems + (i - img * per)));
+  }
+}
+
 // row-major [c][h][w]) index, optionally transposing a rank-2 source: serves
 // Flatten/Reshape/Squeeze/ExpandDims and rank-2 Permute.
 struct RelayoutParams {

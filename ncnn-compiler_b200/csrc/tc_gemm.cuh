@@ -37,7 +37,16 @@ enum : int { GEMM_TF32 = 0, GEMM_TF32X3 = 1, GEMM_I8 = 2, GEMM_BF16X3 = 3 };
 
 __host__ __device__ constexpr int tc_planes(int kind) { return kind == GEMM_TF32X3 || kind == GEMM_BF16X3 ? 2 : 1; }
 __host__ __device__ constexpr int tc_elem_bytes(int kind) { return kind == GEMM_I8 ? 1 : (kind == GEMM_BF16X3 ? 2 : 4); }
-enum : int { ACT_NONE = 0, ACT_RELU = 1, ACT_LEAKY = 2, ACT_CLIP = 3 };
+// ACT_SIGMOID..ACT_SCALE follow the reference's separate activation ops:
+//   SIGMOID      1/(1+exp(-clamp(x, +-88.376...)))            (ConvertSigmoid, NCNNToTosa.cpp:2991-3021)
+//   SWISH        x * 1/(1+exp(-x))                            (ConvertSwish, :3702-3720)
+//   HARDSIGMOID  clamp(x*alpha + beta, 0, 1), HARDSWISH x * that (ConvertHardActivation, :3023-3072)
+//   TANH         tanh(x)                                      (ConvertTanH, :3722-3736)
+//   SCALE        x * a                                        (ConvertDropout, :2047-2070)
+enum : int {
+  ACT_NONE = 0, ACT_RELU = 1, ACT_LEAKY = 2, ACT_CLIP = 3, ACT_SIGMOID = 4, ACT_SWISH = 5, ACT_HARDSIGMOID = 6,
+  ACT_HARDSWISH = 7, ACT_TANH = 8, ACT_SCALE = 9
+};
 // OUT_F32        plain fp32
 // OUT_F32_SPLIT  two fp32 planes: hi = value rounded to tf32, lo = value - hi
 // OUT_I8         int8 after requantisation with out_scale
@@ -125,6 +134,18 @@ __device__ __forceinline__ float apply_act(float y, int act, float a, float b) {
   if (act == ACT_RELU) return fmaxf(y, 0.0f);
   if (act == ACT_LEAKY) return y >= 0.0f ? y : __fmul_rn(y, a);
   if (act == ACT_CLIP) return fminf(fmaxf(y, a), b);
+  if (act == ACT_NONE) return y;
+  if (act == ACT_SIGMOID) {
+    const float c = fminf(fmaxf(y, -88.3762626647949f), 88.3762626647949f);
+    return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-c)));
+  }
+  if (act == ACT_SWISH) return __fmul_rn(y, __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-y))));
+  if (act == ACT_HARDSIGMOID || act == ACT_HARDSWISH) {
+    const float gate = fminf(fmaxf(__fadd_rn(__fmul_rn(y, a), b), 0.0f), 1.0f);
+    return act == ACT_HARDSWISH ? __fmul_rn(y, gate) : gate;
+  }
+  if (act == ACT_TANH) return tanhf(y);
+  if (act == ACT_SCALE) return __fmul_rn(y, a);
   return y;
 }
 
@@ -311,6 +332,9 @@ __device__ __forceinline__ void tc_epilogue_values(const uint32_t (&v)[16], cons
   } else if (act == ACT_LEAKY) {
 #pragma unroll
     for (int j = 0; j < 16; ++j) y[j] = y[j] >= 0.0f ? y[j] : __fmul_rn(y[j], act_a);
+  } else if (act != ACT_NONE) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j) y[j] = apply_act(y[j], act, act_a, act_b);
   }
 }
 

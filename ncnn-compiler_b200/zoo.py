@@ -160,6 +160,40 @@ def residual_block(prefix, seed=600, h=16, w=16, c=64, cout=96, k=3):
     return wr.save(prefix)
 
 
+def fire_classifier(prefix, seed=700, size=32, classes=10, act="ReLU"):
+    """SqueezeNet-style stand-in for the operators next to the hot path: stem convolution, two
+    fire modules (1x1 squeeze, 1x1 and 3x3 expand joined by a channel Concat), Dropout, a 1x1
+    classifier convolution, global average pooling and Softmax.  `act` names the activation
+    layer placed after every convolution (ReLU, Swish, HardSwish, Sigmoid, TanH)."""
+    net = _Net(seed)
+    wr = net.w
+
+    def activation(name, bottom, top):
+        extra = "0=0.166667 1=0.5" if act in ("HardSwish", "HardSigmoid") else ("0=0.0" if act == "ReLU" else "")
+        wr.layer(act, name, [bottom], [top], extra)
+
+    wr.layer("Input", "input", [], ["data"], f"0={size} 1={size} 2=3")
+    net.conv("conv1", "data", "c1", 3, 64, 3, 2, 1, zero_bias=False)
+    activation("act1", "c1", "a1")
+    cur, cin = "a1", 64
+    for k, (sq, ex) in enumerate([(16, 64), (32, 128)]):
+        tag = f"fire{k + 1}"
+        net.conv(f"{tag}_squeeze", cur, f"{tag}_s", cin, sq, 1, 1, 0, zero_bias=False)
+        activation(f"{tag}_sa", f"{tag}_s", f"{tag}_sq")
+        wr.layer("Split", f"{tag}_split", [f"{tag}_sq"], [f"{tag}_l", f"{tag}_r"])
+        net.conv(f"{tag}_e1", f"{tag}_l", f"{tag}_e1c", sq, ex, 1, 1, 0, zero_bias=False)
+        activation(f"{tag}_e1a", f"{tag}_e1c", f"{tag}_e1o")
+        net.conv(f"{tag}_e3", f"{tag}_r", f"{tag}_e3c", sq, ex, 3, 1, 1, zero_bias=False)
+        activation(f"{tag}_e3a", f"{tag}_e3c", f"{tag}_e3o")
+        wr.layer("Concat", f"{tag}_cat", [f"{tag}_e1o", f"{tag}_e3o"], [f"{tag}_out"], "0=0")
+        cur, cin = f"{tag}_out", 2 * ex
+    wr.layer("Dropout", "drop", [cur], ["dropped"], "0=0.5")
+    net.conv("classifier", "dropped", "logits", cin, classes, 1, 1, 0, zero_bias=False)
+    wr.layer("Pooling", "gap", ["logits"], ["pooled"], "0=1 4=1")
+    wr.layer("Softmax", "prob", ["pooled"], ["output"], "0=0 1=1")
+    return wr.save(prefix)
+
+
 def resnet18(prefix, seed=200, int8=False, size=224, classes=1000):
     """Configs 1 and 3: ResNet-18 topology, BatchNorm folded (zero bias), He-normal weights."""
     net = _Net(seed if not int8 else seed + 200, int8=int8)

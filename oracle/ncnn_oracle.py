@@ -313,6 +313,8 @@ def _act(y, act_type, act_params=None):
         return np.where(y >= 0, y, (y * slope).astype(F32)).astype(F32)
     if act_type == 3:
         return np.minimum(np.maximum(y, F32(act_params[0])), F32(act_params[1]))
+    if act_type == 4:
+        return op_sigmoid(y)
     raise ValueError(f"unsupported activation {act_type}")
 
 
@@ -537,6 +539,72 @@ def op_clip(layer: Layer, x):
     return _act(x, 3, [layer.getf(0, -np.finfo(F32).max), layer.getf(1, np.finfo(F32).max)])
 
 
+def op_sigmoid(x):
+    """ConvertSigmoid (NCNNToTosa.cpp:2991-3021): clamp to +-88.3762626647949, then
+    tosa.sigmoid = 1 / (1 + exp(-x)), all in f32."""
+    c = np.minimum(np.maximum(x.astype(F32), F32(-88.3762626647949)), F32(88.3762626647949))
+    return (F32(1) / (F32(1) + np.exp(-c, dtype=F32))).astype(F32)
+
+
+def op_swish(x):
+    """ConvertSwish (NCNNToTosa.cpp:3702-3720): x * sigmoid(x), no clamp."""
+    x = x.astype(F32)
+    with np.errstate(over="ignore"):
+        return (x * (F32(1) / (F32(1) + np.exp(-x, dtype=F32)))).astype(F32)
+
+
+def op_hard_activation(layer: Layer, x, swish):
+    """ConvertHardActivation (NCNNToTosa.cpp:3023-3072): gate = clamp(x*alpha + beta, 0, 1)
+    (separate multiply and add); HardSwish multiplies x by the gate.  Defaults alpha 0.2,
+    beta 0.5; alpha must be positive (ImportOps.cpp:120-157)."""
+    alpha, beta = F32(layer.getf(0, 0.2)), F32(layer.getf(1, 0.5))
+    if not alpha > 0:
+        raise ValueError("alpha must be positive")
+    x = x.astype(F32)
+    gate = np.minimum(np.maximum(((x * alpha).astype(F32) + beta).astype(F32), F32(0)), F32(1))
+    return (x * gate).astype(F32) if swish else gate
+
+
+def op_dropout(layer: Layer, x):
+    """ConvertDropout (NCNNToTosa.cpp:2047-2070): identity for scale 1, else x * scale."""
+    scale = F32(layer.getf(0, 1.0))
+    return x if scale == 1 else (x.astype(F32) * scale).astype(F32)
+
+
+def _storage_axis(rank, axis):
+    """Logical ncnn axis ([c,h,w] / [h,w] / [w], negative from the end) -> axis of the
+    array as this oracle stores it (rank 3 is HWC, like the reference's NHWC; convertAxis)."""
+    if axis < 0:
+        axis += rank
+    if not 0 <= axis < rank:
+        raise ValueError("axis is out of range")
+    return {0: 2, 1: 0, 2: 1}[axis] if rank == 3 else axis
+
+
+def op_softmax(layer: Layer, x):
+    """import_softmax (ImportActivation.cpp:648-695) + ConvertSoftmax (NCNNToTosa.cpp:2072-2112):
+    m = reduce_max, e = exp(x - m), s = reduce_sum(e), out = e * reciprocal(s)."""
+    axis, fixbug = layer.geti(0, 0), layer.geti(1, 0)
+    if fixbug not in (0, 1):
+        raise ValueError("fixbug0 must be 0 or 1")
+    if fixbug == 0 and axis != 0:
+        raise ValueError("legacy Softmax only supports axis 0 unless fixbug0 is 1")
+    if x.ndim == 1:
+        axis = 0
+    ax = _storage_axis(x.ndim, axis)
+    x = x.astype(F32)
+    e = np.exp((x - x.max(axis=ax, keepdims=True)).astype(F32), dtype=F32)
+    s = e.sum(axis=ax, keepdims=True, dtype=F32)
+    return (e * (F32(1) / s).astype(F32)).astype(F32)
+
+
+def op_concat(layer: Layer, ins):
+    """import_concat (ImportTensor.cpp:48-96) + ConvertConcat (NCNNToTosa.cpp:2012-2045)."""
+    if len(ins) < 2:
+        raise ValueError("Concat requires at least two inputs")
+    return np.ascontiguousarray(np.concatenate(ins, axis=_storage_axis(ins[0].ndim, layer.geti(0, 0))))
+
+
 def op_dequantize(acc_i32, scale, bias=None):
     """dequantizeNcnn (NCNNToTosa.cpp:411-460): float(v)*s[c] (+bias[c]); c = last axis."""
     y = (acc_i32.astype(F32) * np.asarray(scale, F32)).astype(F32)
@@ -650,6 +718,20 @@ class Model:
                 out = op_relu(l, ins[0])
             elif t == "Clip":
                 out = op_clip(l, ins[0])
+            elif t == "Sigmoid":
+                out = op_sigmoid(ins[0])
+            elif t == "Swish":
+                out = op_swish(ins[0])
+            elif t == "TanH":
+                out = np.tanh(ins[0].astype(F32), dtype=F32)  # ConvertTanH (NCNNToTosa.cpp:3722-3736)
+            elif t in ("HardSigmoid", "HardSwish"):
+                out = op_hard_activation(l, ins[0], t == "HardSwish")
+            elif t == "Dropout":
+                out = op_dropout(l, ins[0])
+            elif t == "Softmax":
+                out = op_softmax(l, ins[0])
+            elif t == "Concat":
+                out = op_concat(l, ins)
             elif t == "BatchNorm":
                 scale, offset = batchnorm_scale_offset(*l.weights, l.getf(1, 0.0))
                 if ins[0].ndim == 2:  # channel axis is dimension 0 unless the tensor is rank 3

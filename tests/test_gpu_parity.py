@@ -328,7 +328,7 @@ def test_null_pointer_and_bad_batch_status(pkg, tmp_path):
 
 
 def test_unsupported_layers_fail_loudly(pkg, tmp_path):
-    for name in ("softmax", "sigmoid", "deconvolution", "concat"):
+    for name in ("deconvolution", "gelu", "interp", "concat_rank4"):
         param = os.path.join(FIXTURES, name + ".param")
         with pytest.raises(pkg.NcnnB200Error) as e:
             pkg.Model(param, os.path.join(FIXTURES, "relu.bin"))
@@ -388,3 +388,71 @@ def test_residual_block_operand_formats(pkg, oracle, tmp_path, monkeypatch, halo
     halo_expected = (halo == "1" and c % (64 if kind == "bf16x3" else 32) == 0
                      and (h * w) / (-(-h // 16) * 16 * -(-w // 8) * 8) >= 0.70)
     assert (f"tc_conv_halo_kernel<{kind}>" in kernels) == halo_expected, kernels
+
+
+# ------------------------------------------------------------------ operators next to the hot path
+ELEMENTWISE_FIXTURES = ["sigmoid", "hard_sigmoid", "hard_swish", "dropout", "softmax", "softmax_channel",
+                        "softmax_height", "softmax_width", "softmax_negative_channel", "softmax_negative_height",
+                        "softmax_negative_width", "split_three"]
+
+
+@pytest.mark.parametrize("name", ELEMENTWISE_FIXTURES)
+def test_reference_fixture_activation_softmax(pkg, oracle, name):
+    """Sigmoid / HardSigmoid / HardSwish / Dropout / Softmax fixtures of the reference: fp32 element-wise
+    math with exp in it is held to 2e-6 relative L2 (the GPU's expf differs from libm by an ulp or two);
+    multiply/clamp-only operators and the Split+Concat chain are exact."""
+    param, bin_ = fixture(name)
+    shapes = _input_shape(pkg, param, bin_)
+    x = (np.random.default_rng(len(name)).standard_normal((5, *shapes[0])) * 3).astype(np.float32)
+    got, want = run_both(pkg, oracle, param, bin_, x, 0)
+    if name in ("hard_sigmoid", "hard_swish", "dropout", "split_three"):
+        assert np.array_equal(got, want)
+    else:
+        assert rel_l2(got, want) <= 2e-6
+        assert np.max(np.abs(got - want)) <= 1e-6
+
+
+@pytest.mark.parametrize("name", ["concat", "concat_height", "concat_width", "concat_negative_channel",
+                                  "concat_negative_height", "concat_negative_width"])
+def test_reference_fixture_concat_exact(pkg, oracle, name):
+    param, bin_ = fixture(name)
+    m = pkg.Model(param, bin_)
+    rng = np.random.default_rng(21)
+    a = rng.standard_normal((4, *m.input_shapes[0])).astype(np.float32)
+    b = rng.standard_normal((4, *m.input_shapes[1])).astype(np.float32)
+    got = m.run(a, b)[0]
+    m.close()
+    om = oracle.Model(param, bin_)
+    want = np.stack([om.run([a[i], b[i]])[0] for i in range(4)])
+    assert got.shape == want.shape
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("act", ["ReLU", "Swish", "HardSwish", "Sigmoid", "TanH"])
+def test_fire_classifier_with_fused_activations(pkg, oracle, tmp_path, act):
+    """SqueezeNet-style network: every activation is fused into the epilogue of the convolution
+    before it, Concat joins tensor-core outputs along channels, Softmax ends the graph."""
+    param, bin_ = pkg.zoo.fire_classifier(str(tmp_path / "fire"), act=act)
+    x = np.random.default_rng(31).uniform(-1, 1, (6, 3, 32, 32)).astype(np.float32)
+    for mode in (0, 2):
+        got, want = run_both(pkg, oracle, param, bin_, x, mode)
+        assert got.shape == (6, 10)
+        assert rel_l2(got, want) <= TOL[0]
+        assert np.allclose(got.sum(axis=1), 1.0, atol=1e-5)
+    m = pkg.Model(param, bin_)
+    kernels = [row["kernel"] for row in m.profile(6, repeat=1)]
+    m.close()
+    assert "k_softmax" in kernels and "k_concat_copy" in kernels
+    # the only element-wise launches left are the Dropout scale and the output edge
+    assert sum(k == "k_unary" for k in kernels) <= 2
+
+
+def test_unsupported_activation_inputs_fail_loudly(pkg, tmp_path):
+    p = tmp_path / "bad.param"
+    p.write_text("7767517\n2 2\nInput input 0 1 data 0=4 1=4 2=2\nSoftmax s 1 1 data output 0=1\n")
+    (tmp_path / "bad.bin").write_bytes(b"")
+    with pytest.raises(pkg.NcnnB200Error, match="legacy Softmax"):
+        pkg.Model(str(p), str(tmp_path / "bad.bin"))
+    p.write_text("7767517\n2 2\nInput input 0 1 data 0=4 1=4 2=2\nHardSwish s 1 1 data output 0=-1.0\n")
+    with pytest.raises(pkg.NcnnB200Error, match="alpha must be positive"):
+        pkg.Model(str(p), str(tmp_path / "bad.bin"))

@@ -256,3 +256,62 @@ def test_oracle_is_deterministic_and_thread_count_independent(oracle, pkg, tmp_p
     b = oracle.Model(param, bin_).run([x])[0]
     assert np.array_equal(a, b)
     assert a.shape == (1000,) and np.isfinite(a).all()
+
+
+# ------------------------------------------------------------------ activations, softmax, concat
+def _run_fixture(oracle, name, *inputs):
+    param, bin_ = fixture(name)
+    return oracle.Model(param, bin_).run(list(inputs))[0]
+
+
+def test_sigmoid_and_hard_activations_by_hand(oracle):
+    import math
+    x = np.array([-100.0, -3.0, -1.0, 0.0, 0.5, 2.9, 3.0, 100.0], F32)
+    full = np.zeros((2, 2, 5), F32)
+    full.reshape(-1)[:8] = x
+    got = _run_fixture(oracle, "sigmoid", full).reshape(-1)[:8]
+    # clamp to +-88.376..., then 1/(1+exp(-x)) (NCNNToTosa.cpp:3008-3015)
+    want = [1.0 / (1.0 + math.exp(-min(max(float(v), -88.3762626647949), 88.3762626647949))) for v in x]
+    assert np.allclose(got, want, rtol=2e-7, atol=1e-38)
+    assert got[3] == F32(0.5) and got[0] > 0 and got[7] == F32(1.0)
+    # hard_sigmoid / hard_swish fixtures: alpha 0.166667, beta 0.5 -> gate = clamp(x/6 + 0.5, 0, 1)
+    full = np.zeros((3, 4, 5), F32)
+    full.reshape(-1)[:8] = x
+    gate = np.clip((x * F32(0.166667)).astype(F32) + F32(0.5), 0, 1).astype(F32)
+    assert np.array_equal(_run_fixture(oracle, "hard_sigmoid", full).reshape(-1)[:8], gate)
+    assert np.array_equal(_run_fixture(oracle, "hard_swish", full).reshape(-1)[:8], (x * gate).astype(F32))
+    # dropout fixture: scale 0.375 is a plain multiplication
+    assert np.array_equal(_run_fixture(oracle, "dropout", full).reshape(-1)[:8], (x * F32(0.375)).astype(F32))
+
+
+@pytest.mark.parametrize("name,axis", [("softmax", 0), ("softmax_channel", 0), ("softmax_height", 1), ("softmax_width", 2),
+                                       ("softmax_negative_channel", 0), ("softmax_negative_height", 1),
+                                       ("softmax_negative_width", 2)])
+def test_softmax_axes(oracle, name, axis):
+    """Axis numbers are over the logical [c, h, w] dims (negative from the end); every line sums
+    to one and equals the textbook formula computed in float64."""
+    x = np.random.default_rng(11).standard_normal((3, 4, 5)).astype(F32)
+    got = _run_fixture(oracle, name, x)
+    e = np.exp(x.astype(np.float64) - x.max(axis=axis, keepdims=True))
+    want = e / e.sum(axis=axis, keepdims=True)
+    assert got.shape == x.shape
+    assert np.allclose(got, want, rtol=3e-6, atol=1e-9)
+    assert np.allclose(got.sum(axis=axis), 1.0, atol=1e-6)
+
+
+@pytest.mark.parametrize("name,axis,shapes", [("concat", 0, [(1, 3, 4), (2, 3, 4)]), ("concat_height", 1, [(2, 3, 4), (2, 2, 4)]),
+                                              ("concat_width", 2, [(2, 3, 4), (2, 3, 2)]),
+                                              ("concat_negative_channel", 0, [(1, 3, 4), (2, 3, 4)]),
+                                              ("concat_negative_height", 1, [(2, 3, 4), (2, 2, 4)]),
+                                              ("concat_negative_width", 2, [(2, 3, 4), (2, 3, 2)])])
+def test_concat_axes(oracle, name, axis, shapes):
+    rng = np.random.default_rng(12)
+    ins = [rng.standard_normal(s).astype(F32) for s in shapes]
+    got = _run_fixture(oracle, name, *ins)
+    assert np.array_equal(got, np.concatenate(ins, axis=axis))
+
+
+def test_split_three_concat_chain(oracle):
+    x = np.random.default_rng(13).standard_normal((3, 4, 5)).astype(F32)
+    got = _run_fixture(oracle, "split_three", x)
+    assert np.array_equal(got, np.concatenate([x, x, x], axis=0))
