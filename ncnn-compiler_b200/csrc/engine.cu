@@ -1251,7 +1251,7 @@ bool EngineImpl::prepare_weights(std::string* err) {
     if (!(contraction && n.impl == IMPL_TC && n.term == 0)) continue;
     const int src = resolve(n.in[0]);
     feeds_tc[src] = 1;
-    const bool can = n.kind == N_CONV ? (n.stem ? n.stem_bf16 : tensors_[src].c % 32 == 0) : (n.K % 8 == 0);
+    const bool can = n.kind == N_CONV ? (n.stem ? n.stem_bf16 : tensors_[src].c % 8 == 0) : (n.K % 8 == 0);
     if (!can) bf16_ok[src] = 0;
   }
   for (size_t i = 0; i < tensors_.size(); ++i) {

@@ -435,10 +435,17 @@ static __global__ void k_depthwise(ActRef in, ActRef out, const void* __restrict
 }
 
 // 3x3 depthwise, fp32, dilation 1.  A block stages the input patch of an 8x8 output tile
-// for 32 channels in shared memory (hi + lo planes are summed on the way in), every thread
-// issuing several independent 128-bit loads, then each thread produces two outputs from
-// shared memory.  The patch is read once per tile (1.6x halo overhead at stride 1)
-// instead of once per filter tap.
+// for 32 channels in shared memory, then each thread produces two outputs from shared memory.
+// The patch is read once per tile (1.6x halo overhead at stride 1) instead of once per filter
+// tap.  Plain fp32 inputs (the usual case: the producer is a 1x1 convolution whose result
+// feeds only this layer) are copied with cp.async, 16 bytes per request, all requests of the
+// block in flight at once and no registers held (zero fill outside the image); split formats
+// take the register path, which adds the planes on the way in.
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* src, int src_bytes) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(src_bytes) : "memory");
+}
+
 template <int STRIDE>
 static __global__ void __launch_bounds__(256) k_depthwise3x3_tile(ActRef in, ActRef out,
                                                                   const float* __restrict__ weights,
@@ -446,7 +453,9 @@ static __global__ void __launch_bounds__(256) k_depthwise3x3_tile(ActRef in, Act
   constexpr int TO = 8;                      // output tile edge
   constexpr int TI = (TO - 1) * STRIDE + 3;  // input patch edge
   constexpr int CG = 8;                      // float4 channel groups per block
+  constexpr int LOADS = (TI * TI * CG + 255) / 256;
   __shared__ float4 patch[TI * TI * CG];
+  __shared__ float4 taps[9 * CG];
   const int tiles_w = (g.OW + TO - 1) / TO;
   const int tile_y = blockIdx.x / tiles_w, tile_x = blockIdx.x - tile_y * tiles_w;
   const int cg0 = blockIdx.y * CG;
@@ -454,16 +463,30 @@ static __global__ void __launch_bounds__(256) k_depthwise3x3_tile(ActRef in, Act
   const long long img = blockIdx.z;
   const int oy0 = tile_y * TO, ox0 = tile_x * TO;
   const int iy0 = oy0 * STRIDE - g.pt, ix0 = ox0 * STRIDE - g.pl;
-  for (int idx = threadIdx.x; idx < TI * TI * CG; idx += 256) {
+  const bool plain = in.fmt == FMT_F32;
+#pragma unroll
+  for (int k = 0; k < LOADS; ++k) {
+    const int idx = threadIdx.x + k * 256;
+    if (idx >= TI * TI * CG) break;
     const int cg = idx % CG;
     const int px = idx / CG;
     const int py = px / TI;
     const int iy = iy0 + py, ix = ix0 + (px - py * TI);
-    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (cg0 + cg < cv && iy >= 0 && iy < g.H && ix >= 0 && ix < g.W)
-      v = act_load4(in, ((img * g.H + iy) * g.W + ix) * static_cast<long long>(g.C) + (cg0 + cg) * 4);
-    patch[idx] = v;
+    const bool valid = cg0 + cg < cv && iy >= 0 && iy < g.H && ix >= 0 && ix < g.W;
+    const long long off = valid ? ((img * g.H + iy) * g.W + ix) * static_cast<long long>(g.C) + (cg0 + cg) * 4 : 0;
+    if (plain) {
+      cp_async_16(&patch[idx], in.p0 + off, valid ? 16 : 0);
+    } else {
+      patch[idx] = valid ? act_load4(in, off) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
   }
+  if (threadIdx.x < 9 * CG) {
+    const int cg = threadIdx.x % CG, tap = threadIdx.x / CG;
+    taps[threadIdx.x] = cg0 + cg < cv ? __ldg(reinterpret_cast<const float4*>(weights + tap * g.C + (cg0 + cg) * 4))
+                                      : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   __syncthreads();
   for (int o = threadIdx.x; o < TO * TO * CG; o += 256) {
     const int cg = o % CG;
@@ -479,7 +502,7 @@ static __global__ void __launch_bounds__(256) k_depthwise3x3_tile(ActRef in, Act
 #pragma unroll
       for (int kw = 0; kw < 3; ++kw) {
         const float4 x = patch[((ty * STRIDE + kh) * TI + tx * STRIDE + kw) * CG + cg];
-        const float4 k = __ldg(reinterpret_cast<const float4*>(weights + (kh * 3 + kw) * g.C + c));
+        const float4 k = taps[(kh * 3 + kw) * CG + cg];
         acc.x = fmaf(x.x, k.x, acc.x);
         acc.y = fmaf(x.y, k.y, acc.y);
         acc.z = fmaf(x.z, k.z, acc.z);

@@ -239,7 +239,9 @@ int tc_row_bytes(int kind, int channels) {
     if (channels % 16 != 0) return 0;
     return channels > 64 ? 128 : (channels > 32 ? 64 : 32);
   }
-  if (kind == GEMM_BF16X3) return channels % 64 == 0 ? 128 : (channels % 32 == 0 ? 64 : 0);
+  // bf16 rows: 64 channels when they divide evenly, else 32 per block; a last block that
+  // reaches past the tensor is zero-filled by TMA (pixel rows must stay 16-byte multiples)
+  if (kind == GEMM_BF16X3) return channels % 64 == 0 ? 128 : (channels % 8 == 0 ? 64 : 0);
   if (channels % 4 != 0) return 0;
   return 128;
 }

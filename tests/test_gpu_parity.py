@@ -370,10 +370,11 @@ def test_depthwise_3x3_tile_kernel(pkg, oracle, tmp_path, c, h, w, stride, pad):
 @pytest.mark.parametrize("halo", ["0", "1"])
 @pytest.mark.parametrize("c,h,w,k,cout", [(64, 16, 16, 3, 96), (64, 30, 15, 3, 64), (128, 17, 9, 3, 256),
                                           (64, 16, 24, 5, 32), (32, 16, 16, 3, 48), (192, 14, 14, 3, 100), (48, 16, 16, 3, 40),
-                                          (96, 15, 8, 3, 160)])
+                                          (96, 15, 8, 3, 160), (20, 16, 16, 3, 40), (24, 9, 9, 3, 144)])
 def test_residual_block_operand_formats(pkg, oracle, tmp_path, monkeypatch, halo, c, h, w, k, cout):
-    """A residual block whose tensor-core operands are bf16 pairs (channels a multiple of 32; 64-byte
-    operand rows when not a multiple of 64) or fp32 hi/lo planes (otherwise), through the im2col kernel (halo=0) and the patch-resident
+    """A residual block whose tensor-core operands are bf16 pairs (channels a multiple of 8; 64-byte
+    operand rows, the last block zero-filled by TMA, when not a multiple of 64) or fp32 hi/lo planes
+    (otherwise), through the im2col kernel (halo=0) and the patch-resident
     kernel where it applies (halo=1): fused bias, residual and ReLU in every output format."""
     monkeypatch.setenv("NCNN_B200_HALO", halo)
     param, bin_ = pkg.zoo.residual_block(str(tmp_path / "rb"), seed=600 + c + h, h=h, w=w, c=c, cout=cout, k=k)
@@ -383,7 +384,7 @@ def test_residual_block_operand_formats(pkg, oracle, tmp_path, monkeypatch, halo
     m = pkg.Model(param, bin_)
     kernels = {row["kernel"] for row in m.profile(5, repeat=1)}
     m.close()
-    kind = "bf16x3" if c % 32 == 0 else "tf32x3"
+    kind = "bf16x3" if c % 8 == 0 else "tf32x3"
     assert f"tc_gemm_kernel<{kind}>" in kernels  # the 1x1 convolution at least
     halo_expected = (halo == "1" and c % (64 if kind == "bf16x3" else 32) == 0
                      and (h * w) / (-(-h // 16) * 16 * -(-w // 8) * 8) >= 0.70)
