@@ -1834,6 +1834,17 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
     PoolParams p = node.pool;
     p.images = n;
     const bool vec = p.C % 4 == 0;
+    if (p.kind == 0 && p.KH == 3 && p.KW == 3 && p.sh == 2 && p.sw == 2 && vec && !tensors_[resolve(node.in[0])].i8 &&
+        n <= 65535 && p.OH * p.OW >= 64) {
+      const dim3 grid(((p.OH + 7) / 8) * ((p.OW + 7) / 8), (p.C / 4 + 7) / 8, static_cast<unsigned>(n));
+      s.kernel = "k_maxpool3x3s2_tile";
+      s.run = [=](cudaStream_t st) {
+        k_maxpool3x3s2_tile<<<grid, 256, 0, st>>>(in, out, p);
+        return launch_ok();
+      };
+      plan.steps.push_back(std::move(s));
+      return true;
+    }
     const int grid = grid_for(n * p.OH * p.OW * (vec ? p.C / 4 : p.C));
     s.kernel = "k_pool";
     s.run = [=](cudaStream_t st) {
@@ -1943,7 +1954,15 @@ void EngineImpl::make_edge_steps(int64_t n, const std::vector<const float*>& d_i
       ep.Wp = t.Wp;
       ep.w_off = t.w_off;
       ep.quant_scale = t.input_quant_scale;
-      if (t.c <= 4 && (t.Cp == 4 || t.Cp == 16)) {
+      if (t.c <= 4 && t.Cp == 4 && t.fmt != FMT_I8 && t.w % 4 == 0 && n <= 65535 &&
+          (reinterpret_cast<uintptr_t>(src_ptr) & 15) == 0) {
+        const dim3 grid(static_cast<unsigned>(std::min(148 * 8, (t.h * t.w / 4 + 255) / 256)), static_cast<unsigned>(n));
+        s.kernel = "k_chw_to_nhwc_small_x4";
+        s.run = [=](cudaStream_t st) {
+          k_chw_to_nhwc_small_x4<<<grid, 256, 0, st>>>(src_ptr, dst, ep);
+          return launch_ok();
+        };
+      } else if (t.c <= 4 && (t.Cp == 4 || t.Cp == 16)) {
         const int grid = grid_for(n * t.h * t.w);
         s.kernel = "k_chw_to_nhwc_small";
         s.run = [=](cudaStream_t st) {

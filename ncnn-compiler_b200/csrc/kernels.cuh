@@ -179,6 +179,31 @@ static __global__ void k_nhwc_to_chw_tiled(ActRef src, float* __restrict__ dst, 
   }
 }
 
+// The same for rows whose width is a multiple of 4 and fp32 / bf16-pair storage with Cp == 4:
+// one thread per 4 consecutive pixels of a row, one 128-bit load per channel plane and 64 or
+// 32 contiguous bytes stored per output plane; grid = (row quads, images), 32-bit indices.
+static __global__ void k_chw_to_nhwc_small_x4(const float* __restrict__ src, ActRef dst, EdgeParams p) {
+  const int hw = p.H * p.W;
+  const int quads = hw / 4;
+  const long long img = blockIdx.y;
+  const float* s = src + img * static_cast<long long>(p.C) * hw;
+  for (int q = blockIdx.x * blockDim.x + threadIdx.x; q < quads; q += gridDim.x * blockDim.x) {
+    const int px = q * 4;
+    const int h = px / p.W, w = px - h * p.W;
+    float4 ch[3];
+#pragma unroll
+    for (int c = 0; c < 3; ++c)
+      ch[c] = c < p.C ? __ldg(reinterpret_cast<const float4*>(s + static_cast<long long>(c) * hw + px))
+                      : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float4 c3 = p.C > 3 ? __ldg(reinterpret_cast<const float4*>(s + 3ll * hw + px)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const long long o = ((img * p.H + h) * static_cast<long long>(p.Wp) + w + p.w_off) * 4;
+    const float v[4][4] = {{ch[0].x, ch[1].x, ch[2].x, c3.x}, {ch[0].y, ch[1].y, ch[2].y, c3.y},
+                           {ch[0].z, ch[1].z, ch[2].z, c3.z}, {ch[0].w, ch[1].w, ch[2].w, c3.w}};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) act_store4(dst, o + 4 * k, make_float4(v[k][0], v[k][1], v[k][2], v[k][3]));
+  }
+}
+
 // ----------------------------------------------------------------- element-wise
 enum : int { UN_COPY = 0, UN_ACT = 1, UN_AFFINE = 2, UN_QUANT = 3 };
 struct UnaryParams {
@@ -517,6 +542,68 @@ static __global__ void __launch_bounds__(256) k_depthwise3x3_tile(ActRef in, Act
     acc.z = conv_finish_f32(e, acc.z, res.z);
     acc.w = conv_finish_f32(e, acc.w, res.w);
     act_store4(out, off, acc);
+  }
+}
+
+// 3x3 stride-2 max pooling through the same shared-memory tile as the depthwise kernel: the
+// 17x17 input patch of an 8x8 output tile is staged once for 32 channels (cp.async for plain
+// fp32 inputs), then every thread takes the maximum over the taps that lie inside the image
+// (padding never wins, ConvertPooling, NCNNToTosa.cpp:1913-1954).
+static __global__ void __launch_bounds__(256) k_maxpool3x3s2_tile(ActRef in, ActRef out, PoolParams p) {
+  constexpr int TO = 8, TI = 17, CG = 8;
+  constexpr int LOADS = (TI * TI * CG + 255) / 256;
+  __shared__ float4 patch[TI * TI * CG];
+  const int tiles_w = (p.OW + TO - 1) / TO;
+  const int tile_y = blockIdx.x / tiles_w, tile_x = blockIdx.x - tile_y * tiles_w;
+  const int cg0 = blockIdx.y * CG;
+  const int cv = p.C / 4;
+  const long long img = blockIdx.z;
+  const int oy0 = tile_y * TO, ox0 = tile_x * TO;
+  const int iy0 = oy0 * 2 - p.pt, ix0 = ox0 * 2 - p.pl;
+  const bool plain = in.fmt == FMT_F32;
+#pragma unroll
+  for (int k = 0; k < LOADS; ++k) {
+    const int idx = threadIdx.x + k * 256;
+    if (idx >= TI * TI * CG) break;
+    const int cg = idx % CG;
+    const int px = idx / CG;
+    const int py = px / TI;
+    const int iy = iy0 + py, ix = ix0 + (px - py * TI);
+    const bool valid = cg0 + cg < cv && iy >= 0 && iy < p.H && ix >= 0 && ix < p.W;
+    const long long off = valid ? ((img * p.H + iy) * p.W + ix) * static_cast<long long>(p.C) + (cg0 + cg) * 4 : 0;
+    if (plain) {
+      cp_async_16(&patch[idx], in.p0 + off, valid ? 16 : 0);
+    } else {
+      patch[idx] = valid ? act_load4(in, off) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();
+  for (int o = threadIdx.x; o < TO * TO * CG; o += 256) {
+    const int cg = o % CG;
+    const int q = o / CG;
+    const int ty = q / TO, tx = q - ty * TO;
+    const int oy = oy0 + ty, ox = ox0 + tx;
+    if (cg0 + cg >= cv || oy >= p.OH || ox >= p.OW) continue;
+    const float ninf = __int_as_float(0xff800000);
+    float4 acc = make_float4(ninf, ninf, ninf, ninf);
+#pragma unroll
+    for (int kh = 0; kh < 3; ++kh) {
+      const int iy = oy * 2 - p.pt + kh;
+      if (iy < 0 || iy >= p.H) continue;
+#pragma unroll
+      for (int kw = 0; kw < 3; ++kw) {
+        const int ix = ox * 2 - p.pl + kw;
+        if (ix < 0 || ix >= p.W) continue;
+        const float4 x = patch[((ty * 2 + kh) * TI + tx * 2 + kw) * CG + cg];
+        acc.x = fmaxf(acc.x, x.x);
+        acc.y = fmaxf(acc.y, x.y);
+        acc.z = fmaxf(acc.z, x.z);
+        acc.w = fmaxf(acc.w, x.w);
+      }
+    }
+    act_store4(out, ((img * p.OH + oy) * p.OW + ox) * static_cast<long long>(p.C) + (cg0 + cg) * 4, acc);
   }
 }
 

@@ -457,3 +457,24 @@ def test_unsupported_activation_inputs_fail_loudly(pkg, tmp_path):
     p.write_text("7767517\n2 2\nInput input 0 1 data 0=4 1=4 2=2\nHardSwish s 1 1 data output 0=-1.0\n")
     with pytest.raises(pkg.NcnnB200Error, match="alpha must be positive"):
         pkg.Model(str(p), str(tmp_path / "bad.bin"))
+
+
+@pytest.mark.parametrize("c,h,w,pad,pad_mode", [(8, 17, 19, 1, 1), (12, 30, 16, 0, 0), (64, 33, 33, 1, 0), (4, 16, 40, 1, 1),
+                                                (36, 21, 18, 0, 1)])
+def test_maxpool_3x3_stride2_tile_kernel(pkg, oracle, tmp_path, c, h, w, pad, pad_mode):
+    """3x3 stride-2 max pooling over shapes with ragged tiles, padding and (pad_mode 0) tail windows;
+    inputs are all negative in one image so that padding can never win.  Exact."""
+    prefix = str(tmp_path / "mp")
+    with open(prefix + ".param", "w") as f:
+        f.write("7767517\n2 2\n")
+        f.write(f"Input input 0 1 data 0={w} 1={h} 2={c}\n")
+        f.write(f"Pooling pool 1 1 data output 0=0 1=3 2=2 3={pad} 5={pad_mode}\n")
+    open(prefix + ".bin", "wb").close()
+    x = np.random.default_rng(c + h).standard_normal((4, c, h, w)).astype(np.float32)
+    x[1] = -np.abs(x[1]) - 1.0
+    got, want = run_both(pkg, oracle, prefix + ".param", prefix + ".bin", x, 0)
+    assert np.array_equal(got, want)
+    m = pkg.Model(prefix + ".param", prefix + ".bin")
+    kernels = {row["kernel"] for row in m.profile(4, repeat=1)}
+    m.close()
+    assert "k_maxpool3x3s2_tile" in kernels
