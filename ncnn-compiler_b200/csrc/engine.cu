@@ -15,7 +15,7 @@
 namespace nb {
 namespace {
 
-enum NodeKind { N_CONV, N_DW, N_IP, N_GEMM, N_POOL, N_BINARY, N_UNARY, N_RELAYOUT, N_SOFTMAX, N_CONCAT };
+enum NodeKind { N_CONV, N_DW, N_IP, N_GEMM, N_POOL, N_BINARY, N_UNARY, N_RELAYOUT, N_SOFTMAX, N_CONCAT, N_REMAP, N_REDUCE };
 enum Impl { IMPL_NONE, IMPL_TC, IMPL_DIRECT };
 
 struct Tensor {
@@ -71,6 +71,10 @@ struct Node {
   RelayoutParams relayout{};
   SoftmaxParams softmax{};
   std::vector<ConcatParams> concat;  // one per input
+  RemapParams remap{};
+  ReduceParams reduce{};
+  bool broadcast = false;  // N_BINARY whose operands differ in shape
+  BroadcastParams bcast{};
   // device-side parameters
   void* d_w0 = nullptr;
   void* d_w1 = nullptr;
@@ -861,10 +865,43 @@ bool EngineImpl::import_layers(std::string* err) {
       if (!n.bin.use_scalar) {
         const int b = by_name_.at(l.bottoms[1]);
         const Tensor& tb = tensors_[resolve(b)];
-        if (tb.rank != ta.rank || tb.c != ta.c || tb.h != ta.h || tb.w != ta.w)
-          return fail(err, where + "broadcasting between different shapes is outside the supported path");
         if (ta.i8 != tb.i8 || (ta.i8 && n.bin.op != BIN_MAX))
           return fail(err, where + "int8 operands support only two-input max");
+        if (tb.rank != ta.rank || tb.c != ta.c || tb.h != ta.h || tb.w != ta.w) {
+          // computeBinaryResult (NCNNOps.cpp:1219-1244): right-aligned broadcasting of the logical dims
+          if (t == "Eltwise" || ta.i8) return fail(err, where + "operands must have the same shape");
+          auto dims3 = [](const Tensor& x, int d[3]) {
+            d[0] = x.rank == 3 ? x.c : 1;
+            d[1] = x.rank >= 2 ? x.h : 1;
+            d[2] = x.w;
+          };
+          int da[3], db[3], dout[3];
+          dims3(ta, da);
+          dims3(tb, db);
+          for (int k = 0; k < 3; ++k) {
+            if (da[k] == 1) dout[k] = db[k];
+            else if (db[k] == 1 || db[k] == da[k]) dout[k] = da[k];
+            else return fail(err, where + "BinaryOp input shapes are not broadcastable");
+          }
+          n.broadcast = true;
+          BroadcastParams& bp = n.bcast;
+          bp.rank = std::max(ta.rank, tb.rank);
+          bp.C = dout[0];
+          bp.H = dout[1];
+          bp.W = dout[2];
+          auto strides = [](const Tensor& x, const int d[3], int* sc, int* sh, int* sw) {
+            // storage: rank 3 [h][w][c], rank 2 [h][w], rank 1 [w]
+            const int c_stride = 1, w_stride = x.rank == 3 ? x.c : 1, h_stride = x.rank == 3 ? x.w * x.c : x.w;
+            *sc = (x.rank == 3 && d[0] != 1) ? c_stride : 0;
+            *sh = (x.rank >= 2 && d[1] != 1) ? h_stride : 0;
+            *sw = d[2] != 1 ? w_stride : 0;
+          };
+          strides(ta, da, &bp.a_sc, &bp.a_sh, &bp.a_sw);
+          strides(tb, db, &bp.b_sc, &bp.b_sh, &bp.b_sw);
+          bp.a_image = ta.logical();
+          bp.b_image = tb.logical();
+          bp.o_image = static_cast<long long>(dout[0]) * dout[1] * dout[2];
+        }
         n.in.push_back(b);
       } else if (ta.i8) {
         return fail(err, where + "int8 operands support only two-input max");
@@ -876,6 +913,222 @@ bool EngineImpl::import_layers(std::string* err) {
       to.name = keep;
       to.alias = -1;
       to.is_input = false;
+      if (n.broadcast) {
+        to.rank = n.bcast.rank;
+        to.c = n.bcast.C;
+        to.h = n.bcast.H;
+        to.w = n.bcast.W;
+        to.Cp = to.rank == 3 ? to.c : 1;
+        to.Wp = to.w;
+      }
+      nodes_.push_back(std::move(n));
+    } else if (t == "UnaryOp") {
+      // import_unary_op (ImportOps.cpp:407-433): the square operation only
+      if (l.bottoms.size() != 1 || l.tops.size() != 1) return fail(err, where + "expects one input and one output");
+      const int in = by_name_.at(l.bottoms[0]);
+      const Tensor ti = tensors_[resolve(in)];
+      if (ti.i8 || l.params.get_int(0, 0) != 4) return fail(err, where + "UnaryOp supports the square operation (op_type=4) on f32 only");
+      Node n;
+      n.kind = N_UNARY;
+      n.name = l.name;
+      n.type = t;
+      n.un.op = UN_ACT;
+      n.un.act = ACT_SQUARE;
+      n.in = {in};
+      n.out = new_tensor(l.tops[0]);
+      Tensor& to = tensors_[n.out];
+      const std::string keep = to.name;
+      to = ti;
+      to.name = keep;
+      to.alias = -1;
+      to.is_input = false;
+      nodes_.push_back(std::move(n));
+    } else if (t == "Slice") {
+      // import_slice (ImportTensor.cpp:136-193) + inferSliceResults (NCNNOps.cpp:1538-1591)
+      if (l.bottoms.size() != 1 || l.tops.size() < 2) return fail(err, where + "requires one input and at least two outputs");
+      const int in = by_name_.at(l.bottoms[0]);
+      const Tensor ti = tensors_[resolve(in)];
+      if (ti.i8) return fail(err, where + "Slice input must be f32");
+      const std::vector<int64_t>* sizes = l.params.get_int_array(0);
+      if (sizes == nullptr) return fail(err, where + "parameter 0 (slices) must be an integer array");
+      if (sizes->size() != l.tops.size()) return fail(err, where + "slice count must match output count");
+      int64_t axis = l.params.get_int(1, 0);
+      if (axis < 0) axis += ti.rank;
+      if (axis < 0 || axis >= ti.rank) return fail(err, where + "Slice axis is outside input rank");
+      std::vector<int> dims;
+      if (ti.rank == 3) dims = {ti.c, ti.h, ti.w};
+      else if (ti.rank == 2) dims = {ti.h, ti.w};
+      else dims = {ti.w};
+      const int extent = dims[axis];
+      int consumed = 0;
+      for (size_t k = 0; k < sizes->size(); ++k) {
+        int64_t size = (*sizes)[k];
+        if (size == -233) size = (extent - consumed) / static_cast<int64_t>(sizes->size() - k);
+        if (size <= 0 || size > extent - consumed) return fail(err, where + "Slice sizes must be positive and fit input");
+        Node n;
+        n.kind = N_CONCAT;
+        n.name = l.name + ":" + std::to_string(k);
+        n.type = t;
+        n.in = {in};
+        n.out = new_tensor(l.tops[k]);
+        Tensor& to = tensors_[n.out];
+        const std::string keep = to.name;
+        to = ti;
+        to.name = keep;
+        to.alias = -1;
+        to.is_input = false;
+        std::vector<int> od = dims;
+        od[axis] = static_cast<int>(size);
+        if (ti.rank == 3) { to.c = od[0]; to.h = od[1]; to.w = od[2]; to.Cp = to.c; to.Wp = to.w; }
+        else if (ti.rank == 2) { to.h = od[0]; to.w = od[1]; to.Wp = to.w; }
+        else { to.w = od[0]; to.Wp = to.w; }
+        ConcatParams cp{};
+        cp.slice = 1;
+        cp.in_image_elems = to.logical();
+        cp.out_image_elems = ti.logical();
+        if (ti.rank == 3) {
+          if (axis == 0) { cp.outer = ti.h * ti.w; cp.len_in = to.c; cp.len_out = ti.c; cp.inner = 1; }
+          else if (axis == 1) { cp.outer = 1; cp.len_in = to.h; cp.len_out = ti.h; cp.inner = ti.w * ti.c; }
+          else { cp.outer = ti.h; cp.len_in = to.w; cp.len_out = ti.w; cp.inner = ti.c; }
+        } else if (ti.rank == 2) {
+          if (axis == 0) { cp.outer = 1; cp.len_in = to.h; cp.len_out = ti.h; cp.inner = ti.w; }
+          else { cp.outer = ti.h; cp.len_in = to.w; cp.len_out = ti.w; cp.inner = 1; }
+        } else {
+          cp.outer = 1; cp.len_in = to.w; cp.len_out = ti.w; cp.inner = 1;
+        }
+        cp.offset = consumed;
+        consumed += static_cast<int>(size);
+        n.concat.push_back(cp);
+        nodes_.push_back(std::move(n));
+      }
+      if (consumed != extent) return fail(err, where + "Slice sizes must consume the entire axis");
+    } else if (t == "Reduction") {
+      // import_reduction (ImportTensor.cpp:195-255) + computeReductionResult (NCNNOps.cpp:1593-1640):
+      // f32 mean only; explicit axes need fixbug0 = 1
+      if (l.bottoms.size() != 1 || l.tops.size() != 1) return fail(err, where + "expects one input and one output");
+      const int in = by_name_.at(l.bottoms[0]);
+      const Tensor ti = tensors_[resolve(in)];
+      const int64_t reduce_all = l.params.get_int(1, 1), keep = l.params.get_int(4, 0);
+      const std::vector<int64_t>* axes = l.params.get_int_array(3);
+      if (ti.i8 || l.params.get_int(0, 0) != 3 || (reduce_all != 0 && reduce_all != 1) || (keep != 0 && keep != 1) ||
+          (l.params.has(3) && axes == nullptr))
+        return fail(err, where + "Reduction supports static FP32 mean with integer axes only");
+      if (!reduce_all && (axes == nullptr || axes->empty() || l.params.get_int(5, 0) != 1))
+        return fail(err, where + "explicit Reduction axes require fixbug0=1");
+      if (ti.rank != 3) return fail(err, where + "Reduction of tensors that are not rank 3 is outside the supported path");
+      bool red[3] = {reduce_all != 0, reduce_all != 0, reduce_all != 0};
+      if (!reduce_all) {
+        for (int64_t a : *axes) {
+          if (a < 0) a += 3;
+          if (a < 0 || a > 2 || red[a]) return fail(err, where + "Reduction axes must be unique and in range");
+          red[a] = true;
+        }
+      }
+      std::vector<int> kept;
+      const int dims[3] = {ti.c, ti.h, ti.w};
+      long long count = 1;
+      for (int a = 0; a < 3; ++a) {
+        if (red[a]) count *= dims[a];
+        if (!red[a]) kept.push_back(dims[a]);
+        else if (keep) kept.push_back(1);
+      }
+      if (kept.empty()) kept.push_back(1);
+      // Without keepdims, dropping only h or only w leaves a rank-2 result whose element order the
+      // reference takes from a plain reshape of its channel-last buffer; that case stays out.
+      if (!keep && kept.size() == 2 && !red[0]) return fail(err, where + "this combination of Reduction axes is outside the supported path");
+      Node n;
+      n.kind = N_REDUCE;
+      n.name = l.name;
+      n.type = t;
+      n.reduce.C = ti.c;
+      n.reduce.H = ti.h;
+      n.reduce.W = ti.w;
+      n.reduce.red_c = red[0];
+      n.reduce.red_h = red[1];
+      n.reduce.red_w = red[2];
+      n.reduce.factor = static_cast<float>(static_cast<double>(l.params.get_float(2, 1.0f)) / static_cast<double>(count));
+      n.in = {in};
+      n.out = new_tensor(l.tops[0]);
+      Tensor& to = tensors_[n.out];
+      const std::string keep_name = to.name;
+      to = ti;
+      to.name = keep_name;
+      to.alias = -1;
+      to.is_input = false;
+      to.rank = static_cast<int>(kept.size());
+      to.w = kept.back();
+      to.h = to.rank >= 2 ? kept[to.rank - 2] : 1;
+      to.c = to.rank == 3 ? kept[0] : 1;
+      to.Cp = to.rank == 3 ? to.c : 1;
+      to.Wp = to.w;
+      nodes_.push_back(std::move(n));
+    } else if (t == "ShuffleChannel" || t == "Padding" || t == "Interp") {
+      if (l.bottoms.size() != 1 || l.tops.size() != 1)
+        return fail(err, where + (t == "Interp" ? "a dynamic target size is outside the supported path" : "expects one input and one output"));
+      const int in = by_name_.at(l.bottoms[0]);
+      const Tensor ti = tensors_[resolve(in)];
+      if (ti.i8 || ti.rank != 3) return fail(err, where + "requires a rank-3 f32 input");
+      Node n;
+      n.kind = N_REMAP;
+      n.name = l.name;
+      n.type = t;
+      RemapParams& r = n.remap;
+      r.C = ti.c;
+      r.H = ti.h;
+      r.W = ti.w;
+      r.OH = ti.h;
+      r.OW = ti.w;
+      if (t == "ShuffleChannel") {
+        // import_shuffle_channel (ImportTensor.cpp:98-134), ConvertShuffleChannel (NCNNToTosa.cpp:5394-5456)
+        const int64_t group = l.params.get_int(0, 1), reverse = l.params.get_int(1, 0);
+        if ((reverse != 0 && reverse != 1) || group <= 0) return fail(err, where + "group must be positive and reverse 0 or 1");
+        if (ti.c % group != 0) return fail(err, where + "group must divide channel count");
+        r.mode = REMAP_SHUFFLE;
+        r.group = static_cast<int>(reverse ? ti.c / group : group);
+      } else if (t == "Padding") {
+        // import_padding (ImportDetection.cpp:31-112): constant spatial padding only
+        const int64_t top = l.params.get_int(0, 0), bottom = l.params.get_int(1, 0), left = l.params.get_int(2, 0),
+                      right = l.params.get_int(3, 0);
+        if (l.params.get_int(4, 0) != 0 || l.params.get_int(6, 0) != 0 || l.params.get_int(7, 0) != 0 ||
+            l.params.get_int(8, 0) != 0)
+          return fail(err, where + "Padding only supports constant spatial padding without per-channel data");
+        if (top < 0 || bottom < 0 || left < 0 || right < 0) return fail(err, where + "padding must be non-negative");
+        r.mode = REMAP_PAD;
+        r.top = static_cast<int>(top);
+        r.left = static_cast<int>(left);
+        r.value = l.params.get_float(5, 0.0f);
+        r.OH = static_cast<int>(ti.h + top + bottom);
+        r.OW = static_cast<int>(ti.w + left + right);
+      } else {
+        // import_interp (ImportDetection.cpp:114-205)
+        const int64_t type = l.params.get_int(0, 0), oh = l.params.get_int(3, 0), ow = l.params.get_int(4, 0),
+                      align = l.params.get_int(6, 0);
+        const float hs = l.params.get_float(1, 1.0f), ws = l.params.get_float(2, 1.0f);
+        if ((type != 1 && type != 2) || (type == 1 && align != 0) || (align != 0 && align != 1) ||
+            l.params.get_int(5, 0) != 0 || l.params.has(9) || !std::isfinite(hs) || !std::isfinite(ws) || hs < 1.0f ||
+            ws < 1.0f || std::trunc(hs) != hs || std::trunc(ws) != ws || oh < 0 || ow < 0)
+          return fail(err, where + "Interp supports nearest or bilinear resize with valid integer scale and alignment only");
+        r.mode = type == 1 ? REMAP_NEAREST : REMAP_BILINEAR;
+        r.scale_h = static_cast<int>(hs);
+        r.scale_w = static_cast<int>(ws);
+        r.explicit_h = oh != 0;
+        r.explicit_w = ow != 0;
+        r.align_corner = static_cast<int>(align);
+        r.OH = static_cast<int>(oh != 0 ? oh : ti.h * r.scale_h);
+        r.OW = static_cast<int>(ow != 0 ? ow : ti.w * r.scale_w);
+        if (type == 2 && (ti.h < 2 || ti.w < 2)) return fail(err, where + "bilinear resize needs at least two rows and columns");
+      }
+      n.in = {in};
+      n.out = new_tensor(l.tops[0]);
+      Tensor& to = tensors_[n.out];
+      const std::string keep = to.name;
+      to = ti;
+      to.name = keep;
+      to.alias = -1;
+      to.is_input = false;
+      to.h = r.OH;
+      to.w = r.OW;
+      to.Wp = to.w;
       nodes_.push_back(std::move(n));
     } else if (t == "BatchNorm") {
       const int in = by_name_.at(l.bottoms[0]);
@@ -1121,7 +1374,7 @@ void EngineImpl::fuse() {
   // operand exists.
   for (size_t k = 0; k < nodes_.size(); ++k) {
     Node& b = nodes_[k];
-    if (b.kind != N_BINARY || b.bin.op != BIN_ADD || b.bin.use_scalar || b.bin.scale_a || b.bin.scale_b) continue;
+    if (b.kind != N_BINARY || b.broadcast || b.bin.op != BIN_ADD || b.bin.use_scalar || b.bin.scale_a || b.bin.scale_b) continue;
     if (tensors_[resolve(b.in[0])].i8) continue;
     const std::vector<int> uses = count_uses();
     int best = -1, other = -1;
@@ -1850,6 +2103,47 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
     s.run = [=](cudaStream_t st) {
       if (vec) k_pool<4><<<grid, 256, 0, st>>>(in, out, p);
       else k_pool<1><<<grid, 256, 0, st>>>(in, out, p);
+      return launch_ok();
+    };
+    plan.steps.push_back(std::move(s));
+    return true;
+  }
+  if (node.kind == N_REDUCE) {
+    const ActRef in = ref(node.in[0], n);
+    ReduceParams rp = node.reduce;
+    rp.images = n;
+    const int grid = grid_for(to.logical() * n);
+    s.kernel = "k_reduce_mean";
+    s.run = [=](cudaStream_t st) {
+      k_reduce_mean<<<grid, 256, 0, st>>>(in, out, rp);
+      return launch_ok();
+    };
+    plan.steps.push_back(std::move(s));
+    return true;
+  }
+  if (node.kind == N_REMAP) {
+    const ActRef in = ref(node.in[0], n);
+    RemapParams rp = node.remap;
+    rp.images = n;
+    const int grid = grid_for(to.logical() * n);
+    s.kernel = "k_remap";
+    s.run = [=](cudaStream_t st) {
+      k_remap<<<grid, 256, 0, st>>>(in, out, rp);
+      return launch_ok();
+    };
+    plan.steps.push_back(std::move(s));
+    return true;
+  }
+  if (node.kind == N_BINARY && node.broadcast) {
+    const ActRef a = ref(node.in[0], n);
+    const ActRef b = ref(node.in[1], n);
+    BroadcastParams bp = node.bcast;
+    bp.images = n;
+    bp.op = node.bin;
+    const int grid = grid_for(bp.o_image * n);
+    s.kernel = "k_binary_broadcast";
+    s.run = [=](cudaStream_t st) {
+      k_binary_broadcast<<<grid, 256, 0, st>>>(a, b, out, bp);
       return launch_ok();
     };
     plan.steps.push_back(std::move(s));

@@ -758,6 +758,8 @@ static __global__ void k_softmax(ActRef in, ActRef out, SoftmaxParams p) {
 struct ConcatParams {
   long long images, in_image_elems, out_image_elems;
   int outer, len_in, len_out, inner, offset;
+  int slice;  // 1: the other direction (ConvertSlice, NCNNToTosa.cpp:5458-5544): `in` is the long
+              // tensor [outer][len_out][inner], `out` receives [outer][len_in][inner] from `offset`
 };
 
 static __global__ void k_concat_copy(ActRef in, ActRef out, ConcatParams p) {
@@ -771,8 +773,10 @@ static __global__ void k_concat_copy(ActRef in, ActRef out, ConcatParams p) {
     r /= p.inner;
     const int l = static_cast<int>(r % p.len_in);
     const int o = static_cast<int>(r / p.len_in);
-    const long long dst = img * p.out_image_elems + (static_cast<long long>(o) * p.len_out + p.offset + l) * p.inner + in_i;
-    act_store(out, dst, act_load(in, img * p.in_image_elems + (i - img * per)));
+    const long long wide = img * p.out_image_elems + (static_cast<long long>(o) * p.len_out + p.offset + l) * p.inner + in_i;
+    const long long narrow = img * p.in_image_elems + (i - img * per);
+    if (p.slice) act_store(out, narrow, act_load(in, wide));
+    else act_store(out, wide, act_load(in, narrow));
   }
 }
 
@@ -812,6 +816,148 @@ static __global__ void k_relayout(ActRef in, ActRef out, RelayoutParams p) {
     const long long so = img * p.count + storage_offset(p.src_rank, p.sc, p.sh, p.sw, src_l);
     const long long dof = img * p.count + storage_offset(p.dst_rank, p.dc, p.dh, p.dw, l);
     act_store(out, dof, act_load(in, so));
+  }
+}
+
+// ----------------------------------------------------------------- broadcast, remap
+// BinaryOp with numpy-style broadcasting over the logical [c, h, w] dims (computeBinaryResult,
+// NCNNOps.cpp:1181-1245; ConvertBinary, NCNNToTosa.cpp:5111-5223).  Every operand is addressed as
+// c*sc + h*sh + w*sw in its own storage, with a zero stride where it is broadcast.
+struct BroadcastParams {
+  long long images;
+  int rank, C, H, W;                  // output logical dims (missing leading dims are 1)
+  long long a_image, b_image, o_image;  // elements per image
+  int a_sc, a_sh, a_sw, b_sc, b_sh, b_sw;
+  BinaryParams op;
+};
+
+static __global__ void k_binary_broadcast(ActRef a, ActRef b, ActRef out, BroadcastParams p) {
+  const long long total = p.images * p.o_image;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long img = i / p.o_image;
+    long long r = i - img * p.o_image;
+    int c = 0, h = 0, w = 0;
+    if (p.rank == 3) {  // storage [h][w][c]
+      c = static_cast<int>(r % p.C);
+      r /= p.C;
+      w = static_cast<int>(r % p.W);
+      h = static_cast<int>(r / p.W);
+    } else {            // [h][w] or [w]
+      w = static_cast<int>(r % p.W);
+      h = static_cast<int>(r / p.W);
+    }
+    const float x = act_load(a, img * p.a_image + static_cast<long long>(c) * p.a_sc + static_cast<long long>(h) * p.a_sh + static_cast<long long>(w) * p.a_sw);
+    const float y = act_load(b, img * p.b_image + static_cast<long long>(c) * p.b_sc + static_cast<long long>(h) * p.b_sh + static_cast<long long>(w) * p.b_sw);
+    act_store(out, i, binary_apply(p.op, x, y));
+  }
+}
+
+// Index remapping of rank-3 tensors: out(h, w, c) takes one input element (or a constant, or a
+// bilinear blend of four).  REMAP_PAD: constant padding (ConvertPadding, NCNNToTosa.cpp:2114-2250);
+// REMAP_SHUFFLE: channel shuffle, [group][C/group] -> [C/group][group] (ConvertShuffleChannel,
+// :5394-5456); REMAP_NEAREST / REMAP_BILINEAR: Interp (ConvertInterp, :2252-2572).
+enum : int { REMAP_PAD = 0, REMAP_SHUFFLE = 1, REMAP_NEAREST = 2, REMAP_BILINEAR = 3 };
+struct RemapParams {
+  long long images;
+  int mode;
+  int C, H, W, OH, OW;      // input and output extents (channels unchanged)
+  int top, left;            // REMAP_PAD
+  float value;
+  int group;                // REMAP_SHUFFLE
+  int scale_h, scale_w;     // REMAP_NEAREST without an explicit size
+  int explicit_h, explicit_w;
+  int align_corner;         // REMAP_BILINEAR
+};
+
+// source coordinate of bilinear resize exactly as the reference spells it in f32
+__device__ __forceinline__ void bilinear_coordinate(int index, int in, int out, int align, int* base, float* frac) {
+  const float in_f = static_cast<float>(in), out_f = static_cast<float>(out), idx = static_cast<float>(index);
+  const float in_max = __fadd_rn(in_f, -1.0f);
+  float src;
+  if (align) src = __fdiv_rn(__fmul_rn(idx, in_max), __fadd_rn(out_f, -1.0f));
+  else src = __fadd_rn(__fdiv_rn(__fmul_rn(__fadd_rn(idx, 0.5f), in_f), out_f), -0.5f);
+  src = fminf(fmaxf(src, 0.0f), in_max);
+  int b = static_cast<int>(floorf(src));
+  b = min(b, in - 2);
+  *base = b;
+  *frac = __fadd_rn(src, -static_cast<float>(b));
+}
+
+static __global__ void k_remap(ActRef in, ActRef out, RemapParams p) {
+  const long long in_image = static_cast<long long>(p.H) * p.W * p.C;
+  const long long out_image = static_cast<long long>(p.OH) * p.OW * p.C;
+  const long long total = p.images * out_image;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long img = i / out_image;
+    long long r = i - img * out_image;
+    const int c = static_cast<int>(r % p.C);
+    r /= p.C;
+    const int w = static_cast<int>(r % p.OW);
+    const int h = static_cast<int>(r / p.OW);
+    const long long base = img * in_image;
+    auto at = [&](int y, int x, int ch) { return act_load(in, base + (static_cast<long long>(y) * p.W + x) * p.C + ch); };
+    float v;
+    if (p.mode == REMAP_PAD) {
+      const int y = h - p.top, x = w - p.left;
+      v = (y >= 0 && y < p.H && x >= 0 && x < p.W) ? at(y, x, c) : p.value;
+    } else if (p.mode == REMAP_SHUFFLE) {
+      v = at(h, w, (c % p.group) * (p.C / p.group) + c / p.group);
+    } else if (p.mode == REMAP_NEAREST) {
+      const int y = p.explicit_h ? static_cast<int>((static_cast<long long>(h) * p.H) / p.OH) : h / p.scale_h;
+      const int x = p.explicit_w ? static_cast<int>((static_cast<long long>(w) * p.W) / p.OW) : w / p.scale_w;
+      v = at(y, x, c);
+    } else {
+      int y0, x0;
+      float fy, fx;
+      bilinear_coordinate(h, p.H, p.OH, p.align_corner, &y0, &fy);
+      bilinear_coordinate(w, p.W, p.OW, p.align_corner, &x0, &fx);
+      const float gx = __fadd_rn(1.0f, -fx), gy = __fadd_rn(1.0f, -fy);
+      const float top = __fadd_rn(__fmul_rn(at(y0, x0, c), gx), __fmul_rn(at(y0, x0 + 1, c), fx));
+      const float bottom = __fadd_rn(__fmul_rn(at(y0 + 1, x0, c), gx), __fmul_rn(at(y0 + 1, x0 + 1, c), fx));
+      v = __fadd_rn(__fmul_rn(top, gy), __fmul_rn(bottom, fy));
+    }
+    act_store(out, i, v);
+  }
+}
+
+// Mean over a set of logical axes of a rank-3 tensor (ConvertReduction, NCNNToTosa.cpp:5546-5682):
+// reduce_sum axis by axis in storage order (h, then w, then c), then one multiplication by
+// coeff / count.  One thread per output element; `red_*` is 1 where the axis is reduced.
+struct ReduceParams {
+  long long images;
+  int C, H, W;
+  int red_c, red_h, red_w;
+  float factor;
+};
+
+static __global__ void k_reduce_mean(ActRef in, ActRef out, ReduceParams p) {
+  const int oc = p.red_c ? 1 : p.C, oh = p.red_h ? 1 : p.H, ow = p.red_w ? 1 : p.W;
+  const long long per = static_cast<long long>(oc) * oh * ow;
+  const long long in_image = static_cast<long long>(p.C) * p.H * p.W;
+  const long long total = p.images * per;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long img = i / per;
+    long long r = i - img * per;  // output storage order [h][w][c] over the kept extents
+    const int c0 = static_cast<int>(r % oc);
+    r /= oc;
+    const int w0 = static_cast<int>(r % ow);
+    const int h0 = static_cast<int>(r / ow);
+    const int nc = p.red_c ? p.C : 1, nh = p.red_h ? p.H : 1, nw = p.red_w ? p.W : 1;
+    float sc = 0.0f;
+    for (int c = 0; c < nc; ++c) {
+      float sw = 0.0f;
+      for (int w = 0; w < nw; ++w) {
+        float sh = 0.0f;
+        for (int h = 0; h < nh; ++h)
+          sh = __fadd_rn(sh, act_load(in, img * in_image + (static_cast<long long>(h0 + h) * p.W + (w0 + w)) * p.C + c0 + c));
+        sw = __fadd_rn(sw, sh);
+      }
+      sc = __fadd_rn(sc, sw);
+    }
+    act_store(out, i, __fmul_rn(sc, p.factor));
   }
 }
 

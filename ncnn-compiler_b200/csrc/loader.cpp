@@ -45,6 +45,11 @@ const std::vector<float>* ParamDict::get_float_array(int id) const {
   return (v != nullptr && v->kind == ParamValue::kFloatArray) ? &v->fa : nullptr;
 }
 
+const std::vector<int64_t>* ParamDict::get_int_array(int id) const {
+  const ParamValue* v = find(id);
+  return (v != nullptr && v->kind == ParamValue::kIntArray) ? &v->ia : nullptr;
+}
+
 // ------------------------------------------------------------------ value parsing
 namespace {
 

@@ -34,6 +34,7 @@ class ParamDict {
   int64_t get_int(int id, int64_t dflt = 0) const;
   float get_float(int id, float dflt = 0.0f) const;
   const std::vector<float>* get_float_array(int id) const;
+  const std::vector<int64_t>* get_int_array(int id) const;
   const std::vector<std::pair<int, ParamValue>>& entries() const { return entries_; }
 
  private:

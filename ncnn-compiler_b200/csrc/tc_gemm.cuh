@@ -43,9 +43,10 @@ __host__ __device__ constexpr int tc_elem_bytes(int kind) { return kind == GEMM_
 //   HARDSIGMOID  clamp(x*alpha + beta, 0, 1), HARDSWISH x * that (ConvertHardActivation, :3023-3072)
 //   TANH         tanh(x)                                      (ConvertTanH, :3722-3736)
 //   SCALE        x * a                                        (ConvertDropout, :2047-2070)
+//   SQUARE       x * x                                        (ConvertUnary, :5225-5252)
 enum : int {
   ACT_NONE = 0, ACT_RELU = 1, ACT_LEAKY = 2, ACT_CLIP = 3, ACT_SIGMOID = 4, ACT_SWISH = 5, ACT_HARDSIGMOID = 6,
-  ACT_HARDSWISH = 7, ACT_TANH = 8, ACT_SCALE = 9
+  ACT_HARDSWISH = 7, ACT_TANH = 8, ACT_SCALE = 9, ACT_SQUARE = 10
 };
 // OUT_F32        plain fp32
 // OUT_F32_SPLIT  two fp32 planes: hi = value rounded to tf32, lo = value - hi
@@ -146,6 +147,7 @@ __device__ __forceinline__ float apply_act(float y, int act, float a, float b) {
   }
   if (act == ACT_TANH) return tanhf(y);
   if (act == ACT_SCALE) return __fmul_rn(y, a);
+  if (act == ACT_SQUARE) return __fmul_rn(y, y);
   return y;
 }
 

@@ -518,6 +518,14 @@ def op_binary(layer: Layer, ins):
     op = layer.geti(0, 0)
     a = ins[0]
     b = F32(layer.getf(2, 0.0)) if layer.geti(1, 0) else ins[1]
+    if not layer.geti(1, 0) and a.shape != b.shape:
+        # computeBinaryResult (NCNNOps.cpp:1219-1244): right-aligned broadcasting over the logical
+        # [c,h,w] dims; this oracle keeps rank-3 arrays as HWC, so go through CHW views
+        def chw(x):
+            return x.transpose(2, 0, 1) if x.ndim == 3 else x
+        a, b = np.broadcast_arrays(chw(a), chw(b))
+        back = (lambda y: np.ascontiguousarray(y.transpose(1, 2, 0))) if a.ndim == 3 else (lambda y: y)
+        a, b = back(a), back(b)
     if op == 0:
         return (a + b).astype(F32)
     if op == 1:
@@ -603,6 +611,121 @@ def op_concat(layer: Layer, ins):
     if len(ins) < 2:
         raise ValueError("Concat requires at least two inputs")
     return np.ascontiguousarray(np.concatenate(ins, axis=_storage_axis(ins[0].ndim, layer.geti(0, 0))))
+
+
+def op_slice(layer: Layer, x):
+    """import_slice (ImportTensor.cpp:136-193) + inferSliceResults (NCNNOps.cpp:1538-1591): sizes along
+    one logical axis, -233 = an equal share of what is left; the sizes must consume the axis."""
+    sizes = list(layer.params[0])
+    if len(sizes) < 2:
+        raise ValueError("Slice requires at least two slices")
+    ax = _storage_axis(x.ndim, layer.geti(1, 0))
+    extent, consumed, outs = x.shape[ax], 0, []
+    for k, size in enumerate(sizes):
+        if size == -233:
+            size = (extent - consumed) // (len(sizes) - k)
+        if size <= 0 or size > extent - consumed:
+            raise ValueError("Slice sizes must be positive and fit input")
+        outs.append(np.ascontiguousarray(np.take(x, range(consumed, consumed + size), axis=ax)))
+        consumed += size
+    if consumed != extent:
+        raise ValueError("Slice sizes must consume the entire axis")
+    return outs
+
+
+def op_shuffle_channel(layer: Layer, x):
+    """ConvertShuffleChannel (NCNNToTosa.cpp:5394-5456): channels [group][C/group] -> [C/group][group];
+    reverse uses C/group groups."""
+    group, reverse = layer.geti(0, 1), layer.geti(1, 0)
+    C = x.shape[2]
+    if group <= 0 or C % group:
+        raise ValueError("group must divide channel count")
+    g = C // group if reverse else group
+    H, W = x.shape[:2]
+    return np.ascontiguousarray(x.reshape(H, W, g, C // g).transpose(0, 1, 3, 2).reshape(H, W, C))
+
+
+def op_padding(layer: Layer, x):
+    """import_padding (ImportDetection.cpp:31-112) + ConvertPadding (NCNNToTosa.cpp:2231-2248):
+    constant spatial padding of a rank-3 tensor."""
+    if layer.geti(4, 0) != 0 or layer.geti(6, 0) or layer.geti(7, 0) or layer.geti(8, 0):
+        raise ValueError("Padding only supports constant spatial padding without per-channel data")
+    t, b, l, r = (layer.geti(k, 0) for k in range(4))
+    v = layer.params.get(5, 0.0)
+    value = F32(0.0) if isinstance(v, int) else F32(v)
+    return np.pad(x, ((t, b), (l, r), (0, 0)), constant_values=value).astype(F32)
+
+
+def _bilinear_coordinate(index, n_in, n_out, align):
+    """Source coordinate exactly as ConvertInterp spells it in f32 (NCNNToTosa.cpp:2371-2434)."""
+    idx, fin, fout = index.astype(F32), F32(n_in), F32(n_out)
+    in_max = F32(fin - F32(1))
+    if align:
+        src = ((idx * in_max).astype(F32) / F32(fout - F32(1))).astype(F32)
+    else:
+        src = ((((idx + F32(0.5)).astype(F32) * fin).astype(F32) / fout).astype(F32) - F32(0.5)).astype(F32)
+    src = np.minimum(np.maximum(src, F32(0)), in_max)
+    base = np.minimum(np.floor(src).astype(np.int64), n_in - 2)
+    return base, (src - base.astype(F32)).astype(F32)
+
+
+def op_interp(layer: Layer, x):
+    """import_interp (ImportDetection.cpp:114-205) + ConvertInterp (NCNNToTosa.cpp:2252-2572): nearest
+    = floor(out / scale), or (out * in) / out_size with an explicit size; bilinear in f32 step by step."""
+    kind, align = layer.geti(0, 0), layer.geti(6, 0)
+    hs, ws = layer.getf(1, 1.0), layer.getf(2, 1.0)
+    oh, ow = layer.geti(3, 0), layer.geti(4, 0)
+    if kind not in (1, 2) or (kind == 1 and align) or hs < 1 or ws < 1 or hs != int(hs) or ws != int(ws) or layer.geti(5, 0):
+        raise ValueError("Interp supports nearest or bilinear resize with valid integer scale and alignment only")
+    H, W, _ = x.shape
+    OH, OW = (oh or H * int(hs)), (ow or W * int(ws))
+    ys, xs = np.arange(OH), np.arange(OW)
+    if kind == 1:
+        iy = (ys * H) // OH if oh else ys // int(hs)
+        ix = (xs * W) // OW if ow else xs // int(ws)
+        return np.ascontiguousarray(x[iy][:, ix])
+    y0, fy = _bilinear_coordinate(ys, H, OH, align)
+    x0, fx = _bilinear_coordinate(xs, W, OW, align)
+    fx, fy = fx[None, :, None], fy[:, None, None]
+    gx, gy = (F32(1) - fx).astype(F32), (F32(1) - fy).astype(F32)
+    v00, v01 = x[y0][:, x0], x[y0][:, x0 + 1]
+    v10, v11 = x[y0 + 1][:, x0], x[y0 + 1][:, x0 + 1]
+    top = ((v00 * gx).astype(F32) + (v01 * fx).astype(F32)).astype(F32)
+    bottom = ((v10 * gx).astype(F32) + (v11 * fx).astype(F32)).astype(F32)
+    return ((top * gy).astype(F32) + (bottom * fy).astype(F32)).astype(F32)
+
+
+def op_reduction(layer: Layer, x):
+    """import_reduction (ImportTensor.cpp:195-255) + ConvertReduction (NCNNToTosa.cpp:5546-5682): f32
+    mean = reduce_sum axis by axis in storage order (h, w, c), times float(coeff / count)."""
+    reduce_all, keep = layer.geti(1, 1), layer.geti(4, 0)
+    axes = list(layer.params.get(3, []))
+    if layer.geti(0, 0) != 3:
+        raise ValueError("Reduction supports static FP32 mean with integer axes only")
+    if not reduce_all and (not axes or layer.geti(5, 0) != 1):
+        raise ValueError("explicit Reduction axes require fixbug0=1")
+    if x.ndim != 3:
+        raise ValueError("Reduction of tensors that are not rank 3 is outside the supported path")
+    logical = sorted({a + 3 if a < 0 else a for a in axes}) if not reduce_all else [0, 1, 2]
+    if not reduce_all and len(logical) != len(axes):
+        raise ValueError("Reduction axes must be unique and in range")
+    y = x.astype(F32)
+    count = 1
+    for sa in sorted(_storage_axis(3, a) for a in logical):
+        count *= y.shape[sa]
+        acc = np.zeros(np.delete(y.shape, sa), F32)
+        for k in range(y.shape[sa]):  # sequential accumulation, like the lowered loop
+            acc = (acc + np.take(y, k, axis=sa)).astype(F32)
+        y = np.expand_dims(acc, sa)
+    y = (y * F32(float(F32(layer.getf(2, 1.0))) / count)).astype(F32)
+    kept = [d for a, d in enumerate((x.shape[2], x.shape[0], x.shape[1])) if a not in logical]  # logical c, h, w
+    if keep:
+        return y
+    if len(kept) == 2 and 0 in logical:
+        return y.reshape(kept)  # [h, w]
+    if len(kept) == 2:
+        raise ValueError("this combination of Reduction axes is outside the supported path")
+    return y.reshape(kept if kept else [1])
 
 
 def op_dequantize(acc_i32, scale, bias=None):
@@ -732,6 +855,22 @@ class Model:
                 out = op_softmax(l, ins[0])
             elif t == "Concat":
                 out = op_concat(l, ins)
+            elif t == "UnaryOp":
+                if l.geti(0, 0) != 4:  # ConvertUnary (NCNNToTosa.cpp:5225-5252): square only
+                    raise ValueError("UnaryOp supports the square operation (op_type=4) only")
+                out = (ins[0].astype(F32) * ins[0].astype(F32)).astype(F32)
+            elif t == "Slice":
+                for top, piece in zip(l.tops, op_slice(l, ins[0])):
+                    env[top] = piece
+                continue
+            elif t == "ShuffleChannel":
+                out = op_shuffle_channel(l, ins[0])
+            elif t == "Padding":
+                out = op_padding(l, ins[0])
+            elif t == "Interp":
+                out = op_interp(l, ins[0])
+            elif t == "Reduction":
+                out = op_reduction(l, ins[0])
             elif t == "BatchNorm":
                 scale, offset = batchnorm_scale_offset(*l.weights, l.getf(1, 0.0))
                 if ins[0].ndim == 2:  # channel axis is dimension 0 unless the tensor is rank 3
@@ -744,9 +883,20 @@ class Model:
                 for top in l.tops:
                     env[top] = ins[0]
                 continue
-            elif t in ("Flatten", "Reshape"):
+            elif t == "Flatten":
                 x = ins[0]
                 out = x.transpose(2, 0, 1).reshape(-1) if x.ndim == 3 else x.reshape(-1)
+            elif t == "Reshape":
+                # ncnn Reshape over the logical [c,h,w] order: 0=w 1=h 2=c, -233 unused, 0 copies the
+                # input extent, -1 is inferred (import_reshape, ImportOps.cpp:166-300)
+                x = ins[0]
+                chw = np.ascontiguousarray(x.transpose(2, 0, 1)) if x.ndim == 3 else x
+                d = [l.geti(0, -233), l.geti(1, -233), l.geti(2, -233)]
+                src = [chw.shape[-1], chw.shape[-2] if chw.ndim >= 2 else 1, chw.shape[0] if chw.ndim == 3 else 1]
+                rank = 3 if d[2] != -233 else (2 if d[1] != -233 else 1)
+                dims = [src[i] if d[i] == 0 else d[i] for i in range(rank)]
+                flat = chw.reshape(dims[::-1])  # numpy infers a single -1
+                out = np.ascontiguousarray(flat.transpose(1, 2, 0)) if rank == 3 else flat
             elif t == "Squeeze":
                 x = ins[0]
                 chw = x.transpose(2, 0, 1) if x.ndim == 3 else x

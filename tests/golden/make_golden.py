@@ -38,7 +38,10 @@ NO_WEIGHTS = ["pooling", "pooling_tail", "pooling_average", "pooling_asymmetric"
               "sigmoid", "hard_sigmoid", "hard_swish", "dropout", "softmax", "softmax_channel", "softmax_height",
               "softmax_width", "softmax_negative_channel", "softmax_negative_height", "softmax_negative_width",
               "concat", "concat_height", "concat_width", "concat_negative_channel", "concat_negative_height",
-              "concat_negative_width", "split_three"]
+              "concat_negative_width", "split_three", "binary_mul_channel", "binary_mul_reverse_broadcast",
+              "unary_square", "slice", "shuffle_channel", "shuffle_channel_reverse", "padding", "padding_four_sides",
+              "padding_identity", "interp", "interp_asymmetric", "interp_eightfold", "interp_explicit_target",
+              "interp_identity", "reduction_mean", "reduction_mean_keepdims_coeff"]
 
 
 def main():

@@ -328,7 +328,7 @@ def test_null_pointer_and_bad_batch_status(pkg, tmp_path):
 
 
 def test_unsupported_layers_fail_loudly(pkg, tmp_path):
-    for name in ("deconvolution", "gelu", "interp", "concat_rank4"):
+    for name in ("deconvolution", "gelu", "permute_rank4", "concat_rank4"):
         param = os.path.join(FIXTURES, name + ".param")
         with pytest.raises(pkg.NcnnB200Error) as e:
             pkg.Model(param, os.path.join(FIXTURES, "relu.bin"))
@@ -478,3 +478,93 @@ def test_maxpool_3x3_stride2_tile_kernel(pkg, oracle, tmp_path, c, h, w, pad, pa
     kernels = {row["kernel"] for row in m.profile(4, repeat=1)}
     m.close()
     assert "k_maxpool3x3s2_tile" in kernels
+
+
+@pytest.mark.parametrize("name", ["unary_square", "shuffle_channel", "shuffle_channel_reverse", "padding",
+                                  "padding_four_sides", "padding_identity", "interp", "interp_asymmetric",
+                                  "interp_eightfold", "interp_explicit_target", "interp_identity"])
+def test_reference_fixture_remap_ops_exact(pkg, oracle, name):
+    """UnaryOp square, ShuffleChannel, constant Padding and nearest Interp move or multiply values once: exact."""
+    param, bin_ = fixture(name)
+    shapes = _input_shape(pkg, param, bin_)
+    x = np.random.default_rng(len(name) + 40).standard_normal((4, *shapes[0])).astype(np.float32)
+    got, want = run_both(pkg, oracle, param, bin_, x, 0)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("name", ["binary_mul_channel", "binary_mul_reverse_broadcast"])
+def test_reference_fixture_binary_broadcast_exact(pkg, oracle, name):
+    param, bin_ = fixture(name)
+    m = pkg.Model(param, bin_)
+    rng = np.random.default_rng(22)
+    a = rng.standard_normal((4, *m.input_shapes[0])).astype(np.float32)
+    b = rng.standard_normal((4, *m.input_shapes[1])).astype(np.float32)
+    got = m.run(a, b)[0]
+    m.close()
+    om = oracle.Model(param, bin_)
+    want = np.stack([om.run([a[i], b[i]])[0] for i in range(4)])
+    assert got.shape == want.shape and np.array_equal(got, want)
+
+
+def test_reference_fixture_slice_exact(pkg, oracle):
+    param, bin_ = fixture("slice")
+    m = pkg.Model(param, bin_)
+    x = np.random.default_rng(23).standard_normal((3, *m.input_shapes[0])).astype(np.float32)
+    got = m.run(x)
+    m.close()
+    om = oracle.Model(param, bin_)
+    for k in range(2):
+        want = np.stack([om.run([xi])[k] for xi in x])
+        assert got[k].shape == want.shape and np.array_equal(got[k], want)
+
+
+@pytest.mark.parametrize("name", ["reduction_mean", "reduction_mean_keepdims_coeff"])
+def test_reference_fixture_reduction_mean(pkg, oracle, name):
+    """Mean over the spatial axes: the same axis-by-axis sequential sums as the oracle, exact."""
+    param, bin_ = fixture(name)
+    shapes = _input_shape(pkg, param, bin_)
+    x = np.random.default_rng(26).standard_normal((5, *shapes[0])).astype(np.float32)
+    got, want = run_both(pkg, oracle, param, bin_, x, 0)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("align", [0, 1])
+def test_bilinear_interp(pkg, oracle, tmp_path, align):
+    """Bilinear resize follows the reference's f32 formula step by step; the GPU uses the same
+    separate multiplies and adds, so the result is exact."""
+    p = tmp_path / "bil.param"
+    p.write_text("7767517\n2 2\nInput input 0 1 data 0=9 1=7 2=12\n"
+                 f"Interp up 1 1 data output 0=2 1=2.0 2=3.0 3=15 4=20 6={align}\n")
+    (tmp_path / "bil.bin").write_bytes(b"")
+    x = np.random.default_rng(24).standard_normal((3, 12, 7, 9)).astype(np.float32)
+    got, want = run_both(pkg, oracle, str(p), str(tmp_path / "bil.bin"), x, 0)
+    assert got.shape == (3, 12, 15, 20)
+    assert np.array_equal(got, want)
+
+
+def test_squeeze_excite_block(pkg, oracle, tmp_path):
+    """Global pooling -> 1x1 convolutions -> HardSigmoid gate -> channel-wise multiply (BinaryOp
+    broadcast of a [c,1,1] tensor), the way MobileNetV3 / EfficientNet blocks are exported."""
+    import struct
+    rng = np.random.default_rng(25)
+    c, r = 32, 8
+    w1 = (rng.standard_normal((r, c, 1, 1)) * 0.2).astype(np.float32)
+    w2 = (rng.standard_normal((c, r, 1, 1)) * 0.2).astype(np.float32)
+    prefix = str(tmp_path / "se")
+    with open(prefix + ".param", "w") as f:
+        f.write("7767517\n8 9\n")
+        f.write(f"Input input 0 1 data 0=10 1=12 2={c}\n")
+        f.write("Split split 1 2 data a b\n")
+        f.write("Pooling gap 1 1 a pooled 0=1 4=1\n")
+        f.write(f"Reshape r 1 1 pooled p3 0=1 1=1 2={c}\n")
+        f.write(f"Convolution fc1 1 1 p3 h1 0={r} 1=1 5=1 6={w1.size} 9=1\n")
+        f.write(f"Convolution fc2 1 1 h1 h2 0={c} 1=1 5=1 6={w2.size}\n")
+        f.write("HardSigmoid gate 1 1 h2 g 0=0.166667 1=0.5\n")
+        f.write("BinaryOp scale 2 1 b g output 0=2\n")
+    with open(prefix + ".bin", "wb") as f:
+        f.write(struct.pack("<I", 0) + w1.tobytes() + np.zeros(r, np.float32).tobytes())
+        f.write(struct.pack("<I", 0) + w2.tobytes() + np.zeros(c, np.float32).tobytes())
+    x = rng.standard_normal((4, c, 12, 10)).astype(np.float32)
+    got, want = run_both(pkg, oracle, prefix + ".param", prefix + ".bin", x, 0)
+    assert got.shape == (4, c, 12, 10)
+    assert rel_l2(got, want) <= TOL[0]

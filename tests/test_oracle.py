@@ -315,3 +315,68 @@ def test_split_three_concat_chain(oracle):
     x = np.random.default_rng(13).standard_normal((3, 4, 5)).astype(F32)
     got = _run_fixture(oracle, "split_three", x)
     assert np.array_equal(got, np.concatenate([x, x, x], axis=0))
+
+
+# ------------------------------------------------------------------ broadcast, slice, shuffle, padding, interp
+def test_binary_broadcast_square_slice_shuffle(oracle):
+    rng = np.random.default_rng(14)
+    a, s = rng.standard_normal((2, 3, 4)).astype(F32), rng.standard_normal((2, 1, 1)).astype(F32)
+    assert np.array_equal(_run_fixture(oracle, "binary_mul_channel", a, s), a * s)
+    assert np.array_equal(_run_fixture(oracle, "binary_mul_reverse_broadcast", s, a), s * a)
+    x = rng.standard_normal((4, 2, 3)).astype(F32)
+    assert np.array_equal(_run_fixture(oracle, "unary_square", x), x * x)
+    # slice fixture (array notation: count first): 5 channels as 2 and the rest along axis 0
+    x = rng.standard_normal((5, 3, 4)).astype(F32)
+    param, bin_ = fixture("slice")
+    m = oracle.Model(param, bin_)
+    outs = m.run([x], want=["left", "right"])
+    assert np.array_equal(outs[0], x[:2]) and np.array_equal(outs[1], x[2:])
+    # shuffle: 6 channels, group 2: output channel j = a*2 + b takes input channel b*3 + a
+    x = rng.standard_normal((6, 3, 4)).astype(F32)
+    want = x.reshape(2, 3, 3, 4).transpose(1, 0, 2, 3).reshape(6, 3, 4)
+    assert np.array_equal(_run_fixture(oracle, "shuffle_channel", x), want)
+    want = x.reshape(3, 2, 3, 4).transpose(1, 0, 2, 3).reshape(6, 3, 4)  # reverse: 6/2 = 3 groups
+    assert np.array_equal(_run_fixture(oracle, "shuffle_channel_reverse", x), want)
+
+
+def test_padding_and_interp_by_hand(oracle):
+    x = np.arange(12, dtype=F32).reshape(2, 2, 3)
+    got = _run_fixture(oracle, "padding_four_sides", x)  # top 1, bottom 2, left 3, right 4, value -7.25
+    assert got.shape == (2, 5, 10)
+    assert np.array_equal(got[:, 1:3, 3:6], x) and got[0, 0, 0] == F32(-7.25) and got[1, 4, 9] == F32(-7.25)
+    assert np.array_equal(_run_fixture(oracle, "padding_identity", np.ones((2, 3, 4), F32)), np.ones((2, 3, 4), F32))
+    got = _run_fixture(oracle, "interp", x)  # nearest, scale 2: out[y, x] = in[y // 2, x // 2]
+    assert np.array_equal(got, x.repeat(2, axis=1).repeat(2, axis=2))
+    got = _run_fixture(oracle, "interp_asymmetric", x)  # explicit 6 x 12 from 2 x 3: (o * in) // out
+    assert got.shape == (2, 6, 12)
+    assert np.array_equal(got, x[:, (np.arange(6) * 2) // 6][:, :, (np.arange(12) * 3) // 12])
+
+
+def test_bilinear_interp_matches_textbook(oracle, tmp_path):
+    for align in (0, 1):
+        p = tmp_path / f"bil{align}.param"
+        p.write_text("7767517\n2 2\nInput input 0 1 data 0=5 1=4 2=2\n"
+                     f"Interp up 1 1 data output 0=2 1=2.0 2=3.0 6={align}\n")
+        (tmp_path / f"bil{align}.bin").write_bytes(b"")
+        x = np.random.default_rng(15).standard_normal((2, 4, 5)).astype(F32)
+        got = oracle.Model(str(p), str(tmp_path / f"bil{align}.bin")).run([x])[0]
+        assert got.shape == (2, 8, 15)
+        want = np.zeros((2, 8, 15))
+        for oy in range(8):
+            for ox in range(15):
+                sy = oy * 3 / 7 if align else (oy + 0.5) * 4 / 8 - 0.5
+                sx = ox * 4 / 14 if align else (ox + 0.5) * 5 / 15 - 0.5
+                sy, sx = min(max(sy, 0), 3), min(max(sx, 0), 4)
+                y0, x0 = min(int(np.floor(sy)), 2), min(int(np.floor(sx)), 3)
+                fy, fx = sy - y0, sx - x0
+                v = x[:, y0:y0 + 2, x0:x0 + 2].astype(np.float64)
+                want[:, oy, ox] = (v[:, 0, 0] * (1 - fx) + v[:, 0, 1] * fx) * (1 - fy) + (v[:, 1, 0] * (1 - fx) + v[:, 1, 1] * fx) * fy
+        assert np.allclose(got, want, rtol=1e-5, atol=2e-6)
+
+
+def test_reduction_mean_fixtures(oracle):
+    x = np.random.default_rng(16).standard_normal((4, 3, 4)).astype(F32)
+    got = _run_fixture(oracle, "reduction_mean", x)  # axes (1, 2) without keepdims -> [c]
+    assert got.shape == (4,) and np.allclose(got, x.mean(axis=(1, 2)), rtol=1e-6, atol=1e-7)
+    got = _run_fixture(oracle, "reduction_mean_keepdims_coeff", x)  # keepdims, coeff 0.5
+    assert got.shape == (4, 1, 1) and np.allclose(got[:, 0, 0], 0.5 * x.mean(axis=(1, 2)), rtol=1e-6, atol=1e-7)
