@@ -138,7 +138,11 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
   // a bf16-pair output or residual is staged 32 columns at a time
   const int res_mode = e.res0 == nullptr ? RES_NONE : (e.res_bf16 ? RES_BF16X2 : (e.res1 != nullptr ? RES_SPLIT : RES_F32));
   const bool wide = e.out_mode == OUT_BF16X2 || res_mode == RES_BF16X2;
-  p.block_n = choose_block_n(p.tiles_m, N, sm_count, wide ? 32 : 16);
+  // int8 results can leave through TMA stores in chunks of 64 columns when every tile is a
+  // multiple of 64 wide, rows are 16-byte multiples and nothing is added after requantisation
+  const bool i8_staged = e.out_mode == OUT_I8 && N % 64 == 0 && e.ldo % 16 == 0 && e.res0 == nullptr &&
+                         (reinterpret_cast<uintptr_t>(e.outq) & 15) == 0;
+  p.block_n = choose_block_n(p.tiles_m, N, sm_count, i8_staged ? 64 : (wide ? 32 : 16));
   p.tiles_n = (N + p.block_n - 1) / p.block_n;
   const int planes = tc_planes(kind);
   // a stage holds the A tile(s) and block_n rows of B, every sub-buffer 1 KB aligned
@@ -156,9 +160,10 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
                                                   res_mode == RES_SPLIT))
                     ? 1
                     : 0;
+  if (i8_staged) p.tma_store = 1;
   // residual tiles (16 KB) + two to four output tiles of 8 KB per plane; fewer when the
   // operand ring would drop below three stages
-  const int out_tile = (e.out_mode == OUT_F32_SPLIT || wide ? 2 : 1) * 8192;
+  const int out_tile = (e.out_mode != OUT_I8 && (e.out_mode == OUT_F32_SPLIT || wide) ? 2 : 1) * 8192;
   int staging = 0;
   p.out_bufs = 2;
   if (p.tma_store) {
@@ -223,6 +228,19 @@ std::string encode_plane(CUtensorMap* map, const void* base, long long M, int N,
 
 std::string encode_epilogue_maps(TcLaunch* L, const TcEpilogue& e) {
   if (!L->p.tma_store) return {};
+  if (e.out_mode == OUT_I8) {
+    // [M][N] int8 plane, boxes of 64 columns x 128 rows, 64-byte swizzle
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(L->p.N), static_cast<cuuint64_t>(L->p.M)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(e.ldo)};
+    const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(kTcBlockM)};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    const CUresult r = g_encode_tiled(&L->map_o0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, e.outq, dims, strides, box,
+                                      elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+      return "cuTensorMapEncodeTiled failed for an int8 output plane with code " + std::to_string(static_cast<int>(r));
+    return {};
+  }
   const bool ob = e.out_mode == OUT_BF16X2;
   std::string err = encode_plane(&L->map_o0, e.out0, L->p.M, L->p.N, e.ldo, ob);
   if (err.empty() && (e.out_mode == OUT_F32_SPLIT || ob))

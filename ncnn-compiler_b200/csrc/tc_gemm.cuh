@@ -531,6 +531,57 @@ __device__ __forceinline__ bool tc_staged_epilogue(const TcStageCfg c, const IO&
   return ok;
 }
 
+// Staged epilogue for int8 results (no residual): a chunk is 64 accumulator columns, one
+// 64-byte staging row of int8 per accumulator row.  Dequantise, add the bias, requantise with
+// out_scale, clamp at zero for a fused ReLU (the order of the reference's int8 path), pack, and
+// store the [128][64] tile with one TMA store.
+template <int KIND, class IO>
+__device__ __forceinline__ void tc_staged_epilogue_i8(const TcStageCfg c, float out_scale, const IO& io,
+                                                      uint32_t t_row, int n0, int row, bool leader,
+                                                      const float* tile_bias, const float* tile_scale,
+                                                      int& out_slot) {
+  using namespace ptx;
+  named_barrier_sync(1, 128);  // tile constants are in place
+  for (int c0 = 0; c0 < c.block_n && n0 + c0 < c.N; c0 += 64) {
+    const uint32_t stage0 = c.out_stage + static_cast<uint32_t>(out_slot) * 8192u;
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      uint32_t v[16];
+      tmem_ld16(t_row + static_cast<uint32_t>(c0 + 16 * h), v);
+      tmem_ld_wait();
+      uint32_t w[4];
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const float4 b4 = *reinterpret_cast<const float4*>(&tile_bias[c0 + 16 * h + 4 * g]);
+        const float4 s4 = *reinterpret_cast<const float4*>(&tile_scale[c0 + 16 * h + 4 * g]);
+        const float bias[4] = {b4.x, b4.y, b4.z, b4.w}, scale[4] = {s4.x, s4.y, s4.z, s4.w};
+        uint32_t word = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float t = KIND == GEMM_I8 ? __fmul_rn(static_cast<float>(static_cast<int>(v[4 * g + e])), scale[e])
+                                    : __uint_as_float(v[4 * g + e]);
+          t = __fadd_rn(t, bias[e]);
+          int q = quantize_rha(t, out_scale);
+          if (c.act == ACT_RELU) q = max(q, 0);
+          word |= (static_cast<uint32_t>(q) & 0xffu) << (8 * e);
+        }
+        w[g] = word;
+      }
+      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage0 + stage_chunk_offset(row, h)), "r"(w[0]),
+                   "r"(w[1]), "r"(w[2]), "r"(w[3])
+                   : "memory");
+    }
+    fence_proxy_async_smem();
+    named_barrier_sync(2, 128);
+    if (leader) {
+      io.store_out(0, stage0, n0 + c0);
+      tma_store_commit();
+      tma_store_wait_read(c.out_bufs - 2);
+    }
+    if (++out_slot == c.out_bufs) out_slot = 0;
+  }
+}
+
 template <int KIND>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ CUtensorMap map_a0,
@@ -828,9 +879,14 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
             ptx::tma_store_2d(plane ? o1 : o0, src, col, m_first);
           }
         } io{&map_o0, &map_o1, &map_r0, &map_r1, m_first};
-        ok = tc_staged_epilogue<KIND>(cfg, io, t_row, n0, quarter * 32 + lane, threadIdx.x == 64, tile_bias,
-                                      tile_scale, res_ph, out_slot, abort_ptr);
-        if (!ok) break;
+        if (e_out_mode == OUT_I8) {
+          tc_staged_epilogue_i8<KIND>(cfg, p.out_scale, io, t_row, n0, quarter * 32 + lane, threadIdx.x == 64,
+                                      tile_bias, tile_scale, out_slot);
+        } else {
+          ok = tc_staged_epilogue<KIND>(cfg, io, t_row, n0, quarter * 32 + lane, threadIdx.x == 64, tile_bias,
+                                        tile_scale, res_ph, out_slot, abort_ptr);
+          if (!ok) break;
+        }
       } else {
         named_barrier_sync(3, 128);
         const bool bf16_io = e_out_mode == OUT_BF16X2 || e_res_mode == RES_BF16X2;
