@@ -74,6 +74,9 @@ struct Node {
   RemapParams remap{};
   ReduceParams reduce{};
   bool broadcast = false;  // N_BINARY whose operands differ in shape
+  // N_CONV (tensor-core path) that writes straight into a channel Concat's result: its output
+  // rows are `out_ld` channels long and start `out_ch_off` channels in (0 = dense, its own tensor)
+  int out_ld = 0, out_ch_off = 0;
   BroadcastParams bcast{};
   // device-side parameters
   void* d_w0 = nullptr;
@@ -186,6 +189,7 @@ class EngineImpl {
   int launch(Plan* plan, const std::vector<const float*>& d_in, const std::vector<float*>& d_out, cudaStream_t st);
   int finish_host_run(cudaStream_t st);
   void choose_head_limit();
+  void fold_channel_concats();
   int profile(int64_t n, int repeat, std::vector<LayerTiming>* out);
   Plan* plan_for(int64_t n);
 
@@ -1458,6 +1462,54 @@ bool EngineImpl::choose_impl(std::string* err) {
   return true;
 }
 
+// A channel Concat whose inputs are all single-use results of tensor-core convolutions needs no
+// copy: each convolution's epilogue already takes an output row stride, so it writes its
+// channels straight into the Concat's tensor (TMA stores clip at the convolution's own width).
+// Offsets and the total width must keep every row 16-byte aligned in any format (multiples of 8).
+void EngineImpl::fold_channel_concats() {
+  for (size_t k = 0; k < nodes_.size(); ++k) {
+    Node& cat = nodes_[k];
+    if (cat.kind != N_CONCAT || cat.concat.empty() || cat.concat[0].slice) continue;
+    const Tensor& to = tensors_[resolve(cat.out)];
+    if (to.rank != 3 || to.i8 || to.c % 8 != 0) continue;
+    bool channel_axis = true;
+    for (const ConcatParams& cp : cat.concat) channel_axis = channel_axis && cp.inner == 1 && cp.len_out == to.c;
+    if (!channel_axis) continue;
+    std::vector<int> uses(tensors_.size(), 0);
+    for (const Node& n : nodes_) {
+      for (int t : n.in) ++uses[resolve(t)];
+      if (n.res >= 0) ++uses[resolve(n.res)];
+    }
+    for (int o : outputs_) ++uses[resolve(o)];
+    std::vector<int> producers;
+    bool ok = true;
+    for (size_t i = 0; i < cat.in.size() && ok; ++i) {
+      const int src = resolve(cat.in[i]);
+      int pj = -1;
+      for (size_t j = 0; j < k; ++j)
+        if (resolve(nodes_[j].out) == src) pj = static_cast<int>(j);
+      ok = pj >= 0 && uses[src] == 1 && cat.concat[i].offset % 8 == 0;
+      if (ok) {
+        const Node& p = nodes_[pj];
+        ok = p.kind == N_CONV && p.impl == IMPL_TC && !p.stem && p.term == 0 && p.out_ld == 0 && p.res < 0 &&
+             p.O == cat.concat[i].len_in;
+        for (int other : producers) ok = ok && other != pj;
+      }
+      producers.push_back(pj);
+    }
+    if (!ok) continue;
+    const int target = resolve(cat.out);
+    for (size_t i = 0; i < cat.in.size(); ++i) {
+      Node& p = nodes_[producers[i]];
+      p.out_ld = to.c;
+      p.out_ch_off = cat.concat[i].offset;
+      tensors_[resolve(p.out)].alias = target;
+    }
+    nodes_.erase(nodes_.begin() + k);
+    --k;
+  }
+}
+
 bool EngineImpl::prepare_weights(std::string* err) {
   const int f32_kind = opt_.accuracy_mode == kAccuracyTf32 ? GEMM_TF32 : GEMM_TF32X3;
   // insert Quantize steps in front of int8 contractions whose input is fp32
@@ -1827,6 +1879,7 @@ bool EngineImpl::build(const std::string& param, const std::string& bin, const E
   fold_batchnorm();
   fuse();
   if (!choose_impl(err)) return false;
+  fold_channel_concats();
   if (opt.plan_only) return true;
   if (!prepare_weights(err)) return false;
   choose_head_limit();
@@ -1902,6 +1955,13 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
       te.out1 = out.p1;
       te.outq = out.q;
       te.ldo = node.O;
+      if (node.out_ld > 0) {
+        // a view into a Concat result: longer rows, starting `out_ch_off` channels in
+        te.ldo = node.out_ld;
+        const size_t skip = static_cast<size_t>(node.out_ch_off) * to.elem_bytes();
+        te.out0 = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(out.p0) + skip);
+        if (out.p1 != nullptr) te.out1 = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(out.p1) + skip);
+      }
       te.act = node.act;
       te.act_a = node.act_a;
       te.act_b = node.act_b;
@@ -1920,7 +1980,7 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
       std::string perr;
       // stride-1 filters with spatial extent: the patch-resident kernel loads each input pixel
       // once per tile instead of once per tap
-      if (node.kind == N_CONV && !i8 && !node.stem && halo_preferred() &&
+      if (node.kind == N_CONV && !i8 && !node.stem && node.out_ld == 0 && halo_preferred() &&
           tc_halo_applies(kind, ti.c, node.KH, node.KW, node.sh, node.sw, node.dh, node.dw, node.OH, node.OW, node.O,
                           te.out_mode)) {
         TcHaloConv hc;

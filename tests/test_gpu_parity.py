@@ -432,7 +432,8 @@ def test_reference_fixture_concat_exact(pkg, oracle, name):
 @pytest.mark.parametrize("act", ["ReLU", "Swish", "HardSwish", "Sigmoid", "TanH"])
 def test_fire_classifier_with_fused_activations(pkg, oracle, tmp_path, act):
     """SqueezeNet-style network: every activation is fused into the epilogue of the convolution
-    before it, Concat joins tensor-core outputs along channels, Softmax ends the graph."""
+    before it, channel Concats of tensor-core outputs are folded into the convolutions' output
+    strides, Softmax ends the graph."""
     param, bin_ = pkg.zoo.fire_classifier(str(tmp_path / "fire"), act=act)
     x = np.random.default_rng(31).uniform(-1, 1, (6, 3, 32, 32)).astype(np.float32)
     for mode in (0, 2):
@@ -443,7 +444,8 @@ def test_fire_classifier_with_fused_activations(pkg, oracle, tmp_path, act):
     m = pkg.Model(param, bin_)
     kernels = [row["kernel"] for row in m.profile(6, repeat=1)]
     m.close()
-    assert "k_softmax" in kernels and "k_concat_copy" in kernels
+    # the channel Concats cost nothing: the expand convolutions write straight into the joined tensor
+    assert "k_softmax" in kernels and "k_concat_copy" not in kernels
     # the only element-wise launches left are the Dropout scale and the output edge
     assert sum(k == "k_unary" for k in kernels) <= 2
 
@@ -568,3 +570,37 @@ def test_squeeze_excite_block(pkg, oracle, tmp_path):
     got, want = run_both(pkg, oracle, prefix + ".param", prefix + ".bin", x, 0)
     assert got.shape == (4, c, 12, 10)
     assert rel_l2(got, want) <= TOL[0]
+
+
+def test_channel_concat_folded_into_convolutions(pkg, oracle, tmp_path):
+    """Two convolutions joined by a channel Concat that is a graph output (plain fp32) and also feeds
+    a third convolution: the Concat is folded into the producers' output strides, no copy kernel runs,
+    and a Concat with a graph input as one operand keeps the copy."""
+    import struct
+    rng = np.random.default_rng(41)
+    w1 = (rng.standard_normal((24, 16, 1, 1)) * 0.2).astype(np.float32)
+    w2 = (rng.standard_normal((40, 16, 3, 3)) * 0.1).astype(np.float32)
+    w3 = (rng.standard_normal((32, 64, 1, 1)) * 0.1).astype(np.float32)
+    prefix = str(tmp_path / "cat")
+    with open(prefix + ".param", "w") as f:
+        f.write("7767517\n8 10\n")
+        f.write("Input input 0 1 data 0=14 1=9 2=16\n")
+        f.write("Split split 1 2 data a b\n")
+        f.write(f"Convolution c1 1 1 a x1 0=24 1=1 5=1 6={w1.size} 9=1\n")
+        f.write(f"Convolution c2 1 1 b x2 0=40 1=3 4=1 5=1 6={w2.size}\n")
+        f.write("Concat cat 2 1 x1 x2 joined 0=0\n")
+        f.write("Split split2 1 2 joined j1 j2\n")
+        f.write(f"Convolution c3 1 1 j1 y 0=32 1=1 5=1 6={w3.size}\n")
+        f.write("Concat cat2 2 1 y j2 output 0=0\n")
+    with open(prefix + ".bin", "wb") as f:
+        for w, o in ((w1, 24), (w2, 40), (w3, 32)):
+            f.write(struct.pack("<I", 0) + w.tobytes() + (rng.standard_normal(o) * 0.1).astype(np.float32).tobytes())
+    x = rng.standard_normal((5, 16, 9, 14)).astype(np.float32)
+    got, want = run_both(pkg, oracle, prefix + ".param", prefix + ".bin", x, 0)
+    assert got.shape == (5, 96, 9, 14) and rel_l2(got, want) <= TOL[0]
+    m = pkg.Model(prefix + ".param", prefix + ".bin")
+    kernels = [row["kernel"] for row in m.profile(5, repeat=1)]
+    m.close()
+    # cat is folded (both inputs are tensor-core results used once); cat2 joins a convolution result
+    # with a tensor that has another producer's data already in place, so it copies
+    assert kernels.count("k_concat_copy") == 2
