@@ -2230,6 +2230,20 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
     const UnaryParams up = node.un;
     const long long count = to.logical() * n;
     const bool vec = count % 4 == 0;
+    if (up.op == UN_QUANT && up.nscale == 1 && in.fmt == FMT_F32 && out.fmt == FMT_I8 && count % 16 == 0 &&
+        !node.un_scale.empty()) {
+      const float scale = node.un_scale[0];
+      const int grid16 = grid_for(count / 16);
+      const float* xp = in.p0;
+      int8_t* yp = out.q;
+      s.kernel = "k_quantize16";
+      s.run = [=](cudaStream_t st) {
+        k_quantize16<<<grid16, 256, 0, st>>>(xp, yp, count / 16, scale);
+        return launch_ok();
+      };
+      plan.steps.push_back(std::move(s));
+      return true;
+    }
     const int grid = grid_for(vec ? count / 4 : count);
     s.kernel = "k_unary";
     s.run = [=](cudaStream_t st) {
