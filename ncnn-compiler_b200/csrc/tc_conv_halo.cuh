@@ -290,6 +290,7 @@ tc_conv_halo_kernel(const __grid_constant__ TcHaloParams p, const __grid_constan
     cfg.act_b = p.act_b;
     cfg.N = p.N;
     cfg.block_n = p.block_n;
+    cfg.wide = (p.out_mode == OUT_BF16X2 || p.res_mode == RES_BF16X2) ? 1 : 0;
     const int e_N = p.N;
     int acc = 0, out_slot = 0;
     uint32_t acc_ph = 0, res_ph = 0;

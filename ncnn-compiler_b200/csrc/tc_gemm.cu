@@ -137,7 +137,10 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
   p.tiles_m = static_cast<int>((M + kTcBlockM - 1) / kTcBlockM);
   // a bf16-pair output or residual is staged 32 columns at a time
   const int res_mode = e.res0 == nullptr ? RES_NONE : (e.res_bf16 ? RES_BF16X2 : (e.res1 != nullptr ? RES_SPLIT : RES_F32));
-  const bool wide = e.out_mode == OUT_BF16X2 || res_mode == RES_BF16X2;
+  // Shallow contractions are bound by the epilogue: plain fp32 results then also go out 32 columns
+  // at a time (half as many barriers and store rounds per tile).
+  const bool shallow_f32 = e.out_mode == OUT_F32 && res_mode != RES_SPLIT && N % 16 == 0 && N >= 32 && p.k_blocks <= 4;
+  const bool wide = e.out_mode == OUT_BF16X2 || res_mode == RES_BF16X2 || shallow_f32;
   // int8 results can leave through TMA stores in chunks of 64 columns when every tile is a
   // multiple of 64 wide, rows are 16-byte multiples and nothing is added after requantisation
   const bool i8_staged = e.out_mode == OUT_I8 && N % 64 == 0 && e.ldo % 16 == 0 && e.res0 == nullptr &&
@@ -198,6 +201,7 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
   p.res0 = e.res0;
   p.res1 = e.res1;
   p.res_mode = res_mode;
+  p.wide = wide ? 1 : 0;
   p.ldo = e.ldo;
   p.out_mode = e.out_mode;
   p.act = e.act;

@@ -98,6 +98,7 @@ struct TcGemmParams {
   float out_scale;     // requantisation scale (OUT_I8)
   int* status;         // device word, stays 0 unless a bounded wait gave up
   int tma_store;       // fp32 outputs leave through shared-memory staging tiles and TMA stores
+  int wide;            // staged chunks are 32 columns wide (always with bf16 pairs; plain fp32 when it pays)
   int out_bufs;        // staging tiles in flight (1..4), each 8 KB per output plane
   long long* trace;    // optional (bring-up): per-role clock stamps of CTA 0, 8 values per tile
 };
@@ -364,6 +365,7 @@ struct TcStageCfg {
   int act;
   float act_a, act_b;
   int N, block_n;
+  int wide;  // 32-column chunks
 };
 
 // IO: load_res(plane, smem_dst, bar, column) and store_out(plane, smem_src, column) issue the
@@ -375,7 +377,7 @@ __device__ __forceinline__ bool tc_staged_epilogue(const TcStageCfg c, const IO&
                                                    volatile int* abort_ptr) {
   using namespace ptx;
   const bool has_res = c.res_mode != RES_NONE;
-  const bool wide = c.out_mode == OUT_BF16X2 || c.res_mode == RES_BF16X2;
+  const bool wide = c.wide != 0;
   const int cw = wide ? 32 : 16;
   const bool two_out = wide || c.out_mode == OUT_F32_SPLIT;
   const uint32_t out_tile_bytes = two_out ? 16384u : 8192u;
@@ -868,6 +870,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
         cfg.act_b = e_act_b;
         cfg.N = e_N;
         cfg.block_n = e_block_n;
+        cfg.wide = p.wide;
         const int m_first = m_blk * kTcBlockM;
         struct {
           const CUtensorMap *o0, *o1, *r0, *r1;

@@ -1,6 +1,6 @@
 """Regenerates tests/golden from the reference checkout (run in the build container only).
 
-    python tests/golden/make_golden.py [/root/reference]
+    python tests/golden/make_golden.py [path of the reference checkout]
 
 1. fixtures/*.param are the reference's own operator fixtures for the hot path
    (test/Numerical/fixtures), copied as data; fixtures/*.bin are produced by RUNNING
