@@ -278,7 +278,8 @@ tc_conv_halo_kernel(const __grid_constant__ TcHaloParams p, const __grid_constan
     // ------------------------------------------------------------ epilogue
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;  // accumulator row = pixel (row / 8, row % 8) of the tile
-    TcStageCfg cfg;
+    TcStageCfg cfg{};
+    cfg.bar_base = 1;
     cfg.res_stage = res_stage;
     cfg.out_stage = out_stage;
     cfg.res_bar = smem_u32(&res_bar);

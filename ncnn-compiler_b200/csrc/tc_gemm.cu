@@ -105,9 +105,10 @@ std::string encode_im2col(CUtensorMap* map, int kind, const void* base, const Tc
   return {};
 }
 
-// Dynamic shared memory a CTA may fill: 227 KB per block, minus ~1.2 KB of static shared
-// memory (barriers, per-tile constants), minus 1 KB of alignment slack.
-constexpr int kTcSmemBudget = 224 * 1024;
+// Dynamic shared memory a CTA may fill: 227 KB per block, minus the kernel's static shared
+// memory (barriers and per-tile constants: 1.2 KB, 2.2 KB for the int8 kernel with its
+// dequantisation factors), minus 1 KB of alignment slack.
+constexpr int tc_smem_budget(int kind) { return (kind == GEMM_I8 ? 223 : 224) * 1024; }
 // From this many K blocks per tile on, the main loop of the next tile hides even the slower
 // direct epilogue, and a third ring stage is worth more than the staging tiles.
 constexpr int kDirectEpilogueDepth = 32;
@@ -147,6 +148,7 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
                          (reinterpret_cast<uintptr_t>(e.outq) & 15) == 0;
   p.block_n = choose_block_n(p.tiles_m, N, sm_count, i8_staged ? 64 : (wide ? 32 : 16));
   p.tiles_n = (N + p.block_n - 1) / p.block_n;
+  const int kTcSmemBudget = tc_smem_budget(kind);
   const int planes = tc_planes(kind);
   // a stage holds the A tile(s) and block_n rows of B, every sub-buffer 1 KB aligned
   const int b_bytes = (p.block_n * p.row_bytes + 1023) / 1024 * 1024;
@@ -183,6 +185,16 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
       p.tma_store = 0;
       staging = 0;
     }
+  }
+  // Shallow contractions (a few K blocks per tile) are bound by the epilogue: a second epilogue
+  // group drains every other tile, with a staging area of its own.
+  const long long tiles_total = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  p.staging_bytes = staging;
+  p.epi_groups = 1;
+  if (p.tma_store && p.k_blocks <= 4 && tiles_total >= 2ll * sm_count &&
+      (kTcSmemBudget - 2 * staging) / p.stage_bytes >= 4) {
+    p.epi_groups = 2;
+    staging *= 2;
   }
   const int budget = kTcSmemBudget - staging;
   p.stages = std::max(2, std::min(kTcMaxStages, budget / p.stage_bytes));
@@ -364,7 +376,7 @@ cudaError_t tc_launch(const TcLaunch& L, cudaStream_t stream) {
   static std::once_flag attr_once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(attr_once, [] {
-    const int max_smem = kTcSmemBudget + 1024;  // contents + alignment slack
+    const int max_smem = tc_smem_budget(GEMM_TF32) + 1024;  // contents + alignment slack
     cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<GEMM_TF32>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
     if (e == cudaSuccess)
@@ -372,14 +384,14 @@ cudaError_t tc_launch(const TcLaunch& L, cudaStream_t stream) {
                                cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(tc_gemm_kernel<GEMM_I8>,
-                               cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem_budget(GEMM_I8) + 1024);
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(tc_gemm_kernel<GEMM_BF16X3>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
     attr_err = e;
   });
   if (attr_err != cudaSuccess) return attr_err;
-  const dim3 grid(L.grid), block(kTcThreads);
+  const dim3 grid(L.grid), block(L.p.epi_groups == 2 ? kTcThreadsTwoEpi : kTcThreads);
   switch (L.kind) {
     case GEMM_TF32:
       tc_gemm_kernel<GEMM_TF32>
@@ -483,6 +495,7 @@ std::string tc_plan_conv_halo(TcHaloLaunch* L, int kind, const TcHaloConv& c, co
   const int out_tile = (e.out_mode == OUT_F32_SPLIT || wide ? 2 : 1) * 8192;
   const int fixed = 2 * planes * p.patch_bytes + (res_mode != RES_NONE ? 16384 : 0);
   p.out_bufs = 4;
+  const int kTcSmemBudget = 222 * 1024;  // the halo kernel's own static shared memory is ~2 KB
   p.stages = (kTcSmemBudget - fixed - p.out_bufs * out_tile) / (planes * p.b_bytes);
   if (p.stages < 4) {
     p.out_bufs = 2;
@@ -526,7 +539,7 @@ cudaError_t tc_launch_halo(const TcHaloLaunch& L, cudaStream_t stream) {
   static std::once_flag attr_once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(attr_once, [] {
-    const int max_smem = kTcSmemBudget + 1024;
+    const int max_smem = 223 * 1024;
     cudaError_t e = cudaFuncSetAttribute(tc_conv_halo_kernel<GEMM_TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          max_smem);
     if (e == cudaSuccess)

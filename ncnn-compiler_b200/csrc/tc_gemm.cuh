@@ -64,7 +64,8 @@ enum : int {
   TC_TIMEOUT_EPILOGUE = 3,
 };
 
-constexpr int kTcThreads = 224;  // warps: 0 A producer, 1 MMA issuer, 2-5 epilogue, 6 B producer
+constexpr int kTcThreads = 224;      // warps: 0 A producer, 1 MMA issuer, 2-5 epilogue, 6 B producer
+constexpr int kTcThreadsTwoEpi = 352;  // + warps 7-10: a second epilogue group for shallow contractions
 constexpr int kTcBlockM = 128;
 constexpr int kTcMaxStages = 8;
 constexpr uint32_t kTcTmemCols = 256;           // two accumulators of up to 128 columns
@@ -98,6 +99,8 @@ struct TcGemmParams {
   float out_scale;     // requantisation scale (OUT_I8)
   int* status;         // device word, stays 0 unless a bounded wait gave up
   int tma_store;       // fp32 outputs leave through shared-memory staging tiles and TMA stores
+  int staging_bytes;   // staging area of one epilogue group (residual + output tiles)
+  int epi_groups;      // 1 or 2 epilogue warpgroups (2: accumulator g is drained by group g; shallow layers)
   int wide;            // staged chunks are 32 columns wide (always with bf16 pairs; plain fp32 when it pays)
   int out_bufs;        // staging tiles in flight (1..4), each 8 KB per output plane
   long long* trace;    // optional (bring-up): per-role clock stamps of CTA 0, 8 values per tile
@@ -365,7 +368,8 @@ struct TcStageCfg {
   int act;
   float act_a, act_b;
   int N, block_n;
-  int wide;  // 32-column chunks
+  int wide;      // 32-column chunks
+  int bar_base;  // named barriers bar_base and bar_base + 1 belong to this epilogue group
 };
 
 // IO: load_res(plane, smem_dst, bar, column) and store_out(plane, smem_src, column) issue the
@@ -392,7 +396,7 @@ __device__ __forceinline__ bool tc_staged_epilogue(const TcStageCfg c, const IO&
     }
   };
   if (leader && has_res) fetch_res(n0);
-  named_barrier_sync(1, 128);  // tile constants are in place
+  named_barrier_sync(c.bar_base, 128);  // tile constants are in place
   bool ok = true;
   for (int c0 = 0; c0 < c.block_n && n0 + c0 < c.N; c0 += cw) {
     const uint32_t stage0 = c.out_stage + static_cast<uint32_t>(out_slot) * out_tile_bytes;
@@ -514,7 +518,7 @@ __device__ __forceinline__ bool tc_staged_epilogue(const TcStageCfg c, const IO&
       }
     }
     fence_proxy_async_smem();
-    named_barrier_sync(2, 128);
+    named_barrier_sync(c.bar_base + 1, 128);
     if (leader) {
       // rows and columns of a tile that fall outside the tensor are clipped by the store
       io.store_out(0, stage0, n0 + c0);
@@ -543,7 +547,7 @@ __device__ __forceinline__ void tc_staged_epilogue_i8(const TcStageCfg c, float 
                                                       const float* tile_bias, const float* tile_scale,
                                                       int& out_slot) {
   using namespace ptx;
-  named_barrier_sync(1, 128);  // tile constants are in place
+  named_barrier_sync(c.bar_base, 128);  // tile constants are in place
   for (int c0 = 0; c0 < c.block_n && n0 + c0 < c.N; c0 += 64) {
     const uint32_t stage0 = c.out_stage + static_cast<uint32_t>(out_slot) * 8192u;
 #pragma unroll
@@ -574,7 +578,7 @@ __device__ __forceinline__ void tc_staged_epilogue_i8(const TcStageCfg c, float 
                    : "memory");
     }
     fence_proxy_async_smem();
-    named_barrier_sync(2, 128);
+    named_barrier_sync(c.bar_base + 1, 128);
     if (leader) {
       io.store_out(0, stage0, n0 + c0);
       tma_store_commit();
@@ -585,7 +589,7 @@ __device__ __forceinline__ void tc_staged_epilogue_i8(const TcStageCfg c, float 
 }
 
 template <int KIND>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(kTcThreadsTwoEpi, 1)
 tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ CUtensorMap map_a0,
                const __grid_constant__ CUtensorMap map_a1,
                const __grid_constant__ CUtensorMap map_b0,
@@ -602,9 +606,9 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
   __shared__ __align__(8) uint64_t empty_bar[kTcMaxStages];
   __shared__ __align__(8) uint64_t tfull_bar[2];
   __shared__ __align__(8) uint64_t tempty_bar[2];
-  __shared__ __align__(8) uint64_t res_bar;
-  __shared__ __align__(16) float tile_bias[128];
-  __shared__ __align__(16) float tile_scale[128];
+  __shared__ __align__(8) uint64_t res_bar[2];
+  __shared__ __align__(16) float tile_bias_all[2][128];
+  __shared__ __align__(16) float tile_scale_all[2][128];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -629,7 +633,8 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
       mbar_init(smem_u32(&tfull_bar[i]), 1);
       mbar_init(smem_u32(&tempty_bar[i]), 4);
     }
-    mbar_init(smem_u32(&res_bar), 1);
+    mbar_init(smem_u32(&res_bar[0]), 1);
+    mbar_init(smem_u32(&res_bar[1]), 1);
     fence_mbar_init();
     prefetch_tensormap(&map_a0);
     prefetch_tensormap(&map_b0);
@@ -819,8 +824,19 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
     }
   } else {
     // ------------------------------------------------------------ epilogue
+    // One group (warps 2-5) drains both accumulators in turn; with two groups (shallow
+    // contractions, where the epilogue sets the pace) group g = warps 2-5 / 7-10 drains
+    // accumulator g only, i.e. every other tile, with its own staging tiles, barrier ids,
+    // per-tile constants and residual barrier.
+    const int group = warp >= 7 ? 1 : 0;
+    const int groups = p.epi_groups;
+    const int first_thread = group ? 224 : 64;
+    const bool leader = static_cast<int>(threadIdx.x) == first_thread;
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+31] belong to this warp
-    int acc = 0;
+    float* tile_bias = tile_bias_all[group];
+    float* tile_scale = tile_scale_all[group];
+    const int bar_base = 1 + 3 * group;
+    int acc = groups == 2 ? group : 0;
     uint32_t acc_ph = 0;
     uint32_t res_ph = 0;
     int out_slot = 0;
@@ -832,12 +848,15 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
     const float e_act_a = p.act_a, e_act_b = p.act_b;
     const int e_res_mode = p.res_mode;
     const int e_out_mode = p.out_mode, e_N = p.N, e_block_n = p.block_n, e_out_bufs = p.out_bufs;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+    const bool tracing = p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64;
+    const int tile_step = static_cast<int>(gridDim.x) * groups;
+    for (int tile = blockIdx.x + (groups == 2 ? group * static_cast<int>(gridDim.x) : 0); tile < total_tiles && ok;
+         tile += tile_step) {
       const int m_blk = tile / p.tiles_n;
       const int n_blk = tile - m_blk * p.tiles_n;
       const long long m = static_cast<long long>(m_blk) * kTcBlockM + quarter * 32 + lane;
       const int n0 = n_blk * p.block_n;
-      if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64) p.trace[(tile / gridDim.x) * 16 + 3] = clock64();
+      if (tracing) p.trace[(tile / gridDim.x) * 16 + 3] = clock64();
       // the vote keeps the warp together: tcgen05.ld below needs all 32 lanes
       ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&tfull_bar[acc]), acc_ph, abort_ptr,
                                                      kTcWaitLimitNs)
@@ -845,23 +864,23 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
                                        : 0) != 0;
       if (!ok) break;
       tc_fence_after_sync();
-      if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64) p.trace[(tile / gridDim.x) * 16 + 4] = clock64();
+      if (tracing) p.trace[(tile / gridDim.x) * 16 + 4] = clock64();
       const uint32_t t_row =
           tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc) * 128u;
       {
-        // per-column constants of this tile, fetched once (every warp has left the previous
-        // tile's last chunk: it ends with a barrier)
-        const int t = static_cast<int>(threadIdx.x) - 64;
+        // per-column constants of this tile, fetched once (every warp of the group has left the
+        // previous tile's last chunk: it ends with a barrier)
+        const int t = static_cast<int>(threadIdx.x) - first_thread;
         const int n = n0 + t;
         tile_bias[t] = (p.bias != nullptr && n < p.N) ? __ldg(p.bias + n) : 0.0f;
         tile_scale[t] = (KIND == GEMM_I8 && n < p.N) ? __ldg(p.scale + n) : 0.0f;
       }
       if (p.tma_store) {
-        // staging area behind the ring: residual tiles (16 KB), then the output tiles
-        TcStageCfg cfg;
-        cfg.res_stage = smem_base + static_cast<uint32_t>(S) * stage_bytes;
+        // staging area behind the ring, one per group: residual tiles (16 KB), then the output tiles
+        TcStageCfg cfg{};
+        cfg.res_stage = smem_base + static_cast<uint32_t>(S) * stage_bytes + static_cast<uint32_t>(group) * p.staging_bytes;
         cfg.out_stage = cfg.res_stage + (e_res_mode != RES_NONE ? 16384u : 0u);
-        cfg.res_bar = smem_u32(&res_bar);
+        cfg.res_bar = smem_u32(&res_bar[group]);
         cfg.out_bufs = e_out_bufs;
         cfg.out_mode = e_out_mode;
         cfg.res_mode = e_res_mode;
@@ -871,6 +890,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
         cfg.N = e_N;
         cfg.block_n = e_block_n;
         cfg.wide = p.wide;
+        cfg.bar_base = bar_base;
         const int m_first = m_blk * kTcBlockM;
         struct {
           const CUtensorMap *o0, *o1, *r0, *r1;
@@ -883,15 +903,15 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
           }
         } io{&map_o0, &map_o1, &map_r0, &map_r1, m_first};
         if (e_out_mode == OUT_I8) {
-          tc_staged_epilogue_i8<KIND>(cfg, p.out_scale, io, t_row, n0, quarter * 32 + lane, threadIdx.x == 64,
-                                      tile_bias, tile_scale, out_slot);
+          tc_staged_epilogue_i8<KIND>(cfg, p.out_scale, io, t_row, n0, quarter * 32 + lane, leader, tile_bias,
+                                      tile_scale, out_slot);
         } else {
-          ok = tc_staged_epilogue<KIND>(cfg, io, t_row, n0, quarter * 32 + lane, threadIdx.x == 64, tile_bias,
-                                        tile_scale, res_ph, out_slot, abort_ptr);
+          ok = tc_staged_epilogue<KIND>(cfg, io, t_row, n0, quarter * 32 + lane, leader, tile_bias, tile_scale,
+                                        res_ph, out_slot, abort_ptr);
           if (!ok) break;
         }
       } else {
-        named_barrier_sync(3, 128);
+        named_barrier_sync(bar_base + 2, 128);
         const bool bf16_io = e_out_mode == OUT_BF16X2 || e_res_mode == RES_BF16X2;
         for (int c0 = 0; c0 < e_block_n; c0 += 16) {
           uint32_t v[16];
@@ -902,19 +922,23 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
             else tc_epilogue_chunk<KIND, false>(lp, v, m, n0 + c0, tile_bias + c0, tile_scale + c0);
           }
         }
-        named_barrier_sync(3, 128);  // nobody reads the tile constants any more
+        named_barrier_sync(bar_base + 2, 128);  // nobody reads the tile constants any more
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 64) p.trace[(tile / gridDim.x) * 16 + 5] = clock64();
+      if (tracing) p.trace[(tile / gridDim.x) * 16 + 5] = clock64();
       if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
-      acc ^= 1;
-      if (acc == 0) acc_ph ^= 1u;
+      if (groups == 2) {
+        acc_ph ^= 1u;  // this group's accumulator is used by every tile it sees
+      } else {
+        acc ^= 1;
+        if (acc == 0) acc_ph ^= 1u;
+      }
     }
     if (!ok && lane == 0) {
       if (atomicCAS(const_cast<int*>(abort_ptr), 0, 1) == 0) atomicCAS(p.status, 0, TC_TIMEOUT_EPILOGUE);
     }
-    if (p.tma_store && threadIdx.x == 64) tma_store_wait_all();  // stores still read shared memory
+    if (p.tma_store && leader) tma_store_wait_all();  // stores still read shared memory
   }
 
   tc_fence_before_sync();
