@@ -48,12 +48,15 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi.  The process is started before the
+    warm-up (nvidia-smi needs a second to come up); every line is stamped on arrival, and the
+    summary uses the samples that fell inside the marked window."""
 
     def __init__(self, index):
         self.index = index
         self.proc = None
-        self.lines = []
+        self.samples = []  # (arrival time, line)
+        self.t0 = self.t1 = None
 
     def start(self):
         q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
@@ -61,7 +64,7 @@ class ClockSampler:
              "clocks_event_reasons.sw_power_cap")
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -69,12 +72,23 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.samples.append((time.monotonic(), line.strip()))
+
+    def count(self):
+        return len(self.samples)
+
+    def mark_begin(self):
+        self.t0 = time.monotonic()
+
+    def mark_end(self):
+        self.t1 = time.monotonic()
+
+    def in_window(self):
+        return sum(1 for t, _ in self.samples if self.t0 is not None and self.t0 <= t <= (self.t1 or time.monotonic()))
 
     def stop(self):
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+            return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -82,7 +96,12 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        inside = [(t, line) for t, line in self.samples if self.t0 is not None and self.t0 <= t <= self.t1]
+        window = "timed region (and the same steps right after it when it was shorter than a sample period)"
+        if not inside:
+            # e.g. the gather mode, where ranks cannot run extra steps: the warm-up ran the same load
+            inside, window = list(self.samples), "warm-up and timed region of the same load"
+        for t, line in inside:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 7:
                 continue
@@ -95,7 +114,7 @@ class ClockSampler:
                 if flag.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons), "window": window}
 
 
 def use_all_host_threads():
@@ -231,16 +250,22 @@ def main():
         if gathered is not None:
             dist.all_gather(gathered, y_dev)
 
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(max(args.warmup, 3)):
         step_device()
     torch.cuda.synchronize()
+    # keep the same load running until nvidia-smi delivers its first sample (bounded)
+    wait_until = time.monotonic() + 5.0
+    while gathered is None and sampler.proc is not None and sampler.count() == 0 and time.monotonic() < wait_until:
+        step_device()
+        torch.cuda.synchronize()
     model.check_status()
 
-    sampler = ClockSampler(local_rank)
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
-    sampler.start()
+    sampler.mark_begin()
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     for i in range(args.steps):
@@ -251,9 +276,17 @@ def main():
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
+    ms_dev = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
+    # a timed region of a few milliseconds can fall between two samples: the same steps keep
+    # running (untimed) until one sample has been taken under this load
+    wait_until = time.monotonic() + 2.0
+    while gathered is None and sampler.proc is not None and sampler.in_window() == 0 and time.monotonic() < wait_until:
+        flush.fill_(0)
+        step_device()
+        torch.cuda.synchronize()
+    sampler.mark_end()
     clocks = sampler.stop()
     model.check_status()
-    ms_dev = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
 
     # end to end through the host-pointer entry: H2D + run + D2H inside the timed call
     for _ in range(2):
