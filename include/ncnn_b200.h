@@ -54,6 +54,11 @@ typedef struct ncnn_b200_options {
   /* 1 = parse, validate and infer shapes only, without touching a GPU: enough for
    * ncnn_b200_emit_stub and the shape queries (a compile step), not for running. */
   int32_t plan_only;
+  /* 1 = an InnerProduct whose input is a rank-2 [M,K] tensor keeps its rows ([M,N]) also when
+   * M is 1, as the reference lowers a dynamic M (NCNNToTosa.cpp:5290-5303); 0 = a static input
+   * with exactly K elements is flattened to [N] (NCNNOps.cpp:1247-1312).  Set by the dynamic
+   * loader for its specialisations. */
+  int32_t keep_matrix_rows;
 } ncnn_b200_options;
 
 /* Replaces ncnn_graph::Graph::load + the compile pipeline (graph.hpp:379-380,
@@ -117,6 +122,56 @@ int64_t ncnn_b200_describe(const char *param_path, const char *bin_path, char *b
  * given .param/.bin through this library and forwards to ncnn_b200_run. */
 int ncnn_b200_emit_stub(const ncnn_b200_model *model, const char *name, const char *param_path,
                         const char *bin_path, const char *directory);
+
+/* ---- fixed-rank dynamic input shapes ---------------------------------------------------
+ * Replaces the dynamic half of the reference's generated wrapper: models compiled with
+ * `--input-shape=3x?x?` / `--input-dim-constraint=0:1:min=32,multiple=32`
+ * (docs/ncnn-compile-command-line.md 2.5-2.6) export
+ *     int <model>(const float *input1, const int64_t input1_shape[3], float *output1,
+ *                 uint64_t output1_capacity)
+ *     int <model>_infer_output_shapes(const int64_t input1_shape[3], int64_t output1_shape[R])
+ * (tools/ncnn-compile.cpp:1108-1215; test/Numerical/support/numerical_test_support.cpp:204-263),
+ * whose wrapper validates in this order (lib/Transforms/GenerateCAPI/GenerateCAPI.cpp:1053-1480):
+ * NULL pointer 1; dynamic extent <= 0 or static extent mismatch 2; minimum / multiple violated 3;
+ * element or byte count overflow 4; non-positive result extent 2; capacity (elements) too small 5.
+ * Here a dynamic model is a table of static specialisations keyed by the extents: the first call
+ * with a new shape plans (and for a run, packs and uploads) it, later calls replay it; the 8 most
+ * recently used runnable specialisations are kept. */
+typedef struct ncnn_b200_dynamic_model ncnn_b200_dynamic_model;
+
+typedef struct ncnn_b200_dim_constraint {
+  int32_t input;       /* Input index, layer order */
+  int32_t dim;         /* dimension of that input, [c,h,w] order; must be dynamic */
+  int64_t minimum;     /* > 0 */
+  int64_t multiple_of; /* > 0 */
+} ncnn_b200_dim_constraint;
+
+/* `options->input_shapes` holds one template per Input without dimensions, as for
+ * ncnn_b200_load, with -1 for every `?` extent.  Needs no GPU (shapes are planned, nothing is
+ * uploaded until the first run).  Invalid constraints fail here, as they fail the reference's
+ * compile step. */
+int ncnn_b200_dynamic_load(const char *param_path, const char *bin_path, const ncnn_b200_options *options,
+                           const ncnn_b200_dim_constraint *constraints, int32_t constraint_count,
+                           ncnn_b200_dynamic_model **out);
+void ncnn_b200_dynamic_free(ncnn_b200_dynamic_model *model);
+const char *ncnn_b200_dynamic_last_error(const ncnn_b200_dynamic_model *model);
+int ncnn_b200_dynamic_input_count(const ncnn_b200_dynamic_model *model);
+int ncnn_b200_dynamic_output_count(const ncnn_b200_dynamic_model *model);
+/* Rank and extents, -1 where the extent is dynamic (for outputs: where it follows the inputs). */
+int ncnn_b200_dynamic_input_shape(const ncnn_b200_dynamic_model *model, int index, int64_t dims[3]);
+int ncnn_b200_dynamic_output_shape(const ncnn_b200_dynamic_model *model, int index, int64_t dims[3]);
+/* `input_shapes[i]` is read for inputs with a dynamic extent (others may be NULL);
+ * `output_shapes[o]` receives rank-many extents when not NULL. */
+int ncnn_b200_dynamic_infer_output_shapes(ncnn_b200_dynamic_model *model, const int64_t *const *input_shapes,
+                                          int64_t *const *output_shapes);
+/* One image, host buffers.  `output_capacities[o]` (elements) is read for outputs with a
+ * dynamic extent. */
+int ncnn_b200_dynamic_run(ncnn_b200_dynamic_model *model, const float *const *inputs,
+                          const int64_t *const *input_shapes, float *const *outputs,
+                          const uint64_t *output_capacities);
+/* Header, manifest and stub for the two reference entry points above. */
+int ncnn_b200_dynamic_emit_stub(const ncnn_b200_dynamic_model *model, const char *name, const char *param_path,
+                                const char *bin_path, const char *directory);
 
 /* Stand-alone int8 boundary operators on device arrays (cudaStream_t as void*).
  * Element i belongs to channel (i / inner) % channels; scale/bias counts are 1 or

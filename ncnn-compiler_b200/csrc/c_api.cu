@@ -75,6 +75,7 @@ int ncnn_b200_load(const char* param_path, const char* bin_path, const ncnn_b200
     opt.device = options->device;
     opt.use_cuda_graph = options->use_cuda_graph;
     opt.plan_only = options->plan_only;
+    opt.keep_matrix_rows = options->keep_matrix_rows;
     const int64_t* p = options->input_shapes;
     for (int i = 0; i < options->input_shape_count && p != nullptr; ++i) {
       const int64_t rank = *p++;

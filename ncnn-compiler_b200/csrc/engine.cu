@@ -417,7 +417,7 @@ bool EngineImpl::import_ip(const LayerDef& l, std::string* err) {
   // NCNNOps.cpp:1247-1312: static form flattens any input with numel == K; the
   // rank-2 form [M,K] -> [M,O] keeps the rows.
   bool rows = false;
-  if (ti.rank == 2 && ti.w == n.K && ti.logical() != n.K) {
+  if (ti.rank == 2 && ti.w == n.K && (ti.logical() != n.K || opt_.keep_matrix_rows)) {
     rows = true;
   } else if (ti.logical() != n.K) {
     return fail(err, where + "input element count does not match the weight");
@@ -1236,32 +1236,71 @@ bool EngineImpl::import_layers(std::string* err) {
         to.w = static_cast<int>(d[0]);
         to.h = rank >= 2 ? static_cast<int>(d[1]) : 1;
         to.c = rank == 3 ? static_cast<int>(d[2]) : 1;
-      } else if (t == "Squeeze") {
+      } else if (t == "Squeeze" || t == "ExpandDims") {
+        // explicit axes over the logical [c,h,w] order only (import_squeeze / import_expand_dims,
+        // ImportTensor.cpp:270-341; computeSqueezeResult / computeExpandDimsResult, NCNNOps.cpp:868-927)
+        const std::vector<int64_t>* axes = l.params.get_int_array(3);
+        if (axes == nullptr) return fail(err, where + "parameter 3 (axes) must be an integer array");
+        if (t == "Squeeze" && (l.params.has(0) || l.params.has(1) || l.params.has(2) || l.params.has(11)))
+          return fail(err, where + "Squeeze requires explicit axes only");
         std::vector<int> dims;
         if (ti.rank == 3) dims = {ti.c, ti.h, ti.w};
         if (ti.rank == 2) dims = {ti.h, ti.w};
         if (ti.rank == 1) dims = {ti.w};
         std::vector<int> kept;
-        for (int v : dims)
-          if (v != 1) kept.push_back(v);
-        if (kept.empty()) kept.push_back(1);
+        if (t == "Squeeze") {
+          std::vector<char> drop(dims.size(), 0);
+          for (int64_t a : *axes) {
+            if (a < 0) a += static_cast<int64_t>(dims.size());
+            if (a < 0 || a >= static_cast<int64_t>(dims.size()) || drop[a] == 2)
+              return fail(err, where + "Squeeze axes must be unique and in range");
+            drop[a] = 2;
+          }
+          // a named axis whose extent is not 1 stays
+          for (size_t i = 0; i < dims.size(); ++i)
+            if (!(drop[i] == 2 && dims[i] == 1)) kept.push_back(dims[i]);
+          if (kept.empty()) kept.push_back(1);
+        } else {
+          const int64_t out_rank = static_cast<int64_t>(dims.size() + axes->size());
+          if (out_rank > 3) return fail(err, where + "rank-4 tensors are outside the supported path");
+          std::vector<char> fresh(static_cast<size_t>(out_rank), 0);
+          for (int64_t a : *axes) {
+            if (a < 0) a += out_rank;
+            if (a < 0 || a >= out_rank || fresh[a]) return fail(err, where + "ExpandDims axes must be unique and in output rank");
+            fresh[a] = 1;
+          }
+          size_t next = 0;
+          for (int64_t i = 0; i < out_rank; ++i) kept.push_back(fresh[i] ? 1 : dims[next++]);
+        }
         to.rank = static_cast<int>(kept.size());
         to.w = kept.back();
         to.h = to.rank >= 2 ? kept[to.rank - 2] : 1;
         to.c = to.rank == 3 ? kept[0] : 1;
-      } else if (t == "ExpandDims") {
-        return fail(err, where + "ExpandDims is outside the supported path");
       } else {  // Permute
+        // import_permute (ImportTensor.cpp:343-400): rank 2 order 0/1, rank 3 order 2 ([h,c,w]) or
+        // 4 ([w,c,h]); result extent i is the input extent perm[i]
         const int64_t order = l.params.get_int(0, 0);
-        if (ti.rank != 2 || (order != 0 && order != 1)) return fail(err, where + "only rank-2 Permute is supported");
-        to.rank = 2;
-        if (order == 1) {
-          to.h = ti.w;
-          to.w = ti.h;
-          transpose = true;
+        if (ti.rank == 2 && (order == 0 || order == 1)) {
+          to.rank = 2;
+          if (order == 1) {
+            to.h = ti.w;
+            to.w = ti.h;
+            transpose = true;
+          } else {
+            to.h = ti.h;
+            to.w = ti.w;
+          }
+        } else if (ti.rank == 3 && (order == 2 || order == 4)) {
+          const int src[3] = {ti.c, ti.h, ti.w};
+          const int perm[3] = {order == 2 ? 1 : 2, 0, order == 2 ? 2 : 1};
+          to.rank = 3;
+          to.c = src[perm[0]];
+          to.h = src[perm[1]];
+          to.w = src[perm[2]];
+          for (int i = 0; i < 3; ++i) n.relayout.perm[i] = perm[i];
+          n.relayout.permute3d = 1;
         } else {
-          to.h = ti.h;
-          to.w = ti.w;
+          return fail(err, where + "Permute supports rank-2 order 0/1 and rank-3 order 2/4 only");
         }
       }
       RelayoutParams& r = n.relayout;

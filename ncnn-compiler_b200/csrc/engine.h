@@ -28,6 +28,8 @@ struct EngineOptions {
   // 1: parse, validate, fuse and infer shapes only (no CUDA call, nothing uploaded); the
   // model can describe itself and emit its stub but cannot run -- what a compile step needs
   int plan_only = 0;
+  // 1: InnerProduct over a rank-2 [M,K] input yields [M,N] even when M is 1 (dynamic-M lowering)
+  int keep_matrix_rows = 0;
   // shape overrides for Input layers that carry no dimensions, in Input order,
   // each as ncnn dims [c,h,w] / [h,w] / [w]
   std::vector<std::vector<int64_t>> input_shapes;

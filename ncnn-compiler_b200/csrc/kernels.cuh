@@ -807,6 +807,8 @@ struct RelayoutParams {
   int src_rank, sc, sh, sw;   // logical dims (rank 1: sw; rank 2: sh x sw; rank 3: sc x sh x sw)
   int dst_rank, dc, dh, dw;
   int transpose2d;            // source is read as its rank-2 transpose
+  int permute3d;              // rank 3 to rank 3: destination extent i is source extent perm[i]
+  int perm[3];
 };
 
 __device__ __forceinline__ long long storage_offset(int rank, int c_dim, int h_dim, int w_dim,
@@ -831,6 +833,15 @@ static __global__ void k_relayout(ActRef in, ActRef out, RelayoutParams p) {
       const int col = static_cast<int>(l % p.dw);
       const int row = static_cast<int>(l / p.dw);
       src_l = static_cast<long long>(col) * p.sw + row;
+    } else if (p.permute3d) {
+      int d[3], sidx[3];
+      d[2] = static_cast<int>(l % p.dw);
+      const long long r = l / p.dw;
+      d[1] = static_cast<int>(r % p.dh);
+      d[0] = static_cast<int>(r / p.dh);
+#pragma unroll
+      for (int k = 0; k < 3; ++k) sidx[p.perm[k]] = d[k];
+      src_l = (static_cast<long long>(sidx[0]) * p.sh + sidx[1]) * p.sw + sidx[2];
     }
     const long long so = img * p.count + storage_offset(p.src_rank, p.sc, p.sh, p.sw, src_l);
     const long long dof = img * p.count + storage_offset(p.dst_rank, p.dc, p.dh, p.dw, l);

@@ -9,6 +9,7 @@
 // library exports the entry symbol and nothing else (tools/ncnn-compile.cpp:2129-2136).
 // Flag names follow the reference (tools/ncnn-compile.cpp:40-198); CPU code-generation
 // flags are accepted and ignored.
+#include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -85,7 +86,8 @@ int fail(const std::string& message) {
 int main(int argc, char** argv) {
   std::string param, bin, name, out_dir, target = "sm_100a", value;
   std::vector<std::vector<int64_t>> shapes;
-  bool verbose = false, name_only = false;
+  std::vector<ncnn_b200_dim_constraint> constraints;
+  bool verbose = false, name_only = false, dynamic = false;
   int accuracy = NCNN_B200_FP32_SPLIT;
   for (int i = 1; i < argc; ++i) {
     const std::string a = argv[i];
@@ -98,14 +100,28 @@ int main(int argc, char** argv) {
       std::vector<int64_t> dims;
       size_t pos = 0;
       while (pos <= value.size()) {
-        const size_t x = value.find('x', pos);
+        const size_t x = value.find_first_of("xX", pos);
         const std::string tok = value.substr(pos, x == std::string::npos ? std::string::npos : x - pos);
-        if (tok.empty() || tok == "?") return fail("--input-shape needs positive static extents for the sm_100a target");
-        dims.push_back(std::atoll(tok.c_str()));
+        if (tok.empty() || tok == "*") return fail("--input-shape takes CxHxW with positive extents or ? (dynamic rank is not supported by the sm_100a target)");
+        const int64_t extent = tok == "?" ? -1 : std::atoll(tok.c_str());
+        if (extent == 0 || extent < -1) return fail("--input-shape extents are positive integers or ?");
+        if (extent < 0) dynamic = true;
+        dims.push_back(extent);
         if (x == std::string::npos) break;
         pos = x + 1;
       }
       shapes.push_back(dims);
+    } else if (value_of(a, "--input-dim-constraint", &value)) {
+      // INPUT:DIM:min=N,multiple=N (docs/ncnn-compile-command-line.md 2.6)
+      ncnn_b200_dim_constraint c{};
+      long long input = 0, dim = 0, minimum = 0, multiple = 0;
+      if (std::sscanf(value.c_str(), "%lld:%lld:min=%lld,multiple=%lld", &input, &dim, &minimum, &multiple) != 4)
+        return fail("--input-dim-constraint takes INPUT:DIM:min=N,multiple=N");
+      c.input = static_cast<int32_t>(input);
+      c.dim = static_cast<int32_t>(dim);
+      c.minimum = minimum;
+      c.multiple_of = multiple;
+      constraints.push_back(c);
     } else if (value_of(a, "--accuracy-mode", &value)) {
       if (value == "fp32" || value == "fp32-split") accuracy = NCNN_B200_FP32_SPLIT;
       else if (value == "tf32") accuracy = NCNN_B200_TF32;
@@ -155,14 +171,32 @@ int main(int argc, char** argv) {
   opt.input_shape_count = static_cast<int32_t>(shapes.size());
   opt.input_shapes = flat.empty() ? nullptr : flat.data();
   opt.plan_only = 1;
-  ncnn_b200_model* model = nullptr;
-  if (ncnn_b200_load(param.c_str(), bin.c_str(), &opt, &model) != 0) return fail(ncnn_b200_last_error(nullptr));
   char real_param[4096], real_bin[4096];
   if (realpath(param.c_str(), real_param) == nullptr || realpath(bin.c_str(), real_bin) == nullptr)
     return fail("cannot resolve the model paths");
-  if (ncnn_b200_emit_stub(model, fn.c_str(), real_param, real_bin, out_dir.c_str()) != 0)
-    return fail("cannot write into " + out_dir);
-  ncnn_b200_free(model);
+  bool infer_entry = false;
+  if (dynamic) {
+    // fixed-rank dynamic extents: the stub carries the shape templates and constraints
+    ncnn_b200_dynamic_model* model = nullptr;
+    if (ncnn_b200_dynamic_load(param.c_str(), bin.c_str(), &opt, constraints.data(),
+                               static_cast<int32_t>(constraints.size()), &model) != 0)
+      return fail(ncnn_b200_last_error(nullptr));
+    for (int o = 0; o < ncnn_b200_dynamic_output_count(model); ++o) {
+      int64_t dims[3];
+      const int rank = ncnn_b200_dynamic_output_shape(model, o, dims);
+      for (int d = 0; d < rank; ++d) infer_entry = infer_entry || dims[d] < 0;
+    }
+    if (ncnn_b200_dynamic_emit_stub(model, fn.c_str(), real_param, real_bin, out_dir.c_str()) != 0)
+      return fail("cannot write into " + out_dir);
+    ncnn_b200_dynamic_free(model);
+  } else {
+    if (!constraints.empty()) return fail("--input-dim-constraint must name a dynamic (?) dimension");
+    ncnn_b200_model* model = nullptr;
+    if (ncnn_b200_load(param.c_str(), bin.c_str(), &opt, &model) != 0) return fail(ncnn_b200_last_error(nullptr));
+    if (ncnn_b200_emit_stub(model, fn.c_str(), real_param, real_bin, out_dir.c_str()) != 0)
+      return fail("cannot write into " + out_dir);
+    ncnn_b200_free(model);
+  }
 
   const std::string lib_dir = dir_of(argv[0]);
   char real_lib[4096];
@@ -187,9 +221,14 @@ int main(int argc, char** argv) {
     if (!sym.empty()) exported.push_back(sym);
   }
   pclose(pipe);
-  if (exported.size() != 1 || exported[0] != fn) {
+  std::vector<std::string> expected = {fn};
+  if (infer_entry) expected.push_back(fn + "_infer_output_shapes");
+  std::sort(exported.begin(), exported.end());
+  std::sort(expected.begin(), expected.end());
+  if (exported != expected) {
     std::remove(so.c_str());
-    return fail("export audit failed: the library must export exactly '" + fn + "'");
+    return fail("export audit failed: the library must export exactly '" + fn + "'" +
+                (infer_entry ? " and its shape inference entry" : ""));
   }
   if (verbose) std::fprintf(stderr, "wrote %s/{lib%s.so,%s.h,%s.json,%s.c}\n", out_dir.c_str(), fn.c_str(), fn.c_str(), fn.c_str(), fn.c_str());
   return 0;

@@ -23,7 +23,11 @@ class NcnnB200Error(RuntimeError):
 class _Options(ctypes.Structure):
     _fields_ = [("struct_size", ctypes.c_uint32), ("accuracy_mode", c_int32), ("device", c_int32),
                 ("use_cuda_graph", c_int32), ("input_shape_count", c_int32),
-                ("input_shapes", POINTER(c_int64)), ("plan_only", c_int32)]
+                ("input_shapes", POINTER(c_int64)), ("plan_only", c_int32), ("keep_matrix_rows", c_int32)]
+
+
+class _DimConstraint(ctypes.Structure):
+    _fields_ = [("input", c_int32), ("dim", c_int32), ("minimum", c_int64), ("multiple_of", c_int64)]
 
 
 def lib_path() -> str:
@@ -69,6 +73,19 @@ def load_library():
                                           c_void_p, c_int32, c_void_p, c_int32, c_int32, c_void_p]
     L.ncnn_b200_inner_product_int8_noalloc.argtypes = [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
                                                        c_int64, c_int32, c_int32, c_int32, c_void_p]
+    L.ncnn_b200_dynamic_load.argtypes = [c_char_p, c_char_p, POINTER(_Options), POINTER(_DimConstraint), c_int32,
+                                         POINTER(c_void_p)]
+    L.ncnn_b200_dynamic_free.argtypes = [c_void_p]
+    L.ncnn_b200_dynamic_free.restype = None
+    L.ncnn_b200_dynamic_last_error.argtypes = [c_void_p]
+    L.ncnn_b200_dynamic_last_error.restype = c_char_p
+    for f in ("ncnn_b200_dynamic_input_count", "ncnn_b200_dynamic_output_count"):
+        getattr(L, f).argtypes = [c_void_p]
+    for f in ("ncnn_b200_dynamic_input_shape", "ncnn_b200_dynamic_output_shape"):
+        getattr(L, f).argtypes = [c_void_p, c_int, POINTER(c_int64)]
+    L.ncnn_b200_dynamic_infer_output_shapes.argtypes = [c_void_p, pp_in, pp_out]
+    L.ncnn_b200_dynamic_run.argtypes = [c_void_p, pp_in, pp_in, pp_out, POINTER(ctypes.c_uint64)]
+    L.ncnn_b200_dynamic_emit_stub.argtypes = [c_void_p, c_char_p, c_char_p, c_char_p, c_char_p]
     _LIB = L
     return L
 
@@ -104,7 +121,7 @@ class Model:
             flat.extend(int(d) for d in s)
         arr = (c_int64 * max(len(flat), 1))(*flat)
         opt = _Options(ctypes.sizeof(_Options), accuracy_mode, device, 1 if use_cuda_graph else 0,
-                       len(input_shapes or []), ctypes.cast(arr, POINTER(c_int64)), 1 if plan_only else 0)
+                       len(input_shapes or []), ctypes.cast(arr, POINTER(c_int64)), 1 if plan_only else 0, 0)
         st = self._L.ncnn_b200_load(param_path.encode(), bin_path.encode() if bin_path else None, byref(opt),
                                     byref(self._h))
         if st != 0:
@@ -182,6 +199,94 @@ class Model:
     def emit_stub(self, name, param_path, bin_path, directory):
         self._check(self._L.ncnn_b200_emit_stub(self._h, name.encode(), param_path.encode(), bin_path.encode(),
                                                  directory.encode()))
+
+
+class DynamicModel:
+    """A model with fixed-rank dynamic input extents: the counterpart of the reference's
+    `--input-shape=3x?x?` libraries.  `input_shapes` holds one [c,h,w] template per Input without
+    dimensions, None (or -1) where the extent is dynamic; `constraints` are tuples
+    (input, dim, minimum, multiple_of).  Loading and shape inference need no GPU."""
+
+    def __init__(self, param_path, bin_path, input_shapes, constraints=(), accuracy_mode=FP32_SPLIT, device=-1,
+                 use_cuda_graph=True):
+        self._L = load_library()
+        self._h = c_void_p()
+        flat = []
+        for s in input_shapes:
+            flat.append(len(s))
+            flat.extend(-1 if d is None else int(d) for d in s)
+        arr = (c_int64 * max(len(flat), 1))(*flat)
+        opt = _Options(ctypes.sizeof(_Options), accuracy_mode, device, 1 if use_cuda_graph else 0,
+                       len(input_shapes), ctypes.cast(arr, POINTER(c_int64)), 0, 0)
+        lim = (_DimConstraint * max(len(constraints), 1))()
+        for k, c in enumerate(constraints):
+            lim[k] = _DimConstraint(*[int(v) for v in c])
+        st = self._L.ncnn_b200_dynamic_load(param_path.encode(), bin_path.encode() if bin_path else None, byref(opt),
+                                            lim, len(constraints), byref(self._h))
+        if st != 0:
+            raise NcnnB200Error(st, self._L.ncnn_b200_last_error(None).decode())
+        self.input_shapes = [self._shape(self._L.ncnn_b200_dynamic_input_shape, i)
+                             for i in range(self._L.ncnn_b200_dynamic_input_count(self._h))]
+        self.output_shapes = [self._shape(self._L.ncnn_b200_dynamic_output_shape, i)
+                              for i in range(self._L.ncnn_b200_dynamic_output_count(self._h))]
+
+    def _shape(self, fn, i):
+        dims = (c_int64 * 3)()
+        rank = fn(self._h, i, dims)
+        return tuple(int(dims[k]) for k in range(rank))
+
+    def close(self):
+        if self._h:
+            self._L.ncnn_b200_dynamic_free(self._h)
+            self._h = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _shape_table(self, shapes):
+        keep = [(c_int64 * 3)(*[int(d) for d in s]) if s is not None else None for s in shapes]
+        return keep, _ptr_array([ctypes.addressof(a) if a is not None else None for a in keep])
+
+    def infer_status(self, shapes):
+        """(status, output shapes) of `<model>_infer_output_shapes` for per-input [c,h,w] lists."""
+        keep, table = self._shape_table(shapes)
+        outs = [(c_int64 * 3)() for _ in self.output_shapes]
+        st = self._L.ncnn_b200_dynamic_infer_output_shapes(self._h, table,
+                                                           _ptr_array([ctypes.addressof(o) for o in outs]))
+        return st, [tuple(int(o[k]) for k in range(len(s))) for o, s in zip(outs, self.output_shapes)]
+
+    def infer(self, shapes):
+        st, out = self.infer_status(shapes)
+        if st != 0:
+            raise NcnnB200Error(st, self._L.ncnn_b200_dynamic_last_error(self._h).decode())
+        return out
+
+    def run_status(self, inputs, shapes, outputs, capacities):
+        """Status of the reference-shaped call: host arrays, per-input shapes, per-output capacities."""
+        keep, table = self._shape_table(shapes)
+        caps = (ctypes.c_uint64 * max(len(capacities), 1))(*[int(c) for c in capacities])
+        return self._L.ncnn_b200_dynamic_run(self._h, _ptr_array([x.ctypes.data for x in inputs]), table,
+                                             _ptr_array([y.ctypes.data for y in outputs]), caps)
+
+    def run(self, *inputs):
+        """One image per input, shaped like its template with concrete extents."""
+        ins = [np.ascontiguousarray(x, np.float32) for x in inputs]
+        shapes = [list(x.shape) for x in ins]
+        out_shapes = self.infer(shapes)
+        outs = [np.empty(s, np.float32) for s in out_shapes]
+        st = self.run_status(ins, shapes, outs, [y.size for y in outs])
+        if st != 0:
+            raise NcnnB200Error(st, self._L.ncnn_b200_dynamic_last_error(self._h).decode())
+        return outs
+
+    def emit_stub(self, name, param_path, bin_path, directory):
+        st = self._L.ncnn_b200_dynamic_emit_stub(self._h, name.encode(), param_path.encode(), bin_path.encode(),
+                                                 directory.encode())
+        if st != 0:
+            raise NcnnB200Error(st, "cannot write the stub")
 
 
 def _op_status(st):

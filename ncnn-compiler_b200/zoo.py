@@ -272,3 +272,25 @@ def inner_product(prefix, k, n, seed=500, int8=False, relu=True):
     net.w.layer("Input", "input", [], ["data"], f"0={k} 1=1 2=1")
     net.inner_product("ip", "data", "output", k, n, act=1 if relu else 0, std=0.02, bias_std=0.01)
     return net.w.save(prefix)
+
+
+def dynamic_convnet(prefix, seed=800, cin=3, classes=0):
+    """A network whose Input carries no dimensions (compile with `--input-shape=3x?x?`): 3x3 stride-2
+    stem, two 3x3 convolutions around a residual add, then either a 1x1 convolution to 8 channels
+    (classes=0: the result follows the input size, [8, H/2, W/2]) or global average pooling and an
+    InnerProduct (classes>0: a fixed [classes] result)."""
+    net = _Net(seed)
+    wr = net.w
+    wr.layer("Input", "input", [], ["data"], "0=0 1=0 2=0")
+    net.conv("stem", "data", "s", cin, 32, 3, 2, 1, act=1, zero_bias=False)
+    wr.layer("Split", "split", ["s"], ["a", "b"])
+    net.conv("conv1", "a", "c1", 32, 32, 3, 1, 1, act=1, zero_bias=False)
+    net.conv("conv2", "c1", "c2", 32, 32, 3, 1, 1, act=0, zero_bias=False)
+    wr.layer("Eltwise", "add", ["c2", "b"], ["sum"], "0=1")
+    wr.layer("ReLU", "relu", ["sum"], ["act"], "0=0.0")
+    if classes:
+        wr.layer("Pooling", "gap", ["act"], ["pooled"], "0=1 4=1")
+        net.inner_product("fc", "pooled", "output", 32, classes, std=0.1, bias_std=0.01)
+    else:
+        net.conv("head", "act", "output", 32, 8, 1, 1, 0, act=0, zero_bias=False)
+    return wr.save(prefix)

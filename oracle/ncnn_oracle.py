@@ -897,12 +897,40 @@ class Model:
                 dims = [src[i] if d[i] == 0 else d[i] for i in range(rank)]
                 flat = chw.reshape(dims[::-1])  # numpy infers a single -1
                 out = np.ascontiguousarray(flat.transpose(1, 2, 0)) if rank == 3 else flat
-            elif t == "Squeeze":
+            elif t in ("Squeeze", "ExpandDims"):
+                # explicit axes over the logical [c,h,w] order (computeSqueezeResult /
+                # computeExpandDimsResult, NCNNOps.cpp:868-927); a named axis that is not 1 stays
                 x = ins[0]
                 chw = x.transpose(2, 0, 1) if x.ndim == 3 else x
-                out = np.ascontiguousarray(np.squeeze(chw))
+                axes = l.params.get(3)
+                if not isinstance(axes, (list, tuple, np.ndarray)):
+                    raise ValueError(f"{t}: parameter 3 (axes) must be an integer array")
+                axes = [int(a) for a in axes]
+                if t == "Squeeze":
+                    axes = [a + chw.ndim if a < 0 else a for a in axes]
+                    keep = [d for i, d in enumerate(chw.shape) if not (i in axes and d == 1)] or [1]
+                else:
+                    rank = chw.ndim + len(axes)
+                    if rank > 3:
+                        raise ValueError("rank-4 tensors are outside the hot path")
+                    axes = [a + rank if a < 0 else a for a in axes]
+                    it = iter(chw.shape)
+                    keep = [1 if i in axes else next(it) for i in range(rank)]
+                flat = np.ascontiguousarray(chw).reshape(keep)
+                out = np.ascontiguousarray(flat.transpose(1, 2, 0)) if flat.ndim == 3 else flat
             elif t == "Permute":
-                out = np.ascontiguousarray(ins[0].T)
+                # import_permute (ImportTensor.cpp:343-400): rank 2 order 0/1; rank 3 order 2 -> [h,c,w],
+                # order 4 -> [w,c,h] (result extent i = input extent perm[i])
+                x = ins[0]
+                order = l.geti(0, 0)
+                if x.ndim == 2 and order in (0, 1):
+                    out = np.ascontiguousarray(x.T) if order == 1 else x
+                elif x.ndim == 3 and order in (2, 4):
+                    chw = x.transpose(2, 0, 1)
+                    res = chw.transpose((1, 0, 2) if order == 2 else (2, 0, 1))
+                    out = np.ascontiguousarray(res.transpose(1, 2, 0))
+                else:
+                    raise ValueError("Permute supports rank-2 order 0/1 and rank-3 order 2/4 only")
             else:
                 raise ValueError(f"layer type {t} is outside the hot path")
             env[l.tops[0]] = out

@@ -34,7 +34,7 @@ INT8_CASES = ["convolution_int8_term1", "convolution_int8_term2", "convolution_i
 NO_WEIGHTS = ["pooling", "pooling_tail", "pooling_average", "pooling_asymmetric", "pooling_global_average",
               "pooling_global_average_ignored_params", "pooling_global_max", "pooling_global_max_ignored_params",
               "pooling_same_upper", "pooling_same_lower", "eltwise_weighted", "binary_add", "binary_mul_scalar",
-              "relu", "relu_leaky", "split", "reshape", "squeeze", "permute",
+              "relu", "relu_leaky", "split", "reshape", "squeeze", "permute", "expand_dims",
               "sigmoid", "hard_sigmoid", "hard_swish", "dropout", "softmax", "softmax_channel", "softmax_height",
               "softmax_width", "softmax_negative_channel", "softmax_negative_height", "softmax_negative_width",
               "concat", "concat_height", "concat_width", "concat_negative_channel", "concat_negative_height",
