@@ -15,7 +15,7 @@
 namespace nb {
 namespace {
 
-enum NodeKind { N_CONV, N_DW, N_IP, N_GEMM, N_POOL, N_BINARY, N_UNARY, N_RELAYOUT, N_SOFTMAX, N_CONCAT, N_REMAP, N_REDUCE };
+enum NodeKind { N_CONV, N_DW, N_IP, N_GEMM, N_POOL, N_BINARY, N_UNARY, N_RELAYOUT, N_SOFTMAX, N_CONCAT, N_REMAP, N_REDUCE, N_DECONV };
 enum Impl { IMPL_NONE, IMPL_TC, IMPL_DIRECT };
 
 struct Tensor {
@@ -685,13 +685,13 @@ bool EngineImpl::import_layers(std::string* err) {
       to.is_input = false;
       nodes_.push_back(std::move(n));
     } else if (t == "Sigmoid" || t == "Swish" || t == "TanH" || t == "HardSigmoid" || t == "HardSwish" ||
-               t == "Dropout") {
+               t == "Dropout" || t == "GELU" || t == "PReLU") {
       if (l.bottoms.size() != 1 || l.tops.size() != 1) return fail(err, where + "expects one input and one output");
       const int in = by_name_.at(l.bottoms[0]);
       const Tensor ti = tensors_[resolve(in)];
       if (ti.i8) return fail(err, where + "supports one f32 tensor only");
       const bool hard = t == "HardSigmoid" || t == "HardSwish";
-      const int max_id = hard ? 1 : (t == "Dropout" ? 0 : -1);
+      const int max_id = hard ? 1 : (t == "Dropout" || t == "GELU" || t == "PReLU" ? 0 : -1);
       // validate_param_ids (NCNNImporter.cpp:271-282): ids 30 and 31 are always allowed
       for (const auto& entry : l.params.entries())
         if ((entry.first > max_id || entry.first < 0) && entry.first != 30 && entry.first != 31)
@@ -713,6 +713,18 @@ bool EngineImpl::import_layers(std::string* err) {
         // ImportActivation.cpp:617-646, ConvertDropout (NCNNToTosa.cpp:2047-2070): x * scale, identity for 1
         n.un.act = ACT_SCALE;
         n.un.act_a = l.params.get_float(0, 1.0f);
+      } else if (t == "GELU") {
+        // import_gelu (ImportActivation.cpp:543-564): the erf form only
+        if (l.params.get_int(0, 0) != 0) return fail(err, where + "invalid GELU parameters");
+        n.un.act = ACT_GELU;
+      } else if (t == "PReLU") {
+        // import_prelu (ImportActivation.cpp:504-541): one finite scalar slope, lowered as a leaky ReLU
+        if (l.params.get_int(0, 0) != 1 || l.weights.size() != 1 || l.weights[0].count() != 1)
+          return fail(err, where + "PReLU supports exactly one FP32 scalar slope");
+        const float slope = l.weights[0].as_f32()[0];
+        if (!std::isfinite(slope)) return fail(err, where + "PReLU slope must be finite");
+        n.un.act = ACT_LEAKY;
+        n.un.act_a = slope;
       } else {
         n.un.act = t == "Sigmoid" ? ACT_SIGMOID : (t == "Swish" ? ACT_SWISH : ACT_TANH);
       }
@@ -1315,6 +1327,59 @@ bool EngineImpl::import_layers(std::string* err) {
       r.dw = to.w;
       r.transpose2d = transpose ? 1 : 0;
       nodes_.push_back(std::move(n));
+    } else if (t == "Deconvolution") {
+      // import_deconvolution (ImportDetection.cpp:349-470): static fp32 2x2 kernel, stride 2, no
+      // padding, no output padding, activation none or ReLU
+      if (l.bottoms.size() != 1 || l.tops.size() != 1) return fail(err, where + "expects one input and one output");
+      static const int allowed[] = {0, 1, 2, 3, 4, 5, 6, 9, 10, 11, 12, 13, 14, 15, 16, 18, 19, 20, 21, 28, 30, 31};
+      for (const auto& entry : l.params.entries())
+        if (std::find(std::begin(allowed), std::end(allowed), entry.first) == std::end(allowed))
+          return fail(err, where + "unsupported parameter id " + std::to_string(entry.first));
+      const ParamDict& p = l.params;
+      const int64_t kw = p.get_int(1, 0), kh = p.get_int(11, kw), dw = p.get_int(2, 1), dh = p.get_int(12, dw);
+      const int64_t sw = p.get_int(3, 1), sh = p.get_int(13, sw), pl = p.get_int(4, 0), pr = p.get_int(15, pl);
+      const int64_t pt = p.get_int(14, pl), pb = p.get_int(16, pt), opr = p.get_int(18, 0), opb = p.get_int(19, opr);
+      const int64_t ow = p.get_int(20, 0), oh = p.get_int(21, ow), act = p.get_int(9, 0), has_bias = p.get_int(5, 0);
+      if (p.get_int(28, 0) != 0 || kh != 2 || kw != 2 || sh != 2 || sw != 2 || dh != 1 || dw != 1 || pt != 0 || pb != 0 ||
+          pl != 0 || pr != 0 || opb != 0 || opr != 0 || oh != 0 || ow != 0 || (act != 0 && act != 1) ||
+          l.weights.size() != static_cast<size_t>(1 + (has_bias ? 1 : 0)))
+        return fail(err, where + "only static FP32 2x2 stride-2 Deconvolution is supported");
+      const int in = by_name_.at(l.bottoms[0]);
+      const Tensor ti = tensors_[resolve(in)];
+      const WeightTensor& wt = l.weights[0];
+      const int64_t O = p.get_int(0, 0);
+      if (ti.i8 || ti.rank != 3 || wt.shape.size() != 4 || wt.shape[0] != O || wt.shape[1] != ti.c || wt.shape[2] != 2 ||
+          wt.shape[3] != 2 || static_cast<int64_t>(wt.count()) != p.get_int(6, 0))
+        return fail(err, where + "Deconvolution weight shape or weight_data_size is inconsistent");
+      if (wt.type == WeightType::kI8) return fail(err, where + "Deconvolution weight must be floating point");
+      Node n;
+      n.kind = N_DECONV;
+      n.name = l.name;
+      n.type = t;
+      n.O = static_cast<int>(O);
+      n.has_bias = has_bias == 1;
+      n.act = act == 1 ? ACT_RELU : ACT_NONE;
+      if (n.has_bias) n.bias = l.weights[1].as_f32();
+      // repack [o][c][a][b] -> [a][b][c][o]
+      const std::vector<float> w = wt.as_f32();
+      n.w_f32.resize(w.size());
+      for (int o = 0; o < n.O; ++o)
+        for (int c = 0; c < ti.c; ++c)
+          for (int k = 0; k < 4; ++k)
+            n.w_f32[(static_cast<size_t>(k) * ti.c + c) * n.O + o] = w[(static_cast<size_t>(o) * ti.c + c) * 4 + k];
+      n.flops = 2.0 * 4.0 * ti.h * ti.w * ti.c * n.O;
+      n.in = {in};
+      n.out = new_tensor(l.tops[0]);
+      Tensor& to = tensors_[n.out];
+      const std::string keep = to.name;
+      to = ti;
+      to.name = keep;
+      to.alias = -1;
+      to.is_input = false;
+      to.c = n.O;
+      to.h = 2 * ti.h;
+      to.w = 2 * ti.w;
+      nodes_.push_back(std::move(n));
     } else if (t == "Dequantize" || t == "Requantize") {
       return fail(err, where + "needs an int32 producer, which no importable layer provides; "
                                "use the operator entry points instead");
@@ -1619,6 +1684,7 @@ bool EngineImpl::prepare_weights(std::string* err) {
     if (!n.un_offset.empty()) n.d_offset = upload(n.un_offset);
     n.un.scale = n.d_scale;
     n.un.offset = n.d_offset;
+    if (n.kind == N_DECONV) n.d_w0 = upload(n.w_f32);
     if (n.kind == N_CONV) {
       const int src = resolve(n.in[0]);
       Tensor& ti = tensors_[src];
@@ -2202,6 +2268,21 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
     s.run = [=](cudaStream_t st) {
       if (vec) k_pool<4><<<grid, 256, 0, st>>>(in, out, p);
       else k_pool<1><<<grid, 256, 0, st>>>(in, out, p);
+      return launch_ok();
+    };
+    plan.steps.push_back(std::move(s));
+    return true;
+  }
+  if (node.kind == N_DECONV) {
+    const Tensor& ti = tensors_[resolve(node.in[0])];
+    const ActRef in = ref(node.in[0], n);
+    DeconvParams dp{n, ti.h, ti.w, ti.c, node.O, node.act == ACT_RELU ? 1 : 0};
+    const float* w = static_cast<const float*>(node.d_w0);
+    const float* bias = node.d_bias;
+    const int grid = grid_for(to.logical() * n);
+    s.kernel = "k_deconv2x2";
+    s.run = [=](cudaStream_t st) {
+      k_deconv2x2<<<grid, 256, 0, st>>>(in, out, w, bias, dp);
       return launch_ok();
     };
     plan.steps.push_back(std::move(s));

@@ -849,6 +849,36 @@ static __global__ void k_relayout(ActRef in, ActRef out, RelayoutParams p) {
   }
 }
 
+// ----------------------------------------------------------------- 2x2 stride-2 deconvolution
+// The only Deconvolution the reference imports (ImportDetection.cpp:349-470): out[2h+a][2w+b][o] =
+// bias[o] + sum_c in[h][w][c] * W[o][c][a][b], no kernel flip (ConvertDeconvolution,
+// NCNNToTosa.cpp:2737-2990).  Weights arrive repacked [a][b][c][o]; one thread per output value,
+// neighbouring threads neighbouring output channels.
+struct DeconvParams {
+  long long images;
+  int H, W, C, O;  // input extents, output channels
+  int relu;
+};
+
+static __global__ void k_deconv2x2(ActRef in, ActRef out, const float* __restrict__ w,
+                                   const float* __restrict__ bias, DeconvParams p) {
+  const long long total = p.images * 4ll * p.H * p.W * p.O;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int o = static_cast<int>(i % p.O);
+    long long r = i / p.O;
+    const int ow = static_cast<int>(r % (2 * p.W));
+    r /= 2 * p.W;
+    const int oh = static_cast<int>(r % (2 * p.H));
+    const long long img = r / (2 * p.H);
+    const long long src = ((img * p.H + (oh >> 1)) * p.W + (ow >> 1)) * p.C;
+    const float* wk = w + static_cast<long long>((oh & 1) * 2 + (ow & 1)) * p.C * p.O + o;
+    float acc = bias != nullptr ? bias[o] : 0.0f;
+    for (int c = 0; c < p.C; ++c) acc = __fadd_rn(__fmul_rn(act_load(in, src + c), wk[static_cast<long long>(c) * p.O]), acc);
+    act_store(out, i, p.relu ? fmaxf(acc, 0.0f) : acc);
+  }
+}
+
 // ----------------------------------------------------------------- broadcast, remap
 // BinaryOp with numpy-style broadcasting over the logical [c, h, w] dims (computeBinaryResult,
 // NCNNOps.cpp:1181-1245; ConvertBinary, NCNNToTosa.cpp:5111-5223).  Every operand is addressed as

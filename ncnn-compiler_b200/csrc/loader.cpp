@@ -641,9 +641,46 @@ bool load_layer_weights(LayerDef& l, BinCursor& c, std::string* err) {
     static const char* n[] = {"input scale", "output scale", "bias"};
     return load_counts(l, c, {{0, 1}, {1, 1}, {2, 0}}, n, true, err);
   }
+  if (t == "Deconvolution") {  // load_deconvolution_weights, graph.cpp:1573-1636
+    int64_t dyn, nout, kw, kh, bias, wsize;
+    if (!int_param(l.params, 28, 0, "dynamic_weight", &dyn, err)) return false;
+    if (dyn != 0 && dyn != 1) {
+      *err = "deconvolution dynamic_weight must be 0 or 1";
+      return false;
+    }
+    if (dyn == 1) return true;
+    if (!int_param(l.params, 0, 0, "num_output", &nout, err) || !int_param(l.params, 1, 0, "kernel_w", &kw, err) ||
+        !int_param(l.params, 11, kw, "kernel_h", &kh, err) || !int_param(l.params, 5, 0, "bias_term", &bias, err) ||
+        !int_param(l.params, 6, 0, "weight_data_size", &wsize, err))
+      return false;
+    if (nout <= 0 || kw <= 0 || kh <= 0 || wsize <= 0) {
+      *err = "deconvolution channels, kernel, stride, dilation, and weight count must be positive";
+      return false;
+    }
+    if (bias != 0 && bias != 1) {
+      *err = "deconvolution bias_term must be 0 or 1";
+      return false;
+    }
+    const int64_t per_input = nout * kh * kw;
+    if (wsize % per_input != 0) {
+      *err = "deconvolution weight count is not divisible by output/kernel size";
+      return false;
+    }
+    if (!push(l, c, wsize, 0, {nout, wsize / per_input, kh, kw}, "deconvolution weight", err)) return false;
+    return bias == 0 || push(l, c, nout, 1, {nout}, "deconvolution bias", err);
+  }
+  if (t == "PReLU") {  // load_prelu_weights, graph.cpp:1697-1709
+    int64_t count;
+    if (!int_param(l.params, 0, 0, "num_slope", &count, err)) return false;
+    if (count <= 0) {
+      *err = "PReLU num_slope must be positive";
+      return false;
+    }
+    return push(l, c, count, 1, {count}, "PReLU slope", err);
+  }
   // Layer types that carry weights in ncnn but lie outside this runtime's path:
   // their payload cannot be skipped reliably, so the file is rejected.
-  for (const char* w : {"Deconvolution", "PReLU", "MemoryData", "LayerNorm", "Embed",
+  for (const char* w : {"MemoryData", "LayerNorm", "Embed",
                         "MultiHeadAttention", "Scale", "DeconvolutionDepthWise", "InstanceNorm",
                         "GroupNorm", "RNN", "LSTM", "GRU"}) {
     if (t == w) {

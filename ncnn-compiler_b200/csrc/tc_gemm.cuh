@@ -46,7 +46,7 @@ __host__ __device__ constexpr int tc_elem_bytes(int kind) { return kind == GEMM_
 //   SQUARE       x * x                                        (ConvertUnary, :5225-5252)
 enum : int {
   ACT_NONE = 0, ACT_RELU = 1, ACT_LEAKY = 2, ACT_CLIP = 3, ACT_SIGMOID = 4, ACT_SWISH = 5, ACT_HARDSIGMOID = 6,
-  ACT_HARDSWISH = 7, ACT_TANH = 8, ACT_SCALE = 9, ACT_SQUARE = 10
+  ACT_HARDSWISH = 7, ACT_TANH = 8, ACT_SCALE = 9, ACT_SQUARE = 10, ACT_GELU = 11
 };
 // OUT_F32        plain fp32
 // OUT_F32_SPLIT  two fp32 planes: hi = value rounded to tf32, lo = value - hi
@@ -152,6 +152,8 @@ __device__ __forceinline__ float apply_act(float y, int act, float a, float b) {
   if (act == ACT_TANH) return tanhf(y);
   if (act == ACT_SCALE) return __fmul_rn(y, a);
   if (act == ACT_SQUARE) return __fmul_rn(y, y);
+  // (x * erfc(x * -1/sqrt(2))) * 0.5, the order of ConvertGELU (NCNNToTosa.cpp:4670-4738)
+  if (act == ACT_GELU) return __fmul_rn(__fmul_rn(y, erfcf(__fmul_rn(y, -0.7071067811865476f))), 0.5f);
   return y;
 }
 

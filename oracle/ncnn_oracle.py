@@ -185,6 +185,17 @@ def _load_weights(layer: Layer, b: _Bin):
                 layer.weights.append(b.read(n, 0))
             if layer.geti(18):
                 layer.weights.append(b.read(1, 1))
+    elif t == "Deconvolution":
+        # load_deconvolution_weights (graph.cpp:1573-1636): [O, I, kh, kw] then the bias
+        nout, wsize = layer.geti(0), layer.geti(6)
+        layer.weights.append(b.read(wsize, 0))
+        if layer.geti(5):
+            layer.weights.append(b.read(nout, 1))
+    elif t == "PReLU":
+        # load_prelu_weights (graph.cpp:1697-1709)
+        if layer.geti(0, 0) <= 0:
+            raise ValueError("PReLU num_slope must be positive")
+        layer.weights.append(b.read(layer.geti(0), 1))
     elif t == "Quantize":
         layer.weights.append(b.read(layer.geti(0, 1), 1))
     elif t == "Dequantize":
@@ -554,6 +565,57 @@ def op_sigmoid(x):
     return (F32(1) / (F32(1) + np.exp(-c, dtype=F32))).astype(F32)
 
 
+def op_gelu(layer: Layer, x):
+    """ConvertGELU (NCNNToTosa.cpp:4670-4738), erf form only (import_gelu, ImportActivation.cpp:543-564):
+    (x * erfc(x * -0.7071067811865476)) * 0.5, every step rounded to f32."""
+    from scipy.special import erfc
+    if layer.geti(0, 0) != 0:
+        raise ValueError("invalid GELU parameters")
+    x = x.astype(F32)
+    tail = erfc((x * F32(-0.7071067811865476)).astype(F32)).astype(F32)
+    return ((x * tail).astype(F32) * F32(0.5)).astype(F32)
+
+
+def op_deconvolution(layer: Layer, x):
+    """The one Deconvolution the reference imports (import_deconvolution, ImportDetection.cpp:349-470): static
+    fp32 2x2 kernel, stride 2, no padding; ConvertDeconvolution (NCNNToTosa.cpp:2737-2990) computes
+    out[2h+a, 2w+b, o] = bias[o] + sum_c in[h, w, c] * W[o, c, a, b] (no kernel flip), then ReLU for type 1."""
+    kw = layer.geti(1, 0)
+    geom = [layer.geti(11, kw), kw, layer.geti(13, layer.geti(3, 1)), layer.geti(3, 1), layer.geti(12, layer.geti(2, 1)),
+            layer.geti(2, 1)]
+    pl = layer.geti(4, 0)
+    pads = [pl, layer.geti(15, pl), layer.geti(14, pl), layer.geti(16, layer.geti(14, pl)), layer.geti(18, 0),
+            layer.geti(19, layer.geti(18, 0)), layer.geti(20, 0), layer.geti(21, layer.geti(20, 0))]
+    act = layer.geti(9, 0)
+    if layer.geti(28, 0) or geom != [2, 2, 2, 2, 1, 1] or any(pads) or act not in (0, 1):
+        raise ValueError("only static FP32 2x2 stride-2 Deconvolution is supported")
+    H, W, C = x.shape
+    O = layer.geti(0)
+    w = layer.weights[0].astype(F32).reshape(O, C, 2, 2)
+    bias = layer.weights[1].astype(F32) if layer.geti(5) else np.zeros(O, F32)
+    out = np.empty((2 * H, 2 * W, O), F32)
+    xs = x.astype(F32)
+    for a in range(2):
+        for bb in range(2):
+            acc = np.broadcast_to(bias, (H, W, O)).astype(F32)
+            for c in range(C):  # reduction over input channels in index order, one rounding per step
+                acc = (acc + (xs[:, :, c, None] * w[None, None, :, c, a, bb]).astype(F32)).astype(F32)
+            out[a::2, bb::2, :] = acc
+    return np.maximum(out, F32(0)) if act == 1 else out
+
+
+def op_prelu(layer: Layer, x):
+    """import_prelu (ImportActivation.cpp:504-541): exactly one finite f32 slope, lowered as ncnn.relu
+    with that slope: x >= 0 ? x : x * slope."""
+    if layer.geti(0, 0) != 1 or len(layer.weights) != 1 or layer.weights[0].size != 1:
+        raise ValueError("PReLU supports exactly one FP32 scalar slope")
+    slope = F32(layer.weights[0].reshape(-1)[0])
+    if not np.isfinite(slope):
+        raise ValueError("PReLU slope must be finite")
+    x = x.astype(F32)
+    return np.where(x >= 0, x, (x * slope).astype(F32)).astype(F32)
+
+
 def op_swish(x):
     """ConvertSwish (NCNNToTosa.cpp:3702-3720): x * sigmoid(x), no clamp."""
     x = x.astype(F32)
@@ -845,6 +907,12 @@ class Model:
                 out = op_sigmoid(ins[0])
             elif t == "Swish":
                 out = op_swish(ins[0])
+            elif t == "Deconvolution":
+                out = op_deconvolution(l, ins[0])
+            elif t == "GELU":
+                out = op_gelu(l, ins[0])
+            elif t == "PReLU":
+                out = op_prelu(l, ins[0])
             elif t == "TanH":
                 out = np.tanh(ins[0].astype(F32), dtype=F32)  # ConvertTanH (NCNNToTosa.cpp:3722-3736)
             elif t in ("HardSigmoid", "HardSwish"):

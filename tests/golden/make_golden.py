@@ -26,7 +26,8 @@ F32_CASES = ["convolution", "convolution_no_bias", "convolution_dilated", "convo
              "convolution_fp16_storage", "convolution_depthwise", "convolution_depthwise_fp16_storage",
              "convolution_depthwise_7x7", "convolution_depthwise_asymmetric",
              "convolution_depthwise_same_upper", "convolution_depthwise_same_lower", "inner_product",
-             "inner_product_dynamic_m", "inner_product_fused_relu", "batch_norm", "gemm"]
+             "inner_product_dynamic_m", "inner_product_fused_relu", "batch_norm", "gemm", "deconvolution",
+             "deconvolution_no_bias", "deconvolution_tiny_head"]
 INT8_CASES = ["convolution_int8_term1", "convolution_int8_term2", "convolution_int8_term101",
               "convolution_int8_term102", "depthwise_int8_term1", "depthwise_int8_term2",
               "depthwise_int8_term101", "depthwise_int8_term102", "inner_product_int8_term1",
@@ -34,7 +35,7 @@ INT8_CASES = ["convolution_int8_term1", "convolution_int8_term2", "convolution_i
 NO_WEIGHTS = ["pooling", "pooling_tail", "pooling_average", "pooling_asymmetric", "pooling_global_average",
               "pooling_global_average_ignored_params", "pooling_global_max", "pooling_global_max_ignored_params",
               "pooling_same_upper", "pooling_same_lower", "eltwise_weighted", "binary_add", "binary_mul_scalar",
-              "relu", "relu_leaky", "split", "reshape", "squeeze", "permute", "expand_dims",
+              "relu", "relu_leaky", "split", "reshape", "squeeze", "permute", "expand_dims", "gelu",
               "sigmoid", "hard_sigmoid", "hard_swish", "dropout", "softmax", "softmax_channel", "softmax_height",
               "softmax_width", "softmax_negative_channel", "softmax_negative_height", "softmax_negative_width",
               "concat", "concat_height", "concat_width", "concat_negative_channel", "concat_negative_height",

@@ -60,7 +60,7 @@ def test_model_name_sanitising_follows_the_reference(pkg, given, want):
 
 def test_rejects_what_the_runtime_cannot_run(pkg, tmp_path):
     from conftest import FIXTURES
-    r = compile_model(os.path.join(FIXTURES, "gelu.param"), str(tmp_path / "o"), extra=[f"--bin={fixture('relu')[1]}"])
+    r = compile_model(os.path.join(FIXTURES, "detection_output.param"), str(tmp_path / "o"), extra=[f"--bin={fixture('relu')[1]}"])
     assert r.returncode != 0 and "outside the supported path" in r.stderr
     r = compile_model(fixture("relu")[0], str(tmp_path / "o2"), extra=["--target=x86_64"])
     assert r.returncode != 0

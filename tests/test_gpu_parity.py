@@ -328,7 +328,7 @@ def test_null_pointer_and_bad_batch_status(pkg, tmp_path):
 
 
 def test_unsupported_layers_fail_loudly(pkg, tmp_path):
-    for name in ("deconvolution", "gelu", "permute_rank4", "concat_rank4"):
+    for name in ("detection_output", "permute_rank4", "concat_rank4"):
         param = os.path.join(FIXTURES, name + ".param")
         with pytest.raises(pkg.NcnnB200Error) as e:
             pkg.Model(param, os.path.join(FIXTURES, "relu.bin"))
@@ -392,14 +392,14 @@ def test_residual_block_operand_formats(pkg, oracle, tmp_path, monkeypatch, halo
 
 
 # ------------------------------------------------------------------ operators next to the hot path
-ELEMENTWISE_FIXTURES = ["sigmoid", "hard_sigmoid", "hard_swish", "dropout", "softmax", "softmax_channel",
+ELEMENTWISE_FIXTURES = ["gelu", "sigmoid", "hard_sigmoid", "hard_swish", "dropout", "softmax", "softmax_channel",
                         "softmax_height", "softmax_width", "softmax_negative_channel", "softmax_negative_height",
                         "softmax_negative_width", "split_three"]
 
 
 @pytest.mark.parametrize("name", ELEMENTWISE_FIXTURES)
 def test_reference_fixture_activation_softmax(pkg, oracle, name):
-    """Sigmoid / HardSigmoid / HardSwish / Dropout / Softmax fixtures of the reference: fp32 element-wise
+    """GELU / Sigmoid / HardSigmoid / HardSwish / Dropout / Softmax fixtures of the reference: fp32 element-wise
     math with exp in it is held to 2e-6 relative L2 (the GPU's expf differs from libm by an ulp or two);
     multiply/clamp-only operators and the Split+Concat chain are exact."""
     param, bin_ = fixture(name)
@@ -492,6 +492,78 @@ def test_reference_fixture_remap_ops_exact(pkg, oracle, name):
     x = np.random.default_rng(len(name) + 40).standard_normal((4, *shapes[0])).astype(np.float32)
     got, want = run_both(pkg, oracle, param, bin_, x, 0)
     assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("name,shape", [("deconvolution", (2, 2, 3)), ("deconvolution_no_bias", (2, 2, 3)),
+                                        ("deconvolution_tiny_head", (16, 2, 2))])
+def test_reference_fixture_deconvolution(pkg, oracle, name, shape):
+    """2x2 stride-2 Deconvolution, the only form the reference imports; its tests allow 1e-6 (supported_ops_test.cpp:569-619)."""
+    param, bin_ = fixture(name)
+    x = np.random.default_rng(len(name)).uniform(-1, 1, (5, *shape)).astype(np.float32)
+    got, want = run_both(pkg, oracle, param, bin_, x, 0)
+    assert got.shape == want.shape and np.max(np.abs(got - want)) <= 1e-6
+
+
+def test_deconvolution_upsampling_head(pkg, oracle, tmp_path):
+    """A detection-style head: 3x3 convolution -> 2x2 stride-2 Deconvolution + ReLU -> 1x1 convolution, at a size
+    where the convolutions take the tensor-core path."""
+    import struct
+    rng = np.random.default_rng(77)
+    c, h, w, up = 32, 12, 20, 24
+    lines = ["7767517", "4 4", f"Input input 0 1 data 0={w} 1={h} 2={c}",
+             f"Convolution c1 1 1 data a 0={c} 1=3 4=1 5=1 6={c * c * 9} 9=1",
+             f"Deconvolution up 1 1 a b 0={up} 1=2 3=2 5=1 6={up * c * 4} 9=1",
+             f"Convolution c2 1 1 b output 0=8 1=1 5=1 6={8 * up}"]
+    (tmp_path / "m.param").write_text("\n".join(lines) + "\n")
+    blob = b""
+    for count, nb in [(c * c * 9, c), (up * c * 4, up), (8 * up, 8)]:
+        blob += struct.pack("<I", 0) + (rng.standard_normal(count) * 0.1).astype(np.float32).tobytes()
+        blob += (rng.standard_normal(nb) * 0.1).astype(np.float32).tobytes()
+    (tmp_path / "m.bin").write_bytes(blob)
+    x = rng.uniform(-1, 1, (6, c, h, w)).astype(np.float32)
+    got, want = run_both(pkg, oracle, str(tmp_path / "m.param"), str(tmp_path / "m.bin"), x, 0)
+    assert got.shape == (6, 8, 2 * h, 2 * w) and rel_l2(got, want) <= 1e-4
+
+
+def test_gelu_negative_tail_and_prelu(pkg, oracle, tmp_path):
+    """The reference's tail case for GELU (supported_ops_test.cpp:940-955, tolerance 1e-6 there), and PReLU with
+    its single slope, which the reference lowers as a leaky ReLU (ImportActivation.cpp:504-541): exact."""
+    x = np.array([-10, -8, -6, -5, -4, -3, -2, -1, 0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 0.5], np.float32).reshape(1, 2, 2, 5)
+    param, bin_ = fixture("gelu")
+    got, want = run_both(pkg, oracle, param, bin_, x, 0)
+    assert np.max(np.abs(got - want)) <= 1e-6 and np.all(got[x <= -6] == 0) == np.all(want[x <= -6] == 0)
+    p = tmp_path / "prelu.param"
+    p.write_text("7767517\n2 2\nInput input 0 1 data 0=5 1=2 2=2\nPReLU prelu 1 1 data output 0=1\n")
+    (tmp_path / "prelu.bin").write_bytes(np.float32(0.25).tobytes())
+    got, want = run_both(pkg, oracle, str(p), str(tmp_path / "prelu.bin"), x, 0)
+    assert np.array_equal(got, want) and np.array_equal(got, np.where(x >= 0, x, x * np.float32(0.25)))
+    p.write_text("7767517\n2 2\nInput input 0 1 data 0=5 1=2 2=2\nPReLU prelu 1 1 data output 0=2\n")
+    (tmp_path / "prelu.bin").write_bytes(np.zeros(2, np.float32).tobytes())
+    with pytest.raises(pkg.NcnnB200Error, match="exactly one FP32 scalar slope"):
+        pkg.Model(str(p), str(tmp_path / "prelu.bin"))
+
+
+@pytest.mark.parametrize("name", ["squeeze", "expand_dims", "permute", "reshape"])
+def test_reference_fixture_rank_changes_exact(pkg, oracle, name):
+    """Squeeze / ExpandDims with explicit axes, rank-2 Permute, Reshape (supported_ops_test.cpp:977-1024): copies."""
+    param, bin_ = fixture(name)
+    shapes = _input_shape(pkg, param, bin_)
+    x = np.random.default_rng(len(name) + 60).standard_normal((3, *shapes[0])).astype(np.float32)
+    got, want = run_both(pkg, oracle, param, bin_, x, 0)
+    assert got.shape == want.shape and np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("order,c,h,w", [(2, 3, 4, 5), (4, 3, 4, 5), (2, 8, 1, 6), (4, 1, 7, 2)])
+def test_rank3_permute_exact(pkg, oracle, tmp_path, order, c, h, w):
+    """Permute order 2 ([c,h,w] -> [h,c,w]) and 4 ([c,h,w] -> [w,c,h]), import_permute ImportTensor.cpp:343-400."""
+    param = tmp_path / "p.param"
+    param.write_text(f"7767517\n2 2\nInput input 0 1 data 0={w} 1={h} 2={c}\nPermute permute 1 1 data output 0={order}\n")
+    bin_ = tmp_path / "p.bin"
+    bin_.write_bytes(b"")
+    x = np.arange(2 * c * h * w, dtype=np.float32).reshape(2, c, h, w)
+    got, want = run_both(pkg, oracle, str(param), str(bin_), x, 0)
+    ref = x.transpose(0, 2, 1, 3) if order == 2 else x.transpose(0, 3, 1, 2)
+    assert np.array_equal(want, ref) and np.array_equal(got, ref)
 
 
 @pytest.mark.parametrize("name", ["binary_mul_channel", "binary_mul_reverse_broadcast"])

@@ -380,3 +380,67 @@ def test_reduction_mean_fixtures(oracle):
     assert got.shape == (4,) and np.allclose(got, x.mean(axis=(1, 2)), rtol=1e-6, atol=1e-7)
     got = _run_fixture(oracle, "reduction_mean_keepdims_coeff", x)  # keepdims, coeff 0.5
     assert got.shape == (4, 1, 1) and np.allclose(got[:, 0, 0], 0.5 * x.mean(axis=(1, 2)), rtol=1e-6, atol=1e-7)
+
+
+def test_squeeze_expand_dims_permute_by_hand(oracle, tmp_path):
+    """Explicit axes only; a named axis that is not 1 stays (computeSqueezeResult, NCNNOps.cpp:868-901);
+    ExpandDims axes index the result rank (:903-927); rank-3 Permute orders 2 and 4."""
+    x = np.arange(12, dtype=F32).reshape(3, 1, 4)
+    assert np.array_equal(_run_fixture(oracle, "squeeze", x), x.reshape(3, 4))
+    assert np.array_equal(_run_fixture(oracle, "expand_dims", x), x.reshape(3, 1, 4))  # squeeze axis 1, expand at -2
+    assert np.array_equal(_run_fixture(oracle, "permute", x), x.reshape(3, 4).T)
+
+    def run(text, x):
+        p = tmp_path / "m.param"
+        p.write_text(text)
+        (tmp_path / "m.bin").write_bytes(b"")
+        return oracle.Model(str(p), str(tmp_path / "m.bin")).run([x])[0]
+
+    head = "7767517\n2 2\nInput input 0 1 data 0=4 1=1 2=3\n"
+    assert run(head + "Squeeze s 1 1 data output -23303=2,0,1\n", x).shape == (3, 4)   # axis 0 has extent 3: kept
+    assert run(head + "Squeeze s 1 1 data output -23303=1,-2\n", x).shape == (3, 4)
+    with pytest.raises(ValueError):
+        run(head + "Squeeze s 1 1 data output 0=1\n", x)                                 # flags instead of axes
+    y = np.arange(24, dtype=F32).reshape(2, 3, 4)
+    head = "7767517\n2 2\nInput input 0 1 data 0=4 1=3 2=2\n"
+    assert np.array_equal(run(head + "Permute p 1 1 data output 0=2\n", y), y.transpose(1, 0, 2))
+    assert np.array_equal(run(head + "Permute p 1 1 data output 0=4\n", y), y.transpose(2, 0, 1))
+
+
+def test_gelu_and_prelu_by_hand(oracle, tmp_path):
+    """GELU erf form (x * erfc(-x/sqrt 2)) * 0.5 against the closed form in double; PReLU = leaky ReLU with the
+    stored slope; both reject what the reference's importers reject."""
+    import math
+    x = np.array([-10, -8, -6, -5, -4, -3, -2, -1, 0, 1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 0.5], F32).reshape(2, 2, 5)
+    got = _run_fixture(oracle, "gelu", x).reshape(-1)
+    want = [0.5 * float(v) * (1.0 + math.erf(float(v) / math.sqrt(2.0))) for v in x.reshape(-1)]
+    assert np.max(np.abs(got - np.array(want))) <= 1e-6
+    (tmp_path / "m.bin").write_bytes(np.float32(-0.5).tobytes())
+    p = tmp_path / "m.param"
+    p.write_text("7767517\n2 2\nInput input 0 1 data 0=5 1=2 2=2\nPReLU prelu 1 1 data output 0=1\n")
+    got = oracle.Model(str(p), str(tmp_path / "m.bin")).run([x])[0]
+    assert np.array_equal(got, np.where(x >= 0, x, x * F32(-0.5)))
+    p.write_text("7767517\n2 2\nInput input 0 1 data 0=5 1=2 2=2\nGELU gelu 1 1 data output 0=1\n")
+    with pytest.raises(ValueError):
+        oracle.Model(str(p), str(tmp_path / "m.bin")).run([x])
+
+
+def test_deconvolution_by_hand(oracle):
+    """2x2 stride-2 transposed convolution with the reference's literal weights (generate_bins.py:62-78) and its
+    test input (supported_ops_test.cpp:569-599): out[2h+a, 2w+b, o] = bias[o] + sum_c x[c,h,w] * W[o,c,a,b], ReLU."""
+    x = np.array([(i + 1) * (0.25 if i % 2 == 0 else -0.20) for i in range(12)], F32).reshape(2, 2, 3)  # [c,h,w]
+    got = _run_fixture(oracle, "deconvolution", x)
+    w = np.array([0.10, 0.20, 0.30, 0.40, -0.50, -0.60, -0.70, -0.80, -0.15, 0.25, -0.35, 0.45, 0.55, -0.65, 0.75, -0.85],
+                 np.float64).reshape(2, 2, 2, 2)
+    bias = np.array([-0.05, 0.10])
+    want = np.zeros((2, 4, 6))
+    for o in range(2):
+        for h in range(2):
+            for ww in range(3):
+                for a in range(2):
+                    for b in range(2):
+                        want[o, 2 * h + a, 2 * ww + b] = bias[o] + sum(float(x[c, h, ww]) * w[o, c, a, b] for c in range(2))
+    want = np.maximum(want, 0)
+    assert got.shape == (2, 4, 6) and np.max(np.abs(got - want)) <= 1e-6
+    assert np.all(got >= 0) and np.any(got == 0) and np.any(got > 0)   # what the reference's test also asserts
+    assert _run_fixture(oracle, "deconvolution_tiny_head", np.ones((16, 2, 2), F32)).shape == (1, 4, 4)
