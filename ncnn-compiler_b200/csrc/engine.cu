@@ -528,7 +528,10 @@ bool EngineImpl::import_pool(const LayerDef& l, std::string* err) {
   const int mode = static_cast<int>(p.get_int(5, 0));
   if (kind != 0 && kind != 1) return fail(err, where + "pooling kind or boolean mode parameter is invalid");
   if (mode < 0 || mode > 3) return fail(err, where + "pooling pad_mode must be in [0, 3]");
-  if (p.get_int(7, 0) != 0) return fail(err, where + "adaptive pooling is outside the supported path");
+  const int64_t adaptive = p.get_int(7, 0);
+  if ((global != 0 && global != 1) || (adaptive != 0 && adaptive != 1))
+    return fail(err, where + "pooling kind or boolean mode parameter is invalid");
+  if (adaptive && !global && ti.i8) return fail(err, where + "dynamic or adaptive signed i8 pooling is not supported");
   if (ti.i8 && kind != 0) return fail(err, where + "signed i8 pooling only supports maximum");
   Node n;
   n.kind = N_POOL;
@@ -552,6 +555,19 @@ bool EngineImpl::import_pool(const LayerDef& l, std::string* err) {
     pp.OH = pp.OW = 1;
     to.rank = 1;
     to.w = ti.c;
+  } else if (adaptive) {
+    // ImportPooling.cpp:66-69, NCNNOps.cpp:577-586: out_w (8) / out_h (18, default out_w), -233 = the input extent
+    const int64_t out_w = p.get_int(8, 0), out_h = p.get_int(18, out_w);
+    pp.OH = out_h == -233 ? ti.h : static_cast<int>(out_h);
+    pp.OW = out_w == -233 ? ti.w : static_cast<int>(out_w);
+    if (pp.OH <= 0 || pp.OW <= 0) return fail(err, where + "adaptive pooling output dimensions must be positive");
+    pp.adaptive = 1;
+    pp.KH = pp.KW = pp.sh = pp.sw = 1;
+    pp.pt = pp.pl = 0;
+    to.rank = 3;
+    to.c = ti.c;
+    to.h = pp.OH;
+    to.w = pp.OW;
   } else {
     if (kw <= 0 || kh <= 0 || sw <= 0 || sh <= 0) return fail(err, where + "kernel and stride must be positive");
     if (pl < 0 || pr < 0 || pt < 0 || pb < 0) return fail(err, where + "padding must be non-negative");

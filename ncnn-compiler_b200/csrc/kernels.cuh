@@ -318,6 +318,10 @@ struct PoolParams {
   int H, W, C, OH, OW;
   int kind;  // 0 max, 1 average over in-bounds elements
   int KH, KW, sh, sw, pt, pl;
+  // adaptive windows [floor(o*in/out), ceil((o+1)*in/out)) per axis (ConvertPooling's adaptive
+  // branch, NCNNToTosa.cpp:1706-1745); an axis whose output extent equals "same as input" has
+  // one-element windows, which the same formula yields
+  int adaptive;
 };
 
 template <int VEC>
@@ -335,13 +339,21 @@ static __global__ void k_pool(ActRef in, ActRef out, PoolParams p) {
     float acc[VEC];
 #pragma unroll
     for (int e = 0; e < VEC; ++e) acc[e] = p.kind == 0 ? -INFINITY : 0.0f;
+    int hb, he, wb, we;
+    if (p.adaptive) {
+      hb = static_cast<int>(static_cast<long long>(oh) * p.H / p.OH);
+      he = static_cast<int>((static_cast<long long>(oh + 1) * p.H + p.OH - 1) / p.OH);
+      wb = static_cast<int>(static_cast<long long>(ow) * p.W / p.OW);
+      we = static_cast<int>((static_cast<long long>(ow + 1) * p.W + p.OW - 1) / p.OW);
+    } else {
+      hb = max(oh * p.sh - p.pt, 0);
+      he = min(oh * p.sh - p.pt + p.KH, p.H);
+      wb = max(ow * p.sw - p.pl, 0);
+      we = min(ow * p.sw - p.pl + p.KW, p.W);
+    }
     int count = 0;
-    for (int kh = 0; kh < p.KH; ++kh) {
-      const int ih = oh * p.sh - p.pt + kh;
-      if (ih < 0 || ih >= p.H) continue;
-      for (int kw = 0; kw < p.KW; ++kw) {
-        const int iw = ow * p.sw - p.pl + kw;
-        if (iw < 0 || iw >= p.W) continue;
+    for (int ih = hb; ih < he; ++ih) {
+      for (int iw = wb; iw < we; ++iw) {
         const long long idx = ((img * p.H + ih) * p.W + iw) * p.C + c;
         float v[VEC];
         if (VEC == 4) {

@@ -474,6 +474,32 @@ def op_gemm(layer: Layer, a: np.ndarray) -> np.ndarray:
     return y
 
 
+def _adaptive_pooling(layer: Layer, x: np.ndarray, kind: int) -> np.ndarray:
+    """Adaptive mode (ImportPooling.cpp:66-69; ConvertPooling NCNNToTosa.cpp:1706-1745,1768-1870): out_w = param 8,
+    out_h = param 18 (default out_w), -233 keeps the input extent; window of output o on an axis is
+    [floor(o*in/out), ceil((o+1)*in/out)); max, or the row-major sequential sum divided by rows*columns."""
+    if x.dtype == np.int8:
+        raise ValueError("dynamic or adaptive signed i8 pooling is not supported")
+    H, W, C = x.shape
+    out_w = layer.geti(8, 0)
+    out_h = layer.geti(18, out_w)
+    OH = H if out_h == -233 else out_h
+    OW = W if out_w == -233 else out_w
+    if OH <= 0 or OW <= 0:
+        raise ValueError("adaptive pooling output dimensions must be positive")
+    y = np.empty((OH, OW, C), F32)
+    for oh in range(OH):
+        hb, he = (oh * H) // OH, ((oh + 1) * H + OH - 1) // OH
+        for ow in range(OW):
+            wb, we = (ow * W) // OW, ((ow + 1) * W + OW - 1) // OW
+            acc = np.full(C, -np.inf if kind == 0 else 0.0, F32)
+            for r in range(hb, he):
+                for c in range(wb, we):
+                    acc = np.maximum(acc, x[r, c]) if kind == 0 else (acc + x[r, c]).astype(F32)
+            y[oh, ow] = acc if kind == 0 else (acc / F32((he - hb) * (we - wb))).astype(F32)
+    return y
+
+
 def op_pooling(layer: Layer, x: np.ndarray) -> np.ndarray:
     """ConvertPooling static branch (NCNNToTosa.cpp:1879-1994)."""
     L = _ops()
@@ -485,9 +511,9 @@ def op_pooling(layer: Layer, x: np.ndarray) -> np.ndarray:
     mode = layer.geti(5, 0)
     if layer.geti(4):  # global: kernel = H x W, result shape [C] (ImportPooling.cpp:71-77)
         kh, kw, sh, sw, pt, pl, OH, OW = H, W, 1, 1, 0, 0, 1, 1
+    elif layer.geti(7):
+        return _adaptive_pooling(layer, x, kind)
     else:
-        if layer.geti(7):
-            raise ValueError("adaptive pooling is outside the hot path")
         if layer.geti(6) and (pt or pb or pl or pr):
             raise ValueError("avgpool_count_include_pad=1 is rejected by the reference's strict gate")
         if mode in (2, 3):

@@ -63,6 +63,8 @@ def test_constraints_are_checked_at_load_like_the_compile_step(pkg):
     ("sigmoid_dynamic", [3, None, None], [3, 5, 7], [(3, 5, 7)]),
     ("pooling_global_average_dynamic", [3, None, None], [3, 9, 4], [(3,)]),
     ("pooling_padded_max_dynamic", [3, None, None], [3, 9, 10], None),
+    ("pooling_adaptive_average_dynamic", [3, None, None], [3, 9, 10], [(3, 2, 3)]),
+    ("pooling_adaptive_max_dynamic", [3, None, None], [3, 9, 10], [(3, 2, 10)]),
     ("slice_dynamic", [3, None, None], [3, 4, 6], [(2, 4, 6), (1, 4, 6)]),
     ("squeeze_dynamic", [1, None, None], [1, 5, 6], [(5, 6)]),
     ("permute_dynamic", [1, None, None], [1, 5, 6], [(6, 5)]),
@@ -173,6 +175,8 @@ def test_rejects_insufficient_capacity(pkg):
     ("softmax_dynamic", [3, None, None], [[3, 4, 4], [3, 5, 12]]),
     ("pooling_global_average_dynamic", [3, None, None], [[3, 6, 6], [3, 9, 4]]),
     ("pooling_padded_max_dynamic", [3, None, None], [[3, 6, 6], [3, 9, 10]]),
+    ("pooling_adaptive_average_dynamic", [3, None, None], [[3, 6, 6], [3, 9, 10], [3, 1, 2]]),
+    ("pooling_adaptive_max_dynamic", [3, None, None], [[3, 6, 6], [3, 9, 10], [3, 1, 2]]),
     ("slice_dynamic", [3, None, None], [[3, 4, 6], [3, 8, 5]]),
     ("squeeze_dynamic", [1, None, None], [[1, 5, 6], [1, 2, 9]]),
     ("permute_dynamic", [1, None, None], [[1, 5, 6], [1, 2, 9]]),

@@ -525,6 +525,19 @@ def test_deconvolution_upsampling_head(pkg, oracle, tmp_path):
     assert got.shape == (6, 8, 2 * h, 2 * w) and rel_l2(got, want) <= 1e-4
 
 
+@pytest.mark.parametrize("kind", [0, 1])
+@pytest.mark.parametrize("c,h,w,oh,ow", [(8, 14, 14, 7, 7), (12, 9, 10, 2, 3), (4, 5, 7, 5, 3), (16, 13, 6, 4, -233), (3, 7, 7, 1, 1)])
+def test_adaptive_pooling(pkg, oracle, tmp_path, kind, c, h, w, oh, ow):
+    """Adaptive max is exact; adaptive average sums its window row by row like the oracle and divides once."""
+    (tmp_path / "a.param").write_text(f"7767517\n2 2\nInput input 0 1 data 0={w} 1={h} 2={c}\n"
+                                       f"Pooling pool 1 1 data output 0={kind} 7=1 8={ow} 18={oh}\n")
+    (tmp_path / "a.bin").write_bytes(b"")
+    x = np.random.default_rng(c + h).standard_normal((3, c, h, w)).astype(np.float32)
+    got, want = run_both(pkg, oracle, str(tmp_path / "a.param"), str(tmp_path / "a.bin"), x, 0)
+    assert got.shape == (3, c, oh, w if ow == -233 else ow)
+    assert np.array_equal(got, want)
+
+
 def test_gelu_negative_tail_and_prelu(pkg, oracle, tmp_path):
     """The reference's tail case for GELU (supported_ops_test.cpp:940-955, tolerance 1e-6 there), and PReLU with
     its single slope, which the reference lowers as a leaky ReLU (ImportActivation.cpp:504-541): exact."""

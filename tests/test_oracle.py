@@ -444,3 +444,23 @@ def test_deconvolution_by_hand(oracle):
     assert got.shape == (2, 4, 6) and np.max(np.abs(got - want)) <= 1e-6
     assert np.all(got >= 0) and np.any(got == 0) and np.any(got > 0)   # what the reference's test also asserts
     assert _run_fixture(oracle, "deconvolution_tiny_head", np.ones((16, 2, 2), F32)).shape == (1, 4, 4)
+
+
+def test_adaptive_pooling_by_hand(oracle, tmp_path):
+    """Adaptive windows [floor(o*in/out), ceil((o+1)*in/out)) (NCNNToTosa.cpp:1706-1745): 5 -> 3 gives [0,2) [1,4) [3,5)."""
+    x = np.arange(2 * 5 * 4, dtype=F32).reshape(2, 5, 4)
+    p = tmp_path / "a.param"
+    (tmp_path / "a.bin").write_bytes(b"")
+
+    def run(params):
+        p.write_text(f"7767517\n2 2\nInput input 0 1 data 0=4 1=5 2=2\nPooling pool 1 1 data output {params}\n")
+        return oracle.Model(str(p), str(tmp_path / "a.bin")).run([x])[0]
+
+    got = run("0=1 7=1 8=2 18=3")
+    rows = [(0, 2), (1, 4), (3, 5)]
+    want = np.stack([np.stack([x[:, a:b, c:d].mean(axis=(1, 2)) for c, d in [(0, 2), (2, 4)]], -1) for a, b in rows], 1)
+    assert got.shape == (2, 3, 2) and np.allclose(got, want, rtol=0, atol=1e-6)
+    got = run("0=0 7=1 8=-233 18=1")   # width kept, height pooled to one row
+    assert got.shape == (2, 1, 4) and np.array_equal(got, x.max(axis=1, keepdims=True))
+    with pytest.raises(ValueError):
+        run("0=0 7=1 8=0 18=0")
