@@ -186,16 +186,26 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
       staging = 0;
     }
   }
-  // Shallow contractions (a few K blocks per tile) are bound by the epilogue: a second epilogue
-  // group drains every other tile, with a staging area of its own.
+  // Shallow contractions (a few K blocks per tile) are bound by the epilogue, which runs one warp
+  // per scheduler and so pays every instruction's latency in full: a second epilogue group drains
+  // every other tile, with a staging area of its own.  Two groups with two staging tiles each beat
+  // one group with four, so the tile count per group is reduced before the second group is given up.
   const long long tiles_total = static_cast<long long>(p.tiles_m) * p.tiles_n;
-  p.staging_bytes = staging;
   p.epi_groups = 1;
-  if (p.tma_store && p.k_blocks <= 4 && tiles_total >= 2ll * sm_count &&
-      (kTcSmemBudget - 2 * staging) / p.stage_bytes >= 4) {
-    p.epi_groups = 2;
-    staging *= 2;
+  if (p.tma_store && p.k_blocks <= 4 && tiles_total >= 2ll * sm_count) {
+    const int res_bytes = res_mode != RES_NONE ? 16384 : 0;
+    for (int bufs : {4, 3, 2}) {
+      const int both = 2 * (res_bytes + bufs * out_tile);
+      if (bufs > p.out_bufs) continue;
+      if ((kTcSmemBudget - both) / p.stage_bytes >= (bufs == 2 ? 3 : 4)) {
+        p.epi_groups = 2;
+        p.out_bufs = bufs;
+        staging = both;
+        break;
+      }
+    }
   }
+  p.staging_bytes = staging / p.epi_groups;
   const int budget = kTcSmemBudget - staging;
   p.stages = std::max(2, std::min(kTcMaxStages, budget / p.stage_bytes));
   L->smem_bytes = p.stages * p.stage_bytes + staging + 1024;
