@@ -177,11 +177,13 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
       staging = (res_mode != RES_NONE ? 16384 : 0) + bufs * out_tile;
       if ((kTcSmemBudget - staging) / p.stage_bytes >= 3 || bufs == 2) break;
     }
-    // Deep contractions hide even a slow epilogue behind the main loop; there a third ring
-    // stage is worth more than the staging tiles.
+    // Deep contractions hide even a slow epilogue behind the next tile's main loop; there a third
+    // ring stage is worth more than the staging tiles.  With one tile per CTA nothing hides the
+    // epilogue, and the direct one takes several times as long as the staged one.
     const int with = (kTcSmemBudget - staging) / p.stage_bytes;
     const int without = (kTcSmemBudget) / p.stage_bytes;
-    if (with < 3 && without >= 3 && p.k_blocks >= kDirectEpilogueDepth) {
+    const long long tiles_all = static_cast<long long>(p.tiles_m) * p.tiles_n;
+    if (with < 3 && without >= 3 && p.k_blocks >= kDirectEpilogueDepth && tiles_all > sm_count) {
       p.tma_store = 0;
       staging = 0;
     }
