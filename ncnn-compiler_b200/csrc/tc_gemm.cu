@@ -2,6 +2,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -131,6 +132,12 @@ int choose_block_n(long long tiles_m, int N, int sm_count, int step) {
   return best;
 }
 
+// NCNN_B200_PAIR=0 in the environment keeps every tile at 128 rows.
+bool pair_enabled() {
+  const char* f = std::getenv("NCNN_B200_PAIR");
+  return f == nullptr || f[0] != '0';
+}
+
 void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e, int sm_count) {
   TcGemmParams& p = L->p;
   p.M = static_cast<int>(M);
@@ -205,6 +212,31 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
         staging = both;
         break;
       }
+    }
+  }
+  // Paired tiles: two 128-row halves share every B tile, so a K block moves 256 + block_n operand
+  // rows for twice the output instead of 2 x (128 + block_n).  Worth it where the operand fetch sets
+  // the pace (deep contractions over full 128-byte rows; the stem's 64-byte window rows ran 9%
+  // slower paired) and the coarser tiles still fill the SMs wave by wave; the ring then holds two
+  // (larger) stages.
+  p.pair = 0;
+  if (pair_enabled() && p.tma_store && p.epi_groups == 1 && p.k_blocks >= 6 && p.block_n <= 128 &&
+      p.row_bytes >= 128) {
+    const long long pairs_m = (p.tiles_m + 1) / 2;
+    const long long super = pairs_m * p.tiles_n;
+    const long long waves_single = (tiles_total + sm_count - 1) / sm_count;
+    const long long waves_pair = (super + sm_count - 1) / sm_count;
+    const double cost_single = static_cast<double>(waves_single) * (kTcBlockM + p.block_n);
+    const double cost_pair = static_cast<double>(waves_pair) * (2 * kTcBlockM + p.block_n);
+    const int pair_stage = planes * (2 * kTcBlockM * p.row_bytes + b_bytes);
+    const int pair_staging = (res_mode != RES_NONE ? 16384 : 0) + 2 * out_tile;
+    if (cost_pair < 0.97 * cost_single && super * 10 >= 9ll * sm_count &&
+        (kTcSmemBudget - pair_staging) / pair_stage >= 2) {
+      p.pair = 1;
+      p.tiles_m = static_cast<int>(pairs_m);
+      p.stage_bytes = pair_stage;
+      p.out_bufs = 2;
+      staging = pair_staging;
     }
   }
   p.staging_bytes = staging / p.epi_groups;

@@ -68,7 +68,7 @@ constexpr int kTcThreads = 224;      // warps: 0 A producer, 1 MMA issuer, 2-5 e
 constexpr int kTcThreadsTwoEpi = 352;  // + warps 7-10: a second epilogue group for shallow contractions
 constexpr int kTcBlockM = 128;
 constexpr int kTcMaxStages = 8;
-constexpr uint32_t kTcTmemCols = 256;           // two accumulators of up to 128 columns
+constexpr uint32_t kTcTmemCols = 512;           // two accumulators of up to 128 columns, or two pairs of them
 constexpr uint64_t kTcWaitLimitNs = 2000000000ull;  // a wait longer than 2 s is a bug
 
 struct TcGemmParams {
@@ -102,7 +102,10 @@ struct TcGemmParams {
   int staging_bytes;   // staging area of one epilogue group (residual + output tiles)
   int epi_groups;      // 1 or 2 epilogue warpgroups (2: accumulator g is drained by group g; shallow layers)
   int wide;            // staged chunks are 32 columns wide (always with bf16 pairs; plain fp32 when it pays)
-  int out_bufs;        // staging tiles in flight (1..4), each 8 KB per output plane
+  int out_bufs;        // staging tiles in flight (2..4), each 8 KB per output plane
+  // 1: a tile is two 128-row halves that share one B tile per K block (tiles_m then counts these
+  // pairs): the A halves sit side by side in a stage and accumulate into neighbouring column ranges
+  int pair;
   long long* trace;    // optional (bring-up): per-role clock stamps of CTA 0, 8 values per tile
 };
 
@@ -619,7 +622,8 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
   const uint32_t smem_base = (smem_u32(tc_smem_raw) + 1023u) & ~1023u;
   const uint32_t slot = static_cast<uint32_t>(kTcBlockM) * p.row_bytes;
   const uint32_t stage_bytes = static_cast<uint32_t>(p.stage_bytes);
-  const uint32_t b_slot = (stage_bytes / PLANES) - slot;  // B tile, rounded to 1 KB
+  const int AS = p.pair ? 2 : 1;  // A tiles per stage
+  const uint32_t b_slot = (stage_bytes / PLANES) - static_cast<uint32_t>(AS) * slot;  // B tile, rounded to 1 KB
   const uint32_t tx_bytes = PLANES * (slot + static_cast<uint32_t>(p.block_n) * p.row_bytes);
   const int S = p.stages;
   const int total_tiles = p.tiles_m * p.tiles_n;
@@ -662,10 +666,14 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
     // feeds the A tiles, warp 6 the B tiles, each arming the stage for its own bytes (the full
     // barrier counts two arrivals).  Within a warp lane p issues plane p.
     const bool is_b = warp == 6;
-    const bool issuer = lane < PLANES;
-    const CUtensorMap* my_map = is_b ? (lane ? &map_b1 : &map_b0) : (lane ? &map_a1 : &map_a0);
-    const uint32_t my_off = is_b ? PLANES * slot + lane * b_slot : lane * slot;
-    const uint32_t my_tx = PLANES * (is_b ? static_cast<uint32_t>(p.block_n) * p.row_bytes : slot);
+    // (paired tiles: lanes PLANES..2*PLANES-1 of the A warp issue the second half's planes)
+    const bool issuer = lane < (is_b ? PLANES : PLANES * AS);
+    const int my_plane = lane % PLANES;
+    const int my_half = is_b ? 0 : lane / PLANES;
+    const CUtensorMap* my_map = is_b ? (my_plane ? &map_b1 : &map_b0) : (my_plane ? &map_a1 : &map_a0);
+    const uint32_t my_off = is_b ? static_cast<uint32_t>(PLANES * AS) * slot + lane * b_slot : lane * slot;
+    const uint32_t my_tx = is_b ? PLANES * static_cast<uint32_t>(p.block_n) * p.row_bytes
+                                : static_cast<uint32_t>(PLANES * AS) * slot;
     int s = 0;
     uint32_t ph = 0;
     long long issued = 0;
@@ -673,7 +681,9 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       const int m_blk = tile / p.tiles_n;
       const int n_blk = tile - m_blk * p.tiles_n;
-      const long long m0 = static_cast<long long>(m_blk) * kTcBlockM;
+      // a second half that starts past the last row repeats the first (its results are never stored)
+      long long m0 = static_cast<long long>(m_blk) * (kTcBlockM * AS);
+      if (m0 + static_cast<long long>(my_half) * kTcBlockM < p.M) m0 += static_cast<long long>(my_half) * kTcBlockM;
       const int n0 = n_blk * p.block_n;
       int img = 0, h_base = 0, w_base = 0;
       if (p.a_im2col) {
@@ -761,7 +771,10 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
       const uint64_t stage_units = stage_bytes >> 4;
       const uint64_t slot_units = slot >> 4;
       const uint64_t b_slot_units = b_slot >> 4;
-      const uint64_t b_from_a = static_cast<uint64_t>(PLANES) * slot_units;
+      const uint64_t a1_from_a = static_cast<uint64_t>(PLANES) * slot_units;  // second half's planes
+      const uint64_t b_from_a = static_cast<uint64_t>(PLANES * AS) * slot_units;
+      const uint32_t acc_stride = p.pair ? 256u : 128u;
+      const bool pair = p.pair != 0;
       const bool tracing = p.trace != nullptr && blockIdx.x == 0;
       int s = 0;
       uint32_t ph = 0;
@@ -776,7 +789,8 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
         }
         tc_fence_after_sync();
         if (tracing) p.trace[(tile / gridDim.x) * 16 + 1] = clock64();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * 128u;
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * acc_stride;
+        const uint32_t d_tmem1 = d_tmem + 128u;
         uint32_t accumulate = 0u;
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait_bounded(smem_u32(&full_bar[s]), ph, abort_ptr, kTcWaitLimitNs)) {
@@ -788,6 +802,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
           if (tr) p.trace[1024 + kb * 4 + 2] = clock64();
           const uint64_t a0 = a_first + static_cast<uint64_t>(s) * stage_units;
           const uint64_t b0 = a0 + b_from_a;
+          if (!pair) {
 #pragma unroll 4
           for (int k = 0; k < k_steps; ++k) {
             const uint64_t ka = a0 + 2u * k;
@@ -806,6 +821,37 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
               mma_i8(d_tmem, ka, kbd, idesc, accumulate);
             }
             accumulate = 1u;
+          }
+          } else {
+            // both halves against the same B tile; each half has its own accumulator columns
+#pragma unroll 4
+            for (int k = 0; k < k_steps; ++k) {
+              const uint64_t ka = a0 + 2u * k;
+              const uint64_t ka1 = ka + a1_from_a;
+              const uint64_t kbd = b0 + 2u * k;
+              if (KIND == GEMM_TF32) {
+                mma_tf32(d_tmem, ka, kbd, idesc, accumulate);
+                mma_tf32(d_tmem1, ka1, kbd, idesc, accumulate);
+              } else if (KIND == GEMM_TF32X3) {
+                mma_tf32(d_tmem, ka + slot_units, kbd, idesc, accumulate);
+                mma_tf32(d_tmem, ka, kbd + b_slot_units, idesc, 1u);
+                mma_tf32(d_tmem, ka, kbd, idesc, 1u);
+                mma_tf32(d_tmem1, ka1 + slot_units, kbd, idesc, accumulate);
+                mma_tf32(d_tmem1, ka1, kbd + b_slot_units, idesc, 1u);
+                mma_tf32(d_tmem1, ka1, kbd, idesc, 1u);
+              } else if (KIND == GEMM_BF16X3) {
+                mma_f16(d_tmem, ka + slot_units, kbd, idesc, accumulate);
+                mma_f16(d_tmem, ka, kbd + b_slot_units, idesc, 1u);
+                mma_f16(d_tmem, ka, kbd, idesc, 1u);
+                mma_f16(d_tmem1, ka1 + slot_units, kbd, idesc, accumulate);
+                mma_f16(d_tmem1, ka1, kbd + b_slot_units, idesc, 1u);
+                mma_f16(d_tmem1, ka1, kbd, idesc, 1u);
+              } else {
+                mma_i8(d_tmem, ka, kbd, idesc, accumulate);
+                mma_i8(d_tmem1, ka1, kbd, idesc, accumulate);
+              }
+              accumulate = 1u;
+            }
           }
           tc_commit(smem_u32(&empty_bar[s]));
           if (tr) p.trace[1024 + kb * 4 + 3] = clock64();
@@ -856,7 +902,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
          tile += tile_step) {
       const int m_blk = tile / p.tiles_n;
       const int n_blk = tile - m_blk * p.tiles_n;
-      const long long m = static_cast<long long>(m_blk) * kTcBlockM + quarter * 32 + lane;
+      const long long m_tile = static_cast<long long>(m_blk) * (kTcBlockM * AS);
       const int n0 = n_blk * p.block_n;
       if (tracing) p.trace[(tile / gridDim.x) * 16 + 3] = clock64();
       // the vote keeps the warp together: tcgen05.ld below needs all 32 lanes
@@ -867,8 +913,8 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
       if (!ok) break;
       tc_fence_after_sync();
       if (tracing) p.trace[(tile / gridDim.x) * 16 + 4] = clock64();
-      const uint32_t t_row =
-          tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc) * 128u;
+      const uint32_t t_row0 = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
+                              static_cast<uint32_t>(acc) * (p.pair ? 256u : 128u);
       {
         // per-column constants of this tile, fetched once (every warp of the group has left the
         // previous tile's last chunk: it ends with a barrier)
@@ -877,6 +923,12 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
         tile_bias[t] = (p.bias != nullptr && n < p.N) ? __ldg(p.bias + n) : 0.0f;
         tile_scale[t] = (KIND == GEMM_I8 && n < p.N) ? __ldg(p.scale + n) : 0.0f;
       }
+      // a paired tile is drained half by half; a second half past the last row is skipped
+      for (int half = 0; half < AS && ok; ++half) {
+      const long long m_half = m_tile + static_cast<long long>(half) * kTcBlockM;
+      if (half == 1 && m_half >= lp.M) break;
+      const long long m = m_half + quarter * 32 + lane;
+      const uint32_t t_row = t_row0 + static_cast<uint32_t>(half) * 128u;
       if (p.tma_store) {
         // staging area behind the ring, one per group: residual tiles (16 KB), then the output tiles
         TcStageCfg cfg{};
@@ -893,7 +945,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
         cfg.block_n = e_block_n;
         cfg.wide = p.wide;
         cfg.bar_base = bar_base;
-        const int m_first = m_blk * kTcBlockM;
+        const int m_first = static_cast<int>(m_half);
         struct {
           const CUtensorMap *o0, *o1, *r0, *r1;
           int m_first;
@@ -926,6 +978,8 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
         }
         named_barrier_sync(bar_base + 2, 128);  // nobody reads the tile constants any more
       }
+      }
+      if (!ok) break;
       tc_fence_before_sync();
       __syncwarp();
       if (tracing) p.trace[(tile / gridDim.x) * 16 + 5] = clock64();
