@@ -317,7 +317,7 @@ def main():
 
     # per-launch timing with CUDA events on the launching stream (same workload, eager launches)
     rows = model.profile(n, repeat=5)
-    tc = [r for r in rows if r["kernel"].startswith(("tc_gemm_kernel", "tc_conv_halo_kernel"))]
+    tc = [r for r in rows if r["kernel"].startswith(("tc_gemm_kernel", "tc_conv_halo_kernel", "tc_stem_kernel"))]
     peaks = measured_peaks()
     tc_ms = sum(r["ms"] for r in tc)
     tc_flops = sum(r["flops"] for r in tc)

@@ -55,6 +55,7 @@ struct Node {
   int impl = IMPL_NONE;
   bool stem = false;
   bool stem_bf16 = false;  // stem whose window view holds bf16 pairs (64-byte rows)
+  bool stem_rows = false;  // stem_bf16 whose input rows can stay resident in shared memory (tc_stem.cuh)
   // host-side parameters
   std::vector<float> w_f32;   // [O][I][KH][KW] (conv), [O][K] (ip/gemm), [C][KH][KW] (dw)
   std::vector<int8_t> w_i8;
@@ -1530,6 +1531,12 @@ void EngineImpl::fuse() {
   fuse_activations();
 }
 
+// NCNN_B200_STEM_ROWS=0 at load time keeps the stem on the im2col-window path of tc_gemm_kernel.
+static bool stem_rows_enabled() {
+  const char* f = std::getenv("NCNN_B200_STEM_ROWS");
+  return f == nullptr || f[0] != '0';
+}
+
 bool EngineImpl::choose_impl(std::string* err) {
   const bool exact = opt_.accuracy_mode == kAccuracyFp32Cuda;
   std::vector<int> uses(tensors_.size(), 0);
@@ -1563,6 +1570,9 @@ bool EngineImpl::choose_impl(std::string* err) {
             // bf16 pairs halve the window to 64-byte rows and the MMA count with it; the pixel
             // stride of the view must stay a multiple of 16 bytes
             n.stem_bf16 = !i8 && opt_.accuracy_mode == kAccuracyFp32Split && (n.sw * cp * 2) % 16 == 0;
+            // output pixels 16 bytes apart in the padded row: the windows can overlap in shared memory
+            n.stem_rows = n.stem_bf16 && stem_rows_enabled() && n.sw * cp * 2 == 16 && n.OW <= 128 && n.O % 16 == 0 &&
+                          n.O <= 128 && n.KW * cp <= 32 && n.KH <= 16 && n.dh == 1;
           }
         }
       }
@@ -1716,6 +1726,7 @@ bool EngineImpl::prepare_weights(std::string* err) {
           ti.Cp = cp;
           ti.w_off = n.pl;
           ti.Wp = std::max(ti.w + n.pl, ((n.OW - 1) * n.sw * cp + window + cp - 1) / cp);
+          if (n.stem_rows) ti.Wp = (ti.Wp + 15) / 16 * 16;  // rows of whole 128-byte lines
           ti.dedicated = true;
           if (i8) {
             ti.i8 = true;
@@ -2124,6 +2135,29 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
         if (tc_plan_conv_halo(hl.get(), kind, hc, te, sm_count_).empty()) {
           s.kernel = std::string("tc_conv_halo_kernel<") + kind_name + ">";
           s.run = [hl](cudaStream_t st) { return tc_launch_halo(*hl, st); };
+          plan.steps.push_back(std::move(s));
+          return true;
+        }
+      }
+      if (node.kind == N_CONV && node.stem && node.stem_rows && node.res < 0 && node.out_ld == 0) {
+        TcStemConv sc;
+        sc.in0 = in.p0;
+        sc.in1 = in.p1;
+        sc.images = static_cast<int>(n);
+        sc.H = ti.h;
+        sc.row_bytes = ti.Wp * ti.Cp * 2;
+        sc.KH = node.KH;
+        sc.stride_h = node.sh;
+        sc.pad_t = node.pt;
+        sc.OH = node.OH;
+        sc.OW = node.OW;
+        sc.w0 = node.d_w0;
+        sc.w1 = node.d_w1;
+        sc.out_channels = node.O;
+        auto sl = std::make_shared<TcStemLaunch>();
+        if (tc_plan_stem(sl.get(), sc, te, sm_count_).empty()) {
+          s.kernel = "tc_stem_kernel<bf16x3>";
+          s.run = [sl](cudaStream_t st) { return tc_launch_stem(*sl, st); };
           plan.steps.push_back(std::move(s));
           return true;
         }

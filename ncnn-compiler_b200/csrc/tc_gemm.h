@@ -11,6 +11,7 @@
 
 #include "tc_conv_halo.cuh"
 #include "tc_gemm.cuh"
+#include "tc_stem.cuh"
 
 namespace nb {
 
@@ -131,5 +132,34 @@ bool tc_halo_applies(int kind, int C, int KH, int KW, int stride_h, int stride_w
 std::string tc_plan_conv_halo(TcHaloLaunch* launch, int kind, const TcHaloConv& conv, const TcEpilogue& epilogue,
                               int sm_count);
 cudaError_t tc_launch_halo(const TcHaloLaunch& launch, cudaStream_t stream);
+
+// ---- stem convolution with the input rows resident in shared memory (tc_stem.cuh)
+struct TcStemLaunch {
+  TcStemParams p{};
+  alignas(64) CUtensorMap map_a0{};
+  alignas(64) CUtensorMap map_a1{};
+  alignas(64) CUtensorMap map_b0{};
+  alignas(64) CUtensorMap map_b1{};
+  alignas(64) CUtensorMap map_o0{};
+  alignas(64) CUtensorMap map_o1{};
+  int grid = 0;
+  int smem_bytes = 0;
+};
+
+struct TcStemConv {
+  const void* in0 = nullptr;  // bf16 hi plane [images][H][row_bytes]: padded rows of 4-channel pixels
+  const void* in1 = nullptr;  // bf16 mid plane
+  int images = 0, H = 0;
+  int row_bytes = 0;          // bytes of one padded row (a multiple of 128)
+  int KH = 1, stride_h = 1, pad_t = 0, OH = 0, OW = 0;
+  const void* w0 = nullptr;   // packed [O][KH][32] bf16 hi / mid (tc_pack_weights_bf16x2 with 32-element windows)
+  const void* w1 = nullptr;
+  int out_channels = 0;
+};
+
+// Applies when output pixels are 16 bytes apart in the padded input row (stride 2 x 4 channels x
+// bf16), a row of output fits one 128-row tile, and the rows and resident weights fit shared memory.
+std::string tc_plan_stem(TcStemLaunch* launch, const TcStemConv& conv, const TcEpilogue& epilogue, int sm_count);
+cudaError_t tc_launch_stem(const TcStemLaunch& launch, cudaStream_t stream);
 
 }  // namespace nb
