@@ -279,6 +279,41 @@ def test_pipelined_host_path_equals_one_piece(pkg, tmp_path, monkeypatch, net, n
         m.close()
 
 
+@pytest.mark.parametrize("k,stride,pad,cout,h,w,n", [(7, 2, 3, 64, 224, 224, 3), (3, 2, 1, 32, 224, 224, 2), (7, 2, 3, 64, 37, 41, 5),
+                                                   (5, 2, 2, 16, 64, 250, 2), (3, 2, 0, 128, 33, 64, 4)])
+def test_stem_rows_kernel_equals_window_path(pkg, oracle, tmp_path, monkeypatch, k, stride, pad, cout, h, w, n):
+    """Stems with a horizontal stride of 2 keep the input rows of an output row in shared memory and read
+    overlapping windows out of them (tc_stem_kernel); the im2col-window path of tc_gemm_kernel multiplies the
+    same operands in the same order, so both give the same bits, and both match the oracle."""
+    param, bin_ = pkg.zoo.single_conv(str(tmp_path / "stem"), h=h, w=w, cin=3, cout=cout, k=k, stride=stride, pad=pad)
+    x = np.random.default_rng(k + h).uniform(-1, 1, (n, 3, h, w)).astype(np.float32)
+    m = pkg.Model(param, bin_)
+    assert any(r["kernel"].startswith("tc_stem_kernel") for r in m.profile(n, 1))
+    got = m.run(x)[0]
+    m.close()
+    monkeypatch.setenv("NCNN_B200_STEM_ROWS", "0")
+    m = pkg.Model(param, bin_)
+    assert not any(r["kernel"].startswith("tc_stem_kernel") for r in m.profile(n, 1))
+    assert np.array_equal(m.run(x)[0], got)
+    m.close()
+    want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x[:2]])
+    assert rel_l2(got[:2], want) <= 1e-4  # fp32 tolerance of the path: rel-L2 <= 1e-3 required, ~1e-5 achieved
+
+
+def test_paired_tiles_equal_single_tiles(pkg, tmp_path, monkeypatch):
+    """Deep convolutions at sizes that fill the GPU run two 128-row halves per weight tile; every output row
+    still accumulates its products in the same order, so switching the pairing off changes no bit."""
+    param, bin_ = pkg.zoo.residual_block(str(tmp_path / "rb"), h=56, w=56, c=64, cout=96)
+    x = np.random.default_rng(3).uniform(-1, 1, (16, 64, 56, 56)).astype(np.float32)
+    m = pkg.Model(param, bin_)
+    got = m.run(x)[0]
+    m.close()
+    monkeypatch.setenv("NCNN_B200_PAIR", "0")
+    m = pkg.Model(param, bin_)
+    assert np.array_equal(m.run(x)[0], got)
+    m.close()
+
+
 def test_full_batch_properties(pkg, tmp_path):
     """Batch 64 at 224x224 (too slow for the oracle): images are independent, so permuting
     the batch permutes the outputs, and repeated calls give identical bytes."""
