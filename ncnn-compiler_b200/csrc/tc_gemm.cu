@@ -206,7 +206,8 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
     for (int bufs : {4, 3, 2}) {
       const int both = 2 * (res_bytes + bufs * out_tile);
       if (bufs > p.out_bufs) continue;
-      if ((kTcSmemBudget - both) / p.stage_bytes >= (bufs == 2 ? 3 : 4)) {
+      // (a tile of one or two K blocks needs no more than the next tile's operands in flight)
+      if ((kTcSmemBudget - both) / p.stage_bytes >= (bufs == 2 ? (p.k_blocks <= 2 ? 2 : 3) : 4)) {
         p.epi_groups = 2;
         p.out_bufs = bufs;
         staging = both;
