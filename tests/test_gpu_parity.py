@@ -314,6 +314,23 @@ def test_paired_tiles_equal_single_tiles(pkg, tmp_path, monkeypatch):
     m.close()
 
 
+@pytest.mark.parametrize("n", [11, 13])
+def test_paired_tiles_ragged_ends(pkg, oracle, tmp_path, monkeypatch, n):
+    """Paired tiles whose last pair is ragged: n = 11 ends in a half-filled second half, n = 13 in a pair whose
+    second half lies past the last row altogether (it is computed from repeated rows and never stored)."""
+    param, bin_ = pkg.zoo.single_conv(str(tmp_path / "c"), h=56, w=56)
+    x = np.random.default_rng(n).uniform(-1, 1, (n, 64, 56, 56)).astype(np.float32)
+    m = pkg.Model(param, bin_)
+    got = m.run(x)[0]
+    m.close()
+    monkeypatch.setenv("NCNN_B200_PAIR", "0")
+    m = pkg.Model(param, bin_)
+    assert np.array_equal(m.run(x)[0], got)
+    m.close()
+    want = oracle.Model(param, bin_).run([x[-1]])[0]
+    assert rel_l2(got[-1], want) <= 1e-4
+
+
 def test_full_batch_properties(pkg, tmp_path):
     """Batch 64 at 224x224 (too slow for the oracle): images are independent, so permuting
     the batch permutes the outputs, and repeated calls give identical bytes."""
