@@ -55,7 +55,7 @@ struct Node {
   int impl = IMPL_NONE;
   bool stem = false;
   bool stem_bf16 = false;  // stem whose window view holds bf16 pairs (64-byte rows)
-  bool stem_rows = false;  // stem_bf16 whose input rows can stay resident in shared memory (tc_stem.cuh)
+  bool stem_rows = false;  // stem (bf16 pairs or int8) whose input rows can stay resident in shared memory (tc_stem.cuh)
   // host-side parameters
   std::vector<float> w_f32;   // [O][I][KH][KW] (conv), [O][K] (ip/gemm), [C][KH][KW] (dw)
   std::vector<int8_t> w_i8;
@@ -1571,8 +1571,10 @@ bool EngineImpl::choose_impl(std::string* err) {
             // stride of the view must stay a multiple of 16 bytes
             n.stem_bf16 = !i8 && opt_.accuracy_mode == kAccuracyFp32Split && (n.sw * cp * 2) % 16 == 0;
             // output pixels 16 bytes apart in the padded row: the windows can overlap in shared memory
-            n.stem_rows = n.stem_bf16 && stem_rows_enabled() && n.sw * cp * 2 == 16 && n.OW <= 128 && n.O % 16 == 0 &&
-                          n.O <= 128 && n.KW * cp <= 32 && n.KH <= 16 && n.dh == 1;
+            // (bf16 pairs: 4 channels x 2 bytes; int8: 8 channels per pixel instead of 16)
+            const bool rows_geometry = stem_rows_enabled() && n.sw == 2 && n.OW <= 128 && n.O % 16 == 0 && n.O <= 128 &&
+                                       n.KW <= 8 && n.KH <= 16 && n.dh == 1;
+            n.stem_rows = rows_geometry && (n.stem_bf16 || (i8 && (n.term <= 100 || n.O % 64 == 0)));
           }
         }
       }
@@ -1718,8 +1720,9 @@ bool EngineImpl::prepare_weights(std::string* err) {
       if (n.impl == IMPL_TC) {
         const int kind = i8 ? GEMM_I8 : (ti.fmt == FMT_BF16X2 ? GEMM_BF16X3 : f32_kind);
         if (n.stem) {
-          const int cp = i8 ? 16 : 4;
-          const int window = i8 ? 128 : 32;
+          // (row-resident int8 stems: 8 channels per pixel, 64-byte windows of 8 pixels)
+          const int cp = i8 ? (n.stem_rows ? 8 : 16) : 4;
+          const int window = i8 ? (n.stem_rows ? 64 : 128) : 32;
           n.k_elems = window;
           // storage of the input: rows padded on the left by pad_l, wide enough for the
           // last window, channels padded to cp
@@ -2141,11 +2144,12 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
       }
       if (node.kind == N_CONV && node.stem && node.stem_rows && node.res < 0 && node.out_ld == 0) {
         TcStemConv sc;
-        sc.in0 = in.p0;
+        sc.kind = kind;
+        sc.in0 = i8 ? static_cast<const void*>(in.q) : static_cast<const void*>(in.p0);
         sc.in1 = in.p1;
         sc.images = static_cast<int>(n);
         sc.H = ti.h;
-        sc.row_bytes = ti.Wp * ti.Cp * 2;
+        sc.row_bytes = ti.Wp * ti.Cp * (i8 ? 1 : 2);
         sc.KH = node.KH;
         sc.stride_h = node.sh;
         sc.pad_t = node.pt;
@@ -2156,7 +2160,7 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
         sc.out_channels = node.O;
         auto sl = std::make_shared<TcStemLaunch>();
         if (tc_plan_stem(sl.get(), sc, te, sm_count_).empty()) {
-          s.kernel = "tc_stem_kernel<bf16x3>";
+          s.kernel = std::string("tc_stem_kernel<") + kind_name + ">";
           s.run = [sl](cudaStream_t st) { return tc_launch_stem(*sl, st); };
           plan.steps.push_back(std::move(s));
           return true;
@@ -2492,7 +2496,8 @@ void EngineImpl::make_edge_steps(int64_t n, const std::vector<const float*>& d_i
       ep.Wp = t.Wp;
       ep.w_off = t.w_off;
       ep.quant_scale = t.input_quant_scale;
-      if (t.c <= 4 && t.Cp == 4 && t.fmt != FMT_I8 && t.w % 4 == 0 && n <= 65535 &&
+      if (t.c <= 4 && ((t.Cp == 4 && t.fmt != FMT_I8) || (t.Cp == 8 && t.fmt == FMT_I8)) && t.w % 4 == 0 &&
+          n <= 65535 &&
           (reinterpret_cast<uintptr_t>(src_ptr) & 15) == 0) {
         const dim3 grid(static_cast<unsigned>(std::min(148 * 8, (t.h * t.w / 4 + 255) / 256)), static_cast<unsigned>(n));
         s.kernel = "k_chw_to_nhwc_small_x4";
@@ -2500,7 +2505,7 @@ void EngineImpl::make_edge_steps(int64_t n, const std::vector<const float*>& d_i
           k_chw_to_nhwc_small_x4<<<grid, 256, 0, st>>>(src_ptr, dst, ep);
           return launch_ok();
         };
-      } else if (t.c <= 4 && (t.Cp == 4 || t.Cp == 16)) {
+      } else if (t.c <= 4 && (t.Cp == 4 || t.Cp == 16 || (t.Cp == 8 && t.fmt == FMT_I8))) {
         const int grid = grid_for(n * t.h * t.w);
         s.kernel = "k_chw_to_nhwc_small";
         s.run = [=](cudaStream_t st) {

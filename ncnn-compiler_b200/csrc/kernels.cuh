@@ -150,11 +150,12 @@ static __global__ void k_chw_to_nhwc_small(const float* __restrict__ src, ActRef
     for (int c = 0; c < p.C; ++c) v[c] = src[(img * p.C + c) * hw + px];
     const long long o = ((img * p.H + h) * static_cast<long long>(p.Wp) + w + p.w_off) * p.Cp;
     if (dst.fmt == FMT_I8) {
-      // Cp == 16: channels 0..3 carry data, the rest of the 16-byte pixel is zero
+      // Cp == 16 or 8: channels 0..3 carry data, the rest of the 16- or 8-byte pixel is zero
       uint32_t w0 = 0;
       for (int c = 0; c < p.C; ++c)
         w0 |= (static_cast<uint32_t>(quantize_rha(v[c], p.quant_scale)) & 0xffu) << (8 * c);
-      *reinterpret_cast<uint4*>(dst.q + o) = make_uint4(w0, 0u, 0u, 0u);
+      if (p.Cp == 8) *reinterpret_cast<uint2*>(dst.q + o) = make_uint2(w0, 0u);
+      else *reinterpret_cast<uint4*>(dst.q + o) = make_uint4(w0, 0u, 0u, 0u);
     } else {
       act_store4(dst, o, make_float4(v[0], v[1], v[2], v[3]));
     }
@@ -179,7 +180,7 @@ static __global__ void k_nhwc_to_chw_tiled(ActRef src, float* __restrict__ dst, 
   }
 }
 
-// The same for rows whose width is a multiple of 4 and fp32 / bf16-pair storage with Cp == 4:
+// The same for rows whose width is a multiple of 4 and fp32 / bf16-pair storage with Cp == 4 (or int8 with Cp == 8):
 // one thread per 4 consecutive pixels of a row, one 128-bit load per channel plane and 64 or
 // 32 contiguous bytes stored per output plane; grid = (row quads, images), 32-bit indices.
 static __global__ void k_chw_to_nhwc_small_x4(const float* __restrict__ src, ActRef dst, EdgeParams p) {
@@ -196,9 +197,24 @@ static __global__ void k_chw_to_nhwc_small_x4(const float* __restrict__ src, Act
       ch[c] = c < p.C ? __ldg(reinterpret_cast<const float4*>(s + static_cast<long long>(c) * hw + px))
                       : make_float4(0.f, 0.f, 0.f, 0.f);
     const float4 c3 = p.C > 3 ? __ldg(reinterpret_cast<const float4*>(s + 3ll * hw + px)) : make_float4(0.f, 0.f, 0.f, 0.f);
-    const long long o = ((img * p.H + h) * static_cast<long long>(p.Wp) + w + p.w_off) * 4;
+    const long long o = ((img * p.H + h) * static_cast<long long>(p.Wp) + w + p.w_off) * p.Cp;
     const float v[4][4] = {{ch[0].x, ch[1].x, ch[2].x, c3.x}, {ch[0].y, ch[1].y, ch[2].y, c3.y},
                            {ch[0].z, ch[1].z, ch[2].z, c3.z}, {ch[0].w, ch[1].w, ch[2].w, c3.w}};
+    if (dst.fmt == FMT_I8) {
+      // Cp == 8: four quantised channels and four zero bytes per pixel, 32 contiguous bytes per thread
+      uint32_t q[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        q[k] = 0;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          q[k] |= (static_cast<uint32_t>(quantize_rha(v[k][c], p.quant_scale)) & 0xffu) << (8 * c);
+      }
+      uint2* d = reinterpret_cast<uint2*>(dst.q + o);  // (rows start pad_l pixels in: 8-byte alignment only)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) d[k] = make_uint2(q[k], 0u);
+      continue;
+    }
 #pragma unroll
     for (int k = 0; k < 4; ++k) act_store4(dst, o + 4 * k, make_float4(v[k][0], v[k][1], v[k][2], v[k][3]));
   }

@@ -700,11 +700,19 @@ std::string tc_plan_stem(TcStemLaunch* L, const TcStemConv& c, const TcEpilogue&
   if (N % 16 != 0 || N > 128) return "output channels must be a multiple of 16, at most 128";
   if (c.KH < 1 || c.KH > 16) return "filter height out of range";
   if (e.res0 != nullptr) return "the stem kernel takes no residual";
-  if (e.out_mode != OUT_F32 && e.out_mode != OUT_BF16X2) return "output format not handled by the stem kernel";
+  const bool i8 = c.kind == GEMM_I8;
+  if (c.kind != GEMM_BF16X3 && !i8) return "the stem kernel takes bf16-pair or int8 operands";
+  const bool i8_out = e.out_mode == OUT_I8;
+  if (e.out_mode != OUT_F32 && !(e.out_mode == OUT_BF16X2 && !i8) && !(i8_out && i8))
+    return "output format not handled by the stem kernel";
   const bool bf16_out = e.out_mode == OUT_BF16X2;
   if (bf16_out && N % 32 != 0) return "bf16-pair results need channels in multiples of 32";
-  if (e.ldo != N || (reinterpret_cast<uintptr_t>(e.out0) & 15) != 0 || (reinterpret_cast<uintptr_t>(e.out1) & 15) != 0)
+  if (i8_out && N % 64 != 0) return "int8 results need channels in multiples of 64";
+  if (e.ldo != N || (reinterpret_cast<uintptr_t>(e.out0) & 15) != 0 || (reinterpret_cast<uintptr_t>(e.out1) & 15) != 0 ||
+      (reinterpret_cast<uintptr_t>(e.outq) & 15) != 0)
     return "the stem kernel writes dense, 16-byte aligned rows";
+  const int planes = i8 ? 1 : 2;
+  L->kind = c.kind;
   if ((c.OW - 1) * 16 + 64 > c.row_bytes) return "padded rows are shorter than the last window";
   p.tiles = c.images * c.OH;
   p.OH = c.OH;
@@ -720,16 +728,18 @@ std::string tc_plan_stem(TcStemLaunch* L, const TcStemConv& c, const TcEpilogue&
   p.a_plane_bytes = std::max(p.a_plane_bytes, (c.KH * c.row_bytes + 1023) / 1024 * 1024);
   p.b_slot = (N * 64 + 1023) / 1024 * 1024;
   p.bias = e.bias;
+  p.scale = e.scale;
+  p.out_scale = e.out_scale;
   p.out_mode = e.out_mode;
   p.act = e.act;
   p.act_a = e.act_a;
   p.act_b = e.act_b;
   p.status = e.status;
-  p.wide = bf16_out || N % 32 == 0 ? 1 : 0;
+  p.wide = !i8_out && (bf16_out || N % 32 == 0) ? 1 : 0;
   const int out_tile = p.wide ? 16384 : 8192;
-  const int budget = tc_smem_budget(GEMM_BF16X3);
-  const int weights = c.KH * 2 * p.b_slot;
-  const int stage = 2 * p.a_plane_bytes;
+  const int budget = tc_smem_budget(c.kind);
+  const int weights = c.KH * planes * p.b_slot;
+  const int stage = planes * p.a_plane_bytes;
   // the epilogue of a 64-channel row takes longer than its 42 MMAs: two epilogue groups when they fit
   p.epi_groups = 0;
   for (int groups : {2, 1}) {
@@ -750,32 +760,45 @@ std::string tc_plan_stem(TcStemLaunch* L, const TcStemConv& c, const TcEpilogue&
   L->smem_bytes = std::max(L->smem_bytes, 120 * 1024);  // one CTA per SM: each allocates tensor memory
   L->grid = std::min(p.tiles, sm_count);
   // input planes: [images][H][row_bytes / 128][64 bf16], KH whole rows per copy, dense in shared memory
-  std::string err = encode_tiled_4d(&L->map_a0, true, c.in0, 64, c.row_bytes / 128, c.H, c.images, 64,
-                                    static_cast<uint32_t>(c.row_bytes / 128), static_cast<uint32_t>(c.KH),
-                                    CU_TENSOR_MAP_SWIZZLE_NONE);
-  if (err.empty())
-    err = encode_tiled_4d(&L->map_a1, true, c.in1, 64, c.row_bytes / 128, c.H, c.images, 64,
-                          static_cast<uint32_t>(c.row_bytes / 128), static_cast<uint32_t>(c.KH),
-                          CU_TENSOR_MAP_SWIZZLE_NONE);
+  auto rows_map = [&](CUtensorMap* map, const void* base) -> std::string {
+    const cuuint64_t line = i8 ? 128 : 64;  // elements per 128-byte line
+    const cuuint64_t dims[4] = {line, static_cast<cuuint64_t>(c.row_bytes / 128), static_cast<cuuint64_t>(c.H),
+                                static_cast<cuuint64_t>(c.images)};
+    const cuuint64_t strides[3] = {128, static_cast<cuuint64_t>(c.row_bytes),
+                                   static_cast<cuuint64_t>(c.row_bytes) * c.H};
+    const cuuint32_t box[4] = {static_cast<cuuint32_t>(line), static_cast<cuuint32_t>(c.row_bytes / 128),
+                               static_cast<cuuint32_t>(c.KH), 1};
+    const cuuint32_t elem_strides[4] = {1, 1, 1, 1};
+    const CUresult r = g_encode_tiled(map, i8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                                      const_cast<void*>(base), dims, strides, box, elem_strides,
+                                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return "cuTensorMapEncodeTiled failed for the stem input rows with code " + std::to_string(static_cast<int>(r));
+    return {};
+  };
+  std::string err = rows_map(&L->map_a0, c.in0);
+  if (err.empty() && !i8) err = rows_map(&L->map_a1, c.in1);
   if (!err.empty()) return err;
-  const uint64_t k_total = static_cast<uint64_t>(c.KH) * 32;
-  err = encode_tiled_2d(&L->map_b0, GEMM_BF16X3, c.w0, k_total, N, k_total * 2, 32, N, 64);
-  if (err.empty()) err = encode_tiled_2d(&L->map_b1, GEMM_BF16X3, c.w1, k_total, N, k_total * 2, 32, N, 64);
+  const uint64_t window = i8 ? 64 : 32;  // elements of one 64-byte window
+  const uint64_t k_total = static_cast<uint64_t>(c.KH) * window;
+  err = encode_tiled_2d(&L->map_b0, c.kind, c.w0, k_total, N, k_total * (i8 ? 1 : 2), static_cast<uint32_t>(window), N, 64);
+  if (err.empty() && !i8)
+    err = encode_tiled_2d(&L->map_b1, c.kind, c.w1, k_total, N, k_total * 2, static_cast<uint32_t>(window), N, 64);
   if (!err.empty()) return err;
   // outputs: [pixels][N], boxes of 64 bytes x OW rows (one output row of the image), 64-byte swizzle
   auto plane = [&](CUtensorMap* map, const void* base) -> std::string {
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(p.M)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(N) * (bf16_out ? 2 : 4)};
-    const cuuint32_t box[2] = {bf16_out ? 32u : 16u, static_cast<cuuint32_t>(c.OW)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(N) * (i8_out ? 1 : (bf16_out ? 2 : 4))};
+    const cuuint32_t box[2] = {i8_out ? 64u : (bf16_out ? 32u : 16u), static_cast<cuuint32_t>(c.OW)};
     const cuuint32_t elem_strides[2] = {1, 1};
-    const CUresult r = g_encode_tiled(map, bf16_out ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+    const CUresult r = g_encode_tiled(map, i8_out ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : (bf16_out ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32),
                                       2, const_cast<void*>(base), dims, strides, box, elem_strides,
                                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
                                       CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return "cuTensorMapEncodeTiled failed for a stem output plane with code " + std::to_string(static_cast<int>(r));
     return {};
   };
-  err = plane(&L->map_o0, e.out0);
+  err = plane(&L->map_o0, i8_out ? static_cast<const void*>(e.outq) : static_cast<const void*>(e.out0));
   if (err.empty() && bf16_out) err = plane(&L->map_o1, e.out1);
   return err;
 }
@@ -786,10 +809,17 @@ cudaError_t tc_launch_stem(const TcStemLaunch& L, cudaStream_t stream) {
   std::call_once(attr_once, [] {
     attr_err = cudaFuncSetAttribute(tc_stem_kernel<GEMM_BF16X3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     tc_smem_budget(GEMM_BF16X3) + 1024);
+    if (attr_err == cudaSuccess)
+      attr_err = cudaFuncSetAttribute(tc_stem_kernel<GEMM_I8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      tc_smem_budget(GEMM_I8) + 1024);
   });
   if (attr_err != cudaSuccess) return attr_err;
-  tc_stem_kernel<GEMM_BF16X3><<<L.grid, kStemThreads, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
-                                                                  L.map_o1);
+  if (L.kind == GEMM_I8)
+    tc_stem_kernel<GEMM_I8><<<L.grid, kStemThreads, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1,
+                                                                            L.map_o0, L.map_o1);
+  else
+    tc_stem_kernel<GEMM_BF16X3><<<L.grid, kStemThreads, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0,
+                                                                                L.map_b1, L.map_o0, L.map_o1);
   return cudaGetLastError();
 }
 

@@ -142,17 +142,19 @@ struct TcStemLaunch {
   alignas(64) CUtensorMap map_b1{};
   alignas(64) CUtensorMap map_o0{};
   alignas(64) CUtensorMap map_o1{};
+  int kind = GEMM_BF16X3;
   int grid = 0;
   int smem_bytes = 0;
 };
 
 struct TcStemConv {
-  const void* in0 = nullptr;  // bf16 hi plane [images][H][row_bytes]: padded rows of 4-channel pixels
+  int kind = GEMM_BF16X3;     // GEMM_BF16X3 (4-channel pixels, bf16 hi/mid planes) or GEMM_I8 (8-channel int8 pixels)
+  const void* in0 = nullptr;  // [images][H][row_bytes]: padded rows of 8-byte pixels (bf16 hi plane, or int8)
   const void* in1 = nullptr;  // bf16 mid plane
   int images = 0, H = 0;
   int row_bytes = 0;          // bytes of one padded row (a multiple of 128)
   int KH = 1, stride_h = 1, pad_t = 0, OH = 0, OW = 0;
-  const void* w0 = nullptr;   // packed [O][KH][32] bf16 hi / mid (tc_pack_weights_bf16x2 with 32-element windows)
+  const void* w0 = nullptr;   // packed [O][KH][32] bf16 hi / mid, or [O][KH][64] int8 (one 64-byte window per filter row)
   const void* w1 = nullptr;
   int out_channels = 0;
 };

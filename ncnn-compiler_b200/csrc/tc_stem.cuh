@@ -1,4 +1,4 @@
-// Stem convolution (few input channels, fp32 accuracy mode) with the input rows resident in
+// Stem convolution (few input channels; fp32 accuracy mode or int8) with the input rows resident in
 // shared memory: one tile is one output row of one image.
 //
 // The graph input is stored channel-padded to 4 and width-padded, as bf16 pairs: 8 bytes per pixel
@@ -12,7 +12,8 @@
 // (13 KB for the 7x7 ResNet stem, against 112 KB of window copies); the weights of all KH filter
 // rows stay resident.  Replaces the stem case of ConvertConvolution (lib/Conversion/NCNNToTosa/
 // NCNNToTosa.cpp:1403-1528); results are bit-identical to tc_gemm_kernel's (same products, same
-// K order).
+// K order).  The int8 form stores 8 channels per pixel (8 bytes), so the same 16-byte pitch holds: 64-byte
+// windows of 8 pixels, one plane, kind::i8 with K = 32 per instruction.
 #pragma once
 
 #include "tc_gemm.cuh"
@@ -33,6 +34,8 @@ struct TcStemParams {
   int b_slot;         // one weight tile of one plane: N rows x 64 bytes, rounded to 1 KB
   int stages;         // A ring depth
   const float* bias;
+  const float* scale;  // int8: dequantisation factor per output channel
+  float out_scale;     // int8 results: requantisation scale
   int out_mode, act;
   float act_a, act_b;
   int wide, out_bufs, staging_bytes, epi_groups;
@@ -49,8 +52,7 @@ __device__ __forceinline__ uint64_t smem_desc_plain(uint32_t smem_addr, uint32_t
   return d;
 }
 
-// (a template like the other contraction kernels, so that the header can be included more than once
-// per program; GEMM_BF16X3 is the only kind)
+// KIND is GEMM_BF16X3 (two planes: hi, mid) or GEMM_I8 (one plane)
 template <int KIND>
 __global__ void __launch_bounds__(kStemThreads, 1)
 tc_stem_kernel(const __grid_constant__ TcStemParams p, const __grid_constant__ CUtensorMap map_a0,
@@ -58,6 +60,7 @@ tc_stem_kernel(const __grid_constant__ TcStemParams p, const __grid_constant__ C
                const __grid_constant__ CUtensorMap map_b1, const __grid_constant__ CUtensorMap map_o0,
                const __grid_constant__ CUtensorMap map_o1) {
   using namespace ptx;
+  constexpr int PLANES = tc_planes(KIND);
   extern __shared__ uint8_t stem_smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kStemMaxStages];
   __shared__ __align__(8) uint64_t empty_bar[kStemMaxStages];
@@ -66,7 +69,7 @@ tc_stem_kernel(const __grid_constant__ TcStemParams p, const __grid_constant__ C
   __shared__ __align__(8) uint64_t weights_bar;
   __shared__ __align__(8) uint64_t unused_res_bar[2];
   __shared__ __align__(16) float tile_bias_all[2][128];
-  __shared__ __align__(16) float tile_scale_all[2][4];
+  __shared__ __align__(16) float tile_scale_all[2][KIND == GEMM_I8 ? 128 : 4];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -75,8 +78,8 @@ tc_stem_kernel(const __grid_constant__ TcStemParams p, const __grid_constant__ C
   const uint32_t smem_base = (smem_u32(stem_smem_raw) + 1023u) & ~1023u;
   const int S = p.stages;
   const uint32_t b_region = smem_base;  // [KH][plane][b_slot]
-  const uint32_t a_region = b_region + static_cast<uint32_t>(p.KH) * 2u * static_cast<uint32_t>(p.b_slot);
-  const uint32_t stage_bytes = 2u * static_cast<uint32_t>(p.a_plane_bytes);
+  const uint32_t a_region = b_region + static_cast<uint32_t>(p.KH * PLANES) * static_cast<uint32_t>(p.b_slot);
+  const uint32_t stage_bytes = static_cast<uint32_t>(PLANES) * static_cast<uint32_t>(p.a_plane_bytes);
   const uint32_t staging = a_region + static_cast<uint32_t>(S) * stage_bytes;
   volatile int* abort_ptr = &abort_flag;
 
@@ -94,9 +97,11 @@ tc_stem_kernel(const __grid_constant__ TcStemParams p, const __grid_constant__ C
     mbar_init(smem_u32(&weights_bar), 1);
     fence_mbar_init();
     prefetch_tensormap(&map_a0);
-    prefetch_tensormap(&map_a1);
     prefetch_tensormap(&map_b0);
-    prefetch_tensormap(&map_b1);
+    if (PLANES == 2) {
+      prefetch_tensormap(&map_a1);
+      prefetch_tensormap(&map_b1);
+    }
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(&tmem_slot), 256);
@@ -112,11 +117,13 @@ tc_stem_kernel(const __grid_constant__ TcStemParams p, const __grid_constant__ C
     const CUtensorMap* map_a = lane ? &map_a1 : &map_a0;
     const CUtensorMap* map_b = lane ? &map_b1 : &map_b0;
     const uint32_t wb = smem_u32(&weights_bar);
-    if (lane == 0) mbar_arrive_expect_tx(wb, static_cast<uint32_t>(p.KH) * 2u * static_cast<uint32_t>(p.N) * 64u);
+    if (lane == 0) mbar_arrive_expect_tx(wb, static_cast<uint32_t>(p.KH * PLANES) * static_cast<uint32_t>(p.N) * 64u);
     __syncwarp();
-    if (lane < 2) {
+    if (lane < PLANES) {
+      // (the K coordinate counts elements: 32 bf16 or 64 int8 per filter row)
       for (int kh = 0; kh < p.KH; ++kh)
-        tma_load_2d(b_region + static_cast<uint32_t>(kh * 2 + lane) * p.b_slot, map_b, wb, kh * 32, 0);
+        tma_load_2d(b_region + static_cast<uint32_t>(kh * PLANES + lane) * p.b_slot, map_b, wb,
+                    kh * (KIND == GEMM_I8 ? 64 : 32), 0);
     }
     int s = 0;
     uint32_t ph = 0;
@@ -129,7 +136,7 @@ tc_stem_kernel(const __grid_constant__ TcStemParams p, const __grid_constant__ C
       int w = 1;
       if (lane == 0) {
         w = mbar_wait_bounded(smem_u32(&empty_bar[s]), ph ^ 1u, abort_ptr, kTcWaitLimitNs) ? 1 : 0;
-        if (w) mbar_arrive_expect_tx(fb, 2u * static_cast<uint32_t>(p.KH) * static_cast<uint32_t>(p.row_bytes));
+        if (w) mbar_arrive_expect_tx(fb, static_cast<uint32_t>(PLANES * p.KH) * static_cast<uint32_t>(p.row_bytes));
       }
       w = __shfl_sync(0xffffffffu, w, 0);
       if (!w) {
@@ -137,7 +144,7 @@ tc_stem_kernel(const __grid_constant__ TcStemParams p, const __grid_constant__ C
         break;
       }
       // rows above or below the image are filled with zeros by the copy
-      if (lane < 2)
+      if (lane < PLANES)
         tma_load_4d(a_region + static_cast<uint32_t>(s) * stage_bytes + static_cast<uint32_t>(lane) * p.a_plane_bytes,
                     map_a, fb, 0, 0, oh * p.stride_h - p.pad_t, img);
       ++issued;
@@ -160,7 +167,8 @@ tc_stem_kernel(const __grid_constant__ TcStemParams p, const __grid_constant__ C
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = instr_desc(1u, 1u, kTcBlockM, static_cast<uint32_t>(p.N));
+      const uint32_t idesc = KIND == GEMM_I8 ? instr_desc(2u, 1u, kTcBlockM, static_cast<uint32_t>(p.N))
+                                             : instr_desc(1u, 1u, kTcBlockM, static_cast<uint32_t>(p.N));
       bool ok = mbar_wait_bounded(smem_u32(&weights_bar), 0, abort_ptr, kTcWaitLimitNs);
       tc_fence_after_sync();
       const uint64_t a_fixed = smem_desc_plain(0u, 16u, 128u);
@@ -185,14 +193,18 @@ tc_stem_kernel(const __grid_constant__ TcStemParams p, const __grid_constant__ C
         uint32_t accumulate = 0u;
         for (int kh = 0; kh < p.KH; ++kh) {
           const uint64_t a_hi = a_hi0 + static_cast<uint64_t>(kh) * row_units;
-          const uint64_t b_hi = b_first + static_cast<uint64_t>(2 * kh) * b_slot_units;
+          const uint64_t b_hi = b_first + static_cast<uint64_t>(PLANES * kh) * b_slot_units;
 #pragma unroll
-          for (int ks = 0; ks < 2; ++ks) {  // 32 window elements = two K steps of 16 (32 bytes = 2 units)
+          for (int ks = 0; ks < 2; ++ks) {  // a 64-byte window = two K steps of 32 bytes (2 units)
             const uint64_t ka = a_hi + 2u * ks;
             const uint64_t kb = b_hi + 2u * ks;
-            mma_f16(d_tmem, ka + a_plane_units, kb, idesc, accumulate);  // mid * hi
-            mma_f16(d_tmem, ka, kb + b_slot_units, idesc, 1u);           // hi * mid
-            mma_f16(d_tmem, ka, kb, idesc, 1u);                          // hi * hi
+            if (KIND == GEMM_I8) {
+              mma_i8(d_tmem, ka, kb, idesc, accumulate);
+            } else {
+              mma_f16(d_tmem, ka + a_plane_units, kb, idesc, accumulate);  // mid * hi
+              mma_f16(d_tmem, ka, kb + b_slot_units, idesc, 1u);           // hi * mid
+              mma_f16(d_tmem, ka, kb, idesc, 1u);                          // hi * hi
+            }
             accumulate = 1u;
           }
         }
@@ -220,7 +232,8 @@ tc_stem_kernel(const __grid_constant__ TcStemParams p, const __grid_constant__ C
       {
         const int t = static_cast<int>(threadIdx.x) - first_thread;
         tile_bias[t] = (p.bias != nullptr && t < p.N) ? __ldg(p.bias + t) : 0.0f;
-        if (t < 4) tile_scale[t] = 0.0f;
+        if (KIND == GEMM_I8) tile_scale[t] = t < p.N ? __ldg(p.scale + t) : 0.0f;
+        else if (t < 4) tile_scale[t] = 0.0f;
       }
       int acc = groups == 2 ? group : 0;
       uint32_t acc_ph = 0, res_ph = 0;
@@ -259,9 +272,14 @@ tc_stem_kernel(const __grid_constant__ TcStemParams p, const __grid_constant__ C
             ptx::tma_store_2d(plane ? o1 : o0, src, col, m_first);
           }
         } io{&map_o0, &map_o1, tile * p.OW};
-        ok = tc_staged_epilogue<KIND>(cfg, io, t_row, 0, quarter * 32 + lane, leader, tile_bias, tile_scale,
-                                             res_ph, out_slot, abort_ptr);
-        if (!ok) break;
+        if (KIND == GEMM_I8 && p.out_mode == OUT_I8) {
+          tc_staged_epilogue_i8<KIND>(cfg, p.out_scale, io, t_row, 0, quarter * 32 + lane, leader, tile_bias, tile_scale,
+                                      out_slot);
+        } else {
+          ok = tc_staged_epilogue<KIND>(cfg, io, t_row, 0, quarter * 32 + lane, leader, tile_bias, tile_scale, res_ph,
+                                        out_slot, abort_ptr);
+          if (!ok) break;
+        }
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
