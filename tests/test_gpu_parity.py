@@ -300,6 +300,24 @@ def test_stem_rows_kernel_equals_window_path(pkg, oracle, tmp_path, monkeypatch,
     assert rel_l2(got[:2], want) <= 1e-4  # fp32 tolerance of the path: rel-L2 <= 1e-3 required, ~1e-5 achieved
 
 
+def test_int8_stem_rows_kernel_is_bit_exact(pkg, oracle, tmp_path, monkeypatch):
+    """The int8 stem through the row-resident kernel (8-channel pixels, overlapping 64-byte windows): same int8
+    bits as the oracle and as the im2col-window path (16-channel pixels, 128-byte windows)."""
+    param, bin_ = pkg.zoo.resnet18(str(tmp_path / "r8"), int8=True, size=96, classes=20)
+    x = np.random.default_rng(21).uniform(-1, 1, (3, 3, 96, 96)).astype(np.float32)
+    m = pkg.Model(param, bin_)
+    assert any(r["kernel"] == "tc_stem_kernel<i8>" for r in m.profile(3, 1))
+    got = m.run(x)[0]
+    m.close()
+    monkeypatch.setenv("NCNN_B200_STEM_ROWS", "0")
+    m = pkg.Model(param, bin_)
+    assert not any(r["kernel"].startswith("tc_stem_kernel") for r in m.profile(3, 1))
+    assert np.array_equal(m.run(x)[0], got)
+    m.close()
+    want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x])
+    assert np.array_equal(got, want)
+
+
 def test_paired_tiles_equal_single_tiles(pkg, tmp_path, monkeypatch):
     """Deep convolutions at sizes that fill the GPU run two 128-row halves per weight tile; every output row
     still accumulates its products in the same order, so switching the pairing off changes no bit."""
