@@ -331,7 +331,11 @@ def main():
             entry_ = json.load(f).get(workload)
         if entry_:
             traffic = entry_["dram_bytes_read"] + entry_["dram_bytes_write"]  # bytes per pass, from the ncu capture
-    roofline = {"bound": "tensor", "kernel": tc[0]["kernel"] if tc else None, "achieved": achieved,
+    by_kernel = {}
+    for r in tc:
+        by_kernel[r["kernel"]] = by_kernel.get(r["kernel"], 0.0) + r["ms"]
+    dominant = max(by_kernel, key=by_kernel.get) if by_kernel else None  # the tensor-core kernel with the most time
+    roofline = {"bound": "tensor", "kernel": dominant, "achieved": achieved,
                 "peak": peaks["bf16_sustained"], "unit": "TFLOP/s", "frac": achieved / peaks["bf16_sustained"],
                 "peak_source": f"dense bf16 sustained, {peaks['source']}", "traffic": traffic,
                 "traffic_note": "DRAM bytes of all tensor-core launches of one pass (ncu, profiles/)" if traffic else None,
