@@ -221,20 +221,37 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
   // slower paired) and the coarser tiles still fill the SMs wave by wave; the ring then holds two
   // (larger) stages.
   p.pair = 0;
+  p.pair_rows = 0;
   if (pair_enabled() && p.tma_store && p.epi_groups == 1 && p.k_blocks >= 6 && p.block_n <= 128 &&
       p.row_bytes >= 128) {
-    const long long pairs_m = (p.tiles_m + 1) / 2;
-    const long long super = pairs_m * p.tiles_n;
-    const long long waves_single = (tiles_total + sm_count - 1) / sm_count;
-    const long long waves_pair = (super + sm_count - 1) / sm_count;
-    const double cost_single = static_cast<double>(waves_single) * (kTcBlockM + p.block_n);
-    const double cost_pair = static_cast<double>(waves_pair) * (2 * kTcBlockM + p.block_n);
     const int pair_stage = planes * (2 * kTcBlockM * p.row_bytes + b_bytes);
     const int pair_staging = (res_mode != RES_NONE ? 16384 : 0) + 2 * out_tile;
-    if (cost_pair < 0.97 * cost_single && super * 10 >= 9ll * sm_count &&
+    const long long waves_single = (tiles_total + sm_count - 1) / sm_count;
+    const double cost_single = static_cast<double>(waves_single) * (kTcBlockM + p.block_n);
+    // whole waves of pairs first, single tiles for what is left; k waves of pairs cover
+    // floor(k * SMs / tiles_n) tile rows of 256
+    const int max_pair_rows = p.tiles_m / 2;
+    double best = cost_single;
+    int best_rows = 0;
+    for (int k = 1; k <= 65; ++k) {  // up to 64 waves of pairs, then "all pairs"
+      const int rows = k == 65 ? max_pair_rows
+                               : static_cast<int>(std::min<long long>(max_pair_rows, static_cast<long long>(k) * sm_count / p.tiles_n));
+      const long long pair_tiles = static_cast<long long>(rows) * p.tiles_n;
+      const long long single_tiles = static_cast<long long>(p.tiles_m - 2 * rows) * p.tiles_n;
+      const double cost = static_cast<double>((pair_tiles + sm_count - 1) / sm_count) * (2 * kTcBlockM + p.block_n) +
+                          static_cast<double>((single_tiles + sm_count - 1) / sm_count) * (kTcBlockM + p.block_n);
+      if (cost < best - 1e-9) {
+        best = cost;
+        best_rows = rows;
+      }
+      if (rows == max_pair_rows) break;
+    }
+    const long long tiles_mixed = static_cast<long long>(p.tiles_m - best_rows) * p.tiles_n;
+    if (best_rows > 0 && best < 0.97 * cost_single && tiles_mixed * 10 >= 9ll * sm_count &&
         (kTcSmemBudget - pair_staging) / pair_stage >= 2) {
       p.pair = 1;
-      p.tiles_m = static_cast<int>(pairs_m);
+      p.pair_rows = best_rows;
+      p.tiles_m = p.tiles_m - best_rows;  // tile rows: best_rows pairs, then singles
       p.stage_bytes = pair_stage;
       p.out_bufs = 2;
       staging = pair_staging;

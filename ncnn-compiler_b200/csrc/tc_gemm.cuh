@@ -103,9 +103,12 @@ struct TcGemmParams {
   int epi_groups;      // 1 or 2 epilogue warpgroups (2: accumulator g is drained by group g; shallow layers)
   int wide;            // staged chunks are 32 columns wide (always with bf16 pairs; plain fp32 when it pays)
   int out_bufs;        // staging tiles in flight (2..4), each 8 KB per output plane
-  // 1: a tile is two 128-row halves that share one B tile per K block (tiles_m then counts these
-  // pairs): the A halves sit side by side in a stage and accumulate into neighbouring column ranges
+  // 1: tiles may be two 128-row halves that share one B tile per K block: the A halves sit side by
+  // side in a stage and accumulate into neighbouring column ranges.  The first pair_rows tile rows
+  // are such pairs (256 rows each), the remaining tiles_m - pair_rows tile rows are single tiles:
+  // whole waves of pairs, then a last wave that is not coarser than it has to be.
   int pair;
+  int pair_rows;
   long long* trace;    // optional (bring-up): per-role clock stamps of CTA 0, 8 values per tile
 };
 
@@ -672,8 +675,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
     const int my_half = is_b ? 0 : lane / PLANES;
     const CUtensorMap* my_map = is_b ? (my_plane ? &map_b1 : &map_b0) : (my_plane ? &map_a1 : &map_a0);
     const uint32_t my_off = is_b ? static_cast<uint32_t>(PLANES * AS) * slot + lane * b_slot : lane * slot;
-    const uint32_t my_tx = is_b ? PLANES * static_cast<uint32_t>(p.block_n) * p.row_bytes
-                                : static_cast<uint32_t>(PLANES * AS) * slot;
+    const uint32_t b_tx = PLANES * static_cast<uint32_t>(p.block_n) * p.row_bytes;
     int s = 0;
     uint32_t ph = 0;
     long long issued = 0;
@@ -681,9 +683,14 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       const int m_blk = tile / p.tiles_n;
       const int n_blk = tile - m_blk * p.tiles_n;
+      const bool pair_tile = m_blk < p.pair_rows;
       // a second half that starts past the last row repeats the first (its results are never stored)
-      long long m0 = static_cast<long long>(m_blk) * (kTcBlockM * AS);
-      if (m0 + static_cast<long long>(my_half) * kTcBlockM < p.M) m0 += static_cast<long long>(my_half) * kTcBlockM;
+      long long m0 = pair_tile ? static_cast<long long>(m_blk) * (2 * kTcBlockM)
+                               : static_cast<long long>(p.pair_rows) * (2 * kTcBlockM) +
+                                     static_cast<long long>(m_blk - p.pair_rows) * kTcBlockM;
+      if (pair_tile && m0 + static_cast<long long>(my_half) * kTcBlockM < p.M) m0 += static_cast<long long>(my_half) * kTcBlockM;
+      const bool issues = issuer && (is_b || pair_tile || my_half == 0);
+      const uint32_t my_tx = is_b ? b_tx : static_cast<uint32_t>(PLANES * (pair_tile ? 2 : 1)) * slot;
       const int n0 = n_blk * p.block_n;
       int img = 0, h_base = 0, w_base = 0;
       if (p.a_im2col) {
@@ -711,7 +718,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
         }
         const bool tr = p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0 && tile == static_cast<int>(gridDim.x) && kb < 32;
         if (tr) p.trace[1024 + kb * 4 + 0] = clock64();
-        if (issuer) {
+        if (issues) {
           const uint32_t dst = smem_base + s * stage_bytes + my_off;
           if (is_b) {
             tma_load_2d(dst, my_map, fb, kb * p.k_elems, n0);
@@ -774,7 +781,8 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
       const uint64_t a1_from_a = static_cast<uint64_t>(PLANES) * slot_units;  // second half's planes
       const uint64_t b_from_a = static_cast<uint64_t>(PLANES * AS) * slot_units;
       const uint32_t acc_stride = p.pair ? 256u : 128u;
-      const bool pair = p.pair != 0;
+      const int pair_rows = p.pair_rows;
+      const int tiles_n = p.tiles_n;
       const bool tracing = p.trace != nullptr && blockIdx.x == 0;
       int s = 0;
       uint32_t ph = 0;
@@ -791,6 +799,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
         if (tracing) p.trace[(tile / gridDim.x) * 16 + 1] = clock64();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * acc_stride;
         const uint32_t d_tmem1 = d_tmem + 128u;
+        const bool pair = tile / tiles_n < pair_rows;
         uint32_t accumulate = 0u;
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!mbar_wait_bounded(smem_u32(&full_bar[s]), ph, abort_ptr, kTcWaitLimitNs)) {
@@ -902,7 +911,10 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
          tile += tile_step) {
       const int m_blk = tile / p.tiles_n;
       const int n_blk = tile - m_blk * p.tiles_n;
-      const long long m_tile = static_cast<long long>(m_blk) * (kTcBlockM * AS);
+      const bool pair_tile = m_blk < p.pair_rows;
+      const long long m_tile = pair_tile ? static_cast<long long>(m_blk) * (2 * kTcBlockM)
+                                         : static_cast<long long>(p.pair_rows) * (2 * kTcBlockM) +
+                                               static_cast<long long>(m_blk - p.pair_rows) * kTcBlockM;
       const int n0 = n_blk * p.block_n;
       if (tracing) p.trace[(tile / gridDim.x) * 16 + 3] = clock64();
       // the vote keeps the warp together: tcgen05.ld below needs all 32 lanes
@@ -924,7 +936,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
         tile_scale[t] = (KIND == GEMM_I8 && n < p.N) ? __ldg(p.scale + n) : 0.0f;
       }
       // a paired tile is drained half by half; a second half past the last row is skipped
-      for (int half = 0; half < AS && ok; ++half) {
+      for (int half = 0; half < (pair_tile ? 2 : 1) && ok; ++half) {
       const long long m_half = m_tile + static_cast<long long>(half) * kTcBlockM;
       if (half == 1 && m_half >= lp.M) break;
       const long long m = m_half + quarter * 32 + lane;
