@@ -757,11 +757,12 @@ std::string tc_plan_stem(TcStemLaunch* L, const TcStemConv& c, const TcEpilogue&
   const int budget = tc_smem_budget(c.kind);
   const int weights = c.KH * planes * p.b_slot;
   const int stage = planes * p.a_plane_bytes;
-  // the epilogue of a 64-channel row takes longer than its 42 MMAs: two epilogue groups when they fit
+  // the epilogue of a 64-channel row takes longer than its 42 MMAs: two epilogue groups when they fit, and
+  // staging tiles before a third row stage (a stage holds a whole tile's input: two are a double buffer)
   p.epi_groups = 0;
   for (int groups : {2, 1}) {
     for (int bufs : {4, 3, 2}) {
-      if ((budget - weights - groups * bufs * out_tile) / stage >= 3) {
+      if ((budget - weights - groups * bufs * out_tile) / stage >= 2) {
         p.epi_groups = groups;
         p.out_bufs = bufs;
         break;
@@ -769,7 +770,7 @@ std::string tc_plan_stem(TcStemLaunch* L, const TcStemConv& c, const TcEpilogue&
     }
     if (p.epi_groups != 0) break;
   }
-  if (p.epi_groups == 0) return "shared memory cannot hold the weights, three row stages and the staging tiles";
+  if (p.epi_groups == 0) return "shared memory cannot hold the weights, two row stages and the staging tiles";
   if (p.tiles < 2 * sm_count) p.epi_groups = 1;
   p.staging_bytes = p.out_bufs * out_tile;
   p.stages = std::min(kStemMaxStages, (budget - weights - p.epi_groups * p.staging_bytes) / stage);
