@@ -225,7 +225,14 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
   if (pair_enabled() && p.tma_store && p.epi_groups == 1 && p.k_blocks >= 6 && p.block_n <= 128 &&
       p.row_bytes >= 128) {
     const int pair_stage = planes * (2 * kTcBlockM * p.row_bytes + b_bytes);
-    const int pair_staging = (res_mode != RES_NONE ? 16384 : 0) + 2 * out_tile;
+    // as many output tiles as still leave two stages (the leader waits less for stores to drain)
+    int pair_bufs = 2;
+    for (int bufs : {4, 3})
+      if ((kTcSmemBudget - (res_mode != RES_NONE ? 16384 : 0) - bufs * out_tile) / pair_stage >= 2) {
+        pair_bufs = bufs;
+        break;
+      }
+    const int pair_staging = (res_mode != RES_NONE ? 16384 : 0) + pair_bufs * out_tile;
     const long long waves_single = (tiles_total + sm_count - 1) / sm_count;
     const double cost_single = static_cast<double>(waves_single) * (kTcBlockM + p.block_n);
     // whole waves of pairs first, single tiles for what is left; k waves of pairs cover
@@ -253,7 +260,7 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
       p.pair_rows = best_rows;
       p.tiles_m = p.tiles_m - best_rows;  // tile rows: best_rows pairs, then singles
       p.stage_bytes = pair_stage;
-      p.out_bufs = 2;
+      p.out_bufs = pair_bufs;
       staging = pair_staging;
     }
   }
