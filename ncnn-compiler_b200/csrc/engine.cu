@@ -207,6 +207,8 @@ class EngineImpl {
   size_t arena_bytes_ = 0;
   size_t arena_per_image_ = 0;
   int* d_status_ = nullptr;
+  uint32_t* d_split_ws_ = nullptr;
+  int* d_split_flags_ = nullptr;
   int sm_count_ = 148;
   cudaStream_t stream_ = nullptr;
   cudaStream_t copy_stream_ = nullptr;  // uploads of the pipelined host-pointer path
@@ -2025,6 +2027,14 @@ bool EngineImpl::build(const std::string& param, const std::string& bin, const E
   cudaMemset(st, 0, 256);
   device_allocs_.push_back(st);
   d_status_ = static_cast<int*>(st);
+  // workspace of the contraction kernel that splits tiles between CTA pairs: partial accumulators
+  // and one flag word per CTA (zero between launches); all launches of a model run on one stream
+  void* ws = nullptr;
+  if (cudaMalloc(&ws, kTcSplitWorkspaceBytes + 1024) != cudaSuccess) return fail(err, "out of device memory");
+  cudaMemset(ws, 0, kTcSplitWorkspaceBytes + 1024);
+  device_allocs_.push_back(ws);
+  d_split_ws_ = static_cast<uint32_t*>(ws);
+  d_split_flags_ = reinterpret_cast<int*>(static_cast<uint8_t*>(ws) + kTcSplitWorkspaceBytes);
   return true;
 }
 
@@ -2100,8 +2110,18 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
       te.act = node.act;
       te.act_a = node.act_a;
       te.act_b = node.act_b;
+      // Gemm: (A*B^T + beta*C) * alpha; beta is in the bias already, alpha multiplies in the epilogue
+      const bool alpha_fused = node.kind == N_GEMM && node.alpha != 1.0f && node.act == ACT_NONE;
+      if (alpha_fused) {
+        te.act = ACT_SCALE;
+        te.act_a = node.alpha;
+      }
       te.out_scale = node.s_out;
       te.status = d_status_;
+      te.sk_ws = d_split_ws_;
+      te.sk_ws_bytes = kTcSplitWorkspaceBytes;
+      te.sk_flags = d_split_flags_;
+      te.sk_flag_count = kTcSplitFlagCount;
       te.out_mode = to.fmt == FMT_I8 ? OUT_I8 : (to.fmt == FMT_SPLIT ? OUT_F32_SPLIT : (to.fmt == FMT_TF32 ? OUT_F32_TF32 : (to.fmt == FMT_BF16X2 ? OUT_BF16X2 : OUT_F32)));
       if (node.res >= 0) {
         const ActRef r = ref(node.res, n);
@@ -2213,7 +2233,7 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
         perr = tc_plan_gemm(launch.get(), kind, a0, in.p1, M, node.K, node.K, node.d_w0, node.d_w1, node.O, te, sm_count_);
       }
       if (!perr.empty()) return fail(err, "layer " + node.name + ": " + perr);
-      s.kernel = std::string("tc_gemm_kernel<") + kind_name + ">";
+      s.kernel = std::string(launch->cta2 ? (launch->p.streamk ? "tc_gemm2_kernel:split<" : "tc_gemm2_kernel<") : "tc_gemm_kernel<") + kind_name + ">";
       s.run = [launch](cudaStream_t st) { return tc_launch(*launch, st); };
       plan.steps.push_back(std::move(s));
     } else if (node.kind == N_CONV || node.kind == N_DW) {
@@ -2283,7 +2303,7 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
       };
       plan.steps.push_back(std::move(s));
     }
-    if (node.kind == N_GEMM && node.alpha != 1.0f) {
+    if (node.kind == N_GEMM && node.alpha != 1.0f && !(node.impl == IMPL_TC && node.act == ACT_NONE)) {
       Step m;
       m.name = node.name + ":alpha";
       m.kernel = "k_binary";
@@ -2719,6 +2739,7 @@ int EngineImpl::finish_host_run(cudaStream_t st) {
   if (status != 0) {
     error_ = "a tensor-core pipeline wait timed out (status " + std::to_string(status) + ")";
     cudaMemset(d_status_, 0, 4);
+    cudaMemset(d_split_flags_, 0, kTcSplitFlagCount * sizeof(int));  // pieces nobody consumed
     return 7;
   }
   return 0;
@@ -2994,6 +3015,7 @@ int Engine::check_status() {
   if (status != 0) {
     impl_->error_ = "a tensor-core pipeline wait timed out (status " + std::to_string(status) + ")";
     cudaMemset(impl_->d_status_, 0, 4);
+    cudaMemset(impl_->d_split_flags_, 0, kTcSplitFlagCount * sizeof(int));
     return 7;
   }
   return 0;

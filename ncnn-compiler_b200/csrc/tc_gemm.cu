@@ -294,6 +294,106 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
   L->map_o0 = L->map_o1 = L->map_r0 = L->map_r1 = CUtensorMap{};
 }
 
+// ---- CTA pairs (tc_gemm2.cuh)
+// NCNN_B200_CTA2=0 keeps every contraction on the one-CTA kernel; NCNN_B200_STREAMK=0 never splits
+// a tile between pairs, =1 always does where it can; NCNN_B200_CTA2_MIN_KB sets the shallowest
+// contraction (K blocks per tile) that goes to pairs.
+int env_int(const char* name, int fallback) {
+  const char* f = std::getenv(name);
+  return f == nullptr || f[0] == 0 ? fallback : std::atoi(f);
+}
+
+int max_pairs_resident(int kind, int smem_bytes, int sm_count);
+
+// True when the pair kernel takes this contraction; fills the plan like finish_plan does.
+bool finish_plan_pairs(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e, int sm_count) {
+  TcGemmParams& p = L->p;
+  if (env_int("NCNN_B200_CTA2", 1) == 0 || sm_count < 2) return false;
+  if (p.k_blocks < env_int("NCNN_B200_CTA2_MIN_KB", 6)) return false;
+  const int res_mode = e.res0 == nullptr ? RES_NONE : (e.res_bf16 ? RES_BF16X2 : (e.res1 != nullptr ? RES_SPLIT : RES_F32));
+  const bool wide = e.out_mode == OUT_BF16X2 || res_mode == RES_BF16X2;
+  const bool i8_staged = e.out_mode == OUT_I8 && N % 64 == 0 && e.ldo % 16 == 0 && e.res0 == nullptr &&
+                         (reinterpret_cast<uintptr_t>(e.outq) & 15) == 0;
+  const bool f32_out = e.out_mode != OUT_I8;
+  const bool aligned = e.ldo % (wide ? 8 : 4) == 0 && (reinterpret_cast<uintptr_t>(e.out0) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(e.out1) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(e.res0) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(e.res1) & 15) == 0;
+  const bool staged = i8_staged || (f32_out && aligned &&
+                                    !(wide && (e.out_mode == OUT_F32_SPLIT || e.out_mode == OUT_F32_TF32 ||
+                                               res_mode == RES_SPLIT)));
+  if (!staged) return false;  // the pair kernel has the staged epilogue only
+  p.M = static_cast<int>(M);
+  p.N = N;
+  p.tiles_m = static_cast<int>((M + kTc2TileM - 1) / kTc2TileM);
+  // the widest tile that wastes no columns: operand traffic per output falls with the width
+  const int step = i8_staged ? 64 : (wide ? 32 : 16);
+  const int n_tiles = (N + kTc2MaxBlockN - 1) / kTc2MaxBlockN;
+  p.block_n = ((N + n_tiles - 1) / n_tiles + step - 1) / step * step;
+  p.tiles_n = (N + p.block_n - 1) / p.block_n;
+  const int budget_all = tc_smem_budget(kind);
+  const int planes = tc_planes(kind);
+  const int b_bytes = ((p.block_n / 2) * p.row_bytes + 1023) / 1024 * 1024;
+  p.stage_bytes = planes * (kTcBlockM * p.row_bytes + b_bytes);
+  p.tma_store = 1;
+  const int out_tile = (e.out_mode != OUT_I8 && (e.out_mode == OUT_F32_SPLIT || wide) ? 2 : 1) * 8192;
+  const int res_bytes = res_mode != RES_NONE ? 16384 : 0;
+  int staging = 0;
+  // as many staging tiles as leave three ring stages; one tile is the least (int8 results: two)
+  const int min_bufs = e.out_mode == OUT_I8 ? 2 : 1;
+  for (int bufs = 4; bufs >= min_bufs; --bufs) {
+    p.out_bufs = bufs;
+    staging = res_bytes + bufs * out_tile;
+    if ((budget_all - staging) / p.stage_bytes >= 3) break;
+  }
+  p.stages = std::min(kTcMaxStages, (budget_all - staging) / p.stage_bytes);
+  if (p.stages < 2) return false;
+  p.epi_groups = 1;
+  p.pair = 0;
+  p.pair_rows = 0;
+  p.staging_bytes = staging;
+  L->smem_bytes = std::max(p.stages * p.stage_bytes + staging + 1024, 120 * 1024);
+  L->kind = kind;
+  L->cta2 = 1;
+  // workers: one pair per TPC, all resident at once
+  int pairs = std::min(sm_count / 2, max_pairs_resident(kind, L->smem_bytes, sm_count));
+  if (pairs < 1) return false;
+  const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  const long long units = tiles * p.k_blocks;
+  // Splitting tiles pays when whole tiles leave SMs idle in the last wave; the pair that finishes a
+  // split tile spends about three K blocks' time on the partial sums.
+  const double cost_whole = static_cast<double>((tiles + pairs - 1) / pairs) * p.k_blocks;
+  const double cost_split = static_cast<double>((units + pairs - 1) / pairs) + 3.0;
+  const size_t ws_need = static_cast<size_t>(2 * pairs) * kTcBlockM * p.block_n * 4;
+  const bool can_split = e.sk_ws != nullptr && e.sk_flags != nullptr && e.sk_ws_bytes >= ws_need &&
+                         e.sk_flag_count >= 2 * pairs && units >= pairs;
+  const int forced = env_int("NCNN_B200_STREAMK", -1);
+  p.streamk = can_split && (forced == 1 || (forced != 0 && cost_split < 0.95 * cost_whole)) ? 1 : 0;
+  if (!p.streamk) pairs = static_cast<int>(std::min<long long>(pairs, tiles));
+  p.sk_ws = e.sk_ws;
+  p.sk_flags = e.sk_flags;
+  L->grid = 2 * pairs;
+  p.bias = e.bias;
+  p.scale = e.scale;
+  p.out0 = e.out0;
+  p.out1 = e.out1;
+  p.outq = e.outq;
+  p.res0 = e.res0;
+  p.res1 = e.res1;
+  p.res_mode = res_mode;
+  p.wide = wide ? 1 : 0;
+  p.ldo = e.ldo;
+  p.out_mode = e.out_mode;
+  p.act = e.act;
+  p.act_a = e.act_a;
+  p.act_b = e.act_b;
+  p.out_scale = e.out_scale;
+  p.status = e.status;
+  p.trace = nullptr;
+  L->map_o0 = L->map_o1 = L->map_r0 = L->map_r1 = CUtensorMap{};
+  return true;
+}
+
 // [M][N] plane seen as a 2-D tensor (N innermost) with boxes of 64 bytes (16 fp32 or 32 bf16)
 // x 128 rows, 64-byte swizzle
 std::string encode_plane(CUtensorMap* map, const void* base, long long M, int N, long long ld, bool bf16) {
@@ -379,7 +479,9 @@ std::string tc_plan_conv(TcLaunch* L, int kind, const TcIm2colView& v, const voi
   p.dil_w = v.dil_w;
   const long long M = static_cast<long long>(v.N) * v.OH * v.OW;
   if (M > 0x7fffffffll) return "too many output pixels for one launch";
-  finish_plan(L, kind, M, out_channels, e, sm_count);
+  L->cta2 = 0;
+  if (!finish_plan_pairs(L, kind, M, out_channels, e, sm_count)) finish_plan(L, kind, M, out_channels, e, sm_count);
+  const uint32_t b_box_rows = static_cast<uint32_t>(L->cta2 ? p.block_n / 2 : p.block_n);
 
   std::string err = encode_im2col(&L->map_a0, kind, v.plane0, v, p.k_elems, rb);
   if (!err.empty()) return err;
@@ -391,11 +493,11 @@ std::string tc_plan_conv(TcLaunch* L, int kind, const TcIm2colView& v, const voi
   }
   const uint64_t k_total = static_cast<uint64_t>(p.k_blocks) * p.k_elems;
   err = encode_tiled_2d(&L->map_b0, kind, w0, k_total, out_channels,
-                        k_total * elem_bytes(kind), p.k_elems, p.block_n, rb);
+                        k_total * elem_bytes(kind), p.k_elems, b_box_rows, rb);
   if (!err.empty()) return err;
   if (tc_planes(kind) == 2) {
     err = encode_tiled_2d(&L->map_b1, kind, w1, k_total, out_channels,
-                          k_total * elem_bytes(kind), p.k_elems, p.block_n, rb);
+                          k_total * elem_bytes(kind), p.k_elems, b_box_rows, rb);
     if (!err.empty()) return err;
   } else {
     L->map_b1 = L->map_b0;
@@ -420,7 +522,9 @@ std::string tc_plan_gemm(TcLaunch* L, int kind, const void* a0, const void* a1, 
   p.a_im2col = 0;
   p.OH = p.OW = p.KW = 1;
   p.stride_h = p.stride_w = p.dil_h = p.dil_w = 1;
-  finish_plan(L, kind, M, N, e, sm_count);
+  L->cta2 = 0;
+  if (!finish_plan_pairs(L, kind, M, N, e, sm_count)) finish_plan(L, kind, M, N, e, sm_count);
+  const uint32_t b_box_rows = static_cast<uint32_t>(L->cta2 ? p.block_n / 2 : p.block_n);
   std::string err = encode_tiled_2d(&L->map_a0, kind, a0, K, M, lda * es, p.k_elems, kTcBlockM, 128);
   if (!err.empty()) return err;
   if (tc_planes(kind) == 2) {
@@ -430,10 +534,10 @@ std::string tc_plan_gemm(TcLaunch* L, int kind, const void* a0, const void* a1, 
     L->map_a1 = L->map_a0;
   }
   const uint64_t k_total = static_cast<uint64_t>(p.k_blocks) * p.k_elems;
-  err = encode_tiled_2d(&L->map_b0, kind, w0, k_total, N, k_total * es, p.k_elems, p.block_n, 128);
+  err = encode_tiled_2d(&L->map_b0, kind, w0, k_total, N, k_total * es, p.k_elems, b_box_rows, 128);
   if (!err.empty()) return err;
   if (tc_planes(kind) == 2) {
-    err = encode_tiled_2d(&L->map_b1, kind, w1, k_total, N, k_total * es, p.k_elems, p.block_n, 128);
+    err = encode_tiled_2d(&L->map_b1, kind, w1, k_total, N, k_total * es, p.k_elems, b_box_rows, 128);
     if (!err.empty()) return err;
   } else {
     L->map_b1 = L->map_b0;
@@ -441,7 +545,86 @@ std::string tc_plan_gemm(TcLaunch* L, int kind, const void* a0, const void* a1, 
   return encode_epilogue_maps(L, e);
 }
 
+namespace {
+
+template <int KIND>
+cudaError_t prepare_pair_kernel() {
+  return cudaFuncSetAttribute(tc_gemm2_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              tc_smem_budget(KIND) + 1024);
+}
+
+cudaError_t prepare_pair_kernels() {
+  static std::once_flag once;
+  static cudaError_t result = cudaSuccess;
+  std::call_once(once, [] {
+    cudaError_t e = prepare_pair_kernel<GEMM_TF32>();
+    if (e == cudaSuccess) e = prepare_pair_kernel<GEMM_TF32X3>();
+    if (e == cudaSuccess) e = prepare_pair_kernel<GEMM_I8>();
+    if (e == cudaSuccess) e = prepare_pair_kernel<GEMM_BF16X3>();
+    result = e;
+  });
+  return result;
+}
+
+template <int KIND>
+int pairs_resident(int smem_bytes, int sm_count) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(static_cast<unsigned>(sm_count / 2 * 2));
+  cfg.blockDim = dim3(kTc2Threads);
+  cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
+  int clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&clusters, tc_gemm2_kernel<KIND>, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    return 0;
+  }
+  return clusters;
+}
+
+// how many CTA pairs of the kernel the device runs at once (no device: as many as there are TPCs)
+int max_pairs_resident(int kind, int smem_bytes, int sm_count) {
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) {
+    cudaGetLastError();
+    return sm_count / 2;
+  }
+  if (prepare_pair_kernels() != cudaSuccess) return 0;
+  switch (kind) {
+    case GEMM_TF32: return pairs_resident<GEMM_TF32>(smem_bytes, sm_count);
+    case GEMM_TF32X3: return pairs_resident<GEMM_TF32X3>(smem_bytes, sm_count);
+    case GEMM_BF16X3: return pairs_resident<GEMM_BF16X3>(smem_bytes, sm_count);
+    default: return pairs_resident<GEMM_I8>(smem_bytes, sm_count);
+  }
+}
+
+cudaError_t tc_launch_pairs(const TcLaunch& L, cudaStream_t stream) {
+  const cudaError_t prep = prepare_pair_kernels();
+  if (prep != cudaSuccess) return prep;
+  const dim3 grid(L.grid), block(kTc2Threads);
+  switch (L.kind) {
+    case GEMM_TF32:
+      tc_gemm2_kernel<GEMM_TF32><<<grid, block, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1,
+                                                                        L.map_o0, L.map_o1, L.map_r0, L.map_r1);
+      break;
+    case GEMM_TF32X3:
+      tc_gemm2_kernel<GEMM_TF32X3><<<grid, block, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1,
+                                                                          L.map_o0, L.map_o1, L.map_r0, L.map_r1);
+      break;
+    case GEMM_BF16X3:
+      tc_gemm2_kernel<GEMM_BF16X3><<<grid, block, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1,
+                                                                          L.map_o0, L.map_o1, L.map_r0, L.map_r1);
+      break;
+    default:
+      tc_gemm2_kernel<GEMM_I8><<<grid, block, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1,
+                                                                      L.map_o0, L.map_o1, L.map_r0, L.map_r1);
+      break;
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace
+
 cudaError_t tc_launch(const TcLaunch& L, cudaStream_t stream) {
+  if (L.cta2) return tc_launch_pairs(L, stream);
   static std::once_flag attr_once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(attr_once, [] {

@@ -110,6 +110,13 @@ struct TcGemmParams {
   int pair;
   int pair_rows;
   long long* trace;    // optional (bring-up): per-role clock stamps of CTA 0, 8 values per tile
+  // CTA pairs (tc_gemm2.cuh): tiles are 256 rows, tiles_m counts those.
+  // streamk = 1: every pair gets an equal share of all (tile, K block) units, so a tile may be split
+  // between neighbouring pairs; the pair that holds a tile's last K block adds the others' partial
+  // accumulators (exchanged through sk_ws) and runs the epilogue.
+  int streamk;
+  uint32_t* sk_ws;     // one slot of 128 x block_n accumulator words per CTA
+  int* sk_flags;       // one word per CTA: 1 while its slot holds a partial that nobody has consumed
 };
 
 // round-half-away-from-zero exactly as the reference evaluates it in fp32:
@@ -378,7 +385,43 @@ struct TcStageCfg {
   int N, block_n;
   int wide;      // 32-column chunks
   int bar_base;  // named barriers bar_base and bar_base + 1 belong to this epilogue group
+  // partial accumulators of other CTAs to add before the epilogue (split tiles): fix_count slots,
+  // the first at fix_ws, each fix_stride words after the one before; laid out [16-column group][row][16]
+  const uint32_t* fix_ws;
+  long long fix_stride;
+  int fix_count;
 };
+
+// Sum of the partial accumulators of one row over 16 columns.  The slots were written by other SMs
+// during this launch: read them from L2, never through L1.
+template <int KIND>
+__device__ __forceinline__ void tc_load_partials(const TcStageCfg& c, int col, int row, uint32_t (&sum)[16]) {
+  const uint32_t* src = c.fix_ws + (static_cast<size_t>(col >> 4) * 128 + row) * 16;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) sum[j] = 0u;
+  for (int i = 0; i < c.fix_count; ++i) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint4 a = __ldcg(reinterpret_cast<const uint4*>(src) + q);
+      const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if (KIND == GEMM_I8) sum[4 * q + e] += w[e];
+        else sum[4 * q + e] = __float_as_uint(__fadd_rn(__uint_as_float(sum[4 * q + e]), __uint_as_float(w[e])));
+      }
+    }
+    src += c.fix_stride;
+  }
+}
+
+template <int KIND>
+__device__ __forceinline__ void tc_add_partials(uint32_t (&v)[16], const uint32_t (&sum)[16]) {
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    if (KIND == GEMM_I8) v[j] += sum[j];
+    else v[j] = __float_as_uint(__fadd_rn(__uint_as_float(v[j]), __uint_as_float(sum[j])));
+  }
+}
 
 // IO: load_res(plane, smem_dst, bar, column) and store_out(plane, smem_src, column) issue the
 // TMA copies of one staging tile; the caller binds tensor maps and row coordinates.
@@ -406,6 +449,9 @@ __device__ __forceinline__ bool tc_staged_epilogue(const TcStageCfg c, const IO&
   if (leader && has_res) fetch_res(n0);
   named_barrier_sync(c.bar_base, 128);  // tile constants are in place
   bool ok = true;
+  // split tiles: the other CTAs' partial sums, fetched one 16-column group ahead of their use
+  uint32_t part[16];
+  if (c.fix_count > 0) tc_load_partials<KIND>(c, 0, row, part);
   for (int c0 = 0; c0 < c.block_n && n0 + c0 < c.N; c0 += cw) {
     const uint32_t stage0 = c.out_stage + static_cast<uint32_t>(out_slot) * out_tile_bytes;
     if (has_res) {
@@ -419,6 +465,11 @@ __device__ __forceinline__ bool tc_staged_epilogue(const TcStageCfg c, const IO&
       uint32_t v[16];
       tmem_ld16(t_row + static_cast<uint32_t>(c0 + 16 * h), v);
       tmem_ld_wait();
+      if (c.fix_count > 0) {
+        tc_add_partials<KIND>(v, part);
+        const int next = c0 + 16 * h + 16;
+        if (next < c.block_n) tc_load_partials<KIND>(c, next, row, part);
+      }
       float r[16];
       if (c.res_mode == RES_BF16X2) {
 #pragma unroll
@@ -536,11 +587,13 @@ __device__ __forceinline__ bool tc_staged_epilogue(const TcStageCfg c, const IO&
         io.store_out(1, stage0 + 8192u, n0 + c0);
       }
       tma_store_commit();
-      tma_store_wait_read(c.out_bufs - 2);
+      tma_store_wait_read(c.out_bufs >= 2 ? c.out_bufs - 2 : 0);
       const int c1 = c0 + cw;
       if (has_res && c1 < c.block_n && n0 + c1 < c.N) fetch_res(n0 + c1);
     }
-    if (++out_slot == c.out_bufs) out_slot = 0;
+    // a single staging tile is written again only after its store has read it
+    if (c.out_bufs == 1) named_barrier_sync(c.bar_base, 128);
+    if (++out_slot >= c.out_bufs) out_slot = 0;
   }
   return ok;
 }
@@ -556,6 +609,8 @@ __device__ __forceinline__ void tc_staged_epilogue_i8(const TcStageCfg c, float 
                                                       int& out_slot) {
   using namespace ptx;
   named_barrier_sync(c.bar_base, 128);  // tile constants are in place
+  uint32_t part[16];
+  if (c.fix_count > 0) tc_load_partials<KIND>(c, 0, row, part);
   for (int c0 = 0; c0 < c.block_n && n0 + c0 < c.N; c0 += 64) {
     const uint32_t stage0 = c.out_stage + static_cast<uint32_t>(out_slot) * 8192u;
 #pragma unroll
@@ -563,6 +618,11 @@ __device__ __forceinline__ void tc_staged_epilogue_i8(const TcStageCfg c, float 
       uint32_t v[16];
       tmem_ld16(t_row + static_cast<uint32_t>(c0 + 16 * h), v);
       tmem_ld_wait();
+      if (c.fix_count > 0) {
+        tc_add_partials<KIND>(v, part);
+        const int next = c0 + 16 * h + 16;
+        if (next < c.block_n) tc_load_partials<KIND>(c, next, row, part);
+      }
       uint32_t w[4];
 #pragma unroll
       for (int g = 0; g < 4; ++g) {

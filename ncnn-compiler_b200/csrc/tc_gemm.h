@@ -11,6 +11,7 @@
 
 #include "tc_conv_halo.cuh"
 #include "tc_gemm.cuh"
+#include "tc_gemm2.cuh"
 #include "tc_stem.cuh"
 
 namespace nb {
@@ -28,6 +29,7 @@ struct TcLaunch {
   int kind = GEMM_TF32;
   int grid = 0;
   int smem_bytes = 0;
+  int cta2 = 0;  // 1: tc_gemm2_kernel on CTA pairs (grid counts CTAs, two per pair)
 };
 
 // Activation tensor as TMA sees it for an im2col load, innermost dimension first:
@@ -61,7 +63,17 @@ struct TcEpilogue {
   float out_scale = 1.0f;
   int* status = nullptr;
   long long* trace = nullptr;
+  // workspace for tiles split between CTA pairs (tc_gemm2.cuh): partial accumulators and one flag
+  // word per CTA, zero before the first launch; without it tiles are never split
+  uint32_t* sk_ws = nullptr;
+  size_t sk_ws_bytes = 0;
+  int* sk_flags = nullptr;
+  int sk_flag_count = 0;
 };
+
+// bytes of partial-accumulator workspace and flag words that let every layer split tiles
+constexpr size_t kTcSplitWorkspaceBytes = 160ull * kTcBlockM * kTc2MaxBlockN * 4;
+constexpr int kTcSplitFlagCount = 160;
 
 // Elements per K block for a kind and a channel count; 0 when the tensor-core
 // path cannot address that channel count (rows must be multiples of 16 bytes).

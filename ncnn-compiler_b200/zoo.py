@@ -294,3 +294,48 @@ def dynamic_convnet(prefix, seed=800, cin=3, classes=0):
     else:
         net.conv("head", "act", "output", 32, 8, 1, 1, 0, act=0, zero_bias=False)
     return wr.save(prefix)
+
+
+def gemm(prefix, m, k, n, alpha=0.5, beta=-1.25, seed=510):
+    """Gemm in the one form the reference lowers (dynamic A [M,K], constant transposed B [N,K], constant
+    row bias C [N]): y = (A * B^T + beta * C) * alpha.  Run with any batch; each image is one [M,K] matrix."""
+    net = _Net(seed)
+    wr = net.w
+    wr.layer("Input", "input", [], ["data"], f"0={k} 1=1 2={m}")
+    wr.layer("Squeeze", "squeeze", ["data"], ["matrix"], "-23303=1,1")
+    wr.layer("Gemm", "gemm", ["matrix"], ["output"], f"0={alpha!r} 1={beta!r} 3=1 5=1 6=1 8={n} 9={k} 10=4")
+    wr.f32((net.rng.standard_normal((n, k)) * 0.02).astype(np.float32), tagged=True)
+    wr.f32((net.rng.standard_normal(n) * 0.01).astype(np.float32), tagged=True)
+    return wr.save(prefix)
+
+
+def conv_batchnorm(prefix, kind="conv", c=64, cout=64, h=14, w=14, eps=1e-5, zero_var_channels=(), bias=True,
+                   int8=False, seed=900):
+    """Input -> Convolution | ConvolutionDepthWise (3x3, no activation) -> BatchNorm -> ReLU.  The reference folds
+    the BatchNorm into an fp32 convolution and leaves it alone after a quantised one.  Channels listed in
+    `zero_var_channels` get variance 0 (with eps = 0 they take the reference's 10000 branch)."""
+    net = _Net(seed, int8=int8)
+    wr = net.w
+    wr.layer("Input", "input", [], ["data"], f"0={w} 1={h} 2={c}")
+    if kind == "depthwise":
+        cout = c
+        net.depthwise("dw", "data", "x", c, 3, 1, 1)
+    else:
+        wt = net._he((cout, c, 3, 3), c * 9)
+        if bias:
+            net.conv("conv", "data", "x", c, cout, 3, 1, 1, act=0, zero_bias=False, term=1 if int8 else 0, weights=wt)
+        else:
+            wr.layer("Convolution", "conv", ["data"], ["x"], f"0={cout} 1=3 3=1 4=1 5=0 6={wt.size}")
+            wr.f32(wt, tagged=True)
+    rng = net.rng
+    slope = rng.uniform(0.5, 1.5, cout).astype(np.float32)
+    mean = (rng.standard_normal(cout) * 0.1).astype(np.float32)
+    var = rng.uniform(0.5, 2.0, cout).astype(np.float32)
+    for ch in zero_var_channels:
+        var[ch] = 0.0
+    beta = (rng.standard_normal(cout) * 0.1).astype(np.float32)
+    wr.layer("BatchNorm", "bn", ["x"], ["y"], f"0={cout} 1={float(eps)!r}")
+    for a in (slope, mean, var, beta):
+        wr.f32(a)
+    wr.layer("ReLU", "relu", ["y"], ["output"], "0=0.0")
+    return wr.save(prefix)

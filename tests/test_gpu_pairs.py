@@ -1,0 +1,199 @@
+"""GPU parity of the paths that the benchmark configurations exercise at full width: the contraction kernel
+on CTA pairs (with and without tiles split between pairs), the whole InnerProduct/Gemm grid, Gemm on the
+tensor cores with alpha and beta, Conv -> BatchNorm folding, and the batch-256 property checks.
+
+Bars as everywhere: int8 bit exact against the oracle; fp32 relative L2 <= 1e-4 per layer (1e-3 is what the
+benchmark contract allows), stated per test.
+"""
+import numpy as np
+import pytest
+
+from conftest import rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+def _kernels(model, n):
+    return [r["kernel"] for r in model.profile(n, 1)]
+
+
+def _run(pkg, param, bin_, x, **kw):
+    m = pkg.Model(param, bin_, **kw)
+    got = m.run(x)[0].copy()
+    kernels = _kernels(m, x.shape[0])
+    m.close()
+    return got, kernels
+
+
+# ------------------------------------------------------------------ CTA pairs against the one-CTA kernel
+@pytest.mark.parametrize("h,c,cout,n", [(56, 64, 96, 8), (28, 128, 128, 8), (14, 256, 256, 16), (7, 512, 512, 24),
+                                         (9, 192, 320, 5)])
+def test_pair_kernel_equals_one_cta_kernel(pkg, oracle, tmp_path, monkeypatch, h, c, cout, n):
+    """A tile of the pair kernel is 256 rows on two CTAs; every output still accumulates its K blocks in the
+    same order as on one CTA, so the results are the same bits (whole tiles, nothing split)."""
+    param, bin_ = pkg.zoo.residual_block(str(tmp_path / "rb"), h=h, w=h, c=c, cout=cout)
+    x = np.random.default_rng(h + c).uniform(-1, 1, (n, c, h, h)).astype(np.float32)
+    monkeypatch.setenv("NCNN_B200_STREAMK", "0")
+    monkeypatch.setenv("NCNN_B200_CTA2", "1")
+    got, kernels = _run(pkg, param, bin_, x)
+    assert any(k.startswith("tc_gemm2_kernel<") for k in kernels), kernels
+    monkeypatch.setenv("NCNN_B200_CTA2", "0")
+    base, kernels = _run(pkg, param, bin_, x)
+    assert not any(k.startswith("tc_gemm2_kernel") for k in kernels), kernels
+    assert np.array_equal(got, base)
+    want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x[:2]])
+    assert rel_l2(got[:2], want) <= 1e-4
+
+
+@pytest.mark.parametrize("h,c,cout,n", [(14, 256, 256, 16), (7, 512, 512, 24), (28, 128, 128, 8), (9, 192, 320, 5)])
+def test_split_tiles_fp32(pkg, oracle, tmp_path, monkeypatch, h, c, cout, n):
+    """Tiles split between pairs: partial sums are added in a fixed order, so the result is reproducible and
+    differs from the unsplit sum only by fp32 rounding."""
+    param, bin_ = pkg.zoo.residual_block(str(tmp_path / "rb"), h=h, w=h, c=c, cout=cout)
+    x = np.random.default_rng(h * c).uniform(-1, 1, (n, c, h, h)).astype(np.float32)
+    monkeypatch.setenv("NCNN_B200_STREAMK", "1")
+    got, kernels = _run(pkg, param, bin_, x)
+    assert any(k.startswith("tc_gemm2_kernel:split<") for k in kernels), kernels
+    again, _ = _run(pkg, param, bin_, x)
+    assert np.array_equal(got, again)
+    monkeypatch.setenv("NCNN_B200_CTA2", "0")
+    base, _ = _run(pkg, param, bin_, x)
+    assert rel_l2(got, base) <= 2e-6
+    want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x[:2]])
+    assert rel_l2(got[:2], want) <= 1e-4
+
+
+@pytest.mark.parametrize("split", ["0", "1"])
+def test_pairs_int8_resnet18_bit_exact(pkg, oracle, tmp_path, monkeypatch, split):
+    """Integer sums do not depend on their order: the int8 network on CTA pairs, split or not, is bit exact."""
+    param, bin_ = pkg.zoo.resnet18(str(tmp_path / "r18q"), int8=True)
+    x = np.random.default_rng(401).uniform(-1, 1, (3, 3, 224, 224)).astype(np.float32)
+    monkeypatch.setenv("NCNN_B200_STREAMK", split)
+    got, kernels = _run(pkg, param, bin_, x)
+    assert any(k.startswith("tc_gemm2_kernel") for k in kernels), kernels
+    want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x])
+    assert np.array_equal(got, want)
+
+
+def test_split_tiles_repeat_and_recover_flags(pkg, tmp_path, monkeypatch):
+    """The flag words of the split workspace are back at zero after every launch: many runs in a row, with another
+    batch size in between, give the same bits."""
+    monkeypatch.setenv("NCNN_B200_STREAMK", "1")
+    param, bin_ = pkg.zoo.resnet18(str(tmp_path / "r18"), size=64, classes=100)
+    rng = np.random.default_rng(9)
+    x = rng.uniform(-1, 1, (16, 3, 64, 64)).astype(np.float32)
+    m = pkg.Model(param, bin_)
+    first = m.run(x)[0].copy()
+    for _ in range(5):
+        assert np.array_equal(m.run(x)[0], first)
+    m.run(x[:5])
+    assert np.array_equal(m.run(x)[0], first)
+    assert m.check_status() == 0
+    m.close()
+
+
+# ------------------------------------------------------------------ config 4: the whole InnerProduct grid
+GRID = [(m, k, n) for m in (1, 32, 256, 4096) for k in (512, 1024, 4096) for n in (512, 1024, 4096)]
+
+
+def _oracle_rows(oracle, param, bin_, x, rows):
+    model = oracle.Model(param, bin_)
+    return np.stack([model.run([x[i]])[0] for i in rows])
+
+
+@pytest.mark.parametrize("m,k,n", GRID)
+def test_inner_product_grid(pkg, oracle, tmp_path, m, k, n):
+    """Every (M, K, N) of the sweep, fp32 (rel-L2 <= 1e-4) and int8 (bit exact).  The oracle is a scalar loop, so
+    at M = 4096 it checks 48 rows spread over the batch; the other rows are covered by the row-independence
+    check (a row's result does not depend on which rows share its tile)."""
+    x = np.random.default_rng(500 + m).uniform(-1, 1, (m, 1, 1, k)).astype(np.float32)
+    rows = list(range(m)) if m <= 256 else sorted(set(np.random.default_rng(1).integers(0, m, 44).tolist() + [0, 127, 128, m - 1]))
+    for int8 in (False, True):
+        param, bin_ = pkg.zoo.inner_product(str(tmp_path / ("ipq" if int8 else "ip")), k, n, int8=int8)
+        model = pkg.Model(param, bin_)
+        got = model.run(x)[0].copy()
+        if m > 256:
+            sub = model.run(x[rows])[0]
+            assert np.array_equal(sub, got[rows])
+        model.close()
+        want = _oracle_rows(oracle, param, bin_, x, rows)
+        if int8:
+            assert np.array_equal(got[rows], want)
+        else:
+            assert rel_l2(got[rows], want) <= 1e-4
+
+
+@pytest.mark.parametrize("m,k,n,alpha,beta", [(256, 512, 1024, 0.5, -1.25), (32, 1024, 512, 1.75, 0.5),
+                                              (200, 4096, 520, -0.25, 2.0), (1, 512, 512, 3.0, -1.0)])
+def test_gemm_on_tensor_cores_alpha_beta(pkg, oracle, tmp_path, m, k, n, alpha, beta):
+    """Gemm with static M at tensor-core shapes: y = (A * B^T + beta * C) * alpha, bias scaled by beta first, then
+    the sum by alpha (NCNNToTosa.cpp:5079-5096).  The scaling runs in the contraction's epilogue."""
+    param, bin_ = pkg.zoo.gemm(str(tmp_path / "g"), m, k, n, alpha, beta)
+    x = np.random.default_rng(m + n).uniform(-1, 1, (2, m, 1, k)).astype(np.float32)
+    model = pkg.Model(param, bin_)
+    kernels = _kernels(model, 2)
+    assert any(kn.startswith("tc_gemm") for kn in kernels), kernels
+    assert "k_binary" not in kernels, kernels
+    got = model.run(x)[0]
+    model.close()
+    want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x])
+    assert got.shape == want.shape == (2, m, n)
+    assert rel_l2(got, want) <= 1e-4
+    exact, _ = _run(pkg, param, bin_, x, accuracy_mode=2)
+    assert rel_l2(exact, want) <= 2e-6
+
+
+# ------------------------------------------------------------------ Conv -> BatchNorm
+@pytest.mark.parametrize("kind,kw", [("conv", {}), ("conv", {"bias": False}), ("depthwise", {}),
+                                     ("conv", {"eps": 0.0, "zero_var_channels": (0, 5, 63)}),
+                                     ("depthwise", {"eps": 0.0, "zero_var_channels": (1, 2)})])
+@pytest.mark.parametrize("mode", [0, 2])
+def test_batchnorm_folds_into_fp32_convolution(pkg, oracle, tmp_path, kind, kw, mode):
+    """FoldNCNNBatchNorm.cpp:55-178: the BatchNorm after a single-use fp32 convolution disappears into its weights
+    and bias (var + eps == 0 takes the factor 10000, :99-160); one launch fewer, same values as the oracle's fold."""
+    param, bin_ = pkg.zoo.conv_batchnorm(str(tmp_path / "cbn"), kind=kind, **kw)
+    x = np.random.default_rng(77).uniform(-1, 1, (3, 64, 14, 14)).astype(np.float32)
+    got, kernels = _run(pkg, param, bin_, x, accuracy_mode=mode)
+    assert "k_unary" not in [k for k in kernels[1:-1]], kernels  # no stand-alone BatchNorm between the edges
+    want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x])
+    assert np.isfinite(want).all()
+    assert rel_l2(got, want) <= {0: 1e-4, 2: 2e-6}[mode]
+
+
+def test_batchnorm_after_int8_convolution_is_not_folded(pkg, oracle, tmp_path):
+    """A quantised convolution keeps its BatchNorm (FoldNCNNBatchNorm.cpp:63): integer weights cannot absorb the
+    scale.  int8 sum, dequantise, then the explicit fp32 affine map: same bits as the oracle."""
+    param, bin_ = pkg.zoo.conv_batchnorm(str(tmp_path / "cbnq"), int8=True)
+    x = np.random.default_rng(78).uniform(-1, 1, (3, 64, 14, 14)).astype(np.float32)
+    got, kernels = _run(pkg, param, bin_, x)
+    assert "k_unary" in kernels[1:-1], kernels
+    want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x])
+    assert np.array_equal(got, want)
+
+
+# ------------------------------------------------------------------ batch 256 (configs 2 and 3)
+@pytest.mark.parametrize("net", ["mobilenet_v2", "resnet18_int8"])
+def test_batch_256_properties(pkg, oracle, tmp_path, net):
+    """At the benchmark's batch 256 the oracle would need minutes, so: images are independent (a permuted batch
+    gives permuted results, a repeated image repeated results, bit for bit), and the first and last two images
+    match the oracle (int8: exactly)."""
+    if net == "mobilenet_v2":
+        param, bin_ = pkg.zoo.mobilenet_v2(str(tmp_path / "m"))
+    else:
+        param, bin_ = pkg.zoo.resnet18(str(tmp_path / "r"), int8=True)
+    rng = np.random.default_rng(256)
+    x = rng.uniform(-1, 1, (256, 3, 224, 224)).astype(np.float32)
+    x[100] = x[3]
+    m = pkg.Model(param, bin_)
+    y = m.run(x)[0].copy()
+    assert np.array_equal(y[100], y[3])
+    perm = rng.permutation(256)
+    assert np.array_equal(m.run(x[perm])[0], y[perm])
+    m.close()
+    idx = [0, 1, 254, 255]
+    om = oracle.Model(param, bin_)
+    want = np.stack([om.run([x[i]])[0] for i in idx])
+    if net.endswith("int8"):
+        assert np.array_equal(y[idx], want)
+    else:
+        assert rel_l2(y[idx], want) <= 2e-4
