@@ -2030,8 +2030,8 @@ bool EngineImpl::build(const std::string& param, const std::string& bin, const E
   // workspace of the contraction kernel that splits tiles between CTA pairs: partial accumulators
   // and one flag word per CTA (zero between launches); all launches of a model run on one stream
   void* ws = nullptr;
-  if (cudaMalloc(&ws, kTcSplitWorkspaceBytes + 1024) != cudaSuccess) return fail(err, "out of device memory");
-  cudaMemset(ws, 0, kTcSplitWorkspaceBytes + 1024);
+  if (cudaMalloc(&ws, kTcSplitWorkspaceBytes + 4096) != cudaSuccess) return fail(err, "out of device memory");
+  cudaMemset(ws, 0, kTcSplitWorkspaceBytes + 4096);
   device_allocs_.push_back(ws);
   d_split_ws_ = static_cast<uint32_t*>(ws);
   d_split_flags_ = reinterpret_cast<int*>(static_cast<uint8_t*>(ws) + kTcSplitWorkspaceBytes);
@@ -2233,7 +2233,7 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
         perr = tc_plan_gemm(launch.get(), kind, a0, in.p1, M, node.K, node.K, node.d_w0, node.d_w1, node.O, te, sm_count_);
       }
       if (!perr.empty()) return fail(err, "layer " + node.name + ": " + perr);
-      s.kernel = std::string(launch->cta2 ? (launch->p.streamk ? "tc_gemm2_kernel:split<" : "tc_gemm2_kernel<") : "tc_gemm_kernel<") + kind_name + ">";
+      s.kernel = std::string(launch->cta2 == 2 ? (launch->p.streamk ? "tc_gemm2_kernel:pairs+split<" : "tc_gemm2_kernel:pairs<") : (launch->cta2 == 1 ? "tc_gemm2_kernel:split<" : "tc_gemm_kernel<")) + kind_name + ">";
       s.run = [launch](cudaStream_t st) { return tc_launch(*launch, st); };
       plan.steps.push_back(std::move(s));
     } else if (node.kind == N_CONV || node.kind == N_DW) {
@@ -2506,7 +2506,23 @@ void EngineImpl::make_edge_steps(int64_t n, const std::vector<const float*>& d_i
     Step s;
     s.name = "input:" + t.name;
     s.bytes = static_cast<double>(t.logical()) * n * (4 + t.elem_bytes() * t.planes());
-    if (t.rank == 3) {
+    // one channel, or one pixel: channel-last order is the caller's order, a flat copy does it
+    const bool flat_layout = (t.c == 1 || t.h * t.w == 1) && t.Cp == t.c && t.Wp == t.w && t.w_off == 0;
+    const bool flat_quant = t.rank == 3 && flat_layout && t.input_quant_scale > 0.0f && dst.fmt == FMT_I8 &&
+                            (t.logical() * n) % 16 == 0 && (reinterpret_cast<uintptr_t>(src_ptr) & 15) == 0 &&
+                            (reinterpret_cast<uintptr_t>(dst.q) & 15) == 0;
+    const bool flat_in = t.rank != 3 || (flat_layout && t.input_quant_scale <= 0.0f);
+    if (flat_quant) {
+      const long long count16 = t.logical() * n / 16;
+      const int grid = grid_for(count16);
+      const float scale = t.input_quant_scale;
+      int8_t* q = dst.q;
+      s.kernel = "k_quantize16";
+      s.run = [=](cudaStream_t st) {
+        k_quantize16<<<grid, 256, 0, st>>>(src_ptr, q, count16, scale);
+        return launch_ok();
+      };
+    } else if (!flat_in) {
       EdgeParams ep{};
       ep.images = n;
       ep.C = t.c;
@@ -2547,10 +2563,12 @@ void EngineImpl::make_edge_steps(int64_t n, const std::vector<const float*>& d_i
       UnaryParams up{};
       up.op = UN_COPY;
       const long long count = t.logical() * n;
-      const int grid = grid_for(count);
+      const bool vec = count % 4 == 0 && (reinterpret_cast<uintptr_t>(src_ptr) & 15) == 0;
+      const int grid = grid_for(vec ? count / 4 : count);
       s.kernel = "k_unary";
       s.run = [=](cudaStream_t st) {
-        k_unary<1><<<grid, 256, 0, st>>>(src, dst, count, up);
+        if (vec) k_unary<4><<<grid, 256, 0, st>>>(src, dst, count, up);
+        else k_unary<1><<<grid, 256, 0, st>>>(src, dst, count, up);
         return launch_ok();
       };
     }
@@ -2563,7 +2581,8 @@ void EngineImpl::make_edge_steps(int64_t n, const std::vector<const float*>& d_i
     Step s;
     s.name = "output:" + t.name;
     s.bytes = static_cast<double>(t.logical()) * n * (4 + t.elem_bytes() * t.planes());
-    if (t.rank == 3) {
+    const bool flat_out = t.rank != 3 || ((t.c == 1 || t.h * t.w == 1) && t.Cp == t.c && t.Wp == t.w && t.w_off == 0);
+    if (!flat_out) {
       const dim3 grid((t.h * t.w + 31) / 32, (t.c + 31) / 32, static_cast<unsigned>(n));
       const int C = t.c, HW = t.h * t.w, Cp = t.Cp;
       s.kernel = "k_nhwc_to_chw_tiled";
@@ -2578,10 +2597,12 @@ void EngineImpl::make_edge_steps(int64_t n, const std::vector<const float*>& d_i
       UnaryParams up{};
       up.op = UN_COPY;
       const long long count = t.logical() * n;
-      const int grid = grid_for(count);
+      const bool vec = count % 4 == 0 && (reinterpret_cast<uintptr_t>(dst_ptr) & 15) == 0;
+      const int grid = grid_for(vec ? count / 4 : count);
       s.kernel = "k_unary";
       s.run = [=](cudaStream_t st) {
-        k_unary<1><<<grid, 256, 0, st>>>(src, dst, count, up);
+        if (vec) k_unary<4><<<grid, 256, 0, st>>>(src, dst, count, up);
+        else k_unary<1><<<grid, 256, 0, st>>>(src, dst, count, up);
         return launch_ok();
       };
     }

@@ -305,8 +305,12 @@ int env_int(const char* name, int fallback) {
 
 int max_pairs_resident(int kind, int smem_bytes, int sm_count);
 
-// True when the pair kernel takes this contraction; fills the plan like finish_plan does.
-bool finish_plan_pairs(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e, int sm_count) {
+// True when tc_gemm2_kernel takes this contraction (on CTA pairs, or on single CTAs with tiles split
+// between them); fills the plan like finish_plan does.
+// `half_blocks_ok`: K blocks of half the size (64-byte rows) address the same packed operands, so
+// the plan may trade K-block size for staging tiles.
+bool finish_plan_workers(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e, int sm_count,
+                         bool half_blocks_ok) {
   TcGemmParams& p = L->p;
   if (env_int("NCNN_B200_CTA2", 1) == 0 || sm_count < 2) return false;
   if (p.k_blocks < env_int("NCNN_B200_CTA2_MIN_KB", 6)) return false;
@@ -322,57 +326,138 @@ bool finish_plan_pairs(TcLaunch* L, int kind, long long M, int N, const TcEpilog
   const bool staged = i8_staged || (f32_out && aligned &&
                                     !(wide && (e.out_mode == OUT_F32_SPLIT || e.out_mode == OUT_F32_TF32 ||
                                                res_mode == RES_SPLIT)));
-  if (!staged) return false;  // the pair kernel has the staged epilogue only
+  if (!staged) return false;  // this kernel has the staged epilogue only
+  const int step = i8_staged ? 64 : (wide ? 32 : 16);
+  auto even_width = [&](int widest) {
+    const int n_tiles = (N + widest - 1) / widest;
+    return ((N + n_tiles - 1) / n_tiles + step - 1) / step * step;
+  };
+  const int full_kb = p.k_blocks;
+  const int forced_split = env_int("NCNN_B200_STREAMK", -1);
+  const bool ws_given = e.sk_ws != nullptr && e.sk_flags != nullptr;
+
+  // Form 1, CTA pairs: tiles of 256 rows x up to 256 columns.  Measured on ResNet-18 at batch 64: tiles of
+  // 256 columns keep the tensor pipe busy through the whole main loop (the operand path of an SM carries half
+  // the bytes per product); narrower pair tiles gain nothing over the one-CTA kernel's paired tiles and pay
+  // more barrier hand-shakes per output.  Taken when whole tiles fill at least one wave of pairs.
+  const int pair_bn = even_width(kTc2MaxBlockN);
+  const long long pair_tiles = ((M + kTc2TileM - 1) / kTc2TileM) * ((N + pair_bn - 1) / pair_bn);
+  const bool pair_form = pair_bn >= env_int("NCNN_B200_CTA2_MIN_BN", 192) &&
+                         (pair_tiles >= sm_count / 2 || env_int("NCNN_B200_CTA2_ALWAYS", 0) != 0);
+  // Form 2, single CTAs with split tiles: tiles of 128 rows x up to 128 columns, every SM an equal share of
+  // the K blocks.  Taken when whole tiles would leave SMs idle (few, deep tiles) and the workspace allows.
+  const int one_bn = even_width(128);
+  const long long one_tiles = ((M + kTcBlockM - 1) / kTcBlockM) * ((N + one_bn - 1) / one_bn);
+  const long long one_units = one_tiles * full_kb;
+  const int one_workers = static_cast<int>(std::min<long long>(sm_count, one_units / 4));
+  bool split_form = false;
+  if (!pair_form && ws_given && forced_split != 0 && one_workers >= 2) {
+    // Every worker ends with the tile it finishes, whose partial sums arrive no earlier than the other
+    // workers finish theirs: publishing, waiting and adding them is an exposed tail worth about twenty
+    // K blocks (measured on 3x3 convolutions of 256 and 512 channels at batch 64, where splitting lost).
+    const double cost_whole = static_cast<double>((one_tiles + sm_count - 1) / sm_count) * full_kb;
+    const double cost_split = static_cast<double>((one_units + one_workers - 1) / one_workers) + 20.0;
+    split_form = forced_split == 1 || cost_split < 0.9 * cost_whole;
+  }
+  if (!pair_form && !split_form) return false;
+  const int ctas = pair_form ? 2 : 1;
+  const int tile_m = pair_form ? kTc2TileM : kTcBlockM;
+
   p.M = static_cast<int>(M);
   p.N = N;
-  p.tiles_m = static_cast<int>((M + kTc2TileM - 1) / kTc2TileM);
-  // the widest tile that wastes no columns: operand traffic per output falls with the width
-  const int step = i8_staged ? 64 : (wide ? 32 : 16);
-  const int n_tiles = (N + kTc2MaxBlockN - 1) / kTc2MaxBlockN;
-  p.block_n = ((N + n_tiles - 1) / n_tiles + step - 1) / step * step;
+  p.tiles_m = static_cast<int>((M + tile_m - 1) / tile_m);
+  p.block_n = pair_form ? pair_bn : one_bn;
   p.tiles_n = (N + p.block_n - 1) / p.block_n;
   const int budget_all = tc_smem_budget(kind);
   const int planes = tc_planes(kind);
-  const int b_bytes = ((p.block_n / 2) * p.row_bytes + 1023) / 1024 * 1024;
-  p.stage_bytes = planes * (kTcBlockM * p.row_bytes + b_bytes);
   p.tma_store = 1;
   const int out_tile = (e.out_mode != OUT_I8 && (e.out_mode == OUT_F32_SPLIT || wide) ? 2 : 1) * 8192;
   const int res_bytes = res_mode != RES_NONE ? 16384 : 0;
+  // Choose epilogue groups, K-block size and staging tiles.  Two groups (each half of the columns) come
+  // first: the epilogue of a wide tile is what a worker with one or two tiles cannot hide.  Then full-size
+  // K blocks, then as many staging tiles as leave the ring deep enough to cover the copy latency.
+  const bool two_groups_ok = env_int("NCNN_B200_CTA2_GROUPS", 2) >= 2 && p.block_n >= 128 && (p.block_n / 2) % step == 0;
+  const int full_rb = p.row_bytes, full_cb = p.c_blocks, full_ke = p.k_elems;
+  bool chosen = false;
   int staging = 0;
-  // as many staging tiles as leave three ring stages; one tile is the least (int8 results: two)
-  const int min_bufs = e.out_mode == OUT_I8 ? 2 : 1;
-  for (int bufs = 4; bufs >= min_bufs; --bufs) {
+  auto try_config = [&](int groups, bool half_blocks, int bufs, int min_stages) {
+    const int rb = half_blocks ? full_rb / 2 : full_rb;
+    const int b_bytes = ((p.block_n / ctas) * rb + 1023) / 1024 * 1024;
+    const int stage = planes * (kTcBlockM * rb + b_bytes);
+    const int stg = groups * (res_bytes + bufs * out_tile);
+    const int stages = std::min(kTcMaxStages, (budget_all - stg) / stage);
+    if (stages < min_stages) return false;
+    p.epi_groups = groups;
     p.out_bufs = bufs;
-    staging = res_bytes + bufs * out_tile;
-    if ((budget_all - staging) / p.stage_bytes >= 3) break;
+    p.row_bytes = rb;
+    p.k_elems = half_blocks ? full_ke / 2 : full_ke;
+    p.c_blocks = half_blocks ? full_cb * 2 : full_cb;
+    p.k_blocks = half_blocks ? full_kb * 2 : full_kb;
+    p.stage_bytes = stage;
+    p.stages = stages;
+    staging = stg;
+    return true;
+  };
+  const bool halves = half_blocks_ok && full_rb == 128 && kind == GEMM_BF16X3;
+  for (int groups : {2, 1}) {
+    if (groups == 2 && !two_groups_ok) continue;
+    for (int hb = 0; hb < 2 && !chosen; ++hb) {
+      if (hb == 1 && !halves) continue;
+      for (int bufs : {4, 3, 2})
+        if (!chosen && try_config(groups, hb == 1, bufs, hb ? 4 : 3)) chosen = true;
+    }
+    if (chosen) break;
   }
-  p.stages = std::min(kTcMaxStages, (budget_all - staging) / p.stage_bytes);
-  if (p.stages < 2) return false;
-  p.epi_groups = 1;
+  // last resort: one group, one or two staging tiles, two stages
+  if (!chosen)
+    for (int bufs : {2, 1})
+      if (!chosen && (bufs >= 2 || e.out_mode != OUT_I8) && try_config(1, false, bufs, 2)) chosen = true;
+  if (!chosen) {
+    p.row_bytes = full_rb;
+    p.k_elems = full_ke;
+    p.c_blocks = full_cb;
+    p.k_blocks = full_kb;
+    return false;
+  }
   p.pair = 0;
   p.pair_rows = 0;
-  p.staging_bytes = staging;
+  p.staging_bytes = staging / p.epi_groups;
   L->smem_bytes = std::max(p.stages * p.stage_bytes + staging + 1024, 120 * 1024);
   L->kind = kind;
-  L->cta2 = 1;
-  // workers: one pair per TPC, all resident at once
-  int pairs = std::min(sm_count / 2, max_pairs_resident(kind, L->smem_bytes, sm_count));
-  if (pairs < 1) return false;
+  L->cta2 = ctas;
+  // workers: one per TPC (pairs) or per SM, all resident at once
+  int workers = pair_form ? std::min(sm_count / 2, max_pairs_resident(kind, L->smem_bytes, sm_count)) : sm_count;
+  if (workers < 1) return false;
   const long long tiles = static_cast<long long>(p.tiles_m) * p.tiles_n;
   const long long units = tiles * p.k_blocks;
-  // Splitting tiles pays when whole tiles leave SMs idle in the last wave; the pair that finishes a
+  // Splitting tiles pays when whole tiles leave SMs idle in the last wave; the worker that finishes a
   // split tile spends about three K blocks' time on the partial sums.
-  const double cost_whole = static_cast<double>((tiles + pairs - 1) / pairs) * p.k_blocks;
-  const double cost_split = static_cast<double>((units + pairs - 1) / pairs) + 3.0;
-  const size_t ws_need = static_cast<size_t>(2 * pairs) * kTcBlockM * p.block_n * 4;
-  const bool can_split = e.sk_ws != nullptr && e.sk_flags != nullptr && e.sk_ws_bytes >= ws_need &&
-                         e.sk_flag_count >= 2 * pairs && units >= pairs;
-  const int forced = env_int("NCNN_B200_STREAMK", -1);
-  p.streamk = can_split && (forced == 1 || (forced != 0 && cost_split < 0.95 * cost_whole)) ? 1 : 0;
-  if (!p.streamk) pairs = static_cast<int>(std::min<long long>(pairs, tiles));
+  const double cost_whole = static_cast<double>((tiles + workers - 1) / workers) * p.k_blocks;
+  const double cost_split = static_cast<double>((units + workers - 1) / workers) + 20.0 * p.k_blocks / full_kb;
+  const size_t ws_need = static_cast<size_t>(ctas * workers) * kTcBlockM * p.block_n * 4;
+  const bool can_split = ws_given && e.sk_ws_bytes >= ws_need && e.sk_flag_count >= 2 * ctas * workers &&
+                         units >= 4ll * workers;
+  if (split_form) {
+    if (!can_split && units < 4ll * workers) workers = static_cast<int>(std::max<long long>(1, units / 4));
+    p.streamk = ws_given && e.sk_ws_bytes >= static_cast<size_t>(workers) * kTcBlockM * p.block_n * 4 &&
+                        e.sk_flag_count >= 2 * workers
+                    ? 1
+                    : 0;
+    if (!p.streamk) {
+      p.row_bytes = full_rb;
+      p.k_elems = full_ke;
+      p.c_blocks = full_cb;
+      p.k_blocks = full_kb;
+      L->cta2 = 0;
+      return false;
+    }
+  } else {
+    p.streamk = can_split && (forced_split == 1 || (forced_split != 0 && cost_split < 0.95 * cost_whole)) ? 1 : 0;
+  }
+  if (!p.streamk) workers = static_cast<int>(std::min<long long>(workers, tiles));
   p.sk_ws = e.sk_ws;
   p.sk_flags = e.sk_flags;
-  L->grid = 2 * pairs;
+  L->grid = ctas * workers;
   p.bias = e.bias;
   p.scale = e.scale;
   p.out0 = e.out0;
@@ -389,7 +474,7 @@ bool finish_plan_pairs(TcLaunch* L, int kind, long long M, int N, const TcEpilog
   p.act_b = e.act_b;
   p.out_scale = e.out_scale;
   p.status = e.status;
-  p.trace = nullptr;
+  p.trace = e.trace;
   L->map_o0 = L->map_o1 = L->map_r0 = L->map_r1 = CUtensorMap{};
   return true;
 }
@@ -480,24 +565,26 @@ std::string tc_plan_conv(TcLaunch* L, int kind, const TcIm2colView& v, const voi
   const long long M = static_cast<long long>(v.N) * v.OH * v.OW;
   if (M > 0x7fffffffll) return "too many output pixels for one launch";
   L->cta2 = 0;
-  if (!finish_plan_pairs(L, kind, M, out_channels, e, sm_count)) finish_plan(L, kind, M, out_channels, e, sm_count);
-  const uint32_t b_box_rows = static_cast<uint32_t>(L->cta2 ? p.block_n / 2 : p.block_n);
+  if (!finish_plan_workers(L, kind, M, out_channels, e, sm_count, v.C % 64 == 0))
+    finish_plan(L, kind, M, out_channels, e, sm_count);
+  const uint32_t b_box_rows = static_cast<uint32_t>(L->cta2 == 2 ? p.block_n / 2 : p.block_n);
+  const int prb = p.row_bytes;  // the pair plan may have halved the K blocks
 
-  std::string err = encode_im2col(&L->map_a0, kind, v.plane0, v, p.k_elems, rb);
+  std::string err = encode_im2col(&L->map_a0, kind, v.plane0, v, p.k_elems, prb);
   if (!err.empty()) return err;
   if (tc_planes(kind) == 2) {
-    err = encode_im2col(&L->map_a1, kind, v.plane1, v, p.k_elems, rb);
+    err = encode_im2col(&L->map_a1, kind, v.plane1, v, p.k_elems, prb);
     if (!err.empty()) return err;
   } else {
     L->map_a1 = L->map_a0;
   }
   const uint64_t k_total = static_cast<uint64_t>(p.k_blocks) * p.k_elems;
   err = encode_tiled_2d(&L->map_b0, kind, w0, k_total, out_channels,
-                        k_total * elem_bytes(kind), p.k_elems, b_box_rows, rb);
+                        k_total * elem_bytes(kind), p.k_elems, b_box_rows, prb);
   if (!err.empty()) return err;
   if (tc_planes(kind) == 2) {
     err = encode_tiled_2d(&L->map_b1, kind, w1, k_total, out_channels,
-                          k_total * elem_bytes(kind), p.k_elems, b_box_rows, rb);
+                          k_total * elem_bytes(kind), p.k_elems, b_box_rows, prb);
     if (!err.empty()) return err;
   } else {
     L->map_b1 = L->map_b0;
@@ -523,21 +610,22 @@ std::string tc_plan_gemm(TcLaunch* L, int kind, const void* a0, const void* a1, 
   p.OH = p.OW = p.KW = 1;
   p.stride_h = p.stride_w = p.dil_h = p.dil_w = 1;
   L->cta2 = 0;
-  if (!finish_plan_pairs(L, kind, M, N, e, sm_count)) finish_plan(L, kind, M, N, e, sm_count);
-  const uint32_t b_box_rows = static_cast<uint32_t>(L->cta2 ? p.block_n / 2 : p.block_n);
-  std::string err = encode_tiled_2d(&L->map_a0, kind, a0, K, M, lda * es, p.k_elems, kTcBlockM, 128);
+  if (!finish_plan_workers(L, kind, M, N, e, sm_count, K % 64 == 0)) finish_plan(L, kind, M, N, e, sm_count);
+  const uint32_t b_box_rows = static_cast<uint32_t>(L->cta2 == 2 ? p.block_n / 2 : p.block_n);
+  const int prb = p.row_bytes;  // the pair plan may have halved the K blocks
+  std::string err = encode_tiled_2d(&L->map_a0, kind, a0, K, M, lda * es, p.k_elems, kTcBlockM, prb);
   if (!err.empty()) return err;
   if (tc_planes(kind) == 2) {
-    err = encode_tiled_2d(&L->map_a1, kind, a1, K, M, lda * es, p.k_elems, kTcBlockM, 128);
+    err = encode_tiled_2d(&L->map_a1, kind, a1, K, M, lda * es, p.k_elems, kTcBlockM, prb);
     if (!err.empty()) return err;
   } else {
     L->map_a1 = L->map_a0;
   }
   const uint64_t k_total = static_cast<uint64_t>(p.k_blocks) * p.k_elems;
-  err = encode_tiled_2d(&L->map_b0, kind, w0, k_total, N, k_total * es, p.k_elems, b_box_rows, 128);
+  err = encode_tiled_2d(&L->map_b0, kind, w0, k_total, N, k_total * es, p.k_elems, b_box_rows, prb);
   if (!err.empty()) return err;
   if (tc_planes(kind) == 2) {
-    err = encode_tiled_2d(&L->map_b1, kind, w1, k_total, N, k_total * es, p.k_elems, b_box_rows, 128);
+    err = encode_tiled_2d(&L->map_b1, kind, w1, k_total, N, k_total * es, p.k_elems, b_box_rows, prb);
     if (!err.empty()) return err;
   } else {
     L->map_b1 = L->map_b0;
@@ -548,32 +636,54 @@ std::string tc_plan_gemm(TcLaunch* L, int kind, const void* a0, const void* a1, 
 namespace {
 
 template <int KIND>
-cudaError_t prepare_pair_kernel() {
-  return cudaFuncSetAttribute(tc_gemm2_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              tc_smem_budget(KIND) + 1024);
+cudaError_t prepare_worker_kernel() {
+  cudaError_t e = cudaFuncSetAttribute(tc_gemm2_kernel<KIND, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       tc_smem_budget(KIND) + 1024);
+  if (e == cudaSuccess)
+    e = cudaFuncSetAttribute(tc_gemm2_kernel<KIND, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             tc_smem_budget(KIND) + 1024);
+  return e;
 }
 
-cudaError_t prepare_pair_kernels() {
+cudaError_t prepare_worker_kernels() {
   static std::once_flag once;
   static cudaError_t result = cudaSuccess;
   std::call_once(once, [] {
-    cudaError_t e = prepare_pair_kernel<GEMM_TF32>();
-    if (e == cudaSuccess) e = prepare_pair_kernel<GEMM_TF32X3>();
-    if (e == cudaSuccess) e = prepare_pair_kernel<GEMM_I8>();
-    if (e == cudaSuccess) e = prepare_pair_kernel<GEMM_BF16X3>();
+    cudaError_t e = prepare_worker_kernel<GEMM_TF32>();
+    if (e == cudaSuccess) e = prepare_worker_kernel<GEMM_TF32X3>();
+    if (e == cudaSuccess) e = prepare_worker_kernel<GEMM_I8>();
+    if (e == cudaSuccess) e = prepare_worker_kernel<GEMM_BF16X3>();
     result = e;
   });
   return result;
 }
 
+// launch configuration of tc_gemm2_kernel: clusters of two CTAs for the pair form
+struct WorkerLaunchConfig {
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attrs[2];
+  WorkerLaunchConfig(int grid, int threads, int smem_bytes, bool pair, cudaStream_t stream) {
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(static_cast<unsigned>(threads));
+    cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
+    cfg.stream = stream;
+    cfg.attrs = attrs;
+    cfg.numAttrs = 0;
+    if (pair) {
+      attrs[cfg.numAttrs].id = cudaLaunchAttributeClusterDimension;
+      attrs[cfg.numAttrs].val.clusterDim.x = 2;
+      attrs[cfg.numAttrs].val.clusterDim.y = 1;
+      attrs[cfg.numAttrs].val.clusterDim.z = 1;
+      ++cfg.numAttrs;
+    }
+  }
+};
+
 template <int KIND>
 int pairs_resident(int smem_bytes, int sm_count) {
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3(static_cast<unsigned>(sm_count / 2 * 2));
-  cfg.blockDim = dim3(kTc2Threads);
-  cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
+  WorkerLaunchConfig wc(sm_count / 2 * 2, kTc2ThreadsTwoEpi, smem_bytes, true, nullptr);
   int clusters = 0;
-  if (cudaOccupancyMaxActiveClusters(&clusters, tc_gemm2_kernel<KIND>, &cfg) != cudaSuccess) {
+  if (cudaOccupancyMaxActiveClusters(&clusters, tc_gemm2_kernel<KIND, true>, &wc.cfg) != cudaSuccess) {
     cudaGetLastError();
     return 0;
   }
@@ -587,7 +697,7 @@ int max_pairs_resident(int kind, int smem_bytes, int sm_count) {
     cudaGetLastError();
     return sm_count / 2;
   }
-  if (prepare_pair_kernels() != cudaSuccess) return 0;
+  if (prepare_worker_kernels() != cudaSuccess) return 0;
   switch (kind) {
     case GEMM_TF32: return pairs_resident<GEMM_TF32>(smem_bytes, sm_count);
     case GEMM_TF32X3: return pairs_resident<GEMM_TF32X3>(smem_bytes, sm_count);
@@ -596,35 +706,34 @@ int max_pairs_resident(int kind, int smem_bytes, int sm_count) {
   }
 }
 
-cudaError_t tc_launch_pairs(const TcLaunch& L, cudaStream_t stream) {
-  const cudaError_t prep = prepare_pair_kernels();
+template <int KIND>
+cudaError_t launch_workers(const TcLaunch& L, cudaStream_t stream) {
+  const bool pair = L.cta2 == 2;
+  WorkerLaunchConfig wc(L.grid, L.p.epi_groups == 2 ? kTc2ThreadsTwoEpi : kTc2Threads, L.smem_bytes, pair, stream);
+  if (pair)
+    return cudaLaunchKernelEx(&wc.cfg, tc_gemm2_kernel<KIND, true>, L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1,
+                              L.map_o0, L.map_o1, L.map_r0, L.map_r1);
+  return cudaLaunchKernelEx(&wc.cfg, tc_gemm2_kernel<KIND, false>, L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1,
+                            L.map_o0, L.map_o1, L.map_r0, L.map_r1);
+}
+
+cudaError_t tc_launch_workers(const TcLaunch& L, cudaStream_t stream) {
+  const cudaError_t prep = prepare_worker_kernels();
   if (prep != cudaSuccess) return prep;
-  const dim3 grid(L.grid), block(kTc2Threads);
+  cudaError_t e;
   switch (L.kind) {
-    case GEMM_TF32:
-      tc_gemm2_kernel<GEMM_TF32><<<grid, block, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1,
-                                                                        L.map_o0, L.map_o1, L.map_r0, L.map_r1);
-      break;
-    case GEMM_TF32X3:
-      tc_gemm2_kernel<GEMM_TF32X3><<<grid, block, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1,
-                                                                          L.map_o0, L.map_o1, L.map_r0, L.map_r1);
-      break;
-    case GEMM_BF16X3:
-      tc_gemm2_kernel<GEMM_BF16X3><<<grid, block, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1,
-                                                                          L.map_o0, L.map_o1, L.map_r0, L.map_r1);
-      break;
-    default:
-      tc_gemm2_kernel<GEMM_I8><<<grid, block, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1,
-                                                                      L.map_o0, L.map_o1, L.map_r0, L.map_r1);
-      break;
+    case GEMM_TF32: e = launch_workers<GEMM_TF32>(L, stream); break;
+    case GEMM_TF32X3: e = launch_workers<GEMM_TF32X3>(L, stream); break;
+    case GEMM_BF16X3: e = launch_workers<GEMM_BF16X3>(L, stream); break;
+    default: e = launch_workers<GEMM_I8>(L, stream); break;
   }
-  return cudaGetLastError();
+  return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 }  // namespace
 
 cudaError_t tc_launch(const TcLaunch& L, cudaStream_t stream) {
-  if (L.cta2) return tc_launch_pairs(L, stream);
+  if (L.cta2) return tc_launch_workers(L, stream);
   static std::once_flag attr_once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(attr_once, [] {

@@ -29,7 +29,7 @@ struct TcLaunch {
   int kind = GEMM_TF32;
   int grid = 0;
   int smem_bytes = 0;
-  int cta2 = 0;  // 1: tc_gemm2_kernel on CTA pairs (grid counts CTAs, two per pair)
+  int cta2 = 0;  // CTAs per worker of tc_gemm2_kernel: 2 = CTA pairs, 1 = single CTAs with split tiles, 0 = tc_gemm_kernel
 };
 
 // Activation tensor as TMA sees it for an im2col load, innermost dimension first:
@@ -73,7 +73,7 @@ struct TcEpilogue {
 
 // bytes of partial-accumulator workspace and flag words that let every layer split tiles
 constexpr size_t kTcSplitWorkspaceBytes = 160ull * kTcBlockM * kTc2MaxBlockN * 4;
-constexpr int kTcSplitFlagCount = 160;
+constexpr int kTcSplitFlagCount = 640;  // two per CTA (one per epilogue group)
 
 // Elements per K block for a kind and a channel count; 0 when the tensor-core
 // path cannot address that channel count (rows must be multiples of 16 bytes).

@@ -21,15 +21,22 @@
 //   those flags (bounded), adds the partial sums in a fixed order and runs the epilogue.  A worker
 //   therefore never waits for anything that itself waits, and sums are reproducible run to run.
 //
-// Warps of a CTA (224 threads): 0 A producer, 1 MMA issuer (CTA 0) / idle (CTA 1), 2-5 epilogue,
-// 6 B producer.  All waits are bounded and end in the status word.
+// The same kernel also runs with one CTA per worker (PAIR = false: tiles of 128 rows, the whole B tile in
+// the CTA, cta_group::1 instructions, no cluster): that form serves contractions whose few tiles must be
+// split to fill the GPU but whose B operand one SM should stream alone (InnerProduct with a handful of rows:
+// a pair's CTA sees only half of the weights per MMA, which halves the rate at which an SM can stream them).
+//
+// Warps of a CTA: 0 A producer, 1 MMA issuer (CTA 0) / idle (CTA 1), 2-5 epilogue, 6 B producer, and for
+// wide tiles 7-10 a second epilogue group that drains the other half of the columns.  All waits are
+// bounded and end in the status word.
 #pragma once
 
 #include "tc_gemm.cuh"
 
 namespace nb {
 
-constexpr int kTc2Threads = 224;
+constexpr int kTc2Threads = 224;        // warps: 0 A producer, 1 MMA issuer, 2-5 epilogue, 6 B producer
+constexpr int kTc2ThreadsTwoEpi = 352;  // + warps 7-10: a second epilogue group for the other half of the columns
 constexpr int kTc2TileM = 256;  // rows of a pair's tile
 constexpr int kTc2MaxBlockN = 256;
 constexpr int kTc2AccStride = 256;  // tensor-memory columns between the two accumulators
@@ -95,8 +102,8 @@ struct Tc2Work {
   }
 };
 
-template <int KIND>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kTc2Threads, 1)
+template <int KIND, bool PAIR>
+__global__ void __launch_bounds__(kTc2ThreadsTwoEpi, 1)
 tc_gemm2_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ CUtensorMap map_a0,
                 const __grid_constant__ CUtensorMap map_a1,
                 const __grid_constant__ CUtensorMap map_b0,
@@ -113,7 +120,7 @@ tc_gemm2_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ 
   __shared__ __align__(8) uint64_t empty_bar[kTcMaxStages];  // per CTA: the MMAs that read the stage are done
   __shared__ __align__(8) uint64_t tfull_bar[2];             // per CTA: accumulator complete
   __shared__ __align__(8) uint64_t tempty_bar[2];            // used in CTA 0: both CTAs' epilogues have drained it
-  __shared__ __align__(8) uint64_t res_bar;
+  __shared__ __align__(8) uint64_t res_bar[2];
   __shared__ __align__(16) float tile_bias[kTc2MaxBlockN];
   __shared__ __align__(16) float tile_scale[KIND == GEMM_I8 ? kTc2MaxBlockN : 4];
   __shared__ uint32_t tmem_slot;
@@ -121,17 +128,20 @@ tc_gemm2_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const uint32_t rank = cluster_ctarank();
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;
+  constexpr int CTAS = PAIR ? 2 : 1;               // CTAs per worker
+  constexpr int TILE_M = PAIR ? kTc2TileM : kTcBlockM;  // rows of a worker's tile
   const uint32_t smem_base = (smem_u32(tc2_smem_raw) + 1023u) & ~1023u;
   const uint32_t slot = static_cast<uint32_t>(kTcBlockM) * p.row_bytes;
   const uint32_t stage_bytes = static_cast<uint32_t>(p.stage_bytes);
   const uint32_t b_slot = (stage_bytes / PLANES) - slot;  // this CTA's half of the B tile, rounded to 1 KB
-  const int b_rows = p.block_n / 2;
+  const int b_rows = p.block_n / CTAS;
   const int S = p.stages;
   volatile int* abort_ptr = &abort_flag;
 
+  const unsigned trace_cta = (gridDim.x / 4u) * 2u;  // bring-up stamps come from a pair in the middle of the grid
   Tc2Work work;
-  work.init(p, static_cast<int>(blockIdx.x >> 1), static_cast<int>(gridDim.x >> 1));
+  work.init(p, static_cast<int>(blockIdx.x) / CTAS, static_cast<int>(gridDim.x) / CTAS);
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -141,9 +151,10 @@ tc_gemm2_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ 
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(smem_u32(&tfull_bar[i]), 1);
-      mbar_init(smem_u32(&tempty_bar[i]), 8);  // four epilogue warps of each CTA
+      mbar_init(smem_u32(&tempty_bar[i]), 4u * CTAS * static_cast<uint32_t>(p.epi_groups));  // every epilogue warp of the worker
     }
-    mbar_init(smem_u32(&res_bar), 1);
+    mbar_init(smem_u32(&res_bar[0]), 1);
+    mbar_init(smem_u32(&res_bar[1]), 1);
     fence_mbar_init();
     prefetch_tensormap(&map_a0);
     prefetch_tensormap(&map_b0);
@@ -153,12 +164,17 @@ tc_gemm2_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ 
     }
   }
   if (warp == 1) {
-    tmem_alloc_pair(smem_u32(&tmem_slot), kTcTmemCols);
-    tmem_relinquish_pair();
+    if (PAIR) {
+      tmem_alloc_pair(smem_u32(&tmem_slot), kTcTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(&tmem_slot), kTcTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
-  cluster_sync_all();  // the other CTA's barriers exist before anything is sent to them
+  if (PAIR) cluster_sync_all();  // the other CTA's barriers exist before anything is sent to them
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
 
@@ -170,7 +186,7 @@ tc_gemm2_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ 
     const bool issuer = lane < PLANES;
     const CUtensorMap* my_map = is_b ? (lane ? &map_b1 : &map_b0) : (lane ? &map_a1 : &map_a0);
     const uint32_t my_off = is_b ? static_cast<uint32_t>(PLANES) * slot + lane * b_slot : lane * slot;
-    const uint32_t tx_both = 2u * PLANES * (is_b ? static_cast<uint32_t>(b_rows) * p.row_bytes : slot);
+    const uint32_t tx_both = static_cast<uint32_t>(CTAS) * PLANES * (is_b ? static_cast<uint32_t>(b_rows) * p.row_bytes : slot);
     int s = 0;
     uint32_t ph = 0;
     long long issued = 0;
@@ -181,7 +197,7 @@ tc_gemm2_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ 
       const int m_blk = tile / p.tiles_n;
       const int n_blk = tile - m_blk * p.tiles_n;
       // a second half that starts past the last row repeats the first (its results are never stored)
-      long long m0 = static_cast<long long>(m_blk) * kTc2TileM;
+      long long m0 = static_cast<long long>(m_blk) * TILE_M;
       if (m0 + static_cast<long long>(rank) * kTcBlockM < p.M) m0 += static_cast<long long>(rank) * kTcBlockM;
       const int n0 = n_blk * p.block_n + static_cast<int>(rank) * b_rows;
       int img = 0, h_base = 0, w_base = 0;
@@ -199,7 +215,7 @@ tc_gemm2_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ 
       int kh = tap0 / p.KW;
       int kw = tap0 - kh * p.KW;
       for (int kb = kb0; kb < kb1; ++kb) {
-        const uint32_t fb = map_to_cta(smem_u32(&full_bar[s]), 0u);
+        const uint32_t fb = PAIR ? map_to_cta(smem_u32(&full_bar[s]), 0u) : smem_u32(&full_bar[s]);
         int w = 1;
         if (lane == 0) {
           w = mbar_wait_bounded(smem_u32(&empty_bar[s]), ph ^ 1u, abort_ptr, kTcWaitLimitNs) ? 1 : 0;
@@ -210,17 +226,31 @@ tc_gemm2_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ 
           ok = false;
           break;
         }
+        const bool tr = p.trace != nullptr && blockIdx.x == trace_cta && threadIdx.x == 0 && i == 0 && kb - kb0 < 40;
+        if (tr) p.trace[16 + 4 * (kb - kb0) + 2] = clock64();
         if (issuer) {
           const uint32_t dst = smem_base + s * stage_bytes + my_off;
-          if (is_b) {
-            tma_load_2d_pair(dst, my_map, fb, kb * p.k_elems, n0);
-          } else if (p.a_im2col) {
-            tma_load_im2col_4d_pair(dst, my_map, fb, cb * p.k_elems, w_base, h_base, img,
-                                    static_cast<uint16_t>(kw * p.dil_w), static_cast<uint16_t>(kh * p.dil_h));
+          if (PAIR) {
+            if (is_b) {
+              tma_load_2d_pair(dst, my_map, fb, kb * p.k_elems, n0);
+            } else if (p.a_im2col) {
+              tma_load_im2col_4d_pair(dst, my_map, fb, cb * p.k_elems, w_base, h_base, img,
+                                      static_cast<uint16_t>(kw * p.dil_w), static_cast<uint16_t>(kh * p.dil_h));
+            } else {
+              tma_load_2d_pair(dst, my_map, fb, kb * p.k_elems, static_cast<int>(m0));
+            }
           } else {
-            tma_load_2d_pair(dst, my_map, fb, kb * p.k_elems, static_cast<int>(m0));
+            if (is_b) {
+              tma_load_2d(dst, my_map, fb, kb * p.k_elems, n0);
+            } else if (p.a_im2col) {
+              tma_load_im2col_4d(dst, my_map, fb, cb * p.k_elems, w_base, h_base, img,
+                                 static_cast<uint16_t>(kw * p.dil_w), static_cast<uint16_t>(kh * p.dil_h));
+            } else {
+              tma_load_2d(dst, my_map, fb, kb * p.k_elems, static_cast<int>(m0));
+            }
           }
         }
+        if (tr) p.trace[16 + 4 * (kb - kb0) + 3] = clock64();
         ++issued;
         if (++cb == p.c_blocks) {
           cb = 0;
@@ -255,8 +285,8 @@ tc_gemm2_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ 
     // ---------------------------------------------------------- MMA issuer (CTA 0 only)
     if (lane == 0 && rank == 0) {
       const uint32_t idesc = KIND == GEMM_I8
-                                 ? instr_desc(2u, 1u, kTc2TileM, static_cast<uint32_t>(p.block_n))
-                                 : instr_desc(1u, KIND == GEMM_BF16X3 ? 1u : 2u, kTc2TileM,
+                                 ? instr_desc(2u, 1u, TILE_M, static_cast<uint32_t>(p.block_n))
+                                 : instr_desc(1u, KIND == GEMM_BF16X3 ? 1u : 2u, TILE_M,
                                               static_cast<uint32_t>(p.block_n));
       const int k_steps = p.row_bytes / 32;
       const uint64_t desc_fixed = smem_desc_kmajor(0u, static_cast<uint32_t>(p.row_bytes));
@@ -280,41 +310,76 @@ tc_gemm2_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ 
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * kTc2AccStride;
         uint32_t accumulate = 0u;
+        const bool tracing = p.trace != nullptr && blockIdx.x == trace_cta && i == 0;
+        if (tracing) {
+          p.trace[0] = clock64();
+          p.trace[1] = static_cast<long long>(global_timer_ns());
+        }
+        const bool ptr = p.trace != nullptr && blockIdx.x == trace_cta && i < 6;
+        if (ptr) p.trace[512 + 8 * i] = clock64();
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait_bounded(smem_u32(&full_bar[s]), ph, abort_ptr, kTcWaitLimitNs)) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
+          if (tracing && kb - kb0 < 40) p.trace[16 + 4 * (kb - kb0)] = clock64();
           const uint64_t a0 = a_first + static_cast<uint64_t>(s) * stage_units;
           const uint64_t b0 = a0 + b_from_a;
 #pragma unroll 4
           for (int k = 0; k < k_steps; ++k) {
             const uint64_t ka = a0 + 2u * k;
             const uint64_t kbd = b0 + 2u * k;
-            if (KIND == GEMM_TF32) {
-              mma_tf32_pair(d_tmem, ka, kbd, idesc, accumulate);
-            } else if (KIND == GEMM_TF32X3) {
-              mma_tf32_pair(d_tmem, ka + slot_units, kbd, idesc, accumulate);  // lo * hi
-              mma_tf32_pair(d_tmem, ka, kbd + b_slot_units, idesc, 1u);        // hi * lo
-              mma_tf32_pair(d_tmem, ka, kbd, idesc, 1u);                       // hi * hi
-            } else if (KIND == GEMM_BF16X3) {
-              mma_f16_pair(d_tmem, ka + slot_units, kbd, idesc, accumulate);  // mid * hi
-              mma_f16_pair(d_tmem, ka, kbd + b_slot_units, idesc, 1u);        // hi * mid
-              mma_f16_pair(d_tmem, ka, kbd, idesc, 1u);                       // hi * hi
+            if (PAIR) {
+              if (KIND == GEMM_TF32) {
+                mma_tf32_pair(d_tmem, ka, kbd, idesc, accumulate);
+              } else if (KIND == GEMM_TF32X3) {
+                mma_tf32_pair(d_tmem, ka + slot_units, kbd, idesc, accumulate);  // lo * hi
+                mma_tf32_pair(d_tmem, ka, kbd + b_slot_units, idesc, 1u);        // hi * lo
+                mma_tf32_pair(d_tmem, ka, kbd, idesc, 1u);                       // hi * hi
+              } else if (KIND == GEMM_BF16X3) {
+                mma_f16_pair(d_tmem, ka + slot_units, kbd, idesc, accumulate);  // mid * hi
+                mma_f16_pair(d_tmem, ka, kbd + b_slot_units, idesc, 1u);        // hi * mid
+                mma_f16_pair(d_tmem, ka, kbd, idesc, 1u);                       // hi * hi
+              } else {
+                mma_i8_pair(d_tmem, ka, kbd, idesc, accumulate);
+              }
             } else {
-              mma_i8_pair(d_tmem, ka, kbd, idesc, accumulate);
+              if (KIND == GEMM_TF32) {
+                mma_tf32(d_tmem, ka, kbd, idesc, accumulate);
+              } else if (KIND == GEMM_TF32X3) {
+                mma_tf32(d_tmem, ka + slot_units, kbd, idesc, accumulate);
+                mma_tf32(d_tmem, ka, kbd + b_slot_units, idesc, 1u);
+                mma_tf32(d_tmem, ka, kbd, idesc, 1u);
+              } else if (KIND == GEMM_BF16X3) {
+                mma_f16(d_tmem, ka + slot_units, kbd, idesc, accumulate);
+                mma_f16(d_tmem, ka, kbd + b_slot_units, idesc, 1u);
+                mma_f16(d_tmem, ka, kbd, idesc, 1u);
+              } else {
+                mma_i8(d_tmem, ka, kbd, idesc, accumulate);
+              }
             }
             accumulate = 1u;
           }
-          tc_commit_pair(smem_u32(&empty_bar[s]), 3);  // the stage is free in both CTAs
+          if (PAIR) tc_commit_pair(smem_u32(&empty_bar[s]), 3);  // the stage is free in both CTAs
+          else tc_commit(smem_u32(&empty_bar[s]));
+          if (tracing && kb - kb0 < 40) p.trace[16 + 4 * (kb - kb0) + 1] = clock64();
           if (++s == S) {
             s = 0;
             ph ^= 1u;
           }
         }
         if (!ok) break;
-        tc_commit_pair(smem_u32(&tfull_bar[acc]), 3);  // both CTAs' halves of the accumulator are complete
+        if (PAIR) tc_commit_pair(smem_u32(&tfull_bar[acc]), 3);  // both CTAs' halves of the accumulator are complete
+        else tc_commit(smem_u32(&tfull_bar[acc]));
+        if (tracing) {
+          p.trace[2] = clock64();
+          p.trace[3] = static_cast<long long>(global_timer_ns());
+        }
+        if (ptr) {
+          p.trace[512 + 8 * i + 1] = clock64();
+          p.trace[512 + 8 * i + 5] = kb1 - kb0;
+        }
         acc ^= 1;
         if (acc == 0) acc_ph ^= 1u;
       }
@@ -323,20 +388,34 @@ tc_gemm2_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ 
       }
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2-5 of both CTAs)
-    const bool leader = threadIdx.x == 64;
+    // ------------------------------------------------------------ epilogue (both CTAs)
+    // One group (warps 2-5) drains all block_n columns; with two groups (352 threads) warps 2-5 take
+    // the first half of the columns and warps 7-10 the second, each with its own staging tiles,
+    // barriers, residual barrier and workspace flags.  An epilogue warp runs alone on its scheduler
+    // and pays every instruction's latency, so two groups nearly halve the time of a wide tile.
+    const int groups = p.epi_groups;
+    const int group = warp >= 7 ? 1 : 0;
+    const int first_thread = group ? 224 : 64;
+    const bool leader = static_cast<int>(threadIdx.x) == first_thread;
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+31] belong to this warp
     const int row = quarter * 32 + lane;
+    const int half = p.block_n / groups;  // columns of this group
+    const int col0 = group * half;        // first column of the group inside the tile
     const size_t slot_words = static_cast<size_t>(kTcBlockM) * p.block_n;
+    const int bar_base = 1 + 3 * group;   // named barriers bar_base .. bar_base + 2
+    const int my_flag = static_cast<int>(blockIdx.x) * 2 + group;
+    const int flag_step = 2 * CTAS;  // flag words between this CTA and the same CTA of the worker before
+    float* my_bias = tile_bias + col0;
+    float* my_scale = tile_scale + (KIND == GEMM_I8 ? col0 : 0);
     int acc = 0;
     uint32_t acc_ph = 0;
     uint32_t res_ph = 0;
     int out_slot = 0;
     bool ok = true;
     TcStageCfg cfg{};
-    cfg.res_stage = smem_base + static_cast<uint32_t>(S) * stage_bytes;
+    cfg.res_stage = smem_base + static_cast<uint32_t>(S) * stage_bytes + static_cast<uint32_t>(group) * p.staging_bytes;
     cfg.out_stage = cfg.res_stage + (p.res_mode != RES_NONE ? 16384u : 0u);
-    cfg.res_bar = smem_u32(&res_bar);
+    cfg.res_bar = smem_u32(&res_bar[group]);
     cfg.out_bufs = p.out_bufs;
     cfg.out_mode = p.out_mode;
     cfg.res_mode = p.res_mode;
@@ -344,40 +423,58 @@ tc_gemm2_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ 
     cfg.act_a = p.act_a;
     cfg.act_b = p.act_b;
     cfg.N = p.N;
-    cfg.block_n = p.block_n;
+    cfg.block_n = half;
     cfg.wide = p.wide;
-    cfg.bar_base = 1;
-    cfg.fix_stride = -2ll * static_cast<long long>(slot_words);  // the same CTA rank of the pair before
-    const uint32_t tempty0 = map_to_cta(smem_u32(&tempty_bar[0]), 0u);
-    const uint32_t tempty1 = map_to_cta(smem_u32(&tempty_bar[1]), 0u);
+    cfg.bar_base = bar_base;
+    cfg.fix_stride = -static_cast<long long>(CTAS) * static_cast<long long>(slot_words);  // the same CTA of the worker before
+    const uint32_t tempty0 = PAIR ? map_to_cta(smem_u32(&tempty_bar[0]), 0u) : smem_u32(&tempty_bar[0]);
+    const uint32_t tempty1 = PAIR ? map_to_cta(smem_u32(&tempty_bar[1]), 0u) : smem_u32(&tempty_bar[1]);
     for (int i = 0; i < work.nseg && ok; ++i) {
       int tile, kb0, kb1, owned;
       work.seg(i, &tile, &kb0, &kb1, &owned);
       const int m_blk = tile / p.tiles_n;
       const int n_blk = tile - m_blk * p.tiles_n;
-      const long long m_first = static_cast<long long>(m_blk) * kTc2TileM + static_cast<long long>(rank) * kTcBlockM;
-      const int n0 = n_blk * p.block_n;
+      const long long m_first = static_cast<long long>(m_blk) * TILE_M + static_cast<long long>(rank) * kTcBlockM;
+      const bool row_valid = m_first + row < p.M;  // rows past the end hold nothing worth exchanging
+      const int n0 = n_blk * p.block_n + col0;
       // the vote keeps the warp together: tcgen05.ld below needs all 32 lanes
       ok = __all_sync(0xffffffffu,
                       mbar_wait_bounded(smem_u32(&tfull_bar[acc]), acc_ph, abort_ptr, kTcWaitLimitNs) ? 1 : 0) != 0;
       if (!ok) break;
       tc_fence_after_sync();
+      const bool etr = p.trace != nullptr && blockIdx.x == trace_cta && threadIdx.x == 64 && i == 0;
+      if (etr) p.trace[4] = clock64();
+      const bool eptr = p.trace != nullptr && blockIdx.x == trace_cta && threadIdx.x == 64 && i < 6;
+      if (eptr) {
+        p.trace[512 + 8 * i + 2] = clock64();
+        p.trace[512 + 8 * i + 6] = owned;
+      }
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) +
-                             static_cast<uint32_t>(acc) * kTc2AccStride;
+                             static_cast<uint32_t>(acc) * kTc2AccStride + static_cast<uint32_t>(col0);
+      // this group's columns of a CTA's workspace slot: [16-column group][row][16]
+      const size_t ws_group = static_cast<size_t>(col0 >> 4) * 128 * 16;
       if (!owned) {
         // a piece of a tile that another pair finishes: raw accumulator to this CTA's slot, then the flag
-        uint32_t* dst = p.sk_ws + static_cast<size_t>(blockIdx.x) * slot_words;
-        for (int c0 = 0; c0 < p.block_n; c0 += 16) {
-          uint32_t v[16];
+        uint32_t* dst = p.sk_ws + static_cast<size_t>(blockIdx.x) * slot_words + ws_group;
+        for (int c0 = 0; c0 < half; c0 += 32) {
+          uint32_t v[16], w[16];
           tmem_ld16(t_row + static_cast<uint32_t>(c0), v);
+          tmem_ld16(t_row + static_cast<uint32_t>(c0 + 16), w);
           tmem_ld_wait();
           uint4* d4 = reinterpret_cast<uint4*>(dst + (static_cast<size_t>(c0 >> 4) * 128 + row) * 16);
+          if (row_valid) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) d4[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            for (int q = 0; q < 4; ++q) d4[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            if (c0 + 16 < half) {
+              d4 += 128 * 4;
+#pragma unroll
+              for (int q = 0; q < 4; ++q) d4[q] = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+            }
+          }
         }
         __threadfence();
-        named_barrier_sync(3, 128);
-        if (leader) st_release_gpu(p.sk_flags + blockIdx.x, 1);
+        named_barrier_sync(bar_base + 2, 128);
+        if (leader) st_release_gpu(p.sk_flags + my_flag, 1);
       } else {
         const int fix = work.contributors(tile, kb0);
         if (fix > 0) {
@@ -385,7 +482,7 @@ tc_gemm2_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ 
           int got = 1;
           if (lane == 0) {
             for (int c = 1; c <= fix && got; ++c) {
-              const int* flag = p.sk_flags + (static_cast<int>(blockIdx.x) - 2 * c);
+              const int* flag = p.sk_flags + (my_flag - flag_step * c);
               uint64_t t0 = 0;
               uint32_t polls = 0;
               while (ld_acquire_gpu(flag) == 0) {
@@ -406,16 +503,21 @@ tc_gemm2_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ 
           }
           ok = __all_sync(0xffffffffu, got) != 0;
           if (!ok) break;
+          if (eptr) {
+            p.trace[512 + 8 * i + 4] = clock64();
+            p.trace[512 + 8 * i + 7] = fix;
+          }
         }
         if (m_first < p.M) {
-          cfg.fix_count = fix;
-          cfg.fix_ws = fix > 0 ? p.sk_ws + static_cast<size_t>(static_cast<int>(blockIdx.x) - 2) * slot_words : nullptr;
-          // per-column constants of this tile (every warp has left the previous tile's last chunk:
-          // it ends with a barrier)
-          for (int t = static_cast<int>(threadIdx.x) - 64; t < p.block_n; t += 128) {
+          cfg.fix_count = row_valid ? fix : 0;  // (a row past the end skips the loads; its results are clipped)
+          cfg.fix_ws = fix > 0 ? p.sk_ws + static_cast<size_t>(static_cast<int>(blockIdx.x) - CTAS) * slot_words + ws_group
+                               : nullptr;
+          // per-column constants of this tile (every warp of the group has left the previous tile's last
+          // chunk: it ends with a barrier)
+          for (int t = static_cast<int>(threadIdx.x) - first_thread; t < half; t += 128) {
             const int n = n0 + t;
-            tile_bias[t] = (p.bias != nullptr && n < p.N) ? __ldg(p.bias + n) : 0.0f;
-            if (KIND == GEMM_I8) tile_scale[t] = n < p.N ? __ldg(p.scale + n) : 0.0f;
+            my_bias[t] = (p.bias != nullptr && n < p.N) ? __ldg(p.bias + n) : 0.0f;
+            if (KIND == GEMM_I8) my_scale[t] = n < p.N ? __ldg(p.scale + n) : 0.0f;
           }
           const int m_row = static_cast<int>(m_first);
           struct {
@@ -429,23 +531,28 @@ tc_gemm2_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ 
             }
           } io{&map_o0, &map_o1, &map_r0, &map_r1, m_row};
           if (p.out_mode == OUT_I8) {
-            tc_staged_epilogue_i8<KIND>(cfg, p.out_scale, io, t_row, n0, row, leader, tile_bias, tile_scale, out_slot);
+            tc_staged_epilogue_i8<KIND>(cfg, p.out_scale, io, t_row, n0, row, leader, my_bias, my_scale, out_slot);
           } else {
-            ok = tc_staged_epilogue<KIND>(cfg, io, t_row, n0, row, leader, tile_bias, tile_scale, res_ph, out_slot,
+            ok = tc_staged_epilogue<KIND>(cfg, io, t_row, n0, row, leader, my_bias, my_scale, res_ph, out_slot,
                                           abort_ptr);
             if (!ok) break;
           }
         }
         if (fix > 0) {
-          // every warp has read the slots (it passed the chunk barriers, or this one): free them
-          named_barrier_sync(3, 128);
+          // every warp of the group has read the slots (it passed the chunk barriers, or this one): free them
+          named_barrier_sync(bar_base + 2, 128);
           if (leader)
-            for (int c = 1; c <= fix; ++c) p.sk_flags[static_cast<int>(blockIdx.x) - 2 * c] = 0;
+            for (int c = 1; c <= fix; ++c) p.sk_flags[my_flag - flag_step * c] = 0;
         }
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(acc ? tempty1 : tempty0);
+      if (etr) p.trace[5] = clock64();
+      if (eptr) p.trace[512 + 8 * i + 3] = clock64();
+      if (lane == 0) {
+        if (PAIR) mbar_arrive_cluster(acc ? tempty1 : tempty0);
+        else mbar_arrive(acc ? tempty1 : tempty0);
+      }
       acc ^= 1;
       if (acc == 0) acc_ph ^= 1u;
     }
@@ -458,9 +565,12 @@ tc_gemm2_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ 
   // Neither CTA leaves while the other may still signal its barriers or read its shared memory.
   tc_fence_before_sync();
   __syncthreads();
-  cluster_sync_all();
+  if (PAIR) cluster_sync_all();
   tc_fence_after_sync();
-  if (warp == 1) tmem_dealloc_pair(tmem_base, kTcTmemCols);
+  if (warp == 1) {
+    if (PAIR) tmem_dealloc_pair(tmem_base, kTcTmemCols);
+    else tmem_dealloc(tmem_base, kTcTmemCols);
+  }
 }
 
 }  // namespace nb

@@ -32,19 +32,52 @@ import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "libncnn_oracle.so")
+_FAST_LIB_PATH = os.path.join(_HERE, "libncnn_oracle_fast.so")
 _lib = None
 
 F32 = np.float32
 
 
-def build(force: bool = False) -> str:
-    """Compiles ncnn_ops.c into libncnn_oracle.so (gcc, no fast-math, OpenMP)."""
+def build(force: bool = False, fast: bool = False) -> str:
+    """Compiles ncnn_ops.c (gcc, no fast-math, no contraction, OpenMP).  The checker is the -O2 build
+    libncnn_oracle.so; `fast` builds libncnn_oracle_fast.so with -O3 -march=native for the timed CPU arm of
+    the benchmark (same source, same fp32 semantics: contraction and fast-math stay off)."""
     src = os.path.join(_HERE, "ncnn_ops.c")
-    if force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src):
+    out = _FAST_LIB_PATH if fast else _LIB_PATH
+    if force or not os.path.exists(out) or os.path.getmtime(out) < os.path.getmtime(src):
+        opt = ["-O3", "-march=native"] if fast else ["-O2"]
         subprocess.check_call(
-            ["gcc", "-O2", "-fopenmp", "-ffp-contract=off", "-fno-fast-math", "-shared", "-fPIC",
-             "-o", _LIB_PATH, src, "-lm"])
-    return _LIB_PATH
+            ["gcc", *opt, "-fopenmp", "-ffp-contract=off", "-fno-fast-math", "-shared", "-fPIC",
+             "-o", out, src, "-lm"])
+    return out
+
+
+def use_fast_library() -> str:
+    """Switches this process to the -O3 -march=native build (benchmark arm only; tests keep the checker).
+    The library is compiled on the machine that runs it, since -march=native binds it to that CPU."""
+    global _lib
+    path = build(fast=True, force=not _built_here(_FAST_LIB_PATH))
+    _lib = ctypes.CDLL(path)
+    return path
+
+
+def _built_here(path: str) -> bool:
+    """True when `path` was compiled by this host (a marker file holds the host's CPU model)."""
+    marker = path + ".host"
+    try:
+        with open("/proc/cpuinfo") as f:
+            model = next((l.split(":", 1)[1].strip() for l in f if l.startswith("model name")), "unknown")
+    except OSError:
+        model = "unknown"
+    try:
+        with open(marker) as f:
+            same = f.read() == model
+    except OSError:
+        same = False
+    if not same:
+        with open(marker, "w") as f:
+            f.write(model)
+    return same and os.path.exists(path)
 
 
 def _ops():

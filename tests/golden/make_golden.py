@@ -18,7 +18,8 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else (os.environ.get("NCNN_COMPILER_REFERENCE") or
+                                             os.path.join(os.path.dirname(ROOT), "reference"))
 FIX = os.path.join(REF, "test", "Numerical", "fixtures")
 
 F32_CASES = ["convolution", "convolution_no_bias", "convolution_dilated", "convolution_asymmetric",

@@ -26,6 +26,15 @@ def _run(pkg, param, bin_, x, **kw):
 
 
 # ------------------------------------------------------------------ CTA pairs against the one-CTA kernel
+def _force(monkeypatch, pairs, split):
+    """pairs: every deep contraction goes to CTA pairs, whatever its width and tile count (by default only wide
+    tiles that fill a wave do); split: tiles are split between workers wherever the workspace allows."""
+    monkeypatch.setenv("NCNN_B200_CTA2", "1")
+    monkeypatch.setenv("NCNN_B200_CTA2_ALWAYS", "1" if pairs else "0")
+    monkeypatch.setenv("NCNN_B200_CTA2_MIN_BN", "32" if pairs else "192")
+    monkeypatch.setenv("NCNN_B200_STREAMK", "1" if split else "0")
+
+
 @pytest.mark.parametrize("h,c,cout,n", [(56, 64, 96, 8), (28, 128, 128, 8), (14, 256, 256, 16), (7, 512, 512, 24),
                                          (9, 192, 320, 5)])
 def test_pair_kernel_equals_one_cta_kernel(pkg, oracle, tmp_path, monkeypatch, h, c, cout, n):
@@ -33,10 +42,9 @@ def test_pair_kernel_equals_one_cta_kernel(pkg, oracle, tmp_path, monkeypatch, h
     same order as on one CTA, so the results are the same bits (whole tiles, nothing split)."""
     param, bin_ = pkg.zoo.residual_block(str(tmp_path / "rb"), h=h, w=h, c=c, cout=cout)
     x = np.random.default_rng(h + c).uniform(-1, 1, (n, c, h, h)).astype(np.float32)
-    monkeypatch.setenv("NCNN_B200_STREAMK", "0")
-    monkeypatch.setenv("NCNN_B200_CTA2", "1")
+    _force(monkeypatch, pairs=True, split=False)
     got, kernels = _run(pkg, param, bin_, x)
-    assert any(k.startswith("tc_gemm2_kernel<") for k in kernels), kernels
+    assert any(k.startswith("tc_gemm2_kernel:pairs<") for k in kernels), kernels
     monkeypatch.setenv("NCNN_B200_CTA2", "0")
     base, kernels = _run(pkg, param, bin_, x)
     assert not any(k.startswith("tc_gemm2_kernel") for k in kernels), kernels
@@ -45,50 +53,56 @@ def test_pair_kernel_equals_one_cta_kernel(pkg, oracle, tmp_path, monkeypatch, h
     assert rel_l2(got[:2], want) <= 1e-4
 
 
-@pytest.mark.parametrize("h,c,cout,n", [(14, 256, 256, 16), (7, 512, 512, 24), (28, 128, 128, 8), (9, 192, 320, 5)])
-def test_split_tiles_fp32(pkg, oracle, tmp_path, monkeypatch, h, c, cout, n):
-    """Tiles split between pairs: partial sums are added in a fixed order, so the result is reproducible and
-    differs from the unsplit sum only by fp32 rounding."""
+@pytest.mark.parametrize("pairs", [True, False])
+@pytest.mark.parametrize("h,c,cout,n", [(14, 256, 256, 16), (7, 512, 512, 24), (28, 128, 128, 8), (9, 192, 320, 24)])
+def test_split_tiles_fp32(pkg, oracle, tmp_path, monkeypatch, pairs, h, c, cout, n):
+    """Tiles split between workers (CTA pairs, or single CTAs): partial sums are added in a fixed order, so the
+    result is reproducible; it differs from the unsplit sum by the rounding of the accumulator (tensor memory
+    accumulates in fp32 with truncation, ~1e-5 relative L2 either way)."""
     param, bin_ = pkg.zoo.residual_block(str(tmp_path / "rb"), h=h, w=h, c=c, cout=cout)
     x = np.random.default_rng(h * c).uniform(-1, 1, (n, c, h, h)).astype(np.float32)
-    monkeypatch.setenv("NCNN_B200_STREAMK", "1")
+    _force(monkeypatch, pairs=pairs, split=True)
     got, kernels = _run(pkg, param, bin_, x)
-    assert any(k.startswith("tc_gemm2_kernel:split<") for k in kernels), kernels
+    name = "tc_gemm2_kernel:pairs+split<" if pairs else "tc_gemm2_kernel:split<"
+    assert any(k.startswith(name) for k in kernels), kernels
     again, _ = _run(pkg, param, bin_, x)
     assert np.array_equal(got, again)
     monkeypatch.setenv("NCNN_B200_CTA2", "0")
     base, _ = _run(pkg, param, bin_, x)
-    assert rel_l2(got, base) <= 2e-6
+    assert rel_l2(got, base) <= 3e-5
     want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x[:2]])
     assert rel_l2(got[:2], want) <= 1e-4
 
 
-@pytest.mark.parametrize("split", ["0", "1"])
-def test_pairs_int8_resnet18_bit_exact(pkg, oracle, tmp_path, monkeypatch, split):
-    """Integer sums do not depend on their order: the int8 network on CTA pairs, split or not, is bit exact."""
+@pytest.mark.parametrize("pairs,split", [(True, False), (True, True), (False, True)])
+def test_workers_int8_resnet18_bit_exact(pkg, oracle, tmp_path, monkeypatch, pairs, split):
+    """Integer sums do not depend on their order: the int8 network on CTA pairs or on single CTAs, tiles split
+    or not, is bit exact."""
     param, bin_ = pkg.zoo.resnet18(str(tmp_path / "r18q"), int8=True)
     x = np.random.default_rng(401).uniform(-1, 1, (3, 3, 224, 224)).astype(np.float32)
-    monkeypatch.setenv("NCNN_B200_STREAMK", split)
+    _force(monkeypatch, pairs=pairs, split=split)
     got, kernels = _run(pkg, param, bin_, x)
     assert any(k.startswith("tc_gemm2_kernel") for k in kernels), kernels
     want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x])
     assert np.array_equal(got, want)
 
 
-def test_split_tiles_repeat_and_recover_flags(pkg, tmp_path, monkeypatch):
+@pytest.mark.parametrize("pairs", [True, False])
+def test_split_tiles_repeat_and_recover_flags(pkg, tmp_path, monkeypatch, pairs):
     """The flag words of the split workspace are back at zero after every launch: many runs in a row, with another
     batch size in between, give the same bits."""
-    monkeypatch.setenv("NCNN_B200_STREAMK", "1")
+    _force(monkeypatch, pairs=pairs, split=True)
     param, bin_ = pkg.zoo.resnet18(str(tmp_path / "r18"), size=64, classes=100)
     rng = np.random.default_rng(9)
-    x = rng.uniform(-1, 1, (16, 3, 64, 64)).astype(np.float32)
+    x = rng.uniform(-1, 1, (64, 3, 64, 64)).astype(np.float32)
     m = pkg.Model(param, bin_)
+    assert any("split<" in k for k in _kernels(m, 64))
     first = m.run(x)[0].copy()
     for _ in range(5):
         assert np.array_equal(m.run(x)[0], first)
     m.run(x[:5])
     assert np.array_equal(m.run(x)[0], first)
-    assert m.check_status() == 0
+    m.check_status()  # raises when the device status word is set
     m.close()
 
 
@@ -113,8 +127,9 @@ def test_inner_product_grid(pkg, oracle, tmp_path, m, k, n):
         model = pkg.Model(param, bin_)
         got = model.run(x)[0].copy()
         if m > 256:
+            # (a smaller batch may be planned with other tiles; fp32 sums then round differently)
             sub = model.run(x[rows])[0]
-            assert np.array_equal(sub, got[rows])
+            assert np.array_equal(sub, got[rows]) if int8 else rel_l2(sub, got[rows]) <= 3e-5
         model.close()
         want = _oracle_rows(oracle, param, bin_, x, rows)
         if int8:
