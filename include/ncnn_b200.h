@@ -96,7 +96,14 @@ int ncnn_b200_run_batch(ncnn_b200_model *model, int64_t n, const float *const *i
 
 /* Same with device pointers on the caller's CUDA stream (a cudaStream_t passed as
  * void*); asynchronous.  ncnn_b200_check_status reports a device-side time-out after
- * the caller synchronised. */
+ * the caller synchronised.
+ * One call in flight per handle: a model owns one activation arena, so the next call on the
+ * same handle (on any stream, including ncnn_b200_launch_count and a run with a batch size
+ * not seen before, which lay the arena out anew) belongs after the previous one has finished.
+ * The first use of a new batch size synchronises the device for that reason.  Plans (CUDA
+ * graphs, staging buffers) are cached for the eight most recently used batch sizes.
+ * Every entry point makes the model's device (options.device) current for the call and puts
+ * the caller's device back before it returns. */
 int ncnn_b200_run_batch_device(ncnn_b200_model *model, int64_t n, const float *const *inputs,
                                float *const *outputs, void *stream);
 int ncnn_b200_check_status(ncnn_b200_model *model);
@@ -187,6 +194,26 @@ int ncnn_b200_op_requantize(const int32_t *x, int8_t *y, int64_t count, int64_t 
                             const float *scale_out, int32_t scale_out_count, const float *bias,
                             int32_t bias_count, int32_t relu, void *stream);
 
+/* ---- One model on several GPUs of one box (batch sharding).
+ * The reference has no counterpart: its entry point takes one image per call and keeps no state between
+ * calls (lib/Conversion/NCNNToTosa/NCNNToTosa.cpp:48-52), which is what makes the images of a batch
+ * independent.  A multi-device handle keeps one replica of the model per listed device (weights copied to
+ * each, one stream, one captured graph and one host thread per device).  ncnn_b200_multi_run_batch cuts the
+ * n images into contiguous shards of ceil(n / devices) images (ncnn_b200_multi_partition gives the cut),
+ * every device runs its shard, and each copies its results straight into the caller's host arrays: no
+ * collective and no peer traffic.  A device ordinal may be listed more than once (two replicas on one GPU).
+ * Arguments and status codes are those of ncnn_b200_run_batch; one call in flight per handle. */
+typedef struct ncnn_b200_multi ncnn_b200_multi;
+int ncnn_b200_multi_load(const char *param_path, const char *bin_path, const ncnn_b200_options *options,
+                         const int32_t *devices, int32_t device_count, ncnn_b200_multi **out);
+void ncnn_b200_multi_free(ncnn_b200_multi *model);
+const char *ncnn_b200_multi_last_error(const ncnn_b200_multi *model);
+int32_t ncnn_b200_multi_device_count(const ncnn_b200_multi *model);
+int ncnn_b200_multi_run_batch(ncnn_b200_multi *model, int64_t n, const float *const *inputs,
+                              float *const *outputs);
+/* first[g], count[g] for g < parts: the images of shard g of a batch of n (pure arithmetic, no GPU). */
+int ncnn_b200_multi_partition(int64_t n, int32_t parts, int64_t *first, int64_t *count);
+
 /* No counterpart in the reference.  For hosts that are not allowed to allocate on the
  * GPU (a real-time loop after start-up, a sandbox that forbids cudaMalloc, a process whose
  * own pool already owns the whole device): the int8 InnerProduct
@@ -194,11 +221,14 @@ int ncnn_b200_op_requantize(const int32_t *x, int8_t *y, int64_t count, int64_t 
  * on device arrays, with its only scratch (the int8 copy of x) taken from an 8 MiB array
  * built into the library.  It calls no allocation routine.  Limits and rules:
  * m*k <= 8 388 608, otherwise status 5 and a message in ncnn_b200_last_error(NULL); every
- * GPU that loads the library holds those 8 MiB until exit; calls on one device share the
+ * GPU on which the library's code is loaded (lazily, at the first call on that device: make
+ * it at start-up) holds those 8 MiB until exit; calls on one device share the
  * array, so calls that may overlap on the GPU race and must be serialised; the first call
- * on a device resolves the array's address and should happen before any stream capture.
- * x is fp32 [m][k], weight int8 [n][k], bias fp32 [n] or NULL, y fp32 [m][n]; the
- * arithmetic equals the InnerProduct layer of a loaded int8 model bit for bit. */
+ * on a device resolves the array's address and should happen before any stream capture;
+ * the address is cached, so do not call this after cudaDeviceReset() on that device.
+ * x is fp32 [m][k], weight int8 [n][k] at any byte alignment, bias fp32 [n] or NULL,
+ * y fp32 [m][n]; the arithmetic equals the InnerProduct layer of a loaded int8 model bit
+ * for bit. */
 int ncnn_b200_inner_product_int8_noalloc(const float *x, const int8_t *weight,
                                          const float *weight_scales, float input_scale,
                                          const float *bias, float *y, int64_t m, int32_t k, int32_t n,

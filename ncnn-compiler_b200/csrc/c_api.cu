@@ -53,12 +53,27 @@ int grid_for(long long work) {
 namespace nb {
 // lets other translation units of the library report through ncnn_b200_last_error(NULL)
 void set_global_error(const std::string& message) { g_load_error = message; }
+
+// a path as the inside of a C string literal
+std::string c_string_escape(const char* text) {
+  std::string out;
+  for (const char* c = text; *c != 0; ++c) {
+    if (*c == '\\' || *c == '"') out.push_back('\\');
+    if (*c == '\n') {
+      out += "\\n";
+      continue;
+    }
+    out.push_back(*c);
+  }
+  return out;
+}
+
 }  // namespace nb
 
 extern "C" {
 
 int ncnn_b200_load(const char* param_path, const char* bin_path, const ncnn_b200_options* options,
-                   ncnn_b200_model** out) {
+                   ncnn_b200_model** out) try {
   if (out == nullptr) return NCNN_B200_STATUS_NULL_POINTER;
   *out = nullptr;
   if (param_path == nullptr) {
@@ -100,6 +115,12 @@ int ncnn_b200_load(const char* param_path, const char* bin_path, const ncnn_b200
   m->engine = std::move(engine);
   *out = m;
   return NCNN_B200_STATUS_SUCCESS;
+} catch (const std::exception& e) {
+  nb::set_global_error(std::string("internal error: ") + e.what());
+  return NCNN_B200_STATUS_LOAD;
+} catch (...) {
+  nb::set_global_error("internal error");
+  return NCNN_B200_STATUS_LOAD;
 }
 
 void ncnn_b200_free(ncnn_b200_model* model) { delete model; }
@@ -142,7 +163,7 @@ static int check_pointers(ncnn_b200_model* m, const float* const* inputs, float*
 }
 
 int ncnn_b200_run_batch(ncnn_b200_model* m, int64_t n, const float* const* inputs,
-                        float* const* outputs) {
+                        float* const* outputs) try {
   const int st = check_pointers(m, inputs, outputs);
   if (st != 0) return st;
   if (n <= 0) {
@@ -152,6 +173,12 @@ int ncnn_b200_run_batch(ncnn_b200_model* m, int64_t n, const float* const* input
   const int r = m->engine->run_host(n, inputs, outputs);
   if (r != 0) m->error = m->engine->last_error();
   return r;
+} catch (const std::exception& e) {
+  nb::set_global_error(std::string("internal error: ") + e.what());
+  return NCNN_B200_STATUS_RUNTIME;
+} catch (...) {
+  nb::set_global_error("internal error");
+  return NCNN_B200_STATUS_RUNTIME;
 }
 
 int ncnn_b200_run(ncnn_b200_model* m, const float* const* inputs, float* const* outputs) {
@@ -159,7 +186,7 @@ int ncnn_b200_run(ncnn_b200_model* m, const float* const* inputs, float* const* 
 }
 
 int ncnn_b200_run_batch_device(ncnn_b200_model* m, int64_t n, const float* const* inputs,
-                               float* const* outputs, void* stream) {
+                               float* const* outputs, void* stream) try {
   const int st = check_pointers(m, inputs, outputs);
   if (st != 0) return st;
   if (n <= 0) {
@@ -169,21 +196,39 @@ int ncnn_b200_run_batch_device(ncnn_b200_model* m, int64_t n, const float* const
   const int r = m->engine->run_device(n, inputs, outputs, static_cast<cudaStream_t>(stream));
   if (r != 0) m->error = m->engine->last_error();
   return r;
+} catch (const std::exception& e) {
+  nb::set_global_error(std::string("internal error: ") + e.what());
+  return NCNN_B200_STATUS_RUNTIME;
+} catch (...) {
+  nb::set_global_error("internal error");
+  return NCNN_B200_STATUS_RUNTIME;
 }
 
-int ncnn_b200_check_status(ncnn_b200_model* m) {
+int ncnn_b200_check_status(ncnn_b200_model* m) try {
   if (m == nullptr) return NCNN_B200_STATUS_NULL_POINTER;
   const int r = m->engine->check_status();
   if (r != 0) m->error = m->engine->last_error();
   return r;
+} catch (const std::exception& e) {
+  nb::set_global_error(std::string("internal error: ") + e.what());
+  return NCNN_B200_STATUS_RUNTIME;
+} catch (...) {
+  nb::set_global_error("internal error");
+  return NCNN_B200_STATUS_RUNTIME;
 }
 
-int ncnn_b200_launch_count(ncnn_b200_model* m, int64_t n) {
+int ncnn_b200_launch_count(ncnn_b200_model* m, int64_t n) try {
   if (m == nullptr) return -1;
   return m->engine->launches_per_run(n);
+} catch (const std::exception& e) {
+  nb::set_global_error(std::string("internal error: ") + e.what());
+  return -1;
+} catch (...) {
+  nb::set_global_error("internal error");
+  return -1;
 }
 
-int64_t ncnn_b200_profile(ncnn_b200_model* m, int64_t n, int repeat, char* buffer, size_t capacity) {
+int64_t ncnn_b200_profile(ncnn_b200_model* m, int64_t n, int repeat, char* buffer, size_t capacity) try {
   if (m == nullptr) return -NCNN_B200_STATUS_NULL_POINTER;
   std::vector<nb::LayerTiming> t;
   const int r = m->engine->profile(n, repeat, &t);
@@ -195,10 +240,16 @@ int64_t ncnn_b200_profile(ncnn_b200_model* m, int64_t n, int repeat, char* buffe
   for (const auto& x : t)
     o << x.kernel << "\t" << x.name << "\t" << x.ms << "\t" << x.flops << "\t" << x.bytes << "\n";
   return copy_out(o.str(), buffer, capacity);
+} catch (const std::exception& e) {
+  nb::set_global_error(std::string("internal error: ") + e.what());
+  return -1;
+} catch (...) {
+  nb::set_global_error("internal error");
+  return -1;
 }
 
 int64_t ncnn_b200_describe(const char* param_path, const char* bin_path, char* buffer,
-                           size_t capacity) {
+                           size_t capacity) try {
   if (param_path == nullptr) return -NCNN_B200_STATUS_NULL_POINTER;
   nb::ModelDef model;
   std::string err;
@@ -209,10 +260,16 @@ int64_t ncnn_b200_describe(const char* param_path, const char* bin_path, char* b
     text = nb::describe_model(model);
   }
   return copy_out(text, buffer, capacity);
+} catch (const std::exception& e) {
+  nb::set_global_error(std::string("internal error: ") + e.what());
+  return -1;
+} catch (...) {
+  nb::set_global_error("internal error");
+  return -1;
 }
 
 int ncnn_b200_emit_stub(const ncnn_b200_model* m, const char* name, const char* param_path,
-                        const char* bin_path, const char* directory) {
+                        const char* bin_path, const char* directory) try {
   if (m == nullptr || name == nullptr || param_path == nullptr || bin_path == nullptr ||
       directory == nullptr)
     return NCNN_B200_STATUS_NULL_POINTER;
@@ -281,7 +338,7 @@ int ncnn_b200_emit_stub(const ncnn_b200_model* m, const char* name, const char* 
     << "    if (outputs[i] == NULL) return NCNN_STATUS_NULL_POINTER;\n"
     << "  while (__atomic_exchange_n(&g_lock, 1, __ATOMIC_ACQUIRE)) {\n  }\n"
     << "  int status = 0;\n"
-    << "  if (g_model == NULL) status = ncnn_b200_load(\"" << param_path << "\", \"" << bin_path
+    << "  if (g_model == NULL) status = ncnn_b200_load(\"" << nb::c_string_escape(param_path) << "\", \"" << nb::c_string_escape(bin_path)
     << "\", NULL, &g_model);\n"
     << "  if (status == 0) status = ncnn_b200_run(g_model, inputs, outputs);\n"
     << "  __atomic_store_n(&g_lock, 0, __ATOMIC_RELEASE);\n"
@@ -302,6 +359,12 @@ int ncnn_b200_emit_stub(const ncnn_b200_model* m, const char* name, const char* 
     out << f.second;
   }
   return NCNN_B200_STATUS_SUCCESS;
+} catch (const std::exception& e) {
+  nb::set_global_error(std::string("internal error: ") + e.what());
+  return NCNN_B200_STATUS_RUNTIME;
+} catch (...) {
+  nb::set_global_error("internal error");
+  return NCNN_B200_STATUS_RUNTIME;
 }
 
 int ncnn_b200_op_quantize(const float* x, int8_t* y, int64_t count, int64_t inner, int32_t channels,

@@ -29,6 +29,7 @@
 
 namespace nb {
 void set_global_error(const std::string& message);
+std::string c_string_escape(const char* text);  // c_api.cu
 }
 
 namespace {
@@ -176,7 +177,7 @@ extern "C" {
 
 int ncnn_b200_dynamic_load(const char* param_path, const char* bin_path, const ncnn_b200_options* options,
                            const ncnn_b200_dim_constraint* constraints, int32_t constraint_count,
-                           ncnn_b200_dynamic_model** out) {
+                           ncnn_b200_dynamic_model** out) try {
   if (out == nullptr) return NCNN_B200_STATUS_NULL_POINTER;
   *out = nullptr;
   if (param_path == nullptr || options == nullptr || (constraint_count > 0 && constraints == nullptr))
@@ -283,6 +284,12 @@ int ncnn_b200_dynamic_load(const char* param_path, const char* bin_path, const n
       if (o.mask & (1u << k)) o.dims[k] = -1;
   *out = model.release();
   return NCNN_B200_STATUS_SUCCESS;
+} catch (const std::exception& e) {
+  nb::set_global_error(std::string("internal error: ") + e.what());
+  return NCNN_B200_STATUS_LOAD;
+} catch (...) {
+  nb::set_global_error("internal error");
+  return NCNN_B200_STATUS_LOAD;
 }
 
 void ncnn_b200_dynamic_free(ncnn_b200_dynamic_model* model) { delete model; }
@@ -308,7 +315,7 @@ int ncnn_b200_dynamic_output_shape(const ncnn_b200_dynamic_model* m, int i, int6
 }
 
 int ncnn_b200_dynamic_infer_output_shapes(ncnn_b200_dynamic_model* m, const int64_t* const* input_shapes,
-                                          int64_t* const* output_shapes) {
+                                          int64_t* const* output_shapes) try {
   if (m == nullptr || output_shapes == nullptr) return NCNN_B200_STATUS_NULL_POINTER;
   std::lock_guard<std::mutex> guard(m->lock);
   std::vector<int64_t> key;
@@ -323,10 +330,16 @@ int ncnn_b200_dynamic_infer_output_shapes(ncnn_b200_dynamic_model* m, const int6
     for (int k = 0; k < rank; ++k) output_shapes[o][k] = dims[k];
   }
   return NCNN_B200_STATUS_SUCCESS;
+} catch (const std::exception& e) {
+  nb::set_global_error(std::string("internal error: ") + e.what());
+  return NCNN_B200_STATUS_RUNTIME;
+} catch (...) {
+  nb::set_global_error("internal error");
+  return NCNN_B200_STATUS_RUNTIME;
 }
 
 int ncnn_b200_dynamic_run(ncnn_b200_dynamic_model* m, const float* const* inputs, const int64_t* const* input_shapes,
-                          float* const* outputs, const uint64_t* output_capacities) {
+                          float* const* outputs, const uint64_t* output_capacities) try {
   if (m == nullptr || inputs == nullptr || outputs == nullptr) return NCNN_B200_STATUS_NULL_POINTER;
   for (size_t i = 0; i < m->inputs.size(); ++i)
     if (inputs[i] == nullptr) return NCNN_B200_STATUS_NULL_POINTER;
@@ -356,10 +369,16 @@ int ncnn_b200_dynamic_run(ncnn_b200_dynamic_model* m, const float* const* inputs
   status = ncnn_b200_run(engine, inputs, outputs);
   if (status != NCNN_B200_STATUS_SUCCESS) m->error = ncnn_b200_last_error(engine);
   return status;
+} catch (const std::exception& e) {
+  nb::set_global_error(std::string("internal error: ") + e.what());
+  return NCNN_B200_STATUS_RUNTIME;
+} catch (...) {
+  nb::set_global_error("internal error");
+  return NCNN_B200_STATUS_RUNTIME;
 }
 
 int ncnn_b200_dynamic_emit_stub(const ncnn_b200_dynamic_model* m, const char* name, const char* param_path,
-                                const char* bin_path, const char* directory) {
+                                const char* bin_path, const char* directory) try {
   if (m == nullptr || name == nullptr || param_path == nullptr || bin_path == nullptr || directory == nullptr)
     return NCNN_B200_STATUS_NULL_POINTER;
   const std::string fn = name, macro = upper(fn), guard = "NCNN_" + macro + "_H";
@@ -466,7 +485,7 @@ int ncnn_b200_dynamic_emit_stub(const ncnn_b200_dynamic_model* m, const char* na
     << "  options.struct_size = sizeof(options);\n  options.device = -1;\n  options.use_cuda_graph = 1;\n"
     << "  options.accuracy_mode = " << m->options.accuracy_mode << ";\n"
     << "  options.input_shape_count = " << templated << ";\n  options.input_shapes = shapes;\n"
-    << "  return ncnn_b200_dynamic_load(\"" << param_path << "\", \"" << bin_path << "\", &options, limits, "
+    << "  return ncnn_b200_dynamic_load(\"" << nb::c_string_escape(param_path) << "\", \"" << nb::c_string_escape(bin_path) << "\", &options, limits, "
     << n_limits << ", &g_model);\n}\n\n";
   auto shape_table = [&]() {
     c << "  const int64_t *shapes[" << n_in << "] = {";
@@ -532,6 +551,12 @@ int ncnn_b200_dynamic_emit_stub(const ncnn_b200_dynamic_model* m, const char* na
     out << f.second;
   }
   return NCNN_B200_STATUS_SUCCESS;
+} catch (const std::exception& e) {
+  nb::set_global_error(std::string("internal error: ") + e.what());
+  return NCNN_B200_STATUS_RUNTIME;
+} catch (...) {
+  nb::set_global_error("internal error");
+  return NCNN_B200_STATUS_RUNTIME;
 }
 
 }  // extern "C"

@@ -100,6 +100,7 @@ constexpr int kMaxChunks = 4;
 
 struct Plan {
   int64_t n = 0;
+  uint64_t last_used = 0;  // for the bounded plan cache
   std::vector<Step> steps;
   std::vector<float*> d_in, d_out;  // staging used by host-pointer runs
   cudaGraphExec_t graph = nullptr;
@@ -127,6 +128,8 @@ struct Plan {
     d_out.clear();
   }
 };
+
+constexpr size_t kMaxCachedPlans = 8;  // batch sizes whose plans (graphs, staging buffers) stay alive
 
 // Host-pointer runs that upload at least this much are pipelined.
 constexpr size_t kPipelineUploadBytes = 4u << 20;
@@ -167,9 +170,30 @@ int host_quantize(float x, float s) {
 
 }  // namespace
 
+// Makes the model's device current for the duration of a call and puts the caller's device back:
+// a process may hold one handle per GPU and call them in any order from one thread.
+struct DeviceGuard {
+  int previous = -1;
+  bool switched = false;
+  explicit DeviceGuard(int device) {
+    if (device < 0) return;
+    if (cudaGetDevice(&previous) != cudaSuccess) {
+      previous = -1;
+      cudaGetLastError();
+    }
+    if (previous != device) switched = cudaSetDevice(device) == cudaSuccess && previous >= 0;
+  }
+  ~DeviceGuard() {
+    if (switched) cudaSetDevice(previous);
+  }
+  DeviceGuard(const DeviceGuard&) = delete;
+  DeviceGuard& operator=(const DeviceGuard&) = delete;
+};
+
 class EngineImpl {
  public:
   ~EngineImpl() {
+    DeviceGuard guard(device_);
     for (auto& kv : plans_) kv.second.release();
     for (void* p : device_allocs_) cudaFree(p);
     if (arena_ != nullptr) cudaFree(arena_);
@@ -206,6 +230,9 @@ class EngineImpl {
   uint8_t* arena_ = nullptr;
   size_t arena_bytes_ = 0;
   size_t arena_per_image_ = 0;
+  bool stall_injected_ = false;
+  int device_ = -1;  // the CUDA device that owns every allocation, stream and graph of this model
+  uint64_t use_counter_ = 0;
   int* d_status_ = nullptr;
   uint32_t* d_split_ws_ = nullptr;
   int* d_split_flags_ = nullptr;
@@ -616,6 +643,9 @@ bool EngineImpl::import_layers(std::string* err) {
     for (const auto& b : l.bottoms)
       if (by_name_.find(b) == by_name_.end()) return fail(err, where + "unknown bottom blob " + b);
     const std::string& t = l.type;
+    // every importer below reads bottoms[0] and tops[0]: a line without them is malformed, not a crash
+    if (t != "Input" && (l.bottoms.empty() || l.tops.empty()))
+      return fail(err, where + "layer needs at least one bottom and one top blob");
     if (t == "Input") {
       // ImportInput.cpp:22-80: w/h/c all given (rank 3) or all omitted plus an override
       const int64_t w = l.params.get_int(0, 0), h = l.params.get_int(1, 0), c = l.params.get_int(2, 0);
@@ -1997,14 +2027,23 @@ ActRef EngineImpl::ref(int tensor, int64_t n) const {
 bool EngineImpl::build(const std::string& param, const std::string& bin, const EngineOptions& opt,
                        std::string* err) {
   opt_ = opt;
+  // the requested device is current only inside this call; the caller's choice is put back on return
+  DeviceGuard guard(opt.plan_only ? -1 : opt.device);
   if (opt.accuracy_mode < 0 || opt.accuracy_mode > 2) return fail(err, "unknown accuracy mode");
   if (!opt.plan_only) {
     int count = 0;
     if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0)
       return fail(err, "no CUDA device is available: this runtime has no CPU path");
-    if (opt.device >= 0 && cudaSetDevice(opt.device) != cudaSuccess) return fail(err, "cannot select the requested CUDA device");
     int dev = 0;
-    cudaGetDevice(&dev);
+    if (opt.device >= 0) {
+      int available = 0;
+      if (cudaGetDeviceCount(&available) != cudaSuccess || opt.device >= available)
+        return fail(err, "cannot select the requested CUDA device");
+      dev = opt.device;
+    } else {
+      cudaGetDevice(&dev);
+    }
+    device_ = dev;
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return fail(err, "cannot query the CUDA device");
     if (prop.major != 10) return fail(err, std::string("this runtime is built for sm_100a only; device is ") + prop.name);
@@ -2616,7 +2655,21 @@ Plan* EngineImpl::plan_for(int64_t n) {
     return nullptr;
   }
   auto it = plans_.find(n);
-  if (it != plans_.end()) return &it->second;
+  if (it != plans_.end()) {
+    it->second.last_used = ++use_counter_;
+    return &it->second;
+  }
+  // A new batch size lays the shared arena out anew and clears it: nothing of this model may still be
+  // running, on any stream (one call in flight per handle is the rule; this makes a violation harmless).
+  cudaDeviceSynchronize();
+  // bounded cache: a plan owns graphs and staging buffers; the least recently used one goes first
+  while (plans_.size() >= kMaxCachedPlans) {
+    auto oldest = plans_.begin();
+    for (auto p = plans_.begin(); p != plans_.end(); ++p)
+      if (p->second.last_used < oldest->second.last_used) oldest = p;
+    oldest->second.release();
+    plans_.erase(oldest);
+  }
   // the arena is shared by all plans; grow it when a larger batch arrives.  Offsets
   // scale with n, so plans of other batch sizes stay valid only for their own n.
   const size_t need = arena_per_image_ * static_cast<size_t>(n) + 4096;
@@ -2646,6 +2699,7 @@ Plan* EngineImpl::plan_for(int64_t n) {
       return nullptr;
     }
   }
+  plan.last_used = ++use_counter_;
   auto res = plans_.emplace(n, std::move(plan));
   return &res.first->second;
 }
@@ -2892,6 +2946,13 @@ int EngineImpl::run(int64_t n, const float* const* in, float* const* out, bool h
   }
   Plan* plan = plan_for(n);
   if (plan == nullptr) return 6;
+  // Host tests of the time-out path: NCNN_B200_TEST_STALL makes the one-CTA contraction kernel leave one stage
+  // unfilled, so its bounded waits run out (nothing faults or hangs; the run returns status 7).
+  const bool stall = std::getenv("NCNN_B200_TEST_STALL") != nullptr;
+  if (stall != stall_injected_) {
+    cudaMemsetAsync(d_status_ + 1, stall ? 1 : 0, sizeof(int), host ? stream_ : user_stream);
+    stall_injected_ = stall;
+  }
   const char* pipe_env = std::getenv("NCNN_B200_PIPELINE");
   if (host && n % 2 == 0 && !(pipe_env != nullptr && pipe_env[0] == '0')) {
     // worth it when the upload is a visible part of the call: a few MB or more
@@ -2940,8 +3001,17 @@ int EngineImpl::profile(int64_t n, int repeat, std::vector<LayerTiming>* out) {
   } else {
     all = plan->steps;
   }
-  std::vector<cudaEvent_t> ev(all.size() + 1);
-  for (auto& e : ev) cudaEventCreate(&e);
+  struct Events {
+    std::vector<cudaEvent_t> ev;
+    explicit Events(size_t n) : ev(n, nullptr) {
+      for (auto& e : ev) cudaEventCreate(&e);
+    }
+    ~Events() {
+      for (auto& e : ev)
+        if (e != nullptr) cudaEventDestroy(e);
+    }
+    cudaEvent_t operator[](size_t i) const { return ev[i]; }
+  } ev(all.size() + 1);
   std::vector<double> total(all.size(), 0.0);
   for (int r = 0; r < repeat + 1; ++r) {
     cudaEventRecord(ev[0], stream_);
@@ -2973,13 +3043,12 @@ int EngineImpl::profile(int64_t n, int repeat, std::vector<LayerTiming>* out) {
     t.bytes = all[i].bytes;
     out->push_back(t);
   }
-  for (auto& e : ev) cudaEventDestroy(e);
   return 0;
 }
 
 // ---------------------------------------------------------------------- Engine
 Engine::Engine() : impl_(new EngineImpl) {}
-Engine::~Engine() = default;
+Engine::~Engine() = default;  // (~EngineImpl selects the model's device while it frees)
 
 std::unique_ptr<Engine> Engine::create(const std::string& param_path, const std::string& bin_path,
                                        const EngineOptions& options, std::string* error) {
@@ -3017,16 +3086,22 @@ const std::string& Engine::input_name(int i) const { return impl_->tensors_[impl
 const std::string& Engine::output_name(int i) const { return impl_->tensors_[impl_->outputs_[i]].name; }
 
 int Engine::run_host(int64_t n, const float* const* inputs, float* const* outputs) {
+  DeviceGuard guard(impl_->device_);
   impl_->error_.clear();
   return impl_->run(n, inputs, outputs, true, nullptr);
 }
 int Engine::run_device(int64_t n, const float* const* inputs, float* const* outputs, cudaStream_t stream) {
+  DeviceGuard guard(impl_->device_);
   impl_->error_.clear();
   return impl_->run(n, inputs, outputs, false, stream);
 }
-int Engine::profile(int64_t n, int repeat, std::vector<LayerTiming>* out) { return impl_->profile(n, repeat, out); }
+int Engine::profile(int64_t n, int repeat, std::vector<LayerTiming>* out) {
+  DeviceGuard guard(impl_->device_);
+  return impl_->profile(n, repeat, out);
+}
 int Engine::check_status() {
   if (impl_->opt_.plan_only) return 0;
+  DeviceGuard guard(impl_->device_);
   int status = 0;
   if (cudaDeviceSynchronize() != cudaSuccess ||
       cudaMemcpy(&status, impl_->d_status_, 4, cudaMemcpyDeviceToHost) != cudaSuccess) {
@@ -3042,6 +3117,7 @@ int Engine::check_status() {
   return 0;
 }
 int Engine::launches_per_run(int64_t n) {
+  DeviceGuard guard(impl_->device_);
   Plan* p = impl_->plan_for(n);
   if (p == nullptr) return -1;
   return static_cast<int>(p->steps.size() + impl_->inputs_.size() + impl_->outputs_.size());
@@ -3049,6 +3125,7 @@ int Engine::launches_per_run(int64_t n) {
 const std::string& Engine::last_error() const { return impl_->error_; }
 
 std::string Engine::plan_summary(int64_t n) {
+  DeviceGuard guard(impl_->device_);
   Plan* p = impl_->plan_for(n);
   std::ostringstream o;
   if (p == nullptr) return "error: " + impl_->error_;

@@ -11,8 +11,9 @@
 // the library image itself, so no allocation call of any kind is made here.
 //
 // Consequences of the fixed array, all of which the caller must know:
-//  * every GPU that loads the library carries kNoAllocScratchBytes (8 MiB) until the
-//    process exits;
+//  * every GPU on which the library's code gets loaded carries kNoAllocScratchBytes (8 MiB) from
+//    that moment until the process exits (the CUDA runtime loads the module lazily, typically at
+//    the first call into the library on that device; make that call at start-up);
 //  * M*K may not exceed that size; larger requests are refused, never truncated;
 //  * all calls on one device share the array, and it keeps whatever the last call
 //    left there (nothing in it needs clearing: each call overwrites the M*K bytes
@@ -20,7 +21,11 @@
 //    or different host threads -- race and must be serialised by the caller;
 //  * the first call on a device looks up the array's device address
 //    (cudaGetSymbolAddress), so make that first call before starting any stream
-//    capture.
+//    capture;
+//  * the looked-up address is cached per device for the life of the process: a host program that
+//    calls cudaDeviceReset() must not use this entry point on that device afterwards;
+//  * `weight` may sit at any byte address (a sub-allocated blob, say): rows are read four bytes
+//    at a time only when the pointer and K allow it, byte by byte otherwise.
 #include "../../include/ncnn_b200.h"
 
 #include <mutex>
@@ -56,7 +61,7 @@ __global__ void k_na_quantize(const float* __restrict__ x, int8_t* __restrict__ 
 __global__ void k_na_inner_product(const int8_t* __restrict__ xq, const int8_t* __restrict__ w,
                                    const float* __restrict__ weight_scales, float input_scale,
                                    const float* __restrict__ bias, float* __restrict__ y, long long M,
-                                   int K, int N, int relu) {
+                                   int K, int N, int relu, int words) {
   const long long total = M * N;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -66,7 +71,7 @@ __global__ void k_na_inner_product(const int8_t* __restrict__ xq, const int8_t* 
     const int8_t* b = w + static_cast<long long>(n) * K;
     int acc = 0;
     int k = 0;
-    if (K % 4 == 0) {
+    if (words) {  // both operands 4-byte aligned in every row (checked on the host)
       for (; k < K; k += 4)
         acc = __dp4a(*reinterpret_cast<const int*>(a + k), *reinterpret_cast<const int*>(b + k), acc);
     }
@@ -96,9 +101,10 @@ extern "C" int ncnn_b200_inner_product_int8_noalloc(const float* x, const int8_t
   if (m <= 0 || k <= 0 || n <= 0 || !(input_scale > 0.0f))
     return fail(NCNN_B200_STATUS_INVALID_SHAPE,
                 "inner_product_int8_noalloc: m, k, n and input_scale must be positive");
-  if (static_cast<unsigned long long>(m) * static_cast<unsigned long long>(k) > kNoAllocScratchBytes)
+  // (a quotient, not a product: m*k could wrap for absurd m)
+  if (m > static_cast<int64_t>(kNoAllocScratchBytes / static_cast<uint64_t>(k)))
     return fail(NCNN_B200_STATUS_OUTPUT_CAPACITY,
-                "inner_product_int8_noalloc: m*k = " + std::to_string(m * k) +
+                "inner_product_int8_noalloc: m = " + std::to_string(m) + " rows of k = " + std::to_string(k) +
                     " int8 activations exceed the built-in scratch of " +
                     std::to_string(kNoAllocScratchBytes) + " bytes; split the rows into several calls");
   int device = 0;
@@ -126,8 +132,10 @@ extern "C" int ncnn_b200_inner_product_int8_noalloc(const float* x, const int8_t
   k_na_quantize<<<grid_q, 256, 0, st>>>(x, xq, count, input_scale);
   const long long outputs = static_cast<long long>(m) * n;
   const int grid_m = static_cast<int>(std::min<long long>((outputs + 255) / 256, 148 * 16));
+  // the scratch rows start at multiples of k from a 256-byte boundary; the caller's weight may not
+  const int words = (k % 4 == 0 && (reinterpret_cast<uintptr_t>(weight) & 3u) == 0) ? 1 : 0;
   k_na_inner_product<<<grid_m, 256, 0, st>>>(xq, weight, weight_scales, input_scale, bias, y, m, k, n,
-                                             relu ? 1 : 0);
+                                             relu ? 1 : 0, words);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess)
     return fail(NCNN_B200_STATUS_RUNTIME,

@@ -176,6 +176,15 @@ __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }
 
+// ------------------------------------------------- programmatic dependent launch
+// A kernel launched with programmatic stream serialisation may start while the kernel before it in the
+// stream still runs.  grid_dependency_wait() returns once that kernel has completed and its memory
+// operations are visible: nothing it wrote may be read, and nothing it reads may be overwritten, before
+// this call.  grid_dependency_trigger() lets the next kernel in the stream start its own preamble early
+// (it still waits for this whole grid in its own grid_dependency_wait()).
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ----------------------------------------------------------------- tcgen05
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_result_addr, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(

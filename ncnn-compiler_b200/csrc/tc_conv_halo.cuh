@@ -54,6 +54,7 @@ tc_conv_halo_kernel(const __grid_constant__ TcHaloParams p, const __grid_constan
                     const __grid_constant__ CUtensorMap map_r0,
                     const __grid_constant__ CUtensorMap map_r1) {
   using namespace ptx;
+  grid_dependency_trigger();  // the next kernel of the stream may begin its preamble
   constexpr int PLANES = tc_planes(KIND);
 
   extern __shared__ uint8_t halo_smem_raw[];
@@ -109,6 +110,9 @@ tc_conv_halo_kernel(const __grid_constant__ TcHaloParams p, const __grid_constan
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
+  // barriers, tensor memory and descriptors are ready: from here on the kernel touches tensors that the
+  // kernel before it in the stream may still be writing
+  grid_dependency_wait();
 
   // tile -> (image, tile row, tile column, channel block); channel blocks of one pixel tile
   // are neighbours so that CTAs working side by side share the patch in L2

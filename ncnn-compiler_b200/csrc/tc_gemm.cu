@@ -305,6 +305,41 @@ int env_int(const char* name, int fallback) {
 
 int max_pairs_resident(int kind, int smem_bytes, int sm_count);
 
+// NCNN_B200_PDL=0 launches every contraction kernel fully serialised behind its predecessor.
+bool pdl_enabled() {
+  static const bool on = env_int("NCNN_B200_PDL", 1) != 0;
+  return on;
+}
+
+// Launch attributes of the contraction kernels: clusters of two CTAs for the pair form, and programmatic
+// stream serialisation: the kernel's preamble (barriers, tensor memory, descriptor prefetch) may run while
+// the previous kernel of the stream drains; the kernel itself waits (grid_dependency_wait) before it
+// touches any tensor.
+struct KernelLaunchConfig {
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attrs[2];
+  KernelLaunchConfig(int grid, int threads, int smem_bytes, bool pair, cudaStream_t stream) {
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(static_cast<unsigned>(threads));
+    cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
+    cfg.stream = stream;
+    cfg.attrs = attrs;
+    cfg.numAttrs = 0;
+    if (pair) {
+      attrs[cfg.numAttrs].id = cudaLaunchAttributeClusterDimension;
+      attrs[cfg.numAttrs].val.clusterDim.x = 2;
+      attrs[cfg.numAttrs].val.clusterDim.y = 1;
+      attrs[cfg.numAttrs].val.clusterDim.z = 1;
+      ++cfg.numAttrs;
+    }
+    if (pdl_enabled()) {
+      attrs[cfg.numAttrs].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attrs[cfg.numAttrs].val.programmaticStreamSerializationAllowed = 1;
+      ++cfg.numAttrs;
+    }
+  }
+};
+
 // True when tc_gemm2_kernel takes this contraction (on CTA pairs, or on single CTAs with tiles split
 // between them); fills the plan like finish_plan does.
 // `half_blocks_ok`: K blocks of half the size (64-byte rows) address the same packed operands, so
@@ -658,30 +693,9 @@ cudaError_t prepare_worker_kernels() {
   return result;
 }
 
-// launch configuration of tc_gemm2_kernel: clusters of two CTAs for the pair form
-struct WorkerLaunchConfig {
-  cudaLaunchConfig_t cfg{};
-  cudaLaunchAttribute attrs[2];
-  WorkerLaunchConfig(int grid, int threads, int smem_bytes, bool pair, cudaStream_t stream) {
-    cfg.gridDim = dim3(static_cast<unsigned>(grid));
-    cfg.blockDim = dim3(static_cast<unsigned>(threads));
-    cfg.dynamicSmemBytes = static_cast<size_t>(smem_bytes);
-    cfg.stream = stream;
-    cfg.attrs = attrs;
-    cfg.numAttrs = 0;
-    if (pair) {
-      attrs[cfg.numAttrs].id = cudaLaunchAttributeClusterDimension;
-      attrs[cfg.numAttrs].val.clusterDim.x = 2;
-      attrs[cfg.numAttrs].val.clusterDim.y = 1;
-      attrs[cfg.numAttrs].val.clusterDim.z = 1;
-      ++cfg.numAttrs;
-    }
-  }
-};
-
 template <int KIND>
 int pairs_resident(int smem_bytes, int sm_count) {
-  WorkerLaunchConfig wc(sm_count / 2 * 2, kTc2ThreadsTwoEpi, smem_bytes, true, nullptr);
+  KernelLaunchConfig wc(sm_count / 2 * 2, kTc2ThreadsTwoEpi, smem_bytes, true, nullptr);
   int clusters = 0;
   if (cudaOccupancyMaxActiveClusters(&clusters, tc_gemm2_kernel<KIND, true>, &wc.cfg) != cudaSuccess) {
     cudaGetLastError();
@@ -709,7 +723,7 @@ int max_pairs_resident(int kind, int smem_bytes, int sm_count) {
 template <int KIND>
 cudaError_t launch_workers(const TcLaunch& L, cudaStream_t stream) {
   const bool pair = L.cta2 == 2;
-  WorkerLaunchConfig wc(L.grid, L.p.epi_groups == 2 ? kTc2ThreadsTwoEpi : kTc2Threads, L.smem_bytes, pair, stream);
+  KernelLaunchConfig wc(L.grid, L.p.epi_groups == 2 ? kTc2ThreadsTwoEpi : kTc2Threads, L.smem_bytes, pair, stream);
   if (pair)
     return cudaLaunchKernelEx(&wc.cfg, tc_gemm2_kernel<KIND, true>, L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1,
                               L.map_o0, L.map_o1, L.map_r0, L.map_r1);
@@ -752,30 +766,27 @@ cudaError_t tc_launch(const TcLaunch& L, cudaStream_t stream) {
     attr_err = e;
   });
   if (attr_err != cudaSuccess) return attr_err;
-  const dim3 grid(L.grid), block(L.p.epi_groups == 2 ? kTcThreadsTwoEpi : kTcThreads);
+  KernelLaunchConfig lc(L.grid, L.p.epi_groups == 2 ? kTcThreadsTwoEpi : kTcThreads, L.smem_bytes, false, stream);
+  cudaError_t e;
   switch (L.kind) {
     case GEMM_TF32:
-      tc_gemm_kernel<GEMM_TF32>
-          <<<grid, block, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
-                                                  L.map_o1, L.map_r0, L.map_r1);
+      e = cudaLaunchKernelEx(&lc.cfg, tc_gemm_kernel<GEMM_TF32>, L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
+                             L.map_o1, L.map_r0, L.map_r1);
       break;
     case GEMM_TF32X3:
-      tc_gemm_kernel<GEMM_TF32X3>
-          <<<grid, block, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
-                                                  L.map_o1, L.map_r0, L.map_r1);
+      e = cudaLaunchKernelEx(&lc.cfg, tc_gemm_kernel<GEMM_TF32X3>, L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
+                             L.map_o1, L.map_r0, L.map_r1);
       break;
     case GEMM_BF16X3:
-      tc_gemm_kernel<GEMM_BF16X3>
-          <<<grid, block, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
-                                                  L.map_o1, L.map_r0, L.map_r1);
+      e = cudaLaunchKernelEx(&lc.cfg, tc_gemm_kernel<GEMM_BF16X3>, L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
+                             L.map_o1, L.map_r0, L.map_r1);
       break;
     default:
-      tc_gemm_kernel<GEMM_I8>
-          <<<grid, block, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
-                                                  L.map_o1, L.map_r0, L.map_r1);
+      e = cudaLaunchKernelEx(&lc.cfg, tc_gemm_kernel<GEMM_I8>, L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
+                             L.map_o1, L.map_r0, L.map_r1);
       break;
   }
-  return cudaGetLastError();
+  return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 // ------------------------------------------------------------------ patch-resident convolution
@@ -912,17 +923,19 @@ cudaError_t tc_launch_halo(const TcHaloLaunch& L, cudaStream_t stream) {
     attr_err = e;
   });
   if (attr_err != cudaSuccess) return attr_err;
+  KernelLaunchConfig lc(L.grid, kHaloThreads, L.smem_bytes, false, stream);
+  cudaError_t e;
   if (L.kind == GEMM_BF16X3) {
-    tc_conv_halo_kernel<GEMM_BF16X3><<<L.grid, kHaloThreads, L.smem_bytes, stream>>>(
-        L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0, L.map_o1, L.map_r0, L.map_r1);
+    e = cudaLaunchKernelEx(&lc.cfg, tc_conv_halo_kernel<GEMM_BF16X3>, L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
+                           L.map_o1, L.map_r0, L.map_r1);
   } else if (L.kind == GEMM_TF32X3) {
-    tc_conv_halo_kernel<GEMM_TF32X3><<<L.grid, kHaloThreads, L.smem_bytes, stream>>>(
-        L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0, L.map_o1, L.map_r0, L.map_r1);
+    e = cudaLaunchKernelEx(&lc.cfg, tc_conv_halo_kernel<GEMM_TF32X3>, L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
+                           L.map_o1, L.map_r0, L.map_r1);
   } else {
-    tc_conv_halo_kernel<GEMM_TF32><<<L.grid, kHaloThreads, L.smem_bytes, stream>>>(
-        L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0, L.map_o1, L.map_r0, L.map_r1);
+    e = cudaLaunchKernelEx(&lc.cfg, tc_conv_halo_kernel<GEMM_TF32>, L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
+                           L.map_o1, L.map_r0, L.map_r1);
   }
-  return cudaGetLastError();
+  return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 float tf32_round_host(float x) {
@@ -1131,13 +1144,14 @@ cudaError_t tc_launch_stem(const TcStemLaunch& L, cudaStream_t stream) {
                                       tc_smem_budget(GEMM_I8) + 1024);
   });
   if (attr_err != cudaSuccess) return attr_err;
+  KernelLaunchConfig lc(L.grid, kStemThreads, L.smem_bytes, false, stream);
+  cudaError_t e;
   if (L.kind == GEMM_I8)
-    tc_stem_kernel<GEMM_I8><<<L.grid, kStemThreads, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1,
-                                                                            L.map_o0, L.map_o1);
+    e = cudaLaunchKernelEx(&lc.cfg, tc_stem_kernel<GEMM_I8>, L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0, L.map_o1);
   else
-    tc_stem_kernel<GEMM_BF16X3><<<L.grid, kStemThreads, L.smem_bytes, stream>>>(L.p, L.map_a0, L.map_a1, L.map_b0,
-                                                                                L.map_b1, L.map_o0, L.map_o1);
-  return cudaGetLastError();
+    e = cudaLaunchKernelEx(&lc.cfg, tc_stem_kernel<GEMM_BF16X3>, L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
+                           L.map_o1);
+  return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 }  // namespace nb

@@ -97,7 +97,8 @@ struct TcGemmParams {
   int act;
   float act_a, act_b;  // leaky slope / clip bounds
   float out_scale;     // requantisation scale (OUT_I8)
-  int* status;         // device word, stays 0 unless a bounded wait gave up
+  int* status;         // device words: [0] stays 0 unless a bounded wait gave up; [1] non-zero injects a stalled
+                       // stage into tc_gemm_kernel (host tests of the time-out path), zero in production
   int tma_store;       // fp32 outputs leave through shared-memory staging tiles and TMA stores
   int staging_bytes;   // staging area of one epilogue group (residual + output tiles)
   int epi_groups;      // 1 or 2 epilogue warpgroups (2: accumulator g is drained by group g; shallow layers)
@@ -667,6 +668,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
                const __grid_constant__ CUtensorMap map_r0,
                const __grid_constant__ CUtensorMap map_r1) {
   using namespace ptx;
+  grid_dependency_trigger();  // the next kernel of the stream may begin its preamble
   constexpr int PLANES = tc_planes(KIND);
 
   extern __shared__ uint8_t tc_smem_raw[];
@@ -720,6 +722,14 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
+  // barriers, tensor memory and descriptors are ready: from here on the kernel touches tensors that the
+  // kernel before it in the stream may still be writing
+  grid_dependency_wait();
+  // Fault injection for the time-out path (host tests only; status[1] is zero in production): the first
+  // tile's first stage is never armed, so the MMA issuer's bounded wait on it runs out, every role leaves
+  // through the abort path, and the host reads status 7.  The limit shrinks to 2 ms for such a run.
+  const int test_stall = p.status[1];
+  const uint64_t wait_limit = test_stall ? 2000000ull : kTcWaitLimitNs;
 
   if (warp == 0 || warp == 6) {
     // ------------------------------------------------------------ producers
@@ -768,8 +778,8 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
         const uint32_t fb = smem_u32(&full_bar[s]);
         int w = 1;
         if (lane == 0) {
-          w = mbar_wait_bounded(smem_u32(&empty_bar[s]), ph ^ 1u, abort_ptr, kTcWaitLimitNs) ? 1 : 0;
-          if (w) mbar_arrive_expect_tx(fb, my_tx);
+          w = mbar_wait_bounded(smem_u32(&empty_bar[s]), ph ^ 1u, abort_ptr, wait_limit) ? 1 : 0;
+          if (w && !(test_stall && kb == 0 && tile == static_cast<int>(blockIdx.x))) mbar_arrive_expect_tx(fb, my_tx);
         }
         w = __shfl_sync(0xffffffffu, w, 0);
         if (!w) {
@@ -778,7 +788,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
         }
         const bool tr = p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0 && tile == static_cast<int>(gridDim.x) && kb < 32;
         if (tr) p.trace[1024 + kb * 4 + 0] = clock64();
-        if (issues) {
+        if (issues && !(test_stall && kb == 0 && tile == static_cast<int>(blockIdx.x))) {
           const uint32_t dst = smem_base + s * stage_bytes + my_off;
           if (is_b) {
             tma_load_2d(dst, my_map, fb, kb * p.k_elems, n0);
@@ -816,7 +826,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
         for (long long i = first; i < issued; ++i) {
           const int st = static_cast<int>(i % S);
           const uint32_t par = static_cast<uint32_t>((i / S) & 1);
-          mbar_wait_bounded(smem_u32(&full_bar[st]), par, &zero, 200000000ull);
+          mbar_wait_bounded(smem_u32(&full_bar[st]), par, &zero, test_stall ? 2000000ull : 200000000ull);
         }
       }
     }
@@ -850,8 +860,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
       uint32_t acc_ph = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        if (!mbar_wait_bounded(smem_u32(&tempty_bar[acc]), acc_ph ^ 1u, abort_ptr,
-                               kTcWaitLimitNs)) {
+        if (!mbar_wait_bounded(smem_u32(&tempty_bar[acc]), acc_ph ^ 1u, abort_ptr, wait_limit)) {
           ok = false;
           break;
         }
@@ -862,7 +871,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
         const bool pair = tile / tiles_n < pair_rows;
         uint32_t accumulate = 0u;
         for (int kb = 0; kb < k_blocks; ++kb) {
-          if (!mbar_wait_bounded(smem_u32(&full_bar[s]), ph, abort_ptr, kTcWaitLimitNs)) {
+          if (!mbar_wait_bounded(smem_u32(&full_bar[s]), ph, abort_ptr, wait_limit)) {
             ok = false;
             break;
           }
@@ -978,10 +987,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
       const int n0 = n_blk * p.block_n;
       if (tracing) p.trace[(tile / gridDim.x) * 16 + 3] = clock64();
       // the vote keeps the warp together: tcgen05.ld below needs all 32 lanes
-      ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&tfull_bar[acc]), acc_ph, abort_ptr,
-                                                     kTcWaitLimitNs)
-                                       ? 1
-                                       : 0) != 0;
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&tfull_bar[acc]), acc_ph, abort_ptr, wait_limit) ? 1 : 0) != 0;
       if (!ok) break;
       tc_fence_after_sync();
       if (tracing) p.trace[(tile / gridDim.x) * 16 + 4] = clock64();

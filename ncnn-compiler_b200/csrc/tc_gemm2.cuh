@@ -113,6 +113,7 @@ tc_gemm2_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ 
                 const __grid_constant__ CUtensorMap map_r0,
                 const __grid_constant__ CUtensorMap map_r1) {
   using namespace ptx;
+  grid_dependency_trigger();  // the next kernel of the stream may begin its preamble
   constexpr int PLANES = tc_planes(KIND);
 
   extern __shared__ uint8_t tc2_smem_raw[];
@@ -177,6 +178,9 @@ tc_gemm2_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ 
   if (PAIR) cluster_sync_all();  // the other CTA's barriers exist before anything is sent to them
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
+  // barriers, tensor memory and descriptors are ready: from here on the kernel touches tensors that the
+  // kernel before it in the stream may still be writing
+  grid_dependency_wait();
 
   if (warp == 0 || warp == 6) {
     // ------------------------------------------------------------ producers

@@ -60,6 +60,7 @@ tc_stem_kernel(const __grid_constant__ TcStemParams p, const __grid_constant__ C
                const __grid_constant__ CUtensorMap map_b1, const __grid_constant__ CUtensorMap map_o0,
                const __grid_constant__ CUtensorMap map_o1) {
   using namespace ptx;
+  grid_dependency_trigger();  // the next kernel of the stream may begin its preamble
   constexpr int PLANES = tc_planes(KIND);
   extern __shared__ uint8_t stem_smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kStemMaxStages];
@@ -111,6 +112,9 @@ tc_stem_kernel(const __grid_constant__ TcStemParams p, const __grid_constant__ C
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = tmem_slot;
+  // barriers, tensor memory and descriptors are ready: from here on the kernel touches tensors that the
+  // kernel before it in the stream may still be writing
+  grid_dependency_wait();
 
   if (warp == 0) {
     // ------------------------------------------------------------ producer: weights once, then rows

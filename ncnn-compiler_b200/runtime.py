@@ -73,6 +73,14 @@ def load_library():
                                           c_void_p, c_int32, c_void_p, c_int32, c_int32, c_void_p]
     L.ncnn_b200_inner_product_int8_noalloc.argtypes = [c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
                                                        c_int64, c_int32, c_int32, c_int32, c_void_p]
+    L.ncnn_b200_multi_load.argtypes = [c_char_p, c_char_p, POINTER(_Options), POINTER(c_int32), c_int32, POINTER(c_void_p)]
+    L.ncnn_b200_multi_free.argtypes = [c_void_p]
+    L.ncnn_b200_multi_free.restype = None
+    L.ncnn_b200_multi_last_error.argtypes = [c_void_p]
+    L.ncnn_b200_multi_last_error.restype = c_char_p
+    L.ncnn_b200_multi_device_count.argtypes = [c_void_p]
+    L.ncnn_b200_multi_run_batch.argtypes = [c_void_p, c_int64, pp_in, pp_out]
+    L.ncnn_b200_multi_partition.argtypes = [c_int64, c_int32, POINTER(c_int64), POINTER(c_int64)]
     L.ncnn_b200_dynamic_load.argtypes = [c_char_p, c_char_p, POINTER(_Options), POINTER(_DimConstraint), c_int32,
                                          POINTER(c_void_p)]
     L.ncnn_b200_dynamic_free.argtypes = [c_void_p]
@@ -321,3 +329,55 @@ def inner_product_int8_noalloc(x_ptr, weight_ptr, weight_scales_ptr, input_scale
     st = L.ncnn_b200_inner_product_int8_noalloc(x_ptr, weight_ptr, weight_scales_ptr, c_float(input_scale), bias_ptr,
                                                 y_ptr, m, k, n, 1 if relu else 0, c_void_p(stream))
     return st, L.ncnn_b200_last_error(None).decode()
+
+
+def multi_partition(n, parts):
+    """[(first, count)] of the contiguous shards ncnn_b200_multi_run_batch gives each device."""
+    L = load_library()
+    first = (c_int64 * parts)()
+    count = (c_int64 * parts)()
+    st = L.ncnn_b200_multi_partition(n, parts, first, count)
+    if st != 0:
+        raise NcnnB200Error(st, "invalid partition request")
+    return [(int(first[g]), int(count[g])) for g in range(parts)]
+
+
+class MultiModel:
+    """One model replicated on several GPUs of a box; `run` shards the batch across them
+    (ncnn_b200_multi_*).  Host arrays in, host arrays out."""
+
+    def __init__(self, param_path, bin_path, devices, accuracy_mode=FP32_SPLIT, use_cuda_graph=True):
+        self._L = load_library()
+        self._h = c_void_p()
+        opt = _Options(ctypes.sizeof(_Options), accuracy_mode, -1, 1 if use_cuda_graph else 0, 0, None, 0, 0)
+        devs = (c_int32 * len(devices))(*devices)
+        st = self._L.ncnn_b200_multi_load(param_path.encode(), bin_path.encode() if bin_path else None, byref(opt), devs,
+                                          len(devices), byref(self._h))
+        if st != 0:
+            raise NcnnB200Error(st, self._L.ncnn_b200_last_error(None).decode())
+        single = Model(param_path, bin_path, plan_only=True)
+        self.input_shapes, self.output_shapes = single.input_shapes, single.output_shapes
+        single.close()
+
+    def close(self):
+        if self._h:
+            self._L.ncnn_b200_multi_free(self._h)
+            self._h = c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def run_raw(self, n, in_ptrs, out_ptrs):
+        return self._L.ncnn_b200_multi_run_batch(self._h, n, _ptr_array(in_ptrs), _ptr_array(out_ptrs))
+
+    def run(self, *inputs):
+        xs = [np.ascontiguousarray(x, np.float32) for x in inputs]
+        n = xs[0].shape[0]
+        outs = [np.empty((n, *s), np.float32) for s in self.output_shapes]
+        st = self.run_raw(n, [x.ctypes.data for x in xs], [y.ctypes.data for y in outs])
+        if st != 0:
+            raise NcnnB200Error(st, self._L.ncnn_b200_multi_last_error(self._h).decode())
+        return outs

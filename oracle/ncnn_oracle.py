@@ -87,6 +87,20 @@ def _ops():
     return _lib
 
 
+_libm = None
+
+
+def _powf(x: float, y: float) -> float:
+    """powf of the C library (single precision in, single precision out)."""
+    global _libm
+    if _libm is None:
+        import ctypes.util
+        _libm = ctypes.CDLL(ctypes.util.find_library("m") or "libm.so.6")
+        _libm.powf.restype = ctypes.c_float
+        _libm.powf.argtypes = [ctypes.c_float, ctypes.c_float]
+    return float(_libm.powf(x, y))
+
+
 def _p(a, t):
     return a.ctypes.data_as(ctypes.POINTER(t))
 
@@ -869,8 +883,8 @@ def op_requantize(acc_i32, scale_in, scale_out, bias=None, relu=False):
 def batchnorm_scale_offset(slope, mean, var, bias, eps):
     """FoldNCNNBatchNorm.cpp:99-124 / ConvertBatchNorm (NCNNToTosa.cpp:4740-4800)."""
     ve = (var.astype(F32) + F32(eps)).astype(F32)
-    with np.errstate(divide="ignore", invalid="ignore"):
-        inv = np.power(ve, F32(-0.5)).astype(F32)
+    # std::pow(float, float) in the fold and math.powf behind tosa.pow: the C library's powf, not NumPy's
+    inv = np.array([_powf(float(v), -0.5) if v != 0 else 10000.0 for v in ve], F32)
     inv = np.where(ve == 0, F32(10000.0), inv).astype(F32)
     scale = (slope.astype(F32) * inv).astype(F32)
     offset = (bias.astype(F32) - (scale * mean.astype(F32)).astype(F32)).astype(F32)

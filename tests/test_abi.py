@@ -69,3 +69,22 @@ def test_shard_range_covers_the_batch_exactly(pkg):
             assert max(e - b for b, e in spans) == -(-total // world) if total else True
     with pytest.raises(ValueError):
         pkg.shard_range(4, 2, 2)
+
+
+def test_multi_device_partition_is_contiguous_and_complete(pkg):
+    """The shards ncnn_b200_multi_run_batch hands to its devices: contiguous, ceil(n / devices) images each, the
+    last ones short or empty, every image exactly once (pure arithmetic: no GPU)."""
+    for n in (1, 2, 7, 32, 255, 256, 1000):
+        for parts in (1, 2, 3, 4, 8):
+            shards = pkg.multi_partition(n, parts)
+            per = -(-n // parts)
+            assert len(shards) == parts
+            covered = []
+            for first, count in shards:
+                assert 0 <= count <= per
+                covered.extend(range(first, first + count))
+            assert covered == list(range(n))
+            assert all(c == per for _, c in shards[:n // per])
+    import pytest as _pytest
+    with _pytest.raises(pkg.NcnnB200Error):
+        pkg.multi_partition(4, 0)

@@ -212,3 +212,62 @@ def test_batch_256_properties(pkg, oracle, tmp_path, net):
         assert np.array_equal(y[idx], want)
     else:
         assert rel_l2(y[idx], want) <= 2e-4
+
+
+# ------------------------------------------------------------------ a bounded wait that runs out
+def test_bounded_wait_runs_out_as_status_7_and_the_handle_recovers(pkg, oracle, tmp_path, monkeypatch):
+    """Every device-side wait of the contraction kernels has a limit and ends in a status word.  With
+    NCNN_B200_TEST_STALL set, the one-CTA kernel leaves one pipeline stage unfilled (and shrinks the limit to 2 ms):
+    the issuing warp's wait runs out, every role leaves through the abort path, tensor memory is released and the
+    kernel returns.  Nothing faults or hangs.  The call reports status 7; the next call on the same handle is
+    clean and correct."""
+    param, bin_ = pkg.zoo.single_conv(str(tmp_path / "c"), h=8, w=8)
+    x = np.random.default_rng(5).uniform(-1, 1, (2, 64, 8, 8)).astype(np.float32)
+    m = pkg.Model(param, bin_)
+    assert any(k.startswith("tc_gemm_kernel<") for k in _kernels(m, 2))
+    good = m.run(x)[0].copy()
+    monkeypatch.setenv("NCNN_B200_TEST_STALL", "1")
+    with pytest.raises(pkg.NcnnB200Error) as err:
+        m.run(x)
+    assert err.value.status == 7 and "timed out" in str(err.value)
+    monkeypatch.delenv("NCNN_B200_TEST_STALL")
+    assert np.array_equal(m.run(x)[0], good)
+    m.check_status()
+    m.close()
+    want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x])
+    assert rel_l2(good, want) <= 1e-4
+
+
+# ------------------------------------------------------------------ several devices behind one handle
+@pytest.mark.parametrize("n", [1, 5, 16])
+def test_multi_device_handle_equals_single_handle(pkg, tmp_path, n):
+    """ncnn_b200_multi_*: the batch is cut into contiguous shards, one replica (stream, graph, host thread) per
+    listed device.  On a box with one GPU the same ordinal is listed twice (two replicas side by side); with more
+    GPUs the first two.  Same bits as one handle: images are independent and every kernel is the same."""
+    import torch
+    devices = [0, 1] if torch.cuda.device_count() >= 2 else [0, 0]
+    param, bin_ = pkg.zoo.resnet18(str(tmp_path / "r"), size=64, classes=50)
+    x = np.random.default_rng(n).uniform(-1, 1, (n, 3, 64, 64)).astype(np.float32)
+    single = pkg.Model(param, bin_)
+    want = single.run(x)[0].copy()
+    single.close()
+    multi = pkg.MultiModel(param, bin_, devices)
+    for _ in range(2):
+        got = multi.run(x)[0]
+        assert np.array_equal(got, want)
+    multi.close()
+
+
+def test_handles_on_their_own_device_leave_the_callers_device_alone(pkg, tmp_path):
+    """Every entry point makes the model's device current for the call and restores the caller's."""
+    import torch
+    param, bin_ = pkg.zoo.single_conv(str(tmp_path / "c"), h=8, w=8)
+    last = torch.cuda.device_count() - 1
+    torch.cuda.set_device(0)
+    m = pkg.Model(param, bin_, device=last)
+    assert torch.cuda.current_device() == 0
+    x = np.random.default_rng(0).uniform(-1, 1, (2, 64, 8, 8)).astype(np.float32)
+    y = m.run(x)[0]
+    assert torch.cuda.current_device() == 0 and np.isfinite(y).all()
+    m.close()
+    assert torch.cuda.current_device() == 0

@@ -63,6 +63,34 @@ def test_no_alloc_entry_matches_model_path_twice(pkg, tmp_path, m, k, n, relu):
         assert np.array_equal(got, want), f"call {call}: max abs diff {np.abs(got - want).max()}"
 
 
+def test_no_alloc_entry_takes_weights_at_any_byte_offset_and_matches_the_oracle(pkg, oracle, tmp_path):
+    """A weight blob carved out of a larger buffer may start at an odd address: the entry point then reads it byte
+    by byte instead of word by word.  Checked against the CPU oracle (the reference's int8 InnerProduct
+    arithmetic), bit for bit, and against the aligned call."""
+    import torch
+    rng = np.random.default_rng(78)
+    m, k, n = 9, 256, 33
+    wq = rng.integers(-127, 128, (n, k)).astype(np.int8)
+    bias = (rng.standard_normal(n) * 0.1).astype(np.float32)
+    ws = rng.uniform(20, 200, n).astype(np.float32)
+    s_in = np.float32(23.5)
+    param, bin_ = write_int8_inner_product(str(tmp_path / "ip"), wq, bias, ws, s_in, True)
+    x = rng.uniform(-1.5, 1.5, (m, 1, 1, k)).astype(np.float32)
+    om = oracle.Model(param, bin_)
+    want = np.stack([om.run([xi])[0] for xi in x])
+    blob = torch.zeros(n * k + 16, dtype=torch.int8, device="cuda")
+    d_ws, d_b = torch.from_numpy(ws).cuda(), torch.from_numpy(bias).cuda()
+    d_x = torch.from_numpy(x.reshape(m, k)).cuda()
+    for offset in (0, 1, 2, 3):
+        blob[offset:offset + n * k] = torch.from_numpy(wq.reshape(-1)).cuda()
+        d_y = torch.full((m, n), float("nan"), device="cuda")
+        status, message = pkg.inner_product_int8_noalloc(d_x.data_ptr(), blob.data_ptr() + offset, d_ws.data_ptr(),
+                                                         float(s_in), d_b.data_ptr(), d_y.data_ptr(), m, k, n, True, 0)
+        assert status == 0, message
+        torch.cuda.synchronize()
+        assert np.array_equal(d_y.cpu().numpy(), want), f"weight offset {offset}"
+
+
 def test_no_alloc_entry_refuses_oversized_requests(pkg):
     import torch
     t = torch.zeros(16, device="cuda")
@@ -72,3 +100,7 @@ def test_no_alloc_entry_refuses_oversized_requests(pkg):
     assert status == 5 and "exceed the built-in scratch" in message
     status, _ = pkg.inner_product_int8_noalloc(None, w.data_ptr(), t.data_ptr(), 1.0, None, t.data_ptr(), 1, 16, 1)
     assert status == 1
+    # a row count whose product with k wraps around 64 bits is refused like any other (nothing is launched)
+    status, message = pkg.inner_product_int8_noalloc(t.data_ptr(), w.data_ptr(), t.data_ptr(), 1.0, None, t.data_ptr(),
+                                                     2**61 + 1, 8, 1, False, 0)
+    assert status == 5 and "exceed the built-in scratch" in message
