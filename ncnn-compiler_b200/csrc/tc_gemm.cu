@@ -386,7 +386,12 @@ bool finish_plan_workers(TcLaunch* L, int kind, long long M, int N, const TcEpil
   const long long one_units = one_tiles * full_kb;
   const int one_workers = static_cast<int>(std::min<long long>(sm_count, one_units / 4));
   bool split_form = false;
-  if (!pair_form && ws_given && forced_split != 0 && one_workers >= 2) {
+  // Where a tile is cut depends on how many tiles there are, so a split layer rounds its fp32 sums
+  // differently at different batch sizes.  Convolutions keep whole tiles (splitting them gained nothing
+  // on the benchmark networks, and a batch then equals its images run one by one bit for bit);
+  // InnerProduct and Gemm, where a handful of rows must stream megabytes of weights, are split.
+  const bool may_split = forced_split == 1 || (forced_split != 0 && !p.a_im2col);
+  if (!pair_form && ws_given && may_split && one_workers >= 2) {
     // Every worker ends with the tile it finishes, whose partial sums arrive no earlier than the other
     // workers finish theirs: publishing, waiting and adding them is an exposed tail worth about twenty
     // K blocks (measured on 3x3 convolutions of 256 and 512 channels at batch 64, where splitting lost).
@@ -487,7 +492,7 @@ bool finish_plan_workers(TcLaunch* L, int kind, long long M, int N, const TcEpil
       return false;
     }
   } else {
-    p.streamk = can_split && (forced_split == 1 || (forced_split != 0 && cost_split < 0.95 * cost_whole)) ? 1 : 0;
+    p.streamk = can_split && may_split && (forced_split == 1 || cost_split < 0.95 * cost_whole) ? 1 : 0;
   }
   if (!p.streamk) workers = static_cast<int>(std::min<long long>(workers, tiles));
   p.sk_ws = e.sk_ws;
