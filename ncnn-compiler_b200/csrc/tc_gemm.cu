@@ -305,6 +305,25 @@ int env_int(const char* name, int fallback) {
 
 int max_pairs_resident(int kind, int smem_bytes, int sm_count);
 
+// Function attributes (the opt-in to more than 48 KB of dynamic shared memory) belong to a device's
+// context: they are set once per device, with that device current, not once per process.
+struct PerDeviceOnce {
+  std::mutex mutex;
+  bool done[64] = {};
+  cudaError_t result[64] = {};
+  template <class F>
+  cudaError_t run(F&& setup) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(mutex);
+    if (!done[device]) {
+      result[device] = setup();
+      done[device] = true;
+    }
+    return result[device];
+  }
+};
+
 // NCNN_B200_PDL=0 launches every contraction kernel fully serialised behind its predecessor.
 bool pdl_enabled() {
   static const bool on = env_int("NCNN_B200_PDL", 1) != 0;
@@ -686,16 +705,14 @@ cudaError_t prepare_worker_kernel() {
 }
 
 cudaError_t prepare_worker_kernels() {
-  static std::once_flag once;
-  static cudaError_t result = cudaSuccess;
-  std::call_once(once, [] {
+  static PerDeviceOnce once;
+  return once.run([] {
     cudaError_t e = prepare_worker_kernel<GEMM_TF32>();
     if (e == cudaSuccess) e = prepare_worker_kernel<GEMM_TF32X3>();
     if (e == cudaSuccess) e = prepare_worker_kernel<GEMM_I8>();
     if (e == cudaSuccess) e = prepare_worker_kernel<GEMM_BF16X3>();
-    result = e;
+    return e;
   });
-  return result;
 }
 
 template <int KIND>
@@ -753,9 +770,8 @@ cudaError_t tc_launch_workers(const TcLaunch& L, cudaStream_t stream) {
 
 cudaError_t tc_launch(const TcLaunch& L, cudaStream_t stream) {
   if (L.cta2) return tc_launch_workers(L, stream);
-  static std::once_flag attr_once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(attr_once, [] {
+  static PerDeviceOnce attr_once;
+  const cudaError_t attr_err = attr_once.run([] {
     const int max_smem = tc_smem_budget(GEMM_TF32) + 1024;  // contents + alignment slack
     cudaError_t e = cudaFuncSetAttribute(tc_gemm_kernel<GEMM_TF32>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
@@ -768,7 +784,7 @@ cudaError_t tc_launch(const TcLaunch& L, cudaStream_t stream) {
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(tc_gemm_kernel<GEMM_BF16X3>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-    attr_err = e;
+    return e;
   });
   if (attr_err != cudaSuccess) return attr_err;
   KernelLaunchConfig lc(L.grid, L.p.epi_groups == 2 ? kTcThreadsTwoEpi : kTcThreads, L.smem_bytes, false, stream);
@@ -913,9 +929,8 @@ std::string tc_plan_conv_halo(TcHaloLaunch* L, int kind, const TcHaloConv& c, co
 }
 
 cudaError_t tc_launch_halo(const TcHaloLaunch& L, cudaStream_t stream) {
-  static std::once_flag attr_once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(attr_once, [] {
+  static PerDeviceOnce attr_once;
+  const cudaError_t attr_err = attr_once.run([] {
     const int max_smem = 223 * 1024;
     cudaError_t e = cudaFuncSetAttribute(tc_conv_halo_kernel<GEMM_TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          max_smem);
@@ -925,7 +940,7 @@ cudaError_t tc_launch_halo(const TcHaloLaunch& L, cudaStream_t stream) {
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(tc_conv_halo_kernel<GEMM_BF16X3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                max_smem);
-    attr_err = e;
+    return e;
   });
   if (attr_err != cudaSuccess) return attr_err;
   KernelLaunchConfig lc(L.grid, kHaloThreads, L.smem_bytes, false, stream);
@@ -1139,14 +1154,14 @@ std::string tc_plan_stem(TcStemLaunch* L, const TcStemConv& c, const TcEpilogue&
 }
 
 cudaError_t tc_launch_stem(const TcStemLaunch& L, cudaStream_t stream) {
-  static std::once_flag attr_once;
-  static cudaError_t attr_err = cudaSuccess;
-  std::call_once(attr_once, [] {
-    attr_err = cudaFuncSetAttribute(tc_stem_kernel<GEMM_BF16X3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    tc_smem_budget(GEMM_BF16X3) + 1024);
-    if (attr_err == cudaSuccess)
-      attr_err = cudaFuncSetAttribute(tc_stem_kernel<GEMM_I8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      tc_smem_budget(GEMM_I8) + 1024);
+  static PerDeviceOnce attr_once;
+  const cudaError_t attr_err = attr_once.run([] {
+    cudaError_t e = cudaFuncSetAttribute(tc_stem_kernel<GEMM_BF16X3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         tc_smem_budget(GEMM_BF16X3) + 1024);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(tc_stem_kernel<GEMM_I8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               tc_smem_budget(GEMM_I8) + 1024);
+    return e;
   });
   if (attr_err != cudaSuccess) return attr_err;
   KernelLaunchConfig lc(L.grid, kStemThreads, L.smem_bytes, false, stream);
