@@ -46,6 +46,9 @@ struct Node {
   std::string name, type;
   std::vector<int> in;
   int out = -1;
+  // int8 copies of the fp32 result that this node writes as well, each quantised with the input scale of
+  // the int8 contraction that reads it (tensor id, scale): the Quantize steps they replace are gone
+  std::vector<std::pair<int, float>> side_q;
   // contraction geometry
   int KH = 1, KW = 1, sh = 1, sw = 1, pt = 0, pl = 0, dh = 1, dw = 1, O = 0, OH = 1, OW = 1;
   int term = 0;
@@ -215,6 +218,7 @@ class EngineImpl {
   int finish_host_run(cudaStream_t st);
   void choose_head_limit();
   void fold_channel_concats();
+  void fuse_quantize_steps();
   int profile(int64_t n, int repeat, std::vector<LayerTiming>* out);
   Plan* plan_for(int64_t n);
 
@@ -1674,6 +1678,47 @@ void EngineImpl::fold_channel_concats() {
   }
 }
 
+static bool halo_preferred();
+
+// A Quantize step in front of an int8 contraction re-reads an fp32 tensor that a tensor-core contraction or
+// a pooling layer has just written.  Where that producer can quantise on the way out (plain fp32 result,
+// channels in multiples of 16 for the contraction's 16-byte stores, 4 for pooling), the int8 copy becomes a
+// second result of the producer and the Quantize step disappears.  The value quantised is the value stored,
+// so the bits are those of the separate step.
+// Measured on the int8 ResNet-18 at batch 64: folding into the pooling layers pays (they run at full
+// occupancy: +3 us on the pooling pass for a 16 us Quantize pass saved); folding into the residual
+// convolutions' epilogue does not (+20..29 us on the convolution for 16 us saved: the epilogue warps run one
+// per scheduler and are what bounds those layers already), so it is opt-in.
+//   NCNN_B200_FUSE_QUANT=0  keep every Quantize step;  =1 (default) fold into pooling layers;
+//   =2 fold into tensor-core contractions as well.
+void EngineImpl::fuse_quantize_steps() {
+  const char* env = std::getenv("NCNN_B200_FUSE_QUANT");
+  const int level = env == nullptr || env[0] == 0 ? 1 : std::atoi(env);
+  if (level <= 0) return;
+  for (size_t k = 0; k < nodes_.size(); ++k) {
+    const Node& q = nodes_[k];
+    if (q.kind != N_UNARY || q.un.op != UN_QUANT || q.un.nscale != 1 || q.un_scale.empty()) continue;
+    const int src = resolve(q.in[0]);
+    const Tensor& ts = tensors_[src];
+    if (ts.fmt != FMT_F32 || ts.is_input) continue;
+    int pj = -1;
+    for (size_t j = 0; j < k; ++j)
+      if (resolve(nodes_[j].out) == src) pj = static_cast<int>(j);
+    if (pj < 0) continue;
+    Node& p = nodes_[pj];
+    const int channels = ts.rank == 3 ? ts.c : ts.w;
+    bool ok = false;
+    if (level >= 2 && (p.kind == N_CONV || p.kind == N_IP) && p.impl == IMPL_TC && p.term != 0 && !p.stem && p.out_ld == 0)
+      ok = channels % 16 == 0 && p.side_q.size() < 2;
+    else if (p.kind == N_POOL)
+      ok = channels % 4 == 0 && p.side_q.empty() && ts.Cp == ts.c && ts.Wp == ts.w;
+    if (!ok) continue;
+    p.side_q.emplace_back(q.out, q.un_scale[0]);
+    nodes_.erase(nodes_.begin() + k);
+    --k;
+  }
+}
+
 bool EngineImpl::prepare_weights(std::string* err) {
   const int f32_kind = opt_.accuracy_mode == kAccuracyTf32 ? GEMM_TF32 : GEMM_TF32X3;
   // insert Quantize steps in front of int8 contractions whose input is fp32
@@ -1736,6 +1781,7 @@ bool EngineImpl::prepare_weights(std::string* err) {
       t.fmt = FMT_F32;
     }
   }
+  fuse_quantize_steps();
   for (Node& n : nodes_) {
     const bool i8 = n.term != 0;
     if (n.has_bias) n.d_bias = upload(n.bias);
@@ -1953,6 +1999,11 @@ void EngineImpl::plan_memory() {
     o.last_use = std::max(o.last_use, k);
     for (int t : n.in) tensors_[resolve(t)].last_use = std::max(tensors_[resolve(t)].last_use, k);
     if (n.res >= 0) tensors_[resolve(n.res)].last_use = std::max(tensors_[resolve(n.res)].last_use, k);
+    for (const auto& side : n.side_q) {
+      Tensor& sq = tensors_[resolve(side.first)];
+      if (sq.first_def < 0) sq.first_def = k;
+      sq.last_use = std::max(sq.last_use, k);
+    }
   }
   for (int t : inputs_) {
     tensors_[resolve(t)].first_def = -1;
@@ -2157,6 +2208,11 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
       }
       te.out_scale = node.s_out;
       te.status = d_status_;
+      te.side_count = static_cast<int>(node.side_q.size());
+      for (int i = 0; i < te.side_count; ++i) {
+        te.side_q[i] = ref(node.side_q[i].first, n).q;
+        te.side_scale[i] = node.side_q[i].second;
+      }
       te.sk_ws = d_split_ws_;
       te.sk_ws_bytes = kTcSplitWorkspaceBytes;
       te.sk_flags = d_split_flags_;
@@ -2364,6 +2420,8 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
     const ActRef in = ref(node.in[0], n);
     PoolParams p = node.pool;
     p.images = n;
+    p.side_q = node.side_q.empty() ? nullptr : ref(node.side_q[0].first, n).q;
+    p.side_scale = node.side_q.empty() ? 0.0f : node.side_q[0].second;
     const bool vec = p.C % 4 == 0;
     if (p.kind == 0 && p.KH == 3 && p.KW == 3 && p.sh == 2 && p.sw == 2 && vec && !tensors_[resolve(node.in[0])].i8 &&
         n <= 65535 && p.OH * p.OW >= 64) {

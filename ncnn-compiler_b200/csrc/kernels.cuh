@@ -338,7 +338,18 @@ struct PoolParams {
   // branch, NCNNToTosa.cpp:1706-1745); an axis whose output extent equals "same as input" has
   // one-element windows, which the same formula yields
   int adaptive;
+  // optional int8 copy of the result for an int8 contraction that reads it next: Q(value, side_scale),
+  // same layout as the fp32 result
+  int8_t* side_q;
+  float side_scale;
 };
+
+__device__ __forceinline__ void pool_store_side4(const PoolParams& p, long long o, float a, float b, float c, float d) {
+  if (p.side_q == nullptr) return;
+  *reinterpret_cast<char4*>(p.side_q + o) =
+      make_char4(static_cast<signed char>(quantize_rha(a, p.side_scale)), static_cast<signed char>(quantize_rha(b, p.side_scale)),
+                 static_cast<signed char>(quantize_rha(c, p.side_scale)), static_cast<signed char>(quantize_rha(d, p.side_scale)));
+}
 
 template <int VEC>
 static __global__ void k_pool(ActRef in, ActRef out, PoolParams p) {
@@ -395,8 +406,10 @@ static __global__ void k_pool(ActRef in, ActRef out, PoolParams p) {
     const long long o = ((img * p.OH + oh) * p.OW + ow) * p.C + c;
     if (VEC == 4) {
       act_store4(out, o, make_float4(acc[0], acc[1 % VEC], acc[2 % VEC], acc[3 % VEC]));
+      pool_store_side4(p, o, acc[0], acc[1 % VEC], acc[2 % VEC], acc[3 % VEC]);
     } else {
       act_store(out, o, acc[0]);
+      if (p.side_q != nullptr) p.side_q[o] = static_cast<int8_t>(quantize_rha(acc[0], p.side_scale));
     }
   }
 }
@@ -650,7 +663,9 @@ static __global__ void __launch_bounds__(256) k_maxpool3x3s2_tile(ActRef in, Act
         acc.w = fmaxf(acc.w, x.w);
       }
     }
-    act_store4(out, ((img * p.OH + oy) * p.OW + ox) * static_cast<long long>(p.C) + (cg0 + cg) * 4, acc);
+    const long long dst = ((img * p.OH + oy) * p.OW + ox) * static_cast<long long>(p.C) + (cg0 + cg) * 4;
+    act_store4(out, dst, acc);
+    pool_store_side4(p, dst, acc.x, acc.y, acc.z, acc.w);
   }
 }
 

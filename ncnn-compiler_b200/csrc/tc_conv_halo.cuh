@@ -323,6 +323,7 @@ tc_conv_halo_kernel(const __grid_constant__ TcHaloParams p, const __grid_constan
         __device__ __forceinline__ void store_out(int plane, uint32_t src, int col) const {
           ptx::tma_store_4d(plane ? o1 : o0, src, col, x, y, img);
         }
+        __device__ __forceinline__ void store_side(int, uint32_t, int) const {}
       } io{&map_o0, &map_o1, &map_r0, &map_r1, ox0, oy0, img};
       ok = tc_staged_epilogue<KIND>(cfg, io, t_row, n0, row, threadIdx.x == 64, tile_bias, tile_bias, res_ph,
                                     out_slot, abort_ptr);

@@ -138,6 +138,8 @@ bool pair_enabled() {
   return f == nullptr || f[0] != '0';
 }
 
+int env_int(const char* name, int fallback);
+
 void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e, int sm_count) {
   TcGemmParams& p = L->p;
   p.M = static_cast<int>(M);
@@ -153,7 +155,13 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
   // multiple of 64 wide, rows are 16-byte multiples and nothing is added after requantisation
   const bool i8_staged = e.out_mode == OUT_I8 && N % 64 == 0 && e.ldo % 16 == 0 && e.res0 == nullptr &&
                          (reinterpret_cast<uintptr_t>(e.outq) & 15) == 0;
-  p.block_n = choose_block_n(p.tiles_m, N, sm_count, i8_staged ? 64 : (wide ? 32 : 16));
+  // int8 copies of an fp32 result (TcEpilogue::side_q) leave 64 columns at a time through staging tiles of
+  // their own (two [128][64] tiles per copy) when rows and tiles come in 64-channel units
+  const bool side_staged = e.side_count > 0 && e.out_mode != OUT_I8 && N % 64 == 0 && e.ldo % 16 == 0 &&
+                           (reinterpret_cast<uintptr_t>(e.side_q[0]) & 15) == 0 &&
+                           (reinterpret_cast<uintptr_t>(e.side_q[1]) & 15) == 0;
+  const int side_bytes = side_staged ? e.side_count * 16384 : 0;
+  p.block_n = choose_block_n(p.tiles_m, N, sm_count, (i8_staged || side_staged) ? 64 : (wide ? 32 : 16));
   p.tiles_n = (N + p.block_n - 1) / p.block_n;
   const int kTcSmemBudget = tc_smem_budget(kind);
   const int planes = tc_planes(kind);
@@ -181,7 +189,7 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
   if (p.tma_store) {
     for (int bufs : {4, 3, 2}) {
       p.out_bufs = bufs;
-      staging = (res_mode != RES_NONE ? 16384 : 0) + bufs * out_tile;
+      staging = ((res_mode != RES_NONE ? 16384 : 0) + side_bytes) + bufs * out_tile;
       if ((kTcSmemBudget - staging) / p.stage_bytes >= 3 || bufs == 2) break;
     }
     // Deep contractions hide even a slow epilogue behind the next tile's main loop; there a third
@@ -200,9 +208,18 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
   // every other tile, with a staging area of its own.  Two groups with two staging tiles each beat
   // one group with four, so the tile count per group is reduced before the second group is given up.
   const long long tiles_total = static_cast<long long>(p.tiles_m) * p.tiles_n;
+  // The same holds for deeper contractions whose K blocks are cheap (int8: a K block is 128 channels
+  // and one or two MMAs): estimate both sides per tile, in cycles, from measured figures -- about 1800
+  // cycles per fp32 chunk and 3000 per 64-column int8 chunk in the epilogue; per K block the larger of
+  // the MMA issue time and the operand fetch at 45 bytes per cycle.
+  const int chunk_cols = e.out_mode == OUT_I8 ? 64 : (wide ? 32 : 16);
+  const double epi_cycles = static_cast<double>((p.block_n + chunk_cols - 1) / chunk_cols) * (e.out_mode == OUT_I8 ? 3000.0 : 1800.0);
+  const double mma_cycles = (planes == 2 ? 3.0 : 1.0) * (p.row_bytes / 32) * (p.block_n <= 64 ? 48.0 : 64.0 * p.block_n / 128.0);
+  const double main_cycles = p.k_blocks * std::max(mma_cycles, p.stage_bytes / 45.0);
+  const bool epilogue_bound = env_int("NCNN_B200_EPI2", 1) != 0 && epi_cycles > 1.2 * main_cycles;
   p.epi_groups = 1;
-  if (p.tma_store && p.k_blocks <= 4 && tiles_total >= 2ll * sm_count) {
-    const int res_bytes = res_mode != RES_NONE ? 16384 : 0;
+  if (p.tma_store && (p.k_blocks <= 4 || epilogue_bound) && tiles_total >= 2ll * sm_count) {
+    const int res_bytes = (res_mode != RES_NONE ? 16384 : 0) + side_bytes;
     for (int bufs : {4, 3, 2}) {
       const int both = 2 * (res_bytes + bufs * out_tile);
       if (bufs > p.out_bufs) continue;
@@ -228,11 +245,11 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
     // as many output tiles as still leave two stages (the leader waits less for stores to drain)
     int pair_bufs = 2;
     for (int bufs : {4, 3})
-      if ((kTcSmemBudget - (res_mode != RES_NONE ? 16384 : 0) - bufs * out_tile) / pair_stage >= 2) {
+      if ((kTcSmemBudget - ((res_mode != RES_NONE ? 16384 : 0) + side_bytes) - bufs * out_tile) / pair_stage >= 2) {
         pair_bufs = bufs;
         break;
       }
-    const int pair_staging = (res_mode != RES_NONE ? 16384 : 0) + pair_bufs * out_tile;
+    const int pair_staging = ((res_mode != RES_NONE ? 16384 : 0) + side_bytes) + pair_bufs * out_tile;
     const long long waves_single = (tiles_total + sm_count - 1) / sm_count;
     const double cost_single = static_cast<double>(waves_single) * (kTcBlockM + p.block_n);
     // whole waves of pairs first, single tiles for what is left; k waves of pairs cover
@@ -291,7 +308,14 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
   p.out_scale = e.out_scale;
   p.status = e.status;
   p.trace = e.trace;
-  L->map_o0 = L->map_o1 = L->map_r0 = L->map_r1 = CUtensorMap{};
+  p.side_staged = side_staged && p.tma_store ? 1 : 0;
+  p.side_count = e.side_count;
+  p.side_ld = e.ldo;
+  p.side_q0 = e.side_q[0];
+  p.side_q1 = e.side_q[1];
+  p.side_scale0 = e.side_scale[0];
+  p.side_scale1 = e.side_scale[1];
+  L->map_o0 = L->map_o1 = L->map_r0 = L->map_r1 = L->map_s0 = L->map_s1 = CUtensorMap{};
 }
 
 // ---- CTA pairs (tc_gemm2.cuh)
@@ -381,6 +405,7 @@ bool finish_plan_workers(TcLaunch* L, int kind, long long M, int N, const TcEpil
                                     !(wide && (e.out_mode == OUT_F32_SPLIT || e.out_mode == OUT_F32_TF32 ||
                                                res_mode == RES_SPLIT)));
   if (!staged) return false;  // this kernel has the staged epilogue only
+  if (e.side_count > 0) return false;  // int8 copies of the result: the one-CTA kernel writes those
   const int step = i8_staged ? 64 : (wide ? 32 : 16);
   auto even_width = [&](int widest) {
     const int n_tiles = (N + widest - 1) / widest;
@@ -534,6 +559,13 @@ bool finish_plan_workers(TcLaunch* L, int kind, long long M, int N, const TcEpil
   p.out_scale = e.out_scale;
   p.status = e.status;
   p.trace = e.trace;
+  p.side_staged = 0;  // (this kernel stores the int8 copies thread by thread)
+  p.side_count = e.side_count;
+  p.side_ld = e.ldo;
+  p.side_q0 = e.side_q[0];
+  p.side_q1 = e.side_q[1];
+  p.side_scale0 = e.side_scale[0];
+  p.side_scale1 = e.side_scale[1];
   L->map_o0 = L->map_o1 = L->map_r0 = L->map_r1 = CUtensorMap{};
   return true;
 }
@@ -576,6 +608,17 @@ std::string encode_epilogue_maps(TcLaunch* L, const TcEpilogue& e) {
     err = encode_plane(&L->map_o1, e.out1, L->p.M, L->p.N, e.ldo, ob);
   if (err.empty() && e.res0 != nullptr) err = encode_plane(&L->map_r0, e.res0, L->p.M, L->p.N, e.ldo, e.res_bf16);
   if (err.empty() && e.res1 != nullptr) err = encode_plane(&L->map_r1, e.res1, L->p.M, L->p.N, e.ldo, e.res_bf16);
+  for (int i = 0; i < e.side_count && err.empty() && L->p.side_staged; ++i) {
+    // [M][N] int8 plane, boxes of 64 columns x 128 rows, 64-byte swizzle
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(L->p.N), static_cast<cuuint64_t>(L->p.M)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(e.ldo)};
+    const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(kTcBlockM)};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    const CUresult r = g_encode_tiled(i ? &L->map_s1 : &L->map_s0, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, e.side_q[i], dims,
+                                      strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) err = "cuTensorMapEncodeTiled failed for an int8 copy of the result with code " + std::to_string(static_cast<int>(r));
+  }
   return err;
 }
 
@@ -784,6 +827,9 @@ cudaError_t tc_launch(const TcLaunch& L, cudaStream_t stream) {
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(tc_gemm_kernel<GEMM_BF16X3>,
                                cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(tc_gemm_kernel<GEMM_I8, true>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem_budget(GEMM_I8) + 1024);
     return e;
   });
   if (attr_err != cudaSuccess) return attr_err;
@@ -792,19 +838,24 @@ cudaError_t tc_launch(const TcLaunch& L, cudaStream_t stream) {
   switch (L.kind) {
     case GEMM_TF32:
       e = cudaLaunchKernelEx(&lc.cfg, tc_gemm_kernel<GEMM_TF32>, L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
-                             L.map_o1, L.map_r0, L.map_r1);
+                             L.map_o1, L.map_r0, L.map_r1, L.map_s0, L.map_s1);
       break;
     case GEMM_TF32X3:
       e = cudaLaunchKernelEx(&lc.cfg, tc_gemm_kernel<GEMM_TF32X3>, L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
-                             L.map_o1, L.map_r0, L.map_r1);
+                             L.map_o1, L.map_r0, L.map_r1, L.map_s0, L.map_s1);
       break;
     case GEMM_BF16X3:
       e = cudaLaunchKernelEx(&lc.cfg, tc_gemm_kernel<GEMM_BF16X3>, L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
-                             L.map_o1, L.map_r0, L.map_r1);
+                             L.map_o1, L.map_r0, L.map_r1, L.map_s0, L.map_s1);
       break;
     default:
-      e = cudaLaunchKernelEx(&lc.cfg, tc_gemm_kernel<GEMM_I8>, L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
-                             L.map_o1, L.map_r0, L.map_r1);
+      // (int8 copies of an fp32 result are written by an instantiation of its own)
+      if (L.p.side_count > 0)
+        e = cudaLaunchKernelEx(&lc.cfg, tc_gemm_kernel<GEMM_I8, true>, L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
+                               L.map_o1, L.map_r0, L.map_r1, L.map_s0, L.map_s1);
+      else
+        e = cudaLaunchKernelEx(&lc.cfg, tc_gemm_kernel<GEMM_I8>, L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
+                               L.map_o1, L.map_r0, L.map_r1, L.map_s0, L.map_s1);
       break;
   }
   return e != cudaSuccess ? e : cudaGetLastError();

@@ -116,6 +116,15 @@ struct TcGemmParams {
   // between neighbouring pairs; the pair that holds a tile's last K block adds the others' partial
   // accumulators (exchanged through sk_ws) and runs the epilogue.
   int streamk;
+  // Quantised copies of an fp32 result for the int8 contractions that read it next (up to two, each with
+  // its consumer's input scale): written by the epilogue next to the fp32 tensor, so no Quantize pass
+  // re-reads it.  Q(.) is the reference's (NCNNToTosa.cpp:356-385) applied to the value that is stored.
+  int side_count;
+  int8_t* side_q0;
+  int8_t* side_q1;
+  float side_scale0, side_scale1;
+  long long side_ld;   // row stride of the int8 copies in elements
+  int side_staged;     // the copies leave through staging tiles and TMA stores (tc_gemm_kernel, channels in 64s)
   uint32_t* sk_ws;     // one slot of 128 x block_n accumulator words per CTA
   int* sk_flags;       // one word per CTA: 1 while its slot holds a partial that nobody has consumed
 };
@@ -171,9 +180,36 @@ __device__ __forceinline__ float apply_act(float y, int act, float a, float b) {
   return y;
 }
 
+// 16 fp32 results of one row -> 16 int8 with the reference's rounding, one 16-byte store
+__device__ __forceinline__ void tc_store_side_quant(int8_t* q, float scale, const float (&y)[16]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    w[g] = (static_cast<uint32_t>(quantize_rha(y[4 * g + 0], scale)) & 0xffu) |
+           ((static_cast<uint32_t>(quantize_rha(y[4 * g + 1], scale)) & 0xffu) << 8) |
+           ((static_cast<uint32_t>(quantize_rha(y[4 * g + 2], scale)) & 0xffu) << 16) |
+           ((static_cast<uint32_t>(quantize_rha(y[4 * g + 3], scale)) & 0xffu) << 24);
+  }
+  *reinterpret_cast<uint4*>(q) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// the same 16 bytes into a shared-memory staging tile
+__device__ __forceinline__ void tc_stage_side_quant(uint32_t smem_at, float scale, const float (&y)[16]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    w[g] = (static_cast<uint32_t>(quantize_rha(y[4 * g + 0], scale)) & 0xffu) |
+           ((static_cast<uint32_t>(quantize_rha(y[4 * g + 1], scale)) & 0xffu) << 8) |
+           ((static_cast<uint32_t>(quantize_rha(y[4 * g + 2], scale)) & 0xffu) << 16) |
+           ((static_cast<uint32_t>(quantize_rha(y[4 * g + 3], scale)) & 0xffu) << 24);
+  }
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(smem_at), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+               : "memory");
+}
+
 // BF16IO: a bf16-pair tensor takes part (as output or residual); kept out of the other
 // instantiation so that the int8 and plain fp32 epilogues stay lean.
-template <int KIND, bool BF16IO>
+template <int KIND, bool BF16IO, bool SIDE = false>
 __device__ __forceinline__ void tc_epilogue_chunk(const TcGemmParams& p, const uint32_t (&v)[16],
                                                   long long m, int n_first, const float* tile_bias,
                                                   const float* tile_scale) {
@@ -271,6 +307,10 @@ __device__ __forceinline__ void tc_epilogue_chunk(const TcGemmParams& p, const u
   }
 #pragma unroll
   for (int j = 0; j < 16; ++j) y[j] = apply_act(y[j], p.act, p.act_a, p.act_b);
+  if (SIDE && p.side_count > 0) {
+    tc_store_side_quant(p.side_q0 + m * p.side_ld + n_first, p.side_scale0, y);
+    if (p.side_count > 1) tc_store_side_quant(p.side_q1 + m * p.side_ld + n_first, p.side_scale1, y);
+  }
   if (BF16IO && p.out_mode == OUT_BF16X2) {
     uint16_t* o0 = reinterpret_cast<uint16_t*>(p.out0);
     uint16_t* o1 = reinterpret_cast<uint16_t*>(p.out1);
@@ -391,7 +431,20 @@ struct TcStageCfg {
   const uint32_t* fix_ws;
   long long fix_stride;
   int fix_count;
+  // int8 copies of the result (see TcGemmParams::side_q): pointers at this tile's first row and column,
+  // rows of the tile that exist
+  int side_count;
+  int8_t* side_q0;
+  int8_t* side_q1;
+  float side_scale0, side_scale1;
+  long long side_ld;
+  int side_rows;
+  // staged form of the int8 copies (side_stage != 0): 64 columns of a copy are collected in a [128][64]
+  // int8 tile (64-byte swizzle, two tiles per copy used in turn) and leave through one TMA store
+  // (io.store_side); otherwise every thread stores its 16 bytes itself
+  uint32_t side_stage;
 };
+
 
 // Sum of the partial accumulators of one row over 16 columns.  The slots were written by other SMs
 // during this launch: read them from L2, never through L1.
@@ -426,11 +479,14 @@ __device__ __forceinline__ void tc_add_partials(uint32_t (&v)[16], const uint32_
 
 // IO: load_res(plane, smem_dst, bar, column) and store_out(plane, smem_src, column) issue the
 // TMA copies of one staging tile; the caller binds tensor maps and row coordinates.
-template <int KIND, class IO>
+// EXTRAS: partial sums of split tiles and int8 copies of the result take part.  They are compiled out of
+// the plain instantiation: an epilogue warp runs alone on its scheduler, so every instruction and every live
+// register of a path that is not taken still costs the layers that never take it.
+template <int KIND, class IO, bool EXTRAS = false>
 __device__ __forceinline__ bool tc_staged_epilogue(const TcStageCfg c, const IO& io, uint32_t t_row, int n0,
                                                    int row, bool leader, const float* tile_bias,
                                                    const float* tile_scale, uint32_t& res_ph, int& out_slot,
-                                                   volatile int* abort_ptr) {
+                                                   volatile int* abort_ptr, int* side_slot = nullptr) {
   using namespace ptx;
   const bool has_res = c.res_mode != RES_NONE;
   const bool wide = c.wide != 0;
@@ -451,8 +507,8 @@ __device__ __forceinline__ bool tc_staged_epilogue(const TcStageCfg c, const IO&
   named_barrier_sync(c.bar_base, 128);  // tile constants are in place
   bool ok = true;
   // split tiles: the other CTAs' partial sums, fetched one 16-column group ahead of their use
-  uint32_t part[16];
-  if (c.fix_count > 0) tc_load_partials<KIND>(c, 0, row, part);
+  uint32_t part[EXTRAS ? 16 : 1];
+  if (EXTRAS && c.fix_count > 0) tc_load_partials<KIND>(c, 0, row, reinterpret_cast<uint32_t (&)[16]>(part));
   for (int c0 = 0; c0 < c.block_n && n0 + c0 < c.N; c0 += cw) {
     const uint32_t stage0 = c.out_stage + static_cast<uint32_t>(out_slot) * out_tile_bytes;
     if (has_res) {
@@ -466,10 +522,10 @@ __device__ __forceinline__ bool tc_staged_epilogue(const TcStageCfg c, const IO&
       uint32_t v[16];
       tmem_ld16(t_row + static_cast<uint32_t>(c0 + 16 * h), v);
       tmem_ld_wait();
-      if (c.fix_count > 0) {
-        tc_add_partials<KIND>(v, part);
+      if (EXTRAS && c.fix_count > 0) {
+        tc_add_partials<KIND>(v, reinterpret_cast<uint32_t (&)[16]>(part));
         const int next = c0 + 16 * h + 16;
-        if (next < c.block_n) tc_load_partials<KIND>(c, next, row, part);
+        if (next < c.block_n) tc_load_partials<KIND>(c, next, row, reinterpret_cast<uint32_t (&)[16]>(part));
       }
       float r[16];
       if (c.res_mode == RES_BF16X2) {
@@ -536,6 +592,18 @@ __device__ __forceinline__ bool tc_staged_epilogue(const TcStageCfg c, const IO&
         }
       }
       tc_epilogue_values<KIND>(v, cb, cs, r, c.act, c.act_a, c.act_b, y);
+      if (!EXTRAS) {
+      } else if (c.side_count > 0 && c.side_stage != 0u) {
+        // staged: this row's 16 bytes of the current 64-column group, tile *side_slot of each copy
+        const uint32_t at = c.side_stage + static_cast<uint32_t>(*side_slot) * 8192u +
+                            stage_chunk_offset(row, ((c0 + 16 * h) >> 4) & 3);
+        tc_stage_side_quant(at, c.side_scale0, y);
+        if (c.side_count > 1) tc_stage_side_quant(at + 16384u, c.side_scale1, y);
+      } else if (c.side_count > 0 && row < c.side_rows && n0 + c0 + 16 * h < c.N) {
+        const long long at = static_cast<long long>(row) * c.side_ld + c0 + 16 * h;
+        tc_store_side_quant(c.side_q0 + at, c.side_scale0, y);
+        if (c.side_count > 1) tc_store_side_quant(c.side_q1 + at, c.side_scale1, y);
+      }
       if (c.out_mode == OUT_BF16X2) {
 #pragma unroll
         for (int jj = 0; jj < 2; ++jj) {
@@ -587,6 +655,11 @@ __device__ __forceinline__ bool tc_staged_epilogue(const TcStageCfg c, const IO&
       } else if (two_out) {
         io.store_out(1, stage0 + 8192u, n0 + c0);
       }
+      if (EXTRAS && c.side_count > 0 && c.side_stage != 0u && (((c0 + cw) & 63) == 0 || c0 + cw >= c.block_n || n0 + c0 + cw >= c.N)) {
+        const uint32_t src = c.side_stage + static_cast<uint32_t>(*side_slot) * 8192u;
+        io.store_side(0, src, n0 + (c0 & ~63));
+        if (c.side_count > 1) io.store_side(1, src + 16384u, n0 + (c0 & ~63));
+      }
       tma_store_commit();
       tma_store_wait_read(c.out_bufs >= 2 ? c.out_bufs - 2 : 0);
       const int c1 = c0 + cw;
@@ -595,6 +668,9 @@ __device__ __forceinline__ bool tc_staged_epilogue(const TcStageCfg c, const IO&
     // a single staging tile is written again only after its store has read it
     if (c.out_bufs == 1) named_barrier_sync(c.bar_base, 128);
     if (++out_slot >= c.out_bufs) out_slot = 0;
+    // the other tile of each int8 copy for the next 64-column group (every thread keeps the same count)
+    if (EXTRAS && c.side_count > 0 && c.side_stage != 0u && (((c0 + cw) & 63) == 0 || c0 + cw >= c.block_n || n0 + c0 + cw >= c.N))
+      *side_slot ^= 1;
   }
   return ok;
 }
@@ -603,15 +679,15 @@ __device__ __forceinline__ bool tc_staged_epilogue(const TcStageCfg c, const IO&
 // 64-byte staging row of int8 per accumulator row.  Dequantise, add the bias, requantise with
 // out_scale, clamp at zero for a fused ReLU (the order of the reference's int8 path), pack, and
 // store the [128][64] tile with one TMA store.
-template <int KIND, class IO>
+template <int KIND, class IO, bool EXTRAS = false>
 __device__ __forceinline__ void tc_staged_epilogue_i8(const TcStageCfg c, float out_scale, const IO& io,
                                                       uint32_t t_row, int n0, int row, bool leader,
                                                       const float* tile_bias, const float* tile_scale,
                                                       int& out_slot) {
   using namespace ptx;
   named_barrier_sync(c.bar_base, 128);  // tile constants are in place
-  uint32_t part[16];
-  if (c.fix_count > 0) tc_load_partials<KIND>(c, 0, row, part);
+  uint32_t part[EXTRAS ? 16 : 1];
+  if (EXTRAS && c.fix_count > 0) tc_load_partials<KIND>(c, 0, row, reinterpret_cast<uint32_t (&)[16]>(part));
   for (int c0 = 0; c0 < c.block_n && n0 + c0 < c.N; c0 += 64) {
     const uint32_t stage0 = c.out_stage + static_cast<uint32_t>(out_slot) * 8192u;
 #pragma unroll
@@ -619,10 +695,10 @@ __device__ __forceinline__ void tc_staged_epilogue_i8(const TcStageCfg c, float 
       uint32_t v[16];
       tmem_ld16(t_row + static_cast<uint32_t>(c0 + 16 * h), v);
       tmem_ld_wait();
-      if (c.fix_count > 0) {
-        tc_add_partials<KIND>(v, part);
+      if (EXTRAS && c.fix_count > 0) {
+        tc_add_partials<KIND>(v, reinterpret_cast<uint32_t (&)[16]>(part));
         const int next = c0 + 16 * h + 16;
-        if (next < c.block_n) tc_load_partials<KIND>(c, next, row, part);
+        if (next < c.block_n) tc_load_partials<KIND>(c, next, row, reinterpret_cast<uint32_t (&)[16]>(part));
       }
       uint32_t w[4];
 #pragma unroll
@@ -657,7 +733,9 @@ __device__ __forceinline__ void tc_staged_epilogue_i8(const TcStageCfg c, float 
   }
 }
 
-template <int KIND>
+// SIDE: the instantiation that also writes int8 copies of its fp32 result (TcGemmParams::side_q); kept out
+// of the plain kernel so that layers without such copies run exactly the code they ran before.
+template <int KIND, bool SIDE = false>
 __global__ void __launch_bounds__(kTcThreadsTwoEpi, 1)
 tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ CUtensorMap map_a0,
                const __grid_constant__ CUtensorMap map_a1,
@@ -666,7 +744,9 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
                const __grid_constant__ CUtensorMap map_o0,
                const __grid_constant__ CUtensorMap map_o1,
                const __grid_constant__ CUtensorMap map_r0,
-               const __grid_constant__ CUtensorMap map_r1) {
+               const __grid_constant__ CUtensorMap map_r1,
+               const __grid_constant__ CUtensorMap map_s0,
+               const __grid_constant__ CUtensorMap map_s1) {
   using namespace ptx;
   grid_dependency_trigger();  // the next kernel of the stream may begin its preamble
   constexpr int PLANES = tc_planes(KIND);
@@ -966,6 +1046,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
     uint32_t acc_ph = 0;
     uint32_t res_ph = 0;
     int out_slot = 0;
+    int side_slot = 0;
     bool ok = true;
     // a register copy: the helper below takes the struct by reference, and a reference to the
     // kernel parameter itself turns every field access into a generic load
@@ -1023,9 +1104,22 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
         cfg.block_n = e_block_n;
         cfg.wide = p.wide;
         cfg.bar_base = bar_base;
+        if (SIDE) {
+          cfg.side_count = p.side_count;
+          cfg.side_ld = p.side_ld;
+          cfg.side_rows = static_cast<int>(lp.M - m_half < kTcBlockM ? lp.M - m_half : kTcBlockM);
+          cfg.side_q0 = p.side_q0 != nullptr ? p.side_q0 + m_half * p.side_ld + n0 : nullptr;
+          cfg.side_q1 = p.side_q1 != nullptr ? p.side_q1 + m_half * p.side_ld + n0 : nullptr;
+          cfg.side_scale0 = p.side_scale0;
+          cfg.side_scale1 = p.side_scale1;
+        }
         const int m_first = static_cast<int>(m_half);
+        // staging tiles of the int8 copies sit behind this group's output tiles
+        cfg.side_stage = SIDE && p.side_staged ? cfg.out_stage + static_cast<uint32_t>(e_out_bufs) *
+                                                             ((p.wide || e_out_mode == OUT_F32_SPLIT) ? 16384u : 8192u)
+                                       : 0u;
         struct {
-          const CUtensorMap *o0, *o1, *r0, *r1;
+          const CUtensorMap *o0, *o1, *r0, *r1, *s0, *s1;
           int m_first;
           __device__ __forceinline__ void load_res(int plane, uint32_t dst, uint32_t bar, int col) const {
             ptx::tma_load_2d(dst, plane ? r1 : r0, bar, col, m_first);
@@ -1033,13 +1127,20 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
           __device__ __forceinline__ void store_out(int plane, uint32_t src, int col) const {
             ptx::tma_store_2d(plane ? o1 : o0, src, col, m_first);
           }
-        } io{&map_o0, &map_o1, &map_r0, &map_r1, m_first};
+          __device__ __forceinline__ void store_side(int copy, uint32_t src, int col) const {
+            ptx::tma_store_2d(copy ? s1 : s0, src, col, m_first);
+          }
+        } io{&map_o0, &map_o1, &map_r0, &map_r1, &map_s0, &map_s1, m_first};
         if (e_out_mode == OUT_I8) {
           tc_staged_epilogue_i8<KIND>(cfg, p.out_scale, io, t_row, n0, quarter * 32 + lane, leader, tile_bias,
                                       tile_scale, out_slot);
         } else {
-          ok = tc_staged_epilogue<KIND>(cfg, io, t_row, n0, quarter * 32 + lane, leader, tile_bias, tile_scale,
-                                        res_ph, out_slot, abort_ptr);
+          if (SIDE && p.side_count > 0)
+            ok = tc_staged_epilogue<KIND, decltype(io), true>(cfg, io, t_row, n0, quarter * 32 + lane, leader, tile_bias,
+                                                              tile_scale, res_ph, out_slot, abort_ptr, &side_slot);
+          else
+            ok = tc_staged_epilogue<KIND>(cfg, io, t_row, n0, quarter * 32 + lane, leader, tile_bias, tile_scale,
+                                          res_ph, out_slot, abort_ptr);
           if (!ok) break;
         }
       } else {
@@ -1050,7 +1151,8 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
           tmem_ld16(t_row + static_cast<uint32_t>(c0), v);
           tmem_ld_wait();
           if (m < lp.M && n0 + c0 < e_N) {
-            if (bf16_io) tc_epilogue_chunk<KIND, true>(lp, v, m, n0 + c0, tile_bias + c0, tile_scale + c0);
+            if (SIDE && lp.side_count > 0) tc_epilogue_chunk<KIND, true, true>(lp, v, m, n0 + c0, tile_bias + c0, tile_scale + c0);
+            else if (bf16_io) tc_epilogue_chunk<KIND, true>(lp, v, m, n0 + c0, tile_bias + c0, tile_scale + c0);
             else tc_epilogue_chunk<KIND, false>(lp, v, m, n0 + c0, tile_bias + c0, tile_scale + c0);
           }
         }

@@ -26,6 +26,8 @@ struct TcLaunch {
   alignas(64) CUtensorMap map_o1{};
   alignas(64) CUtensorMap map_r0{};  // residual planes
   alignas(64) CUtensorMap map_r1{};
+  alignas(64) CUtensorMap map_s0{};  // int8 copies of the result (TcEpilogue::side_q)
+  alignas(64) CUtensorMap map_s1{};
   int kind = GEMM_TF32;
   int grid = 0;
   int smem_bytes = 0;
@@ -63,6 +65,10 @@ struct TcEpilogue {
   float out_scale = 1.0f;
   int* status = nullptr;
   long long* trace = nullptr;
+  // int8 copies of an fp32 result, quantised with side_scale[i] (out_mode OUT_F32, channels a multiple of 16)
+  int side_count = 0;
+  int8_t* side_q[2] = {nullptr, nullptr};
+  float side_scale[2] = {0.0f, 0.0f};
   // workspace for tiles split between CTA pairs (tc_gemm2.cuh): partial accumulators and one flag
   // word per CTA, zero before the first launch; without it tiles are never split
   uint32_t* sk_ws = nullptr;

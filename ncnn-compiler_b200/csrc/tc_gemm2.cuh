@@ -513,6 +513,13 @@ tc_gemm2_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ 
           }
         }
         if (m_first < p.M) {
+          cfg.side_count = p.side_count;
+          cfg.side_ld = p.side_ld;
+          cfg.side_rows = static_cast<int>(p.M - m_first < kTcBlockM ? p.M - m_first : kTcBlockM);
+          cfg.side_q0 = p.side_q0 != nullptr ? p.side_q0 + m_first * p.side_ld + n0 : nullptr;
+          cfg.side_q1 = p.side_q1 != nullptr ? p.side_q1 + m_first * p.side_ld + n0 : nullptr;
+          cfg.side_scale0 = p.side_scale0;
+          cfg.side_scale1 = p.side_scale1;
           cfg.fix_count = row_valid ? fix : 0;  // (a row past the end skips the loads; its results are clipped)
           cfg.fix_ws = fix > 0 ? p.sk_ws + static_cast<size_t>(static_cast<int>(blockIdx.x) - CTAS) * slot_words + ws_group
                                : nullptr;
@@ -533,12 +540,22 @@ tc_gemm2_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ 
             __device__ __forceinline__ void store_out(int plane, uint32_t src, int col) const {
               ptx::tma_store_2d(plane ? o1 : o0, src, col, m_first);
             }
+            __device__ __forceinline__ void store_side(int, uint32_t, int) const {}
           } io{&map_o0, &map_o1, &map_r0, &map_r1, m_row};
+          const bool extras = fix > 0 || p.side_count > 0;
           if (p.out_mode == OUT_I8) {
-            tc_staged_epilogue_i8<KIND>(cfg, p.out_scale, io, t_row, n0, row, leader, my_bias, my_scale, out_slot);
+            if (extras)
+              tc_staged_epilogue_i8<KIND, decltype(io), true>(cfg, p.out_scale, io, t_row, n0, row, leader, my_bias, my_scale,
+                                                              out_slot);
+            else
+              tc_staged_epilogue_i8<KIND>(cfg, p.out_scale, io, t_row, n0, row, leader, my_bias, my_scale, out_slot);
           } else {
-            ok = tc_staged_epilogue<KIND>(cfg, io, t_row, n0, row, leader, my_bias, my_scale, res_ph, out_slot,
-                                          abort_ptr);
+            if (extras)
+              ok = tc_staged_epilogue<KIND, decltype(io), true>(cfg, io, t_row, n0, row, leader, my_bias, my_scale, res_ph,
+                                                                out_slot, abort_ptr);
+            else
+              ok = tc_staged_epilogue<KIND>(cfg, io, t_row, n0, row, leader, my_bias, my_scale, res_ph, out_slot,
+                                            abort_ptr);
             if (!ok) break;
           }
         }

@@ -275,6 +275,7 @@ tc_stem_kernel(const __grid_constant__ TcStemParams p, const __grid_constant__ C
           __device__ __forceinline__ void store_out(int plane, uint32_t src, int col) const {
             ptx::tma_store_2d(plane ? o1 : o0, src, col, m_first);
           }
+          __device__ __forceinline__ void store_side(int, uint32_t, int) const {}
         } io{&map_o0, &map_o1, tile * p.OW};
         if (KIND == GEMM_I8 && p.out_mode == OUT_I8) {
           tc_staged_epilogue_i8<KIND>(cfg, p.out_scale, io, t_row, 0, quarter * 32 + lane, leader, tile_bias, tile_scale,
