@@ -2134,10 +2134,11 @@ static cudaError_t launch_ok() { return cudaGetLastError(); }
 // networks (batch 64, 3x3 filters at 56/28/14 pixels) it ties with the im2col kernel once the
 // operands are bf16 pairs, and loses a little where its 16x8 tiles overhang the image, so it
 // is opt-in: NCNN_B200_HALO=1 at load time selects it wherever it applies.
-static bool halo_preferred() {
+static int halo_level() {
   const char* f = std::getenv("NCNN_B200_HALO");
-  return f != nullptr && f[0] == '1';
+  return f == nullptr || f[0] == 0 ? 0 : std::atoi(f);
 }
+static bool halo_preferred() { return halo_level() >= 1; }
 
 bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string* err) {
   const Tensor& to = tensors_[resolve(node.out)];
@@ -2250,8 +2251,8 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
         hc.w1 = node.d_w1;
         hc.out_channels = node.O;
         auto hl = std::make_shared<TcHaloLaunch>();
-        if (tc_plan_conv_halo(hl.get(), kind, hc, te, sm_count_).empty()) {
-          s.kernel = std::string("tc_conv_halo_kernel<") + kind_name + ">";
+        if (tc_plan_conv_halo(hl.get(), kind, hc, te, sm_count_, halo_level() >= 2).empty()) {
+          s.kernel = std::string(hl->pair ? "tc_conv_halo_kernel:pairs<" : "tc_conv_halo_kernel<") + kind_name + ">";
           s.run = [hl](cudaStream_t st) { return tc_launch_halo(*hl, st); };
           plan.steps.push_back(std::move(s));
           return true;

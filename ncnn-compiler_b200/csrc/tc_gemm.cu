@@ -896,7 +896,8 @@ bool tc_halo_applies(int kind, int C, int KH, int KW, int stride_h, int stride_w
   return static_cast<double>(OH) * OW / covered >= 0.70;
 }
 
-std::string tc_plan_conv_halo(TcHaloLaunch* L, int kind, const TcHaloConv& c, const TcEpilogue& e, int sm_count) {
+std::string tc_plan_conv_halo(TcHaloLaunch* L, int kind, const TcHaloConv& c, const TcEpilogue& e, int sm_count,
+                              bool pair) {
   load_driver_entry_points();
   if (!g_driver_error.empty()) return g_driver_error;
   TcHaloParams& p = L->p;
@@ -917,8 +918,15 @@ std::string tc_plan_conv_halo(TcHaloLaunch* L, int kind, const TcHaloConv& c, co
   p.tiles_x = (c.OW + kHaloTileW - 1) / kHaloTileW;
   // an MMA of any N <= 128 costs the same issue time: take the widest tile
   const int step = wide ? 32 : 16;
-  p.block_n = c.out_channels >= 128 ? 128 : (c.out_channels + step - 1) / step * step;
+  const int widest = pair ? 256 : 128;  // a pair's CTA holds half of the weight rows of a tap
+  {
+    const int n_tiles = (c.out_channels + widest - 1) / widest;
+    p.block_n = ((c.out_channels + n_tiles - 1) / n_tiles + step - 1) / step * step;
+  }
   p.tiles_n = (c.out_channels + p.block_n - 1) / p.block_n;
+  const int ctas = pair ? 2 : 1;
+  L->pair = pair ? 1 : 0;
+  if (pair && (p.block_n / 2) % 8 != 0) return "a pair's half of the weight tile must be whole 8-row groups";
   p.k_elems = 128 / tc_elem_bytes(kind);
   p.c_blocks = c.C / p.k_elems;
   p.taps = c.KH * c.KW;
@@ -928,7 +936,7 @@ std::string tc_plan_conv_halo(TcHaloLaunch* L, int kind, const TcHaloConv& c, co
   p.patch_h = kHaloTileH + c.KH - 1;
   p.patch_w = kHaloTileW + c.KW - 1;
   p.patch_bytes = (p.patch_h * p.patch_w * 128 + 1023) / 1024 * 1024;
-  p.b_bytes = (p.block_n * 128 + 1023) / 1024 * 1024;
+  p.b_bytes = ((p.block_n / ctas) * 128 + 1023) / 1024 * 1024;
   p.bias = e.bias;
   p.res_mode = res_mode;
   p.out_mode = e.out_mode;
@@ -936,6 +944,7 @@ std::string tc_plan_conv_halo(TcHaloLaunch* L, int kind, const TcHaloConv& c, co
   p.act_a = e.act_a;
   p.act_b = e.act_b;
   p.status = e.status;
+  p.trace = e.trace;
   const int out_tile = (e.out_mode == OUT_F32_SPLIT || wide ? 2 : 1) * 8192;
   const int fixed = 2 * planes * p.patch_bytes + (res_mode != RES_NONE ? 16384 : 0);
   p.out_bufs = 4;
@@ -949,9 +958,10 @@ std::string tc_plan_conv_halo(TcHaloLaunch* L, int kind, const TcHaloConv& c, co
   if (p.stages < 2) return "shared memory cannot hold the patch buffers and two weight stages";
   L->smem_bytes = fixed + p.out_bufs * out_tile + p.stages * planes * p.b_bytes + 1024;
   L->smem_bytes = std::max(L->smem_bytes, 120 * 1024);
-  const long long tiles = static_cast<long long>(c.images) * p.tiles_y * p.tiles_x * p.tiles_n;
-  if (tiles > 0x7fffffffll) return "too many tiles for one launch";
-  L->grid = static_cast<int>(std::min<long long>(tiles, sm_count));
+  const long long pixel_tiles = static_cast<long long>(c.images) * p.tiles_y * p.tiles_x;
+  const long long tiles = ((pixel_tiles + ctas - 1) / ctas) * p.tiles_n;
+  if (pixel_tiles * p.tiles_n > 0x7fffffffll) return "too many tiles for one launch";
+  L->grid = ctas * static_cast<int>(std::min<long long>(tiles, sm_count / ctas));
   L->kind = kind;
 
   std::string err = encode_tiled_4d(&L->map_a0, a_bf16, c.in0, c.C, c.W, c.H, c.images, p.k_elems, p.patch_w,
@@ -962,10 +972,10 @@ std::string tc_plan_conv_halo(TcHaloLaunch* L, int kind, const TcHaloConv& c, co
   if (!err.empty()) return err;
   const uint64_t k_total = static_cast<uint64_t>(p.taps) * p.c_blocks * p.k_elems;
   err = encode_tiled_2d(&L->map_b0, kind, c.w0, k_total, c.out_channels, k_total * tc_elem_bytes(kind), p.k_elems,
-                        p.block_n, 128);
+                        p.block_n / ctas, 128);
   if (err.empty() && planes == 2)
     err = encode_tiled_2d(&L->map_b1, kind, c.w1, k_total, c.out_channels, k_total * tc_elem_bytes(kind), p.k_elems,
-                          p.block_n, 128);
+                          p.block_n / ctas, 128);
   if (!err.empty()) return err;
   // outputs and residuals: [image][OH][OW][N], tiles of 64 bytes of channels x 8 x 16 pixels, 64-byte swizzle
   auto plane = [&](CUtensorMap* map, const void* base, bool bf16) {
@@ -991,21 +1001,34 @@ cudaError_t tc_launch_halo(const TcHaloLaunch& L, cudaStream_t stream) {
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(tc_conv_halo_kernel<GEMM_BF16X3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                max_smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(tc_conv_halo_kernel<GEMM_TF32, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               max_smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(tc_conv_halo_kernel<GEMM_TF32X3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               max_smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(tc_conv_halo_kernel<GEMM_BF16X3, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               max_smem);
     return e;
   });
   if (attr_err != cudaSuccess) return attr_err;
-  KernelLaunchConfig lc(L.grid, kHaloThreads, L.smem_bytes, false, stream);
+  KernelLaunchConfig lc(L.grid, kHaloThreads, L.smem_bytes, L.pair != 0, stream);
   cudaError_t e;
+#define NB_LAUNCH_HALO(KIND, PAIRED)                                                                             \
+  e = cudaLaunchKernelEx(&lc.cfg, tc_conv_halo_kernel<KIND, PAIRED>, L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, \
+                         L.map_o0, L.map_o1, L.map_r0, L.map_r1)
   if (L.kind == GEMM_BF16X3) {
-    e = cudaLaunchKernelEx(&lc.cfg, tc_conv_halo_kernel<GEMM_BF16X3>, L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
-                           L.map_o1, L.map_r0, L.map_r1);
+    if (L.pair) NB_LAUNCH_HALO(GEMM_BF16X3, true);
+    else NB_LAUNCH_HALO(GEMM_BF16X3, false);
   } else if (L.kind == GEMM_TF32X3) {
-    e = cudaLaunchKernelEx(&lc.cfg, tc_conv_halo_kernel<GEMM_TF32X3>, L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
-                           L.map_o1, L.map_r0, L.map_r1);
+    if (L.pair) NB_LAUNCH_HALO(GEMM_TF32X3, true);
+    else NB_LAUNCH_HALO(GEMM_TF32X3, false);
   } else {
-    e = cudaLaunchKernelEx(&lc.cfg, tc_conv_halo_kernel<GEMM_TF32>, L.p, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0,
-                           L.map_o1, L.map_r0, L.map_r1);
+    if (L.pair) NB_LAUNCH_HALO(GEMM_TF32, true);
+    else NB_LAUNCH_HALO(GEMM_TF32, false);
   }
+#undef NB_LAUNCH_HALO
   return e != cudaSuccess ? e : cudaGetLastError();
 }
 

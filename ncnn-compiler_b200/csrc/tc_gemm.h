@@ -131,6 +131,7 @@ struct TcHaloLaunch {
   int kind = GEMM_TF32;
   int grid = 0;
   int smem_bytes = 0;
+  int pair = 0;  // 1: two pixel tiles per cluster of two CTAs (grid counts CTAs)
 };
 
 struct TcHaloConv {
@@ -147,8 +148,9 @@ struct TcHaloConv {
 // dilation 1, channels in blocks of 32, output rows of 16 bytes, tiles mostly inside the image.
 bool tc_halo_applies(int kind, int C, int KH, int KW, int stride_h, int stride_w, int dil_h, int dil_w, int OH,
                      int OW, int out_channels, int out_mode);
+// `pair`: plan the form that runs two pixel tiles on a cluster of two CTAs (tiles up to 256 channels wide)
 std::string tc_plan_conv_halo(TcHaloLaunch* launch, int kind, const TcHaloConv& conv, const TcEpilogue& epilogue,
-                              int sm_count);
+                              int sm_count, bool pair = false);
 cudaError_t tc_launch_halo(const TcHaloLaunch& launch, cudaStream_t stream);
 
 // ---- stem convolution with the input rows resident in shared memory (tc_stem.cuh)

@@ -295,3 +295,27 @@ def test_quantize_steps_fold_into_their_producers(pkg, oracle, tmp_path, monkeyp
     assert np.array_equal(results["1"], results["0"]) and np.array_equal(results["2"], results["0"])
     want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x[:2]])
     assert np.array_equal(results["1"][:2], want)
+
+
+# ------------------------------------------------------------------ patch-resident convolution on CTA pairs
+@pytest.mark.parametrize("h,c,cout,n", [(56, 64, 96, 4), (28, 128, 128, 5), (14, 256, 256, 7), (40, 64, 64, 3)])
+def test_patch_resident_pairs_match_the_im2col_kernel(pkg, oracle, tmp_path, monkeypatch, h, c, cout, n):
+    """NCNN_B200_HALO=2: 3x3 stride-1 convolutions keep each tile's input patch in shared memory (loaded once per
+    channel block, every tap reads it through a shifted descriptor) and run two pixel tiles per cluster of two
+    CTAs that share each tap's weights.  Same products per output as the im2col kernel; sums may round
+    differently (the channel blocks are the outer loop), so: rel-L2 <= 3e-5 against it, <= 1e-4 against the
+    oracle, and the same bits from run to run.  Odd tile counts (a pair whose second tile does not exist) and
+    images that the 8x16 tiles overhang are part of the cases."""
+    param, bin_ = pkg.zoo.residual_block(str(tmp_path / "rb"), h=h, w=h, c=c, cout=cout)
+    x = np.random.default_rng(h + n).uniform(-1, 1, (n, c, h, h)).astype(np.float32)
+    monkeypatch.setenv("NCNN_B200_HALO", "2")
+    got, kernels = _run(pkg, param, bin_, x)
+    assert any(k.startswith("tc_conv_halo_kernel:pairs<") for k in kernels), kernels
+    again, _ = _run(pkg, param, bin_, x)
+    assert np.array_equal(got, again)
+    monkeypatch.setenv("NCNN_B200_HALO", "0")
+    base, kernels = _run(pkg, param, bin_, x)
+    assert not any(k.startswith("tc_conv_halo_kernel") for k in kernels), kernels
+    assert rel_l2(got, base) <= 3e-5
+    want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x[:2]])
+    assert rel_l2(got[:2], want) <= 1e-4
