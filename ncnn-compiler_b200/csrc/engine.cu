@@ -91,6 +91,15 @@ struct Node {
   float* d_offset = nullptr;
   int k_elems = 0;
   double flops = 0.0;  // per image
+  // N_CONV (1x1, tensor cores) that also computes the 3x3 depthwise layer in front of it (tc_dw_project.cuh):
+  // in[0] is then the depthwise layer's input, these are its parameters
+  bool dw_fused = false;
+  const float* dw_w = nullptr;  // [9][C]
+  const float* dw_bias = nullptr;
+  int dw_act = ACT_NONE;
+  float dw_act_a = 0.0f, dw_act_b = 0.0f;
+  int dw_pt = 1, dw_pl = 1;
+  std::string dw_name;
 };
 
 struct Step {
@@ -219,6 +228,7 @@ class EngineImpl {
   void choose_head_limit();
   void fold_channel_concats();
   void fuse_quantize_steps();
+  void fuse_depthwise_projection();
   int profile(int64_t n, int repeat, std::vector<LayerTiming>* out);
   Plan* plan_for(int64_t n);
 
@@ -1719,6 +1729,66 @@ void EngineImpl::fuse_quantize_steps() {
   }
 }
 
+// A stride-1 3x3 depthwise layer whose only consumer is a 1x1 tensor-core convolution (the second half of
+// an inverted-residual block) runs inside that convolution's kernel: its result goes from the CUDA cores
+// into the shared-memory operand tile of the MMAs and never to HBM.  The values, their bf16 split and the
+// order of the products are those of the two separate layers.  NCNN_B200_FUSE_DW=0 keeps them apart.
+void EngineImpl::fuse_depthwise_projection() {
+  const char* env = std::getenv("NCNN_B200_FUSE_DW");
+  if (env != nullptr && env[0] == '0') return;
+  if (opt_.accuracy_mode != kAccuracyFp32Split) return;
+  std::vector<int> uses(tensors_.size(), 0);
+  for (const Node& n : nodes_) {
+    for (int t : n.in) ++uses[resolve(t)];
+    if (n.res >= 0) ++uses[resolve(n.res)];
+    for (const auto& side : n.side_q) (void)side;
+  }
+  for (int o : outputs_) ++uses[resolve(o)];
+  for (size_t k = 0; k + 1 < nodes_.size(); ++k) {
+    const Node& dw = nodes_[k];
+    if (dw.kind != N_DW || dw.term != 0 || dw.KH != 3 || dw.KW != 3 || dw.sh != 1 || dw.sw != 1 || dw.dh != 1 ||
+        dw.dw != 1 || dw.res >= 0 || !dw.side_q.empty() || dw.d_w0 == nullptr)
+      continue;
+    const int mid = resolve(dw.out);
+    const int src = resolve(dw.in[0]);
+    const Tensor& tin = tensors_[src];
+    const Tensor& tmid = tensors_[mid];
+    if (uses[mid] != 1 || tin.rank != 3 || tin.fmt != FMT_F32 || tin.Cp != tin.c || tin.Wp != tin.w || tin.w_off != 0 ||
+        tmid.fmt != FMT_BF16X2 || dw.OH != tin.h || dw.OW != tin.w || dw.pt > 2 || dw.pl > 2)
+      continue;
+    // the consumer: the next node that reads the depthwise result
+    size_t j = k + 1;
+    for (; j < nodes_.size(); ++j)
+      if (!nodes_[j].in.empty() && resolve(nodes_[j].in[0]) == mid) break;
+    if (j >= nodes_.size()) continue;
+    Node& pw = nodes_[j];
+    if (pw.kind != N_CONV || pw.impl != IMPL_TC || pw.term != 0 || pw.stem || pw.out_ld != 0 || pw.KH != 1 || pw.KW != 1 ||
+        pw.sh != 1 || pw.sw != 1 || pw.pt != 0 || pw.pl != 0 || !pw.side_q.empty() || pw.d_w0 == nullptr || pw.d_w1 == nullptr)
+      continue;
+    const Tensor& tout = tensors_[resolve(pw.out)];
+    const int out_mode = tout.fmt == FMT_BF16X2 ? OUT_BF16X2 : (tout.fmt == FMT_F32 ? OUT_F32 : -1);
+    if (out_mode < 0) continue;
+    const bool has_res = pw.res >= 0;
+    const bool res_bf16 = has_res && tensors_[resolve(pw.res)].fmt == FMT_BF16X2;
+    if (has_res && !res_bf16 && tensors_[resolve(pw.res)].fmt != FMT_F32) continue;
+    if (dw.act != ACT_NONE && dw.act != ACT_RELU && dw.act != ACT_CLIP) continue;  // the fused kernel clamps, nothing else
+    if (!tc_dw_project_applies(tin.c, pw.O, tin.h, tin.w, out_mode, has_res, res_bf16)) continue;
+    pw.dw_fused = true;
+    pw.dw_w = static_cast<const float*>(dw.d_w0);
+    pw.dw_bias = dw.d_bias;
+    pw.dw_act = dw.act;
+    pw.dw_act_a = dw.act_a;
+    pw.dw_act_b = dw.act_b;
+    pw.dw_pt = dw.pt;
+    pw.dw_pl = dw.pl;
+    pw.dw_name = dw.name;
+    pw.in[0] = dw.in[0];
+    pw.flops += dw.flops;
+    nodes_.erase(nodes_.begin() + k);
+    --k;
+  }
+}
+
 bool EngineImpl::prepare_weights(std::string* err) {
   const int f32_kind = opt_.accuracy_mode == kAccuracyTf32 ? GEMM_TF32 : GEMM_TF32X3;
   // insert Quantize steps in front of int8 contractions whose input is fp32
@@ -2109,6 +2179,7 @@ bool EngineImpl::build(const std::string& param, const std::string& bin, const E
   fold_channel_concats();
   if (opt.plan_only) return true;
   if (!prepare_weights(err)) return false;
+  fuse_depthwise_projection();
   choose_head_limit();
   plan_memory();
   if (cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking) != cudaSuccess) return fail(err, "cannot create a stream");
@@ -2229,6 +2300,32 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
       const char* kind_name = kind == GEMM_I8 ? "i8" : (kind == GEMM_TF32 ? "tf32" : (kind == GEMM_BF16X3 ? "bf16x3" : "tf32x3"));
       auto launch = std::make_shared<TcLaunch>();
       std::string perr;
+      if (node.dw_fused) {
+        TcDwProjConv dc;
+        dc.x = in.p0;
+        dc.images = static_cast<int>(n);
+        dc.H = ti.h;
+        dc.W = ti.w;
+        dc.C = ti.c;
+        dc.pad_t = node.dw_pt;
+        dc.pad_l = node.dw_pl;
+        dc.dw_weights = node.dw_w;
+        dc.dw_bias = node.dw_bias;
+        dc.dw_act = node.dw_act;
+        dc.dw_act_a = node.dw_act_a;
+        dc.dw_act_b = node.dw_act_b;
+        dc.w0 = node.d_w0;
+        dc.w1 = node.d_w1;
+        dc.out_channels = node.O;
+        auto dl = std::make_shared<TcDwProjLaunch>();
+        const std::string derr = tc_plan_dw_project(dl.get(), dc, te, sm_count_);
+        if (!derr.empty()) return fail(err, "layers " + node.dw_name + " + " + node.name + ": " + derr);
+        s.name = node.dw_name + "+" + node.name;
+        s.kernel = "tc_dw_project_kernel<bf16x3>";
+        s.run = [dl](cudaStream_t st) { return tc_launch_dw_project(*dl, st); };
+        plan.steps.push_back(std::move(s));
+        return true;
+      }
       // stride-1 filters with spatial extent: the patch-resident kernel loads each input pixel
       // once per tile instead of once per tap
       if (node.kind == N_CONV && !i8 && !node.stem && node.out_ld == 0 && halo_preferred() &&

@@ -1,0 +1,443 @@
+// 3x3 depthwise convolution fused into the 1x1 convolution that follows it (the second half of an
+// inverted-residual block: ConvolutionDepthWise + activation, then a pointwise "projection").
+//
+// Run one after the other, the depthwise layer writes its result to HBM and the projection reads it
+// back: two passes over the widest tensor of the block, on layers that are bound by HBM either way.
+// Here the depthwise result never leaves the SM.  A tile is a 16 x 8 rectangle of output pixels of one
+// image (128 rows of the projection's GEMM); per block of 32 channels
+//   * TMA loads the (16+2) x (8+2) fp32 input patch once (coordinates outside the image read as zero:
+//     that is the padding),
+//   * eight CUDA-core warps compute the 128 x 32 depthwise results from it with the arithmetic of the
+//     stand-alone kernel (bias, nine fmaf in filter order, activation), split each value into its bf16
+//     pair (hi = bf16(x), mid = bf16(x - hi)) and write both planes straight into the K-major,
+//     64-byte-swizzled operand tile that tcgen05.mma reads,
+//   * one thread issues the projection's MMAs (mid*hi + hi*mid + hi*hi, as tc_gemm_kernel does) against
+//     that channel block's weights, which TMA streams through a small ring,
+// and the usual epilogue warps drain the accumulator (bias, residual, activation, TMA stores).
+// Operands, their order and the accumulation are those of the two separate kernels, so the results are
+// the same bits.
+//
+// Warps (448 threads): 0 TMA producer, 1 MMA issuer, 2-5 epilogue, 6-13 depthwise.  Every wait is
+// bounded and ends in the status word.
+#pragma once
+
+#include "tc_gemm.cuh"
+
+namespace nb {
+
+constexpr int kDwpThreads = 448;
+constexpr int kDwpTileH = 16, kDwpTileW = 8;
+constexpr int kDwpChannels = 32;                                  // channels per block: 64-byte bf16 rows
+constexpr int kDwpPatchH = kDwpTileH + 2, kDwpPatchW = kDwpTileW + 2;
+constexpr int kDwpPatchBytes = (kDwpPatchH * kDwpPatchW * kDwpChannels * 4 + 1023) / 1024 * 1024;
+constexpr int kDwpAPlaneBytes = kTcBlockM * 64;                   // one bf16 plane of the operand tile
+constexpr int kDwpMaxStages = 4;
+
+struct TcDwProjParams {
+  int images, H, W, C;  // depthwise input = output extent (stride 1), channels
+  int N;                // projection output channels
+  int tiles_y, tiles_x, tiles_n, block_n;
+  int c_blocks;         // blocks of 32 channels (the last one may be partly past C: zero-filled)
+  int pad_t, pad_l;
+  int stages;           // weight ring depth
+  int b_bytes;          // one plane of a weight stage, rounded to 1 KB
+  int out_bufs;
+  const float* dw_weights;  // [9][C], tap-major
+  const float* dw_bias;     // [C] or null
+  int dw_act;
+  float dw_act_a, dw_act_b;
+  const float* bias;        // projection bias [N] or null
+  int res_mode, out_mode, act;
+  float act_a, act_b;
+  int* status;
+  long long* trace;
+};
+
+// (KIND: the projection's arithmetic; bf16 pairs are the only form built)
+template <int KIND>
+__global__ void __launch_bounds__(kDwpThreads, 1)
+tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_constant__ CUtensorMap map_x,
+                     const __grid_constant__ CUtensorMap map_b0, const __grid_constant__ CUtensorMap map_b1,
+                     const __grid_constant__ CUtensorMap map_o0, const __grid_constant__ CUtensorMap map_o1,
+                     const __grid_constant__ CUtensorMap map_r0, const __grid_constant__ CUtensorMap map_r1) {
+  using namespace ptx;
+  grid_dependency_trigger();  // the next kernel of the stream may begin its preamble
+
+  extern __shared__ uint8_t dwp_smem_raw[];
+  __shared__ __align__(8) uint64_t patch_full[2], patch_empty[2];
+  __shared__ __align__(8) uint64_t a_full[2], a_empty[2];
+  __shared__ __align__(8) uint64_t b_full[kDwpMaxStages], b_empty[kDwpMaxStages];
+  __shared__ __align__(8) uint64_t tfull_bar[2], tempty_bar[2];
+  __shared__ __align__(8) uint64_t res_bar;
+  __shared__ __align__(16) float tile_bias[256];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(dwp_smem_raw) + 1023u) & ~1023u;
+  const uint32_t patch_base = smem_base;                                  // two fp32 patches
+  const uint32_t a_base = patch_base + 2u * kDwpPatchBytes;               // two operand tiles (hi, mid planes)
+  const uint32_t a_stage_bytes = 2u * kDwpAPlaneBytes;
+  const uint32_t b_base = a_base + 2u * a_stage_bytes;                    // weight ring (hi, mid planes)
+  const uint32_t b_bytes = static_cast<uint32_t>(p.b_bytes);
+  const uint32_t b_stage_bytes = 2u * b_bytes;
+  const int S = p.stages;
+  const uint32_t res_stage = b_base + static_cast<uint32_t>(S) * b_stage_bytes;
+  const uint32_t out_stage = res_stage + (p.res_mode != RES_NONE ? 16384u : 0u);
+  const int tiles_per_image = p.tiles_y * p.tiles_x;
+  const int total_tiles = p.images * tiles_per_image * p.tiles_n;
+  volatile int* abort_ptr = &abort_flag;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&patch_full[i]), 1);
+      mbar_init(smem_u32(&patch_empty[i]), 8);  // one arrival per depthwise warp
+      mbar_init(smem_u32(&a_full[i]), 8);
+      mbar_init(smem_u32(&a_empty[i]), 1);
+      mbar_init(smem_u32(&tfull_bar[i]), 1);
+      mbar_init(smem_u32(&tempty_bar[i]), 4);
+    }
+    for (int i = 0; i < S; ++i) {
+      mbar_init(smem_u32(&b_full[i]), 1);
+      mbar_init(smem_u32(&b_empty[i]), 1);
+    }
+    mbar_init(smem_u32(&res_bar), 1);
+    fence_mbar_init();
+    prefetch_tensormap(&map_x);
+    prefetch_tensormap(&map_b0);
+    prefetch_tensormap(&map_b1);
+    prefetch_tensormap(&map_o0);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_slot), kTcTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = tmem_slot;
+  grid_dependency_wait();
+
+  // channel blocks of one pixel tile are neighbours, so CTAs working side by side share the patch in L2
+  auto decode = [&](int tile, int* img, int* oy0, int* ox0, int* n0) {
+    const int n_blk = tile % p.tiles_n;
+    int t = tile / p.tiles_n;
+    const int tx = t % p.tiles_x;
+    t /= p.tiles_x;
+    const int ty = t % p.tiles_y;
+    *img = t / p.tiles_y;
+    *oy0 = ty * kDwpTileH;
+    *ox0 = tx * kDwpTileW;
+    *n0 = n_blk * p.block_n;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer
+    // lane 0: the fp32 patch of a channel block; lanes 1, 2: the two planes of that block's weights
+    const uint32_t patch_tx = static_cast<uint32_t>(kDwpPatchH * kDwpPatchW * kDwpChannels * 4);
+    const uint32_t b_tx = 2u * static_cast<uint32_t>(p.block_n) * 64u;
+    int s = 0, pb = 0;
+    uint32_t ph = 0, p_ph = 0;
+    long long patches = 0, weights = 0, pw = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      int img, oy0, ox0, n0;
+      decode(tile, &img, &oy0, &ox0, &n0);
+      for (int cb = 0; cb < p.c_blocks && ok; ++cb) {
+        int w = 1;
+        const long long g0 = clock64();
+        if (lane == 0) {
+          w = mbar_wait_bounded(smem_u32(&patch_empty[pb]), p_ph ^ 1u, abort_ptr, kTcWaitLimitNs) ? 1 : 0;
+          if (w) {
+            mbar_arrive_expect_tx(smem_u32(&patch_full[pb]), patch_tx);
+            tma_load_4d(patch_base + static_cast<uint32_t>(pb) * kDwpPatchBytes, &map_x, smem_u32(&patch_full[pb]),
+                        cb * kDwpChannels, ox0 - p.pad_l, oy0 - p.pad_t, img);
+          }
+        }
+        w = __shfl_sync(0xffffffffu, w, 0);
+        if (!w) {
+          ok = false;
+          break;
+        }
+        ++patches;
+        pw += clock64() - g0;
+        pb ^= 1;
+        if (pb == 0) p_ph ^= 1u;
+        if (lane == 0) {
+          w = mbar_wait_bounded(smem_u32(&b_empty[s]), ph ^ 1u, abort_ptr, kTcWaitLimitNs) ? 1 : 0;
+          if (w) mbar_arrive_expect_tx(smem_u32(&b_full[s]), b_tx);
+        }
+        w = __shfl_sync(0xffffffffu, w, 0);
+        if (!w) {
+          ok = false;
+          break;
+        }
+        if (lane == 1 || lane == 2)
+          tma_load_2d(b_base + static_cast<uint32_t>(s) * b_stage_bytes + (lane - 1) * b_bytes,
+                      lane == 1 ? &map_b0 : &map_b1, smem_u32(&b_full[s]), cb * kDwpChannels, n0);
+        ++weights;
+        if (++s == S) {
+          s = 0;
+          ph ^= 1u;
+        }
+      }
+    }
+    if (lane == 0 && p.trace != nullptr && blockIdx.x == gridDim.x / 2) p.trace[8] = pw;
+    if (lane == 0) {
+      if (!ok) {
+        if (atomicCAS(const_cast<int*>(abort_ptr), 0, 1) == 0) atomicCAS(p.status, 0, TC_TIMEOUT_PRODUCER);
+      }
+      if (*abort_ptr != 0) {
+        // copies issued by this warp may still be landing: wait (bounded) for the last ones
+        int zero = 0;
+        for (long long i = weights > S ? weights - S : 0; i < weights; ++i)
+          mbar_wait_bounded(smem_u32(&b_full[i % S]), static_cast<uint32_t>((i / S) & 1), &zero, 200000000ull);
+        for (long long i = patches > 2 ? patches - 2 : 0; i < patches; ++i)
+          mbar_wait_bounded(smem_u32(&patch_full[i % 2]), static_cast<uint32_t>((i / 2) & 1), &zero, 200000000ull);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc(1u, 1u, kTcBlockM, static_cast<uint32_t>(p.block_n));
+      const uint64_t fixed = smem_desc_kmajor(0u, 64u);  // 64-byte rows, 64-byte swizzle
+      const uint64_t a_plane_units = kDwpAPlaneBytes >> 4;
+      const uint64_t b_units = b_bytes >> 4;
+      const uint32_t acc_stride = p.block_n > 128 ? 256u : 128u;
+      const int c_blocks = p.c_blocks;
+      int s = 0, as = 0, acc = 0;
+      uint32_t ph = 0, a_ph = 0, acc_ph = 0;
+      bool ok = true;
+      const bool tr = p.trace != nullptr && blockIdx.x == gridDim.x / 2;
+      long long m0 = 0, m1 = 0, m2 = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const long long q0 = clock64();
+        if (!mbar_wait_bounded(smem_u32(&tempty_bar[acc]), acc_ph ^ 1u, abort_ptr, kTcWaitLimitNs)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        m0 += clock64() - q0;
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * acc_stride;
+        uint32_t accumulate = 0u;
+        for (int cb = 0; cb < c_blocks; ++cb) {
+          const long long q1 = clock64();
+          if (!mbar_wait_bounded(smem_u32(&a_full[as]), a_ph, abort_ptr, kTcWaitLimitNs)) { ok = false; break; }
+          const long long q2 = clock64();
+          if (!mbar_wait_bounded(smem_u32(&b_full[s]), ph, abort_ptr, kTcWaitLimitNs)) {
+            ok = false;
+            break;
+          }
+          m1 += q2 - q1; m2 += clock64() - q2;
+          tc_fence_after_sync();
+          const uint64_t a0 = fixed + (((a_base + static_cast<uint32_t>(as) * a_stage_bytes) & 0x3ffffu) >> 4);
+          const uint64_t b0 = fixed + (((b_base + static_cast<uint32_t>(s) * b_stage_bytes) & 0x3ffffu) >> 4);
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {  // two K steps of 16 channels (32 bytes = 2 units) per block
+            const uint64_t ka = a0 + 2u * k;
+            const uint64_t kb = b0 + 2u * k;
+            mma_f16(d_tmem, ka + a_plane_units, kb, idesc, accumulate);  // mid * hi
+            mma_f16(d_tmem, ka, kb + b_units, idesc, 1u);                // hi * mid
+            mma_f16(d_tmem, ka, kb, idesc, 1u);                          // hi * hi
+            accumulate = 1u;
+          }
+          tc_commit(smem_u32(&a_empty[as]));
+          tc_commit(smem_u32(&b_empty[s]));
+          as ^= 1;
+          if (as == 0) a_ph ^= 1u;
+          if (++s == S) {
+            s = 0;
+            ph ^= 1u;
+          }
+        }
+        if (!ok) break;
+        tc_commit(smem_u32(&tfull_bar[acc]));
+        acc ^= 1;
+        if (acc == 0) acc_ph ^= 1u;
+      }
+      if (tr) { p.trace[16] = m0; p.trace[17] = m1; p.trace[18] = m2; }
+      if (!ok) {
+        if (atomicCAS(const_cast<int*>(abort_ptr), 0, 1) == 0) atomicCAS(p.status, 0, TC_TIMEOUT_MMA);
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------ epilogue (warps 2-5)
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;  // accumulator row = pixel (row / 8, row % 8) of the tile
+    TcStageCfg cfg{};
+    cfg.bar_base = 1;
+    cfg.res_stage = res_stage;
+    cfg.out_stage = out_stage;
+    cfg.res_bar = smem_u32(&res_bar);
+    cfg.out_bufs = p.out_bufs;
+    cfg.out_mode = p.out_mode;
+    cfg.res_mode = p.res_mode;
+    cfg.act = p.act;
+    cfg.act_a = p.act_a;
+    cfg.act_b = p.act_b;
+    cfg.N = p.N;
+    cfg.block_n = p.block_n;
+    cfg.wide = (p.out_mode == OUT_BF16X2 || p.res_mode == RES_BF16X2) ? 1 : 0;
+    const uint32_t acc_stride = p.block_n > 128 ? 256u : 128u;
+    int acc = 0, out_slot = 0;
+    uint32_t acc_ph = 0, res_ph = 0;
+    bool ok = true;
+    const bool tr = p.trace != nullptr && blockIdx.x == gridDim.x / 2 && threadIdx.x == 64;
+    long long e0 = 0, e1 = 0, ecnt = 0;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      int img, oy0, ox0, n0;
+      decode(tile, &img, &oy0, &ox0, &n0);
+      const long long r0 = clock64();
+      ok = __all_sync(0xffffffffu,
+                      mbar_wait_bounded(smem_u32(&tfull_bar[acc]), acc_ph, abort_ptr, kTcWaitLimitNs) ? 1 : 0) != 0;
+      if (!ok) break;
+      tc_fence_after_sync();
+      const long long r1 = clock64();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc) * acc_stride;
+      for (int t = static_cast<int>(threadIdx.x) - 64; t < p.block_n; t += 128) {
+        const int n = n0 + t;
+        tile_bias[t] = (p.bias != nullptr && n < p.N) ? __ldg(p.bias + n) : 0.0f;
+      }
+      struct {
+        const CUtensorMap *o0, *o1, *r0, *r1;
+        int x, y, img;
+        __device__ __forceinline__ void load_res(int plane, uint32_t dst, uint32_t bar, int col) const {
+          ptx::tma_load_4d(dst, plane ? r1 : r0, bar, col, x, y, img);
+        }
+        __device__ __forceinline__ void store_out(int plane, uint32_t src, int col) const {
+          ptx::tma_store_4d(plane ? o1 : o0, src, col, x, y, img);
+        }
+        __device__ __forceinline__ void store_side(int, uint32_t, int) const {}
+      } io{&map_o0, &map_o1, &map_r0, &map_r1, ox0, oy0, img};
+      ok = tc_staged_epilogue<KIND>(cfg, io, t_row, n0, row, threadIdx.x == 64, tile_bias, tile_bias, res_ph,
+                                           out_slot, abort_ptr);
+      if (!ok) break;
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+      acc ^= 1;
+      if (acc == 0) acc_ph ^= 1u;
+      e0 += r1 - r0; e1 += clock64() - r1; ++ecnt;
+    }
+    if (tr) { p.trace[24] = e0; p.trace[25] = e1; p.trace[26] = ecnt; }
+    if (!ok && lane == 0) {
+      if (atomicCAS(const_cast<int*>(abort_ptr), 0, 1) == 0) atomicCAS(p.status, 0, TC_TIMEOUT_EPILOGUE);
+    }
+    if (threadIdx.x == 64) tma_store_wait_all();
+  } else {
+    // ------------------------------------------------------------ depthwise (warps 6-13, 256 threads)
+    // A thread owns one group of four channels, one column of the tile and four rows below each other: its
+    // six input rows x three columns are read once for the four results.
+    const int t = static_cast<int>(threadIdx.x) - 192;
+    const int quad = t & 7;            // channels 4*quad .. 4*quad+3 of the block
+    const int col = (t >> 3) & 7;      // column of the tile
+    const int row0 = (t >> 6) * 4;     // first of the thread's four rows
+    int pb = 0, as = 0;
+    uint32_t p_ph = 0, a_ph = 0;
+    bool ok = true;
+    // none / ReLU / clip as one clamp: fminf(fmaxf(y, lo), hi) returns y itself between the bounds
+    const float act_lo = p.dw_act == ACT_RELU ? 0.0f : (p.dw_act == ACT_CLIP ? p.dw_act_a : -INFINITY);
+    const float act_hi = p.dw_act == ACT_CLIP ? p.dw_act_b : INFINITY;
+    const bool tr = p.trace != nullptr && blockIdx.x == gridDim.x / 2 && t == 0;
+    long long tw0 = 0, tw1 = 0, tw2 = 0, tw3 = 0, tw4 = 0, tcnt = 0;
+    const long long tstart = clock64();
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int cb = 0; cb < p.c_blocks && ok; ++cb) {
+        const long long c0 = clock64();
+        const int c = cb * kDwpChannels + quad * 4;  // first channel of the thread
+        const bool live = c < p.C;                   // (C is a multiple of 4; a dead group writes zeros)
+        float4 tap[9];
+        float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < 9; ++k)
+          tap[k] = live ? __ldg(reinterpret_cast<const float4*>(p.dw_weights + static_cast<size_t>(k) * p.C + c))
+                        : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (live && p.dw_bias != nullptr) bias = __ldg(reinterpret_cast<const float4*>(p.dw_bias + c));
+        // the vote keeps the warp together for the barrier arrivals below
+        ok = __all_sync(0xffffffffu,
+                        mbar_wait_bounded(smem_u32(&patch_full[pb]), p_ph, abort_ptr, kTcWaitLimitNs) ? 1 : 0) != 0;
+        if (!ok) break;
+        const long long c1 = clock64();
+        const uint32_t patch = patch_base + static_cast<uint32_t>(pb) * kDwpPatchBytes;
+        float4 acc[4];
+#pragma unroll
+        for (int r = 0; r < 4; ++r) acc[r] = bias;
+        // input rows row0 .. row0+5; input row i feeds result row r with filter row kh = i - r
+#pragma unroll
+        for (int i = 0; i < 6; ++i) {
+          float4 x[3];
+#pragma unroll
+          for (int kw = 0; kw < 3; ++kw) {
+            const uint32_t at = patch + static_cast<uint32_t>((((row0 + i) * kDwpPatchW + col + kw) * kDwpChannels + quad * 4) * 4);
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x[kw].x), "=f"(x[kw].y), "=f"(x[kw].z), "=f"(x[kw].w) : "r"(at));
+          }
+#pragma unroll
+          for (int r = 0; r < 4; ++r) {
+            const int kh = i - r;
+            if (kh < 0 || kh > 2) continue;
+#pragma unroll
+            for (int kw = 0; kw < 3; ++kw) {
+              const float4 k = tap[kh * 3 + kw];
+              acc[r].x = fmaf(x[kw].x, k.x, acc[r].x);
+              acc[r].y = fmaf(x[kw].y, k.y, acc[r].y);
+              acc[r].z = fmaf(x[kw].z, k.z, acc[r].z);
+              acc[r].w = fmaf(x[kw].w, k.w, acc[r].w);
+            }
+          }
+        }
+        // the patch has been read: the producer may refill it
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&patch_empty[pb]));
+        pb ^= 1;
+        if (pb == 0) p_ph ^= 1u;
+        const long long c2 = clock64();
+        // the operand tile of two channel blocks ago must have been consumed by its MMAs
+        ok = __all_sync(0xffffffffu,
+                        mbar_wait_bounded(smem_u32(&a_empty[as]), a_ph ^ 1u, abort_ptr, kTcWaitLimitNs) ? 1 : 0) != 0;
+        if (!ok) break;
+        const long long c3 = clock64();
+        const uint32_t a_tile = a_base + static_cast<uint32_t>(as) * a_stage_bytes;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          float4 y;
+          y.x = fminf(fmaxf(acc[r].x, act_lo), act_hi);
+          y.y = fminf(fmaxf(acc[r].y, act_lo), act_hi);
+          y.z = fminf(fmaxf(acc[r].z, act_lo), act_hi);
+          y.w = fminf(fmaxf(acc[r].w, act_lo), act_hi);
+          uint32_t hi0, mid0, hi1, mid1;
+          split_bf16x2(y.x, y.y, hi0, mid0);
+          split_bf16x2(y.z, y.w, hi1, mid1);
+          // operand row = pixel (row, col) of the tile; 64-byte rows with the 64-byte swizzle: the
+          // 16-byte chunk j of row m lives at m*64 + ((j ^ ((m >> 1) & 3)) * 16)
+          const int m = (row0 + r) * kDwpTileW + col;
+          const uint32_t at = a_tile + stage_chunk_offset(m, quad >> 1) + static_cast<uint32_t>((quad & 1) * 8);
+          asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(at), "r"(hi0), "r"(hi1) : "memory");
+          asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(at + kDwpAPlaneBytes), "r"(mid0), "r"(mid1) : "memory");
+        }
+        const long long c3a = clock64();
+        fence_proxy_async_smem();  // the tensor core reads what these stores wrote
+        const long long c3b = clock64();
+        tw4 += c3b - c3a;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&a_full[as]));
+        as ^= 1;
+        if (as == 0) a_ph ^= 1u;
+        const long long c4 = clock64();
+        tw0 += c1 - c0; tw1 += c2 - c1; tw2 += c3 - c2; tw3 += c4 - c3; ++tcnt;
+      }
+    }
+    if (tr) { p.trace[0] = tw0; p.trace[1] = tw1; p.trace[2] = tw2; p.trace[3] = tw3; p.trace[4] = tcnt; p.trace[5] = clock64() - tstart; p.trace[6] = tw4; }
+    if (!ok && lane == 0) {
+      if (atomicCAS(const_cast<int*>(abort_ptr), 0, 1) == 0) atomicCAS(p.status, 0, TC_TIMEOUT_EPILOGUE);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (warp == 1) tmem_dealloc(tmem_base, kTcTmemCols);
+}
+
+}  // namespace nb

@@ -1032,6 +1032,144 @@ cudaError_t tc_launch_halo(const TcHaloLaunch& L, cudaStream_t stream) {
   return e != cudaSuccess ? e : cudaGetLastError();
 }
 
+// ------------------------------------------------------------------ depthwise + projection
+namespace {
+
+struct DwProjShape {
+  int block_n = 0, tiles_n = 0, stages = 0, out_bufs = 0, b_bytes = 0, smem = 0;
+  bool ok = false;
+};
+
+DwProjShape dw_project_shape(int N, int out_mode, int res_mode) {
+  DwProjShape r;
+  const bool wide = out_mode == OUT_BF16X2 || res_mode == RES_BF16X2;
+  if (out_mode != OUT_BF16X2 && out_mode != OUT_F32) return r;
+  if (wide && res_mode == RES_SPLIT) return r;
+  const int step = wide ? 32 : 16;
+  const int n_tiles = (N + 255) / 256;
+  r.block_n = ((N + n_tiles - 1) / n_tiles + step - 1) / step * step;
+  if (r.block_n > 256 || r.block_n % 16 != 0) return r;
+  r.tiles_n = (N + r.block_n - 1) / r.block_n;
+  r.b_bytes = (r.block_n * 64 + 1023) / 1024 * 1024;
+  const int out_tile = wide ? 16384 : 8192;
+  const int fixed = 2 * kDwpPatchBytes + 2 * 2 * kDwpAPlaneBytes + (res_mode != RES_NONE ? 16384 : 0);
+  const int budget = 222 * 1024;  // the kernel's own static shared memory is ~2 KB
+  for (int bufs : {4, 3, 2}) {
+    const int stages = std::min(kDwpMaxStages, (budget - fixed - bufs * out_tile) / (2 * r.b_bytes));
+    if (stages >= 2) {
+      r.stages = stages;
+      r.out_bufs = bufs;
+      r.smem = fixed + bufs * out_tile + stages * 2 * r.b_bytes + 1024;
+      r.ok = true;
+      return r;
+    }
+  }
+  return r;
+}
+
+}  // namespace
+
+bool tc_dw_project_applies(int C, int N, int H, int W, int out_mode, bool has_res, bool res_bf16) {
+  if (C % 4 != 0 || C < 8 || N % 8 != 0 || H < 1 || W < 1) return false;
+  // 16 x 8 pixel tiles: an image that fills less than 60 % of its tiles (7 x 7 fills 38 %) is faster as two layers
+  const int tiles = ((H + kDwpTileH - 1) / kDwpTileH) * ((W + kDwpTileW - 1) / kDwpTileW);
+  if (env_int("NCNN_B200_FUSE_DW", 1) < 2 && static_cast<long long>(H) * W * 10 < 6ll * tiles * kDwpTileH * kDwpTileW) return false;
+  const int res_mode = !has_res ? RES_NONE : (res_bf16 ? RES_BF16X2 : RES_F32);
+  if (out_mode == OUT_F32 && N % 4 != 0) return false;
+  return dw_project_shape(N, out_mode, res_mode).ok;
+}
+
+std::string tc_plan_dw_project(TcDwProjLaunch* L, const TcDwProjConv& c, const TcEpilogue& e, int sm_count) {
+  load_driver_entry_points();
+  if (!g_driver_error.empty()) return g_driver_error;
+  TcDwProjParams& p = L->p;
+  std::memset(&p, 0, sizeof(p));
+  const int res_mode = e.res0 == nullptr ? RES_NONE : (e.res_bf16 ? RES_BF16X2 : (e.res1 != nullptr ? RES_SPLIT : RES_F32));
+  const DwProjShape shape = dw_project_shape(c.out_channels, e.out_mode, res_mode);
+  if (!shape.ok) return "the fused depthwise + projection kernel does not take this output format or width";
+  if (e.ldo != c.out_channels) return "the fused depthwise + projection kernel writes dense channel-last rows";
+  if ((reinterpret_cast<uintptr_t>(c.x) & 15) != 0 || (static_cast<size_t>(c.C) * 4) % 16 != 0)
+    return "depthwise input rows must be 16-byte aligned";
+  const bool out_bf16 = e.out_mode == OUT_BF16X2;
+  p.images = c.images;
+  p.H = c.H;
+  p.W = c.W;
+  p.C = c.C;
+  p.N = c.out_channels;
+  p.tiles_y = (c.H + kDwpTileH - 1) / kDwpTileH;
+  p.tiles_x = (c.W + kDwpTileW - 1) / kDwpTileW;
+  p.block_n = shape.block_n;
+  p.tiles_n = shape.tiles_n;
+  p.c_blocks = (c.C + kDwpChannels - 1) / kDwpChannels;
+  p.pad_t = c.pad_t;
+  p.pad_l = c.pad_l;
+  p.stages = shape.stages;
+  p.b_bytes = shape.b_bytes;
+  p.out_bufs = shape.out_bufs;
+  p.dw_weights = c.dw_weights;
+  p.dw_bias = c.dw_bias;
+  p.dw_act = c.dw_act;
+  p.dw_act_a = c.dw_act_a;
+  p.dw_act_b = c.dw_act_b;
+  p.bias = e.bias;
+  p.res_mode = res_mode;
+  p.out_mode = e.out_mode;
+  p.act = e.act;
+  p.act_a = e.act_a;
+  p.act_b = e.act_b;
+  p.status = e.status;
+  L->smem_bytes = std::max(shape.smem, 120 * 1024);
+  const long long tiles = static_cast<long long>(c.images) * p.tiles_y * p.tiles_x * p.tiles_n;
+  if (tiles > 0x7fffffffll) return "too many tiles for one launch";
+  L->grid = static_cast<int>(std::min<long long>(tiles, sm_count));
+  // fp32 input patches: [image][H][W][C], boxes of 32 channels x 10 x 18 pixels, dense in shared memory
+  std::string err = encode_tiled_4d(&L->map_x, false, c.x, c.C, c.W, c.H, c.images, kDwpChannels, kDwpPatchW, kDwpPatchH,
+                                    CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (!err.empty()) return err;
+  const uint64_t k_total = static_cast<uint64_t>(p.c_blocks) * kDwpChannels;
+  err = encode_tiled_2d(&L->map_b0, GEMM_BF16X3, c.w0, k_total, c.out_channels, k_total * 2, kDwpChannels, p.block_n, 64);
+  if (err.empty())
+    err = encode_tiled_2d(&L->map_b1, GEMM_BF16X3, c.w1, k_total, c.out_channels, k_total * 2, kDwpChannels, p.block_n, 64);
+  if (!err.empty()) return err;
+  auto plane = [&](CUtensorMap* map, const void* base, bool bf16) {
+    return encode_tiled_4d(map, bf16, base, c.out_channels, c.W, c.H, c.images, bf16 ? 32 : 16, kDwpTileW, kDwpTileH,
+                           CU_TENSOR_MAP_SWIZZLE_64B);
+  };
+  err = plane(&L->map_o0, e.out0, out_bf16);
+  if (err.empty() && out_bf16) err = plane(&L->map_o1, e.out1, true);
+  if (err.empty() && e.res0 != nullptr) err = plane(&L->map_r0, e.res0, e.res_bf16);
+  if (err.empty() && e.res1 != nullptr) err = plane(&L->map_r1, e.res1, e.res_bf16);
+  return err;
+}
+
+cudaError_t tc_launch_dw_project(const TcDwProjLaunch& L, cudaStream_t stream) {
+  static PerDeviceOnce attr_once;
+  const cudaError_t attr_err = attr_once.run([] {
+    return cudaFuncSetAttribute(tc_dw_project_kernel<GEMM_BF16X3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+  });
+  if (attr_err != cudaSuccess) return attr_err;
+  KernelLaunchConfig lc(L.grid, kDwpThreads, L.smem_bytes, false, stream);
+  static long long* d_trace = nullptr;
+  cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+  cudaStreamIsCapturing(stream, &cs);
+  if (std::getenv("NCNN_B200_DWP_TRACE") != nullptr && cs == cudaStreamCaptureStatusNone) {
+    if (d_trace == nullptr) cudaMalloc(&d_trace, 64 * 8);
+    cudaMemsetAsync(d_trace, 0, 64 * 8, stream);
+    TcDwProjLaunch T = L;
+    T.p.trace = d_trace;
+    cudaLaunchKernelEx(&lc.cfg, tc_dw_project_kernel<GEMM_BF16X3>, T.p, T.map_x, T.map_b0, T.map_b1, T.map_o0, T.map_o1, T.map_r0, T.map_r1);
+    cudaStreamSynchronize(stream);
+    long long h[64];
+    cudaMemcpy(h, d_trace, sizeof(h), cudaMemcpyDeviceToHost);
+    std::fprintf(stderr, "DWP C=%d N=%d HxW=%dx%d cblocks=%d grid=%d smem=%d | dw: n=%lld wait_patch=%lld compute=%lld wait_a=%lld store=%lld (fence %lld) total=%lld | prod wait=%lld | mma: tempty=%lld a_full=%lld b_full=%lld | epi: n=%lld wait=%lld run=%lld\n",
+                 L.p.C, L.p.N, L.p.H, L.p.W, L.p.c_blocks, L.grid, L.smem_bytes, h[4], h[0], h[1], h[2], h[3], h[6], h[5], h[8], h[16], h[17], h[18], h[26], h[24], h[25]);
+    return cudaSuccess;
+  }
+  const cudaError_t e = cudaLaunchKernelEx(&lc.cfg, tc_dw_project_kernel<GEMM_BF16X3>, L.p, L.map_x, L.map_b0, L.map_b1, L.map_o0,
+                                           L.map_o1, L.map_r0, L.map_r1);
+  return e != cudaSuccess ? e : cudaGetLastError();
+}
+
 float tf32_round_host(float x) {
   // round to nearest, ties away from zero, onto 10 explicit mantissa bits
   uint32_t u;

@@ -10,6 +10,7 @@
 #include <cuda_runtime.h>
 
 #include "tc_conv_halo.cuh"
+#include "tc_dw_project.cuh"
 #include "tc_gemm.cuh"
 #include "tc_gemm2.cuh"
 #include "tc_stem.cuh"
@@ -152,6 +153,39 @@ bool tc_halo_applies(int kind, int C, int KH, int KW, int stride_h, int stride_w
 std::string tc_plan_conv_halo(TcHaloLaunch* launch, int kind, const TcHaloConv& conv, const TcEpilogue& epilogue,
                               int sm_count, bool pair = false);
 cudaError_t tc_launch_halo(const TcHaloLaunch& launch, cudaStream_t stream);
+
+// ---- 3x3 depthwise convolution fused into the following 1x1 convolution (tc_dw_project.cuh)
+struct TcDwProjLaunch {
+  TcDwProjParams p{};
+  alignas(64) CUtensorMap map_x{};   // fp32 depthwise input, patches of 18 x 10 pixels x 32 channels
+  alignas(64) CUtensorMap map_b0{};  // projection weights, bf16 hi / mid planes
+  alignas(64) CUtensorMap map_b1{};
+  alignas(64) CUtensorMap map_o0{};
+  alignas(64) CUtensorMap map_o1{};
+  alignas(64) CUtensorMap map_r0{};
+  alignas(64) CUtensorMap map_r1{};
+  int grid = 0;
+  int smem_bytes = 0;
+};
+
+struct TcDwProjConv {
+  const float* x = nullptr;  // plain fp32 NHWC input of the depthwise layer
+  int images = 0, H = 0, W = 0, C = 0;
+  int pad_t = 1, pad_l = 1;
+  const float* dw_weights = nullptr;  // [9][C]
+  const float* dw_bias = nullptr;
+  int dw_act = ACT_NONE;
+  float dw_act_a = 0.0f, dw_act_b = 0.0f;
+  const void* w0 = nullptr;  // projection weights packed [N][ceil(C/32)*32] bf16 hi / mid
+  const void* w1 = nullptr;
+  int out_channels = 0;
+};
+
+// True when the fused kernel takes the pair of layers: 3x3, stride 1, dilation 1, output extent equal to the
+// input's, channels in fours; projection 1x1 stride 1 with bf16-pair operands and a staged epilogue.
+bool tc_dw_project_applies(int C, int N, int H, int W, int out_mode, bool has_res, bool res_bf16);
+std::string tc_plan_dw_project(TcDwProjLaunch* launch, const TcDwProjConv& conv, const TcEpilogue& epilogue, int sm_count);
+cudaError_t tc_launch_dw_project(const TcDwProjLaunch& launch, cudaStream_t stream);
 
 // ---- stem convolution with the input rows resident in shared memory (tc_stem.cuh)
 struct TcStemLaunch {

@@ -319,3 +319,45 @@ def test_patch_resident_pairs_match_the_im2col_kernel(pkg, oracle, tmp_path, mon
     assert rel_l2(got, base) <= 3e-5
     want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x[:2]])
     assert rel_l2(got[:2], want) <= 1e-4
+
+
+# ------------------------------------------------------------------ depthwise fused into the projection
+@pytest.mark.parametrize("n", [2, 5])
+def test_depthwise_runs_inside_the_projection_kernel(pkg, oracle, tmp_path, monkeypatch, n):
+    """The stride-1 3x3 depthwise layers of the inverted-residual blocks run inside the 1x1 convolution that
+    follows them (their result goes from the CUDA cores into the MMA's shared-memory operand, never to HBM).
+    Same values, same bf16 split, same order of products as the two separate layers: the same bits; and the
+    network still matches the oracle."""
+    param, bin_ = pkg.zoo.mobilenet_v2(str(tmp_path / "mbv2"))
+    x = np.random.default_rng(300 + n).uniform(-1, 1, (n, 3, 224, 224)).astype(np.float32)
+    got, kernels = _run(pkg, param, bin_, x)
+    fused = kernels.count("tc_dw_project_kernel<bf16x3>")
+    assert fused >= 10, kernels
+    monkeypatch.setenv("NCNN_B200_FUSE_DW", "0")
+    base, plain = _run(pkg, param, bin_, x)
+    assert "tc_dw_project_kernel<bf16x3>" not in plain and len(plain) - len(kernels) == fused
+    assert np.array_equal(got, base)
+    want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x[:2]])
+    assert rel_l2(got[:2], want) <= 2e-4
+
+
+@pytest.mark.parametrize("h,c,cout,n", [(14, 96, 24, 3), (30, 40, 64, 2), (7, 960, 320, 4), (9, 144, 16, 5)])
+def test_depthwise_projection_block_shapes(pkg, oracle, tmp_path, monkeypatch, h, c, cout, n):
+    """Single inverted-residual tails at awkward shapes: channel counts that end inside a 32-channel block, images
+    that the 16 x 8 tiles overhang, a projection wider than one tile (320 = 2 x 160)."""
+    net = pkg.zoo._Net(1000 + h)
+    wr = net.w
+    wr.layer("Input", "input", [], ["data"], f"0={h} 1={h} 2={c}")
+    net.depthwise("dw", "data", "d", c, 3, 1, 1)
+    wr.layer("Clip", "relu6", ["d"], ["d6"], "0=0.0 1=6.0")
+    net.conv("project", "d6", "output", c, cout, 1, 1, 0, act=0, zero_bias=False)
+    param, bin_ = wr.save(str(tmp_path / "blk"))
+    x = np.random.default_rng(h * c).uniform(-3, 3, (n, c, h, h)).astype(np.float32)
+    monkeypatch.setenv("NCNN_B200_FUSE_DW", "2")  # also where the image fills its tiles badly
+    got, kernels = _run(pkg, param, bin_, x)
+    assert "tc_dw_project_kernel<bf16x3>" in kernels, kernels
+    monkeypatch.setenv("NCNN_B200_FUSE_DW", "0")
+    base, _ = _run(pkg, param, bin_, x)
+    assert np.array_equal(got, base)
+    want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x])
+    assert rel_l2(got, want) <= 1e-4
