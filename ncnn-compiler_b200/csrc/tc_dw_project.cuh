@@ -7,7 +7,7 @@
 // image (128 rows of the projection's GEMM); per block of 32 channels
 //   * TMA loads the (16+2) x (8+2) fp32 input patch once (coordinates outside the image read as zero:
 //     that is the padding),
-//   * eight CUDA-core warps compute the 128 x 32 depthwise results from it with the arithmetic of the
+//   * four CUDA-core warps (two such groups take alternate blocks) compute the 128 x 32 depthwise results from it with the arithmetic of the
 //     stand-alone kernel (bias, nine fmaf in filter order, activation), split each value into its bf16
 //     pair (hi = bf16(x), mid = bf16(x - hi)) and write both planes straight into the K-major,
 //     64-byte-swizzled operand tile that tcgen05.mma reads,
@@ -32,6 +32,7 @@ constexpr int kDwpPatchH = kDwpTileH + 2, kDwpPatchW = kDwpTileW + 2;
 constexpr int kDwpPatchBytes = (kDwpPatchH * kDwpPatchW * kDwpChannels * 4 + 1023) / 1024 * 1024;
 constexpr int kDwpAPlaneBytes = kTcBlockM * 64;                   // one bf16 plane of the operand tile
 constexpr int kDwpMaxStages = 4;
+constexpr int kDwpMaxPatches = 4;
 
 struct TcDwProjParams {
   int images, H, W, C;  // depthwise input = output extent (stride 1), channels
@@ -40,6 +41,7 @@ struct TcDwProjParams {
   int c_blocks;         // blocks of 32 channels (the last one may be partly past C: zero-filled)
   int pad_t, pad_l;
   int stages;           // weight ring depth
+  int patch_bufs;       // input patch ring depth (2..4): a patch load takes longer than one block's arithmetic
   int b_bytes;          // one plane of a weight stage, rounded to 1 KB
   int out_bufs;
   const float* dw_weights;  // [9][C], tap-major
@@ -64,7 +66,7 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
   grid_dependency_trigger();  // the next kernel of the stream may begin its preamble
 
   extern __shared__ uint8_t dwp_smem_raw[];
-  __shared__ __align__(8) uint64_t patch_full[2], patch_empty[2];
+  __shared__ __align__(8) uint64_t patch_full[kDwpMaxPatches], patch_empty[kDwpMaxPatches];
   __shared__ __align__(8) uint64_t a_full[2], a_empty[2];
   __shared__ __align__(8) uint64_t b_full[kDwpMaxStages], b_empty[kDwpMaxStages];
   __shared__ __align__(8) uint64_t tfull_bar[2], tempty_bar[2];
@@ -76,8 +78,9 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(dwp_smem_raw) + 1023u) & ~1023u;
-  const uint32_t patch_base = smem_base;                                  // two fp32 patches
-  const uint32_t a_base = patch_base + 2u * kDwpPatchBytes;               // two operand tiles (hi, mid planes)
+  const int P = p.patch_bufs;
+  const uint32_t patch_base = smem_base;                                  // ring of fp32 patches
+  const uint32_t a_base = patch_base + static_cast<uint32_t>(P) * kDwpPatchBytes;               // two operand tiles (hi, mid planes)
   const uint32_t a_stage_bytes = 2u * kDwpAPlaneBytes;
   const uint32_t b_base = a_base + 2u * a_stage_bytes;                    // weight ring (hi, mid planes)
   const uint32_t b_bytes = static_cast<uint32_t>(p.b_bytes);
@@ -85,16 +88,22 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
   const int S = p.stages;
   const uint32_t res_stage = b_base + static_cast<uint32_t>(S) * b_stage_bytes;
   const uint32_t out_stage = res_stage + (p.res_mode != RES_NONE ? 16384u : 0u);
+  const bool wide_out = p.out_mode == OUT_BF16X2 || p.res_mode == RES_BF16X2;
+  // the depthwise filter and bias of every channel, [10][c_blocks * 32] fp32 (taps 0..8, then the bias; zero past C)
+  const uint32_t table = out_stage + static_cast<uint32_t>(p.out_bufs) * (wide_out ? 16384u : 8192u);
+  const int c_pad = p.c_blocks * kDwpChannels;
   const int tiles_per_image = p.tiles_y * p.tiles_x;
   const int total_tiles = p.images * tiles_per_image * p.tiles_n;
   volatile int* abort_ptr = &abort_flag;
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < P; ++i) {
       mbar_init(smem_u32(&patch_full[i]), 1);
-      mbar_init(smem_u32(&patch_empty[i]), 8);  // one arrival per depthwise warp
-      mbar_init(smem_u32(&a_full[i]), 8);
+      mbar_init(smem_u32(&patch_empty[i]), 4);  // one arrival per warp of the depthwise group that read it
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&a_full[i]), 4);
       mbar_init(smem_u32(&a_empty[i]), 1);
       mbar_init(smem_u32(&tfull_bar[i]), 1);
       mbar_init(smem_u32(&tempty_bar[i]), 4);
@@ -113,6 +122,13 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
   if (warp == 1) {
     tmem_alloc(smem_u32(&tmem_slot), kTcTmemCols);
     tmem_relinquish();
+  }
+  // (constants of the layer, not results of the kernel before: they may be read ahead of the dependency wait)
+  for (int i = static_cast<int>(threadIdx.x); i < 10 * c_pad; i += kDwpThreads) {
+    const int k = i / c_pad, c = i - k * c_pad;
+    float v = 0.0f;
+    if (c < p.C) v = k < 9 ? __ldg(p.dw_weights + static_cast<size_t>(k) * p.C + c) : (p.dw_bias != nullptr ? __ldg(p.dw_bias + c) : 0.0f);
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(table + static_cast<uint32_t>(i) * 4u), "f"(v) : "memory");
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -163,8 +179,10 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
         }
         ++patches;
         pw += clock64() - g0;
-        pb ^= 1;
-        if (pb == 0) p_ph ^= 1u;
+        if (++pb == P) {
+          pb = 0;
+          p_ph ^= 1u;
+        }
         if (lane == 0) {
           w = mbar_wait_bounded(smem_u32(&b_empty[s]), ph ^ 1u, abort_ptr, kTcWaitLimitNs) ? 1 : 0;
           if (w) mbar_arrive_expect_tx(smem_u32(&b_full[s]), b_tx);
@@ -194,8 +212,8 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
         int zero = 0;
         for (long long i = weights > S ? weights - S : 0; i < weights; ++i)
           mbar_wait_bounded(smem_u32(&b_full[i % S]), static_cast<uint32_t>((i / S) & 1), &zero, 200000000ull);
-        for (long long i = patches > 2 ? patches - 2 : 0; i < patches; ++i)
-          mbar_wait_bounded(smem_u32(&patch_full[i % 2]), static_cast<uint32_t>((i / 2) & 1), &zero, 200000000ull);
+        for (long long i = patches > P ? patches - P : 0; i < patches; ++i)
+          mbar_wait_bounded(smem_u32(&patch_full[i % P]), static_cast<uint32_t>((i / P) & 1), &zero, 200000000ull);
       }
     }
   } else if (warp == 1) {
@@ -328,14 +346,15 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
     if (threadIdx.x == 64) tma_store_wait_all();
   } else {
     // ------------------------------------------------------------ depthwise (warps 6-13, 256 threads)
-    // A thread owns one group of four channels, one column of the tile and four rows below each other: its
-    // six input rows x three columns are read once for the four results.
+    // Two groups of four warps take alternate channel blocks (group g: blocks g, g+2, ... of the CTA's sequence,
+    // so group g always fills operand tile g): while one group waits for its patch or for its operand tile to be
+    // free, the other computes.  In a group a thread owns four channels, one column of the tile and eight rows
+    // below each other: its ten input rows x three columns are read once for the eight results.
     const int t = static_cast<int>(threadIdx.x) - 192;
-    const int quad = t & 7;            // channels 4*quad .. 4*quad+3 of the block
-    const int col = (t >> 3) & 7;      // column of the tile
-    const int row0 = (t >> 6) * 4;     // first of the thread's four rows
-    int pb = 0, as = 0;
-    uint32_t p_ph = 0, a_ph = 0;
+    const int group = t >> 7;
+    const int quad = t & 7;                 // channels 4*quad .. 4*quad+3 of the block
+    const int col = (t >> 3) & 7;           // column of the tile
+    const int row0 = ((t >> 6) & 1) * 8;    // first of the thread's eight rows
     bool ok = true;
     // none / ReLU / clip as one clamp: fminf(fmaxf(y, lo), hi) returns y itself between the bounds
     const float act_lo = p.dw_act == ACT_RELU ? 0.0f : (p.dw_act == ACT_CLIP ? p.dw_act_a : -INFINITY);
@@ -343,30 +362,33 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
     const bool tr = p.trace != nullptr && blockIdx.x == gridDim.x / 2 && t == 0;
     long long tw0 = 0, tw1 = 0, tw2 = 0, tw3 = 0, tw4 = 0, tcnt = 0;
     const long long tstart = clock64();
+    const uint32_t a_tile = a_base + static_cast<uint32_t>(group) * a_stage_bytes;
+    long long item = 0;  // position in the CTA's sequence of (tile, channel block)
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-      for (int cb = 0; cb < p.c_blocks && ok; ++cb) {
+      for (int cb = 0; cb < p.c_blocks && ok; ++cb, ++item) {
+        if ((item & 1) != group) continue;
+        const int pb = static_cast<int>(item % P);
+        const uint32_t p_ph = static_cast<uint32_t>((item / P) & 1);
+        const uint32_t a_ph = static_cast<uint32_t>((item >> 1) & 1);
         const long long c0 = clock64();
-        const int c = cb * kDwpChannels + quad * 4;  // first channel of the thread
-        const bool live = c < p.C;                   // (C is a multiple of 4; a dead group writes zeros)
-        float4 tap[9];
-        float4 bias = make_float4(0.f, 0.f, 0.f, 0.f);
+        const uint32_t tc = table + static_cast<uint32_t>(cb * kDwpChannels + quad * 4) * 4u;  // the thread's channels
+        float4 tap[9], bias;
 #pragma unroll
         for (int k = 0; k < 9; ++k)
-          tap[k] = live ? __ldg(reinterpret_cast<const float4*>(p.dw_weights + static_cast<size_t>(k) * p.C + c))
-                        : make_float4(0.f, 0.f, 0.f, 0.f);
-        if (live && p.dw_bias != nullptr) bias = __ldg(reinterpret_cast<const float4*>(p.dw_bias + c));
+          asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(tap[k].x), "=f"(tap[k].y), "=f"(tap[k].z), "=f"(tap[k].w) : "r"(tc + static_cast<uint32_t>(k * c_pad) * 4u));
+        asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(bias.x), "=f"(bias.y), "=f"(bias.z), "=f"(bias.w) : "r"(tc + static_cast<uint32_t>(9 * c_pad) * 4u));
         // the vote keeps the warp together for the barrier arrivals below
         ok = __all_sync(0xffffffffu,
                         mbar_wait_bounded(smem_u32(&patch_full[pb]), p_ph, abort_ptr, kTcWaitLimitNs) ? 1 : 0) != 0;
         if (!ok) break;
         const long long c1 = clock64();
         const uint32_t patch = patch_base + static_cast<uint32_t>(pb) * kDwpPatchBytes;
-        float4 acc[4];
+        float4 acc[8];
 #pragma unroll
-        for (int r = 0; r < 4; ++r) acc[r] = bias;
-        // input rows row0 .. row0+5; input row i feeds result row r with filter row kh = i - r
+        for (int r = 0; r < 8; ++r) acc[r] = bias;
+        // input rows row0 .. row0+9; input row i feeds result row r with filter row kh = i - r
 #pragma unroll
-        for (int i = 0; i < 6; ++i) {
+        for (int i = 0; i < 10; ++i) {
           float4 x[3];
 #pragma unroll
           for (int kw = 0; kw < 3; ++kw) {
@@ -374,7 +396,7 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
             asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(x[kw].x), "=f"(x[kw].y), "=f"(x[kw].z), "=f"(x[kw].w) : "r"(at));
           }
 #pragma unroll
-          for (int r = 0; r < 4; ++r) {
+          for (int r = 0; r < 8; ++r) {
             const int kh = i - r;
             if (kh < 0 || kh > 2) continue;
 #pragma unroll
@@ -390,17 +412,14 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
         // the patch has been read: the producer may refill it
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&patch_empty[pb]));
-        pb ^= 1;
-        if (pb == 0) p_ph ^= 1u;
         const long long c2 = clock64();
-        // the operand tile of two channel blocks ago must have been consumed by its MMAs
+        // the group's operand tile, filled two blocks ago, must have been consumed by its MMAs
         ok = __all_sync(0xffffffffu,
-                        mbar_wait_bounded(smem_u32(&a_empty[as]), a_ph ^ 1u, abort_ptr, kTcWaitLimitNs) ? 1 : 0) != 0;
+                        mbar_wait_bounded(smem_u32(&a_empty[group]), a_ph ^ 1u, abort_ptr, kTcWaitLimitNs) ? 1 : 0) != 0;
         if (!ok) break;
         const long long c3 = clock64();
-        const uint32_t a_tile = a_base + static_cast<uint32_t>(as) * a_stage_bytes;
 #pragma unroll
-        for (int r = 0; r < 4; ++r) {
+        for (int r = 0; r < 8; ++r) {
           float4 y;
           y.x = fminf(fmaxf(acc[r].x, act_lo), act_hi);
           y.y = fminf(fmaxf(acc[r].y, act_lo), act_hi);
@@ -421,9 +440,7 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
         const long long c3b = clock64();
         tw4 += c3b - c3a;
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&a_full[as]));
-        as ^= 1;
-        if (as == 0) a_ph ^= 1u;
+        if (lane == 0) mbar_arrive(smem_u32(&a_full[group]));
         const long long c4 = clock64();
         tw0 += c1 - c0; tw1 += c2 - c1; tw2 += c3 - c2; tw3 += c4 - c3; ++tcnt;
       }

@@ -1036,11 +1036,11 @@ cudaError_t tc_launch_halo(const TcHaloLaunch& L, cudaStream_t stream) {
 namespace {
 
 struct DwProjShape {
-  int block_n = 0, tiles_n = 0, stages = 0, out_bufs = 0, b_bytes = 0, smem = 0;
+  int block_n = 0, tiles_n = 0, stages = 0, out_bufs = 0, patches = 0, b_bytes = 0, smem = 0;
   bool ok = false;
 };
 
-DwProjShape dw_project_shape(int N, int out_mode, int res_mode) {
+DwProjShape dw_project_shape(int N, int out_mode, int res_mode, int C) {
   DwProjShape r;
   const bool wide = out_mode == OUT_BF16X2 || res_mode == RES_BF16X2;
   if (out_mode != OUT_BF16X2 && out_mode != OUT_F32) return r;
@@ -1052,18 +1052,24 @@ DwProjShape dw_project_shape(int N, int out_mode, int res_mode) {
   r.tiles_n = (N + r.block_n - 1) / r.block_n;
   r.b_bytes = (r.block_n * 64 + 1023) / 1024 * 1024;
   const int out_tile = wide ? 16384 : 8192;
-  const int fixed = 2 * kDwpPatchBytes + 2 * 2 * kDwpAPlaneBytes + (res_mode != RES_NONE ? 16384 : 0);
   const int budget = 222 * 1024;  // the kernel's own static shared memory is ~2 KB
-  for (int bufs : {4, 3, 2}) {
-    const int stages = std::min(kDwpMaxStages, (budget - fixed - bufs * out_tile) / (2 * r.b_bytes));
-    if (stages >= 2) {
-      r.stages = stages;
-      r.out_bufs = bufs;
-      r.smem = fixed + bufs * out_tile + stages * 2 * r.b_bytes + 1024;
-      r.ok = true;
-      return r;
-    }
-  }
+  // Deep patch ring first (a patch load outlasts one block's arithmetic), then three weight stages, then
+  // output staging tiles; the last resort is two of each.
+  for (int min_stages : {3, 2})
+    for (int patches : {4, 3, 2})
+      for (int bufs : {4, 3, 2}) {
+        const int table = ((C + kDwpChannels - 1) / kDwpChannels * kDwpChannels * 10 * 4 + 1023) / 1024 * 1024;  // depthwise filter + bias
+        const int fixed = patches * kDwpPatchBytes + 2 * 2 * kDwpAPlaneBytes + (res_mode != RES_NONE ? 16384 : 0) + table;
+        const int stages = std::min(kDwpMaxStages, (budget - fixed - bufs * out_tile) / (2 * r.b_bytes));
+        if (stages >= min_stages) {
+          r.stages = stages;
+          r.out_bufs = bufs;
+          r.patches = patches;
+          r.smem = fixed + bufs * out_tile + stages * 2 * r.b_bytes + 1024;
+          r.ok = true;
+          return r;
+        }
+      }
   return r;
 }
 
@@ -1076,7 +1082,7 @@ bool tc_dw_project_applies(int C, int N, int H, int W, int out_mode, bool has_re
   if (env_int("NCNN_B200_FUSE_DW", 1) < 2 && static_cast<long long>(H) * W * 10 < 6ll * tiles * kDwpTileH * kDwpTileW) return false;
   const int res_mode = !has_res ? RES_NONE : (res_bf16 ? RES_BF16X2 : RES_F32);
   if (out_mode == OUT_F32 && N % 4 != 0) return false;
-  return dw_project_shape(N, out_mode, res_mode).ok;
+  return dw_project_shape(N, out_mode, res_mode, C).ok;
 }
 
 std::string tc_plan_dw_project(TcDwProjLaunch* L, const TcDwProjConv& c, const TcEpilogue& e, int sm_count) {
@@ -1085,7 +1091,7 @@ std::string tc_plan_dw_project(TcDwProjLaunch* L, const TcDwProjConv& c, const T
   TcDwProjParams& p = L->p;
   std::memset(&p, 0, sizeof(p));
   const int res_mode = e.res0 == nullptr ? RES_NONE : (e.res_bf16 ? RES_BF16X2 : (e.res1 != nullptr ? RES_SPLIT : RES_F32));
-  const DwProjShape shape = dw_project_shape(c.out_channels, e.out_mode, res_mode);
+  const DwProjShape shape = dw_project_shape(c.out_channels, e.out_mode, res_mode, c.C);
   if (!shape.ok) return "the fused depthwise + projection kernel does not take this output format or width";
   if (e.ldo != c.out_channels) return "the fused depthwise + projection kernel writes dense channel-last rows";
   if ((reinterpret_cast<uintptr_t>(c.x) & 15) != 0 || (static_cast<size_t>(c.C) * 4) % 16 != 0)
@@ -1104,6 +1110,7 @@ std::string tc_plan_dw_project(TcDwProjLaunch* L, const TcDwProjConv& c, const T
   p.pad_t = c.pad_t;
   p.pad_l = c.pad_l;
   p.stages = shape.stages;
+  p.patch_bufs = shape.patches;
   p.b_bytes = shape.b_bytes;
   p.out_bufs = shape.out_bufs;
   p.dw_weights = c.dw_weights;

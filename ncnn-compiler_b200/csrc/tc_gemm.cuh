@@ -525,7 +525,7 @@ __device__ __forceinline__ bool tc_staged_epilogue(const TcStageCfg c, const IO&
     }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-      if (h == 1 && !wide) break;
+      if (h == 1 && (!wide || n0 + c0 + 16 >= c.N)) break;  // (columns past N are clipped by the store)
       uint32_t v[16];
       tmem_ld16(t_row + static_cast<uint32_t>(c0 + 16 * h), v);
       tmem_ld_wait();
