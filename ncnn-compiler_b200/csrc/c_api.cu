@@ -107,9 +107,7 @@ int ncnn_b200_load(const char* param_path, const char* bin_path, const ncnn_b200
       nb::Engine::create(param_path, bin_path != nullptr ? bin_path : "", opt, &err);
   if (!engine) {
     g_load_error = err;
-    return err.rfind("no CUDA device", 0) == 0 || err.find("sm_100a") != std::string::npos
-               ? NCNN_B200_STATUS_RUNTIME
-               : NCNN_B200_STATUS_LOAD;
+    return nb::load_failure_status(err);
   }
   auto* m = new ncnn_b200_model;
   m->engine = std::move(engine);

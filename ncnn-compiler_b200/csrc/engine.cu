@@ -276,11 +276,26 @@ class EngineImpl {
     *err = msg;
     return false;
   }
+  // Every device allocation of the engine.  NCNN_B200_TEST_FAIL_ALLOC=k makes the k-th one of this engine
+  // fail as the driver would when memory runs out (the out-of-memory paths are tested without filling a GPU).
+  cudaError_t device_alloc(void** p, size_t bytes) {
+    const char* env = std::getenv("NCNN_B200_TEST_FAIL_ALLOC");
+    if (env != nullptr && std::atol(env) == ++alloc_count_) {
+      *p = nullptr;
+      return cudaErrorMemoryAllocation;
+    }
+    return cudaMalloc(p, bytes);
+  }
+  long alloc_count_ = 0;
+  bool upload_failed_ = false;
   template <class T>
   T* upload(const std::vector<T>& v) {
     if (v.empty()) return nullptr;
     void* d = nullptr;
-    if (cudaMalloc(&d, v.size() * sizeof(T)) != cudaSuccess) return nullptr;
+    if (device_alloc(&d, v.size() * sizeof(T)) != cudaSuccess) {
+      upload_failed_ = true;  // prepare_weights() reports it: no kernel may ever see the null pointer
+      return nullptr;
+    }
     cudaMemcpy(d, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice);
     device_allocs_.push_back(d);
     return static_cast<T*>(d);
@@ -2019,6 +2034,7 @@ bool EngineImpl::prepare_weights(std::string* err) {
       if (n.d_w0 == nullptr) return fail(err, "out of device memory while uploading weights of " + n.name);
     }
   }
+  if (upload_failed_) return fail(err, "out of device memory while uploading weights");
   // host copies are no longer needed
   for (Node& n : nodes_) {
     std::vector<float>().swap(n.w_f32);
@@ -2184,14 +2200,14 @@ bool EngineImpl::build(const std::string& param, const std::string& bin, const E
   plan_memory();
   if (cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking) != cudaSuccess) return fail(err, "cannot create a stream");
   void* st = nullptr;
-  if (cudaMalloc(&st, 256) != cudaSuccess) return fail(err, "out of device memory");
+  if (device_alloc(&st, 256) != cudaSuccess) return fail(err, "out of device memory");
   cudaMemset(st, 0, 256);
   device_allocs_.push_back(st);
   d_status_ = static_cast<int*>(st);
   // workspace of the contraction kernel that splits tiles between CTA pairs: partial accumulators
   // and one flag word per CTA (zero between launches); all launches of a model run on one stream
   void* ws = nullptr;
-  if (cudaMalloc(&ws, kTcSplitWorkspaceBytes + 4096) != cudaSuccess) return fail(err, "out of device memory");
+  if (device_alloc(&ws, kTcSplitWorkspaceBytes + 4096) != cudaSuccess) return fail(err, "out of device memory");
   cudaMemset(ws, 0, kTcSplitWorkspaceBytes + 4096);
   device_allocs_.push_back(ws);
   d_split_ws_ = static_cast<uint32_t*>(ws);
@@ -2835,7 +2851,7 @@ Plan* EngineImpl::plan_for(int64_t n) {
     if (arena_ != nullptr) cudaFree(arena_);
     arena_ = nullptr;
     void* p = nullptr;
-    if (cudaMalloc(&p, need) != cudaSuccess) {
+    if (device_alloc(&p, need) != cudaSuccess) {
       error_ = "out of device memory for a batch of " + std::to_string(n) + " (" + std::to_string(need >> 20) + " MiB of activations)";
       arena_bytes_ = 0;
       return nullptr;
@@ -2876,20 +2892,23 @@ void EngineImpl::restore_padding(int64_t n, cudaStream_t st) {
 
 bool EngineImpl::ensure_staging(Plan* plan) {
   if (!plan->d_in.empty() || inputs_.empty()) return true;
+  // all or nothing: a plan with part of its staging arrays would pass the test above on the next call
+  auto give_up = [&](const char* what) {
+    for (float* p : plan->d_in) cudaFree(p);
+    for (float* p : plan->d_out) cudaFree(p);
+    plan->d_in.clear();
+    plan->d_out.clear();
+    error_ = std::string("out of device memory for ") + what + " staging";
+    return false;
+  };
   for (int t : inputs_) {
     void* p = nullptr;
-    if (cudaMalloc(&p, tensors_[resolve(t)].logical() * 4 * plan->n) != cudaSuccess) {
-      error_ = "out of device memory for input staging";
-      return false;
-    }
+    if (device_alloc(&p, tensors_[resolve(t)].logical() * 4 * plan->n) != cudaSuccess) return give_up("input");
     plan->d_in.push_back(static_cast<float*>(p));
   }
   for (int t : outputs_) {
     void* p = nullptr;
-    if (cudaMalloc(&p, tensors_[resolve(t)].logical() * 4 * plan->n) != cudaSuccess) {
-      error_ = "out of device memory for output staging";
-      return false;
-    }
+    if (device_alloc(&p, tensors_[resolve(t)].logical() * 4 * plan->n) != cudaSuccess) return give_up("output");
     plan->d_out.push_back(static_cast<float*>(p));
   }
   return true;

@@ -15,6 +15,14 @@
 
 namespace nb {
 
+// Status of a failed load: the device or the runtime let us down (6), or the model was rejected (8).
+inline int load_failure_status(const std::string& err) {
+  for (const char* runtime_sign : {"no CUDA device", "sm_100a", "cannot select", "out of device memory", "cannot create a stream"})
+    if (err.find(runtime_sign) != std::string::npos) return 6;
+  return 8;
+}
+
+
 enum AccuracyMode : int {
   kAccuracyFp32Split = 0,  // tensor cores, operands split into two bf16 (or tf32) terms, 3 MMAs: ~1e-5
   kAccuracyTf32 = 1,       // tensor cores, one tf32 MMA: ~1e-3, reported separately

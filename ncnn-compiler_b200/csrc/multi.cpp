@@ -144,10 +144,7 @@ int ncnn_b200_multi_load(const char* param_path, const char* bin_path, const ncn
     r->engine = nb::Engine::create(param_path, bin_path != nullptr ? bin_path : "", opt, &err);
     if (!r->engine) {
       nb::set_global_error("device " + std::to_string(devices[g]) + ": " + err);
-      return err.rfind("no CUDA device", 0) == 0 || err.find("sm_100a") != std::string::npos ||
-                     err.find("cannot select") != std::string::npos
-                 ? NCNN_B200_STATUS_RUNTIME
-                 : NCNN_B200_STATUS_LOAD;
+      return nb::load_failure_status(err);
     }
     for (int i = 0; i < r->engine->input_count(); ++i)
       r->in_elems.push_back(static_cast<size_t>(r->engine->input_shape(i).elements()));

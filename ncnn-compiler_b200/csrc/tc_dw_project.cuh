@@ -52,7 +52,6 @@ struct TcDwProjParams {
   int res_mode, out_mode, act;
   float act_a, act_b;
   int* status;
-  long long* trace;
 };
 
 // (KIND: the projection's arithmetic; bf16 pairs are the only form built)
@@ -156,14 +155,13 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
     const uint32_t b_tx = 2u * static_cast<uint32_t>(p.block_n) * 64u;
     int s = 0, pb = 0;
     uint32_t ph = 0, p_ph = 0;
-    long long patches = 0, weights = 0, pw = 0;
+    long long patches = 0, weights = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       int img, oy0, ox0, n0;
       decode(tile, &img, &oy0, &ox0, &n0);
       for (int cb = 0; cb < p.c_blocks && ok; ++cb) {
         int w = 1;
-        const long long g0 = clock64();
         if (lane == 0) {
           w = mbar_wait_bounded(smem_u32(&patch_empty[pb]), p_ph ^ 1u, abort_ptr, kTcWaitLimitNs) ? 1 : 0;
           if (w) {
@@ -178,7 +176,6 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
           break;
         }
         ++patches;
-        pw += clock64() - g0;
         if (++pb == P) {
           pb = 0;
           p_ph ^= 1u;
@@ -202,7 +199,6 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
         }
       }
     }
-    if (lane == 0 && p.trace != nullptr && blockIdx.x == gridDim.x / 2) p.trace[8] = pw;
     if (lane == 0) {
       if (!ok) {
         if (atomicCAS(const_cast<int*>(abort_ptr), 0, 1) == 0) atomicCAS(p.status, 0, TC_TIMEOUT_PRODUCER);
@@ -228,27 +224,20 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
       int s = 0, as = 0, acc = 0;
       uint32_t ph = 0, a_ph = 0, acc_ph = 0;
       bool ok = true;
-      const bool tr = p.trace != nullptr && blockIdx.x == gridDim.x / 2;
-      long long m0 = 0, m1 = 0, m2 = 0;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const long long q0 = clock64();
         if (!mbar_wait_bounded(smem_u32(&tempty_bar[acc]), acc_ph ^ 1u, abort_ptr, kTcWaitLimitNs)) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
-        m0 += clock64() - q0;
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * acc_stride;
         uint32_t accumulate = 0u;
         for (int cb = 0; cb < c_blocks; ++cb) {
-          const long long q1 = clock64();
           if (!mbar_wait_bounded(smem_u32(&a_full[as]), a_ph, abort_ptr, kTcWaitLimitNs)) { ok = false; break; }
-          const long long q2 = clock64();
           if (!mbar_wait_bounded(smem_u32(&b_full[s]), ph, abort_ptr, kTcWaitLimitNs)) {
             ok = false;
             break;
           }
-          m1 += q2 - q1; m2 += clock64() - q2;
           tc_fence_after_sync();
           const uint64_t a0 = fixed + (((a_base + static_cast<uint32_t>(as) * a_stage_bytes) & 0x3ffffu) >> 4);
           const uint64_t b0 = fixed + (((b_base + static_cast<uint32_t>(s) * b_stage_bytes) & 0x3ffffu) >> 4);
@@ -275,7 +264,6 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
         acc ^= 1;
         if (acc == 0) acc_ph ^= 1u;
       }
-      if (tr) { p.trace[16] = m0; p.trace[17] = m1; p.trace[18] = m2; }
       if (!ok) {
         if (atomicCAS(const_cast<int*>(abort_ptr), 0, 1) == 0) atomicCAS(p.status, 0, TC_TIMEOUT_MMA);
       }
@@ -302,17 +290,13 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
     int acc = 0, out_slot = 0;
     uint32_t acc_ph = 0, res_ph = 0;
     bool ok = true;
-    const bool tr = p.trace != nullptr && blockIdx.x == gridDim.x / 2 && threadIdx.x == 64;
-    long long e0 = 0, e1 = 0, ecnt = 0;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
       int img, oy0, ox0, n0;
       decode(tile, &img, &oy0, &ox0, &n0);
-      const long long r0 = clock64();
       ok = __all_sync(0xffffffffu,
                       mbar_wait_bounded(smem_u32(&tfull_bar[acc]), acc_ph, abort_ptr, kTcWaitLimitNs) ? 1 : 0) != 0;
       if (!ok) break;
       tc_fence_after_sync();
-      const long long r1 = clock64();
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc) * acc_stride;
       for (int t = static_cast<int>(threadIdx.x) - 64; t < p.block_n; t += 128) {
         const int n = n0 + t;
@@ -337,9 +321,7 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
       if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
       acc ^= 1;
       if (acc == 0) acc_ph ^= 1u;
-      e0 += r1 - r0; e1 += clock64() - r1; ++ecnt;
     }
-    if (tr) { p.trace[24] = e0; p.trace[25] = e1; p.trace[26] = ecnt; }
     if (!ok && lane == 0) {
       if (atomicCAS(const_cast<int*>(abort_ptr), 0, 1) == 0) atomicCAS(p.status, 0, TC_TIMEOUT_EPILOGUE);
     }
@@ -359,9 +341,6 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
     // none / ReLU / clip as one clamp: fminf(fmaxf(y, lo), hi) returns y itself between the bounds
     const float act_lo = p.dw_act == ACT_RELU ? 0.0f : (p.dw_act == ACT_CLIP ? p.dw_act_a : -INFINITY);
     const float act_hi = p.dw_act == ACT_CLIP ? p.dw_act_b : INFINITY;
-    const bool tr = p.trace != nullptr && blockIdx.x == gridDim.x / 2 && t == 0;
-    long long tw0 = 0, tw1 = 0, tw2 = 0, tw3 = 0, tw4 = 0, tcnt = 0;
-    const long long tstart = clock64();
     const uint32_t a_tile = a_base + static_cast<uint32_t>(group) * a_stage_bytes;
     long long item = 0;  // position in the CTA's sequence of (tile, channel block)
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
@@ -370,7 +349,6 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
         const int pb = static_cast<int>(item % P);
         const uint32_t p_ph = static_cast<uint32_t>((item / P) & 1);
         const uint32_t a_ph = static_cast<uint32_t>((item >> 1) & 1);
-        const long long c0 = clock64();
         const uint32_t tc = table + static_cast<uint32_t>(cb * kDwpChannels + quad * 4) * 4u;  // the thread's channels
         float4 tap[9], bias;
 #pragma unroll
@@ -381,7 +359,6 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
         ok = __all_sync(0xffffffffu,
                         mbar_wait_bounded(smem_u32(&patch_full[pb]), p_ph, abort_ptr, kTcWaitLimitNs) ? 1 : 0) != 0;
         if (!ok) break;
-        const long long c1 = clock64();
         const uint32_t patch = patch_base + static_cast<uint32_t>(pb) * kDwpPatchBytes;
         float4 acc[8];
 #pragma unroll
@@ -412,12 +389,10 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
         // the patch has been read: the producer may refill it
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&patch_empty[pb]));
-        const long long c2 = clock64();
         // the group's operand tile, filled two blocks ago, must have been consumed by its MMAs
         ok = __all_sync(0xffffffffu,
                         mbar_wait_bounded(smem_u32(&a_empty[group]), a_ph ^ 1u, abort_ptr, kTcWaitLimitNs) ? 1 : 0) != 0;
         if (!ok) break;
-        const long long c3 = clock64();
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
           float4 y;
@@ -435,17 +410,11 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
           asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(at), "r"(hi0), "r"(hi1) : "memory");
           asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(at + kDwpAPlaneBytes), "r"(mid0), "r"(mid1) : "memory");
         }
-        const long long c3a = clock64();
         fence_proxy_async_smem();  // the tensor core reads what these stores wrote
-        const long long c3b = clock64();
-        tw4 += c3b - c3a;
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&a_full[group]));
-        const long long c4 = clock64();
-        tw0 += c1 - c0; tw1 += c2 - c1; tw2 += c3 - c2; tw3 += c4 - c3; ++tcnt;
       }
     }
-    if (tr) { p.trace[0] = tw0; p.trace[1] = tw1; p.trace[2] = tw2; p.trace[3] = tw3; p.trace[4] = tcnt; p.trace[5] = clock64() - tstart; p.trace[6] = tw4; }
     if (!ok && lane == 0) {
       if (atomicCAS(const_cast<int*>(abort_ptr), 0, 1) == 0) atomicCAS(p.status, 0, TC_TIMEOUT_EPILOGUE);
     }

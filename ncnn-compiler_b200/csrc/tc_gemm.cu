@@ -1156,22 +1156,6 @@ cudaError_t tc_launch_dw_project(const TcDwProjLaunch& L, cudaStream_t stream) {
   });
   if (attr_err != cudaSuccess) return attr_err;
   KernelLaunchConfig lc(L.grid, kDwpThreads, L.smem_bytes, false, stream);
-  static long long* d_trace = nullptr;
-  cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
-  cudaStreamIsCapturing(stream, &cs);
-  if (std::getenv("NCNN_B200_DWP_TRACE") != nullptr && cs == cudaStreamCaptureStatusNone) {
-    if (d_trace == nullptr) cudaMalloc(&d_trace, 64 * 8);
-    cudaMemsetAsync(d_trace, 0, 64 * 8, stream);
-    TcDwProjLaunch T = L;
-    T.p.trace = d_trace;
-    cudaLaunchKernelEx(&lc.cfg, tc_dw_project_kernel<GEMM_BF16X3>, T.p, T.map_x, T.map_b0, T.map_b1, T.map_o0, T.map_o1, T.map_r0, T.map_r1);
-    cudaStreamSynchronize(stream);
-    long long h[64];
-    cudaMemcpy(h, d_trace, sizeof(h), cudaMemcpyDeviceToHost);
-    std::fprintf(stderr, "DWP C=%d N=%d HxW=%dx%d cblocks=%d grid=%d smem=%d | dw: n=%lld wait_patch=%lld compute=%lld wait_a=%lld store=%lld (fence %lld) total=%lld | prod wait=%lld | mma: tempty=%lld a_full=%lld b_full=%lld | epi: n=%lld wait=%lld run=%lld\n",
-                 L.p.C, L.p.N, L.p.H, L.p.W, L.p.c_blocks, L.grid, L.smem_bytes, h[4], h[0], h[1], h[2], h[3], h[6], h[5], h[8], h[16], h[17], h[18], h[26], h[24], h[25]);
-    return cudaSuccess;
-  }
   const cudaError_t e = cudaLaunchKernelEx(&lc.cfg, tc_dw_project_kernel<GEMM_BF16X3>, L.p, L.map_x, L.map_b0, L.map_b1, L.map_o0,
                                            L.map_o1, L.map_r0, L.map_r1);
   return e != cudaSuccess ? e : cudaGetLastError();

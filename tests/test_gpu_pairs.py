@@ -361,3 +361,46 @@ def test_depthwise_projection_block_shapes(pkg, oracle, tmp_path, monkeypatch, h
     assert np.array_equal(got, base)
     want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x])
     assert rel_l2(got, want) <= 1e-4
+
+
+# ------------------------------------------------------------------ device allocations that fail
+def test_every_failed_device_allocation_is_reported_and_leaves_nothing_behind(pkg, oracle, tmp_path, monkeypatch):
+    """NCNN_B200_TEST_FAIL_ALLOC=k makes the k-th device allocation of an engine return the driver's
+    out-of-memory error (no GPU is filled up for this).  Whichever allocation it is - weights, the status word,
+    the split workspace, the activation arena, the staging arrays of the host-pointer entry - the call that
+    needed it fails with status 6 and an out-of-memory message, no kernel ever sees a null pointer, the same
+    engine works once memory "is back", and the device has as much free memory afterwards as before."""
+    import torch
+    param, bin_ = pkg.zoo.conv_batchnorm(str(tmp_path / "blk"))
+    x = np.random.default_rng(5).uniform(-1, 1, (3, 64, 14, 14)).astype(np.float32)
+    want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x])
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    failures_at_load = failures_at_run = 0
+    for k in range(1, 60):
+        monkeypatch.setenv("NCNN_B200_TEST_FAIL_ALLOC", str(k))
+        try:
+            m = pkg.Model(param, bin_)
+        except pkg.NcnnB200Error as e:
+            assert e.status == 6 and "memory" in e.message, (k, e.message)
+            failures_at_load += 1
+            continue
+        try:
+            got = m.run(x)[0]
+        except pkg.NcnnB200Error as e:
+            assert e.status == 6 and "memory" in e.message, (k, e.message)
+            failures_at_run += 1
+            monkeypatch.delenv("NCNN_B200_TEST_FAIL_ALLOC")
+            got = m.run(x)[0]  # the same engine, now that allocations succeed
+            assert rel_l2(got, want) <= 1e-4
+            m.close()
+            continue
+        assert rel_l2(got, want) <= 1e-4  # k is past the last allocation: nothing failed
+        m.close()
+        break
+    else:
+        raise AssertionError("allocations never ran out")
+    assert failures_at_load >= 3 and failures_at_run >= 2, (failures_at_load, failures_at_run)
+    monkeypatch.delenv("NCNN_B200_TEST_FAIL_ALLOC", raising=False)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] >= free_before - (8 << 20)
