@@ -100,9 +100,22 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
         TcDwProjConv dc;
         dc.x = in.p0;
         dc.images = static_cast<int>(n);
-        dc.H = ti.h;
-        dc.W = ti.w;
-        dc.C = ti.c;
+        dc.H = node.OH;
+        dc.W = node.OW;
+        dc.Hin = node.dw_hin;
+        dc.Win = node.dw_win;
+        dc.C = node.dw_c;
+        dc.stride = node.dw_stride;
+        if (node.ex_fused) {
+          dc.Cin = node.ex_cin;
+          dc.x1 = in.p1;
+          dc.ex_w0 = node.ex_w0;
+          dc.ex_w1 = node.ex_w1;
+          dc.ex_bias = node.ex_bias;
+          dc.ex_act = node.ex_act;
+          dc.ex_act_a = node.ex_act_a;
+          dc.ex_act_b = node.ex_act_b;
+        }
         dc.pad_t = node.dw_pt;
         dc.pad_l = node.dw_pl;
         dc.dw_weights = node.dw_w;
@@ -116,8 +129,9 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
         auto dl = std::make_shared<TcDwProjLaunch>();
         const std::string derr = tc_plan_dw_project(dl.get(), dc, te, sm_count_);
         if (!derr.empty()) return fail(err, "layers " + node.dw_name + " + " + node.name + ": " + derr);
-        s.name = node.dw_name + "+" + node.name;
-        s.kernel = "tc_dw_project_kernel<bf16x3>";
+        s.name = (node.ex_fused ? node.ex_name + "+" : std::string()) + node.dw_name + "+" + node.name;
+        s.kernel = node.ex_fused ? (node.dw_stride == 2 ? "tc_dw_project_kernel:expand+stride2<bf16x3>" : "tc_dw_project_kernel:expand<bf16x3>")
+                                 : "tc_dw_project_kernel<bf16x3>";
         s.run = [dl](cudaStream_t st) { return tc_launch_dw_project(*dl, st); };
         plan.steps.push_back(std::move(s));
         return true;

@@ -103,7 +103,18 @@ struct Node {
   int dw_act = ACT_NONE;
   float dw_act_a = 0.0f, dw_act_b = 0.0f;
   int dw_pt = 1, dw_pl = 1;
+  int dw_stride = 1;
+  int dw_c = 0, dw_hin = 0, dw_win = 0;  // channels and input extent of the depthwise layer
   std::string dw_name;
+  // the 1x1 expand convolution in front of that depthwise layer, merged into the projection node by the same pass
+  bool ex_fused = false;
+  const void* ex_w0 = nullptr;
+  const void* ex_w1 = nullptr;
+  const float* ex_bias = nullptr;
+  int ex_act = ACT_NONE;
+  float ex_act_a = 0.0f, ex_act_b = 0.0f;
+  int ex_cin = 0;
+  std::string ex_name;
 };
 
 struct Step {
@@ -339,5 +350,16 @@ inline int halo_level() {
   return f == nullptr || f[0] == 0 ? 0 : std::atoi(f);
 }
 inline bool halo_preferred() { return halo_level() >= 1; }
+
+inline int env_int_or(const char* name, int fallback) {
+  const char* f = std::getenv(name);
+  return f == nullptr || f[0] == 0 ? fallback : std::atoi(f);
+}
+
+// NAME=0 in the environment switches an optional pass off
+inline bool env_flag_off(const char* name) {
+  const char* f = std::getenv(name);
+  return f != nullptr && f[0] == '0';
+}
 
 }  // namespace nb

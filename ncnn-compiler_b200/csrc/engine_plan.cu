@@ -275,29 +275,51 @@ void EngineImpl::fuse_quantize_steps() {
 // an inverted-residual block) runs inside that convolution's kernel: its result goes from the CUDA cores
 // into the shared-memory operand tile of the MMAs and never to HBM.  The values, their bf16 split and the
 // order of the products are those of the two separate layers.  NCNN_B200_FUSE_DW=0 keeps them apart.
+// Where the depthwise input itself comes from a 1x1 convolution with at most 32 input channels and no other
+// consumer (the "expand" layer of the block; its bf16 weights are already packed as 64-byte rows of 32 input
+// channels, which is what the fused kernel multiplies a patch by), that layer joins too, for depthwise strides
+// 1 and 2: the whole block is one kernel and the expanded tensor never exists in HBM.  NCNN_B200_FUSE_EXPAND=0
+// leaves the expand layers alone.
 void EngineImpl::fuse_depthwise_projection() {
   const char* env = std::getenv("NCNN_B200_FUSE_DW");
-  if (env != nullptr && env[0] == '0') return;
-  if (opt_.accuracy_mode != kAccuracyFp32Split) return;
+  const bool enabled = !(env != nullptr && env[0] == '0') && opt_.accuracy_mode == kAccuracyFp32Split;
   std::vector<int> uses(tensors_.size(), 0);
   for (const Node& n : nodes_) {
     for (int t : n.in) ++uses[resolve(t)];
     if (n.res >= 0) ++uses[resolve(n.res)];
-    for (const auto& side : n.side_q) (void)side;
   }
   for (int o : outputs_) ++uses[resolve(o)];
-  for (size_t k = 0; k + 1 < nodes_.size(); ++k) {
+  for (size_t k = 0; enabled && k + 1 < nodes_.size(); ++k) {
     const Node& dw = nodes_[k];
-    if (dw.kind != N_DW || dw.term != 0 || dw.KH != 3 || dw.KW != 3 || dw.sh != 1 || dw.sw != 1 || dw.dh != 1 ||
+    if (dw.kind != N_DW || dw.term != 0 || dw.KH != 3 || dw.KW != 3 || dw.sh != dw.sw || dw.dh != 1 ||
         dw.dw != 1 || dw.res >= 0 || !dw.side_q.empty() || dw.d_w0 == nullptr)
       continue;
     const int mid = resolve(dw.out);
     const int src = resolve(dw.in[0]);
     const Tensor& tin = tensors_[src];
     const Tensor& tmid = tensors_[mid];
+    // the producer of the depthwise input, when it qualifies as the block's expand layer
+    int je = -1;
+    for (size_t j = 0; j < k && !env_flag_off("NCNN_B200_FUSE_EXPAND"); ++j) {
+      const Node& ex = nodes_[j];
+      if (resolve(ex.out) != src) continue;
+      const bool clamp = ex.act == ACT_NONE || ex.act == ACT_RELU || ex.act == ACT_CLIP;
+      if (ex.kind == N_CONV && ex.impl == IMPL_TC && ex.term == 0 && !ex.stem && ex.out_ld == 0 && ex.KH == 1 && ex.KW == 1 &&
+          ex.sh == 1 && ex.sw == 1 && ex.pt == 0 && ex.pl == 0 && ex.res < 0 && ex.side_q.empty() && clamp && uses[src] == 1 &&
+          ex.k_elems == 32 && ex.d_w0 != nullptr && ex.d_w1 != nullptr)
+        je = static_cast<int>(j);
+    }
+    // Measured on MobileNetV2 at batch 256: with the expand layer inside, stride-2 blocks are 10-16 % faster than
+    // their three layers (the expanded tensor is four times the block's output), stride-1 blocks 35 % slower than
+    // expand + fused pair (per block of 32 channels the kernel then runs 12 more MMAs and a TMEM read-back on top of
+    // the depthwise arithmetic).  So stride-1 blocks join only with NCNN_B200_FUSE_EXPAND=2.
+    if (je >= 0 && dw.sh == 1 && env_int_or("NCNN_B200_FUSE_EXPAND", 1) < 2) je = -1;
+    if (je < 0 && dw.sh != 1) continue;
+    if (dw.sh != 1 && dw.sh != 2) continue;
     if (uses[mid] != 1 || tin.rank != 3 || tin.fmt != FMT_F32 || tin.Cp != tin.c || tin.Wp != tin.w || tin.w_off != 0 ||
-        tmid.fmt != FMT_BF16X2 || dw.OH != tin.h || dw.OW != tin.w || dw.pt > 2 || dw.pl > 2)
+        tmid.fmt != FMT_BF16X2 || dw.pt > 2 || dw.pl > 2)
       continue;
+    if (dw.sh == 1 && (dw.OH != tin.h || dw.OW != tin.w)) continue;
     // the consumer: the next node that reads the depthwise result
     size_t j = k + 1;
     for (; j < nodes_.size(); ++j)
@@ -314,7 +336,14 @@ void EngineImpl::fuse_depthwise_projection() {
     const bool res_bf16 = has_res && tensors_[resolve(pw.res)].fmt == FMT_BF16X2;
     if (has_res && !res_bf16 && tensors_[resolve(pw.res)].fmt != FMT_F32) continue;
     if (dw.act != ACT_NONE && dw.act != ACT_RELU && dw.act != ACT_CLIP) continue;  // the fused kernel clamps, nothing else
-    if (!tc_dw_project_applies(tin.c, pw.O, tin.h, tin.w, out_mode, has_res, res_bf16)) continue;
+    if (je >= 0) {
+      const Node& ex = nodes_[je];
+      const Tensor& tx = tensors_[resolve(ex.in[0])];
+      if (tx.rank != 3 || tx.fmt != FMT_BF16X2 || tx.Cp != tx.c || tx.Wp != tx.w || tx.w_off != 0 ||
+          !tc_block_applies(tx.c, ex.O, pw.O, dw.OH, dw.OW, dw.sh, has_res))
+        je = -1;  // (the depthwise layer and the projection may still pair up)
+    }
+    if (je < 0 && (dw.sh != 1 || !tc_dw_project_applies(tin.c, pw.O, tin.h, tin.w, out_mode, has_res, res_bf16))) continue;
     pw.dw_fused = true;
     pw.dw_w = static_cast<const float*>(dw.d_w0);
     pw.dw_bias = dw.d_bias;
@@ -323,11 +352,30 @@ void EngineImpl::fuse_depthwise_projection() {
     pw.dw_act_b = dw.act_b;
     pw.dw_pt = dw.pt;
     pw.dw_pl = dw.pl;
+    pw.dw_stride = dw.sh;
+    pw.dw_c = tin.c;
+    pw.dw_hin = tin.h;
+    pw.dw_win = tin.w;
     pw.dw_name = dw.name;
     pw.in[0] = dw.in[0];
     pw.flops += dw.flops;
+    if (je >= 0) {
+      Node& ex = nodes_[je];
+      pw.ex_fused = true;
+      pw.ex_w0 = ex.d_w0;
+      pw.ex_w1 = ex.d_w1;
+      pw.ex_bias = ex.d_bias;
+      pw.ex_act = ex.act;
+      pw.ex_act_a = ex.act_a;
+      pw.ex_act_b = ex.act_b;
+      pw.ex_cin = tensors_[resolve(ex.in[0])].c;
+      pw.ex_name = ex.name;
+      pw.in[0] = ex.in[0];
+      pw.flops += ex.flops;
+    }
     nodes_.erase(nodes_.begin() + k);
-    --k;
+    if (je >= 0) nodes_.erase(nodes_.begin() + je);  // (je < k: the index is still valid)
+    k -= je >= 0 ? 2 : 1;
   }
 }
 

@@ -1036,53 +1036,92 @@ cudaError_t tc_launch_halo(const TcHaloLaunch& L, cudaStream_t stream) {
 namespace {
 
 struct DwProjShape {
-  int block_n = 0, tiles_n = 0, stages = 0, out_bufs = 0, patches = 0, b_bytes = 0, smem = 0;
+  int block_n = 0, tiles_n = 0, stages = 0, out_bufs = 0, patches = 0, b_bytes = 0, x_plane_bytes = 0, x_bufs = 0, smem = 0;
   bool ok = false;
 };
 
-DwProjShape dw_project_shape(int N, int out_mode, int res_mode, int C) {
+// Shared-memory plan of tc_dw_project_kernel.  expand: the expand layer is fused in (input patches as bf16 planes
+// of 64-byte rows, one fp32 patch per depthwise group, the block's expand weights beside its projection weights in
+// every ring stage, the expand bias beside the depthwise table).
+DwProjShape dw_project_shape(int N, int out_mode, int res_mode, int C, int stride, bool expand) {
   DwProjShape r;
   const bool wide = out_mode == OUT_BF16X2 || res_mode == RES_BF16X2;
   if (out_mode != OUT_BF16X2 && out_mode != OUT_F32) return r;
   if (wide && res_mode == RES_SPLIT) return r;
+  if (stride != 1 && stride != 2) return r;
+  if (stride == 2 && !expand) return r;  // (patches loaded by TMA are built for stride 1 only)
   const int step = wide ? 32 : 16;
   const int n_tiles = (N + 255) / 256;
   r.block_n = ((N + n_tiles - 1) / n_tiles + step - 1) / step * step;
   if (r.block_n > 256 || r.block_n % 16 != 0) return r;
+  if (expand && r.block_n > 128) return r;  // (the expand accumulators take the TMEM columns past two 128-column ones)
   r.tiles_n = (N + r.block_n - 1) / r.block_n;
   r.b_bytes = (r.block_n * 64 + 1023) / 1024 * 1024;
   const int out_tile = wide ? 16384 : 8192;
   const int budget = 222 * 1024;  // the kernel's own static shared memory is ~2 KB
+  const int c_pad = (C + kDwpChannels - 1) / kDwpChannels * kDwpChannels;
+  const int table = (c_pad * (expand ? 11 : 10) * 4 + 1023) / 1024 * 1024;  // depthwise filter and bias (+ expand bias)
+  const int stage = 2 * r.b_bytes + (expand ? 4096 : 0);
+  r.x_plane_bytes = expand ? (dwp_patch_pixels(stride) * 64 + 1023) / 1024 * 1024 : 0;
   // Deep patch ring first (a patch load outlasts one block's arithmetic), then three weight stages, then
-  // output staging tiles; the last resort is two of each.
-  for (int min_stages : {3, 2})
-    for (int patches : {4, 3, 2})
-      for (int bufs : {4, 3, 2}) {
-        const int table = ((C + kDwpChannels - 1) / kDwpChannels * kDwpChannels * 10 * 4 + 1023) / 1024 * 1024;  // depthwise filter + bias
-        const int fixed = patches * kDwpPatchBytes + 2 * 2 * kDwpAPlaneBytes + (res_mode != RES_NONE ? 16384 : 0) + table;
-        const int stages = std::min(kDwpMaxStages, (budget - fixed - bufs * out_tile) / (2 * r.b_bytes));
-        if (stages >= min_stages) {
-          r.stages = stages;
-          r.out_bufs = bufs;
-          r.patches = patches;
-          r.smem = fixed + bufs * out_tile + stages * 2 * r.b_bytes + 1024;
-          r.ok = true;
-          return r;
+  // output staging tiles; the last resort is two of each.  With the expand layer: two input patch buffers if they
+  // fit, and never fewer than three stages (the expand MMAs run two blocks ahead of the projection's).
+  for (int min_stages : {4, 3, 2}) {
+    if (expand ? min_stages < 3 : min_stages > 3) continue;  // (without the expand layer three stages are plenty)
+    for (int x_bufs : {2, 1}) {
+      if (!expand && x_bufs != 2) continue;
+      for (int patches : {4, 3, 2}) {
+        if (expand && patches != 2) continue;
+        for (int bufs : {4, 3, 2}) {
+          if (expand && bufs == 4) continue;
+          const int fixed = (expand ? x_bufs * 2 * r.x_plane_bytes : 0) + patches * dwp_patch_bytes(stride) +
+                            2 * 2 * dwp_a_plane_bytes(stride) + (res_mode != RES_NONE ? 16384 : 0) + table;
+          const int stages = std::min(kDwpMaxStages, (budget - fixed - bufs * out_tile) / stage);
+          if (stages >= min_stages) {
+            r.stages = stages;
+            r.out_bufs = bufs;
+            r.patches = patches;
+            r.x_bufs = expand ? x_bufs : 0;
+            r.smem = fixed + bufs * out_tile + stages * stage + 1024;
+            r.ok = true;
+            return r;
+          }
         }
       }
+    }
+  }
   return r;
+}
+
+// an image that fills less than 60 % of its tiles (7 x 7 fills 38 % of a 16 x 8 tile) is faster as separate layers
+bool dw_project_fills(int H, int W, int stride) {
+  const int th = dwp_tile_h(stride);
+  const int tiles = ((H + th - 1) / th) * ((W + kDwpTileW - 1) / kDwpTileW);
+  return env_int("NCNN_B200_FUSE_DW", 1) >= 2 || static_cast<long long>(H) * W * 10 >= 6ll * tiles * th * kDwpTileW;
 }
 
 }  // namespace
 
 bool tc_dw_project_applies(int C, int N, int H, int W, int out_mode, bool has_res, bool res_bf16) {
   if (C % 4 != 0 || C < 8 || N % 8 != 0 || H < 1 || W < 1) return false;
-  // 16 x 8 pixel tiles: an image that fills less than 60 % of its tiles (7 x 7 fills 38 %) is faster as two layers
-  const int tiles = ((H + kDwpTileH - 1) / kDwpTileH) * ((W + kDwpTileW - 1) / kDwpTileW);
-  if (env_int("NCNN_B200_FUSE_DW", 1) < 2 && static_cast<long long>(H) * W * 10 < 6ll * tiles * kDwpTileH * kDwpTileW) return false;
+  if (!dw_project_fills(H, W, 1)) return false;
   const int res_mode = !has_res ? RES_NONE : (res_bf16 ? RES_BF16X2 : RES_F32);
   if (out_mode == OUT_F32 && N % 4 != 0) return false;
-  return dw_project_shape(N, out_mode, res_mode, C).ok;
+  return dw_project_shape(N, out_mode, res_mode, C, 1, false).ok;
+}
+
+bool tc_block_applies(int Cin, int C, int N, int OH, int OW, int stride, bool has_res) {
+  if (Cin < 8 || Cin > 32 || Cin % 8 != 0 || C % 8 != 0 || C < 32 || N % 8 != 0 || OH < 1 || OW < 1) return false;
+  if (has_res && stride != 1) return false;
+  if (!dw_project_fills(OH, OW, stride)) return false;
+  // whatever formats the planner gives the output and the residual later
+  for (int out_mode : {OUT_F32, OUT_BF16X2})
+    for (int res_mode : {RES_NONE, RES_F32, RES_BF16X2}) {
+      if (!has_res && res_mode != RES_NONE) continue;
+      if (has_res && res_mode == RES_NONE) continue;
+      if (!dw_project_shape(N, out_mode, res_mode, C, stride, true).ok) return false;
+    }
+  return true;
 }
 
 std::string tc_plan_dw_project(TcDwProjLaunch* L, const TcDwProjConv& c, const TcEpilogue& e, int sm_count) {
@@ -1091,18 +1130,25 @@ std::string tc_plan_dw_project(TcDwProjLaunch* L, const TcDwProjConv& c, const T
   TcDwProjParams& p = L->p;
   std::memset(&p, 0, sizeof(p));
   const int res_mode = e.res0 == nullptr ? RES_NONE : (e.res_bf16 ? RES_BF16X2 : (e.res1 != nullptr ? RES_SPLIT : RES_F32));
-  const DwProjShape shape = dw_project_shape(c.out_channels, e.out_mode, res_mode, c.C);
-  if (!shape.ok) return "the fused depthwise + projection kernel does not take this output format or width";
+  const bool expand = c.ex_w0 != nullptr;
+  const int stride = c.stride;
+  const DwProjShape shape = dw_project_shape(c.out_channels, e.out_mode, res_mode, c.C, stride, expand);
+  if (!shape.ok) return "the fused depthwise + projection kernel does not take this output format, width or stride";
   if (e.ldo != c.out_channels) return "the fused depthwise + projection kernel writes dense channel-last rows";
-  if ((reinterpret_cast<uintptr_t>(c.x) & 15) != 0 || (static_cast<size_t>(c.C) * 4) % 16 != 0)
-    return "depthwise input rows must be 16-byte aligned";
+  const int x_channels = expand ? c.Cin : c.C;
+  if ((reinterpret_cast<uintptr_t>(c.x) & 15) != 0 || (static_cast<size_t>(x_channels) * (expand ? 2 : 4)) % 16 != 0 ||
+      (expand && (c.x1 == nullptr || (reinterpret_cast<uintptr_t>(c.x1) & 15) != 0)))
+    return "input rows of the fused kernel must be 16-byte aligned";
   const bool out_bf16 = e.out_mode == OUT_BF16X2;
+  const int th = dwp_tile_h(stride);
   p.images = c.images;
   p.H = c.H;
   p.W = c.W;
+  p.Hin = c.Hin;
+  p.Win = c.Win;
   p.C = c.C;
   p.N = c.out_channels;
-  p.tiles_y = (c.H + kDwpTileH - 1) / kDwpTileH;
+  p.tiles_y = (c.H + th - 1) / th;
   p.tiles_x = (c.W + kDwpTileW - 1) / kDwpTileW;
   p.block_n = shape.block_n;
   p.tiles_n = shape.tiles_n;
@@ -1118,6 +1164,14 @@ std::string tc_plan_dw_project(TcDwProjLaunch* L, const TcDwProjConv& c, const T
   p.dw_act = c.dw_act;
   p.dw_act_a = c.dw_act_a;
   p.dw_act_b = c.dw_act_b;
+  p.Cin = expand ? c.Cin : 0;
+  p.x_plane_bytes = shape.x_plane_bytes;
+  p.x_bufs = shape.x_bufs;
+  p.ex_ksteps = expand ? (c.Cin + 15) / 16 : 0;
+  p.ex_bias = c.ex_bias;
+  p.ex_act = c.ex_act;
+  p.ex_act_a = c.ex_act_a;
+  p.ex_act_b = c.ex_act_b;
   p.bias = e.bias;
   p.res_mode = res_mode;
   p.out_mode = e.out_mode;
@@ -1125,13 +1179,23 @@ std::string tc_plan_dw_project(TcDwProjLaunch* L, const TcDwProjConv& c, const T
   p.act_a = e.act_a;
   p.act_b = e.act_b;
   p.status = e.status;
+  L->stride = stride;
+  L->expand = expand;
   L->smem_bytes = std::max(shape.smem, 120 * 1024);
   const long long tiles = static_cast<long long>(c.images) * p.tiles_y * p.tiles_x * p.tiles_n;
   if (tiles > 0x7fffffffll) return "too many tiles for one launch";
   L->grid = static_cast<int>(std::min<long long>(tiles, sm_count));
-  // fp32 input patches: [image][H][W][C], boxes of 32 channels x 10 x 18 pixels, dense in shared memory
-  std::string err = encode_tiled_4d(&L->map_x, false, c.x, c.C, c.W, c.H, c.images, kDwpChannels, kDwpPatchW, kDwpPatchH,
-                                    CU_TENSOR_MAP_SWIZZLE_NONE);
+  // input patches, [image][Hin][Win][channels], boxes of 32 channels x patch width x patch height: fp32 and dense
+  // in shared memory for the depthwise filter; with the expand layer fused in, the bf16 planes of the block's input
+  // as 64-byte-swizzled operand rows (channels past Cin read as zero)
+  std::string err = encode_tiled_4d(&L->map_x, expand, c.x, x_channels, c.Win, c.Hin, c.images, kDwpChannels, dwp_patch_w(stride),
+                                    dwp_patch_h(stride), expand ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (err.empty() && expand)
+    err = encode_tiled_4d(&L->map_x1, true, c.x1, x_channels, c.Win, c.Hin, c.images, kDwpChannels, dwp_patch_w(stride),
+                          dwp_patch_h(stride), CU_TENSOR_MAP_SWIZZLE_64B);
+  // expand weights: [C][32] bf16 per plane, one block of 32 rows per copy
+  if (err.empty() && expand) err = encode_tiled_2d(&L->map_e0, GEMM_BF16X3, c.ex_w0, 32, c.C, 64, 32, kDwpChannels, 64);
+  if (err.empty() && expand) err = encode_tiled_2d(&L->map_e1, GEMM_BF16X3, c.ex_w1, 32, c.C, 64, 32, kDwpChannels, 64);
   if (!err.empty()) return err;
   const uint64_t k_total = static_cast<uint64_t>(p.c_blocks) * kDwpChannels;
   err = encode_tiled_2d(&L->map_b0, GEMM_BF16X3, c.w0, k_total, c.out_channels, k_total * 2, kDwpChannels, p.block_n, 64);
@@ -1139,7 +1203,7 @@ std::string tc_plan_dw_project(TcDwProjLaunch* L, const TcDwProjConv& c, const T
     err = encode_tiled_2d(&L->map_b1, GEMM_BF16X3, c.w1, k_total, c.out_channels, k_total * 2, kDwpChannels, p.block_n, 64);
   if (!err.empty()) return err;
   auto plane = [&](CUtensorMap* map, const void* base, bool bf16) {
-    return encode_tiled_4d(map, bf16, base, c.out_channels, c.W, c.H, c.images, bf16 ? 32 : 16, kDwpTileW, kDwpTileH,
+    return encode_tiled_4d(map, bf16, base, c.out_channels, c.W, c.H, c.images, bf16 ? 32 : 16, kDwpTileW, th,
                            CU_TENSOR_MAP_SWIZZLE_64B);
   };
   err = plane(&L->map_o0, e.out0, out_bf16);
@@ -1152,12 +1216,20 @@ std::string tc_plan_dw_project(TcDwProjLaunch* L, const TcDwProjConv& c, const T
 cudaError_t tc_launch_dw_project(const TcDwProjLaunch& L, cudaStream_t stream) {
   static PerDeviceOnce attr_once;
   const cudaError_t attr_err = attr_once.run([] {
-    return cudaFuncSetAttribute(tc_dw_project_kernel<GEMM_BF16X3>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(tc_dw_project_kernel<GEMM_BF16X3, 1, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(tc_dw_project_kernel<GEMM_BF16X3, 1, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(tc_dw_project_kernel<GEMM_BF16X3, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
+    return e;
   });
   if (attr_err != cudaSuccess) return attr_err;
   KernelLaunchConfig lc(L.grid, kDwpThreads, L.smem_bytes, false, stream);
-  const cudaError_t e = cudaLaunchKernelEx(&lc.cfg, tc_dw_project_kernel<GEMM_BF16X3>, L.p, L.map_x, L.map_b0, L.map_b1, L.map_o0,
-                                           L.map_o1, L.map_r0, L.map_r1);
+  cudaError_t e;
+  if (!L.expand)
+    e = cudaLaunchKernelEx(&lc.cfg, tc_dw_project_kernel<GEMM_BF16X3, 1, false>, L.p, L.map_x, L.map_x1, L.map_e0, L.map_e1, L.map_b0, L.map_b1, L.map_o0, L.map_o1, L.map_r0, L.map_r1);
+  else if (L.stride == 1)
+    e = cudaLaunchKernelEx(&lc.cfg, tc_dw_project_kernel<GEMM_BF16X3, 1, true>, L.p, L.map_x, L.map_x1, L.map_e0, L.map_e1, L.map_b0, L.map_b1, L.map_o0, L.map_o1, L.map_r0, L.map_r1);
+  else
+    e = cudaLaunchKernelEx(&lc.cfg, tc_dw_project_kernel<GEMM_BF16X3, 2, true>, L.p, L.map_x, L.map_x1, L.map_e0, L.map_e1, L.map_b0, L.map_b1, L.map_o0, L.map_o1, L.map_r0, L.map_r1);
   return e != cudaSuccess ? e : cudaGetLastError();
 }
 

@@ -157,7 +157,10 @@ cudaError_t tc_launch_halo(const TcHaloLaunch& launch, cudaStream_t stream);
 // ---- 3x3 depthwise convolution fused into the following 1x1 convolution (tc_dw_project.cuh)
 struct TcDwProjLaunch {
   TcDwProjParams p{};
-  alignas(64) CUtensorMap map_x{};   // fp32 depthwise input, patches of 18 x 10 pixels x 32 channels
+  alignas(64) CUtensorMap map_x{};   // fp32 depthwise input, patches of 18 x 10 pixels x 32 channels (expand fused in: bf16 hi plane of the block's input)
+  alignas(64) CUtensorMap map_x1{};  // expand fused in: bf16 mid plane of the block's input
+  alignas(64) CUtensorMap map_e0{};  // expand weights, bf16 hi / mid planes
+  alignas(64) CUtensorMap map_e1{};
   alignas(64) CUtensorMap map_b0{};  // projection weights, bf16 hi / mid planes
   alignas(64) CUtensorMap map_b1{};
   alignas(64) CUtensorMap map_o0{};
@@ -166,12 +169,24 @@ struct TcDwProjLaunch {
   alignas(64) CUtensorMap map_r1{};
   int grid = 0;
   int smem_bytes = 0;
+  int stride = 1;
+  bool expand = false;
 };
 
 struct TcDwProjConv {
-  const float* x = nullptr;  // plain fp32 NHWC input of the depthwise layer
-  int images = 0, H = 0, W = 0, C = 0;
+  const void* x = nullptr;   // NHWC input: plain fp32 of the depthwise layer, or (expand fused in) the bf16 hi plane of the expand layer's
+  const void* x1 = nullptr;  // expand fused in: the bf16 mid plane
+  int images = 0, H = 0, W = 0, C = 0;  // depthwise output extent, depthwise channels
+  int Hin = 0, Win = 0;                 // depthwise input extent
+  int stride = 1;
   int pad_t = 1, pad_l = 1;
+  // expand layer fused in (ex_w0 != nullptr): 1x1 convolution Cin -> C on bf16 pairs, Cin <= 32
+  int Cin = 0;
+  const void* ex_w0 = nullptr;        // packed [C][32] bf16 hi / mid
+  const void* ex_w1 = nullptr;
+  const float* ex_bias = nullptr;     // [C] or null
+  int ex_act = ACT_NONE;
+  float ex_act_a = 0.0f, ex_act_b = 0.0f;
   const float* dw_weights = nullptr;  // [9][C]
   const float* dw_bias = nullptr;
   int dw_act = ACT_NONE;
@@ -184,6 +199,10 @@ struct TcDwProjConv {
 // True when the fused kernel takes the pair of layers: 3x3, stride 1, dilation 1, output extent equal to the
 // input's, channels in fours; projection 1x1 stride 1 with bf16-pair operands and a staged epilogue.
 bool tc_dw_project_applies(int C, int N, int H, int W, int out_mode, bool has_res, bool res_bf16);
+// True when the whole inverted-residual block (1x1 expand Cin -> C with at most 32 input channels, 3x3 depthwise of
+// stride 1 or 2 with output OH x OW, 1x1 projection C -> N) fits the fused kernel, whatever formats its output and
+// residual get.
+bool tc_block_applies(int Cin, int C, int N, int OH, int OW, int stride, bool has_res);
 std::string tc_plan_dw_project(TcDwProjLaunch* launch, const TcDwProjConv& conv, const TcEpilogue& epilogue, int sm_count);
 cudaError_t tc_launch_dw_project(const TcDwProjLaunch& launch, cudaStream_t stream);
 

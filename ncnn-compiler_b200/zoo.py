@@ -266,6 +266,27 @@ def mobilenet_v2(prefix, seed=300, size=224, classes=1000):
     return w.save(prefix)
 
 
+def inverted_residual(prefix, h, w, cin, hidden, cout, stride=1, seed=310, expand_bias=True):
+    """One MobileNetV2 block on its own: 1x1 expand + ReLU6, 3x3 depthwise (stride 1 or 2) + ReLU6, 1x1 projection,
+    and the residual add when stride and channel counts allow it."""
+    net = _Net(seed)
+    wr = net.w
+    wr.layer("Input", "input", [], ["data"], f"0={w} 1={h} 2={cin}")
+    residual = stride == 1 and cin == cout
+    src = "data"
+    if residual:
+        wr.layer("Split", "split", ["data"], ["x", "id"])
+        src = "x"
+    net.conv("expand", src, "e", cin, hidden, 1, 1, 0, zero_bias=not expand_bias)
+    wr.layer("Clip", "expand_relu6", ["e"], ["ea"], "0=0.0 1=6.0")
+    net.depthwise("dw", "ea", "d", hidden, 3, stride, 1)
+    wr.layer("Clip", "dw_relu6", ["d"], ["da"], "0=0.0 1=6.0")
+    net.conv("project", "da", "p" if residual else "output", hidden, cout, 1, 1, 0, zero_bias=False)
+    if residual:
+        wr.layer("Eltwise", "add", ["p", "id"], ["output"], "0=1")
+    return wr.save(prefix)
+
+
 def inner_product(prefix, k, n, seed=500, int8=False, relu=True):
     """Config 4: Input [1,1,K] -> InnerProduct(K -> N, bias, fused ReLU); run with batch M."""
     net = _Net(seed + (7 if int8 else 0), int8=int8)

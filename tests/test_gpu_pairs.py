@@ -327,18 +327,67 @@ def test_depthwise_runs_inside_the_projection_kernel(pkg, oracle, tmp_path, monk
     """The stride-1 3x3 depthwise layers of the inverted-residual blocks run inside the 1x1 convolution that
     follows them (their result goes from the CUDA cores into the MMA's shared-memory operand, never to HBM).
     Same values, same bf16 split, same order of products as the two separate layers: the same bits; and the
-    network still matches the oracle."""
+    network still matches the oracle.  (NCNN_B200_FUSE_EXPAND=0: the expand layers stay on the tensor cores.)"""
     param, bin_ = pkg.zoo.mobilenet_v2(str(tmp_path / "mbv2"))
     x = np.random.default_rng(300 + n).uniform(-1, 1, (n, 3, 224, 224)).astype(np.float32)
+    monkeypatch.setenv("NCNN_B200_FUSE_EXPAND", "0")
     got, kernels = _run(pkg, param, bin_, x)
     fused = kernels.count("tc_dw_project_kernel<bf16x3>")
     assert fused >= 10, kernels
     monkeypatch.setenv("NCNN_B200_FUSE_DW", "0")
     base, plain = _run(pkg, param, bin_, x)
-    assert "tc_dw_project_kernel<bf16x3>" not in plain and len(plain) - len(kernels) == fused
+    assert not any(k.startswith("tc_dw_project_kernel") for k in plain) and len(plain) - len(kernels) == fused
     assert np.array_equal(got, base)
     want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x[:2]])
     assert rel_l2(got[:2], want) <= 2e-4
+
+
+@pytest.mark.parametrize("n", [3, 8])
+def test_whole_inverted_residual_blocks_run_in_one_kernel(pkg, oracle, tmp_path, monkeypatch, n):
+    """Blocks whose input has at most 32 channels run whole in the fused kernel: the expand layer on the CUDA cores
+    in fp32 from the block's input patch, depthwise (stride 1 or 2) and projection as above.  The expanded tensor
+    and the depthwise result never reach HBM.  fp32 instead of three bf16 products for the expand layer: not the
+    bits of the separate layers, but as close to them as they are to the oracle."""
+    param, bin_ = pkg.zoo.mobilenet_v2(str(tmp_path / "mbv2"))
+    x = np.random.default_rng(400 + n).uniform(-1, 1, (n, 3, 224, 224)).astype(np.float32)
+    monkeypatch.setenv("NCNN_B200_FUSE_EXPAND", "2")  # stride-1 blocks too (by default only stride-2 blocks: they gain)
+    got, kernels = _run(pkg, param, bin_, x)
+    whole = [k for k in kernels if k.startswith("tc_dw_project_kernel:expand")]
+    assert len(whole) >= 5 and "tc_dw_project_kernel:expand+stride2<bf16x3>" in whole, kernels
+    monkeypatch.setenv("NCNN_B200_FUSE_EXPAND", "1")
+    _, default_kernels = _run(pkg, param, bin_, x)
+    assert [k for k in default_kernels if k.startswith("tc_dw_project_kernel:expand")] == ["tc_dw_project_kernel:expand+stride2<bf16x3>"] * 3
+    monkeypatch.setenv("NCNN_B200_FUSE_DW", "0")
+    base, plain = _run(pkg, param, bin_, x)
+    assert len(plain) > len(kernels) + 2 * len(whole) - 1
+    assert rel_l2(got, base) <= 2e-5
+    want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x[:2]])
+    assert rel_l2(got[:2], want) <= 2e-4
+
+
+@pytest.mark.parametrize("h,w,cin,hidden,cout,stride,n", [
+    (56, 56, 24, 144, 24, 1, 3),    # residual block, hidden channels end inside a 32-channel block
+    (112, 112, 16, 96, 24, 2, 2),   # the widest tensors of MobileNetV2
+    (56, 56, 24, 144, 32, 2, 3),
+    (28, 28, 32, 192, 32, 1, 4),    # 32 input channels, residual
+    (19, 13, 8, 40, 16, 1, 5),      # ragged tiles both ways, few channels
+    (21, 17, 16, 64, 40, 2, 3),     # odd extent at stride 2: the last output pixel reads the zero padding
+    (9, 9, 8, 72, 24, 1, 2),
+])
+def test_whole_block_shapes(pkg, oracle, tmp_path, monkeypatch, h, w, cin, hidden, cout, stride, n):
+    param, bin_ = pkg.zoo.inverted_residual(str(tmp_path / "blk"), h, w, cin, hidden, cout, stride, seed=h * 31 + cin)
+    x = np.random.default_rng(h * cin + stride).uniform(-2, 2, (n, cin, h, w)).astype(np.float32)
+    monkeypatch.setenv("NCNN_B200_FUSE_DW", "2")  # also where the image fills its tiles badly
+    monkeypatch.setenv("NCNN_B200_FUSE_EXPAND", "2")  # and stride-1 blocks
+    got, kernels = _run(pkg, param, bin_, x)
+    assert len(kernels) == 3 and kernels[1].startswith("tc_dw_project_kernel:expand"), kernels
+    assert ("stride2" in kernels[1]) == (stride == 2)
+    want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x])
+    assert rel_l2(got, want) <= 1e-4
+    monkeypatch.setenv("NCNN_B200_FUSE_DW", "0")
+    base, plain = _run(pkg, param, bin_, x)
+    assert not any(k.startswith("tc_dw_project_kernel") for k in plain)
+    assert rel_l2(got, base) <= 2e-5
 
 
 @pytest.mark.parametrize("h,c,cout,n", [(14, 96, 24, 3), (30, 40, 64, 2), (7, 960, 320, 4), (9, 144, 16, 5)])
