@@ -507,7 +507,7 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
           tc_fence_after_sync();
           const int q = warp & 3;  // the TMEM lanes this warp may read: 32 q .. 32 q + 31
           const uint32_t bias_at = ex_table + static_cast<uint32_t>(cb * kDwpChannels) * 4u;
-#pragma unroll
+#pragma unroll 1  // (one copy of the strip's code: the kernel's roles already compete for the instruction cache)
           for (int mt = 0; mt < MT; ++mt) {
             const int px = mt * 128 + q * 32 + lane;
             if (mt * 128 + q * 32 >= NPX) break;  // (the whole warp is past the patch)
@@ -518,7 +518,7 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + e_col0 + static_cast<uint32_t>(group * MT + mt) * 32u;
             const uint32_t rowat = patch + static_cast<uint32_t>(px) * 128u;
             const uint32_t sw = static_cast<uint32_t>(px & 7);
-#pragma unroll
+#pragma unroll 1
             for (int h = 0; h < 2; ++h) {
               uint32_t v[16];
               tmem_ld16(taddr + 16u * h, v);
