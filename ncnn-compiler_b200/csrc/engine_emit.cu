@@ -233,6 +233,45 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
       } else {
         const long long M = (to.rank == 2 ? static_cast<long long>(ti.h) : 1) * n;
         const void* a0 = i8 ? static_cast<const void*>(in.q) : static_cast<const void*>(in.p0);
+        // a handful of rows: one pass over the weights on the CUDA cores instead of mostly empty 128-row tiles
+        if ((kind == GEMM_BF16X3 || kind == GEMM_I8) && !env_flag_off("NCNN_B200_IP_ROWS") &&
+            ip_rows_applies(M, node.K, node.O, i8, te.out_mode, te.res0 != nullptr, te.side_count > 0)) {
+          IpRowsParams ip{};
+          ip.M = static_cast<int>(M);
+          ip.K = node.K;
+          ip.N = node.O;
+          ip.lda = node.K;
+          ip.ldw = (node.K + node.k_elems - 1) / node.k_elems * node.k_elems;
+          ip.a0 = a0;
+          ip.a1 = in.p1;
+          ip.w0 = node.d_w0;
+          ip.w1 = node.d_w1;
+          ip.bias = te.bias;
+          ip.scale = te.scale;
+          ip.out_scale = te.out_scale;
+          ip.act = te.act;
+          ip.act_a = te.act_a;
+          ip.act_b = te.act_b;
+          ip.out_mode = te.out_mode;
+          ip.out0 = te.out0;
+          ip.out1 = te.out1;
+          ip.outq = te.outq;
+          ip.ldo = te.ldo;
+          const int smem = static_cast<int>(ip_rows_smem_bytes(ip.M, ip.K, i8));
+          const cudaError_t ae = i8 ? cudaFuncSetAttribute(k_ip_rows<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024)
+                                    : cudaFuncSetAttribute(k_ip_rows<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+          if (ae != cudaSuccess) return fail(err, "layer " + node.name + ": " + cudaGetErrorString(ae));
+          const int tasks = (ip.N + kIpRowsCols - 1) / kIpRowsCols;
+          const int grid = std::max(1, std::min(sm_count_, (tasks + kIpRowsThreads / 32 - 1) / (kIpRowsThreads / 32)));
+          s.kernel = i8 ? "k_ip_rows<i8>" : "k_ip_rows<bf16x2>";
+          s.run = [=](cudaStream_t st) {
+            if (i8) k_ip_rows<true><<<grid, kIpRowsThreads, smem, st>>>(ip);
+            else k_ip_rows<false><<<grid, kIpRowsThreads, smem, st>>>(ip);
+            return launch_ok();
+          };
+          plan.steps.push_back(std::move(s));
+          return true;
+        }
         perr = tc_plan_gemm(launch.get(), kind, a0, in.p1, M, node.K, node.K, node.d_w0, node.d_w1, node.O, te, sm_count_);
       }
       if (!perr.empty()) return fail(err, "layer " + node.name + ": " + perr);

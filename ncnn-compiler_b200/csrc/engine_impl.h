@@ -13,6 +13,7 @@
 #include <map>
 #include <sstream>
 
+#include "ip_rows.cuh"
 #include "kernels.cuh"
 #include "loader.h"
 #include "tc_gemm.h"

@@ -138,6 +138,29 @@ def test_inner_product_grid(pkg, oracle, tmp_path, m, k, n):
             assert rel_l2(got[rows], want) <= 1e-4
 
 
+@pytest.mark.parametrize("m,k,n", [(3, 4104, 1031), (8, 2048, 4097), (5, 8192, 528), (1, 25088, 512)])
+def test_few_rows_take_one_pass_over_the_weights(pkg, oracle, tmp_path, m, k, n):
+    """InnerProduct with at most 8 rows and weights of 8 MB or more is a pass over the weights: the row kernel
+    streams the packed bf16-pair (or int8) weights once, rows in shared memory, instead of filling 128-row tiles
+    with one to eight live rows.  Ragged K steps, an odd column count, a K that needs most of shared memory."""
+    x = np.random.default_rng(900 + m).uniform(-1, 1, (m, 1, 1, k)).astype(np.float32)
+    for int8 in (False, True):
+        param, bin_ = pkg.zoo.inner_product(str(tmp_path / ("ipq" if int8 else "ip")), k, n, int8=int8)
+        got, kernels = _run(pkg, param, bin_, x)
+        row_kernel = "k_ip_rows<i8>" if int8 else "k_ip_rows<bf16x2>"
+        expected = k % (16 if int8 else 8) == 0 and k * n * (1 if int8 else 4) >= (8 << 20)
+        assert (row_kernel in kernels) == expected, kernels
+        want = _oracle_rows(oracle, param, bin_, x, range(m))
+        if int8:
+            assert np.array_equal(got, want)
+        else:
+            assert rel_l2(got, want) <= 2e-5
+    # a small layer keeps the tensor-core path at every M: its results do not depend on the batch size
+    param, bin_ = pkg.zoo.inner_product(str(tmp_path / "small"), 512, 1000)
+    _, kernels = _run(pkg, param, bin_, x[:, :, :, :512].copy())
+    assert not any(kn.startswith("k_ip_rows") for kn in kernels), kernels
+
+
 @pytest.mark.parametrize("m,k,n,alpha,beta", [(256, 512, 1024, 0.5, -1.25), (32, 1024, 512, 1.75, 0.5),
                                               (200, 4096, 520, -0.25, 2.0), (1, 512, 512, 3.0, -1.0)])
 def test_gemm_on_tensor_cores_alpha_beta(pkg, oracle, tmp_path, m, k, n, alpha, beta):
