@@ -381,6 +381,18 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
       plan.steps.push_back(std::move(s));
       return true;
     }
+    // one window over the whole image (global pooling, or a window at least as large as an unpadded image)
+    const bool whole = !p.adaptive && p.OH == 1 && p.OW == 1 && p.pt == 0 && p.pl == 0 && p.KH >= p.H && p.KW >= p.W;
+    if (whole && vec && n <= 65535) {
+      const dim3 grid((p.C / 4 + 127) / 128, static_cast<unsigned>(n));
+      s.kernel = "k_global_pool4";
+      s.run = [=](cudaStream_t st) {
+        k_global_pool4<<<grid, 128, 0, st>>>(in, out, p);
+        return launch_ok();
+      };
+      plan.steps.push_back(std::move(s));
+      return true;
+    }
     const int grid = grid_for(n * p.OH * p.OW * (vec ? p.C / 4 : p.C));
     s.kernel = "k_pool";
     s.run = [=](cudaStream_t st) {

@@ -215,6 +215,32 @@ static __global__ void k_chw_to_nhwc_small_x4(const float* __restrict__ src, Act
       for (int k = 0; k < 4; ++k) d[k] = make_uint2(q[k], 0u);
       continue;
     }
+    if (dst.fmt == FMT_BF16X2) {
+      // four pixels = 32 contiguous bytes per plane, 8-byte aligned (rows start pad_l pixels in): 16-byte stores
+      // where the alignment allows, an 8-byte store either side of one 16-byte store where it does not
+      uint2 h[4], m[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        split_bf16x2(v[k][0], v[k][1], h[k].x, m[k].x);
+        split_bf16x2(v[k][2], v[k][3], h[k].y, m[k].y);
+      }
+      uint16_t* d0 = reinterpret_cast<uint16_t*>(dst.p0) + o;
+      uint16_t* d1 = reinterpret_cast<uint16_t*>(dst.p1) + o;
+      if ((o & 7) == 0) {
+        reinterpret_cast<uint4*>(d0)[0] = make_uint4(h[0].x, h[0].y, h[1].x, h[1].y);
+        reinterpret_cast<uint4*>(d0)[1] = make_uint4(h[2].x, h[2].y, h[3].x, h[3].y);
+        reinterpret_cast<uint4*>(d1)[0] = make_uint4(m[0].x, m[0].y, m[1].x, m[1].y);
+        reinterpret_cast<uint4*>(d1)[1] = make_uint4(m[2].x, m[2].y, m[3].x, m[3].y);
+      } else {
+        *reinterpret_cast<uint2*>(d0) = h[0];
+        *reinterpret_cast<uint4*>(d0 + 4) = make_uint4(h[1].x, h[1].y, h[2].x, h[2].y);
+        *reinterpret_cast<uint2*>(d0 + 12) = h[3];
+        *reinterpret_cast<uint2*>(d1) = m[0];
+        *reinterpret_cast<uint4*>(d1 + 4) = make_uint4(m[1].x, m[1].y, m[2].x, m[2].y);
+        *reinterpret_cast<uint2*>(d1 + 12) = m[3];
+      }
+      continue;
+    }
 #pragma unroll
     for (int k = 0; k < 4; ++k) act_store4(dst, o + 4 * k, make_float4(v[k][0], v[k][1], v[k][2], v[k][3]));
   }
@@ -412,6 +438,41 @@ static __global__ void k_pool(ActRef in, ActRef out, PoolParams p) {
       if (p.side_q != nullptr) p.side_q[o] = static_cast<int8_t>(quantize_rha(acc[0], p.side_scale));
     }
   }
+}
+
+// Global pooling (one window = the whole image) with channels in fours: one thread per four channels of an image
+// walks the pixels in the reference's order, seven loads in flight at a time (the generic kernel waits for every
+// pixel in turn: 49 memory latencies for a 7 x 7 image).
+static __global__ void __launch_bounds__(128) k_global_pool4(ActRef in, ActRef out, PoolParams p) {
+  const int c = (blockIdx.x * 128 + threadIdx.x) * 4;
+  const long long img = blockIdx.y;
+  if (c >= p.C) return;
+  const int hw = p.H * p.W;
+  const long long base = img * hw * p.C + c;
+  float4 acc = p.kind == 0 ? make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY) : make_float4(0.f, 0.f, 0.f, 0.f);
+  auto take = [&](const float4& v) {
+    if (p.kind == 0) {
+      acc = make_float4(fmaxf(acc.x, v.x), fmaxf(acc.y, v.y), fmaxf(acc.z, v.z), fmaxf(acc.w, v.w));
+    } else {
+      acc = make_float4(__fadd_rn(acc.x, v.x), __fadd_rn(acc.y, v.y), __fadd_rn(acc.z, v.z), __fadd_rn(acc.w, v.w));
+    }
+  };
+  int px = 0;
+  for (; px + 7 <= hw; px += 7) {
+    float4 v[7];
+#pragma unroll
+    for (int j = 0; j < 7; ++j) v[j] = act_load4(in, base + static_cast<long long>(px + j) * p.C);
+#pragma unroll
+    for (int j = 0; j < 7; ++j) take(v[j]);
+  }
+  for (; px < hw; ++px) take(act_load4(in, base + static_cast<long long>(px) * p.C));
+  if (p.kind == 1) {
+    const float n = static_cast<float>(hw);
+    acc = make_float4(__fdiv_rn(acc.x, n), __fdiv_rn(acc.y, n), __fdiv_rn(acc.z, n), __fdiv_rn(acc.w, n));
+  }
+  const long long o = img * p.C + c;
+  act_store4(out, o, acc);
+  pool_store_side4(p, o, acc.x, acc.y, acc.z, acc.w);
 }
 
 // ----------------------------------------------------------------- depthwise conv
