@@ -486,9 +486,11 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
       const int grid16 = grid_for(count / 16);
       const float* xp = in.p0;
       int8_t* yp = out.q;
-      s.kernel = "k_quantize16";
+      int8_t* y2 = node.side_q.empty() ? nullptr : ref(node.side_q[0].first, n).q;
+      const float scale2 = node.side_q.empty() ? 0.0f : node.side_q[0].second;
+      s.kernel = node.side_q.empty() ? "k_quantize16" : "k_quantize16:two results";
       s.run = [=](cudaStream_t st) {
-        k_quantize16<<<grid16, 256, 0, st>>>(xp, yp, count / 16, scale);
+        k_quantize16<<<grid16, 256, 0, st>>>(xp, yp, count / 16, scale, y2, scale2);
         return launch_ok();
       };
       plan.steps.push_back(std::move(s));
@@ -575,7 +577,7 @@ void EngineImpl::make_edge_steps(int64_t n, const std::vector<const float*>& d_i
       int8_t* q = dst.q;
       s.kernel = "k_quantize16";
       s.run = [=](cudaStream_t st) {
-        k_quantize16<<<grid, 256, 0, st>>>(src_ptr, q, count16, scale);
+        k_quantize16<<<grid, 256, 0, st>>>(src_ptr, q, count16, scale, nullptr, 0.0f);
         return launch_ok();
       };
     } else if (!flat_in) {

@@ -269,6 +269,24 @@ void EngineImpl::fuse_quantize_steps() {
     nodes_.erase(nodes_.begin() + k);
     --k;
   }
+  // Two Quantize steps that are left reading the same fp32 tensor (a block input that feeds the first convolution
+  // and the downsample convolution, each with its own scale) become one pass with two int8 results.
+  for (size_t a = 0; a < nodes_.size(); ++a) {
+    Node& q1 = nodes_[a];
+    if (q1.kind != N_UNARY || q1.un.op != UN_QUANT || q1.un.nscale != 1 || q1.un_scale.size() != 1 || !q1.side_q.empty()) continue;
+    const int src = resolve(q1.in[0]);
+    // (only where the 16-wide kernel runs at every batch size: it is the one with the second result)
+    if (tensors_[src].fmt != FMT_F32 || tensors_[src].logical() % 16 != 0) continue;
+    for (size_t b = a + 1; b < nodes_.size(); ++b) {
+      const Node& q2 = nodes_[b];
+      if (q2.kind != N_UNARY || q2.un.op != UN_QUANT || q2.un.nscale != 1 || q2.un_scale.size() != 1 || !q2.side_q.empty() ||
+          resolve(q2.in[0]) != src)
+        continue;
+      q1.side_q.emplace_back(q2.out, q2.un_scale[0]);
+      nodes_.erase(nodes_.begin() + b);
+      break;
+    }
+  }
 }
 
 // A stride-1 3x3 depthwise layer whose only consumer is a 1x1 tensor-core convolution (the second half of

@@ -291,21 +291,25 @@ static __global__ void k_unary(ActRef in, ActRef out, long long count, UnaryPara
 }
 
 // Per-tensor Quantize of a plain fp32 plane, 16 elements per thread: four 128-bit loads, one
-// 128-bit store of packed int8 (the Quantize steps in front of int8 contractions).
-static __global__ void k_quantize16(const float* __restrict__ x, int8_t* __restrict__ y, long long count16, float scale) {
+// 128-bit store of packed int8 (the Quantize steps in front of int8 contractions); optionally a second
+// int8 result of the same values with another scale.
+__device__ __forceinline__ uint32_t quantize_pack4(const float4& v, float scale) {
+  return (static_cast<uint32_t>(quantize_rha(v.x, scale)) & 0xffu) | ((static_cast<uint32_t>(quantize_rha(v.y, scale)) & 0xffu) << 8) |
+         ((static_cast<uint32_t>(quantize_rha(v.z, scale)) & 0xffu) << 16) | ((static_cast<uint32_t>(quantize_rha(v.w, scale)) & 0xffu) << 24);
+}
+static __global__ void k_quantize16(const float* __restrict__ x, int8_t* __restrict__ y, long long count16, float scale,
+                                    int8_t* __restrict__ y2, float scale2) {
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < count16;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     const float4* src = reinterpret_cast<const float4*>(x) + i * 4;
-    uint32_t w[4];
+    float4 v[4];
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      const float4 v = __ldg(src + g);
-      w[g] = (static_cast<uint32_t>(quantize_rha(v.x, scale)) & 0xffu) |
-             ((static_cast<uint32_t>(quantize_rha(v.y, scale)) & 0xffu) << 8) |
-             ((static_cast<uint32_t>(quantize_rha(v.z, scale)) & 0xffu) << 16) |
-             ((static_cast<uint32_t>(quantize_rha(v.w, scale)) & 0xffu) << 24);
-    }
-    reinterpret_cast<uint4*>(y)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    for (int g = 0; g < 4; ++g) v[g] = __ldg(src + g);
+    reinterpret_cast<uint4*>(y)[i] = make_uint4(quantize_pack4(v[0], scale), quantize_pack4(v[1], scale), quantize_pack4(v[2], scale),
+                                                quantize_pack4(v[3], scale));
+    if (y2 != nullptr)
+      reinterpret_cast<uint4*>(y2)[i] = make_uint4(quantize_pack4(v[0], scale2), quantize_pack4(v[1], scale2),
+                                                   quantize_pack4(v[2], scale2), quantize_pack4(v[3], scale2));
   }
 }
 

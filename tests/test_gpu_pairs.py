@@ -300,7 +300,7 @@ def test_handles_on_their_own_device_leave_the_callers_device_alone(pkg, tmp_pat
 def test_quantize_steps_fold_into_their_producers(pkg, oracle, tmp_path, monkeypatch):
     """The int8 network's Quantize steps (NCNNToTosa.cpp:4802-4824, one in front of every int8 contraction whose
     input is fp32) can be written by the layer that produces the fp32 tensor.  By default the pooling layers do
-    (two launches fewer); with NCNN_B200_FUSE_QUANT=2 the residual convolutions emit the int8 copies for the next
+    (two launches fewer; three more where two steps read the same tensor and become one pass); with NCNN_B200_FUSE_QUANT=2 the residual convolutions emit the int8 copies for the next
     block as well (two where a strided block has a projection): twelve launches fewer.  Either way the same bits
     as the separate steps, and bit exact against the oracle."""
     param, bin_ = pkg.zoo.resnet18(str(tmp_path / "r18q"), int8=True)
@@ -310,10 +310,11 @@ def test_quantize_steps_fold_into_their_producers(pkg, oracle, tmp_path, monkeyp
         monkeypatch.setenv("NCNN_B200_FUSE_QUANT", level)
         m = pkg.Model(param, bin_)
         kernels = _kernels(m, 4)
-        counts[level] = (kernels.count("k_quantize16"), len(kernels))
+        counts[level] = (sum(k.startswith("k_quantize16") for k in kernels), len(kernels))
         results[level] = m.run(x)[0].copy()
         m.close()
-    assert [counts[k][0] for k in ("0", "1", "2")] == [12, 10, 0], counts
+    # (from level 1 on, the two steps that read the input of a strided block are one pass with two results)
+    assert [counts[k][0] for k in ("0", "1", "2")] == [12, 7, 0], counts
     assert counts["0"][1] - counts["2"][1] == 12
     assert np.array_equal(results["1"], results["0"]) and np.array_equal(results["2"], results["0"])
     want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x[:2]])
