@@ -58,7 +58,7 @@ struct TcDwProjParams {
   int c_blocks;         // blocks of 32 channels (the last one may be partly past C: zero-filled)
   int pad_t, pad_l;
   int stages;           // weight ring depth
-  int patch_bufs;       // input patch ring depth (2..4): a patch load takes longer than one block's arithmetic
+  int patch_bufs;       // input patch ring depth, 2 or 4 (even: a slot then always serves the same depthwise group)
   int b_bytes;          // one plane of a weight stage, rounded to 1 KB
   int out_bufs;
   const float* dw_weights;  // [9][C], tap-major

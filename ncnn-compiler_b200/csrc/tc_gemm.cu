@@ -1070,7 +1070,12 @@ DwProjShape dw_project_shape(int N, int out_mode, int res_mode, int C, int strid
     if (expand ? min_stages < 3 : min_stages > 3) continue;  // (without the expand layer three stages are plenty)
     for (int x_bufs : {2, 1}) {
       if (!expand && x_bufs != 2) continue;
-      for (int patches : {4, 3, 2}) {
+      // (an even ring only: the two depthwise groups take alternate blocks, so with an even depth a slot always
+      // belongs to the same group, which waits for its phases in order; with three slots a slot would alternate
+      // between the groups, a group would wait for every second phase of it, and a parity wait cannot tell a
+      // phase from the one two before it: a load delayed past a whole block's arithmetic let a group read a stale
+      // patch, about once in 10^5 loads with the L2 flushed)
+      for (int patches : {4, 2}) {
         if (expand && patches != 2) continue;
         for (int bufs : {4, 3, 2}) {
           if (expand && bufs == 4) continue;

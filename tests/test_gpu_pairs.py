@@ -477,3 +477,19 @@ def test_every_failed_device_allocation_is_reported_and_leaves_nothing_behind(pk
     monkeypatch.delenv("NCNN_B200_TEST_FAIL_ALLOC", raising=False)
     torch.cuda.synchronize()
     assert torch.cuda.mem_get_info()[0] >= free_before - (8 << 20)
+
+
+# ------------------------------------------------------------------ the same bits, pass after pass
+def test_mobilenet_v2_repeats_bit_for_bit(pkg, tmp_path):
+    """150 passes at batch 256 through the host-pointer entry (uploads pipelined over the first layers, so the
+    kernels run against DRAM latency that varies from pass to pass) and 150 at batch 64: every pass gives the bits of
+    the first.  A patch ring of three slots once let a depthwise group, which then meets every second phase of a
+    slot, take a phase for the one two before it when a load was late: one image in ~500 passes came out wrong."""
+    param, bin_ = pkg.zoo.mobilenet_v2(str(tmp_path / "mbv2"))
+    m = pkg.Model(param, bin_)
+    for n in (256, 64):
+        x = np.random.default_rng(n).uniform(-1, 1, (n, 3, 224, 224)).astype(np.float32)
+        first = m.run(x)[0].copy()
+        for i in range(150):
+            assert np.array_equal(m.run(x)[0], first), (n, i)
+    m.close()
