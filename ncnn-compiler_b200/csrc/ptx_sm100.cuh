@@ -402,14 +402,5 @@ __host__ __device__ __forceinline__ uint32_t instr_desc(uint32_t c_format, uint3
          ((m >> 4) << 24);
 }
 
-// Warp-level MMA on register fragments: D(16x8, fp32) += A(16x16, bf16, row) * B(16x8, bf16, col).  For small
-// contractions that one warp finishes on values it already holds (no shared-memory operand tile, no TMEM trip).
-__device__ __forceinline__ void mma_bf16_m16n8k16(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
-}
-
 }  // namespace ptx
 }  // namespace nb

@@ -67,7 +67,9 @@ struct TcDwProjParams {
   float dw_act_a, dw_act_b;
   // expand layer (EXPAND): x is [image][Hin][Win][Cin] as bf16 hi / mid planes, weights packed [C][32] bf16 hi / mid
   int Cin;
-  int x_plane_bytes;        // one bf16 plane of an input patch buffer (rows of 64 bytes), rounded to 1 KB
+  int x_row_bytes;          // operand rows of the input patch and of the expand weights: 64 bytes (32 channels), or 32
+                            // (16 channels) when the block's input has no more: two patch buffers then fit where one did
+  int x_plane_bytes;        // one bf16 plane of an input patch buffer, rounded to 1 KB
   int x_bufs;               // input patch buffers: 2, or 1 when two do not fit
   int ex_ksteps;            // K steps of 16 input channels the expand MMAs run: ceil(Cin / 16)
   const float* ex_bias;     // [C] or null
@@ -206,8 +208,8 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
     // lane 0: the fp32 patch of a channel block (EXPAND: both planes of the tile's input patch); lanes 1, 2: the
     // two planes of that block's projection weights; lanes 3, 4 (EXPAND): the two planes of its expand weights
     const uint32_t patch_tx = static_cast<uint32_t>(NPX * kDwpChannels * 4);
-    const uint32_t x_tx = 2u * static_cast<uint32_t>(NPX) * 64u;
-    const uint32_t b_tx = 2u * static_cast<uint32_t>(p.block_n) * 64u + (EXPAND ? 2u * kExWeightBytes : 0u);
+    const uint32_t x_tx = 2u * static_cast<uint32_t>(NPX) * static_cast<uint32_t>(p.x_row_bytes);
+    const uint32_t b_tx = 2u * static_cast<uint32_t>(p.block_n) * 64u + (EXPAND ? 2u * 32u * static_cast<uint32_t>(p.x_row_bytes) : 0u);
     int s = 0, pb = 0;
     uint32_t ph = 0, p_ph = 0;
     long long patches = 0, weights = 0, tiles_done = 0, x_issued = 0;
@@ -309,6 +311,7 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
       const uint32_t idesc = instr_desc(1u, 1u, kTcBlockM, static_cast<uint32_t>(p.block_n));
       const uint32_t idesc_ex = instr_desc(1u, 1u, kTcBlockM, 32u);
       const uint64_t fixed = smem_desc_kmajor(0u, 64u);  // 64-byte rows, 64-byte swizzle
+      const uint64_t fixed_x = smem_desc_kmajor(0u, EXPAND ? static_cast<uint32_t>(p.x_row_bytes) : 64u);
       const uint64_t a_plane_units = kAPlaneBytes >> 4;
       const uint64_t b_units = b_bytes >> 4;
       const int c_blocks = p.c_blocks;
@@ -330,13 +333,13 @@ tc_dw_project_kernel(const __grid_constant__ TcDwProjParams p, const __grid_cons
         tc_fence_after_sync();
         const uint32_t xa = x_base + static_cast<uint32_t>(xb) * 2u * x_plane;
         const uint32_t wb = b_base + static_cast<uint32_t>(st) * b_stage_bytes + 2u * b_bytes;
-        const uint64_t w0 = fixed + ((wb & 0x3ffffu) >> 4);
+        const uint64_t w0 = fixed_x + ((wb & 0x3ffffu) >> 4);
         const uint64_t w_units = kExWeightBytes >> 4;
         const uint64_t x_units = x_plane >> 4;
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt) {
           const uint32_t d = tmem_base + e_col0 + static_cast<uint32_t>(g * MT + mt) * 32u;
-          const uint64_t a0 = fixed + (((xa + static_cast<uint32_t>(mt) * 128u * 64u) & 0x3ffffu) >> 4);
+          const uint64_t a0 = fixed_x + (((xa + static_cast<uint32_t>(mt) * 128u * static_cast<uint32_t>(p.x_row_bytes)) & 0x3ffffu) >> 4);
 #pragma unroll
           for (int k = 0; k < 2; ++k) {
             if (k >= p.ex_ksteps) break;  // (16 input channels: the second half of the 64-byte rows is zero padding)

@@ -1036,14 +1036,14 @@ cudaError_t tc_launch_halo(const TcHaloLaunch& L, cudaStream_t stream) {
 namespace {
 
 struct DwProjShape {
-  int block_n = 0, tiles_n = 0, stages = 0, out_bufs = 0, patches = 0, b_bytes = 0, x_plane_bytes = 0, x_bufs = 0, smem = 0;
+  int block_n = 0, tiles_n = 0, stages = 0, out_bufs = 0, patches = 0, b_bytes = 0, x_plane_bytes = 0, x_row_bytes = 64, x_bufs = 0, smem = 0;
   bool ok = false;
 };
 
 // Shared-memory plan of tc_dw_project_kernel.  expand: the expand layer is fused in (input patches as bf16 planes
 // of 64-byte rows, one fp32 patch per depthwise group, the block's expand weights beside its projection weights in
 // every ring stage, the expand bias beside the depthwise table).
-DwProjShape dw_project_shape(int N, int out_mode, int res_mode, int C, int stride, bool expand) {
+DwProjShape dw_project_shape(int N, int out_mode, int res_mode, int C, int stride, bool expand, int cin = 32) {
   DwProjShape r;
   const bool wide = out_mode == OUT_BF16X2 || res_mode == RES_BF16X2;
   if (out_mode != OUT_BF16X2 && out_mode != OUT_F32) return r;
@@ -1062,7 +1062,8 @@ DwProjShape dw_project_shape(int N, int out_mode, int res_mode, int C, int strid
   const int c_pad = (C + kDwpChannels - 1) / kDwpChannels * kDwpChannels;
   const int table = (c_pad * (expand ? 11 : 10) * 4 + 1023) / 1024 * 1024;  // depthwise filter and bias (+ expand bias)
   const int stage = 2 * r.b_bytes + (expand ? 4096 : 0);
-  r.x_plane_bytes = expand ? (dwp_patch_pixels(stride) * 64 + 1023) / 1024 * 1024 : 0;
+  r.x_row_bytes = cin <= 16 ? 32 : 64;
+  r.x_plane_bytes = expand ? (dwp_patch_pixels(stride) * r.x_row_bytes + 1023) / 1024 * 1024 : 0;
   // Deep patch ring first (a patch load outlasts one block's arithmetic), then three weight stages, then
   // output staging tiles; the last resort is two of each.  With the expand layer: two input patch buffers if they
   // fit, and never fewer than three stages (the expand MMAs run two blocks ahead of the projection's).
@@ -1124,7 +1125,7 @@ bool tc_block_applies(int Cin, int C, int N, int OH, int OW, int stride, bool ha
     for (int res_mode : {RES_NONE, RES_F32, RES_BF16X2}) {
       if (!has_res && res_mode != RES_NONE) continue;
       if (has_res && res_mode == RES_NONE) continue;
-      if (!dw_project_shape(N, out_mode, res_mode, C, stride, true).ok) return false;
+      if (!dw_project_shape(N, out_mode, res_mode, C, stride, true, Cin).ok) return false;
     }
   return true;
 }
@@ -1137,7 +1138,7 @@ std::string tc_plan_dw_project(TcDwProjLaunch* L, const TcDwProjConv& c, const T
   const int res_mode = e.res0 == nullptr ? RES_NONE : (e.res_bf16 ? RES_BF16X2 : (e.res1 != nullptr ? RES_SPLIT : RES_F32));
   const bool expand = c.ex_w0 != nullptr;
   const int stride = c.stride;
-  const DwProjShape shape = dw_project_shape(c.out_channels, e.out_mode, res_mode, c.C, stride, expand);
+  const DwProjShape shape = dw_project_shape(c.out_channels, e.out_mode, res_mode, c.C, stride, expand, expand ? c.Cin : 32);
   if (!shape.ok) return "the fused depthwise + projection kernel does not take this output format, width or stride";
   if (e.ldo != c.out_channels) return "the fused depthwise + projection kernel writes dense channel-last rows";
   const int x_channels = expand ? c.Cin : c.C;
@@ -1171,8 +1172,9 @@ std::string tc_plan_dw_project(TcDwProjLaunch* L, const TcDwProjConv& c, const T
   p.dw_act_b = c.dw_act_b;
   p.Cin = expand ? c.Cin : 0;
   p.x_plane_bytes = shape.x_plane_bytes;
+  p.x_row_bytes = shape.x_row_bytes;
   p.x_bufs = shape.x_bufs;
-  p.ex_ksteps = expand ? (c.Cin + 15) / 16 : 0;
+  p.ex_ksteps = expand ? (shape.x_row_bytes == 32 ? 1 : (c.Cin + 15) / 16) : 0;
   p.ex_bias = c.ex_bias;
   p.ex_act = c.ex_act;
   p.ex_act_a = c.ex_act_a;
@@ -1193,14 +1195,17 @@ std::string tc_plan_dw_project(TcDwProjLaunch* L, const TcDwProjConv& c, const T
   // input patches, [image][Hin][Win][channels], boxes of 32 channels x patch width x patch height: fp32 and dense
   // in shared memory for the depthwise filter; with the expand layer fused in, the bf16 planes of the block's input
   // as 64-byte-swizzled operand rows (channels past Cin read as zero)
-  std::string err = encode_tiled_4d(&L->map_x, expand, c.x, x_channels, c.Win, c.Hin, c.images, kDwpChannels, dwp_patch_w(stride),
-                                    dwp_patch_h(stride), expand ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE);
+  const uint32_t x_box = expand ? static_cast<uint32_t>(shape.x_row_bytes / 2) : kDwpChannels;
+  const CUtensorMapSwizzle x_swizzle = !expand ? CU_TENSOR_MAP_SWIZZLE_NONE
+                                               : (shape.x_row_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_64B);
+  std::string err = encode_tiled_4d(&L->map_x, expand, c.x, x_channels, c.Win, c.Hin, c.images, x_box, dwp_patch_w(stride),
+                                    dwp_patch_h(stride), x_swizzle);
   if (err.empty() && expand)
-    err = encode_tiled_4d(&L->map_x1, true, c.x1, x_channels, c.Win, c.Hin, c.images, kDwpChannels, dwp_patch_w(stride),
-                          dwp_patch_h(stride), CU_TENSOR_MAP_SWIZZLE_64B);
-  // expand weights: [C][32] bf16 per plane, one block of 32 rows per copy
-  if (err.empty() && expand) err = encode_tiled_2d(&L->map_e0, GEMM_BF16X3, c.ex_w0, 32, c.C, 64, 32, kDwpChannels, 64);
-  if (err.empty() && expand) err = encode_tiled_2d(&L->map_e1, GEMM_BF16X3, c.ex_w1, 32, c.C, 64, 32, kDwpChannels, 64);
+    err = encode_tiled_4d(&L->map_x1, true, c.x1, x_channels, c.Win, c.Hin, c.images, x_box, dwp_patch_w(stride),
+                          dwp_patch_h(stride), x_swizzle);
+  // expand weights: [C][32] bf16 per plane (64-byte pitch), one block of 32 rows per copy, as many K columns as the rows hold
+  if (err.empty() && expand) err = encode_tiled_2d(&L->map_e0, GEMM_BF16X3, c.ex_w0, 32, c.C, 64, x_box, kDwpChannels, shape.x_row_bytes);
+  if (err.empty() && expand) err = encode_tiled_2d(&L->map_e1, GEMM_BF16X3, c.ex_w1, 32, c.C, 64, x_box, kDwpChannels, shape.x_row_bytes);
   if (!err.empty()) return err;
   const uint64_t k_total = static_cast<uint64_t>(p.c_blocks) * kDwpChannels;
   err = encode_tiled_2d(&L->map_b0, GEMM_BF16X3, c.w0, k_total, c.out_channels, k_total * 2, kDwpChannels, p.block_n, 64);
