@@ -397,6 +397,10 @@ def test_whole_inverted_residual_blocks_run_in_one_kernel(pkg, oracle, tmp_path,
     (19, 13, 8, 40, 16, 1, 5),      # ragged tiles both ways, few channels
     (21, 17, 16, 64, 40, 2, 3),     # odd extent at stride 2: the last output pixel reads the zero padding
     (9, 9, 8, 72, 24, 1, 2),
+    (40, 24, 16, 32, 16, 1, 3),     # a single channel block per tile: the two groups alternate tiles
+    (33, 33, 8, 32, 128, 2, 2),     # the same at stride 2, and the widest projection the kernel takes
+    (3, 3, 16, 48, 16, 1, 7),       # an image smaller than a tile
+    (4, 4, 24, 64, 24, 2, 5),
 ])
 def test_whole_block_shapes(pkg, oracle, tmp_path, monkeypatch, h, w, cin, hidden, cout, stride, n):
     param, bin_ = pkg.zoo.inverted_residual(str(tmp_path / "blk"), h, w, cin, hidden, cout, stride, seed=h * 31 + cin)
