@@ -262,7 +262,7 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
                                     : cudaFuncSetAttribute(k_ip_rows<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
           if (ae != cudaSuccess) return fail(err, "layer " + node.name + ": " + cudaGetErrorString(ae));
           const int tasks = (ip.N + kIpRowsCols - 1) / kIpRowsCols;
-          const int grid = std::max(1, std::min(sm_count_, (tasks + kIpRowsThreads / 32 - 1) / (kIpRowsThreads / 32)));
+          const int grid = std::max(1, std::min(sm_count_, tasks));
           s.kernel = i8 ? "k_ip_rows<i8>" : "k_ip_rows<bf16x2>";
           s.run = [=](cudaStream_t st) {
             if (i8) k_ip_rows<true><<<grid, kIpRowsThreads, smem, st>>>(ip);

@@ -96,7 +96,8 @@ static __global__ void __launch_bounds__(kIpRowsThreads, 1) k_ip_rows(const IpRo
   }
   __syncthreads();
   const int tasks = (p.N + COLS - 1) / COLS;
-  for (int task = blockIdx.x * (kIpRowsThreads / 32) + warp; task < tasks; task += gridDim.x * (kIpRowsThreads / 32)) {
+  // (column pairs are dealt out CTA by CTA, so that every SM streams weights even when there are fewer pairs than warps)
+  for (int task = warp * gridDim.x + blockIdx.x; task < tasks; task += gridDim.x * (kIpRowsThreads / 32)) {
     const int n0 = task * COLS;
     float acc[kIpRowsMaxM][COLS];
     int iacc[kIpRowsMaxM][COLS];
