@@ -369,7 +369,7 @@ def main():
 
     # per-launch timing with CUDA events on the launching stream (same workload, eager launches)
     rows = model.profile(n, repeat=5)
-    tc_prefixes = ("tc_gemm_kernel", "tc_gemm2_kernel", "tc_conv_halo_kernel", "tc_stem_kernel", "tc_dw_project_kernel", "k_ip_rows")
+    tc_prefixes = ("tc_gemm_kernel", "tc_gemm2_kernel", "tc_conv_halo_kernel", "tc_stem_kernel", "tc_stem_pool_kernel", "tc_dw_project_kernel", "k_ip_rows")
     tc = [r for r in rows if r["kernel"].startswith(tc_prefixes)]
     peaks = measured_peaks()
     tc_ms = sum(r["ms"] for r in tc)

@@ -8,7 +8,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libncnn_b200.so")
 SOURCES = ["engine.cu", "engine_import.cu", "engine_plan.cu", "engine_emit.cu", "tc_gemm.cu", "c_api.cu", "no_alloc.cu", "loader.cpp", "dynamic.cpp", "multi.cpp"]
-HEADERS = ["exports.map", "engine.h", "engine_impl.h", "tc_gemm.h", "tc_gemm.cuh", "tc_gemm2.cuh", "tc_stem.cuh", "tc_conv_halo.cuh", "tc_dw_project.cuh", "ptx_sm100.cuh", "kernels.cuh", "ip_rows.cuh", "loader.h",
+HEADERS = ["exports.map", "engine.h", "engine_impl.h", "tc_gemm.h", "tc_gemm.cuh", "tc_gemm2.cuh", "tc_stem.cuh", "tc_stem_pool.cuh", "tc_conv_halo.cuh", "tc_dw_project.cuh", "ptx_sm100.cuh", "kernels.cuh", "ip_rows.cuh", "loader.h",
            os.path.join("..", "..", "include", "ncnn_b200.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]

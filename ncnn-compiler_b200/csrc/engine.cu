@@ -41,6 +41,7 @@ bool EngineImpl::build(const std::string& param, const std::string& bin, const E
   if (opt.plan_only) return true;
   if (!prepare_weights(err)) return false;
   fuse_depthwise_projection();
+  fuse_stem_pooling();
   choose_head_limit();
   plan_memory();
   if (cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking) != cudaSuccess) return fail(err, "cannot create a stream");

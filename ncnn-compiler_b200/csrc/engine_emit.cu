@@ -181,6 +181,16 @@ bool EngineImpl::emit_node(Plan& plan, const Node& node, int64_t n, std::string*
         sc.w0 = node.d_w0;
         sc.w1 = node.d_w1;
         sc.out_channels = node.O;
+        if (node.pool_fused) {
+          auto pl = std::make_shared<TcStemPoolLaunch>();
+          const std::string perr2 = tc_plan_stem_pool(pl.get(), sc, te, node.pool_oh, node.pool_ow, sm_count_);
+          if (!perr2.empty()) return fail(err, "layers " + node.name + " + " + node.pool_name + ": " + perr2);
+          s.name = node.name + "+" + node.pool_name;
+          s.kernel = std::string("tc_stem_pool_kernel<") + kind_name + ">";
+          s.run = [pl](cudaStream_t st) { return tc_launch_stem_pool(*pl, st); };
+          plan.steps.push_back(std::move(s));
+          return true;
+        }
         auto sl = std::make_shared<TcStemLaunch>();
         if (tc_plan_stem(sl.get(), sc, te, sm_count_).empty()) {
           s.kernel = std::string("tc_stem_kernel<") + kind_name + ">";

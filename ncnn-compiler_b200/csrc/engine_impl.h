@@ -107,6 +107,10 @@ struct Node {
   int dw_stride = 1;
   int dw_c = 0, dw_hin = 0, dw_win = 0;  // channels and input extent of the depthwise layer
   std::string dw_name;
+  // a 3x3 stride-2 max pooling that runs inside the stem kernel in front of it (fuse_stem_pooling)
+  bool pool_fused = false;
+  int pool_oh = 0, pool_ow = 0;
+  std::string pool_name;
   // the 1x1 expand convolution in front of that depthwise layer, merged into the projection node by the same pass
   bool ex_fused = false;
   const void* ex_w0 = nullptr;
@@ -244,6 +248,7 @@ class EngineImpl {
   void fold_channel_concats();
   void fuse_quantize_steps();
   void fuse_depthwise_projection();
+  void fuse_stem_pooling();
   int profile(int64_t n, int repeat, std::vector<LayerTiming>* out);
   Plan* plan_for(int64_t n);
 

@@ -397,6 +397,41 @@ void EngineImpl::fuse_depthwise_projection() {
   }
 }
 
+// The 3x3 stride-2 max pooling behind a stem that runs on the row-resident kernel moves into that kernel: the
+// stem's result (the largest tensor of the network) is pooled out of shared memory and never written to HBM.
+// Same values, same maxima, same bf16 split as the two launches.  NCNN_B200_STEM_POOL=0 keeps them apart.
+void EngineImpl::fuse_stem_pooling() {
+  if (env_flag_off("NCNN_B200_STEM_POOL") || opt_.accuracy_mode != kAccuracyFp32Split) return;
+  std::vector<int> uses(tensors_.size(), 0);
+  for (const Node& n : nodes_) {
+    for (int t : n.in) ++uses[resolve(t)];
+    if (n.res >= 0) ++uses[resolve(n.res)];
+  }
+  for (int o : outputs_) ++uses[resolve(o)];
+  for (size_t k = 0; k + 1 < nodes_.size(); ++k) {
+    Node& st = nodes_[k];
+    if (st.kind != N_CONV || !st.stem || !st.stem_rows || st.impl != IMPL_TC || st.term != 0 || st.res >= 0 || st.out_ld != 0 ||
+        !st.side_q.empty() || (st.O != 32 && st.O != 64) || st.OW > 128 || st.OH % 2 != 0 || st.OW % 2 != 0)
+      continue;
+    if (st.act != ACT_NONE && st.act != ACT_RELU && st.act != ACT_CLIP) continue;  // the kernel clamps, nothing else
+    const int mid = resolve(st.out);
+    if (uses[mid] != 1 || tensors_[mid].fmt != FMT_F32 || tensors_[resolve(st.in[0])].fmt != FMT_BF16X2) continue;
+    const Node& pl = nodes_[k + 1];
+    if (pl.kind != N_POOL || resolve(pl.in[0]) != mid || !pl.side_q.empty()) continue;
+    const PoolParams& pp = pl.pool;
+    if (pp.kind != 0 || pp.adaptive || pp.KH != 3 || pp.KW != 3 || pp.sh != 2 || pp.sw != 2 || pp.pt != 1 || pp.pl != 1 ||
+        pp.OH * 2 != st.OH || pp.OW * 2 != st.OW || tensors_[resolve(pl.out)].fmt != FMT_BF16X2)
+      continue;
+    st.pool_fused = true;
+    st.pool_oh = pp.OH;
+    st.pool_ow = pp.OW;
+    st.pool_name = pl.name;
+    st.out = pl.out;
+    st.flops += pl.flops;
+    nodes_.erase(nodes_.begin() + k + 1);
+  }
+}
+
 bool EngineImpl::prepare_weights(std::string* err) {
   const int f32_kind = opt_.accuracy_mode == kAccuracyTf32 ? GEMM_TF32 : GEMM_TF32X3;
   // insert Quantize steps in front of int8 contractions whose input is fp32

@@ -1459,4 +1459,56 @@ cudaError_t tc_launch_stem(const TcStemLaunch& L, cudaStream_t stream) {
   return e != cudaSuccess ? e : cudaGetLastError();
 }
 
+std::string tc_plan_stem_pool(TcStemPoolLaunch* L, const TcStemConv& c, const TcEpilogue& e, int pooled_h, int pooled_w, int sm_count) {
+  if (c.kind != GEMM_BF16X3 || e.out_mode != OUT_BF16X2) return "the stem + pooling kernel takes and writes bf16 pairs";
+  const int N = c.out_channels;
+  if (N != 32 && N != 64) return "the stem + pooling kernel takes 32 or 64 output channels";
+  if (e.act != ACT_NONE && e.act != ACT_RELU && e.act != ACT_CLIP) return "the stem + pooling kernel applies no activation but ReLU and clip";
+  if (c.OH != 2 * pooled_h || c.OW != 2 * pooled_w || pooled_h < 1 || pooled_w < 1) return "the pooled extent must be half the convolution's";
+  // the convolution part is planned as for tc_stem_kernel (validation, input and weight maps, operand geometry)
+  TcStemLaunch conv;
+  std::string err = tc_plan_stem(&conv, c, e, sm_count);
+  if (!err.empty()) return err;
+  TcStemPoolParams& pp = L->pp;
+  pp.s = conv.p;
+  pp.images = c.images;
+  pp.POH = pooled_h;
+  pp.POW = pooled_w;
+  pp.ring_row_bytes = (c.OW * N * 4 + 1023) / 1024 * 1024;
+  pp.stage_tile_bytes = (pooled_w * 64 + 1023) / 1024 * 1024;
+  const int weights = c.KH * 2 * conv.p.b_slot;
+  const int stage = 2 * conv.p.a_plane_bytes;
+  const int halves = N / 32;
+  L->smem_bytes = weights + 2 * stage + 3 * pp.ring_row_bytes + 2 * halves * pp.stage_tile_bytes + 1024;
+  if (L->smem_bytes > tc_smem_budget(GEMM_BF16X3) + 1024) return "shared memory cannot hold the weights, two row stages and three result rows";
+  L->smem_bytes = std::max(L->smem_bytes, 120 * 1024);  // one CTA per SM: each allocates tensor memory
+  const long long pooled_rows = static_cast<long long>(c.images) * pooled_h;
+  if (pooled_rows * pooled_w > 0x7fffffffll) return "too many pooled pixels for one launch";
+  L->grid = static_cast<int>(std::min<long long>(pooled_rows, sm_count));
+  L->map_a0 = conv.map_a0;
+  L->map_a1 = conv.map_a1;
+  L->map_b0 = conv.map_b0;
+  L->map_b1 = conv.map_b1;
+  // pooled result: [pooled pixels][N] bf16 per plane, boxes of 32 channels x one pooled row, 64-byte swizzle
+  err = encode_tiled_2d(&L->map_o0, GEMM_BF16X3, e.out0, N, static_cast<uint64_t>(pooled_rows) * pooled_w, static_cast<uint64_t>(N) * 2, 32,
+                        static_cast<uint32_t>(pooled_w), 64);
+  if (err.empty())
+    err = encode_tiled_2d(&L->map_o1, GEMM_BF16X3, e.out1, N, static_cast<uint64_t>(pooled_rows) * pooled_w, static_cast<uint64_t>(N) * 2, 32,
+                          static_cast<uint32_t>(pooled_w), 64);
+  return err;
+}
+
+cudaError_t tc_launch_stem_pool(const TcStemPoolLaunch& L, cudaStream_t stream) {
+  static PerDeviceOnce attr_once;
+  const cudaError_t attr_err = attr_once.run([] {
+    return cudaFuncSetAttribute(tc_stem_pool_kernel<GEMM_BF16X3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                tc_smem_budget(GEMM_BF16X3) + 1024);
+  });
+  if (attr_err != cudaSuccess) return attr_err;
+  KernelLaunchConfig lc(L.grid, kStemPoolThreads, L.smem_bytes, false, stream);
+  const cudaError_t e = cudaLaunchKernelEx(&lc.cfg, tc_stem_pool_kernel<GEMM_BF16X3>, L.pp, L.map_a0, L.map_a1, L.map_b0, L.map_b1,
+                                           L.map_o0, L.map_o1);
+  return e != cudaSuccess ? e : cudaGetLastError();
+}
+
 }  // namespace nb

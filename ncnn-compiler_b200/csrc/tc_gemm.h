@@ -14,6 +14,7 @@
 #include "tc_gemm.cuh"
 #include "tc_gemm2.cuh"
 #include "tc_stem.cuh"
+#include "tc_stem_pool.cuh"
 
 namespace nb {
 
@@ -231,6 +232,24 @@ struct TcStemConv {
   const void* w1 = nullptr;
   int out_channels = 0;
 };
+
+// ---- stem convolution + 3x3 stride-2 max pooling in one kernel (tc_stem_pool.cuh)
+struct TcStemPoolLaunch {
+  TcStemPoolParams pp{};
+  alignas(64) CUtensorMap map_a0{};
+  alignas(64) CUtensorMap map_a1{};
+  alignas(64) CUtensorMap map_b0{};
+  alignas(64) CUtensorMap map_b1{};
+  alignas(64) CUtensorMap map_o0{};  // pooled result, bf16 hi / mid planes
+  alignas(64) CUtensorMap map_o1{};
+  int grid = 0;
+  int smem_bytes = 0;
+};
+// `epilogue` describes the POOLED tensor (bf16 pairs, dense rows of out_channels); pooled extent pooled_h x pooled_w
+// = half the convolution's output extent (3x3 windows, stride 2, one pixel of padding above and to the left).
+std::string tc_plan_stem_pool(TcStemPoolLaunch* launch, const struct TcStemConv& conv, const TcEpilogue& epilogue, int pooled_h,
+                              int pooled_w, int sm_count);
+cudaError_t tc_launch_stem_pool(const TcStemPoolLaunch& launch, cudaStream_t stream);
 
 // Applies when output pixels are 16 bytes apart in the padded input row (stride 2 x 4 channels x
 // bf16), a row of output fits one 128-row tile, and the rows and resident weights fit shared memory.

@@ -300,6 +300,38 @@ def test_stem_rows_kernel_equals_window_path(pkg, oracle, tmp_path, monkeypatch,
     assert rel_l2(got[:2], want) <= 1e-4  # fp32 tolerance of the path: rel-L2 <= 1e-3 required, ~1e-5 achieved
 
 
+@pytest.mark.parametrize("size,n", [(224, 3), (64, 5), (64, 40), (100, 7), (32, 2)])
+def test_stem_with_pooling_inside_equals_two_kernels(pkg, oracle, tmp_path, monkeypatch, size, n):
+    """The 3x3 stride-2 max pooling behind the stem runs inside the stem's kernel (tc_stem_pool_kernel): the stem's
+    rows are pooled out of shared memory.  Same products, same maxima, same bf16 split as the two separate kernels,
+    so the same bits; pooled-row ranges of a CTA that start inside an image, cross into the next image, or hold a
+    single pooled row are all met by these sizes."""
+    param, bin_ = pkg.zoo.resnet18(str(tmp_path / "r"), size=size, classes=24)
+    x = np.random.default_rng(size + n).uniform(-1, 1, (n, 3, size, size)).astype(np.float32)
+    m = pkg.Model(param, bin_)
+    kernels = [r["kernel"] for r in m.profile(n, 1)]
+    assert "tc_stem_pool_kernel<bf16x3>" in kernels and not any(k.startswith("tc_stem_kernel") for k in kernels)
+    got = m.run(x)[0]
+    assert np.array_equal(m.run(x)[0], got)
+    m.close()
+    monkeypatch.setenv("NCNN_B200_STEM_POOL", "0")
+    m = pkg.Model(param, bin_)
+    assert any(k["kernel"].startswith("tc_stem_kernel") for k in m.profile(n, 1))
+    assert np.array_equal(m.run(x)[0], got)
+    m.close()
+    want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x[:1]])
+    assert rel_l2(got[:1], want) <= 1e-3  # the tolerance of the fp32 path through a whole network
+
+
+def test_stem_with_odd_rows_keeps_its_pooling_kernel(pkg, tmp_path):
+    """A stem whose output extent is odd does not pool in place (the pooled rows would not pair up with its rows)."""
+    param, bin_ = pkg.zoo.resnet18(str(tmp_path / "r"), size=90, classes=24)
+    m = pkg.Model(param, bin_)
+    kernels = [r["kernel"] for r in m.profile(2, 1)]
+    assert not any(k.startswith("tc_stem_pool_kernel") for k in kernels)
+    m.close()
+
+
 def test_int8_stem_rows_kernel_is_bit_exact(pkg, oracle, tmp_path, monkeypatch):
     """The int8 stem through the row-resident kernel (8-channel pixels, overlapping 64-byte windows): same int8
     bits as the oracle and as the im2col-window path (16-channel pixels, 128-byte windows)."""
