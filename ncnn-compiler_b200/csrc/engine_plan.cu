@@ -401,7 +401,7 @@ void EngineImpl::fuse_depthwise_projection() {
 // stem's result (the largest tensor of the network) is pooled out of shared memory and never written to HBM.
 // Same values, same maxima, same bf16 split as the two launches.  NCNN_B200_STEM_POOL=0 keeps them apart.
 void EngineImpl::fuse_stem_pooling() {
-  if (env_flag_off("NCNN_B200_STEM_POOL") || opt_.accuracy_mode != kAccuracyFp32Split) return;
+  if (env_flag_off("NCNN_B200_STEM_POOL")) return;
   std::vector<int> uses(tensors_.size(), 0);
   for (const Node& n : nodes_) {
     for (int t : n.in) ++uses[resolve(t)];
@@ -410,23 +410,29 @@ void EngineImpl::fuse_stem_pooling() {
   for (int o : outputs_) ++uses[resolve(o)];
   for (size_t k = 0; k + 1 < nodes_.size(); ++k) {
     Node& st = nodes_[k];
-    if (st.kind != N_CONV || !st.stem || !st.stem_rows || st.impl != IMPL_TC || st.term != 0 || st.res >= 0 || st.out_ld != 0 ||
-        !st.side_q.empty() || (st.O != 32 && st.O != 64) || st.OW > 128 || st.OH % 2 != 0 || st.OW % 2 != 0)
+    if (st.kind != N_CONV || !st.stem || !st.stem_rows || st.impl != IMPL_TC || st.res >= 0 || st.out_ld != 0 || !st.side_q.empty() ||
+        (st.O != 32 && st.O != 64) || st.OW > 128 || st.OH % 2 != 0 || st.OW % 2 != 0)
       continue;
     if (st.act != ACT_NONE && st.act != ACT_RELU && st.act != ACT_CLIP) continue;  // the kernel clamps, nothing else
+    // bf16 pairs in, bf16 pairs out (fp32 accuracy mode); or int8 in, fp32 out with at most one int8 copy of 64 channels
+    const bool i8 = st.term != 0;
     const int mid = resolve(st.out);
-    if (uses[mid] != 1 || tensors_[mid].fmt != FMT_F32 || tensors_[resolve(st.in[0])].fmt != FMT_BF16X2) continue;
+    const int want_in = i8 ? FMT_I8 : FMT_BF16X2, want_out = i8 ? FMT_F32 : FMT_BF16X2;
+    if (!i8 && opt_.accuracy_mode != kAccuracyFp32Split) continue;
+    if (uses[mid] != 1 || tensors_[mid].fmt != FMT_F32 || tensors_[resolve(st.in[0])].fmt != want_in) continue;
     const Node& pl = nodes_[k + 1];
-    if (pl.kind != N_POOL || resolve(pl.in[0]) != mid || !pl.side_q.empty()) continue;
+    if (pl.kind != N_POOL || resolve(pl.in[0]) != mid) continue;
+    if (!pl.side_q.empty() && (!i8 || pl.side_q.size() > 1 || st.O != 64)) continue;
     const PoolParams& pp = pl.pool;
     if (pp.kind != 0 || pp.adaptive || pp.KH != 3 || pp.KW != 3 || pp.sh != 2 || pp.sw != 2 || pp.pt != 1 || pp.pl != 1 ||
-        pp.OH * 2 != st.OH || pp.OW * 2 != st.OW || tensors_[resolve(pl.out)].fmt != FMT_BF16X2)
+        pp.OH * 2 != st.OH || pp.OW * 2 != st.OW || tensors_[resolve(pl.out)].fmt != want_out)
       continue;
     st.pool_fused = true;
     st.pool_oh = pp.OH;
     st.pool_ow = pp.OW;
     st.pool_name = pl.name;
     st.out = pl.out;
+    st.side_q = pl.side_q;
     st.flops += pl.flops;
     nodes_.erase(nodes_.begin() + k + 1);
   }

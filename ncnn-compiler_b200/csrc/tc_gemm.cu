@@ -1459,16 +1459,23 @@ cudaError_t tc_launch_stem(const TcStemLaunch& L, cudaStream_t stream) {
   return e != cudaSuccess ? e : cudaGetLastError();
 }
 
-std::string tc_plan_stem_pool(TcStemPoolLaunch* L, const TcStemConv& c, const TcEpilogue& e, int pooled_h, int pooled_w, int sm_count) {
-  if (c.kind != GEMM_BF16X3 || e.out_mode != OUT_BF16X2) return "the stem + pooling kernel takes and writes bf16 pairs";
+std::string tc_plan_stem_pool(TcStemPoolLaunch* L, const TcStemConv& c, const TcEpilogue& e_in, int pooled_h, int pooled_w, int sm_count) {
+  const bool i8 = c.kind == GEMM_I8;
+  if (!(c.kind == GEMM_BF16X3 && e_in.out_mode == OUT_BF16X2) && !(i8 && e_in.out_mode == OUT_F32))
+    return "the stem + pooling kernel writes bf16 pairs from bf16 pairs, or fp32 from int8";
   const int N = c.out_channels;
   if (N != 32 && N != 64) return "the stem + pooling kernel takes 32 or 64 output channels";
-  if (e.act != ACT_NONE && e.act != ACT_RELU && e.act != ACT_CLIP) return "the stem + pooling kernel applies no activation but ReLU and clip";
+  if (e_in.act != ACT_NONE && e_in.act != ACT_RELU && e_in.act != ACT_CLIP) return "the stem + pooling kernel applies no activation but ReLU and clip";
   if (c.OH != 2 * pooled_h || c.OW != 2 * pooled_w || pooled_h < 1 || pooled_w < 1) return "the pooled extent must be half the convolution's";
-  // the convolution part is planned as for tc_stem_kernel (validation, input and weight maps, operand geometry)
+  if (e_in.side_count > 1 || (e_in.side_count == 1 && (!i8 || N != 64))) return "one int8 copy of 64 channels at most";
+  // the convolution part is planned as for tc_stem_kernel (validation, input and weight maps, operand geometry);
+  // the int8 copy belongs to the pooled tensor
+  TcEpilogue e = e_in;
+  e.side_count = 0;
   TcStemLaunch conv;
   std::string err = tc_plan_stem(&conv, c, e, sm_count);
   if (!err.empty()) return err;
+  const int planes = i8 ? 1 : 2;
   TcStemPoolParams& pp = L->pp;
   pp.s = conv.p;
   pp.images = c.images;
@@ -1476,38 +1483,54 @@ std::string tc_plan_stem_pool(TcStemPoolLaunch* L, const TcStemConv& c, const Tc
   pp.POW = pooled_w;
   pp.ring_row_bytes = (c.OW * N * 4 + 1023) / 1024 * 1024;
   pp.stage_tile_bytes = (pooled_w * 64 + 1023) / 1024 * 1024;
-  const int weights = c.KH * 2 * conv.p.b_slot;
-  const int stage = 2 * conv.p.a_plane_bytes;
-  const int halves = N / 32;
-  L->smem_bytes = weights + 2 * stage + 3 * pp.ring_row_bytes + 2 * halves * pp.stage_tile_bytes + 1024;
+  pp.has_side = e_in.side_count;
+  pp.side_scale = e_in.side_count ? e_in.side_scale[0] : 0.0f;
+  const int weights = c.KH * planes * conv.p.b_slot;
+  const int stage = planes * conv.p.a_plane_bytes;
+  // staging tiles of 64-byte rows: bf16 pairs 2 planes x N / 32, fp32 N / 16 (+ one for the int8 copy)
+  const int tiles = i8 ? N / 16 + pp.has_side : 2 * (N / 32);
+  L->smem_bytes = weights + 2 * stage + 3 * pp.ring_row_bytes + tiles * pp.stage_tile_bytes + 1024;
   if (L->smem_bytes > tc_smem_budget(GEMM_BF16X3) + 1024) return "shared memory cannot hold the weights, two row stages and three result rows";
   L->smem_bytes = std::max(L->smem_bytes, 120 * 1024);  // one CTA per SM: each allocates tensor memory
   const long long pooled_rows = static_cast<long long>(c.images) * pooled_h;
   if (pooled_rows * pooled_w > 0x7fffffffll) return "too many pooled pixels for one launch";
   L->grid = static_cast<int>(std::min<long long>(pooled_rows, sm_count));
+  L->kind = c.kind;
   L->map_a0 = conv.map_a0;
   L->map_a1 = conv.map_a1;
   L->map_b0 = conv.map_b0;
   L->map_b1 = conv.map_b1;
+  const uint64_t pixels = static_cast<uint64_t>(pooled_rows) * pooled_w;
+  if (i8) {
+    // pooled result: [pooled pixels][N] fp32, boxes of 16 channels x one pooled row; the int8 copy in one box
+    err = encode_tiled_2d(&L->map_o0, GEMM_TF32, e.out0, N, pixels, static_cast<uint64_t>(N) * 4, 16, static_cast<uint32_t>(pooled_w), 64);
+    if (err.empty() && pp.has_side)
+      err = encode_tiled_2d(&L->map_o1, GEMM_I8, e_in.side_q[0], N, pixels, static_cast<uint64_t>(N), 64, static_cast<uint32_t>(pooled_w), 64);
+    return err;
+  }
   // pooled result: [pooled pixels][N] bf16 per plane, boxes of 32 channels x one pooled row, 64-byte swizzle
-  err = encode_tiled_2d(&L->map_o0, GEMM_BF16X3, e.out0, N, static_cast<uint64_t>(pooled_rows) * pooled_w, static_cast<uint64_t>(N) * 2, 32,
-                        static_cast<uint32_t>(pooled_w), 64);
+  err = encode_tiled_2d(&L->map_o0, GEMM_BF16X3, e.out0, N, pixels, static_cast<uint64_t>(N) * 2, 32, static_cast<uint32_t>(pooled_w), 64);
   if (err.empty())
-    err = encode_tiled_2d(&L->map_o1, GEMM_BF16X3, e.out1, N, static_cast<uint64_t>(pooled_rows) * pooled_w, static_cast<uint64_t>(N) * 2, 32,
-                          static_cast<uint32_t>(pooled_w), 64);
+    err = encode_tiled_2d(&L->map_o1, GEMM_BF16X3, e.out1, N, pixels, static_cast<uint64_t>(N) * 2, 32, static_cast<uint32_t>(pooled_w), 64);
   return err;
 }
 
 cudaError_t tc_launch_stem_pool(const TcStemPoolLaunch& L, cudaStream_t stream) {
   static PerDeviceOnce attr_once;
   const cudaError_t attr_err = attr_once.run([] {
-    return cudaFuncSetAttribute(tc_stem_pool_kernel<GEMM_BF16X3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                tc_smem_budget(GEMM_BF16X3) + 1024);
+    cudaError_t e = cudaFuncSetAttribute(tc_stem_pool_kernel<GEMM_BF16X3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         tc_smem_budget(GEMM_BF16X3) + 1024);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(tc_stem_pool_kernel<GEMM_I8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               tc_smem_budget(GEMM_BF16X3) + 1024);
+    return e;
   });
   if (attr_err != cudaSuccess) return attr_err;
   KernelLaunchConfig lc(L.grid, kStemPoolThreads, L.smem_bytes, false, stream);
-  const cudaError_t e = cudaLaunchKernelEx(&lc.cfg, tc_stem_pool_kernel<GEMM_BF16X3>, L.pp, L.map_a0, L.map_a1, L.map_b0, L.map_b1,
-                                           L.map_o0, L.map_o1);
+  const cudaError_t e =
+      L.kind == GEMM_I8 ? cudaLaunchKernelEx(&lc.cfg, tc_stem_pool_kernel<GEMM_I8>, L.pp, L.map_a0, L.map_a1, L.map_b0, L.map_b1, L.map_o0, L.map_o1)
+                        : cudaLaunchKernelEx(&lc.cfg, tc_stem_pool_kernel<GEMM_BF16X3>, L.pp, L.map_a0, L.map_a1, L.map_b0, L.map_b1,
+                                             L.map_o0, L.map_o1);
   return e != cudaSuccess ? e : cudaGetLastError();
 }
 

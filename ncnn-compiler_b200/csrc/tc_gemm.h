@@ -240,13 +240,15 @@ struct TcStemPoolLaunch {
   alignas(64) CUtensorMap map_a1{};
   alignas(64) CUtensorMap map_b0{};
   alignas(64) CUtensorMap map_b1{};
-  alignas(64) CUtensorMap map_o0{};  // pooled result, bf16 hi / mid planes
+  alignas(64) CUtensorMap map_o0{};  // pooled result: bf16 hi / mid planes, or fp32 and its int8 copy
   alignas(64) CUtensorMap map_o1{};
   int grid = 0;
   int smem_bytes = 0;
+  int kind = GEMM_BF16X3;
 };
-// `epilogue` describes the POOLED tensor (bf16 pairs, dense rows of out_channels); pooled extent pooled_h x pooled_w
-// = half the convolution's output extent (3x3 windows, stride 2, one pixel of padding above and to the left).
+// `epilogue` describes the POOLED tensor (dense rows of out_channels: bf16 pairs behind a bf16-pair stem, fp32 with at
+// most one int8 copy behind an int8 stem); pooled extent pooled_h x pooled_w = half the convolution's output extent
+// (3x3 windows, stride 2, one pixel of padding above and to the left).
 std::string tc_plan_stem_pool(TcStemPoolLaunch* launch, const struct TcStemConv& conv, const TcEpilogue& epilogue, int pooled_h,
                               int pooled_w, int sm_count);
 cudaError_t tc_launch_stem_pool(const TcStemPoolLaunch& launch, cudaStream_t stream);

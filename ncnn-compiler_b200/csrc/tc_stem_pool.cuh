@@ -1,4 +1,4 @@
-// Stem convolution with the 3x3 stride-2 max pooling that follows it, in one kernel (fp32 accuracy mode).
+// Stem convolution with the 3x3 stride-2 max pooling that follows it, in one kernel (bf16-pair or int8 operands).
 //
 // tc_stem_kernel writes the stem's result (the largest tensor of a ResNet) to HBM and the pooling kernel reads
 // it back.  Here a CTA owns a contiguous range of POOLED rows and walks the convolution rows they need in
@@ -9,14 +9,16 @@
 // epilogue warps take the 3x3 maxima out of the ring, split them into bf16 pairs and store the pooled row with
 // TMA.  The stem's own result never reaches HBM.  One convolution row per range is computed twice (2 % at 148
 // ranges over 64 x 56 pooled rows).  The values and their order are those of the two separate kernels: the
-// same bits.
+// same bits.  Results: bf16 pairs (hi and mid planes) for the bf16 form; fp32, and optionally an int8 copy
+// Q(value, side_scale) for the int8 convolution that reads the pooled tensor next, for the int8 form.
 #pragma once
 
 #include "tc_stem.cuh"
 
 namespace nb {
 
-constexpr int kStemPoolThreads = 192;  // warp 0 producer, 1 MMA, 2-5 epilogue and pooling
+constexpr int kStemPoolThreads = 320;  // warp 0 producer, 1 MMA, 2-9 epilogue and pooling (two warps per TMEM lane quarter)
+constexpr int kStemPoolEpiThreads = 256;
 
 struct TcStemPoolParams {
   TcStemParams s;       // the convolution (tiles, staging and output fields unused)
@@ -24,6 +26,8 @@ struct TcStemPoolParams {
   int POH, POW;         // pooled extent: OH / 2, OW / 2 (3x3 windows, stride 2, one pixel of padding)
   int ring_row_bytes;   // one convolution row in the ring: OW x N fp32, rounded to 1 KB
   int stage_tile_bytes; // one staging tile of the pooled row: POW rows x 64 bytes, rounded to 1 KB
+  int has_side;         // fp32 results: an int8 copy leaves through the second output map
+  float side_scale;
 };
 
 // f(img, oh, last) for every convolution row of this CTA, `last` when the row completes a pooled row
@@ -40,7 +44,6 @@ __device__ __forceinline__ void stem_pool_rows(const TcStemPoolParams& p, F&& f)
   }
 }
 
-// (KIND: bf16 pairs are the only form built; a template so that every translation unit may include this file)
 template <int KIND>
 __global__ void __launch_bounds__(kStemPoolThreads, 1)
 tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_constant__ CUtensorMap map_a0,
@@ -49,6 +52,7 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
                     const __grid_constant__ CUtensorMap map_o1) {
   using namespace ptx;
   const TcStemParams& p = pp.s;
+  constexpr int PLANES = KIND == GEMM_I8 ? 1 : 2;
   grid_dependency_trigger();
   extern __shared__ uint8_t stem_pool_smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[2];
@@ -57,6 +61,7 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
   __shared__ __align__(8) uint64_t tempty_bar[2];
   __shared__ __align__(8) uint64_t weights_bar;
   __shared__ __align__(16) float tile_bias[128];
+  __shared__ __align__(16) float tile_scale[128];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -65,8 +70,8 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
   const uint32_t smem_base = (smem_u32(stem_pool_smem_raw) + 1023u) & ~1023u;
   constexpr int S = 2;  // row stages (a stage holds the KH input rows of one convolution row, both planes)
   const uint32_t b_region = smem_base;  // [KH][plane][b_slot]
-  const uint32_t a_region = b_region + static_cast<uint32_t>(p.KH * 2) * static_cast<uint32_t>(p.b_slot);
-  const uint32_t stage_bytes = 2u * static_cast<uint32_t>(p.a_plane_bytes);
+  const uint32_t a_region = b_region + static_cast<uint32_t>(p.KH * PLANES) * static_cast<uint32_t>(p.b_slot);
+  const uint32_t stage_bytes = static_cast<uint32_t>(PLANES) * static_cast<uint32_t>(p.a_plane_bytes);
   const uint32_t ring = a_region + static_cast<uint32_t>(S) * stage_bytes;           // three convolution rows, fp32
   const uint32_t staging = ring + 3u * static_cast<uint32_t>(pp.ring_row_bytes);    // pooled row: [plane][half][POW][64 B]
   volatile int* abort_ptr = &abort_flag;
@@ -77,16 +82,18 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
       mbar_init(smem_u32(&full_bar[i]), 1);
       mbar_init(smem_u32(&empty_bar[i]), 1);
       mbar_init(smem_u32(&tfull_bar[i]), 1);
-      mbar_init(smem_u32(&tempty_bar[i]), 4);
+      mbar_init(smem_u32(&tempty_bar[i]), kStemPoolEpiThreads / 32);
     }
     mbar_init(smem_u32(&weights_bar), 1);
     fence_mbar_init();
     prefetch_tensormap(&map_a0);
-    prefetch_tensormap(&map_a1);
     prefetch_tensormap(&map_b0);
-    prefetch_tensormap(&map_b1);
+    if (PLANES == 2) {
+      prefetch_tensormap(&map_a1);
+      prefetch_tensormap(&map_b1);
+    }
     prefetch_tensormap(&map_o0);
-    prefetch_tensormap(&map_o1);
+    if (PLANES == 2 || pp.has_side) prefetch_tensormap(&map_o1);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(&tmem_slot), 256);
@@ -94,7 +101,10 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
   }
   if (threadIdx.x >= 64) {
     const int t = static_cast<int>(threadIdx.x) - 64;
-    tile_bias[t] = (p.bias != nullptr && t < p.N) ? __ldg(p.bias + t) : 0.0f;
+    if (t < 128) {
+      tile_bias[t] = (p.bias != nullptr && t < p.N) ? __ldg(p.bias + t) : 0.0f;
+      tile_scale[t] = (KIND == GEMM_I8 && t < p.N) ? __ldg(p.scale + t) : 0.0f;
+    }
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -107,11 +117,12 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
     const CUtensorMap* map_a = lane ? &map_a1 : &map_a0;
     const CUtensorMap* map_b = lane ? &map_b1 : &map_b0;
     const uint32_t wb = smem_u32(&weights_bar);
-    if (lane == 0) mbar_arrive_expect_tx(wb, static_cast<uint32_t>(p.KH * 2) * static_cast<uint32_t>(p.N) * 64u);
+    if (lane == 0) mbar_arrive_expect_tx(wb, static_cast<uint32_t>(p.KH * PLANES) * static_cast<uint32_t>(p.N) * 64u);
     __syncwarp();
-    if (lane < 2) {
+    if (lane < PLANES) {
+      // (the K coordinate counts elements: 32 bf16 or 64 int8 per filter row)
       for (int kh = 0; kh < p.KH; ++kh)
-        tma_load_2d(b_region + static_cast<uint32_t>(kh * 2 + lane) * p.b_slot, map_b, wb, kh * 32, 0);
+        tma_load_2d(b_region + static_cast<uint32_t>(kh * PLANES + lane) * p.b_slot, map_b, wb, kh * (KIND == GEMM_I8 ? 64 : 32), 0);
     }
     int s = 0;
     uint32_t ph = 0;
@@ -122,7 +133,7 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
       int w = 1;
       if (lane == 0) {
         w = mbar_wait_bounded(smem_u32(&empty_bar[s]), ph ^ 1u, abort_ptr, kTcWaitLimitNs) ? 1 : 0;
-        if (w) mbar_arrive_expect_tx(fb, static_cast<uint32_t>(2 * p.KH) * static_cast<uint32_t>(p.row_bytes));
+        if (w) mbar_arrive_expect_tx(fb, static_cast<uint32_t>(PLANES * p.KH) * static_cast<uint32_t>(p.row_bytes));
       }
       w = __shfl_sync(0xffffffffu, w, 0);
       if (!w) {
@@ -130,7 +141,7 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
         return false;
       }
       // rows above or below the image are filled with zeros by the copy
-      if (lane < 2)
+      if (lane < PLANES)
         tma_load_4d(a_region + static_cast<uint32_t>(s) * stage_bytes + static_cast<uint32_t>(lane) * p.a_plane_bytes, map_a, fb,
                     0, 0, oh * p.stride_h - p.pad_t, img);
       ++issued;
@@ -153,7 +164,8 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
   } else if (warp == 1) {
     // ---------------------------------------------------------- MMA issuer (as tc_stem_kernel)
     if (lane == 0) {
-      const uint32_t idesc = instr_desc(1u, 1u, kTcBlockM, static_cast<uint32_t>(p.N));
+      const uint32_t idesc = KIND == GEMM_I8 ? instr_desc(2u, 1u, kTcBlockM, static_cast<uint32_t>(p.N))
+                                             : instr_desc(1u, 1u, kTcBlockM, static_cast<uint32_t>(p.N));
       bool ok = mbar_wait_bounded(smem_u32(&weights_bar), 0, abort_ptr, kTcWaitLimitNs);
       tc_fence_after_sync();
       const uint64_t a_fixed = smem_desc_plain(0u, 16u, 128u);
@@ -177,14 +189,18 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
           uint32_t accumulate = 0u;
           for (int kh = 0; kh < p.KH; ++kh) {
             const uint64_t a_hi = a_hi0 + static_cast<uint64_t>(kh) * row_units;
-            const uint64_t b_hi = b_first + static_cast<uint64_t>(2 * kh) * b_slot_units;
+            const uint64_t b_hi = b_first + static_cast<uint64_t>(PLANES * kh) * b_slot_units;
 #pragma unroll
             for (int ks = 0; ks < 2; ++ks) {
               const uint64_t ka = a_hi + 2u * ks;
               const uint64_t kb = b_hi + 2u * ks;
-              mma_f16(d_tmem, ka + a_plane_units, kb, idesc, accumulate);  // mid * hi
-              mma_f16(d_tmem, ka, kb + b_slot_units, idesc, 1u);           // hi * mid
-              mma_f16(d_tmem, ka, kb, idesc, 1u);                          // hi * hi
+              if (KIND == GEMM_I8) {
+                mma_i8(d_tmem, ka, kb, idesc, accumulate);
+              } else {
+                mma_f16(d_tmem, ka + a_plane_units, kb, idesc, accumulate);  // mid * hi
+                mma_f16(d_tmem, ka, kb + b_slot_units, idesc, 1u);           // hi * mid
+                mma_f16(d_tmem, ka, kb, idesc, 1u);                          // hi * hi
+              }
               accumulate = 1u;
             }
           }
@@ -202,9 +218,11 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
       if (!ok && atomicCAS(const_cast<int*>(abort_ptr), 0, 1) == 0) atomicCAS(p.status, 0, TC_TIMEOUT_MMA);
     }
   } else {
-    // ------------------------------------------------------------ epilogue and pooling (warps 2-5)
-    const int t = static_cast<int>(threadIdx.x) - 64;  // 0..127: the accumulator row = pixel of the convolution row
-    const int quarter = warp & 3;
+    // ------------------------------------------------------------ epilogue and pooling (warps 2-9)
+    // warps 2-5 drain the first half of the channels, warps 6-9 the second; all 256 threads pool
+    const int t = static_cast<int>(threadIdx.x) - 64;
+    const int col_half = warp >= 6 ? 1 : 0;
+    const int quarter = warp & 3;  // TMEM lanes 32*quarter.. = pixels of the convolution row
     const int px = quarter * 32 + lane;
     const int chunks = p.N / 4;                // 16-byte chunks of a ring row entry (N fp32 per pixel)
     const uint32_t mask = static_cast<uint32_t>(chunks > 16 ? 15 : chunks - 1);  // chunk ^ (pixel & mask): spreads the banks
@@ -225,7 +243,7 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc) * 128u;
       const uint32_t slot = ring + static_cast<uint32_t>(oh % 3) * static_cast<uint32_t>(pp.ring_row_bytes);
 #pragma unroll 1
-      for (int c0 = 0; c0 < p.N; c0 += 16) {
+      for (int c0 = col_half * (p.N / 2); c0 < (col_half + 1) * (p.N / 2); c0 += 16) {
         uint32_t v[16];
         tmem_ld16(t_row + static_cast<uint32_t>(c0), v);
         tmem_ld_wait();
@@ -233,11 +251,25 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             const float4 b4 = *reinterpret_cast<const float4*>(&tile_bias[c0 + 4 * g]);
+            float t0, t1, t2, t3;
+            if (KIND == GEMM_I8) {
+              // dequantise: float(accumulator) * scale[channel], then bias (the order of the stand-alone epilogue)
+              const float4 s4 = *reinterpret_cast<const float4*>(&tile_scale[c0 + 4 * g]);
+              t0 = __fmul_rn(static_cast<float>(static_cast<int>(v[4 * g + 0])), s4.x);
+              t1 = __fmul_rn(static_cast<float>(static_cast<int>(v[4 * g + 1])), s4.y);
+              t2 = __fmul_rn(static_cast<float>(static_cast<int>(v[4 * g + 2])), s4.z);
+              t3 = __fmul_rn(static_cast<float>(static_cast<int>(v[4 * g + 3])), s4.w);
+            } else {
+              t0 = __uint_as_float(v[4 * g + 0]);
+              t1 = __uint_as_float(v[4 * g + 1]);
+              t2 = __uint_as_float(v[4 * g + 2]);
+              t3 = __uint_as_float(v[4 * g + 3]);
+            }
             float4 y;
-            y.x = fminf(fmaxf(__fadd_rn(__fadd_rn(__uint_as_float(v[4 * g + 0]), b4.x), 0.0f), act_lo), act_hi);
-            y.y = fminf(fmaxf(__fadd_rn(__fadd_rn(__uint_as_float(v[4 * g + 1]), b4.y), 0.0f), act_lo), act_hi);
-            y.z = fminf(fmaxf(__fadd_rn(__fadd_rn(__uint_as_float(v[4 * g + 2]), b4.z), 0.0f), act_lo), act_hi);
-            y.w = fminf(fmaxf(__fadd_rn(__fadd_rn(__uint_as_float(v[4 * g + 3]), b4.w), 0.0f), act_lo), act_hi);
+            y.x = fminf(fmaxf(__fadd_rn(__fadd_rn(t0, b4.x), 0.0f), act_lo), act_hi);
+            y.y = fminf(fmaxf(__fadd_rn(__fadd_rn(t1, b4.y), 0.0f), act_lo), act_hi);
+            y.z = fminf(fmaxf(__fadd_rn(__fadd_rn(t2, b4.z), 0.0f), act_lo), act_hi);
+            y.w = fminf(fmaxf(__fadd_rn(__fadd_rn(t3, b4.w), 0.0f), act_lo), act_hi);
             const uint32_t chunk = static_cast<uint32_t>(c0 / 4 + g);
             const uint32_t at = slot + static_cast<uint32_t>(px) * entry + ((chunk ^ (static_cast<uint32_t>(px) & mask)) << 4);
             asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(at), "f"(y.x), "f"(y.y), "f"(y.z), "f"(y.w) : "memory");
@@ -249,11 +281,11 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
       if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
       acc ^= 1;
       if (acc == 0) acc_ph ^= 1u;
-      named_barrier_sync(1, 128);  // the row is in the ring
+      named_barrier_sync(1, kStemPoolEpiThreads);  // the row is in the ring
       if (last) {
         // ---- pooled row j: maxima over rows 2j-1 .. 2j+1 and pixels 2x-1 .. 2x+1 that exist
         if (t == 0) tma_store_wait_read(0);  // the staging tiles of the pooled row before have been read out
-        named_barrier_sync(2, 128);
+        named_barrier_sync(2, kStemPoolEpiThreads);
         const int items = pp.POW * chunks;
         // rows and pixels outside the image are replaced by their neighbour inside the window (a maximum
         // does not change when an element is taken twice): nine loads without a branch
@@ -262,7 +294,7 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
         const uint32_t row_b = ring + static_cast<uint32_t>((2 * j) % 3) * static_cast<uint32_t>(pp.ring_row_bytes);
         const uint32_t row_c = ring + static_cast<uint32_t>((2 * j + 1) % 3) * static_cast<uint32_t>(pp.ring_row_bytes);
 #pragma unroll 1
-        for (int item = t; item < items; item += 128) {
+        for (int item = t; item < items; item += kStemPoolEpiThreads) {
           const int x = item >> chunk_shift, c = item & (chunks - 1);
           float4 v[9];
 #pragma unroll
@@ -276,25 +308,46 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
           float4 m = v[0];
 #pragma unroll
           for (int i = 1; i < 9; ++i) m = make_float4(fmaxf(m.x, v[i].x), fmaxf(m.y, v[i].y), fmaxf(m.z, v[i].z), fmaxf(m.w, v[i].w));
-          uint32_t hi0, mid0, hi1, mid1;
-          split_bf16x2(m.x, m.y, hi0, mid0);
-          split_bf16x2(m.z, m.w, hi1, mid1);
-          // staging: [plane][32-channel half][POW rows][64 bytes], 64-byte swizzle as the store expects
-          const int half = c >> 3, c8 = c & 7;
-          const uint32_t at = staging + static_cast<uint32_t>(half) * static_cast<uint32_t>(pp.stage_tile_bytes) +
-                              stage_chunk_offset(x, c8 >> 1) + static_cast<uint32_t>((c8 & 1) * 8);
-          const uint32_t plane = static_cast<uint32_t>((p.N + 31) / 32) * static_cast<uint32_t>(pp.stage_tile_bytes);
-          asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(at), "r"(hi0), "r"(hi1) : "memory");
-          asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(at + plane), "r"(mid0), "r"(mid1) : "memory");
+          if (KIND == GEMM_I8) {
+            // fp32 results: staging [16-channel box][POW rows][64 bytes]; then the int8 copy, one tile of POW rows x N bytes
+            const uint32_t at = staging + static_cast<uint32_t>(c >> 2) * static_cast<uint32_t>(pp.stage_tile_bytes) + stage_chunk_offset(x, c & 3);
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(at), "f"(m.x), "f"(m.y), "f"(m.z), "f"(m.w) : "memory");
+            if (pp.has_side) {
+              const uint32_t word = (static_cast<uint32_t>(quantize_rha(m.x, pp.side_scale)) & 0xffu) |
+                                    ((static_cast<uint32_t>(quantize_rha(m.y, pp.side_scale)) & 0xffu) << 8) |
+                                    ((static_cast<uint32_t>(quantize_rha(m.z, pp.side_scale)) & 0xffu) << 16) |
+                                    ((static_cast<uint32_t>(quantize_rha(m.w, pp.side_scale)) & 0xffu) << 24);
+              const uint32_t side_at = staging + static_cast<uint32_t>(p.N / 16) * static_cast<uint32_t>(pp.stage_tile_bytes) +
+                                       stage_chunk_offset(x, c >> 2) + static_cast<uint32_t>((c & 3) * 4);
+              asm volatile("st.shared.b32 [%0], %1;" ::"r"(side_at), "r"(word) : "memory");
+            }
+          } else {
+            uint32_t hi0, mid0, hi1, mid1;
+            split_bf16x2(m.x, m.y, hi0, mid0);
+            split_bf16x2(m.z, m.w, hi1, mid1);
+            // staging: [plane][32-channel half][POW rows][64 bytes], 64-byte swizzle as the store expects
+            const int half = c >> 3, c8 = c & 7;
+            const uint32_t at = staging + static_cast<uint32_t>(half) * static_cast<uint32_t>(pp.stage_tile_bytes) +
+                                stage_chunk_offset(x, c8 >> 1) + static_cast<uint32_t>((c8 & 1) * 8);
+            const uint32_t plane = static_cast<uint32_t>((p.N + 31) / 32) * static_cast<uint32_t>(pp.stage_tile_bytes);
+            asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(at), "r"(hi0), "r"(hi1) : "memory");
+            asm volatile("st.shared.v2.b32 [%0], {%1, %2};" ::"r"(at + plane), "r"(mid0), "r"(mid1) : "memory");
+          }
         }
         fence_proxy_async_smem();
-        named_barrier_sync(1, 128);  // staged; and every read of the ring for this pooled row is done
+        named_barrier_sync(1, kStemPoolEpiThreads);  // staged; and every read of the ring for this pooled row is done
         if (t == 0) {
-          const int halves = (p.N + 31) / 32;
           const int m_first = static_cast<int>(q) * pp.POW;  // pooled pixels before this row
-          for (int h = 0; h < halves; ++h) {
-            tma_store_2d(&map_o0, staging + static_cast<uint32_t>(h) * pp.stage_tile_bytes, 32 * h, m_first);
-            tma_store_2d(&map_o1, staging + static_cast<uint32_t>(halves + h) * pp.stage_tile_bytes, 32 * h, m_first);
+          if (KIND == GEMM_I8) {
+            const int boxes = p.N / 16;
+            for (int b = 0; b < boxes; ++b) tma_store_2d(&map_o0, staging + static_cast<uint32_t>(b) * pp.stage_tile_bytes, 16 * b, m_first);
+            if (pp.has_side) tma_store_2d(&map_o1, staging + static_cast<uint32_t>(boxes) * pp.stage_tile_bytes, 0, m_first);
+          } else {
+            const int halves = (p.N + 31) / 32;
+            for (int h = 0; h < halves; ++h) {
+              tma_store_2d(&map_o0, staging + static_cast<uint32_t>(h) * pp.stage_tile_bytes, 32 * h, m_first);
+              tma_store_2d(&map_o1, staging + static_cast<uint32_t>(halves + h) * pp.stage_tile_bytes, 32 * h, m_first);
+            }
           }
           tma_store_commit();
         }

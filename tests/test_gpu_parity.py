@@ -323,6 +323,27 @@ def test_stem_with_pooling_inside_equals_two_kernels(pkg, oracle, tmp_path, monk
     assert rel_l2(got[:1], want) <= 1e-3  # the tolerance of the fp32 path through a whole network
 
 
+@pytest.mark.parametrize("size,n", [(224, 3), (64, 5), (64, 40), (100, 7), (32, 2)])
+def test_int8_stem_with_pooling_inside_is_bit_exact(pkg, oracle, tmp_path, monkeypatch, size, n):
+    """The int8 stem pools its rows as well: fp32 maxima and their int8 copy for the next int8 convolution leave
+    the kernel, the dequantised stem result stays in shared memory.  Bit-equal to the two kernels and to the oracle."""
+    param, bin_ = pkg.zoo.resnet18(str(tmp_path / "r8"), int8=True, size=size, classes=24)
+    x = np.random.default_rng(size + n).uniform(-1, 1, (n, 3, size, size)).astype(np.float32)
+    m = pkg.Model(param, bin_)
+    kernels = [r["kernel"] for r in m.profile(n, 1)]
+    assert "tc_stem_pool_kernel<i8>" in kernels and not any(k.startswith("tc_stem_kernel") for k in kernels)
+    got = m.run(x)[0]
+    assert np.array_equal(m.run(x)[0], got)
+    m.close()
+    monkeypatch.setenv("NCNN_B200_STEM_POOL", "0")
+    m = pkg.Model(param, bin_)
+    assert any(k["kernel"].startswith("tc_stem_kernel") for k in m.profile(n, 1))
+    assert np.array_equal(m.run(x)[0], got)
+    m.close()
+    want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x[:2]])
+    assert np.array_equal(got[:2], want)
+
+
 def test_stem_with_odd_rows_keeps_its_pooling_kernel(pkg, tmp_path):
     """A stem whose output extent is odd does not pool in place (the pooled rows would not pair up with its rows)."""
     param, bin_ = pkg.zoo.resnet18(str(tmp_path / "r"), size=90, classes=24)
@@ -338,7 +359,7 @@ def test_int8_stem_rows_kernel_is_bit_exact(pkg, oracle, tmp_path, monkeypatch):
     param, bin_ = pkg.zoo.resnet18(str(tmp_path / "r8"), int8=True, size=96, classes=20)
     x = np.random.default_rng(21).uniform(-1, 1, (3, 3, 96, 96)).astype(np.float32)
     m = pkg.Model(param, bin_)
-    assert any(r["kernel"] == "tc_stem_kernel<i8>" for r in m.profile(3, 1))
+    assert any(r["kernel"] in ("tc_stem_kernel<i8>", "tc_stem_pool_kernel<i8>") for r in m.profile(3, 1))
     got = m.run(x)[0]
     m.close()
     monkeypatch.setenv("NCNN_B200_STEM_ROWS", "0")
