@@ -1489,8 +1489,8 @@ std::string tc_plan_stem_pool(TcStemPoolLaunch* L, const TcStemConv& c, const Tc
   const int stage = planes * conv.p.a_plane_bytes;
   // staging tiles of 64-byte rows: bf16 pairs 2 planes x N / 32, fp32 N / 16 (+ one for the int8 copy)
   const int tiles = i8 ? N / 16 + pp.has_side : 2 * (N / 32);
-  L->smem_bytes = weights + 2 * stage + 3 * pp.ring_row_bytes + tiles * pp.stage_tile_bytes + 1024;
-  if (L->smem_bytes > tc_smem_budget(GEMM_BF16X3) + 1024) return "shared memory cannot hold the weights, two row stages and three result rows";
+  L->smem_bytes = weights + 2 * stage + pp.ring_row_bytes + tiles * pp.stage_tile_bytes + 1024;
+  if (L->smem_bytes > tc_smem_budget(GEMM_BF16X3) + 1024) return "shared memory cannot hold the weights, two row stages and a result row";
   L->smem_bytes = std::max(L->smem_bytes, 120 * 1024);  // one CTA per SM: each allocates tensor memory
   const long long pooled_rows = static_cast<long long>(c.images) * pooled_h;
   if (pooled_rows * pooled_w > 0x7fffffffll) return "too many pooled pixels for one launch";

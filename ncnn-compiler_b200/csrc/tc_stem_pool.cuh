@@ -4,27 +4,29 @@
 // it back.  Here a CTA owns a contiguous range of POOLED rows and walks the convolution rows they need in
 // order: 2j-1, 2j, 2j+1 for the first pooled row j of the range (or of an image), then two new rows per pooled
 // row, because row 2j+1 is also row 2(j+1)-1.  Every convolution row is computed like a tile of tc_stem_kernel
-// (input rows by TMA, windows read in place, three bf16 MMAs per K step), drained from TMEM with bias and
-// activation into a ring of three fp32 rows in shared memory, and after the last row of a pooled row the
-// epilogue warps take the 3x3 maxima out of the ring, split them into bf16 pairs and store the pooled row with
-// TMA.  The stem's own result never reaches HBM.  One convolution row per range is computed twice (2 % at 148
-// ranges over 64 x 56 pooled rows).  The values and their order are those of the two separate kernels: the
-// same bits.  Results: bf16 pairs (hi and mid planes) for the bf16 form; fp32, and optionally an int8 copy
-// Q(value, side_scale) for the int8 convolution that reads the pooled tensor next, for the int8 form.
+// (input rows by TMA, windows read in place, three bf16 MMAs or one int8 MMA per K step; two MMA-issuing warps
+// take alternate rows).  Eight epilogue warps drain it from TMEM with bias and activation; a thread meets the
+// same pixel column and channels in every row, so the maximum over the three rows is kept in registers, and
+// the row that completes a pooled row writes it into one row of shared memory, from which the warps take the
+// maxima over pixels 2x-1 .. 2x+1, convert them and store the pooled row with TMA.  The stem's own result never
+// reaches HBM.  One convolution row per range is computed twice (2 % at 148 ranges over 64 x 56 pooled rows).
+// The values are those of the two separate kernels: the same bits.  Results: bf16 pairs (hi and mid planes)
+// for the bf16 form; fp32, and optionally an int8 copy Q(value, side_scale) for the int8 convolution that reads
+// the pooled tensor next, for the int8 form.
 #pragma once
 
 #include "tc_stem.cuh"
 
 namespace nb {
 
-constexpr int kStemPoolThreads = 320;  // warp 0 producer, 1 MMA, 2-9 epilogue and pooling (two warps per TMEM lane quarter)
+constexpr int kStemPoolThreads = 352;  // warp 0 producer, 1 and 10 MMA, 2-9 epilogue and pooling (two warps per TMEM lane quarter)
 constexpr int kStemPoolEpiThreads = 256;
 
 struct TcStemPoolParams {
   TcStemParams s;       // the convolution (tiles, staging and output fields unused)
   int images;
   int POH, POW;         // pooled extent: OH / 2, OW / 2 (3x3 windows, stride 2, one pixel of padding)
-  int ring_row_bytes;   // one convolution row in the ring: OW x N fp32, rounded to 1 KB
+  int ring_row_bytes;   // the row of vertical maxima: OW x N fp32, rounded to 1 KB
   int stage_tile_bytes; // one staging tile of the pooled row: POW rows x 64 bytes, rounded to 1 KB
   int has_side;         // fp32 results: an int8 copy leaves through the second output map
   float side_scale;
@@ -33,14 +35,17 @@ struct TcStemPoolParams {
 // f(img, oh, last) for every convolution row of this CTA, `last` when the row completes a pooled row
 template <class F>
 __device__ __forceinline__ void stem_pool_rows(const TcStemPoolParams& p, F&& f) {
-  const long long total = static_cast<long long>(p.images) * p.POH;
-  const long long q0 = total * blockIdx.x / gridDim.x, q1 = total * (blockIdx.x + 1) / gridDim.x;
-  for (long long q = q0; q < q1; ++q) {
-    const int img = static_cast<int>(q / p.POH);
-    const int j = static_cast<int>(q - static_cast<long long>(img) * p.POH);
-    const bool first = q == q0 || j == 0;  // nothing of this pooled row's window is in the ring yet
+  const long long total = static_cast<long long>(p.images) * p.POH;  // (fits an int: the planner checks)
+  const int q0 = static_cast<int>(total * blockIdx.x / gridDim.x), q1 = static_cast<int>(total * (blockIdx.x + 1) / gridDim.x);
+  int img = q0 / p.POH, j = q0 - img * p.POH;
+  for (int q = q0; q < q1; ++q) {
+    const bool first = q == q0 || j == 0;  // nothing of this pooled row's window has been computed yet
     for (int oh = max(first ? 2 * j - 1 : 2 * j, 0); oh <= 2 * j + 1; ++oh)
-      if (!f(img, oh, j, oh == 2 * j + 1, q)) return;
+      if (!f(img, oh, j, oh == 2 * j + 1, static_cast<long long>(q))) return;
+    if (++j == p.POH) {
+      j = 0;
+      ++img;
+    }
   }
 }
 
@@ -72,8 +77,8 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
   const uint32_t b_region = smem_base;  // [KH][plane][b_slot]
   const uint32_t a_region = b_region + static_cast<uint32_t>(p.KH * PLANES) * static_cast<uint32_t>(p.b_slot);
   const uint32_t stage_bytes = static_cast<uint32_t>(PLANES) * static_cast<uint32_t>(p.a_plane_bytes);
-  const uint32_t ring = a_region + static_cast<uint32_t>(S) * stage_bytes;           // three convolution rows, fp32
-  const uint32_t staging = ring + 3u * static_cast<uint32_t>(pp.ring_row_bytes);    // pooled row: [plane][half][POW][64 B]
+  const uint32_t ring = a_region + static_cast<uint32_t>(S) * stage_bytes;      // one row of vertical maxima, fp32
+  const uint32_t staging = ring + static_cast<uint32_t>(pp.ring_row_bytes);    // pooled row: tiles of [POW][64 B]
   volatile int* abort_ptr = &abort_flag;
 
   if (threadIdx.x == 0) {
@@ -161,8 +166,12 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
           mbar_wait_bounded(smem_u32(&full_bar[i % S]), static_cast<uint32_t>((i / S) & 1), &zero, 200000000ull);
       }
     }
-  } else if (warp == 1) {
-    // ---------------------------------------------------------- MMA issuer (as tc_stem_kernel)
+  } else if (warp == 1 || warp == 10) {
+    // ---------------------------------------------------------- MMA issuers (the MMAs of a row as in tc_stem_kernel)
+    // A thread issues one of these narrow MMAs every ~75 cycles, the tensor pipe could take one every ~48: two
+    // threads in two warps issue alternate rows, each with its own row stage and its own accumulator (MMAs
+    // into one accumulator must come from one thread, only then are they ordered).
+    const int me = warp == 1 ? 0 : 1;
     if (lane == 0) {
       const uint32_t idesc = KIND == GEMM_I8 ? instr_desc(2u, 1u, kTcBlockM, static_cast<uint32_t>(p.N))
                                              : instr_desc(1u, 1u, kTcBlockM, static_cast<uint32_t>(p.N));
@@ -174,11 +183,14 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
       const uint64_t row_units = static_cast<uint64_t>(p.row_bytes) >> 4;
       const uint64_t b_slot_units = static_cast<uint64_t>(p.b_slot) >> 4;
       const uint64_t b_first = b_fixed + ((b_region & 0x3ffffu) >> 4);
-      int s = 0, acc = 0;
-      uint32_t ph = 0, acc_ph = 0;
+      // row r of this CTA's sequence: stage r & 1, accumulator r & 1, issuer r & 1; phase (r >> 1) & 1 of both
+      const int s = me, acc = me;
+      uint32_t ph = 0;
+      int row = 0;
       if (ok) {
         stem_pool_rows(pp, [&](int, int, int, bool, long long) {
-          if (!mbar_wait_bounded(smem_u32(&tempty_bar[acc]), acc_ph ^ 1u, abort_ptr, kTcWaitLimitNs) ||
+          if ((row++ & 1) != me) return true;
+          if (!mbar_wait_bounded(smem_u32(&tempty_bar[acc]), ph ^ 1u, abort_ptr, kTcWaitLimitNs) ||
               !mbar_wait_bounded(smem_u32(&full_bar[s]), ph, abort_ptr, kTcWaitLimitNs)) {
             ok = false;
             return false;
@@ -206,12 +218,7 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
           }
           tc_commit(smem_u32(&empty_bar[s]));
           tc_commit(smem_u32(&tfull_bar[acc]));
-          if (++s == S) {
-            s = 0;
-            ph ^= 1u;
-          }
-          acc ^= 1;
-          if (acc == 0) acc_ph ^= 1u;
+          ph ^= 1u;
           return true;
         });
       }
@@ -235,44 +242,67 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
     int acc = 0;
     uint32_t acc_ph = 0;
     bool ok = true;
+    // Vertical maxima stay in registers: this thread drains the same pixel column and the same channels of every
+    // convolution row, so the maximum over rows 2j-1, 2j, 2j+1 needs no shared memory.  `odd_row` holds this
+    // thread's values of the last odd row (row 2j+1 is also row 2(j+1)-1), `upper` the maximum of rows 2j-1 and 2j;
+    // the odd row that completes a pooled row writes max(upper, row) into the one row of shared memory from which
+    // the horizontal maxima are taken: a third of the shared-memory reads and half of the writes of pooling out
+    // of three stored rows, next to MMAs that read their operands from the same memory.
+    float odd_row[32], upper[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) odd_row[i] = upper[i] = -INFINITY;
     stem_pool_rows(pp, [&](int img, int oh, int j, bool last, long long q) {
       ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&tfull_bar[acc]), acc_ph, abort_ptr, kTcWaitLimitNs) ? 1 : 0) != 0;
       if (!ok) return false;
       tc_fence_after_sync();
-      // ---- drain: bias and activation as the stand-alone epilogue, into ring slot oh % 3
+      // ---- drain: bias and activation as the stand-alone epilogue
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc) * 128u;
-      const uint32_t slot = ring + static_cast<uint32_t>(oh % 3) * static_cast<uint32_t>(pp.ring_row_bytes);
-#pragma unroll 1
-      for (int c0 = col_half * (p.N / 2); c0 < (col_half + 1) * (p.N / 2); c0 += 16) {
-        uint32_t v[16];
-        tmem_ld16(t_row + static_cast<uint32_t>(c0), v);
-        tmem_ld_wait();
-        if (px < p.OW) {
+      const bool odd = (oh & 1) != 0;
+      const bool row_above = oh > 0;  // an even row has row oh - 1 above it in `odd_row` unless it is the image's first
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        if (cc * 16 < p.N / 2) {
+          const int c0 = col_half * (p.N / 2) + cc * 16;
+          uint32_t v[16];
+          tmem_ld16(t_row + static_cast<uint32_t>(c0), v);
+          tmem_ld_wait();
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             const float4 b4 = *reinterpret_cast<const float4*>(&tile_bias[c0 + 4 * g]);
-            float t0, t1, t2, t3;
+            float y[4];
             if (KIND == GEMM_I8) {
               // dequantise: float(accumulator) * scale[channel], then bias (the order of the stand-alone epilogue)
               const float4 s4 = *reinterpret_cast<const float4*>(&tile_scale[c0 + 4 * g]);
-              t0 = __fmul_rn(static_cast<float>(static_cast<int>(v[4 * g + 0])), s4.x);
-              t1 = __fmul_rn(static_cast<float>(static_cast<int>(v[4 * g + 1])), s4.y);
-              t2 = __fmul_rn(static_cast<float>(static_cast<int>(v[4 * g + 2])), s4.z);
-              t3 = __fmul_rn(static_cast<float>(static_cast<int>(v[4 * g + 3])), s4.w);
+              y[0] = __fmul_rn(static_cast<float>(static_cast<int>(v[4 * g + 0])), s4.x);
+              y[1] = __fmul_rn(static_cast<float>(static_cast<int>(v[4 * g + 1])), s4.y);
+              y[2] = __fmul_rn(static_cast<float>(static_cast<int>(v[4 * g + 2])), s4.z);
+              y[3] = __fmul_rn(static_cast<float>(static_cast<int>(v[4 * g + 3])), s4.w);
             } else {
-              t0 = __uint_as_float(v[4 * g + 0]);
-              t1 = __uint_as_float(v[4 * g + 1]);
-              t2 = __uint_as_float(v[4 * g + 2]);
-              t3 = __uint_as_float(v[4 * g + 3]);
+              y[0] = __uint_as_float(v[4 * g + 0]);
+              y[1] = __uint_as_float(v[4 * g + 1]);
+              y[2] = __uint_as_float(v[4 * g + 2]);
+              y[3] = __uint_as_float(v[4 * g + 3]);
             }
-            float4 y;
-            y.x = fminf(fmaxf(__fadd_rn(__fadd_rn(t0, b4.x), 0.0f), act_lo), act_hi);
-            y.y = fminf(fmaxf(__fadd_rn(__fadd_rn(t1, b4.y), 0.0f), act_lo), act_hi);
-            y.z = fminf(fmaxf(__fadd_rn(__fadd_rn(t2, b4.z), 0.0f), act_lo), act_hi);
-            y.w = fminf(fmaxf(__fadd_rn(__fadd_rn(t3, b4.w), 0.0f), act_lo), act_hi);
-            const uint32_t chunk = static_cast<uint32_t>(c0 / 4 + g);
-            const uint32_t at = slot + static_cast<uint32_t>(px) * entry + ((chunk ^ (static_cast<uint32_t>(px) & mask)) << 4);
-            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(at), "f"(y.x), "f"(y.y), "f"(y.z), "f"(y.w) : "memory");
+            y[0] = fminf(fmaxf(__fadd_rn(__fadd_rn(y[0], b4.x), 0.0f), act_lo), act_hi);
+            y[1] = fminf(fmaxf(__fadd_rn(__fadd_rn(y[1], b4.y), 0.0f), act_lo), act_hi);
+            y[2] = fminf(fmaxf(__fadd_rn(__fadd_rn(y[2], b4.z), 0.0f), act_lo), act_hi);
+            y[3] = fminf(fmaxf(__fadd_rn(__fadd_rn(y[3], b4.w), 0.0f), act_lo), act_hi);
+            float* up = &upper[cc * 16 + 4 * g];
+            float* od = &odd_row[cc * 16 + 4 * g];
+            if (!odd) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) up[e] = row_above ? fmaxf(od[e], y[e]) : y[e];
+            } else {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) od[e] = y[e];
+              if (last && px < p.OW) {
+                const uint32_t chunk = static_cast<uint32_t>(c0 / 4 + g);
+                const uint32_t at = ring + static_cast<uint32_t>(px) * entry + ((chunk ^ (static_cast<uint32_t>(px) & mask)) << 4);
+                asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(at), "f"(fmaxf(up[0], y[0])), "f"(fmaxf(up[1], y[1])),
+                             "f"(fmaxf(up[2], y[2])), "f"(fmaxf(up[3], y[3]))
+                             : "memory");
+              }
+            }
           }
         }
       }
@@ -281,33 +311,25 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
       if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
       acc ^= 1;
       if (acc == 0) acc_ph ^= 1u;
-      named_barrier_sync(1, kStemPoolEpiThreads);  // the row is in the ring
       if (last) {
-        // ---- pooled row j: maxima over rows 2j-1 .. 2j+1 and pixels 2x-1 .. 2x+1 that exist
+        // ---- pooled row j: horizontal maxima over pixels 2x-1 .. 2x+1 of the row of vertical maxima
         if (t == 0) tma_store_wait_read(0);  // the staging tiles of the pooled row before have been read out
-        named_barrier_sync(2, kStemPoolEpiThreads);
+        named_barrier_sync(1, kStemPoolEpiThreads);  // the row of vertical maxima is complete
         const int items = pp.POW * chunks;
-        // rows and pixels outside the image are replaced by their neighbour inside the window (a maximum
-        // does not change when an element is taken twice): nine loads without a branch
-        const int r0 = max(2 * j - 1, 0);
-        const uint32_t row_a = ring + static_cast<uint32_t>(r0 % 3) * static_cast<uint32_t>(pp.ring_row_bytes);
-        const uint32_t row_b = ring + static_cast<uint32_t>((2 * j) % 3) * static_cast<uint32_t>(pp.ring_row_bytes);
-        const uint32_t row_c = ring + static_cast<uint32_t>((2 * j + 1) % 3) * static_cast<uint32_t>(pp.ring_row_bytes);
 #pragma unroll 1
         for (int item = t; item < items; item += kStemPoolEpiThreads) {
           const int x = item >> chunk_shift, c = item & (chunks - 1);
-          float4 v[9];
+          // (pixel -1 is replaced by pixel 0: a maximum does not change when an element is taken twice)
+          float4 v[3];
 #pragma unroll
           for (int dx = 0; dx < 3; ++dx) {
             const int sx = max(2 * x + dx - 1, 0);
             const uint32_t off = static_cast<uint32_t>(sx) * entry + ((static_cast<uint32_t>(c) ^ (static_cast<uint32_t>(sx) & mask)) << 4);
-            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v[dx].x), "=f"(v[dx].y), "=f"(v[dx].z), "=f"(v[dx].w) : "r"(row_a + off));
-            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v[3 + dx].x), "=f"(v[3 + dx].y), "=f"(v[3 + dx].z), "=f"(v[3 + dx].w) : "r"(row_b + off));
-            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v[6 + dx].x), "=f"(v[6 + dx].y), "=f"(v[6 + dx].z), "=f"(v[6 + dx].w) : "r"(row_c + off));
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v[dx].x), "=f"(v[dx].y), "=f"(v[dx].z), "=f"(v[dx].w) : "r"(ring + off));
           }
           float4 m = v[0];
 #pragma unroll
-          for (int i = 1; i < 9; ++i) m = make_float4(fmaxf(m.x, v[i].x), fmaxf(m.y, v[i].y), fmaxf(m.z, v[i].z), fmaxf(m.w, v[i].w));
+          for (int i = 1; i < 3; ++i) m = make_float4(fmaxf(m.x, v[i].x), fmaxf(m.y, v[i].y), fmaxf(m.z, v[i].z), fmaxf(m.w, v[i].w));
           if (KIND == GEMM_I8) {
             // fp32 results: staging [16-channel box][POW rows][64 bytes]; then the int8 copy, one tile of POW rows x N bytes
             const uint32_t at = staging + static_cast<uint32_t>(c >> 2) * static_cast<uint32_t>(pp.stage_tile_bytes) + stage_chunk_offset(x, c & 3);
