@@ -1459,6 +1459,8 @@ cudaError_t tc_launch_stem(const TcStemLaunch& L, cudaStream_t stream) {
   return e != cudaSuccess ? e : cudaGetLastError();
 }
 
+constexpr int kStemPoolMaxSmem = 218 * 1024;  // dynamic shared memory the stem + pooling kernel may ask for
+
 std::string tc_plan_stem_pool(TcStemPoolLaunch* L, const TcStemConv& c, const TcEpilogue& e_in, int pooled_h, int pooled_w, int sm_count) {
   const bool i8 = c.kind == GEMM_I8;
   if (!(c.kind == GEMM_BF16X3 && e_in.out_mode == OUT_BF16X2) && !(i8 && e_in.out_mode == OUT_F32))
@@ -1489,8 +1491,10 @@ std::string tc_plan_stem_pool(TcStemPoolLaunch* L, const TcStemConv& c, const Tc
   const int stage = planes * conv.p.a_plane_bytes;
   // staging tiles of 64-byte rows: bf16 pairs 2 planes x N / 32, fp32 N / 16 (+ one for the int8 copy)
   const int tiles = i8 ? N / 16 + pp.has_side : 2 * (N / 32);
-  L->smem_bytes = weights + 2 * stage + pp.ring_row_bytes + tiles * pp.stage_tile_bytes + 1024;
-  if (L->smem_bytes > tc_smem_budget(GEMM_BF16X3) + 1024) return "shared memory cannot hold the weights, two row stages and a result row";
+  const int fixed = weights + pp.ring_row_bytes + tiles * pp.stage_tile_bytes + 1024;
+  pp.row_stages = fixed + 4 * stage <= kStemPoolMaxSmem ? 4 : 2;
+  L->smem_bytes = fixed + pp.row_stages * stage;
+  if (L->smem_bytes > kStemPoolMaxSmem) return "shared memory cannot hold the weights, two row stages and a result row";
   L->smem_bytes = std::max(L->smem_bytes, 120 * 1024);  // one CTA per SM: each allocates tensor memory
   const long long pooled_rows = static_cast<long long>(c.images) * pooled_h;
   if (pooled_rows * pooled_w > 0x7fffffffll) return "too many pooled pixels for one launch";
@@ -1518,11 +1522,9 @@ std::string tc_plan_stem_pool(TcStemPoolLaunch* L, const TcStemConv& c, const Tc
 cudaError_t tc_launch_stem_pool(const TcStemPoolLaunch& L, cudaStream_t stream) {
   static PerDeviceOnce attr_once;
   const cudaError_t attr_err = attr_once.run([] {
-    cudaError_t e = cudaFuncSetAttribute(tc_stem_pool_kernel<GEMM_BF16X3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         tc_smem_budget(GEMM_BF16X3) + 1024);
+    cudaError_t e = cudaFuncSetAttribute(tc_stem_pool_kernel<GEMM_BF16X3>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStemPoolMaxSmem);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(tc_stem_pool_kernel<GEMM_I8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               tc_smem_budget(GEMM_BF16X3) + 1024);
+      e = cudaFuncSetAttribute(tc_stem_pool_kernel<GEMM_I8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kStemPoolMaxSmem);
     return e;
   });
   if (attr_err != cudaSuccess) return attr_err;

@@ -28,6 +28,7 @@ struct TcStemPoolParams {
   int POH, POW;         // pooled extent: OH / 2, OW / 2 (3x3 windows, stride 2, one pixel of padding)
   int ring_row_bytes;   // the row of vertical maxima: OW x N fp32, rounded to 1 KB
   int stage_tile_bytes; // one staging tile of the pooled row: POW rows x 64 bytes, rounded to 1 KB
+  int row_stages;       // input row stages in shared memory: 4, or 2 where 4 do not fit
   int has_side;         // fp32 results: an int8 copy leaves through the second output map
   float side_scale;
 };
@@ -60,10 +61,10 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
   constexpr int PLANES = KIND == GEMM_I8 ? 1 : 2;
   grid_dependency_trigger();
   extern __shared__ uint8_t stem_pool_smem_raw[];
-  __shared__ __align__(8) uint64_t full_bar[2];
-  __shared__ __align__(8) uint64_t empty_bar[2];
-  __shared__ __align__(8) uint64_t tfull_bar[2];
-  __shared__ __align__(8) uint64_t tempty_bar[2];
+  __shared__ __align__(8) uint64_t full_bar[4];
+  __shared__ __align__(8) uint64_t empty_bar[4];
+  __shared__ __align__(8) uint64_t tfull_bar[4];   // four accumulators of 64 columns: two per MMA issuer
+  __shared__ __align__(8) uint64_t tempty_bar[4];
   __shared__ __align__(8) uint64_t weights_bar;
   __shared__ __align__(16) float tile_bias[128];
   __shared__ __align__(16) float tile_scale[128];
@@ -73,7 +74,7 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(stem_pool_smem_raw) + 1023u) & ~1023u;
-  constexpr int S = 2;  // row stages (a stage holds the KH input rows of one convolution row, both planes)
+  const int S = pp.row_stages;  // row stages (a stage holds the KH input rows of one convolution row, both planes)
   const uint32_t b_region = smem_base;  // [KH][plane][b_slot]
   const uint32_t a_region = b_region + static_cast<uint32_t>(p.KH * PLANES) * static_cast<uint32_t>(p.b_slot);
   const uint32_t stage_bytes = static_cast<uint32_t>(PLANES) * static_cast<uint32_t>(p.a_plane_bytes);
@@ -83,7 +84,7 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 4; ++i) {
       mbar_init(smem_u32(&full_bar[i]), 1);
       mbar_init(smem_u32(&empty_bar[i]), 1);
       mbar_init(smem_u32(&tfull_bar[i]), 1);
@@ -183,20 +184,22 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
       const uint64_t row_units = static_cast<uint64_t>(p.row_bytes) >> 4;
       const uint64_t b_slot_units = static_cast<uint64_t>(p.b_slot) >> 4;
       const uint64_t b_first = b_fixed + ((b_region & 0x3ffffu) >> 4);
-      // row r of this CTA's sequence: stage r & 1, accumulator r & 1, issuer r & 1; phase (r >> 1) & 1 of both
-      const int s = me, acc = me;
-      uint32_t ph = 0;
+      // row r of this CTA's sequence: issuer r & 1, stage r % S, accumulator r & 3 (two per issuer, so that the
+      // MMAs of its next row run while the epilogue drains the row before)
       int row = 0;
       if (ok) {
         stem_pool_rows(pp, [&](int, int, int, bool, long long) {
-          if ((row++ & 1) != me) return true;
-          if (!mbar_wait_bounded(smem_u32(&tempty_bar[acc]), ph ^ 1u, abort_ptr, kTcWaitLimitNs) ||
+          const int r = row++;
+          if ((r & 1) != me) return true;
+          const int s = r % S, acc = r & 3;
+          const uint32_t ph = static_cast<uint32_t>((r / S) & 1), acc_ph = static_cast<uint32_t>((r >> 2) & 1);
+          if (!mbar_wait_bounded(smem_u32(&tempty_bar[acc]), acc_ph ^ 1u, abort_ptr, kTcWaitLimitNs) ||
               !mbar_wait_bounded(smem_u32(&full_bar[s]), ph, abort_ptr, kTcWaitLimitNs)) {
             ok = false;
             return false;
           }
           tc_fence_after_sync();
-          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * 128u;
+          const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * 64u;
           const uint64_t a_hi0 = a_fixed + (((a_region + static_cast<uint32_t>(s) * stage_bytes) & 0x3ffffu) >> 4);
           uint32_t accumulate = 0u;
           for (int kh = 0; kh < p.KH; ++kh) {
@@ -218,7 +221,6 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
           }
           tc_commit(smem_u32(&empty_bar[s]));
           tc_commit(smem_u32(&tfull_bar[acc]));
-          ph ^= 1u;
           return true;
         });
       }
@@ -256,16 +258,26 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
       if (!ok) return false;
       tc_fence_after_sync();
       // ---- drain: bias and activation as the stand-alone epilogue
-      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc) * 128u;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc) * 64u;
       const bool odd = (oh & 1) != 0;
       const bool row_above = oh > 0;  // an even row has row oh - 1 above it in `odd_row` unless it is the image's first
+      // this thread's 16 or 32 accumulator columns into registers, then the accumulator is free for the MMAs again
+      const int c_first = col_half * (p.N / 2);
+      const bool two_chunks = p.N / 2 > 16;
+      uint32_t vv[2][16];
+      tmem_ld16(t_row + static_cast<uint32_t>(c_first), vv[0]);
+      if (two_chunks) tmem_ld16(t_row + static_cast<uint32_t>(c_first + 16), vv[1]);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+      acc = (acc + 1) & 3;
+      if (acc == 0) acc_ph ^= 1u;
 #pragma unroll
       for (int cc = 0; cc < 2; ++cc) {
-        if (cc * 16 < p.N / 2) {
-          const int c0 = col_half * (p.N / 2) + cc * 16;
-          uint32_t v[16];
-          tmem_ld16(t_row + static_cast<uint32_t>(c0), v);
-          tmem_ld_wait();
+        if (cc == 0 || two_chunks) {
+          const int c0 = c_first + cc * 16;
+          const uint32_t (&v)[16] = vv[cc];
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             const float4 b4 = *reinterpret_cast<const float4*>(&tile_bias[c0 + 4 * g]);
@@ -306,11 +318,6 @@ tc_stem_pool_kernel(const __grid_constant__ TcStemPoolParams pp, const __grid_co
           }
         }
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
-      acc ^= 1;
-      if (acc == 0) acc_ph ^= 1u;
       if (last) {
         // ---- pooled row j: horizontal maxima over pixels 2x-1 .. 2x+1 of the row of vertical maxima
         if (t == 0) tma_store_wait_read(0);  // the staging tiles of the pooled row before have been read out
