@@ -283,8 +283,18 @@ void finish_plan(TcLaunch* L, int kind, long long M, int N, const TcEpilogue& e,
   }
   p.staging_bytes = staging / p.epi_groups;
   const int budget = kTcSmemBudget - staging;
-  p.stages = std::max(2, std::min(kTcMaxStages, budget / p.stage_bytes));
-  L->smem_bytes = p.stages * p.stage_bytes + staging + 1024;
+  // int8 K blocks are two to four MMAs over 12-32 KB: arming and releasing a ring stage (~450 cycles of barrier
+  // hand-shake per block, more than the block's copies and MMAs take) sets the pace.  A stage then holds several
+  // K blocks (a divisor of their count, at least three stages deep): one hand-shake for all of them.
+  p.sub_blocks = 1;
+  if (kind == GEMM_I8 && !p.pair && env_int("NCNN_B200_SUB_BLOCKS", 1) != 0)
+    for (int sub : {4, 3, 2})
+      if (p.k_blocks % sub == 0 && budget / (sub * p.stage_bytes) >= 3) {
+        p.sub_blocks = sub;
+        break;
+      }
+  p.stages = std::max(2, std::min(kTcMaxStages, budget / (p.sub_blocks * p.stage_bytes)));
+  L->smem_bytes = p.stages * p.sub_blocks * p.stage_bytes + staging + 1024;
   // never fewer bytes than half an SM's shared memory: two CTAs must not share an
   // SM, each allocates tensor memory for itself
   L->smem_bytes = std::max(L->smem_bytes, 120 * 1024);
@@ -505,6 +515,7 @@ bool finish_plan_workers(TcLaunch* L, int kind, long long M, int N, const TcEpil
   }
   p.pair = 0;
   p.pair_rows = 0;
+  p.sub_blocks = 1;
   p.staging_bytes = staging / p.epi_groups;
   L->smem_bytes = std::max(p.stages * p.stage_bytes + staging + 1024, 120 * 1024);
   L->kind = kind;

@@ -110,6 +110,7 @@ struct TcGemmParams {
   // whole waves of pairs, then a last wave that is not coarser than it has to be.
   int pair;
   int pair_rows;
+  int sub_blocks;  // int8: K blocks per ring stage (one barrier hand-shake for several small copies); 1 elsewhere
   long long* trace;    // optional (bring-up): per-role clock stamps of CTA 0, 8 values per tile
   // CTA pairs (tc_gemm2.cuh): tiles are 256 rows, tiles_m counts those.
   // streamk = 1: every pair gets an equal share of all (tile, K block) units, so a tile may be split
@@ -778,6 +779,10 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
   const uint32_t b_slot = (stage_bytes / PLANES) - static_cast<uint32_t>(AS) * slot;  // B tile, rounded to 1 KB
   const uint32_t tx_bytes = PLANES * (slot + static_cast<uint32_t>(p.block_n) * p.row_bytes);
   const int S = p.stages;
+  // int8 K blocks are small (two MMAs over 12 KB for 64 channels): a stage holds SUB of them, so that the
+  // ~450 cycles of arming and releasing a stage are paid once per SUB blocks
+  const int SUB = KIND == GEMM_I8 ? (p.sub_blocks > 1 ? p.sub_blocks : 1) : 1;
+  const int k_groups = p.k_blocks / SUB;
   const int total_tiles = p.tiles_m * p.tiles_n;
   volatile int* abort_ptr = &abort_flag;
 
@@ -861,40 +866,43 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
       }
       if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.trace[(tile / gridDim.x) * 16 + 0] = clock64();
       int cb = 0, kh = 0, kw = 0;
-      for (int kb = 0; kb < p.k_blocks; ++kb) {
+      for (int kg = 0; kg < k_groups; ++kg) {
         const uint32_t fb = smem_u32(&full_bar[s]);
         int w = 1;
         if (lane == 0) {
           w = mbar_wait_bounded(smem_u32(&empty_bar[s]), ph ^ 1u, abort_ptr, wait_limit) ? 1 : 0;
-          if (w && !(test_stall && kb == 0 && tile == static_cast<int>(blockIdx.x))) mbar_arrive_expect_tx(fb, my_tx);
+          if (w && !(test_stall && kg == 0 && tile == static_cast<int>(blockIdx.x))) mbar_arrive_expect_tx(fb, my_tx * static_cast<uint32_t>(SUB));
         }
         w = __shfl_sync(0xffffffffu, w, 0);
         if (!w) {
           ok = false;
           break;
         }
-        const bool tr = p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0 && tile == static_cast<int>(gridDim.x) && kb < 32;
-        if (tr) p.trace[1024 + kb * 4 + 0] = clock64();
-        if (issues && !(test_stall && kb == 0 && tile == static_cast<int>(blockIdx.x))) {
-          const uint32_t dst = smem_base + s * stage_bytes + my_off;
-          if (is_b) {
-            tma_load_2d(dst, my_map, fb, kb * p.k_elems, n0);
-          } else if (p.a_im2col) {
-            tma_load_im2col_4d(dst, my_map, fb, cb * p.k_elems, w_base, h_base, img,
-                               static_cast<uint16_t>(kw * p.dil_w), static_cast<uint16_t>(kh * p.dil_h));
-          } else {
-            tma_load_2d(dst, my_map, fb, kb * p.k_elems, static_cast<int>(m0));
+        const bool tr = p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0 && tile == static_cast<int>(gridDim.x) && kg < 32;
+        if (tr) p.trace[1024 + kg * 4 + 0] = clock64();
+        for (int sb = 0; sb < SUB; ++sb) {
+          const int kb = kg * SUB + sb;
+          if (issues && !(test_stall && kg == 0 && tile == static_cast<int>(blockIdx.x))) {
+            const uint32_t dst = smem_base + static_cast<uint32_t>(s * SUB + sb) * stage_bytes + my_off;
+            if (is_b) {
+              tma_load_2d(dst, my_map, fb, kb * p.k_elems, n0);
+            } else if (p.a_im2col) {
+              tma_load_im2col_4d(dst, my_map, fb, cb * p.k_elems, w_base, h_base, img,
+                                 static_cast<uint16_t>(kw * p.dil_w), static_cast<uint16_t>(kh * p.dil_h));
+            } else {
+              tma_load_2d(dst, my_map, fb, kb * p.k_elems, static_cast<int>(m0));
+            }
+          }
+          if (++cb == p.c_blocks) {
+            cb = 0;
+            if (++kw == p.KW) {
+              kw = 0;
+              ++kh;
+            }
           }
         }
-        if (tr) p.trace[1024 + kb * 4 + 1] = clock64();
+        if (tr) p.trace[1024 + kg * 4 + 1] = clock64();
         ++issued;
-        if (++cb == p.c_blocks) {
-          cb = 0;
-          if (++kw == p.KW) {
-            kw = 0;
-            ++kh;
-          }
-        }
         if (++s == S) {
           s = 0;
           ph ^= 1u;
@@ -957,7 +965,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
         const uint32_t d_tmem1 = d_tmem + 128u;
         const bool pair = tile / tiles_n < pair_rows;
         uint32_t accumulate = 0u;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = 0; kb < k_groups; ++kb) {
           if (!mbar_wait_bounded(smem_u32(&full_bar[s]), ph, abort_ptr, wait_limit)) {
             ok = false;
             break;
@@ -965,7 +973,8 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
           tc_fence_after_sync();
           const bool tr = tracing && tile == static_cast<int>(gridDim.x) && kb < 32;
           if (tr) p.trace[1024 + kb * 4 + 2] = clock64();
-          const uint64_t a0 = a_first + static_cast<uint64_t>(s) * stage_units;
+          for (int sb = 0; sb < SUB; ++sb) {
+          const uint64_t a0 = a_first + static_cast<uint64_t>(s * SUB + sb) * stage_units;
           const uint64_t b0 = a0 + b_from_a;
           if (!pair) {
 #pragma unroll 4
@@ -1017,6 +1026,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
               }
               accumulate = 1u;
             }
+          }
           }
           tc_commit(smem_u32(&empty_bar[s]));
           if (tr) p.trace[1024 + kb * 4 + 3] = clock64();
@@ -1098,7 +1108,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
       if (p.tma_store) {
         // staging area behind the ring, one per group: residual tiles (16 KB), then the output tiles
         TcStageCfg cfg{};
-        cfg.res_stage = smem_base + static_cast<uint32_t>(S) * stage_bytes + static_cast<uint32_t>(group) * p.staging_bytes;
+        cfg.res_stage = smem_base + static_cast<uint32_t>(S * SUB) * stage_bytes + static_cast<uint32_t>(group) * p.staging_bytes;
         cfg.out_stage = cfg.res_stage + (e_res_mode != RES_NONE ? 16384u : 0u);
         cfg.res_bar = smem_u32(&res_bar[group]);
         cfg.out_bufs = e_out_bufs;
