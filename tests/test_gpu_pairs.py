@@ -497,3 +497,34 @@ def test_mobilenet_v2_repeats_bit_for_bit(pkg, tmp_path):
         for i in range(150):
             assert np.array_equal(m.run(x)[0], first), (n, i)
     m.close()
+
+
+def test_resnet18_repeats_bit_for_bit(pkg, tmp_path):
+    """The stem + pooling kernel (two MMA-issuing warps on alternate rows, four row stages, four accumulators) and the
+    int8 contractions with several K blocks per ring stage: 100 passes of each network through the host-pointer entry
+    give the bits of the first pass."""
+    for int8 in (False, True):
+        param, bin_ = pkg.zoo.resnet18(str(tmp_path / ("r8" if int8 else "r")), int8=int8)
+        m = pkg.Model(param, bin_)
+        x = np.random.default_rng(5).uniform(-1, 1, (64, 3, 224, 224)).astype(np.float32)
+        first = m.run(x)[0].copy()
+        for i in range(100):
+            assert np.array_equal(m.run(x)[0], first), (int8, i)
+        m.close()
+
+
+@pytest.mark.parametrize("size,n", [(224, 4), (64, 9)])
+def test_int8_k_blocks_per_stage_change_no_bit(pkg, oracle, tmp_path, monkeypatch, size, n):
+    """Int8 contractions that are not paired keep 2 to 4 K blocks in one ring stage (one barrier hand-shake for
+    several small copies); the MMAs and their order are the same, so is every bit, and both equal the oracle."""
+    param, bin_ = pkg.zoo.resnet18(str(tmp_path / "r8"), int8=True, size=size, classes=40)
+    x = np.random.default_rng(size).uniform(-1, 1, (n, 3, size, size)).astype(np.float32)
+    m = pkg.Model(param, bin_)
+    got = m.run(x)[0]
+    m.close()
+    monkeypatch.setenv("NCNN_B200_SUB_BLOCKS", "0")
+    m = pkg.Model(param, bin_)
+    assert np.array_equal(m.run(x)[0], got)
+    m.close()
+    want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x[:2]])
+    assert np.array_equal(got[:2], want)
