@@ -832,11 +832,16 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
     // barrier counts two arrivals).  Within a warp lane p issues plane p.
     const bool is_b = warp == 6;
     // (paired tiles: lanes PLANES..2*PLANES-1 of the A warp issue the second half's planes)
-    const bool issuer = lane < (is_b ? PLANES : PLANES * AS);
-    const int my_plane = lane % PLANES;
-    const int my_half = is_b ? 0 : lane / PLANES;
+    // (int8 with several K blocks per stage, never paired: lane b issues the copy of the stage's K block b, so
+    // the copies of a stage cost the warp one instruction's time, not one each)
+    const bool by_block = KIND == GEMM_I8 && SUB > 1;
+    const bool issuer = by_block ? lane < SUB : lane < (is_b ? PLANES : PLANES * AS);
+    const int my_sb = by_block ? lane : 0;
+    const int my_plane = by_block ? 0 : lane % PLANES;
+    const int my_half = is_b || by_block ? 0 : lane / PLANES;
     const CUtensorMap* my_map = is_b ? (my_plane ? &map_b1 : &map_b0) : (my_plane ? &map_a1 : &map_a0);
-    const uint32_t my_off = is_b ? static_cast<uint32_t>(PLANES * AS) * slot + lane * b_slot : lane * slot;
+    const uint32_t my_lane_slot = by_block ? 0u : static_cast<uint32_t>(lane);
+    const uint32_t my_off = is_b ? static_cast<uint32_t>(PLANES * AS) * slot + my_lane_slot * b_slot : my_lane_slot * slot;
     const uint32_t b_tx = PLANES * static_cast<uint32_t>(p.block_n) * p.row_bytes;
     int s = 0;
     uint32_t ph = 0;
@@ -865,7 +870,17 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
         w_base = ow * p.stride_w - p.pad_l;
       }
       if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.trace[(tile / gridDim.x) * 16 + 0] = clock64();
+      // this lane's K block: channel block, filter row and column (lanes that issue by block start at theirs)
       int cb = 0, kh = 0, kw = 0;
+      auto next_k_block = [&]() {
+        if (++cb == p.c_blocks) {
+          cb = 0;
+          if (++kw == p.KW) {
+            kw = 0;
+            ++kh;
+          }
+        }
+      };
       for (int kg = 0; kg < k_groups; ++kg) {
         const uint32_t fb = smem_u32(&full_bar[s]);
         int w = 1;
@@ -880,10 +895,17 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
         }
         const bool tr = p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0 && tile == static_cast<int>(gridDim.x) && kg < 32;
         if (tr) p.trace[1024 + kg * 4 + 0] = clock64();
-        for (int sb = 0; sb < SUB; ++sb) {
-          const int kb = kg * SUB + sb;
+        {
+          const int kb = kg * SUB + my_sb;
+          if (by_block) {
+            // (computed, not stepped: lanes that step by different amounts would diverge and issue one by one)
+            const int tap = kb / p.c_blocks;
+            cb = kb - tap * p.c_blocks;
+            kh = tap / p.KW;
+            kw = tap - kh * p.KW;
+          }
           if (issues && !(test_stall && kg == 0 && tile == static_cast<int>(blockIdx.x))) {
-            const uint32_t dst = smem_base + static_cast<uint32_t>(s * SUB + sb) * stage_bytes + my_off;
+            const uint32_t dst = smem_base + static_cast<uint32_t>(s * SUB + my_sb) * stage_bytes + my_off;
             if (is_b) {
               tma_load_2d(dst, my_map, fb, kb * p.k_elems, n0);
             } else if (p.a_im2col) {
@@ -893,13 +915,7 @@ tc_gemm_kernel(const __grid_constant__ TcGemmParams p, const __grid_constant__ C
               tma_load_2d(dst, my_map, fb, kb * p.k_elems, static_cast<int>(m0));
             }
           }
-          if (++cb == p.c_blocks) {
-            cb = 0;
-            if (++kw == p.KW) {
-              kw = 0;
-              ++kh;
-            }
-          }
+          if (!by_block) next_k_block();
         }
         if (tr) p.trace[1024 + kg * 4 + 1] = clock64();
         ++issued;
