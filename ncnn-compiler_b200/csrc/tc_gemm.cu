@@ -1402,6 +1402,9 @@ std::string tc_plan_stem(TcStemLaunch* L, const TcStemConv& c, const TcEpilogue&
   if (p.tiles < 2 * sm_count) p.epi_groups = 1;
   p.staging_bytes = p.out_bufs * out_tile;
   p.stages = std::min(kStemMaxStages, (budget - weights - p.epi_groups * p.staging_bytes) / stage);
+  // four accumulators of 64 columns where they fit, and then a second MMA-issuing warp for alternate tiles
+  p.accs = N <= 64 ? 4 : 2;
+  p.issuers = p.accs == 4 && env_int("NCNN_B200_STEM_ISSUERS", 2) >= 2 ? 2 : 1;
   L->smem_bytes = weights + p.stages * stage + p.epi_groups * p.staging_bytes + 1024;
   L->smem_bytes = std::max(L->smem_bytes, 120 * 1024);  // one CTA per SM: each allocates tensor memory
   L->grid = std::min(p.tiles, sm_count);

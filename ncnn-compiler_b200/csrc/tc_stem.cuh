@@ -33,6 +33,8 @@ struct TcStemParams {
   int a_plane_bytes;  // KH rows plus what the last window rows overrun, rounded to 1 KB
   int b_slot;         // one weight tile of one plane: N rows x 64 bytes, rounded to 1 KB
   int stages;         // A ring depth
+  int accs;           // accumulators in TMEM: 4 of 64 columns (N <= 64) or 2 of 128
+  int issuers;        // MMA-issuing warps: 2 (warps 1 and 6 take alternate tiles) with four accumulators, else 1
   const float* bias;
   const float* scale;  // int8: dequantisation factor per output channel
   float out_scale;     // int8 results: requantisation scale
@@ -65,8 +67,8 @@ tc_stem_kernel(const __grid_constant__ TcStemParams p, const __grid_constant__ C
   extern __shared__ uint8_t stem_smem_raw[];
   __shared__ __align__(8) uint64_t full_bar[kStemMaxStages];
   __shared__ __align__(8) uint64_t empty_bar[kStemMaxStages];
-  __shared__ __align__(8) uint64_t tfull_bar[2];
-  __shared__ __align__(8) uint64_t tempty_bar[2];
+  __shared__ __align__(8) uint64_t tfull_bar[4];
+  __shared__ __align__(8) uint64_t tempty_bar[4];
   __shared__ __align__(8) uint64_t weights_bar;
   __shared__ __align__(8) uint64_t unused_res_bar[2];
   __shared__ __align__(16) float tile_bias_all[2][128];
@@ -83,6 +85,10 @@ tc_stem_kernel(const __grid_constant__ TcStemParams p, const __grid_constant__ C
   const uint32_t stage_bytes = static_cast<uint32_t>(PLANES) * static_cast<uint32_t>(p.a_plane_bytes);
   const uint32_t staging = a_region + static_cast<uint32_t>(S) * stage_bytes;
   volatile int* abort_ptr = &abort_flag;
+  // tile i of this CTA's sequence: stage i % S, accumulator i % accs, issuer i % issuers
+  const int accs = p.accs == 4 ? 4 : 2;
+  const uint32_t acc_cols = accs == 4 ? 64u : 128u;
+  const int issuers = p.issuers == 2 ? 2 : 1;
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -90,11 +96,11 @@ tc_stem_kernel(const __grid_constant__ TcStemParams p, const __grid_constant__ C
       mbar_init(smem_u32(&full_bar[i]), 1);
       mbar_init(smem_u32(&empty_bar[i]), 1);
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 4; ++i) {
       mbar_init(smem_u32(&tfull_bar[i]), 1);
       mbar_init(smem_u32(&tempty_bar[i]), 4);
-      mbar_init(smem_u32(&unused_res_bar[i]), 1);
     }
+    for (int i = 0; i < 2; ++i) mbar_init(smem_u32(&unused_res_bar[i]), 1);
     mbar_init(smem_u32(&weights_bar), 1);
     fence_mbar_init();
     prefetch_tensormap(&map_a0);
@@ -168,8 +174,11 @@ tc_stem_kernel(const __grid_constant__ TcStemParams p, const __grid_constant__ C
           mbar_wait_bounded(smem_u32(&full_bar[i % S]), static_cast<uint32_t>((i / S) & 1), &zero, 200000000ull);
       }
     }
-  } else if (warp == 1) {
-    // ---------------------------------------------------------- MMA issuer
+  } else if (warp == 1 || (warp == 6 && issuers == 2)) {
+    // ---------------------------------------------------------- MMA issuers
+    // One thread issues a narrow MMA every 75-150 cycles, the tensor pipe takes one every ~48: with four
+    // accumulators warps 1 and 6 issue alternate tiles (MMAs into one accumulator must come from one thread).
+    const int me = warp == 1 ? 0 : 1;
     if (lane == 0) {
       const uint32_t idesc = KIND == GEMM_I8 ? instr_desc(2u, 1u, kTcBlockM, static_cast<uint32_t>(p.N))
                                              : instr_desc(1u, 1u, kTcBlockM, static_cast<uint32_t>(p.N));
@@ -181,18 +190,17 @@ tc_stem_kernel(const __grid_constant__ TcStemParams p, const __grid_constant__ C
       const uint64_t row_units = static_cast<uint64_t>(p.row_bytes) >> 4;
       const uint64_t b_slot_units = static_cast<uint64_t>(p.b_slot) >> 4;
       const uint64_t b_first = b_fixed + ((b_region & 0x3ffffu) >> 4);
-      int s = 0;
-      uint32_t ph = 0;
-      int acc = 0;
-      uint32_t acc_ph = 0;
-      for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x) {
+      int i = me;  // position in this CTA's tile sequence
+      for (int tile = blockIdx.x + me * static_cast<int>(gridDim.x); tile < p.tiles && ok; tile += issuers * static_cast<int>(gridDim.x), i += issuers) {
+        const int s = i % S, acc = i % accs;
+        const uint32_t ph = static_cast<uint32_t>((i / S) & 1), acc_ph = static_cast<uint32_t>((i / accs) & 1);
         if (!mbar_wait_bounded(smem_u32(&tempty_bar[acc]), acc_ph ^ 1u, abort_ptr, kTcWaitLimitNs) ||
             !mbar_wait_bounded(smem_u32(&full_bar[s]), ph, abort_ptr, kTcWaitLimitNs)) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * 128u;
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * acc_cols;
         const uint64_t a_hi0 = a_fixed + (((a_region + static_cast<uint32_t>(s) * stage_bytes) & 0x3ffffu) >> 4);
         uint32_t accumulate = 0u;
         for (int kh = 0; kh < p.KH; ++kh) {
@@ -214,17 +222,12 @@ tc_stem_kernel(const __grid_constant__ TcStemParams p, const __grid_constant__ C
         }
         tc_commit(smem_u32(&empty_bar[s]));
         tc_commit(smem_u32(&tfull_bar[acc]));
-        if (++s == S) {
-          s = 0;
-          ph ^= 1u;
-        }
-        acc ^= 1;
-        if (acc == 0) acc_ph ^= 1u;
       }
       if (!ok && atomicCAS(const_cast<int*>(abort_ptr), 0, 1) == 0) atomicCAS(p.status, 0, TC_TIMEOUT_MMA);
     }
   } else if (warp != 6) {
     // ------------------------------------------------------------ epilogue (as in tc_gemm_kernel)
+    // (with two groups, group g drains the tiles at odd / even positions of the sequence)
     const int group = warp >= 7 ? 1 : 0;
     const int groups = p.epi_groups;
     if (group < groups) {
@@ -239,8 +242,8 @@ tc_stem_kernel(const __grid_constant__ TcStemParams p, const __grid_constant__ C
         if (KIND == GEMM_I8) tile_scale[t] = t < p.N ? __ldg(p.scale + t) : 0.0f;
         else if (t < 4) tile_scale[t] = 0.0f;
       }
-      int acc = groups == 2 ? group : 0;
-      uint32_t acc_ph = 0, res_ph = 0;
+      int i = groups == 2 ? group : 0;  // position in this CTA's tile sequence
+      uint32_t res_ph = 0;
       int out_slot = 0;
       bool ok = true;
       TcStageCfg cfg{};
@@ -259,13 +262,15 @@ tc_stem_kernel(const __grid_constant__ TcStemParams p, const __grid_constant__ C
       cfg.bar_base = 1 + 3 * group;
       const int tile_step = static_cast<int>(gridDim.x) * groups;
       for (int tile = blockIdx.x + (groups == 2 ? group * static_cast<int>(gridDim.x) : 0); tile < p.tiles && ok;
-           tile += tile_step) {
+           tile += tile_step, i += groups) {
+        const int acc = i % accs;
+        const uint32_t acc_ph = static_cast<uint32_t>((i / accs) & 1);
         ok = __all_sync(0xffffffffu,
                         mbar_wait_bounded(smem_u32(&tfull_bar[acc]), acc_ph, abort_ptr, kTcWaitLimitNs) ? 1 : 0) != 0;
         if (!ok) break;
         tc_fence_after_sync();
         const uint32_t t_row =
-            tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc) * 128u;
+            tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(acc) * acc_cols;
         // the stores take OW rows of the staging tile (their box is OW rows high); rows beyond hold
         // whatever followed the input row in shared memory and go nowhere
         struct {
@@ -288,12 +293,6 @@ tc_stem_kernel(const __grid_constant__ TcStemParams p, const __grid_constant__ C
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
-        if (groups == 2) {
-          acc_ph ^= 1u;
-        } else {
-          acc ^= 1;
-          if (acc == 0) acc_ph ^= 1u;
-        }
       }
       if (!ok && lane == 0 && atomicCAS(const_cast<int*>(abort_ptr), 0, 1) == 0)
         atomicCAS(p.status, 0, TC_TIMEOUT_EPILOGUE);
