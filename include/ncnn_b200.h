@@ -80,6 +80,10 @@ int ncnn_b200_input_count(const ncnn_b200_model *model);
 int ncnn_b200_output_count(const ncnn_b200_model *model);
 int ncnn_b200_input_shape(const ncnn_b200_model *model, int index, int64_t dims[3]);
 int ncnn_b200_output_shape(const ncnn_b200_model *model, int index, int64_t dims[3]);
+/* The same for tensors of rank up to 4 ([c,d,h,w]: the reference's rank-4 Reshape / Permute / Slice / Concat results,
+ * lib/Importer/ImportOps.cpp:166-300, ImportTensor.cpp:343-400); the three-extent forms answer -1 for rank 4. */
+int ncnn_b200_input_shape4(const ncnn_b200_model *model, int index, int64_t dims[4]);
+int ncnn_b200_output_shape4(const ncnn_b200_model *model, int index, int64_t dims[4]);
 const char *ncnn_b200_input_name(const ncnn_b200_model *model, int index);
 const char *ncnn_b200_output_name(const ncnn_b200_model *model, int index);
 

@@ -33,8 +33,10 @@ int copy_out(const std::string& text, char* buffer, size_t capacity) {
   return static_cast<int>(text.size());
 }
 
-int shape_out(const nb::TensorShape& s, int64_t dims[3]) {
-  for (int i = 0; i < 3; ++i) dims[i] = i < s.rank ? s.dims[i] : 0;
+// (a rank-4 tensor does not fit the three-extent accessors: they answer -1 for it)
+int shape_out(const nb::TensorShape& s, int64_t* dims, int capacity) {
+  if (s.rank > capacity) return -1;
+  for (int i = 0; i < capacity; ++i) dims[i] = i < s.rank ? s.dims[i] : 0;
   return s.rank;
 }
 
@@ -133,12 +135,22 @@ int ncnn_b200_output_count(const ncnn_b200_model* m) { return m ? m->engine->out
 
 int ncnn_b200_input_shape(const ncnn_b200_model* m, int i, int64_t dims[3]) {
   if (m == nullptr || dims == nullptr || i < 0 || i >= m->engine->input_count()) return -1;
-  return shape_out(m->engine->input_shape(i), dims);
+  return shape_out(m->engine->input_shape(i), dims, 3);
 }
 
 int ncnn_b200_output_shape(const ncnn_b200_model* m, int i, int64_t dims[3]) {
   if (m == nullptr || dims == nullptr || i < 0 || i >= m->engine->output_count()) return -1;
-  return shape_out(m->engine->output_shape(i), dims);
+  return shape_out(m->engine->output_shape(i), dims, 3);
+}
+
+int ncnn_b200_input_shape4(const ncnn_b200_model* m, int i, int64_t dims[4]) {
+  if (m == nullptr || dims == nullptr || i < 0 || i >= m->engine->input_count()) return -1;
+  return shape_out(m->engine->input_shape(i), dims, 4);
+}
+
+int ncnn_b200_output_shape4(const ncnn_b200_model* m, int i, int64_t dims[4]) {
+  if (m == nullptr || dims == nullptr || i < 0 || i >= m->engine->output_count()) return -1;
+  return shape_out(m->engine->output_shape(i), dims, 4);
 }
 
 const char* ncnn_b200_input_name(const ncnn_b200_model* m, int i) {

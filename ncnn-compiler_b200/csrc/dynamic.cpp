@@ -260,6 +260,7 @@ int ncnn_b200_dynamic_load(const char* param_path, const char* bin_path, const n
   for (int o = 0; o < n_out; ++o) {
     DynOutput& out_shape = model->outputs[o];
     out_shape.rank = ncnn_b200_output_shape(base_plan, o, out_shape.dims);
+    if (out_shape.rank < 0) return fail_load("rank-4 outputs are outside the dynamic-shape path");
   }
   size_t slot = 0;
   for (const DynInput& in : model->inputs) {

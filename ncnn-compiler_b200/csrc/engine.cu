@@ -478,7 +478,12 @@ int Engine::output_count() const { return static_cast<int>(impl_->outputs_.size(
 static TensorShape shape_of(const Tensor& t) {
   TensorShape s;
   s.rank = t.rank;
-  if (t.rank == 3) {
+  if (t.rank == 4) {
+    s.dims[0] = t.c;
+    s.dims[1] = t.d;
+    s.dims[2] = t.h;
+    s.dims[3] = t.w;
+  } else if (t.rank == 3) {
     s.dims[0] = t.c;
     s.dims[1] = t.h;
     s.dims[2] = t.w;

@@ -45,7 +45,7 @@ struct EngineOptions {
 
 struct TensorShape {
   int rank = 0;
-  int64_t dims[3] = {0, 0, 0};  // logical dims, outermost first ([c,h,w] for rank 3)
+  int64_t dims[4] = {0, 0, 0, 0};  // logical dims, outermost first ([c,h,w] for rank 3, [c,d,h,w] for rank 4)
   int64_t elements() const {
     int64_t n = 1;
     for (int i = 0; i < rank; ++i) n *= dims[i];

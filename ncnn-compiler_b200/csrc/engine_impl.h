@@ -27,6 +27,7 @@ struct Tensor {
   std::string name;
   int rank = 0;
   int c = 1, h = 1, w = 1;  // logical dims (rank 1: w; rank 2: h x w; rank 3: c x h x w)
+  int d = 1;                // rank 4: c x d x h x w, stored in that order (only data-movement layers take rank 4)
   bool i8 = false;
   int alias = -1;  // Split: shares the storage of another tensor
   bool is_input = false;
@@ -41,7 +42,7 @@ struct Tensor {
   int first_def = -1, last_use = -1;
   bool dedicated = false;          // never shares arena space (padding must stay zero)
 
-  long long logical() const { return static_cast<long long>(c) * h * w; }
+  long long logical() const { return static_cast<long long>(c) * d * h * w; }
   int planes() const { return fmt == FMT_SPLIT || fmt == FMT_BF16X2 ? 2 : 1; }
   int elem_bytes() const { return fmt == FMT_I8 ? 1 : (fmt == FMT_BF16X2 ? 2 : 4); }
 };

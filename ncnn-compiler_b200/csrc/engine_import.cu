@@ -358,6 +358,15 @@ bool EngineImpl::import_layers(std::string* err) {
     // every importer below reads bottoms[0] and tops[0]: a line without them is malformed, not a crash
     if (t != "Input" && (l.bottoms.empty() || l.tops.empty()))
       return fail(err, where + "layer needs at least one bottom and one top blob");
+    // rank-4 tensors [c,d,h,w] exist between data-movement layers only (Reshape, Permute order 3, Slice, Concat,
+    // Flatten, Split and the elementwise activations): a detection head reshapes into them and back
+    static const char* const rank4_layers[] = {"Reshape", "Flatten", "Permute", "Slice", "Concat", "Split", "Sigmoid", "ReLU",
+                                               "Clip", "TanH", "Swish", "HardSigmoid", "HardSwish", "Dropout"};
+    for (const auto& b : l.bottoms)
+      if (tensors_[resolve(by_name_.at(b))].rank == 4 &&
+          std::find_if(std::begin(rank4_layers), std::end(rank4_layers), [&](const char* name) { return t == name; }) ==
+              std::end(rank4_layers))
+        return fail(err, where + "rank-4 input is outside the supported path");
     if (t == "Input") {
       // ImportInput.cpp:22-80: w/h/c all given (rank 3) or all omitted plus an override
       const int64_t w = l.params.get_int(0, 0), h = l.params.get_int(1, 0), c = l.params.get_int(2, 0);
@@ -561,7 +570,8 @@ bool EngineImpl::import_layers(std::string* err) {
       n.type = t;
       auto dims_of = [](const Tensor& x) {
         std::vector<int> d;
-        if (x.rank == 3) d = {x.c, x.h, x.w};
+        if (x.rank == 4) d = {x.c, x.d, x.h, x.w};
+        else if (x.rank == 3) d = {x.c, x.h, x.w};
         else if (x.rank == 2) d = {x.h, x.w};
         else d = {x.w};
         return d;
@@ -585,7 +595,8 @@ bool EngineImpl::import_layers(std::string* err) {
       to.name = keep;
       to.alias = -1;
       to.is_input = false;
-      if (t0.rank == 3) { to.c = od[0]; to.h = od[1]; to.w = od[2]; }
+      if (t0.rank == 4) { to.c = od[0]; to.d = od[1]; to.h = od[2]; to.w = od[3]; }
+      else if (t0.rank == 3) { to.c = od[0]; to.h = od[1]; to.w = od[2]; }
       else if (t0.rank == 2) { to.h = od[0]; to.w = od[1]; }
       else to.w = od[0];
       // storage order: rank 3 [h][w][c] -> concatenation axis as (outer, len, inner)
@@ -595,7 +606,16 @@ bool EngineImpl::import_layers(std::string* err) {
         ConcatParams cp{};
         cp.in_image_elems = tb.logical();
         cp.out_image_elems = to.logical();
-        if (t0.rank == 3) {
+        if (t0.rank == 4) {
+          // stored in logical order: what lies before the axis is the outer extent, what lies behind it the inner
+          const std::vector<int> d = dims_of(tb);
+          cp.outer = 1;
+          cp.inner = 1;
+          for (int k = 0; k < axis; ++k) cp.outer *= d[k];
+          for (int k = static_cast<int>(axis) + 1; k < 4; ++k) cp.inner *= d[k];
+          cp.len_in = d[axis];
+          cp.len_out = od[axis];
+        } else if (t0.rank == 3) {
           if (axis == 0) { cp.outer = tb.h * tb.w; cp.len_in = tb.c; cp.len_out = to.c; cp.inner = 1; }
           else if (axis == 1) { cp.outer = 1; cp.len_in = tb.h; cp.len_out = to.h; cp.inner = tb.w * tb.c; }
           else { cp.outer = tb.h; cp.len_in = tb.w; cp.len_out = to.w; cp.inner = tb.c; }
@@ -733,7 +753,8 @@ bool EngineImpl::import_layers(std::string* err) {
       if (axis < 0) axis += ti.rank;
       if (axis < 0 || axis >= ti.rank) return fail(err, where + "Slice axis is outside input rank");
       std::vector<int> dims;
-      if (ti.rank == 3) dims = {ti.c, ti.h, ti.w};
+      if (ti.rank == 4) dims = {ti.c, ti.d, ti.h, ti.w};
+      else if (ti.rank == 3) dims = {ti.c, ti.h, ti.w};
       else if (ti.rank == 2) dims = {ti.h, ti.w};
       else dims = {ti.w};
       const int extent = dims[axis];
@@ -756,14 +777,22 @@ bool EngineImpl::import_layers(std::string* err) {
         to.is_input = false;
         std::vector<int> od = dims;
         od[axis] = static_cast<int>(size);
-        if (ti.rank == 3) { to.c = od[0]; to.h = od[1]; to.w = od[2]; to.Cp = to.c; to.Wp = to.w; }
+        if (ti.rank == 4) { to.c = od[0]; to.d = od[1]; to.h = od[2]; to.w = od[3]; to.Wp = to.w; }
+        else if (ti.rank == 3) { to.c = od[0]; to.h = od[1]; to.w = od[2]; to.Cp = to.c; to.Wp = to.w; }
         else if (ti.rank == 2) { to.h = od[0]; to.w = od[1]; to.Wp = to.w; }
         else { to.w = od[0]; to.Wp = to.w; }
         ConcatParams cp{};
         cp.slice = 1;
         cp.in_image_elems = to.logical();
         cp.out_image_elems = ti.logical();
-        if (ti.rank == 3) {
+        if (ti.rank == 4) {
+          cp.outer = 1;
+          cp.inner = 1;
+          for (int k = 0; k < axis; ++k) cp.outer *= dims[k];
+          for (int k = static_cast<int>(axis) + 1; k < 4; ++k) cp.inner *= dims[k];
+          cp.len_in = od[axis];
+          cp.len_out = dims[axis];
+        } else if (ti.rank == 3) {
           if (axis == 0) { cp.outer = ti.h * ti.w; cp.len_in = to.c; cp.len_out = ti.c; cp.inner = 1; }
           else if (axis == 1) { cp.outer = 1; cp.len_in = to.h; cp.len_out = ti.h; cp.inner = ti.w * ti.c; }
           else { cp.outer = ti.h; cp.len_in = to.w; cp.len_out = ti.w; cp.inner = ti.c; }
@@ -987,28 +1016,51 @@ bool EngineImpl::import_layers(std::string* err) {
         to.rank = 1;
         to.w = static_cast<int>(ti.logical());
       } else if (t == "Reshape") {
-        // ncnn Reshape: 0=w 1=h 2=c, -233 marks an unused dimension, 0 copies, -1 infers
-        int64_t d[3] = {l.params.get_int(0, -233), l.params.get_int(1, -233), l.params.get_int(2, -233)};
-        const int src[3] = {ti.w, ti.rank >= 2 ? ti.h : 1, ti.rank == 3 ? ti.c : 1};
-        int rank = d[2] != -233 ? 3 : (d[1] != -233 ? 2 : 1);
-        long long known = 1;
+        // import_reshape (ImportOps.cpp:166-300): 0=w 1=h 11=d 2=c; the result's dims are the given ones in the
+        // order [c,d,h,w] (-233 marks an absent one), 0 copies an input extent (w: last, h: last but one, d:
+        // second of a rank-4 input, c: first of a rank >= 3 input), a single -1 is inferred
+        const int64_t raw[4] = {l.params.get_int(2, -233), l.params.get_int(11, -233), l.params.get_int(1, -233),
+                                l.params.get_int(0, -233)};
+        std::vector<int64_t> dims;
         int infer = -1;
-        for (int i = 0; i < rank; ++i) {
-          if (d[i] == 0) d[i] = src[i];
-          if (d[i] == -1) {
-            infer = i;
-          } else {
-            known *= d[i];
+        for (int i = 0; i < 4; ++i) {
+          int64_t v = raw[i];
+          if (v == -233) continue;
+          if (v == 0) {
+            if (i == 3) v = ti.w;
+            else if (i == 2) {
+              if (ti.rank < 2) return fail(err, where + "reshape cannot copy missing height dimension");
+              v = ti.h;
+            } else if (i == 1) {
+              if (ti.rank != 4) return fail(err, where + "reshape cannot copy missing depth dimension");
+              v = ti.d;
+            } else {
+              if (ti.rank < 3) return fail(err, where + "reshape cannot copy missing channel dimension");
+              v = ti.c;
+            }
           }
+          if (v == -1) {
+            if (infer >= 0) return fail(err, where + "reshape allows at most one -1 dimension");
+            infer = static_cast<int>(dims.size());
+          } else if (v <= 0) {
+            return fail(err, where + "reshape dimensions must be positive, 0, -1 or -233");
+          }
+          dims.push_back(v);
         }
-        if (infer >= 0) d[infer] = ti.logical() / std::max<long long>(known, 1);
+        if (dims.empty()) return fail(err, where + "reshape needs at least one dimension");
+        long long known = 1;
+        for (size_t i = 0; i < dims.size(); ++i)
+          if (static_cast<int>(i) != infer) known *= dims[i];
+        if (infer >= 0) dims[infer] = ti.logical() / std::max<long long>(known, 1);
         long long total = 1;
-        for (int i = 0; i < rank; ++i) total *= d[i];
+        for (int64_t v : dims) total *= v;
         if (total != ti.logical()) return fail(err, where + "Reshape does not preserve the element count");
+        const int rank = static_cast<int>(dims.size());
         to.rank = rank;
-        to.w = static_cast<int>(d[0]);
-        to.h = rank >= 2 ? static_cast<int>(d[1]) : 1;
-        to.c = rank == 3 ? static_cast<int>(d[2]) : 1;
+        to.w = static_cast<int>(dims[rank - 1]);
+        to.h = rank >= 2 ? static_cast<int>(dims[rank - 2]) : 1;
+        to.d = rank == 4 ? static_cast<int>(dims[1]) : 1;
+        to.c = rank >= 3 ? static_cast<int>(dims[0]) : 1;
       } else if (t == "Squeeze" || t == "ExpandDims") {
         // explicit axes over the logical [c,h,w] order only (import_squeeze / import_expand_dims,
         // ImportTensor.cpp:270-341; computeSqueezeResult / computeExpandDimsResult, NCNNOps.cpp:868-927)
@@ -1072,8 +1124,19 @@ bool EngineImpl::import_layers(std::string* err) {
           to.w = src[perm[2]];
           for (int i = 0; i < 3; ++i) n.relayout.perm[i] = perm[i];
           n.relayout.permute3d = 1;
+        } else if (ti.rank == 4 && order == 3) {
+          // ncnn order_type 3 of a rank-4 tensor: result [c,h,w,d] (permutation {0,2,3,1} of [c,d,h,w])
+          to.rank = 4;
+          to.c = ti.c;
+          to.d = ti.h;
+          to.h = ti.w;
+          to.w = ti.d;
+          n.relayout.permute4d = 1;
+          n.relayout.s4d = ti.d;
+          n.relayout.s4h = ti.h;
+          n.relayout.s4w = ti.w;
         } else {
-          return fail(err, where + "Permute supports rank-2 order 0/1 and rank-3 order 2/4 only");
+          return fail(err, where + "Permute supports rank-2 order 0/1, rank-3 order 2/4, and rank-4 order 3 only");
         }
       }
       RelayoutParams& r = n.relayout;

@@ -917,6 +917,10 @@ struct RelayoutParams {
   int transpose2d;            // source is read as its rank-2 transpose
   int permute3d;              // rank 3 to rank 3: destination extent i is source extent perm[i]
   int perm[3];
+  // rank 4 [c][d][h][w] -> [c][h][w][d] (ncnn order_type 3, import_permute, ImportTensor.cpp:374-383): both sides
+  // are stored in their logical order; s4 are the source extents d, h, w
+  int permute4d;
+  int s4d, s4h, s4w;
 };
 
 __device__ __forceinline__ long long storage_offset(int rank, int c_dim, int h_dim, int w_dim,
@@ -950,6 +954,15 @@ static __global__ void k_relayout(ActRef in, ActRef out, RelayoutParams p) {
 #pragma unroll
       for (int k = 0; k < 3; ++k) sidx[p.perm[k]] = d[k];
       src_l = (static_cast<long long>(sidx[0]) * p.sh + sidx[1]) * p.sw + sidx[2];
+    } else if (p.permute4d) {
+      // destination index (c, h, w, d) reads source (c, d, h, w)
+      const int dd = static_cast<int>(l % p.s4d);
+      long long r = l / p.s4d;
+      const int ww = static_cast<int>(r % p.s4w);
+      r /= p.s4w;
+      const int hh = static_cast<int>(r % p.s4h);
+      const long long cc = r / p.s4h;
+      src_l = ((cc * p.s4d + dd) * p.s4h + hh) * p.s4w + ww;
     }
     const long long so = img * p.count + storage_offset(p.src_rank, p.sc, p.sh, p.sw, src_l);
     const long long dof = img * p.count + storage_offset(p.dst_rank, p.dc, p.dh, p.dw, l);

@@ -52,7 +52,7 @@ def load_library():
     L.ncnn_b200_last_error.restype = c_char_p
     for f in ("ncnn_b200_input_count", "ncnn_b200_output_count", "ncnn_b200_check_status"):
         getattr(L, f).argtypes = [c_void_p]
-    for f in ("ncnn_b200_input_shape", "ncnn_b200_output_shape"):
+    for f in ("ncnn_b200_input_shape", "ncnn_b200_output_shape", "ncnn_b200_input_shape4", "ncnn_b200_output_shape4"):
         getattr(L, f).argtypes = [c_void_p, c_int, POINTER(c_int64)]
     for f in ("ncnn_b200_input_name", "ncnn_b200_output_name"):
         getattr(L, f).argtypes = [c_void_p, c_int]
@@ -134,16 +134,16 @@ class Model:
                                     byref(self._h))
         if st != 0:
             raise NcnnB200Error(st, self._L.ncnn_b200_last_error(None).decode())
-        self.input_shapes = [self._shape(self._L.ncnn_b200_input_shape, i)
+        self.input_shapes = [self._shape(self._L.ncnn_b200_input_shape4, i, 4)
                              for i in range(self._L.ncnn_b200_input_count(self._h))]
-        self.output_shapes = [self._shape(self._L.ncnn_b200_output_shape, i)
+        self.output_shapes = [self._shape(self._L.ncnn_b200_output_shape4, i, 4)
                               for i in range(self._L.ncnn_b200_output_count(self._h))]
         self.input_names = [self._L.ncnn_b200_input_name(self._h, i).decode() for i in range(len(self.input_shapes))]
         self.output_names = [self._L.ncnn_b200_output_name(self._h, i).decode()
                              for i in range(len(self.output_shapes))]
 
-    def _shape(self, fn, i):
-        dims = (c_int64 * 3)()
+    def _shape(self, fn, i, capacity=3):
+        dims = (c_int64 * capacity)()
         rank = fn(self._h, i, dims)
         return tuple(int(dims[k]) for k in range(rank))
 

@@ -287,6 +287,24 @@ def inverted_residual(prefix, h, w, cin, hidden, cout, stride=1, seed=310, expan
     return wr.save(prefix)
 
 
+def detection_head(prefix, seed=900, h=8, w=8, cin=32, anchors=3, values=7):
+    """A YOLOv5-style head: 1x1 convolution to anchors * values channels, Reshape to the rank-4 tensor
+    [anchors, values, h, w], Permute (order 3) to [anchors, h, w, values], Sigmoid, Slice of the value axis into
+    (box, rest), Reshape of both to matrices [anchors * h * w, n] and Concat back along the width."""
+    net = _Net(seed)
+    wr = net.w
+    wr.layer("Input", "input", [], ["data"], f"0={w} 1={h} 2={cin}")
+    net.conv("head", "data", "raw", cin, anchors * values, 1, 1, 0, act=0, zero_bias=False)
+    wr.layer("Reshape", "to_rank4", ["raw"], ["grid"], f"0={w} 1={h} 11={values} 2={anchors}")
+    wr.layer("Permute", "values_last", ["grid"], ["cells"], "0=3")
+    wr.layer("Sigmoid", "sigmoid", ["cells"], ["prob"], "")
+    wr.layer("Slice", "split_values", ["prob"], ["box", "rest"], f"-23300=2,4,-233 1=3")
+    wr.layer("Reshape", "box_rows", ["box"], ["box_m"], "0=4 1=-1")
+    wr.layer("Reshape", "rest_rows", ["rest"], ["rest_m"], f"0={values - 4} 1=-1")
+    wr.layer("Concat", "join", ["box_m", "rest_m"], ["output"], "0=1")
+    return wr.save(prefix)
+
+
 def inner_product(prefix, k, n, seed=500, int8=False, relu=True):
     """Config 4: Input [1,1,K] -> InnerProduct(K -> N, bias, fused ReLU); run with batch M."""
     net = _Net(seed + (7 if int8 else 0), int8=int8)

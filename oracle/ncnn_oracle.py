@@ -715,8 +715,9 @@ def op_dropout(layer: Layer, x):
 
 
 def _storage_axis(rank, axis):
-    """Logical ncnn axis ([c,h,w] / [h,w] / [w], negative from the end) -> axis of the
-    array as this oracle stores it (rank 3 is HWC, like the reference's NHWC; convertAxis)."""
+    """Logical ncnn axis ([c,d,h,w] / [c,h,w] / [h,w] / [w], negative from the end) -> axis of the
+    array as this oracle stores it (rank 3 is HWC, like the reference's NHWC; convertAxis; rank 4 is kept in
+    its logical order [c,d,h,w])."""
     if axis < 0:
         axis += rank
     if not 0 <= axis < rank:
@@ -1026,18 +1027,38 @@ class Model:
                 continue
             elif t == "Flatten":
                 x = ins[0]
-                out = x.transpose(2, 0, 1).reshape(-1) if x.ndim == 3 else x.reshape(-1)
+                out = x.transpose(2, 0, 1).reshape(-1) if x.ndim == 3 else np.ascontiguousarray(x).reshape(-1)
             elif t == "Reshape":
-                # ncnn Reshape over the logical [c,h,w] order: 0=w 1=h 2=c, -233 unused, 0 copies the
-                # input extent, -1 is inferred (import_reshape, ImportOps.cpp:166-300)
+                # import_reshape (ImportOps.cpp:166-300): 0=w 1=h 11=d 2=c; the result's dims are the given ones
+                # in the order [c,d,h,w] (-233 = absent), 0 copies an input extent (w: last, h: last but one,
+                # d: second of a rank-4 input, c: first of a rank >= 3 input), a single -1 is inferred
                 x = ins[0]
-                chw = np.ascontiguousarray(x.transpose(2, 0, 1)) if x.ndim == 3 else x
-                d = [l.geti(0, -233), l.geti(1, -233), l.geti(2, -233)]
-                src = [chw.shape[-1], chw.shape[-2] if chw.ndim >= 2 else 1, chw.shape[0] if chw.ndim == 3 else 1]
-                rank = 3 if d[2] != -233 else (2 if d[1] != -233 else 1)
-                dims = [src[i] if d[i] == 0 else d[i] for i in range(rank)]
-                flat = chw.reshape(dims[::-1])  # numpy infers a single -1
-                out = np.ascontiguousarray(flat.transpose(1, 2, 0)) if rank == 3 else flat
+                chw = np.ascontiguousarray(x.transpose(2, 0, 1)) if x.ndim == 3 else np.ascontiguousarray(x)
+                raw = [l.geti(2, -233), l.geti(11, -233), l.geti(1, -233), l.geti(0, -233)]
+                dims = []
+                for i, v in enumerate(raw):
+                    if v == -233:
+                        continue
+                    if v == 0:
+                        if i == 3:
+                            v = chw.shape[-1]
+                        elif i == 2:
+                            if chw.ndim < 2:
+                                raise ValueError("reshape cannot copy missing height dimension")
+                            v = chw.shape[-2]
+                        elif i == 1:
+                            if chw.ndim != 4:
+                                raise ValueError("reshape cannot copy missing depth dimension")
+                            v = chw.shape[1]
+                        else:
+                            if chw.ndim < 3:
+                                raise ValueError("reshape cannot copy missing channel dimension")
+                            v = chw.shape[0]
+                    dims.append(v)
+                if dims.count(-1) > 1:
+                    raise ValueError("reshape allows at most one -1 dimension")
+                flat = chw.reshape(dims)  # numpy infers a single -1
+                out = np.ascontiguousarray(flat.transpose(1, 2, 0)) if flat.ndim == 3 else flat
             elif t in ("Squeeze", "ExpandDims"):
                 # explicit axes over the logical [c,h,w] order (computeSqueezeResult /
                 # computeExpandDimsResult, NCNNOps.cpp:868-927); a named axis that is not 1 stays
@@ -1070,8 +1091,11 @@ class Model:
                     chw = x.transpose(2, 0, 1)
                     res = chw.transpose((1, 0, 2) if order == 2 else (2, 0, 1))
                     out = np.ascontiguousarray(res.transpose(1, 2, 0))
+                elif x.ndim == 4 and order == 3:
+                    # rank 4 keeps its logical order [c,d,h,w]; order_type 3 gives [c,h,w,d] (permutation {0,2,3,1})
+                    out = np.ascontiguousarray(x.transpose(0, 2, 3, 1))
                 else:
-                    raise ValueError("Permute supports rank-2 order 0/1 and rank-3 order 2/4 only")
+                    raise ValueError("Permute supports rank-2 order 0/1, rank-3 order 2/4, and rank-4 order 3 only")
             else:
                 raise ValueError(f"layer type {t} is outside the hot path")
             env[l.tops[0]] = out

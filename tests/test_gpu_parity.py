@@ -451,11 +451,48 @@ def test_null_pointer_and_bad_batch_status(pkg, tmp_path):
 
 
 def test_unsupported_layers_fail_loudly(pkg, tmp_path):
-    for name in ("detection_output", "permute_rank4", "concat_rank4"):
+    for name in ("detection_output",):
         param = os.path.join(FIXTURES, name + ".param")
         with pytest.raises(pkg.NcnnB200Error) as e:
             pkg.Model(param, os.path.join(FIXTURES, "relu.bin"))
         assert e.value.status == 8
+
+
+def test_reference_fixtures_rank4_exact(pkg, oracle):
+    """permute_rank4, slice_rank4, concat_rank4 (supported_ops_test.cpp:1035-1078): data movement, exact."""
+    rng = np.random.default_rng(46)
+    x = rng.standard_normal((5, 3, 2, 4)).astype(np.float32)
+    m = pkg.Model(*fixture("permute_rank4"))
+    got = m.run(x)[0]
+    m.close()
+    assert got.shape == (5, 2, 2, 2, 3)
+    assert np.array_equal(got, x.reshape(5, 2, 3, 2, 2).transpose(0, 1, 3, 4, 2))
+    assert np.array_equal(got[0], oracle.Model(*fixture("permute_rank4")).run([x[0]])[0])
+    x = rng.standard_normal((3, 4, 1, 6)).astype(np.float32)
+    m = pkg.Model(*fixture("slice_rank4"))
+    left, right = m.run(x)
+    m.close()
+    assert np.array_equal(left, x.reshape(3, 4, 1, 1, 6)[..., :2]) and np.array_equal(right, x.reshape(3, 4, 1, 1, 6)[..., 2:])
+    a, b = rng.standard_normal((4, 2, 2, 3)).astype(np.float32), rng.standard_normal((4, 1, 2, 2)).astype(np.float32)
+    m = pkg.Model(*fixture("concat_rank4"))
+    got = m.run(a, b)[0]
+    m.close()
+    assert np.array_equal(got, np.concatenate([a.reshape(4, 1, 2, 2, 3), b.reshape(4, 1, 2, 2, 1)], axis=4))
+
+
+def test_detection_head_through_rank4(pkg, oracle, tmp_path):
+    """A YOLOv5-style head: convolution, Reshape to [anchors, values, h, w], Permute order 3, Sigmoid on the rank-4
+    tensor, Slice of its last axis, Reshape to matrices and Concat: against the oracle within the sigmoid's 3e-6 (fp32
+    convolution) and 2e-5 (bf16-pair convolution in front of it)."""
+    param, bin_ = pkg.zoo.detection_head(str(tmp_path / "head"), h=20, w=20, cin=64, anchors=3, values=85)
+    x = np.random.default_rng(47).uniform(-1, 1, (4, 64, 20, 20)).astype(np.float32)
+    want = np.stack([oracle.Model(param, bin_).run([xi])[0] for xi in x])
+    for mode, tol in ((2, 3e-6), (0, 2e-5)):  # CUDA-core fp32 convolution; bf16-pair tensor-core convolution
+        m = pkg.Model(param, bin_, accuracy_mode=mode)
+        got = m.run(x)[0]
+        m.close()
+        assert got.shape == (4, 1200, 85)
+        assert np.allclose(got, want, rtol=0, atol=tol), mode
 
 
 def test_emit_stub_header_matches_reference_layout(pkg, tmp_path):

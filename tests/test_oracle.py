@@ -317,6 +317,41 @@ def test_split_three_concat_chain(oracle):
     assert np.array_equal(got, np.concatenate([x, x, x], axis=0))
 
 
+# ------------------------------------------------------------------ rank-4 tensors between data-movement layers
+def test_rank4_reshape_permute_slice_concat(oracle):
+    """The reference's three rank-4 fixtures (PermuteRankFourOrderThree, SliceRankFourWidthAxis, ConcatRankFourWidthAxis,
+    test/Numerical/operators/supported_ops_test.cpp:1035-1078): Reshape with 11=d gives [c,d,h,w]; Permute order 3
+    gives [c,h,w,d]; Slice and Concat count their axis over [c,d,h,w].  Data movement only: exact."""
+    rng = np.random.default_rng(44)
+    x = rng.standard_normal((3, 2, 4)).astype(F32)
+    got = _run_fixture(oracle, "permute_rank4", x)
+    assert got.shape == (2, 2, 2, 3) and np.array_equal(got, x.reshape(2, 3, 2, 2).transpose(0, 2, 3, 1))
+    x = rng.standard_normal((4, 1, 6)).astype(F32)
+    param, bin_ = fixture("slice_rank4")
+    left, right = oracle.Model(param, bin_).run([x], want=["left", "right"])
+    m = x.reshape(4, 1, 1, 6)
+    assert left.shape == (4, 1, 1, 2) and right.shape == (4, 1, 1, 4)
+    assert np.array_equal(left, m[..., :2]) and np.array_equal(right, m[..., 2:])
+    a, b = rng.standard_normal((2, 2, 3)).astype(F32), rng.standard_normal((1, 2, 2)).astype(F32)
+    got = _run_fixture(oracle, "concat_rank4", a, b)
+    assert got.shape == (1, 2, 2, 4)
+    assert np.array_equal(got, np.concatenate([a.reshape(1, 2, 2, 3), b.reshape(1, 2, 2, 1)], axis=3))
+
+
+def test_detection_head_through_rank4(oracle, pkg, tmp_path):
+    """Convolution -> rank-4 Reshape -> Permute -> Sigmoid -> Slice -> Reshape -> Concat equals the same steps in numpy."""
+    param, bin_ = pkg.zoo.detection_head(str(tmp_path / "head"), h=6, w=5, cin=16, anchors=3, values=7)
+    x = np.random.default_rng(45).uniform(-1, 1, (16, 6, 5)).astype(F32)
+    m = oracle.Model(param, bin_)
+    raw = m.run([x], want=["raw"])[0]
+    got = m.run([x])[0]
+    cells = raw.reshape(3, 7, 6, 5).transpose(0, 2, 3, 1)
+    prob = m.run([x], want=["prob"])[0]
+    assert prob.shape == (3, 6, 5, 7)
+    assert np.allclose(prob, 1.0 / (1.0 + np.exp(-cells.astype(np.float64))), rtol=1e-6, atol=1e-7)
+    assert got.shape == (90, 7) and np.array_equal(got, prob.reshape(90, 7))
+
+
 # ------------------------------------------------------------------ broadcast, slice, shuffle, padding, interp
 def test_binary_broadcast_square_slice_shuffle(oracle):
     rng = np.random.default_rng(14)

@@ -29,6 +29,26 @@ def test_layers_without_blobs_are_refused_not_dereferenced(pkg, tmp_path, layer)
     assert err.value.status in (6, 8) and str(err.value)
 
 
+def test_rank4_shapes_are_planned_and_declared(pkg, tmp_path):
+    """Rank-4 results [c,d,h,w] of Reshape / Permute / Slice / Concat (the reference's permute_rank4, slice_rank4 and
+    concat_rank4 fixtures): shapes through the four-extent accessors, RANK 4 and DIM0..DIM3 in the emitted header,
+    and a loud refusal for layers that do not take rank-4 input."""
+    for name, shapes in (("permute_rank4", [(2, 2, 2, 3)]), ("slice_rank4", [(4, 1, 1, 2), (4, 1, 1, 4)]),
+                         ("concat_rank4", [(1, 2, 2, 4)])):
+        m = pkg.Model(*fixture(name), plan_only=True)
+        assert m.output_shapes == shapes
+        m.emit_stub(name, *fixture(name), str(tmp_path))
+        m.close()
+    header = (tmp_path / "permute_rank4.h").read_text()
+    assert "PERMUTE_RANK4_OUTPUT1_RANK 4" in header and "PERMUTE_RANK4_OUTPUT1_DIM3 INT64_C(3)" in header
+    assert "PERMUTE_RANK4_OUTPUT1_ELEMENTS" in header
+    param, bin_ = _write(tmp_path, "p", ["Input input 0 1 data 0=4 1=2 2=3", "Reshape r 1 1 data m 0=2 1=2 11=3 2=2",
+                                         "Pooling pool 1 1 m out 0=0 1=2"])
+    with pytest.raises(pkg.NcnnB200Error) as err:
+        pkg.Model(param, bin_, plan_only=True)
+    assert err.value.status == 8 and "rank-4" in str(err.value)
+
+
 def test_stub_escapes_quotes_and_backslashes_in_paths(pkg, tmp_path):
     param, bin_ = fixture("convolution")
     m = pkg.Model(param, bin_, plan_only=True)
